@@ -1,0 +1,301 @@
+/* omoknuni_b200.h — C ABI of the B200 (sm_100a) leaf-parallel evaluation path.
+ *
+ * Plain C: opaque handles, plain pointers and sizes, int status returns
+ * (0 = OK), no exceptions, no torch / libtorch types.  Every entry point cites
+ * the interface of the reference project (cosmosapjw-quantum/omoknuni_small,
+ * paths relative to that project's root) that it replaces.
+ *
+ * Two layers:
+ *   ob200_launch_*  raw launchers over caller-owned DEVICE memory, asynchronous
+ *                   on the given stream — the same shape as the reference's
+ *                   `extern "C" launch*Kernel` functions.
+ *   ob200_net_* / ob200_tree_*  handle-based calls that own their device
+ *                   buffers and take HOST buffers — what the reference's C++
+ *                   classes (NeuralNetwork, MCTSEngine) bind through the
+ *                   adapters in omoknuni_small_b200/adapter/.
+ *
+ * There is no CPU fallback: every call needs a CUDA device of compute
+ * capability 10.x and returns OB200_ERR_NO_DEVICE otherwise.
+ */
+#ifndef OMOKNUNI_B200_H
+#define OMOKNUNI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OB200_VERSION 1
+
+/* Status codes. */
+enum {
+    OB200_OK = 0,
+    OB200_ERR_INVALID = 1,     /* null pointer, bad size, bad enum            */
+    OB200_ERR_NO_DEVICE = 2,   /* no CUDA device / not compute capability 10  */
+    OB200_ERR_CUDA = 3,        /* a CUDA runtime call failed                  */
+    OB200_ERR_STATE = 4,       /* call order (weights not finalised, ...)     */
+    OB200_ERR_UNSUPPORTED = 5, /* shape outside what the kernels are built for*/
+    OB200_ERR_TIMEOUT = 6,     /* a bounded device-side wait ran out          */
+    OB200_ERR_TOO_LARGE = 7    /* size beyond a stated maximum                */
+};
+
+/* A CUDA stream handle (cudaStream_t) passed as an opaque pointer; NULL is the
+ * legacy default stream. */
+typedef void* ob200_stream;
+
+/* Thread-local text of the last error raised by a call on this thread. */
+const char* ob200_last_error(void);
+int ob200_version(void);
+/* Number of usable (compute capability 10.x) devices; 0 when none. */
+int ob200_device_count(void);
+
+/* ------------------------------------------------------------------------- *
+ *  Tree statistics: structure of arrays over (node, child slot) edges.
+ *
+ *  Replaces the dense libtorch tensors of GPUBatchEvaluator::TreeTensors
+ *  (include/mcts/gpu_batch_evaluator.h:116-133) and the per-child heap nodes
+ *  of MCTSNode (include/mcts/mcts_node.h:160-198).  Row r of every edge array
+ *  holds the child slots of node r; rows are `pitch` elements apart, pitch a
+ *  multiple of 4 so that rows start on 16-byte boundaries; slots in
+ *  [n_children, pitch) are padding and never selected.  Child slot order is
+ *  the tie-break order (lowest slot wins).
+ * ------------------------------------------------------------------------- */
+typedef struct ob200_tree_view {
+    int32_t* N;              /* [n_nodes][pitch] visit count of the child      */
+    float* W;                /* [n_nodes][pitch] value sum of the child        */
+    float* P;                /* [n_nodes][pitch] prior of the child            */
+    int32_t* VL;             /* [n_nodes][pitch] virtual-loss counter          */
+    uint32_t* legal_bits;    /* [n_nodes][mask_words] bit s = child slot s exists */
+    int32_t* node_visits;    /* [n_nodes] visit count of the node itself       */
+    int32_t* child_node;     /* [n_nodes][pitch] node id of the child, -1 = not
+                                expanded; may be NULL for flat selection       */
+    int32_t n_nodes;
+    int32_t n_children;      /* child slots per node (225, 362, 4672, ...)     */
+    int32_t pitch;           /* >= n_children, multiple of 4                   */
+    int32_t mask_words;      /* >= ceil(n_children / 32)                       */
+} ob200_tree_view;
+
+/* pitch / mask_words the kernels expect for a given child count. */
+int32_t ob200_tree_pitch(int32_t n_children);
+int32_t ob200_tree_mask_words(int32_t n_children);
+
+/* Batched PUCT child selection with virtual loss.
+ * Replaces MCTSNode::selectChild (src/mcts/mcts_node.cpp:90-236) + the
+ * applyVirtualLoss call that follows it in the search loop
+ * (src/mcts/mcts_engine_batch_tree_simple.cpp:102-111), and the launchers
+ * launchUCBKernel + launchPathSelectionKernel
+ * (src/mcts/gpu_batch_evaluator.cpp:9-33).
+ * For i in [0, n): node = node_ids ? node_ids[i] : i;
+ *   sel_out[i] = argmax over existing child slots of
+ *        q + u,  q = (N+VL > 0) ? (W - (float)VL) / (float)(N+VL) : 0
+ *                u = (P * (c_puct * sqrtf((float)node_visits))) / (1 + (float)(N+VL))
+ *   in IEEE fp32 with the reference's operation order; strict '>' so the
+ *   lowest slot wins ties; -1 when the node has no child slot; when no score
+ *   compares greater than -inf (all NaN / -inf) the least-visited slot, as
+ *   the reference's fallback does.
+ *   If apply_vl != 0 and vl_value > 0: atomically VL[node][sel] += vl_value.
+ * Distinct entries of node_ids may repeat; each sees the table as it was when
+ * it read it (entries of one launch are not ordered against each other). */
+int ob200_launch_puct_select(const ob200_tree_view* tree, const int32_t* node_ids, int32_t n,
+                             float c_puct, int32_t vl_value, int32_t apply_vl,
+                             int32_t* sel_out, ob200_stream stream);
+
+/* VL[node][sel] += vl_value for each i with sel[i] >= 0.
+ * Replaces MCTSNode::addVirtualLoss(int) (src/mcts/mcts_node_virtual_loss.cpp:15-20)
+ * and launchApplyVirtualLossKernelCuda (src/mcts/gpu_virtual_loss.cpp:10-20). */
+int ob200_launch_vl_apply(const ob200_tree_view* tree, const int32_t* node_ids,
+                          const int32_t* sel, int32_t n, int32_t vl_value, ob200_stream stream);
+
+/* old = VL; VL -= vl_value; if (old < vl_value) VL = 0   (clamp at zero).
+ * Replaces MCTSNode::removeVirtualLoss(int) (src/mcts/mcts_node_virtual_loss.cpp:32-42)
+ * and launchRemoveVirtualLossKernelCuda (src/mcts/gpu_virtual_loss.cpp:22-32). */
+int ob200_launch_vl_revert(const ob200_tree_view* tree, const int32_t* node_ids,
+                           const int32_t* sel, int32_t n, int32_t vl_value, ob200_stream stream);
+
+/* Backup along recorded paths.  paths[i][d] = (node, child slot) for
+ * d in [0, path_len[i]), root first, layout [n][max_depth][2] as the
+ * reference's selected_paths tensor.  Walking leaf -> root with
+ * v = leaf_values[i]: the edge gets N += 1, W += v, "VL -= 1 if VL > 0"
+ * (MCTSNode::update, src/mcts/mcts_node_virtual_loss.cpp:54-71) then the
+ * clamped VL -= vl_value (revertVirtualLoss), node_visits[node] += 1, and
+ * v = -v per ply (src/mcts/mcts_engine_batch_tree_simple.cpp:276-281).
+ * Replaces launchBackupKernel (src/mcts/gpu_batch_evaluator.cpp:35-46).
+ * leaf_values[i] is the value from the point of view of the player who made
+ * the last move on the path (the deepest edge receives +v). */
+int ob200_launch_backup(const ob200_tree_view* tree, const int32_t* paths,
+                        const int32_t* path_len, const float* leaf_values, int32_t n,
+                        int32_t max_depth, int32_t vl_value, ob200_stream stream);
+
+/* P[node][slot] = clamp(policy[i][action_of_slot[node][slot]], 0, 1) for the
+ * existing child slots of node_ids[i]; no renormalisation.
+ * Replaces MCTSNode::setPriorProbabilities (src/mcts/mcts_node.cpp:512-593).
+ * slot_action: [n_nodes][pitch] action id of each child slot, or NULL when
+ * slot == action.  policy: [n][policy_size] fp32 on the device. */
+int ob200_launch_set_priors(const ob200_tree_view* tree, const int32_t* node_ids, int32_t n,
+                            const float* policy, int32_t policy_size,
+                            const int32_t* slot_action, ob200_stream stream);
+
+/* Root-to-leaf descent, one simulation after another inside each tree, trees
+ * in parallel: sims_per_tree simulations from roots[t]; every step is the
+ * selection above followed by VL += vl_value on the chosen edge, so that
+ * simulation k sees the virtual loss of simulations < k of the same tree.
+ * Descent stops at an edge whose child_node is -1 (leaf to expand) or after
+ * max_depth steps.  paths_out [n_trees*sims_per_tree][max_depth][2],
+ * path_len_out [n_trees*sims_per_tree].
+ * Replaces phase 1 of MCTSEngine::executeBatchedTreeSearch
+ * (src/mcts/mcts_engine_batch_tree_simple.cpp:73-185) and
+ * launchTreeTraversalKernel (include/mcts/gpu_kernels.h:9-26). */
+int ob200_launch_traverse(const ob200_tree_view* tree, const int32_t* roots, int32_t n_trees,
+                          int32_t sims_per_tree, float c_puct, int32_t vl_value,
+                          int32_t max_depth, int32_t* paths_out, int32_t* path_len_out,
+                          ob200_stream stream);
+
+/* ------------------------------------------------------------------------- *
+ *  Board tensors: the activation format of the encoder and the network.
+ *
+ *  bf16, channels-last blocked by 8 ("NHWC8"): element (channel c, board b,
+ *  row y, column x) lives at
+ *        ((c / 8) * PT + G + b * slots + y * GP + x) * 8 + (c % 8)
+ *  with GP = board_size + 1 (one zero column after each row), slots = GP * GP
+ *  (one zero row after each board), G = OB200_GUARD zero positions before the
+ *  first and after the last board, and PT = 2 * G + roundup(B * slots, 128).
+ *  The zero column / row / guards are the 3x3 convolution's padding; every
+ *  producer writes them as zero.
+ * ------------------------------------------------------------------------- */
+#define OB200_GUARD 32
+/* Positions per channel block (PT above) for a batch of B boards. */
+int64_t ob200_board_tensor_positions(int32_t board_size, int32_t B);
+/* Bytes of a board tensor with `channels` channels (rounded up to 8). */
+int64_t ob200_board_tensor_bytes(int32_t board_size, int32_t B, int32_t channels);
+
+/* Gomoku state -> input planes, written as a bf16 board tensor of
+ * `out_channels` (a multiple of 8, >= planes) channels.
+ * Replaces GomokuState::getEnhancedTensorRepresentation
+ * (src/games/gomoku/gomoku_state.cpp:210-372), the attack/defense planes of
+ * GomokuAttackDefenseModule::compute_planes (src/utils/attack_defense_module.cpp:61-111)
+ * and the batching copy of ResNetModel::prepareInputTensor
+ * (src/nn/resnet_model.cpp:240-576).
+ *   history[b][k], k in [0, n_hist[b]) : the k-th most recent move (k = 0 is
+ *       the last move played), action = row * board_size + col; n_hist <= 16.
+ *   to_move[b] : 1 = BLACK, 2 = WHITE.
+ *   planes : 17 or 19.  Plane 2i = the side to move's i-th most recent stone,
+ *       plane 2i+1 = the opponent's i-th most recent stone (one stone per
+ *       plane), plane 16 = all ones iff BLACK is to move, planes 17/18 = the
+ *       attack / defense planes, which the reference's CPU code computes as
+ *       zero for every legal move (it scores the board without the candidate
+ *       stone against itself).
+ * All pointers are device pointers. */
+int ob200_launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist,
+                               const uint8_t* to_move, int32_t B, int32_t board_size,
+                               int32_t planes, int32_t out_channels, void* board_tensor_out,
+                               ob200_stream stream);
+
+/* fp32 planes [B][C][S][S] (NCHW, device) -> bf16 board tensor of out_channels
+ * channels; channels >= C are zero.  The reference feeds such planes from
+ * IGameState::getTensorRepresentation / getEnhancedTensorRepresentation
+ * (include/core/igamestate.h:141,151) through prepareInputTensor. */
+int ob200_launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C,
+                                        int32_t board_size, int32_t out_channels,
+                                        void* board_tensor_out, ob200_stream stream);
+
+/* One 3x3 convolution layer (padding 1, stride 1) on board tensors with the
+ * BatchNorm already folded into weight and bias:
+ *   out = act(conv3x3(in, w) + bias [+ residual]),  act = ReLU if relu != 0.
+ * Replaces one conv + BatchNorm2d + relu (+ residual add) group of
+ * ResNetResidualBlock::forward / ResNetModel::forward
+ * (src/nn/resnet_model.cpp:43-49,150).  `packed_w` comes from
+ * ob200_pack_conv3x3_weights.  in: cin channels (multiple of 16), out and
+ * residual: cout channels; cout must be 64 in this build. */
+int ob200_launch_conv3x3(const void* in, const void* packed_w, const float* bias,
+                         const void* residual, void* out, int32_t B, int32_t board_size,
+                         int32_t cin, int32_t cout, int32_t relu, ob200_stream stream);
+/* Bytes of the packed bf16 weight image for (cin, cout). */
+int64_t ob200_packed_conv3x3_bytes(int32_t cin, int32_t cout);
+/* Host helper: fp32 OIHW weights [cout][cin_real][3][3] scaled per output
+ * channel by scale[cout] (the folded BatchNorm factor; NULL = 1) -> packed
+ * bf16 image for cin >= cin_real input channels (extra channels get zero
+ * weights).  Output is HOST memory of ob200_packed_conv3x3_bytes(cin, cout). */
+int ob200_pack_conv3x3_weights(const float* w_oihw, const float* scale, int32_t cout,
+                               int32_t cin_real, int32_t cin, void* packed_out);
+
+/* ------------------------------------------------------------------------- *
+ *  Network handle: the residual policy/value network.
+ *  Replaces alphazero::nn::ResNetModel behind NeuralNetwork::inference
+ *  (include/nn/neural_network.h:28-29, src/nn/resnet_model.cpp:51-237,594-811).
+ * ------------------------------------------------------------------------- */
+typedef struct ob200_net ob200_net;
+
+typedef struct ob200_net_config {
+    int32_t board_size;       /* S: 15 for Gomoku                              */
+    int32_t input_channels;   /* C_in of the stem (17, 19, 3, ...)             */
+    int32_t filters;          /* tower width; 64 in this build                 */
+    int32_t blocks;           /* residual blocks                               */
+    int32_t policy_size;      /* A: policy outputs                             */
+    int32_t policy_head_ch;   /* channels of the policy 1x1 conv (reference 32)*/
+    int32_t value_head_ch;    /* channels of the value 1x1 conv (reference 32) */
+    int32_t value_hidden;     /* width of value_fc1 (reference 256)            */
+    int32_t max_batch;        /* largest batch any call will pass              */
+    int32_t device;           /* CUDA device ordinal                           */
+} ob200_net_config;
+
+int ob200_net_create(const ob200_net_config* cfg, ob200_net** out);
+void ob200_net_destroy(ob200_net* net);
+
+/* Weights enter under the reference module's parameter / buffer names
+ * (src/nn/resnet_model.cpp:51-102): "input_conv.weight",
+ * "input_bn.{weight,bias,running_mean,running_var}",
+ * "res_blocks.<i>.{conv1,bn1,conv2,bn2}.*", "policy_conv.weight", "policy_bn.*",
+ * "policy_fc.{weight,bias}", "value_conv.weight", "value_bn.*",
+ * "value_fc1.{weight,bias}", "value_fc2.{weight,bias}"; fp32, the layout
+ * libtorch stores (OIHW / [out][in]).  "*.num_batches_tracked" is accepted and
+ * ignored.  Replaces ResNetModel::load (src/nn/resnet_model.cpp:836-857) at
+ * the level of tensors. */
+int ob200_net_set_tensor(ob200_net* net, const char* name, const float* data, int64_t numel);
+/* Folds BatchNorm (eps 1e-5) into the convolutions, rounds tower weights to
+ * bf16, permutes what needs permuting and uploads.  Fails with OB200_ERR_STATE
+ * naming the first tensor that was never set. */
+int ob200_net_finalize(ob200_net* net);
+
+#define OB200_OUT_PROBS 0   /* policy_out = softmax probabilities (what
+                               ResNetModel::inference returns, :752)          */
+#define OB200_OUT_LOGITS 1  /* policy_out = policy_fc outputs before softmax  */
+
+/* HOST in, HOST out.  planes: fp32 [B][C][S][S]; as ResNetModel::forward does
+ * (src/nn/resnet_model.cpp:117-147) the first min(C, input_channels) planes
+ * are used and missing ones are zero.  policy_out [B][A], value_out [B]. */
+int ob200_net_infer_planes(ob200_net* net, const float* planes, int32_t B, int32_t C,
+                           float* policy_out, float* value_out, int32_t out_kind);
+/* HOST in, HOST out, Gomoku states given as move histories (see
+ * ob200_launch_encode_gomoku): encode -> tower -> heads in one call.  This is
+ * the call behind NeuralNetwork::inference for Gomoku states. */
+int ob200_net_infer_gomoku(ob200_net* net, const int16_t* history, const uint8_t* n_hist,
+                           const uint8_t* to_move, int32_t B, float* policy_out,
+                           float* value_out, int32_t out_kind);
+/* DEVICE in, DEVICE out, asynchronous on `stream`: input is a board tensor of
+ * roundup(input_channels, 16) channels for B boards. */
+int ob200_net_forward_device(ob200_net* net, const void* input_board_tensor, int32_t B,
+                             float* policy_out, float* value_out, int32_t out_kind,
+                             ob200_stream stream);
+/* Device pointer of the tower's output board tensor of the last forward
+ * (filters channels), for tests. */
+const void* ob200_net_debug_tower_output(ob200_net* net);
+
+/* Per-device counters for the end-of-run reduction (the only cross-GPU step;
+ * it replaces the MCTSStats fields total_evaluations / total_batches_processed,
+ * include/mcts/mcts_engine.h:154-197). */
+typedef struct ob200_counters {
+    uint64_t evals;            /* positions evaluated by the network          */
+    uint64_t batches;          /* network calls                               */
+    uint64_t selections;       /* node selections made                        */
+    uint64_t backups;          /* paths backed up                             */
+    uint64_t kernel_launches;  /* kernels of this library launched            */
+} ob200_counters;
+int ob200_get_counters(ob200_counters* out);   /* this process, all handles   */
+void ob200_reset_counters(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OMOKNUNI_B200_H */

@@ -1,0 +1,300 @@
+"""ctypes bindings of the oracle libraries (test infrastructure).
+
+liboracle.so       plain-C restatement (oracle/oracle.c), always buildable.
+_ref/libref_tree.so  the reference's MCTSNode / GomokuState compiled from its
+                     own sources (oracle/ref_shim_tree.cpp), when present.
+_ref/libref_net.so   the reference's ResNetModel on libtorch CPU
+                     (oracle/ref_shim_net.cpp), when present.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_i32 = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+_f32 = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+_u32 = np.ctypeslib.ndpointer(np.uint32, flags="C_CONTIGUOUS")
+_i16 = np.ctypeslib.ndpointer(np.int16, flags="C_CONTIGUOUS")
+_u8 = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+_i64 = np.ctypeslib.ndpointer(np.int64, flags="C_CONTIGUOUS")
+
+
+def _opt(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def build():
+    """Compile liboracle.so (and oracle/_ref when the reference checkout exists)."""
+    subprocess.run(["make", "-C", _HERE, "-j8"], check=True, stdout=subprocess.DEVNULL)
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            subprocess.run(["make", "-C", _HERE, "liboracle.so"], check=True, stdout=subprocess.DEVNULL)
+        L = C.CDLL(path)
+        L.oracle_puct_select.argtypes = [_i32, _f32, _f32, _i32, _u32, _i32, C.c_int, C.c_int, C.c_int,
+                                         C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_int, _i32, C.c_int]
+        L.oracle_vl_apply.argtypes = [_i32, C.c_int, C.c_void_p, _i32, C.c_int, C.c_int]
+        L.oracle_vl_revert.argtypes = [_i32, C.c_int, C.c_void_p, _i32, C.c_int, C.c_int]
+        L.oracle_vl_ops.argtypes = [C.c_int, _i32, C.c_int, _i32]
+        L.oracle_backup.argtypes = [_i32, _f32, _i32, _i32, C.c_void_p, C.c_int, _i32, _i32, _f32, C.c_int,
+                                    C.c_int, C.c_int]
+        L.oracle_set_priors.argtypes = [_f32, _u32, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, _f32,
+                                        C.c_int, C.c_void_p]
+        L.oracle_traverse.argtypes = [_i32, _f32, _f32, _i32, _u32, _i32, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                      C.c_int, _i32, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, _i32, _i32]
+        L.oracle_gomoku_encode_batch.argtypes = [_i16, _u8, _u8, C.c_int, C.c_int, C.c_int, _f32, C.c_int]
+        _lib = L
+    return _lib
+
+
+# ---- plain-C restatement -----------------------------------------------------
+def puct_select(tree, node_ids=None, c_puct=1.5, vl_value=3, apply_vl=False, threads=0):
+    """tree: dict of numpy arrays N, W, P, VL [n_nodes, pitch], legal_bits
+    [n_nodes, mask_words], node_visits [n_nodes], n_children.  VL is updated in
+    place when apply_vl."""
+    n_nodes, pitch = tree["N"].shape
+    ids = None if node_ids is None else np.ascontiguousarray(node_ids, np.int32)
+    n = n_nodes if ids is None else len(ids)
+    sel = np.empty(n, np.int32)
+    lib().oracle_puct_select(tree["N"], tree["W"], tree["P"], tree["VL"], tree["legal_bits"],
+                             tree["node_visits"], tree["n_children"], pitch, tree["legal_bits"].shape[1],
+                             _opt(ids), n, c_puct, vl_value, int(apply_vl), sel, threads)
+    return sel
+
+
+def vl_apply(tree, sel, vl_value, node_ids=None):
+    ids = None if node_ids is None else np.ascontiguousarray(node_ids, np.int32)
+    lib().oracle_vl_apply(tree["VL"], tree["VL"].shape[1], _opt(ids), np.ascontiguousarray(sel, np.int32),
+                          len(sel), vl_value)
+
+
+def vl_revert(tree, sel, vl_value, node_ids=None):
+    ids = None if node_ids is None else np.ascontiguousarray(node_ids, np.int32)
+    lib().oracle_vl_revert(tree["VL"], tree["VL"].shape[1], _opt(ids), np.ascontiguousarray(sel, np.int32),
+                           len(sel), vl_value)
+
+
+def vl_ops(initial, ops):
+    ops = np.ascontiguousarray(ops, np.int32)
+    out = np.empty(len(ops), np.int32)
+    lib().oracle_vl_ops(initial, ops, len(ops), out)
+    return out
+
+
+def backup(tree, paths, path_len, leaf_values, vl_value):
+    paths = np.ascontiguousarray(paths, np.int32)
+    n, max_depth, _ = paths.shape
+    cn = tree.get("child_node")
+    lib().oracle_backup(tree["N"], tree["W"], tree["VL"], tree["node_visits"], _opt(cn), tree["N"].shape[1],
+                        paths, np.ascontiguousarray(path_len, np.int32),
+                        np.ascontiguousarray(leaf_values, np.float32), n, max_depth, vl_value)
+
+
+def set_priors(tree, node_ids, policy, slot_action=None):
+    ids = None if node_ids is None else np.ascontiguousarray(node_ids, np.int32)
+    policy = np.ascontiguousarray(policy, np.float32)
+    sa = None if slot_action is None else np.ascontiguousarray(slot_action, np.int32)
+    lib().oracle_set_priors(tree["P"], tree["legal_bits"], tree["n_children"], tree["P"].shape[1],
+                            tree["legal_bits"].shape[1], _opt(ids), policy.shape[0], policy, policy.shape[1],
+                            _opt(sa))
+
+
+def traverse(tree, roots, sims_per_tree, c_puct, vl_value, max_depth):
+    roots = np.ascontiguousarray(roots, np.int32)
+    n = len(roots) * sims_per_tree
+    paths = np.zeros((n, max_depth, 2), np.int32)
+    plen = np.zeros(n, np.int32)
+    n_nodes, pitch = tree["N"].shape
+    lib().oracle_traverse(tree["N"], tree["W"], tree["P"], tree["VL"], tree["legal_bits"], tree["node_visits"],
+                          _opt(tree.get("child_node")), n_nodes, tree["n_children"], pitch,
+                          tree["legal_bits"].shape[1], roots, len(roots), sims_per_tree, c_puct, vl_value,
+                          max_depth, paths, plen)
+    return paths, plen
+
+
+def gomoku_encode(history, n_hist, to_move, board_size=15, planes=19, threads=0):
+    """history [B,16] int16 (k-th most recent move), n_hist [B] u8, to_move [B] u8
+    -> planes [B, planes, S, S] fp32."""
+    history = np.ascontiguousarray(history, np.int16)
+    B = history.shape[0]
+    out = np.empty((B, planes, board_size, board_size), np.float32)
+    lib().oracle_gomoku_encode_batch(history, np.ascontiguousarray(n_hist, np.uint8),
+                                     np.ascontiguousarray(to_move, np.uint8), B, board_size, planes, out, threads)
+    return out
+
+
+# ---- the reference's own classes (oracle/_ref) --------------------------------
+_ref_tree = None
+_ref_net = None
+
+
+def ref_tree_path():
+    return os.path.join(_HERE, "_ref", "libref_tree.so")
+
+
+def ref_net_path():
+    return os.path.join(_HERE, "_ref", "libref_net.so")
+
+
+def have_ref_tree():
+    return os.path.exists(ref_tree_path())
+
+
+def have_ref_net():
+    return os.path.exists(ref_net_path())
+
+
+def ref_tree():
+    global _ref_tree
+    if _ref_tree is None:
+        L = C.CDLL(ref_tree_path())
+        L.ref_select_child.argtypes = [C.c_int, _i32, _f32, _f32, _i32, C.c_int, C.c_float]
+        L.ref_select_batch.restype = C.c_double
+        L.ref_select_batch.argtypes = [C.c_int, _i64, _i32, _f32, _f32, _i32, _i32, C.c_float, C.c_int, _i32,
+                                       C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+        L.ref_vl_ops.argtypes = [C.c_int, _i32, C.c_int, _i32]
+        L.ref_backup_path.argtypes = [C.c_int, _i32, _f32, _i32, C.c_float, C.c_int, _f32]
+        L.ref_gomoku_encode.argtypes = [C.c_int, _i32, C.c_int, C.c_void_p, C.c_void_p]
+        L.ref_gomoku_encode_batch.restype = C.c_double
+        L.ref_gomoku_encode_batch.argtypes = [C.c_int, C.c_int, _i64, _i32, _f32, C.c_int]
+        _ref_tree = L
+    return _ref_tree
+
+
+def compact_rows(tree, node_ids=None):
+    """Existing child slots only, as the reference's children_ vectors hold them.
+    Returns row_ptr, N, W, P, VL (compacted), slot index of each compacted child,
+    node_visits per selected node."""
+    n_nodes, pitch = tree["N"].shape
+    ids = np.arange(n_nodes) if node_ids is None else np.asarray(node_ids)
+    nc = tree["n_children"]
+    bits = np.unpackbits(tree["legal_bits"][ids].view(np.uint8), axis=1, bitorder="little")[:, :nc].astype(bool)
+    counts = bits.sum(1)
+    row_ptr = np.zeros(len(ids) + 1, np.int64)
+    np.cumsum(counts, out=row_ptr[1:])
+    rows, slots = np.nonzero(bits)
+    g = ids[rows]
+    return (row_ptr, np.ascontiguousarray(tree["N"][g, slots]), np.ascontiguousarray(tree["W"][g, slots]),
+            np.ascontiguousarray(tree["P"][g, slots]), np.ascontiguousarray(tree["VL"][g, slots]),
+            slots.astype(np.int32), np.ascontiguousarray(tree["node_visits"][ids]))
+
+
+def ref_select(tree, node_ids=None, c_puct=1.5, vl_value=3, repeats=1, threads=0):
+    """Real MCTSNode::selectChild + applyVirtualLoss + revertVirtualLoss per node.
+    Returns (slot per node, VL after apply, VL after revert, seconds)."""
+    row_ptr, N, W, P, VL, slots, nv = compact_rows(tree, node_ids)
+    n = len(row_ptr) - 1
+    sel_c = np.full(n, -1, np.int32)
+    a = np.zeros(n, np.int32)
+    r = np.zeros(n, np.int32)
+    secs = ref_tree().ref_select_batch(n, row_ptr, N, W, P, VL, nv, c_puct, vl_value, sel_c,
+                                       a.ctypes.data_as(C.c_void_p), r.ctypes.data_as(C.c_void_p), repeats, threads)
+    sel = np.where(sel_c >= 0, slots[np.minimum(row_ptr[:-1] + np.maximum(sel_c, 0), len(slots) - 1)] if len(slots) else -1, -1)
+    return sel.astype(np.int32), a, r, secs
+
+
+def ref_vl_ops(initial, ops):
+    ops = np.ascontiguousarray(ops, np.int32)
+    out = np.empty(len(ops), np.int32)
+    ref_tree().ref_vl_ops(initial, ops, len(ops), out)
+    return out
+
+
+def ref_backup_path(N, W, VL, leaf_value, vl_value):
+    N = np.ascontiguousarray(N, np.int32).copy()
+    VL = np.ascontiguousarray(VL, np.int32).copy()
+    W = np.ascontiguousarray(W, np.float32)
+    mean = np.zeros(len(N), np.float32)
+    ref_tree().ref_backup_path(len(N), N, W, VL, leaf_value, vl_value, mean)
+    return N, VL, mean
+
+
+def ref_gomoku_planes(moves, board_size=15):
+    """Play `moves` on the reference's GomokuState; returns (planes19, planes3, to_move)."""
+    mv = np.ascontiguousarray(moves, np.int32)
+    p19 = np.zeros((19, board_size, board_size), np.float32)
+    p3 = np.zeros((3, board_size, board_size), np.float32)
+    tm = ref_tree().ref_gomoku_encode(board_size, mv, len(mv), p19.ctypes.data_as(C.c_void_p),
+                                      p3.ctypes.data_as(C.c_void_p))
+    if tm < 0:
+        raise ValueError("illegal move in list")
+    return p19, p3, tm
+
+
+def ref_gomoku_encode_batch(move_lists, board_size=15, threads=0):
+    row_ptr = np.zeros(len(move_lists) + 1, np.int64)
+    np.cumsum([len(m) for m in move_lists], out=row_ptr[1:])
+    flat = np.ascontiguousarray(np.concatenate([np.asarray(m, np.int32) for m in move_lists]) if row_ptr[-1] else np.zeros(0, np.int32))
+    out = np.zeros((len(move_lists), 19, board_size, board_size), np.float32)
+    secs = ref_tree().ref_gomoku_encode_batch(board_size, len(move_lists), row_ptr, flat, out, threads)
+    return out, secs
+
+
+class RefNet:
+    """The reference's alphazero::nn::ResNetModel (libtorch, CPU, fp32)."""
+
+    def __init__(self, in_ch, board, blocks, filters, policy, seed=0):
+        global _ref_net
+        if _ref_net is None:
+            L = C.CDLL(ref_net_path())
+            L.ref_net_create.restype = C.c_void_p
+            L.ref_net_create.argtypes = [C.c_int] * 5 + [C.c_uint64]
+            L.ref_net_destroy.argtypes = [C.c_void_p]
+            L.ref_net_names.restype = C.c_int64
+            L.ref_net_names.argtypes = [C.c_void_p, C.c_char_p, C.c_int64]
+            L.ref_net_get.restype = C.c_int64
+            L.ref_net_get.argtypes = [C.c_void_p, C.c_char_p, _f32, C.c_int64]
+            L.ref_net_set.restype = C.c_int64
+            L.ref_net_set.argtypes = [C.c_void_p, C.c_char_p, _f32, C.c_int64]
+            L.ref_net_forward.restype = C.c_double
+            L.ref_net_forward.argtypes = [C.c_void_p, _f32, C.c_int, C.c_int, _f32, _f32, C.c_int, C.c_int]
+            _ref_net = L
+        self.L = _ref_net
+        self.board, self.policy, self.in_ch = board, policy or board * board, in_ch
+        self.h = self.L.ref_net_create(in_ch, board, blocks, filters, policy, seed)
+        if not self.h:
+            raise RuntimeError("reference ResNetModel could not be constructed")
+
+    def names(self):
+        buf = C.create_string_buffer(1 << 20)
+        self.L.ref_net_names(self.h, buf, len(buf))
+        return [(l.split()[0], int(l.split()[1])) for l in buf.value.decode().splitlines()]
+
+    def state(self):
+        out = {}
+        for name, numel in self.names():
+            a = np.empty(numel, np.float32)
+            self.L.ref_net_get(self.h, name.encode(), a, numel)
+            out[name] = a
+        return out
+
+    def set(self, name, arr):
+        a = np.ascontiguousarray(arr, np.float32).ravel()
+        if self.L.ref_net_set(self.h, name.encode(), a, a.size) != a.size:
+            raise KeyError(f"{name}: unknown or size mismatch")
+
+    def forward(self, x, threads=0, repeats=1):
+        """x [B,C,S,S] fp32 -> (log-softmax policy [B,A], value [B], seconds per forward)."""
+        x = np.ascontiguousarray(x, np.float32)
+        B, Cc = x.shape[:2]
+        lp = np.empty((B, self.policy), np.float32)
+        v = np.empty(B, np.float32)
+        secs = self.L.ref_net_forward(self.h, x, B, Cc, lp, v, threads, repeats)
+        if secs < 0:
+            raise RuntimeError("reference forward failed")
+        return lp, v, secs
+
+    def __del__(self):
+        try:
+            self.L.ref_net_destroy(self.h)
+        except Exception:
+            pass

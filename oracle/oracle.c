@@ -1,0 +1,231 @@
+/* TEST INFRASTRUCTURE — not part of the product.
+ *
+ * Plain-C CPU restatement of the reference project's algorithms for the
+ * leaf-parallel evaluation path (cosmosapjw-quantum/omoknuni_small; file:line
+ * below are paths inside that project).  Only tests/, the smoke check and the
+ * benchmark's CPU-baseline leg load this library; the product never does.
+ *
+ * Pinned against the reference's own classes compiled from its sources
+ * (oracle/_ref, see oracle/Makefile) by tests/golden/make_golden.py and
+ * tests/test_oracle_vs_reference.py, and against the known-answer cases of
+ * the reference's unit tests (tests/mcts/mcts_node_test.cpp:237-298,
+ * tests/mcts/virtual_loss_test.cpp:160-224,282-308).
+ *
+ * Compile with -ffp-contract=off: the reference is built without FMA
+ * contraction (x86-64 baseline, -O3), and selection compares fp32 scores.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+#include <limits.h>
+#include <omp.h>
+
+/* MCTSNode::selectChild, src/mcts/mcts_node.cpp:90-236 (RAVE off, no child
+ * pending evaluation), over flat arrays.  Child slots whose legal bit is 0 do
+ * not exist.  Returns the slot, or -1 for a node without children.  The
+ * reference runs its scan twice with identical results; once is enough. */
+static int select_row(const int32_t* N, const float* W, const float* P, const int32_t* VL,
+                      const uint32_t* legal, int n_children, int n_parent, float c_puct) {
+    float best = -INFINITY;
+    int best_i = -1;
+    /* :94-95  exploration_param = c * sqrt((float)visit_count) */
+    const float explore = c_puct * sqrtf((float)n_parent);
+    int have = 0, min_n = INT_MAX, min_i = -1;
+    for (int i = 0; i < n_children; ++i) {
+        if (!((legal[i >> 5] >> (i & 31)) & 1u)) continue;
+        have = 1;
+        const int ev = N[i] + VL[i];                          /* :147 */
+        const float val = W[i] - (float)VL[i];                /* :148 */
+        const float q = ev > 0 ? val / (float)ev : 0.0f;      /* :151-152 */
+        const float u = P[i] * explore / (1.0f + (float)ev);  /* :154-155 */
+        const float s = q + u;                                /* :157 */
+        if (s > best) { best = s; best_i = i; }               /* :160 strict */
+        if (N[i] < min_n) { min_n = N[i]; min_i = i; }        /* :173-181 fallback */
+    }
+    if (best_i < 0 && have) return min_i;
+    return best_i;
+}
+
+void oracle_puct_select(const int32_t* N, const float* W, const float* P, int32_t* VL,
+                        const uint32_t* legal, const int32_t* node_visits, int n_children,
+                        int pitch, int mask_words, const int32_t* node_ids, int n, float c_puct,
+                        int vl_value, int apply_vl, int32_t* sel_out, int threads) {
+    if (threads > 0) omp_set_num_threads(threads);
+#pragma omp parallel for schedule(static) if (!apply_vl || !node_ids)
+    for (int i = 0; i < n; ++i) {
+        const int node = node_ids ? node_ids[i] : i;
+        const size_t r = (size_t)node * pitch;
+        const int s = select_row(N + r, W + r, P + r, VL + r, legal + (size_t)node * mask_words,
+                                 n_children, node_visits[node], c_puct);
+        sel_out[i] = s;
+        /* applyVirtualLoss on the selected child, mcts_engine_batch_tree_simple.cpp:111;
+         * addVirtualLoss ignores amount <= 0, mcts_node_virtual_loss.cpp:15-20 */
+        if (s >= 0 && apply_vl && vl_value > 0) VL[r + s] += vl_value;
+    }
+}
+
+/* MCTSNode::addVirtualLoss(int), src/mcts/mcts_node_virtual_loss.cpp:15-20 */
+void oracle_vl_apply(int32_t* VL, int pitch, const int32_t* node_ids, const int32_t* sel, int n,
+                     int vl_value) {
+    if (vl_value <= 0) return;
+    for (int i = 0; i < n; ++i) {
+        const int node = node_ids ? node_ids[i] : i;
+        if (sel[i] >= 0) VL[(size_t)node * pitch + sel[i]] += vl_value;
+    }
+}
+
+/* MCTSNode::removeVirtualLoss(int), src/mcts/mcts_node_virtual_loss.cpp:32-42 */
+static void remove_vl(int32_t* vl, int amount) {
+    if (amount <= 0) return;
+    const int cur = *vl;
+    *vl = cur - amount;
+    if (cur < amount) *vl = 0;
+}
+/* MCTSNode::removeVirtualLoss(), :22-30 */
+static void remove_vl_one(int32_t* vl) {
+    const int cur = *vl;
+    *vl = cur - 1;
+    if (cur <= 0) *vl = 0;
+}
+
+void oracle_vl_revert(int32_t* VL, int pitch, const int32_t* node_ids, const int32_t* sel, int n,
+                      int vl_value) {
+    for (int i = 0; i < n; ++i) {
+        const int node = node_ids ? node_ids[i] : i;
+        if (sel[i] >= 0) remove_vl(&VL[(size_t)node * pitch + sel[i]], vl_value);
+    }
+}
+
+/* A sequence of operations on one counter (op > 0 add, op < 0 remove(-op),
+ * op == 0 the argument-less remove); out[i] = counter after operation i. */
+void oracle_vl_ops(int initial, const int32_t* ops, int n_ops, int32_t* out) {
+    int32_t vl = 0;
+    if (initial > 0) vl += initial;
+    for (int i = 0; i < n_ops; ++i) {
+        if (ops[i] > 0) vl += ops[i];
+        else if (ops[i] < 0) remove_vl(&vl, -ops[i]);
+        else remove_vl_one(&vl);
+        out[i] = vl;
+    }
+}
+
+/* Backup: MCTSNode::update (src/mcts/mcts_node_virtual_loss.cpp:54-71) followed
+ * by revertVirtualLoss and the sign flip, per path node from leaf to root
+ * (src/mcts/mcts_engine_batch_tree_simple.cpp:276-281), on edge statistics.
+ * paths[i][d] = (node, slot), root first.  Paths are applied in index order. */
+void oracle_backup(int32_t* N, float* W, int32_t* VL, int32_t* node_visits,
+                   const int32_t* child_node, int pitch, const int32_t* paths,
+                   const int32_t* path_len, const float* leaf_values, int n, int max_depth,
+                   int vl_value) {
+    for (int i = 0; i < n; ++i) {
+        int len = path_len[i] > max_depth ? max_depth : path_len[i];
+        float v = leaf_values[i];
+        const int32_t* p = paths + (size_t)i * max_depth * 2;
+        for (int d = len - 1; d >= 0; --d) {
+            const size_t e = (size_t)p[2 * d] * pitch + p[2 * d + 1];
+            N[e] += 1;                         /* visit_count_.fetch_add(1) */
+            W[e] = W[e] + v;                   /* value_sum_ CAS loop       */
+            if (VL[e] > 0) remove_vl_one(&VL[e]);
+            remove_vl(&VL[e], vl_value);       /* revertVirtualLoss(vl)     */
+            if (d == len - 1 && child_node && child_node[e] >= 0) node_visits[child_node[e]] += 1;
+            node_visits[p[2 * d]] += 1;
+            v = -v;
+        }
+    }
+}
+
+/* MCTSNode::setPriorProbabilities, src/mcts/mcts_node.cpp:512-593: the prior of
+ * a child is the policy entry of its action clamped to [0, 1] (:546-553), 0.01
+ * for an action outside the policy (:559), no renormalisation. */
+void oracle_set_priors(float* P, const uint32_t* legal, int n_children, int pitch, int mask_words,
+                       const int32_t* node_ids, int n, const float* policy, int policy_size,
+                       const int32_t* slot_action) {
+    for (int i = 0; i < n; ++i) {
+        const int node = node_ids ? node_ids[i] : i;
+        const size_t r = (size_t)node * pitch;
+        const uint32_t* m = legal + (size_t)node * mask_words;
+        for (int s = 0; s < pitch; ++s) {
+            float p = 0.0f;
+            if (s < n_children && ((m[s >> 5] >> (s & 31)) & 1u)) {
+                const int a = slot_action ? slot_action[r + s] : s;
+                if (a >= 0 && a < policy_size) {
+                    p = policy[(size_t)i * policy_size + a];
+                    p = fminf(1.0f, fmaxf(0.0f, p));
+                } else {
+                    p = 0.01f;
+                }
+            }
+            P[r + s] = p;
+        }
+    }
+}
+
+/* Phase 1 of MCTSEngine::executeBatchedTreeSearch
+ * (src/mcts/mcts_engine_batch_tree_simple.cpp:85-166) with a defined order:
+ * the simulations of one tree run one after another, each selecting with the
+ * virtual loss left by the earlier ones and adding vl_value to the edge it
+ * takes; the descent ends at an unexpanded edge (child_node < 0), at a node
+ * without children, or after max_depth steps. */
+void oracle_traverse(const int32_t* N, const float* W, const float* P, int32_t* VL,
+                     const uint32_t* legal, const int32_t* node_visits, const int32_t* child_node,
+                     int n_nodes, int n_children, int pitch, int mask_words, const int32_t* roots,
+                     int n_trees, int sims_per_tree, float c_puct, int vl_value, int max_depth,
+                     int32_t* paths_out, int32_t* path_len_out) {
+    for (int t = 0; t < n_trees; ++t) {
+        for (int k = 0; k < sims_per_tree; ++k) {
+            const size_t sim = (size_t)t * sims_per_tree + k;
+            int32_t* path = paths_out + sim * max_depth * 2;
+            int node = roots[t], depth = 0;
+            while (depth < max_depth && node >= 0 && node < n_nodes) {
+                const size_t r = (size_t)node * pitch;
+                const int s = select_row(N + r, W + r, P + r, VL + r,
+                                         legal + (size_t)node * mask_words, n_children,
+                                         node_visits[node], c_puct);
+                if (s < 0) break;
+                if (vl_value > 0) VL[r + s] += vl_value;
+                path[2 * depth] = node;
+                path[2 * depth + 1] = s;
+                ++depth;
+                node = child_node ? child_node[r + s] : -1;
+            }
+            path_len_out[sim] = depth;
+        }
+    }
+}
+
+/* GomokuState::getEnhancedTensorRepresentation,
+ * src/games/gomoku/gomoku_state.cpp:210-372, from the move history.
+ * history[k] = k-th most recent move (k = 0 newest).  Move k is the
+ * opponent's when k is even (:228-230) and the side to move's when k is odd
+ * (:231-233); the side to move's i-th most recent move sets plane 2i
+ * (:238-245), the opponent's sets plane 2i+1 (:247-254), i < 8.  Plane 16 is
+ * 1.0 everywhere iff BLACK (1) is to move (:257-262).  Planes 17/18 come from
+ * GomokuAttackDefenseModule::compute_planes
+ * (src/utils/attack_defense_module.cpp:61-111): for every legal (empty) cell
+ * the "before" board of compute_attack_bonus/compute_defense_bonus (:113-154,
+ * :156-203) only clears an already empty cell, so after == before and both
+ * planes are zero.  out: [planes][S][S] fp32, planes = 17 or 19. */
+void oracle_gomoku_encode(const int16_t* history, int n_hist, int to_move, int S, int planes,
+                          float* out) {
+    memset(out, 0, sizeof(float) * (size_t)planes * S * S);
+    for (int k = 0; k < n_hist && k < 16; ++k) {
+        const int a = history[k];
+        const int r = a / S, c = a % S;
+        if (a < 0 || r >= S) continue;
+        const int i = k / 2;
+        const int plane = (k & 1) ? 2 * i : 2 * i + 1;
+        if (plane < 16) out[((size_t)plane * S + r) * S + c] = 1.0f;
+    }
+    if (planes > 16 && to_move == 1)
+        for (int j = 0; j < S * S; ++j) out[(size_t)16 * S * S + j] = 1.0f;
+}
+
+void oracle_gomoku_encode_batch(const int16_t* history, const uint8_t* n_hist,
+                                const uint8_t* to_move, int B, int S, int planes, float* out,
+                                int threads) {
+    if (threads > 0) omp_set_num_threads(threads);
+#pragma omp parallel for schedule(static)
+    for (int b = 0; b < B; ++b)
+        oracle_gomoku_encode(history + (size_t)b * 16, n_hist[b], to_move[b], S, planes,
+                             out + (size_t)b * planes * S * S);
+}

@@ -1,0 +1,244 @@
+// TEST INFRASTRUCTURE — not part of the product.
+//
+// C entry points that drive the reference project's *own* classes, compiled
+// from the reference's source files where they lie (see oracle/Makefile).  The
+// resulting library (oracle/_ref/libref_tree.so) is used only to pin the CPU
+// restatement in oracle/oracle.c and as the timed CPU baseline.
+//
+// Reference classes exercised:
+//   alphazero::mcts::MCTSNode::selectChild        src/mcts/mcts_node.cpp:90
+//   MCTSNode::addVirtualLoss/removeVirtualLoss    src/mcts/mcts_node_virtual_loss.cpp:15,32
+//   MCTSNode::update                              src/mcts/mcts_node_virtual_loss.cpp:54
+//   GomokuState::getEnhancedTensorRepresentation  src/games/gomoku/gomoku_state.cpp:210
+//   GomokuState::getTensorRepresentation          src/games/gomoku/gomoku_state.cpp:184
+#include <cstdint>
+#include <cstring>
+#include <memory>
+#include <optional>
+#include <string>
+#include <vector>
+#include <chrono>
+#include <omp.h>
+
+#include "core/igamestate.h"
+#include "mcts/mcts_node.h"
+#include "games/gomoku/gomoku_state.h"
+
+namespace {
+
+using alphazero::core::GameResult;
+using alphazero::core::GameType;
+using alphazero::core::IGameState;
+using alphazero::mcts::MCTSNode;
+
+// Smallest state the MCTSNode constructor accepts (it calls validate(),
+// getGameResult(), getCurrentPlayer(), getLegalMoves() and getHash()).
+class TinyState final : public IGameState {
+public:
+    TinyState() : IGameState(GameType::UNKNOWN) {}
+    std::vector<int> getLegalMoves() const override { return {0}; }
+    bool isLegalMove(int a) const override { return a == 0; }
+    void makeMove(int) override {}
+    bool undoMove() override { return false; }
+    bool isTerminal() const override { return false; }
+    GameResult getGameResult() const override { return GameResult::ONGOING; }
+    int getCurrentPlayer() const override { return 1; }
+    int getBoardSize() const override { return 1; }
+    int getActionSpaceSize() const override { return 1; }
+    std::vector<std::vector<std::vector<float>>> getTensorRepresentation() const override { return {}; }
+    std::vector<std::vector<std::vector<float>>> getEnhancedTensorRepresentation() const override { return {}; }
+    uint64_t getHash() const override { return 0; }
+    std::unique_ptr<IGameState> clone() const override { return std::make_unique<TinyState>(); }
+    void copyFrom(const IGameState&) override {}
+    std::string actionToString(int a) const override { return std::to_string(a); }
+    std::optional<int> stringToAction(const std::string&) const override { return 0; }
+    std::string toString() const override { return "tiny"; }
+    bool equals(const IGameState&) const override { return true; }
+    std::vector<int> getMoveHistory() const override { return {}; }
+    bool validate() const override { return true; }
+};
+
+// Give a freshly created node the statistics (N, W, VL, P) through its public
+// API only.  update(w) once then update(0) leaves value_sum_ == w exactly;
+// update() removes one unit of virtual loss when present, so VL goes last.
+void load_stats(MCTSNode& node, int n, float w, int vl, float p) {
+    if (n > 0) {
+        node.update(w);
+        for (int i = 1; i < n; ++i) node.update(0.0f);
+    }
+    if (vl > 0) node.addVirtualLoss(vl);
+    node.setPriorProbability(p);
+}
+
+struct Family {
+    std::shared_ptr<MCTSNode> parent;
+};
+
+Family make_family(int n_children, const int32_t* N, const float* W, const float* P,
+                   const int32_t* VL, int n_parent) {
+    Family f;
+    f.parent = MCTSNode::create(std::make_unique<TinyState>());
+    for (int i = 0; i < n_parent; ++i) f.parent->update(0.0f);
+    auto& kids = f.parent->getChildren();
+    kids.reserve(n_children);
+    for (int i = 0; i < n_children; ++i) {
+        auto c = MCTSNode::create(std::make_unique<TinyState>(), f.parent);
+        load_stats(*c, N[i], W[i], VL[i], P[i]);
+        c->setAction(i);
+        kids.push_back(std::move(c));
+    }
+    return f;
+}
+
+int index_of(const Family& f, const std::shared_ptr<MCTSNode>& c) {
+    if (!c) return -1;
+    auto& kids = f.parent->getChildren();
+    for (size_t i = 0; i < kids.size(); ++i) if (kids[i].get() == c.get()) return (int)i;
+    return -1;
+}
+
+}  // namespace
+
+extern "C" {
+
+// selectChild on one parent whose children carry the given statistics
+// (children listed in index order; only existing == legal children are given).
+// Returns the selected child's index or -1 when there are no children.
+int ref_select_child(int n_children, const int32_t* N, const float* W, const float* P,
+                     const int32_t* VL, int n_parent, float c_puct) {
+    Family f = make_family(n_children, N, W, P, VL, n_parent);
+    return index_of(f, f.parent->selectChild(c_puct, false, 3000.0f));
+}
+
+// Batched form over CSR-compacted parents, OpenMP over parents, followed by
+// applyVirtualLoss(vl) and revertVirtualLoss(vl) on the selected child, as the
+// search loop does (src/mcts/mcts_engine_batch_tree_simple.cpp:102-111,279).
+// vl_after_apply / vl_after_revert may be null.  Returns seconds spent inside
+// the select+apply+revert calls only (tree construction excluded), summed over
+// the repeat count, measured as wall time of the parallel region.
+double ref_select_batch(int n_parents, const int64_t* row_ptr, const int32_t* N, const float* W,
+                        const float* P, const int32_t* VL, const int32_t* n_parent, float c_puct,
+                        int vl_amount, int32_t* sel_out, int32_t* vl_after_apply,
+                        int32_t* vl_after_revert, int repeats, int threads) {
+    if (threads > 0) omp_set_num_threads(threads);
+    std::vector<Family> fam(n_parents);
+#pragma omp parallel for schedule(dynamic, 16)
+    for (int p = 0; p < n_parents; ++p) {
+        int64_t a = row_ptr[p], b = row_ptr[p + 1];
+        fam[p] = make_family((int)(b - a), N + a, W + a, P + a, VL + a, n_parent[p]);
+    }
+    double total = 0.0;
+    for (int r = 0; r < (repeats < 1 ? 1 : repeats); ++r) {
+        auto t0 = std::chrono::steady_clock::now();
+#pragma omp parallel for schedule(static)
+        for (int p = 0; p < n_parents; ++p) {
+            auto best = fam[p].parent->selectChild(c_puct, false, 3000.0f);
+            int idx = index_of(fam[p], best);
+            sel_out[p] = idx;
+            if (best) {
+                best->applyVirtualLoss(vl_amount);
+                if (vl_after_apply) vl_after_apply[p] = best->getVirtualLoss();
+                best->revertVirtualLoss(vl_amount);
+                if (vl_after_revert) vl_after_revert[p] = best->getVirtualLoss();
+            }
+        }
+        total += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    }
+    return total;
+}
+
+// A sequence of virtual-loss operations on one node: op > 0 addVirtualLoss(op),
+// op < 0 removeVirtualLoss(-op), op == 0 the argument-less removeVirtualLoss().
+// out[i] = getVirtualLoss() after operation i.
+void ref_vl_ops(int initial, const int32_t* ops, int n_ops, int32_t* out) {
+    auto node = MCTSNode::create(std::make_unique<TinyState>());
+    if (initial > 0) node->addVirtualLoss(initial);
+    for (int i = 0; i < n_ops; ++i) {
+        if (ops[i] > 0) node->addVirtualLoss(ops[i]);
+        else if (ops[i] < 0) node->removeVirtualLoss(-ops[i]);
+        else node->removeVirtualLoss();
+        out[i] = node->getVirtualLoss();
+    }
+}
+
+// The backup loop of the batched search (mcts_engine_batch_tree_simple.cpp:
+// 276-281) on a path of real nodes given root->leaf; walks leaf->root doing
+// update(v); revertVirtualLoss(vl); v = -v.  In/out: N, VL; W in, and
+// mean_out[i] = getValue() (= W/N in fp32) after the walk.
+void ref_backup_path(int depth, int32_t* N, const float* W, int32_t* VL, float leaf_value,
+                     int vl_amount, float* mean_out) {
+    std::vector<std::shared_ptr<MCTSNode>> path;
+    for (int i = 0; i < depth; ++i) {
+        auto n = MCTSNode::create(std::make_unique<TinyState>());
+        load_stats(*n, N[i], W[i], VL[i], 0.0f);
+        path.push_back(n);
+    }
+    float v = leaf_value;
+    for (auto it = path.rbegin(); it != path.rend(); ++it) {
+        (*it)->update(v);
+        (*it)->revertVirtualLoss(vl_amount);
+        v = -v;
+    }
+    for (int i = 0; i < depth; ++i) {
+        N[i] = path[i]->getVisitCount();
+        VL[i] = path[i]->getVirtualLoss();
+        mean_out[i] = path[i]->getValue();
+    }
+}
+
+// Real GomokuState: play `n_moves` actions from the empty board, then write
+// getEnhancedTensorRepresentation() (19 planes) into planes19[19*S*S] and
+// getTensorRepresentation() (3 planes) into planes3[3*S*S] (either may be
+// null).  Returns the side to move (1 = BLACK, 2 = WHITE), or -1 on an
+// illegal move.
+int ref_gomoku_encode(int board_size, const int32_t* moves, int n_moves, float* planes19,
+                      float* planes3) {
+    alphazero::games::gomoku::GomokuState st(board_size, false, false, 0, false);
+    for (int i = 0; i < n_moves; ++i) {
+        if (!st.isLegalMove(moves[i])) return -1;
+        st.makeMove(moves[i]);
+    }
+    const int S = board_size;
+    if (planes19) {
+        auto t = st.getEnhancedTensorRepresentation();
+        for (size_t c = 0; c < t.size(); ++c)
+            for (int r = 0; r < S; ++r)
+                std::memcpy(planes19 + (c * S + r) * S, t[c][r].data(), sizeof(float) * S);
+    }
+    if (planes3) {
+        auto t = st.getTensorRepresentation();
+        for (size_t c = 0; c < t.size(); ++c)
+            for (int r = 0; r < S; ++r)
+                std::memcpy(planes3 + (c * S + r) * S, t[c][r].data(), sizeof(float) * S);
+    }
+    return st.getCurrentPlayer();
+}
+
+// Encoder CPU baseline: encode `n_states` positions (CSR move lists) with
+// OpenMP over states as src/nn/resnet_model.cpp:410 does.  Returns seconds
+// (-1 when a move list is illegal).
+double ref_gomoku_encode_batch(int board_size, int n_states, const int64_t* row_ptr,
+                               const int32_t* moves, float* planes19, int threads) {
+    if (threads > 0) omp_set_num_threads(threads);
+    const int S = board_size;
+    std::vector<std::unique_ptr<alphazero::games::gomoku::GomokuState>> st(n_states);
+    for (int s = 0; s < n_states; ++s) {
+        st[s] = std::make_unique<alphazero::games::gomoku::GomokuState>(S, false, false, 0, false);
+        for (int64_t i = row_ptr[s]; i < row_ptr[s + 1]; ++i) {
+            if (!st[s]->isLegalMove(moves[i])) return -1.0;  // caller must pass legal, unfinished games
+            st[s]->makeMove(moves[i]);
+        }
+    }
+    auto t0 = std::chrono::steady_clock::now();
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int s = 0; s < n_states; ++s) {
+        auto t = st[s]->getEnhancedTensorRepresentation();
+        float* dst = planes19 + (size_t)s * 19 * S * S;
+        for (size_t c = 0; c < t.size(); ++c)
+            for (int r = 0; r < S; ++r)
+                std::memcpy(dst + (c * S + r) * S, t[c][r].data(), sizeof(float) * S);
+    }
+    return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+}
+
+}  // extern "C"
