@@ -9,10 +9,9 @@
  *   ob200_launch_*  raw launchers over caller-owned DEVICE memory, asynchronous
  *                   on the given stream — the same shape as the reference's
  *                   `extern "C" launch*Kernel` functions.
- *   ob200_net_* / ob200_tree_*  handle-based calls that own their device
- *                   buffers and take HOST buffers — what the reference's C++
- *                   classes (NeuralNetwork, MCTSEngine) bind through the
- *                   adapters in omoknuni_small_b200/adapter/.
+ *   ob200_net_*     handle-based calls that own their device buffers and take
+ *                   HOST buffers — what the reference's C++ classes bind
+ *                   through the adapters in omoknuni_small_b200/adapter/.
  *
  * There is no CPU fallback: every call needs a CUDA device of compute
  * capability 10.x and returns OB200_ERR_NO_DEVICE otherwise.
@@ -122,8 +121,8 @@ int ob200_launch_vl_revert(const ob200_tree_view* tree, const int32_t* node_ids,
  * clamped VL -= vl_value (revertVirtualLoss), node_visits[node] += 1, and
  * v = -v per ply (src/mcts/mcts_engine_batch_tree_simple.cpp:276-281).
  * Replaces launchBackupKernel (src/mcts/gpu_batch_evaluator.cpp:35-46).
- * leaf_values[i] is the value from the point of view of the player who made
- * the last move on the path (the deepest edge receives +v). */
+ * The deepest edge receives +leaf_values[i], as the reference's loop adds
+ * nn_output.value to the leaf node itself. */
 int ob200_launch_backup(const ob200_tree_view* tree, const int32_t* paths,
                         const int32_t* path_len, const float* leaf_values, int32_t n,
                         int32_t max_depth, int32_t vl_value, ob200_stream stream);
@@ -274,13 +273,26 @@ int ob200_net_infer_gomoku(ob200_net* net, const int16_t* history, const uint8_t
                            const uint8_t* to_move, int32_t B, float* policy_out,
                            float* value_out, int32_t out_kind);
 /* DEVICE in, DEVICE out, asynchronous on `stream`: input is a board tensor of
- * roundup(input_channels, 16) channels for B boards. */
+ * ob200_net_input_tensor_channels() channels whose channel blocks are
+ * ob200_net_stride_positions() positions apart (B <= max_batch boards in it). */
 int ob200_net_forward_device(ob200_net* net, const void* input_board_tensor, int32_t B,
                              float* policy_out, float* value_out, int32_t out_kind,
                              ob200_stream stream);
 /* Device pointer of the tower's output board tensor of the last forward
  * (filters channels), for tests. */
 const void* ob200_net_debug_tower_output(ob200_net* net);
+/* Layout of the handle's own board tensors, which ob200_net_forward_device
+ * expects of its input: positions between channel blocks (sized once for
+ * max_batch, so that one buffer serves every batch size) and the channel
+ * count of the input tensor (input_channels rounded up to 32 or 64). */
+int64_t ob200_net_stride_positions(ob200_net* net);
+int32_t ob200_net_input_tensor_channels(ob200_net* net);
+
+/* Reads and clears the current device's error word, which a kernel raises when
+ * one of its bounded waits (on a copy or a tensor-core completion barrier)
+ * runs out: 0 = none.  Synchronises the device.  The host-buffer calls above
+ * check it themselves and return OB200_ERR_TIMEOUT. */
+int ob200_device_error_code(int32_t* code_out);
 
 /* Per-device counters for the end-of-run reduction (the only cross-GPU step;
  * it replaces the MCTSStats fields total_evaluations / total_batches_processed,

@@ -1,0 +1,338 @@
+"""ctypes bindings of libomoknuni_b200.so — the Python host-side mirror of the
+C ABI in include/omoknuni_b200.h.  Used by the tests and by bench.py.
+
+Loading fails loudly when the library has not been built; there is no
+fallback implementation.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libomoknuni_b200.so")
+
+OUT_PROBS, OUT_LOGITS = 0, 1
+GUARD = 32
+
+
+class Error(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__(f"omoknuni_b200 error {code}: {text}")
+        self.code = code
+
+
+class TreeView(C.Structure):
+    _fields_ = [("N", C.c_void_p), ("W", C.c_void_p), ("P", C.c_void_p), ("VL", C.c_void_p),
+                ("legal_bits", C.c_void_p), ("node_visits", C.c_void_p), ("child_node", C.c_void_p),
+                ("n_nodes", C.c_int32), ("n_children", C.c_int32), ("pitch", C.c_int32), ("mask_words", C.c_int32)]
+
+
+class NetConfig(C.Structure):
+    _fields_ = [(k, C.c_int32) for k in ("board_size", "input_channels", "filters", "blocks", "policy_size",
+                                          "policy_head_ch", "value_head_ch", "value_hidden", "max_batch", "device")]
+
+
+class Counters(C.Structure):
+    _fields_ = [(k, C.c_uint64) for k in ("evals", "batches", "selections", "backups", "kernel_launches")]
+
+
+# name -> (restype, argtypes); every symbol the header declares
+SIGNATURES = {
+    "ob200_last_error": (C.c_char_p, []),
+    "ob200_version": (C.c_int, []),
+    "ob200_device_count": (C.c_int, []),
+    "ob200_tree_pitch": (C.c_int32, [C.c_int32]),
+    "ob200_tree_mask_words": (C.c_int32, [C.c_int32]),
+    "ob200_launch_puct_select": (C.c_int, [C.POINTER(TreeView), C.c_void_p, C.c_int32, C.c_float, C.c_int32, C.c_int32,
+                                           C.c_void_p, C.c_void_p]),
+    "ob200_launch_vl_apply": (C.c_int, [C.POINTER(TreeView), C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "ob200_launch_vl_revert": (C.c_int, [C.POINTER(TreeView), C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "ob200_launch_backup": (C.c_int, [C.POINTER(TreeView), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                      C.c_int32, C.c_void_p]),
+    "ob200_launch_set_priors": (C.c_int, [C.POINTER(TreeView), C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p,
+                                          C.c_void_p]),
+    "ob200_launch_traverse": (C.c_int, [C.POINTER(TreeView), C.c_void_p, C.c_int32, C.c_int32, C.c_float, C.c_int32,
+                                        C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "ob200_board_tensor_positions": (C.c_int64, [C.c_int32, C.c_int32]),
+    "ob200_board_tensor_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
+    "ob200_launch_encode_gomoku": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                             C.c_int32, C.c_void_p, C.c_void_p]),
+    "ob200_launch_planes_to_board_tensor": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                                      C.c_void_p]),
+    "ob200_launch_conv3x3": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                       C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "ob200_packed_conv3x3_bytes": (C.c_int64, [C.c_int32, C.c_int32]),
+    "ob200_pack_conv3x3_weights": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "ob200_net_create": (C.c_int, [C.POINTER(NetConfig), C.POINTER(C.c_void_p)]),
+    "ob200_net_destroy": (None, [C.c_void_p]),
+    "ob200_net_set_tensor": (C.c_int, [C.c_void_p, C.c_char_p, C.c_void_p, C.c_int64]),
+    "ob200_net_finalize": (C.c_int, [C.c_void_p]),
+    "ob200_net_infer_planes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32]),
+    "ob200_net_infer_gomoku": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+                                         C.c_void_p, C.c_int32]),
+    "ob200_net_forward_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
+                                           C.c_void_p]),
+    "ob200_net_debug_tower_output": (C.c_void_p, [C.c_void_p]),
+    "ob200_net_stride_positions": (C.c_int64, [C.c_void_p]),
+    "ob200_net_input_tensor_channels": (C.c_int32, [C.c_void_p]),
+    "ob200_device_error_code": (C.c_int, [C.POINTER(C.c_int32)]),
+    "ob200_get_counters": (C.c_int, [C.POINTER(Counters)]),
+    "ob200_reset_counters": (None, []),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library.  Raises when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise Error(-1, f"{LIB_PATH} is missing: run `python -m omoknuni_small_b200.build` (there is no fallback)")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def check(rc):
+    if rc != 0:
+        raise Error(rc, lib().ob200_last_error().decode())
+
+
+def counters():
+    c = Counters()
+    check(lib().ob200_get_counters(C.byref(c)))
+    return {k: getattr(c, k) for k, _ in Counters._fields_}
+
+
+def device_error_code():
+    v = C.c_int32(0)
+    check(lib().ob200_device_error_code(C.byref(v)))
+    return v.value
+
+
+def _ptr(t):
+    """Device pointer of a torch tensor (or None)."""
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    import torch
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class DeviceTree:
+    """Edge statistics on the device (torch tensors own the memory) + the view
+    struct the launchers take.  `tree` is a dict as synth.make_selection_tree
+    returns; an optional 'child_node' [n_nodes, pitch] int32 enables descent."""
+
+    def __init__(self, tree, device="cuda:0"):
+        import torch
+        self.torch = torch
+        self.n_nodes, self.pitch = tree["N"].shape
+        self.n_children = int(tree["n_children"])
+        self.t = {k: torch.from_numpy(np.ascontiguousarray(tree[k])).to(device)
+                  for k in ("N", "W", "P", "VL", "node_visits") if k in tree}
+        self.t["legal_bits"] = torch.from_numpy(np.ascontiguousarray(tree["legal_bits"]).view(np.int32)).to(device)
+        if tree.get("child_node") is not None:
+            self.t["child_node"] = torch.from_numpy(np.ascontiguousarray(tree["child_node"])).to(device)
+        self.mask_words = tree["legal_bits"].shape[1]
+        self.device = device
+        self.view = TreeView(self.t["N"].data_ptr(), self.t["W"].data_ptr(), self.t["P"].data_ptr(),
+                             self.t["VL"].data_ptr(), self.t["legal_bits"].data_ptr(),
+                             self.t["node_visits"].data_ptr(),
+                             self.t["child_node"].data_ptr() if "child_node" in self.t else None,
+                             self.n_nodes, self.n_children, self.pitch, self.mask_words)
+
+    def host(self, key):
+        return self.t[key].cpu().numpy()
+
+    def select(self, node_ids=None, c_puct=1.5, vl_value=3, apply_vl=True, out=None):
+        torch = self.torch
+        n = self.n_nodes if node_ids is None else node_ids.numel()
+        if out is None:
+            out = torch.empty(n, dtype=torch.int32, device=self.device)
+        check(lib().ob200_launch_puct_select(C.byref(self.view), _ptr(node_ids), n, c_puct, vl_value, int(apply_vl),
+                                             _ptr(out), _stream()))
+        return out
+
+    def vl_apply(self, sel, vl_value=3, node_ids=None):
+        check(lib().ob200_launch_vl_apply(C.byref(self.view), _ptr(node_ids), _ptr(sel), sel.numel(), vl_value, _stream()))
+
+    def vl_revert(self, sel, vl_value=3, node_ids=None):
+        check(lib().ob200_launch_vl_revert(C.byref(self.view), _ptr(node_ids), _ptr(sel), sel.numel(), vl_value, _stream()))
+
+    def backup(self, paths, path_len, leaf_values, vl_value=3):
+        n, max_depth, _ = paths.shape
+        check(lib().ob200_launch_backup(C.byref(self.view), _ptr(paths), _ptr(path_len), _ptr(leaf_values), n, max_depth,
+                                        vl_value, _stream()))
+
+    def set_priors(self, node_ids, policy, slot_action=None):
+        check(lib().ob200_launch_set_priors(C.byref(self.view), _ptr(node_ids), policy.shape[0], _ptr(policy),
+                                            policy.shape[1], _ptr(slot_action), _stream()))
+
+    def traverse(self, roots, sims_per_tree, c_puct=1.5, vl_value=3, max_depth=64):
+        torch = self.torch
+        n = roots.numel() * sims_per_tree
+        paths = torch.zeros((n, max_depth, 2), dtype=torch.int32, device=self.device)
+        plen = torch.zeros(n, dtype=torch.int32, device=self.device)
+        check(lib().ob200_launch_traverse(C.byref(self.view), _ptr(roots), roots.numel(), sims_per_tree, c_puct, vl_value,
+                                          max_depth, _ptr(paths), _ptr(plen), _stream()))
+        return paths, plen
+
+
+# ---- board tensors -------------------------------------------------------------
+def board_positions(board_size, B):
+    return int(lib().ob200_board_tensor_positions(board_size, B))
+
+
+def board_tensor_to_planes(bt_u16, board_size, B, channels, stride_positions=None):
+    """bf16 board tensor (numpy uint16 view, flat) -> fp32 planes [B, channels, S, S]
+    plus a flag telling whether every padding / guard element covered by the
+    batch is zero.  Host-side helper for tests."""
+    S, GP = board_size, board_size + 1
+    slots = GP * GP
+    PT = board_positions(S, B)
+    stride = stride_positions or PT
+    chunks = (channels + 7) // 8
+    a = np.asarray(bt_u16).reshape(-1)[: chunks * stride * 8].reshape(chunks, stride, 8)[:, :PT]
+    f = (a.astype(np.uint32) << 16).view(np.float32)
+    body = f[:, GUARD:GUARD + B * slots].reshape(chunks, B, GP, GP, 8)
+    planes = body[:, :, :S, :S, :].transpose(1, 0, 4, 2, 3).reshape(B, chunks * 8, S, S)[:, :channels]
+    pad_zero = (not f[:, :GUARD].any() and not f[:, GUARD + B * slots:].any()
+                and not body[:, :, S, :, :].any() and not body[:, :, :, S, :].any())
+    return np.ascontiguousarray(planes), bool(pad_zero)
+
+
+def planes_to_board_tensor_host(planes, out_channels, stride_positions=None):
+    """fp32 planes [B, C, S, S] -> bf16 board tensor as a flat numpy uint16 array
+    (round to nearest even), the host-side twin of the device conversion."""
+    B, Cc, S, _ = planes.shape
+    GP = S + 1
+    PT = board_positions(S, B)
+    stride = stride_positions or PT
+    chunks = out_channels // 8
+    full = np.zeros((chunks * 8, B, GP, GP), np.float32)
+    full[:Cc, :, :S, :S] = planes.transpose(1, 0, 2, 3)
+    u = full.view(np.uint32)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    out = np.zeros((chunks, stride, 8), np.uint16)
+    out[:, GUARD:GUARD + B * GP * GP, :] = r.reshape(chunks, 8, B * GP * GP).transpose(0, 2, 1)
+    return out.reshape(-1)
+
+
+def encode_gomoku(history, n_hist, to_move, board_size=15, planes=19, out_channels=32):
+    """Device tensors in (int16 [B,16], uint8 [B], uint8 [B]) -> bf16 board tensor
+    (torch int16 tensor holding the bf16 bits)."""
+    import torch
+    B = history.shape[0]
+    nbytes = int(lib().ob200_board_tensor_bytes(board_size, B, out_channels))
+    out = torch.empty(nbytes // 2, dtype=torch.int16, device=history.device)
+    check(lib().ob200_launch_encode_gomoku(_ptr(history), _ptr(n_hist), _ptr(to_move), B, board_size, planes,
+                                           out_channels, _ptr(out), _stream()))
+    return out
+
+
+def planes_to_board_tensor(planes, out_channels):
+    import torch
+    B, Cc, S, _ = planes.shape
+    nbytes = int(lib().ob200_board_tensor_bytes(S, B, out_channels))
+    out = torch.empty(nbytes // 2, dtype=torch.int16, device=planes.device)
+    check(lib().ob200_launch_planes_to_board_tensor(_ptr(planes), B, Cc, S, out_channels, _ptr(out), _stream()))
+    return out
+
+
+def pack_conv3x3(w_oihw, scale, cin):
+    """fp32 [cout, cin_real, 3, 3] (+ per-output-channel scale or None) -> packed
+    bf16 image as numpy uint16."""
+    w = np.ascontiguousarray(w_oihw, np.float32)
+    cout, cin_real = w.shape[:2]
+    out = np.empty(int(lib().ob200_packed_conv3x3_bytes(cin, cout)) // 2, np.uint16)
+    sc = None if scale is None else np.ascontiguousarray(scale, np.float32)
+    check(lib().ob200_pack_conv3x3_weights(w.ctypes.data_as(C.c_void_p), None if sc is None else sc.ctypes.data_as(C.c_void_p),
+                                           cout, cin_real, cin, out.ctypes.data_as(C.c_void_p)))
+    return out
+
+
+def conv3x3(x_bt, packed_w, bias, residual_bt, B, board_size, cin, cout=64, relu=True, out=None):
+    """One conv layer on device board tensors (torch int16 tensors with bf16 bits)."""
+    import torch
+    if out is None:
+        nbytes = int(lib().ob200_board_tensor_bytes(board_size, B, cout))
+        out = torch.zeros(nbytes // 2, dtype=torch.int16, device=x_bt.device)
+    check(lib().ob200_launch_conv3x3(_ptr(x_bt), _ptr(packed_w), _ptr(bias), _ptr(residual_bt), _ptr(out), B, board_size,
+                                     cin, cout, int(relu), _stream()))
+    return out
+
+
+# ---- network handle ------------------------------------------------------------
+class Net:
+    """The residual policy/value network on one GPU (host-side mirror of the
+    reference's ResNetModel: constructor arguments in the same order, weights
+    under the same names, inference on host buffers)."""
+
+    def __init__(self, input_channels, board_size, blocks, filters, policy_size, policy_head_ch=32, value_head_ch=32,
+                 value_hidden=256, max_batch=1024, device=0):
+        self.cfg = NetConfig(board_size, input_channels, filters, blocks, policy_size or board_size * board_size,
+                             policy_head_ch, value_head_ch, value_hidden, max_batch, device)
+        self.h = C.c_void_p()
+        check(lib().ob200_net_create(C.byref(self.cfg), C.byref(self.h)))
+        self.policy_size = self.cfg.policy_size
+        self.board_size = board_size
+
+    def load(self, weights):
+        """weights: dict name -> numpy array under the reference's parameter names."""
+        for name, arr in weights.items():
+            a = np.ascontiguousarray(arr, np.float32)
+            check(lib().ob200_net_set_tensor(self.h, name.encode(), a.ctypes.data_as(C.c_void_p), a.size))
+        check(lib().ob200_net_finalize(self.h))
+        return self
+
+    def infer_planes(self, planes, out_kind=OUT_PROBS):
+        x = np.ascontiguousarray(planes, np.float32)
+        B, Cc = x.shape[:2]
+        pol = np.empty((B, self.policy_size), np.float32)
+        val = np.empty(B, np.float32)
+        check(lib().ob200_net_infer_planes(self.h, x.ctypes.data_as(C.c_void_p), B, Cc, pol.ctypes.data_as(C.c_void_p),
+                                           val.ctypes.data_as(C.c_void_p), out_kind))
+        return pol, val
+
+    def infer_gomoku(self, history, n_hist, to_move, out_kind=OUT_PROBS):
+        h = np.ascontiguousarray(history, np.int16)
+        nh = np.ascontiguousarray(n_hist, np.uint8)
+        tm = np.ascontiguousarray(to_move, np.uint8)
+        B = h.shape[0]
+        pol = np.empty((B, self.policy_size), np.float32)
+        val = np.empty(B, np.float32)
+        check(lib().ob200_net_infer_gomoku(self.h, h.ctypes.data_as(C.c_void_p), nh.ctypes.data_as(C.c_void_p),
+                                           tm.ctypes.data_as(C.c_void_p), B, pol.ctypes.data_as(C.c_void_p),
+                                           val.ctypes.data_as(C.c_void_p), out_kind))
+        return pol, val
+
+    def stride_positions(self):
+        return int(lib().ob200_net_stride_positions(self.h))
+
+    def input_tensor_channels(self):
+        return int(lib().ob200_net_input_tensor_channels(self.h))
+
+    def forward_device(self, input_bt, B, policy_out, value_out, out_kind=OUT_PROBS):
+        check(lib().ob200_net_forward_device(self.h, _ptr(input_bt), B, _ptr(policy_out), _ptr(value_out), out_kind,
+                                             _stream()))
+
+    def tower_output_ptr(self):
+        return lib().ob200_net_debug_tower_output(self.h)
+
+    def close(self):
+        if self.h:
+            lib().ob200_net_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,363 @@
+// Network handle: weights under the reference module's names, BatchNorm
+// folding, device buffers, and the forward pass as a sequence of launches on
+// one stream (stem conv, 2 x blocks residual convs, heads).
+//
+// Takes the place of alphazero::nn::ResNetModel (reference
+// src/nn/resnet_model.cpp:51-237 construction + forward, :594-811 inference).
+#include "internal.h"
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+struct ob200_net {
+    ob200_net_config cfg{};
+    int cin_pad = 0;                // stem input channels of the board tensor (32 or 64)
+    long long stride = 0;           // positions between channel blocks (sized for max_batch)
+    std::map<std::string, std::vector<float>> host;  // tensors as given
+    bool finalized = false;
+    std::mutex mu;                  // calls on one handle are serialised
+    cudaStream_t stream = nullptr;  // used by the host-buffer calls
+    // device: tower
+    std::vector<void*> conv_w;      // packed bf16, 1 + 2 * blocks
+    std::vector<float*> conv_b;
+    void* act_in = nullptr;         // cin_pad channels
+    void* act[3] = {nullptr, nullptr, nullptr};      // filters channels each
+    const void* tower_out = nullptr;
+    // device: heads
+    float *head_w = nullptr, *head_b = nullptr;      // [pc+vc][64], [pc+vc]
+    float *WpT = nullptr, *bp = nullptr, *W1T = nullptr, *b1 = nullptr, *w2 = nullptr;
+    float b2 = 0.0f;
+    float *hp = nullptr, *hv = nullptr, *hidden = nullptr;
+    // device + pinned host staging of the host-buffer calls
+    float *d_planes = nullptr, *d_policy = nullptr, *d_value = nullptr;
+    int16_t* d_hist = nullptr; uint8_t *d_nhist = nullptr, *d_tomove = nullptr;
+    float *h_planes = nullptr, *h_policy = nullptr, *h_value = nullptr;
+    int16_t* h_hist = nullptr; uint8_t *h_nhist = nullptr, *h_tomove = nullptr;
+    size_t planes_capacity = 0;     // floats per staging buffer
+    std::vector<void*> owned_dev, owned_host;
+};
+
+namespace ob200 {
+namespace {
+
+constexpr float kBnEps = 1e-5f;     // torch BatchNorm2d default, unchanged by the reference
+
+template <typename T>
+int dev_alloc(ob200_net* n, T** out, size_t count, bool zero) {
+    void* p = nullptr;
+    OB200_CUDA_OK(cudaMalloc(&p, count * sizeof(T)));
+    n->owned_dev.push_back(p);
+    if (zero) OB200_CUDA_OK(cudaMemset(p, 0, count * sizeof(T)));
+    *out = static_cast<T*>(p);
+    return OB200_OK;
+}
+template <typename T>
+int host_alloc(ob200_net* n, T** out, size_t count) {
+    void* p = nullptr;
+    OB200_CUDA_OK(cudaMallocHost(&p, count * sizeof(T)));
+    n->owned_host.push_back(p);
+    *out = static_cast<T*>(p);
+    return OB200_OK;
+}
+template <typename T>
+int upload(ob200_net* n, T** out, const std::vector<T>& v) {
+    if (int rc = dev_alloc(n, out, v.size(), false)) return rc;
+    OB200_CUDA_OK(cudaMemcpy(*out, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
+    return OB200_OK;
+}
+
+// scale = gamma / sqrt(var + eps), shift = beta - mean * scale
+int bn_fold(ob200_net* n, const std::string& prefix, int c, std::vector<float>& scale, std::vector<float>& shift) {
+    const char* leaves[4] = {".weight", ".bias", ".running_mean", ".running_var"};
+    const std::vector<float>* t[4];
+    for (int i = 0; i < 4; ++i) {
+        auto it = n->host.find(prefix + leaves[i]);
+        if (it == n->host.end() || (int)it->second.size() != c)
+            return set_error(OB200_ERR_STATE, "ob200_net_finalize: tensor %s%s missing or not of %d elements",
+                             prefix.c_str(), leaves[i], c);
+        t[i] = &it->second;
+    }
+    scale.resize(c); shift.resize(c);
+    for (int i = 0; i < c; ++i) {
+        const float s = (*t[0])[i] / std::sqrt((*t[3])[i] + kBnEps);
+        scale[i] = s;
+        shift[i] = (*t[1])[i] - (*t[2])[i] * s;
+    }
+    return OB200_OK;
+}
+
+int need(ob200_net* n, const std::string& name, size_t numel, const std::vector<float>** out) {
+    auto it = n->host.find(name);
+    if (it == n->host.end() || it->second.size() != numel)
+        return set_error(OB200_ERR_STATE, "ob200_net_finalize: tensor %s missing or not of %zu elements", name.c_str(),
+                         numel);
+    *out = &it->second;
+    return OB200_OK;
+}
+
+int add_conv(ob200_net* n, const std::string& conv, const std::string& bn, int cin_real, int cin) {
+    const int F = n->cfg.filters;
+    const std::vector<float>* w;
+    if (int rc = need(n, conv + ".weight", (size_t)F * cin_real * 9, &w)) return rc;
+    std::vector<float> scale, shift;
+    if (int rc = bn_fold(n, bn, F, scale, shift)) return rc;
+    std::vector<uint16_t> packed((size_t)9 * cin * F);
+    if (int rc = ob200_pack_conv3x3_weights(w->data(), scale.data(), F, cin_real, cin, packed.data())) return rc;
+    uint16_t* dw = nullptr; float* db = nullptr;
+    if (int rc = upload(n, &dw, packed)) return rc;
+    if (int rc = upload(n, &db, shift)) return rc;
+    n->conv_w.push_back(dw); n->conv_b.push_back(db);
+    return OB200_OK;
+}
+
+}  // namespace
+}  // namespace ob200
+
+using namespace ob200;
+
+extern "C" {
+
+int ob200_net_create(const ob200_net_config* cfg, ob200_net** out) {
+    if (!cfg || !out) return set_error(OB200_ERR_INVALID, "ob200_net_create: null argument");
+    *out = nullptr;
+    if (cfg->board_size < 1 || cfg->board_size > OB200_GUARD - 2 || cfg->input_channels < 1 || cfg->blocks < 0 ||
+        cfg->policy_size < 1 || cfg->policy_head_ch < 1 || cfg->value_head_ch < 1 || cfg->value_hidden < 1 ||
+        cfg->max_batch < 1)
+        return set_error(OB200_ERR_INVALID, "ob200_net_create: bad configuration value");
+    if (cfg->filters != 64)
+        return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_create: this build's tower kernel covers filters = 64, got %d",
+                         cfg->filters);
+    if (cfg->input_channels > 64)
+        return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_create: input_channels %d > 64", cfg->input_channels);
+    if (cudaSetDevice(cfg->device) != cudaSuccess) {
+        cudaGetLastError();
+        return set_error(OB200_ERR_NO_DEVICE, "ob200_net_create: CUDA device %d is not available (there is no CPU path)", cfg->device);
+    }
+    if (int rc = require_device()) return rc;
+    ob200_net* n = new ob200_net;
+    n->cfg = *cfg;
+    n->cin_pad = cfg->input_channels <= 32 ? 32 : 64;
+    n->stride = board_geom(cfg->board_size, cfg->max_batch).PT;
+    *out = n;
+    return OB200_OK;
+}
+
+void ob200_net_destroy(ob200_net* n) {
+    if (!n) return;
+    cudaSetDevice(n->cfg.device);
+    if (n->stream) { cudaStreamSynchronize(n->stream); cudaStreamDestroy(n->stream); }
+    for (void* p : n->owned_dev) cudaFree(p);
+    for (void* p : n->owned_host) cudaFreeHost(p);
+    delete n;
+}
+
+int ob200_net_set_tensor(ob200_net* n, const char* name, const float* data, int64_t numel) {
+    if (!n || !name || !data || numel < 0) return set_error(OB200_ERR_INVALID, "ob200_net_set_tensor: bad argument");
+    std::lock_guard<std::mutex> lk(n->mu);
+    if (n->finalized) return set_error(OB200_ERR_STATE, "ob200_net_set_tensor: weights already finalised");
+    const std::string s(name);
+    if (s.size() > 19 && s.compare(s.size() - 19, 19, "num_batches_tracked") == 0) return OB200_OK;
+    n->host[s].assign(data, data + numel);
+    return OB200_OK;
+}
+
+int ob200_net_finalize(ob200_net* n) {
+    if (!n) return set_error(OB200_ERR_INVALID, "ob200_net_finalize: null handle");
+    std::lock_guard<std::mutex> lk(n->mu);
+    if (n->finalized) return set_error(OB200_ERR_STATE, "ob200_net_finalize: already finalised");
+    const ob200_net_config& c = n->cfg;
+    OB200_CUDA_OK(cudaSetDevice(c.device));
+    const int F = c.filters, S2 = c.board_size * c.board_size, pc = c.policy_head_ch, vc = c.value_head_ch;
+    // tower
+    if (int rc = add_conv(n, "input_conv", "input_bn", c.input_channels, n->cin_pad)) return rc;
+    for (int i = 0; i < c.blocks; ++i) {
+        const std::string p = "res_blocks." + std::to_string(i) + ".";
+        if (int rc = add_conv(n, p + "conv1", p + "bn1", F, F)) return rc;
+        if (int rc = add_conv(n, p + "conv2", p + "bn2", F, F)) return rc;
+    }
+    // heads: 1x1 convolutions with BatchNorm folded, policy rows first
+    const std::vector<float>*pw, *vw, *fcw, *fcb, *f1w, *f1b, *f2w, *f2b;
+    if (int rc = need(n, "policy_conv.weight", (size_t)pc * F, &pw)) return rc;
+    if (int rc = need(n, "value_conv.weight", (size_t)vc * F, &vw)) return rc;
+    std::vector<float> ps, pb, vs, vb;
+    if (int rc = bn_fold(n, "policy_bn", pc, ps, pb)) return rc;
+    if (int rc = bn_fold(n, "value_bn", vc, vs, vb)) return rc;
+    std::vector<float> hw((size_t)(pc + vc) * F), hb(pc + vc);
+    for (int h = 0; h < pc; ++h) { for (int k = 0; k < F; ++k) hw[(size_t)h * F + k] = (*pw)[(size_t)h * F + k] * ps[h]; hb[h] = pb[h]; }
+    for (int h = 0; h < vc; ++h) { for (int k = 0; k < F; ++k) hw[(size_t)(pc + h) * F + k] = (*vw)[(size_t)h * F + k] * vs[h]; hb[pc + h] = vb[h]; }
+    if (int rc = upload(n, &n->head_w, hw)) return rc;
+    if (int rc = upload(n, &n->head_b, hb)) return rc;
+    // fully connected layers, stored transposed ([in][out]) for coalesced reads
+    const int Kp = pc * S2, Kv = vc * S2, A = c.policy_size, H = c.value_hidden;
+    if (int rc = need(n, "policy_fc.weight", (size_t)A * Kp, &fcw)) return rc;
+    if (int rc = need(n, "policy_fc.bias", (size_t)A, &fcb)) return rc;
+    if (int rc = need(n, "value_fc1.weight", (size_t)H * Kv, &f1w)) return rc;
+    if (int rc = need(n, "value_fc1.bias", (size_t)H, &f1b)) return rc;
+    if (int rc = need(n, "value_fc2.weight", (size_t)H, &f2w)) return rc;
+    if (int rc = need(n, "value_fc2.bias", 1, &f2b)) return rc;
+    std::vector<float> wpt((size_t)Kp * A), w1t((size_t)Kv * H);
+    for (int j = 0; j < A; ++j) for (int i = 0; i < Kp; ++i) wpt[(size_t)i * A + j] = (*fcw)[(size_t)j * Kp + i];
+    for (int j = 0; j < H; ++j) for (int i = 0; i < Kv; ++i) w1t[(size_t)i * H + j] = (*f1w)[(size_t)j * Kv + i];
+    if (int rc = upload(n, &n->WpT, wpt)) return rc;
+    if (int rc = upload(n, &n->bp, *fcb)) return rc;
+    if (int rc = upload(n, &n->W1T, w1t)) return rc;
+    if (int rc = upload(n, &n->b1, *f1b)) return rc;
+    if (int rc = upload(n, &n->w2, *f2w)) return rc;
+    n->b2 = (*f2b)[0];
+    // activations (zeroed once: guards and padding stay zero for the handle's lifetime)
+    const size_t rec = (size_t)n->stride * 16;  // bytes per channel block
+    uint8_t* p8 = nullptr;
+    if (int rc = dev_alloc(n, &p8, rec * (n->cin_pad / 8), true)) return rc;
+    n->act_in = p8;
+    for (int i = 0; i < 3; ++i) { if (int rc = dev_alloc(n, &p8, rec * (F / 8), true)) return rc; n->act[i] = p8; }
+    const size_t MB = c.max_batch;
+    if (int rc = dev_alloc(n, &n->hp, MB * Kp, false)) return rc;
+    if (int rc = dev_alloc(n, &n->hv, MB * Kv, false)) return rc;
+    if (int rc = dev_alloc(n, &n->hidden, MB * H, false)) return rc;
+    if (int rc = dev_alloc(n, &n->d_policy, MB * A, false)) return rc;
+    if (int rc = dev_alloc(n, &n->d_value, MB, false)) return rc;
+    n->planes_capacity = MB * (size_t)std::max(c.input_channels, 19) * S2;
+    if (int rc = dev_alloc(n, &n->d_planes, n->planes_capacity, false)) return rc;
+    if (int rc = dev_alloc(n, &n->d_hist, MB * 16, false)) return rc;
+    if (int rc = dev_alloc(n, &n->d_nhist, MB, false)) return rc;
+    if (int rc = dev_alloc(n, &n->d_tomove, MB, false)) return rc;
+    if (int rc = host_alloc(n, &n->h_planes, n->planes_capacity)) return rc;
+    if (int rc = host_alloc(n, &n->h_policy, MB * A)) return rc;
+    if (int rc = host_alloc(n, &n->h_value, MB)) return rc;
+    if (int rc = host_alloc(n, &n->h_hist, MB * 16)) return rc;
+    if (int rc = host_alloc(n, &n->h_nhist, MB)) return rc;
+    if (int rc = host_alloc(n, &n->h_tomove, MB)) return rc;
+    OB200_CUDA_OK(cudaStreamCreateWithFlags(&n->stream, cudaStreamNonBlocking));
+    OB200_CUDA_OK(cudaDeviceSynchronize());
+    n->host.clear();
+    n->finalized = true;
+    return OB200_OK;
+}
+
+}  // extern "C"
+
+namespace ob200 {
+namespace {
+
+// Tower + heads on device buffers. `input` is a board tensor of cin_pad channels
+// whose channel blocks are `in_stride` positions apart.
+int forward_device(ob200_net* n, const void* input, long long in_stride, int B, float* policy_out, float* value_out,
+                   int out_kind, cudaStream_t st) {
+    const ob200_net_config& c = n->cfg;
+    const int S = c.board_size, F = c.filters;
+    // The stem reads `input` with its own stride; everything after uses the handle's stride.
+    // launch_conv3x3 takes one stride for all tensors, so the stem input must share it.
+    if (in_stride != n->stride)
+        return set_error(OB200_ERR_INVALID, "forward: input tensor stride %lld != handle stride %lld", in_stride, n->stride);
+    void *x = n->act[0], *y = n->act[1], *z = n->act[2];
+    if (int rc = launch_conv3x3(input, n->conv_w[0], n->conv_b[0], nullptr, x, B, S, n->cin_pad, F, 1, n->stride, st)) return rc;
+    for (int i = 0; i < c.blocks; ++i) {
+        if (int rc = launch_conv3x3(x, n->conv_w[1 + 2 * i], n->conv_b[1 + 2 * i], nullptr, y, B, S, F, F, 1, n->stride, st)) return rc;
+        if (int rc = launch_conv3x3(y, n->conv_w[2 + 2 * i], n->conv_b[2 + 2 * i], x, z, B, S, F, F, 1, n->stride, st)) return rc;
+        std::swap(x, z);
+    }
+    n->tower_out = x;
+    const int S2 = S * S, pc = c.policy_head_ch, vc = c.value_head_ch;
+    if (int rc = launch_head_conv(x, n->stride, n->head_w, n->head_b, pc + vc, pc, n->hp, n->hv, B, S, st)) return rc;
+    if (int rc = launch_fc(n->hp, n->WpT, n->bp, policy_out, B, pc * S2, c.policy_size, 0, st)) return rc;
+    if (out_kind == OB200_OUT_PROBS)
+        if (int rc = launch_softmax(policy_out, B, c.policy_size, st)) return rc;
+    if (int rc = launch_fc(n->hv, n->W1T, n->b1, n->hidden, B, vc * S2, c.value_hidden, 1, st)) return rc;
+    if (int rc = launch_value_out(n->hidden, n->w2, n->b2, c.value_hidden, B, value_out, st)) return rc;
+    counters().evals.fetch_add((uint64_t)B, std::memory_order_relaxed);
+    counters().batches.fetch_add(1, std::memory_order_relaxed);
+    return OB200_OK;
+}
+
+int check_call(ob200_net* n, int B, const void* a, const void* b, const void* c, int out_kind, const char* who) {
+    if (!n || !a || !b || !c) return set_error(OB200_ERR_INVALID, "%s: null argument", who);
+    if (!n->finalized) return set_error(OB200_ERR_STATE, "%s: weights not finalised", who);
+    if (B < 1 || B > n->cfg.max_batch)
+        return set_error(OB200_ERR_TOO_LARGE, "%s: batch %d outside [1, max_batch %d]", who, B, n->cfg.max_batch);
+    if (out_kind != OB200_OUT_PROBS && out_kind != OB200_OUT_LOGITS)
+        return set_error(OB200_ERR_INVALID, "%s: bad out_kind %d", who, out_kind);
+    return OB200_OK;
+}
+
+// Copies results back, waits, and reports a kernel that gave up on a wait.
+int finish_host_call(ob200_net* n, int B, float* policy_out, float* value_out) {
+    const size_t A = n->cfg.policy_size;
+    OB200_CUDA_OK(cudaMemcpyAsync(n->h_policy, n->d_policy, (size_t)B * A * sizeof(float), cudaMemcpyDeviceToHost, n->stream));
+    OB200_CUDA_OK(cudaMemcpyAsync(n->h_value, n->d_value, (size_t)B * sizeof(float), cudaMemcpyDeviceToHost, n->stream));
+    int* errw = device_error_word();
+    int err = 0;
+    if (errw) OB200_CUDA_OK(cudaMemcpyAsync(&err, errw, sizeof(int), cudaMemcpyDeviceToHost, n->stream));
+    OB200_CUDA_OK(cudaStreamSynchronize(n->stream));
+    if (err) {
+        cudaMemsetAsync(errw, 0, sizeof(int), n->stream);
+        cudaStreamSynchronize(n->stream);
+        return set_error(OB200_ERR_TIMEOUT, "a tower kernel gave up on a bounded wait (role code %d); outputs are not valid", err);
+    }
+    std::memcpy(policy_out, n->h_policy, (size_t)B * A * sizeof(float));
+    std::memcpy(value_out, n->h_value, (size_t)B * sizeof(float));
+    return OB200_OK;
+}
+
+}  // namespace
+}  // namespace ob200
+
+extern "C" {
+
+int ob200_net_infer_planes(ob200_net* n, const float* planes, int32_t B, int32_t C, float* policy_out,
+                           float* value_out, int32_t out_kind) {
+    if (int rc = check_call(n, B, planes, policy_out, value_out, out_kind, "ob200_net_infer_planes")) return rc;
+    std::lock_guard<std::mutex> lk(n->mu);
+    const ob200_net_config& c = n->cfg;
+    const size_t S2 = (size_t)c.board_size * c.board_size;
+    if (C < 1 || (size_t)B * C * S2 > n->planes_capacity)
+        return set_error(OB200_ERR_TOO_LARGE, "ob200_net_infer_planes: %d planes x batch %d exceeds the staging buffer", C, B);
+    OB200_CUDA_OK(cudaSetDevice(c.device));
+    // as ResNetModel::forward: the first min(C, input_channels) planes are used (:117-147);
+    // planes beyond input_channels are dropped while staging
+    const int used = C < c.input_channels ? C : c.input_channels;
+    for (int b = 0; b < B; ++b)
+        std::memcpy(n->h_planes + (size_t)b * used * S2, planes + (size_t)b * C * S2, (size_t)used * S2 * sizeof(float));
+    OB200_CUDA_OK(cudaMemcpyAsync(n->d_planes, n->h_planes, (size_t)B * used * S2 * sizeof(float), cudaMemcpyHostToDevice, n->stream));
+    if (int rc = launch_planes_to_board_tensor(n->d_planes, B, used, c.board_size, n->cin_pad, n->act_in, n->stride, n->stream)) return rc;
+    if (int rc = forward_device(n, n->act_in, n->stride, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
+    return finish_host_call(n, B, policy_out, value_out);
+}
+
+int ob200_net_infer_gomoku(ob200_net* n, const int16_t* history, const uint8_t* n_hist, const uint8_t* to_move,
+                           int32_t B, float* policy_out, float* value_out, int32_t out_kind) {
+    if (int rc = check_call(n, B, history, policy_out, value_out, out_kind, "ob200_net_infer_gomoku")) return rc;
+    if (!n_hist || !to_move) return set_error(OB200_ERR_INVALID, "ob200_net_infer_gomoku: null argument");
+    std::lock_guard<std::mutex> lk(n->mu);
+    const ob200_net_config& c = n->cfg;
+    if (c.input_channels != 17 && c.input_channels != 19)
+        return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_infer_gomoku: the Gomoku encoder makes 17 or 19 planes; the network takes %d",
+                         c.input_channels);
+    OB200_CUDA_OK(cudaSetDevice(c.device));
+    std::memcpy(n->h_hist, history, (size_t)B * 16 * sizeof(int16_t));
+    std::memcpy(n->h_nhist, n_hist, (size_t)B);
+    std::memcpy(n->h_tomove, to_move, (size_t)B);
+    OB200_CUDA_OK(cudaMemcpyAsync(n->d_hist, n->h_hist, (size_t)B * 16 * sizeof(int16_t), cudaMemcpyHostToDevice, n->stream));
+    OB200_CUDA_OK(cudaMemcpyAsync(n->d_nhist, n->h_nhist, (size_t)B, cudaMemcpyHostToDevice, n->stream));
+    OB200_CUDA_OK(cudaMemcpyAsync(n->d_tomove, n->h_tomove, (size_t)B, cudaMemcpyHostToDevice, n->stream));
+    if (int rc = launch_encode_gomoku(n->d_hist, n->d_nhist, n->d_tomove, B, c.board_size, c.input_channels, n->cin_pad,
+                                      n->act_in, n->stride, n->stream)) return rc;
+    if (int rc = forward_device(n, n->act_in, n->stride, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
+    return finish_host_call(n, B, policy_out, value_out);
+}
+
+int ob200_net_forward_device(ob200_net* n, const void* input_board_tensor, int32_t B, float* policy_out,
+                             float* value_out, int32_t out_kind, ob200_stream stream) {
+    if (int rc = check_call(n, B, input_board_tensor, policy_out, value_out, out_kind, "ob200_net_forward_device")) return rc;
+    std::lock_guard<std::mutex> lk(n->mu);
+    OB200_CUDA_OK(cudaSetDevice(n->cfg.device));
+    return forward_device(n, input_board_tensor, n->stride, B, policy_out, value_out, out_kind, as_stream(stream));
+}
+
+const void* ob200_net_debug_tower_output(ob200_net* n) { return n ? n->tower_out : nullptr; }
+int64_t ob200_net_stride_positions(ob200_net* n) { return n ? n->stride : 0; }
+int32_t ob200_net_input_tensor_channels(ob200_net* n) { return n ? n->cin_pad : 0; }
+
+}  // extern "C"

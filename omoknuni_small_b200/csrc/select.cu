@@ -266,10 +266,10 @@ int ob200_launch_puct_select(const ob200_tree_view* tree, const int32_t* node_id
                              float c_puct, int32_t vl_value, int32_t apply_vl, int32_t* sel_out,
                              ob200_stream stream) {
     if (int rc = check_view(tree, "ob200_launch_puct_select")) return rc;
+    if (n == 0) return OB200_OK;
     if (n < 0 || (!node_ids && n > tree->n_nodes) || !sel_out)
         return set_error(OB200_ERR_INVALID, "ob200_launch_puct_select: bad n (%d) or null output", n);
     if (int rc = require_device()) return rc;
-    if (n == 0) return OB200_OK;
     const int blocks = (n + kWarpsPerBlock - 1) / kWarpsPerBlock;
     puct_select_kernel<<<blocks, kWarpsPerBlock * 32, 0, as_stream(stream)>>>(*tree, node_ids, n, c_puct, vl_value,
                                                                              apply_vl, sel_out);

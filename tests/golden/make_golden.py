@@ -1,0 +1,99 @@
+"""Generates the golden fixtures in this directory from the reference
+project's own classes (oracle/_ref, built by `make -C oracle ref` in a
+container where the reference checkout is present).
+
+    python tests/golden/make_golden.py
+
+Inputs come from omoknuni_small_b200.synth with fixed seeds; the fixtures store
+the inputs' checksums and the reference's outputs:
+  select_golden.npz  MCTSNode::selectChild + applyVirtualLoss + revertVirtualLoss
+  encode_golden.npz  GomokuState::getEnhancedTensorRepresentation (bit-packed)
+  net_golden.npz     ResNetModel::forward (log-softmax policy, value): (a) a tiny
+                     model with the reference's own libtorch default
+                     initialisation, its weights stored here rounded to fp16
+                     (the rounded values are what the reference ran with);
+                     (b) the 15x15 / 10-block model with seeded weights set by
+                     name (regenerated from the seed, checked by checksum).
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from omoknuni_small_b200 import synth  # noqa: E402
+from oracle import capi  # noqa: E402
+
+
+def checksum(*arrays):
+    import hashlib
+    h = hashlib.sha256()
+    for a in arrays:
+        h.update(np.ascontiguousarray(a).tobytes())
+    return h.hexdigest()
+
+
+def make_select():
+    out = {}
+    for tag, n_nodes, nc, seed in (("g225", 256, 225, 7), ("c4672", 8, 4672, 11), ("n3", 64, 3, 5)):
+        t = synth.make_selection_tree(n_nodes, nc, seed=seed)
+        sel, vl_apply, vl_revert, _ = capi.ref_select(t, c_puct=1.5, vl_value=3)
+        out[tag + "_sel"] = sel
+        out[tag + "_vl_after_apply"] = vl_apply
+        out[tag + "_vl_after_revert"] = vl_revert
+        out[tag + "_inputs_sha256"] = checksum(t["N"], t["W"], t["P"], t["VL"], t["legal_bits"], t["node_visits"])
+        out[tag + "_shape"] = np.array([n_nodes, nc, seed])
+    np.savez_compressed(os.path.join(HERE, "select_golden.npz"), **out)
+
+
+def make_encode():
+    games, hist, nh, tm = synth.make_gomoku_games(48, 15, seed=2024, max_moves=60)
+    ref, _ = capi.ref_gomoku_encode_batch(games, 15)
+    flat = np.concatenate(games) if sum(map(len, games)) else np.zeros(0, np.int32)
+    ptr = np.cumsum([0] + [len(g) for g in games])
+    np.savez_compressed(os.path.join(HERE, "encode_golden.npz"), moves=flat.astype(np.int16), row_ptr=ptr,
+                        to_move=tm, planes_bits=np.packbits(ref.astype(bool)), planes_shape=np.array(ref.shape),
+                        planes_is_binary=np.array(bool(np.isin(ref, (0.0, 1.0)).all())))
+
+
+def make_net():
+    out = {}
+    # (a) the reference module as its constructor leaves it (libtorch default initialisation
+    #     after torch::manual_seed), tiny shape so that the weights fit in a fixture; every
+    #     weight is rounded to fp16 and pushed back so that fixture and outputs agree exactly
+    net = capi.RefNet(17, 5, 1, 64, 25, seed=1234)
+    x = synth.make_stone_planes(8, 5, 17, seed=77, max_stones=12)
+    for name, arr in net.state().items():
+        if "num_batches" in name:
+            continue
+        r = arr.astype(np.float16)
+        net.set(name, r.astype(np.float32))
+        out["a_w_" + name] = r
+    lp, v, _ = net.forward(x)
+    out["a_logp"], out["a_value"], out["a_x_bits"], out["a_x_shape"] = lp, v, np.packbits(x.astype(bool)), np.array(x.shape)
+    out["a_cfg"] = np.array([17, 5, 1, 64, 25, 32, 32])
+    # (b) benchmark-shaped Gomoku network (15x15, 10 blocks, reference 32/32 heads), seeded
+    #     weights set by name on the reference module, random BatchNorm statistics
+    shapes = synth.net_tensor_shapes(15, 17, 64, 10, 225, 32, 32)
+    w = synth.make_weights(shapes, seed=42, init="torch_default", bn="random")
+    net = capi.RefNet(17, 15, 10, 64, 225, seed=0)
+    for k, a in w.items():
+        net.set(k, a)
+    x = synth.make_stone_planes(8, 15, 17, seed=1000)
+    lp, v, _ = net.forward(x)
+    out["b_logp"], out["b_value"] = lp, v
+    out["b_weights_sha256"] = checksum(*[w[k] for k, _ in shapes])
+    out["b_x_sha256"] = checksum(x)
+    np.savez_compressed(os.path.join(HERE, "net_golden.npz"), **out)
+
+
+if __name__ == "__main__":
+    if not (capi.have_ref_tree() and capi.have_ref_net()):
+        sys.exit("oracle/_ref is not built: run `make -C oracle ref` where the reference checkout exists")
+    make_select()
+    make_encode()
+    make_net()
+    for f in sorted(os.listdir(HERE)):
+        print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -1,0 +1,196 @@
+"""Pins the CPU oracle: against the golden fixtures produced by the reference
+project's own classes, against the known-answer cases of the reference's unit
+tests, and (when oracle/_ref was built) against the reference classes live."""
+import hashlib
+import os
+
+import numpy as np
+import pytest
+
+from omoknuni_small_b200 import synth
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def sha(*arrays):
+    h = hashlib.sha256()
+    for a in arrays:
+        h.update(np.ascontiguousarray(a).tobytes())
+    return h.hexdigest()
+
+
+def tiny_tree(N, W, P, VL, n_parent):
+    n = len(N)
+    pitch, mw = synth.tree_pitch(n), synth.tree_mask_words(n)
+    t = {"N": np.zeros((1, pitch), np.int32), "W": np.zeros((1, pitch), np.float32), "P": np.zeros((1, pitch), np.float32),
+         "VL": np.zeros((1, pitch), np.int32), "legal_bits": np.zeros((1, mw), np.uint32),
+         "node_visits": np.array([n_parent], np.int32), "n_children": n}
+    t["N"][0, :n], t["W"][0, :n], t["P"][0, :n], t["VL"][0, :n] = N, W, P, VL
+    t["legal_bits"][0, 0] = (1 << n) - 1
+    return t
+
+
+# ---- known answers restated from the reference's unit tests ------------------------
+def test_child_selection_known_answers(oracle):
+    # tests/mcts/mcts_node_test.cpp:237-268 — priors .7/.2/.1, parent visited once, c = 1.0
+    t = tiny_tree([0, 0, 0], [0, 0, 0], [.7, .2, .1], [0, 0, 0], 1)
+    assert oracle.puct_select(t, c_puct=1.0)[0] == 0
+    # after child0.update(-1) a different child is chosen
+    t = tiny_tree([1, 0, 0], [-1, 0, 0], [.7, .2, .1], [0, 0, 0], 1)
+    assert oracle.puct_select(t, c_puct=1.0)[0] != 0
+
+
+def test_virtual_loss_known_answers(oracle):
+    # tests/mcts/mcts_node_test.cpp:271-298 — equal priors; VL on the selected child moves the choice, removing restores it
+    t = tiny_tree([0, 0, 0], [0, 0, 0], [1 / 3] * 3, [0, 0, 0], 1)
+    first = oracle.puct_select(t, c_puct=1.0)[0]
+    t["VL"][0, first] += 1
+    assert oracle.puct_select(t, c_puct=1.0)[0] != first
+    t["VL"][0, first] -= 1
+    assert oracle.puct_select(t, c_puct=1.0)[0] == first
+    # tests/mcts/virtual_loss_test.cpp:195-224 — five equal children (10 visits, mean .5), parent 50, VL 3 on one, c = 1.5
+    t = tiny_tree([10] * 5, [5.0] * 5, [.2] * 5, [3, 0, 0, 0, 0], 50)
+    assert oracle.puct_select(t, c_puct=1.5)[0] != 0
+    # :160-193 stacking 1,2,3 then remove(3) twice -> 3, 0 ; :282-308 removing more than present clamps to 0
+    assert list(oracle.vl_ops(0, [1, 2, 3, -3, -3])) == [1, 3, 6, 3, 0]
+    assert list(oracle.vl_ops(0, [2, -5, 0, 0])) == [2, 0, 0, 0]
+
+
+def test_backprop_known_answer(oracle):
+    # tests/mcts/mcts_node_test.cpp:301-313 — two updates 1.0 and 0.5 -> 2 visits, mean 0.75
+    t = tiny_tree([0], [0], [1], [0], 0)
+    paths = np.zeros((1, 1, 2), np.int32)
+    for v in (1.0, 0.5):
+        oracle.backup(t, paths, [1], [v], vl_value=0)
+    assert t["N"][0, 0] == 2 and t["W"][0, 0] / t["N"][0, 0] == 0.75 and t["node_visits"][0] == 2
+
+
+# ---- golden fixtures made by the reference's own classes ---------------------------
+@pytest.mark.parametrize("tag", ["g225", "c4672", "n3"])
+def test_selection_matches_reference_golden(oracle, tag):
+    g = np.load(os.path.join(GOLD, "select_golden.npz"))
+    n_nodes, nc, seed = g[tag + "_shape"]
+    t = synth.make_selection_tree(int(n_nodes), int(nc), seed=int(seed))
+    assert sha(t["N"], t["W"], t["P"], t["VL"], t["legal_bits"], t["node_visits"]) == str(g[tag + "_inputs_sha256"])
+    rows = np.arange(n_nodes)
+    vl0 = t["VL"].copy()
+    sel = oracle.puct_select(t, c_puct=1.5, vl_value=3, apply_vl=True)
+    assert np.array_equal(sel, g[tag + "_sel"])
+    assert np.array_equal(t["VL"][rows, sel], g[tag + "_vl_after_apply"])
+    oracle.vl_revert(t, sel, 3)
+    assert np.array_equal(t["VL"][rows, sel], g[tag + "_vl_after_revert"])
+    assert np.array_equal(t["VL"], vl0)            # apply then revert conserves every counter
+
+
+def load_encode_golden():
+    g = np.load(os.path.join(GOLD, "encode_golden.npz"))
+    shape = tuple(g["planes_shape"])
+    planes = np.unpackbits(g["planes_bits"])[: int(np.prod(shape))].reshape(shape).astype(np.float32)
+    games = [g["moves"][g["row_ptr"][i]:g["row_ptr"][i + 1]].astype(np.int32) for i in range(shape[0])]
+    hist = np.full((shape[0], 16), -1, np.int16)
+    nh = np.zeros(shape[0], np.uint8)
+    for i, mv in enumerate(games):
+        h = mv[::-1][:16]
+        hist[i, :len(h)] = h
+        nh[i] = len(h)
+    return games, hist, nh, g["to_move"], planes, bool(g["planes_is_binary"])
+
+
+def test_encoder_matches_reference_golden(oracle):
+    games, hist, nh, tm, planes, binary = load_encode_golden()
+    assert binary                                   # the reference's planes are all 0/1, so bf16 is exact
+    enc = oracle.gomoku_encode(hist, nh, tm, 15, 19)
+    assert np.array_equal(enc, planes)
+    assert not planes[:, 17:].any()                 # attack/defense planes of the reference's CPU path are zero
+    assert np.array_equal(oracle.gomoku_encode(hist, nh, tm, 15, 17), planes[:, :17])
+
+
+def load_net_golden_a():
+    g = np.load(os.path.join(GOLD, "net_golden.npz"))
+    cin, S, blocks, F, A, pc, vc = [int(v) for v in g["a_cfg"]]
+    shapes = dict(synth.net_tensor_shapes(S, cin, F, blocks, A, pc, vc))
+    w = {k[4:]: g[k].astype(np.float32).reshape(shapes[k[4:]]) for k in g.files if k.startswith("a_w_")}
+    shape = tuple(g["a_x_shape"])
+    x = np.unpackbits(g["a_x_bits"])[: int(np.prod(shape))].reshape(shape).astype(np.float32)
+    return dict(cin=cin, S=S, blocks=blocks, F=F, A=A, pc=pc, vc=vc), w, x, g["a_logp"], g["a_value"]
+
+
+def load_net_golden_b():
+    g = np.load(os.path.join(GOLD, "net_golden.npz"))
+    shapes = synth.net_tensor_shapes(15, 17, 64, 10, 225, 32, 32)
+    w = synth.make_weights(shapes, seed=42, init="torch_default", bn="random")
+    x = synth.make_stone_planes(8, 15, 17, seed=1000)
+    assert sha(*[w[k] for k, _ in shapes]) == str(g["b_weights_sha256"]) and sha(x) == str(g["b_x_sha256"])
+    return w, x, g["b_logp"], g["b_value"]
+
+
+def test_network_restatement_matches_reference_golden():
+    from oracle import net_ref
+    cfg, w, x, logp, value = load_net_golden_a()
+    logits, v = net_ref.forward(w, x)
+    assert np.abs(net_ref.log_softmax(logits) - logp).max() < 2e-6 and np.abs(v - value).max() < 2e-6
+    w, x, logp, value = load_net_golden_b()
+    logits, v = net_ref.forward(w, x)
+    assert np.abs(net_ref.log_softmax(logits) - logp).max() < 2e-5 and np.abs(v - value).max() < 2e-6
+    # what the reference's own test asserts (tests/nn/neural_network_test.cpp:38-72)
+    assert logits.shape == (8, 225) and np.all(np.abs(v) <= 1) and np.allclose(np.exp(logp).sum(1), 1, atol=1e-5)
+
+
+# ---- live against the reference classes (only where oracle/_ref exists) -------------
+def _need_ref(oracle, which):
+    ok = oracle.have_ref_tree() if which == "tree" else oracle.have_ref_net()
+    if not ok:
+        pytest.skip("oracle/_ref not built here (the reference checkout is absent)")
+
+
+def test_selection_live_against_mctsnode(oracle):
+    _need_ref(oracle, "tree")
+    for nc, n_nodes, seed in ((225, 2048, 70), (362, 128, 71), (7, 256, 72)):
+        t = synth.make_selection_tree(n_nodes, nc, seed=seed)
+        sel_ref, a, r, _ = oracle.ref_select(t, c_puct=1.5, vl_value=3)
+        assert np.array_equal(oracle.puct_select(t, c_puct=1.5), sel_ref)
+    ops = [1, 2, 3, -3, -3, -5, 0, 0, 4, -1, -10, 0]
+    assert np.array_equal(oracle.vl_ops(0, ops), oracle.ref_vl_ops(0, ops))
+
+
+def test_backup_live_against_mctsnode(oracle):
+    _need_ref(oracle, "tree")
+    rng = np.random.default_rng(3)
+    for _ in range(20):
+        d = int(rng.integers(1, 9))
+        N = rng.integers(0, 20, d).astype(np.int32)
+        W = (N * rng.uniform(-1, 1, d)).astype(np.float32)
+        VL = rng.integers(0, 8, d).astype(np.int32)
+        leaf = float(np.float32(rng.uniform(-1, 1)))
+        # oracle on an edge table: path node i is edge (i, 0)
+        t = {"N": np.zeros((d, 4), np.int32), "W": np.zeros((d, 4), np.float32), "VL": np.zeros((d, 4), np.int32),
+             "node_visits": np.zeros(d, np.int32)}
+        t["N"][:, 0], t["W"][:, 0], t["VL"][:, 0] = N, W, VL
+        paths = np.zeros((1, d, 2), np.int32)
+        paths[0, :, 0] = np.arange(d)
+        oracle.backup(t, paths, [d], [leaf], vl_value=3)
+        rN, rVL, rmean = oracle.ref_backup_path(N, W, VL, leaf, 3)
+        assert np.array_equal(t["N"][:, 0], rN) and np.array_equal(t["VL"][:, 0], rVL)
+        assert np.array_equal((t["W"][:, 0] / t["N"][:, 0]).astype(np.float32), rmean)
+
+
+def test_encoder_live_against_gomokustate(oracle):
+    _need_ref(oracle, "tree")
+    games, hist, nh, tm = synth.make_gomoku_games(96, 15, seed=9)
+    ref, _ = oracle.ref_gomoku_encode_batch(games, 15)
+    assert np.array_equal(oracle.gomoku_encode(hist, nh, tm, 15, 19), ref)
+    games, hist, nh, tm = synth.make_gomoku_games(16, 9, seed=10, max_moves=30)
+    ref, _ = oracle.ref_gomoku_encode_batch(games, 9)
+    assert np.array_equal(oracle.gomoku_encode(hist, nh, tm, 9, 19), ref)
+
+
+def test_network_live_against_resnetmodel(oracle):
+    _need_ref(oracle, "net")
+    from oracle import net_ref
+    net = oracle.RefNet(17, 9, 2, 64, 81, seed=5)       # the shape of tests/nn/neural_network_test.cpp:17 with 64 filters
+    shapes = dict(synth.net_tensor_shapes(9, 17, 64, 2, 81, 32, 32))
+    w = {k: a.reshape(shapes[k]) for k, a in net.state().items() if "num_batches" not in k}
+    x = synth.make_stone_planes(4, 9, 19, seed=1)        # 19 planes in, 17 used (channel adaptation)
+    lp, v, _ = net.forward(x)
+    logits, val = net_ref.forward(w, x)
+    assert np.abs(net_ref.log_softmax(logits) - lp).max() < 2e-6 and np.abs(val - v).max() < 2e-6

@@ -1,0 +1,186 @@
+"""The tensor-core convolution layer and the whole network against fp32
+references, through the C ABI.
+
+Tolerances.  One layer: inputs and weights are bf16-exact, accumulation is
+fp32, the output is rounded to bf16 once, so |err| <= 2^-8 * |y| + 1e-5.
+Whole network: policy logits within 2e-2 and value within 1e-2 (max-abs) of the
+fp32 forward for the reference module's own initialisation and for seeded
+weights with random BatchNorm statistics; for the Kaiming-normal benchmark
+weights see test_network_kaiming_normal_benchmark_weights."""
+import numpy as np
+import pytest
+
+from omoknuni_small_b200 import synth
+from test_oracle import load_net_golden_a, load_net_golden_b
+
+pytestmark = pytest.mark.gpu
+
+POLICY_TOL, VALUE_TOL = 2e-2, 1e-2
+
+
+@pytest.fixture(scope="module")
+def api(lib):
+    from omoknuni_small_b200 import capi
+    return capi
+
+
+def bf16_round(a):
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
+
+
+def conv_case(api, B, S, cin_real, cin, residual, relu, seed):
+    import torch
+    import torch.nn.functional as F
+    rng = np.random.default_rng(seed)
+    x = bf16_round(rng.normal(0, 1, (B, cin_real, S, S)).astype(np.float32))
+    w = bf16_round(rng.normal(0, 0.1, (64, cin_real, 3, 3)).astype(np.float32))
+    bias = rng.normal(0, 0.5, 64).astype(np.float32)
+    res = bf16_round(rng.normal(0, 1, (B, 64, S, S)).astype(np.float32)) if residual else None
+    y = F.conv2d(torch.from_numpy(x), torch.from_numpy(w), padding=1).numpy() + bias[None, :, None, None]
+    if residual:
+        y = y + res
+    if relu:
+        y = np.maximum(y, 0)
+    xd = torch.from_numpy(api.planes_to_board_tensor_host(x, cin).view(np.int16)).cuda()
+    rd = torch.from_numpy(api.planes_to_board_tensor_host(res, 64).view(np.int16)).cuda() if residual else None
+    wd = torch.from_numpy(api.pack_conv3x3(w, None, cin).view(np.int16)).cuda()
+    bd = torch.from_numpy(bias).cuda()
+    # pre-fill the output with a pattern: the kernel must overwrite padding positions with zero
+    out = torch.full((int(api.lib().ob200_board_tensor_bytes(S, B, 64)) // 2,), 0x3F80, dtype=torch.int16, device="cuda")
+    PT = api.board_positions(S, B)
+    o3 = out.view(8, PT, 8)
+    o3[:, :api.GUARD] = 0
+    o3[:, PT - api.GUARD:] = 0
+    api.conv3x3(xd, wd, bd, rd, B, S, cin, 64, relu, out=out)
+    torch.cuda.synchronize()
+    assert api.device_error_code() == 0
+    got, pad_zero = api.board_tensor_to_planes(out.cpu().numpy().view(np.uint16), S, B, 64)
+    return got, y, pad_zero
+
+
+@pytest.mark.parametrize("B,S,cin_real,cin,residual,relu", [
+    (1, 15, 64, 64, False, False),
+    (2, 15, 64, 64, True, True),
+    (3, 15, 17, 32, False, True),      # the stem: 17 planes in a 32-channel tensor
+    (37, 15, 64, 64, True, True),      # more tiles than fit one wave of 4 stages per CTA? (74 tiles)
+    (700, 15, 64, 64, True, True),     # 1400 tiles: every CTA loops, stages and accumulators wrap
+    (5, 9, 64, 64, True, True),        # 10x10 grid: tiles straddle boards
+    (4, 19, 64, 64, False, True),      # 20x20 grid
+    (9, 5, 64, 64, True, False),
+])
+def test_conv3x3_layer(api, B, S, cin_real, cin, residual, relu):
+    got, want, pad_zero = conv_case(api, B, S, cin_real, cin, residual, relu, seed=B * 100 + S)
+    err = np.abs(got - want)
+    tol = np.abs(want) * 2.0 ** -8 + 1e-5
+    bad = np.argwhere(err > tol)
+    assert bad.size == 0, f"{len(bad)} of {err.size} elements off; first {bad[:5].tolist()}; max err {err.max():.4g}"
+    assert pad_zero, "padding / guard positions of the output are not zero"
+
+
+def make_net(api, w, cfg, max_batch):
+    return api.Net(cfg["cin"], cfg["S"], cfg["blocks"], cfg["F"], cfg["A"], cfg["pc"], cfg["vc"], 256, max_batch).load(w)
+
+
+def test_network_matches_reference_golden_default_init(api):
+    """The reference module with its own libtorch initialisation (fixture (a))."""
+    from oracle import net_ref
+    cfg, w, x, logp, value = load_net_golden_a()
+    net = make_net(api, w, cfg, 16)
+    logits, v = net.infer_planes(x, api.OUT_LOGITS)
+    assert np.abs(net_ref.log_softmax(logits) - logp).max() <= POLICY_TOL
+    assert np.abs(v - value).max() <= VALUE_TOL
+    probs, v2 = net.infer_planes(x, api.OUT_PROBS)
+    assert np.abs(probs - np.exp(logp)).max() <= 1e-3 and np.allclose(probs.sum(1), 1, atol=1e-5)
+    assert np.array_equal(v, v2)
+
+
+def test_network_matches_reference_golden_15x15(api):
+    """15x15, 10 blocks, reference 32/32 heads, seeded weights + random BatchNorm (fixture (b))."""
+    from oracle import net_ref
+    w, x, logp, value = load_net_golden_b()
+    cfg = dict(cin=17, S=15, blocks=10, F=64, A=225, pc=32, vc=32)
+    net = make_net(api, w, cfg, 8)
+    logits, v = net.infer_planes(x, api.OUT_LOGITS)
+    assert np.abs(net_ref.log_softmax(logits) - logp).max() <= POLICY_TOL
+    assert np.abs(v - value).max() <= VALUE_TOL
+
+
+@pytest.mark.parametrize("heads", [(2, 1), (32, 32)])
+def test_network_torch_default_init_benchmark_shape(api, heads):
+    """Benchmark network shape with the distribution the reference's C++ model is born with."""
+    from oracle import net_ref
+    shapes = synth.net_tensor_shapes(15, 17, 64, 10, 225, heads[0], heads[1])
+    w = synth.make_weights(shapes, seed=3, init="torch_default", bn="identity")
+    x = synth.make_stone_planes(64, 15, 17, seed=1001)
+    ref_logits, ref_v = net_ref.forward(w, x)
+    net = make_net(api, w, dict(cin=17, S=15, blocks=10, F=64, A=225, pc=heads[0], vc=heads[1]), 64)
+    logits, v = net.infer_planes(x, api.OUT_LOGITS)
+    assert np.abs(logits - ref_logits).max() <= POLICY_TOL
+    assert np.abs(v - ref_v).max() <= VALUE_TOL
+
+
+def test_network_kaiming_normal_benchmark_weights(api):
+    """The benchmark's weights (Kaiming-normal convolutions with ReLU gain, identity BatchNorm,
+    2/1-channel heads).  With this initialisation the residual stream doubles in variance per
+    block and a bf16 pipeline (8 significant bits per stored activation, 21 layers) sits about
+    0.1 (logits) / 0.02 (value) away from fp32 whatever kernel computes it.  So the kernel is
+    held to 2e-2 / 1e-2 against the fp32-arithmetic emulation of the same bf16 storage
+    (oracle/net_ref.forward_bf16), and the gap to the fp32 forward is bounded and printed."""
+    from oracle import net_ref
+    shapes = synth.net_tensor_shapes(15, 17, 64, 10, 225, 2, 1)
+    w = synth.make_weights(shapes, seed=42, init="kaiming_normal", bn="identity")
+    x = synth.make_stone_planes(256, 15, 17, seed=1000)
+    ref_logits, ref_v = net_ref.forward(w, x)
+    emu_logits, emu_v = net_ref.forward_bf16(w, x)
+    net = make_net(api, w, dict(cin=17, S=15, blocks=10, F=64, A=225, pc=2, vc=1), 256)
+    logits, v = net.infer_planes(x, api.OUT_LOGITS)
+    k_err, kv_err = np.abs(logits - emu_logits).max(), np.abs(v - emu_v).max()
+    f_err, fv_err = np.abs(logits - ref_logits).max(), np.abs(v - ref_v).max()
+    e_err = np.abs(emu_logits - ref_logits).max()
+    print(f"kaiming-normal: max|logit| {np.abs(ref_logits).max():.2f}; device vs bf16 emulation {k_err:.4f} / {kv_err:.4f}; "
+          f"device vs fp32 {f_err:.4f} / {fv_err:.4f}; bf16 emulation vs fp32 {e_err:.4f}")
+    assert k_err <= POLICY_TOL and kv_err <= VALUE_TOL
+    assert f_err <= 0.25 and fv_err <= 0.05                  # the bf16 storage gap itself
+    # the preferred move agrees wherever the fp32 margin exceeds twice the gap
+    order = np.argsort(ref_logits, 1)
+    rows = np.arange(len(order))
+    margin = ref_logits[rows, order[:, -1]] - ref_logits[rows, order[:, -2]]
+    assert (logits.argmax(1) == order[:, -1])[margin > 2 * f_err].all()
+
+
+def test_gomoku_inference_end_to_end(api, oracle):
+    """Host move histories -> encoder -> tower -> heads, against oracle encoder + fp32 forward,
+    including a batch smaller than max_batch after a larger one (buffer reuse)."""
+    from oracle import net_ref
+    shapes = synth.net_tensor_shapes(15, 19, 64, 10, 225, 32, 32)
+    w = synth.make_weights(shapes, seed=8, init="torch_default", bn="random")
+    net = api.Net(19, 15, 10, 64, 225, 32, 32, 256, 300).load(w)
+    for B, seed in ((300, 1), (5, 2), (129, 3)):
+        games, hist, nh, tm = synth.make_gomoku_games(B, 15, seed=seed)
+        planes = oracle.gomoku_encode(hist, nh, tm, 15, 19)
+        ref_logits, ref_v = net_ref.forward(w, planes)
+        probs, v = net.infer_gomoku(hist, nh, tm, api.OUT_PROBS)
+        assert np.abs(probs - net_ref.softmax(ref_logits)).max() <= 1e-3
+        assert np.abs(v - ref_v).max() <= VALUE_TOL
+        assert np.allclose(probs.sum(1), 1, atol=1e-5) and (probs >= 0).all()
+
+
+def test_inference_argument_errors(api):
+    shapes = synth.net_tensor_shapes(15, 17, 64, 1, 225, 2, 1)
+    w = synth.make_weights(shapes, seed=1, init="torch_default")
+    net = api.Net(17, 15, 1, 64, 225, 2, 1, 256, 4)
+    with pytest.raises(api.Error) as e:
+        net.infer_planes(np.zeros((1, 17, 15, 15), np.float32))
+    assert e.value.code == 4                                   # weights not finalised
+    missing = dict(w)
+    del missing["policy_fc.bias"]
+    with pytest.raises(api.Error) as e:
+        api.Net(17, 15, 1, 64, 225, 2, 1, 256, 4).load(missing)
+    assert e.value.code == 4 and "policy_fc.bias" in str(e.value)
+    net.load(w)
+    with pytest.raises(api.Error) as e:
+        net.infer_planes(np.zeros((5, 17, 15, 15), np.float32))
+    assert e.value.code == 7                                   # beyond max_batch
+    with pytest.raises(api.Error):
+        api.Net(17, 15, 1, 128, 225)                           # tower width outside this build
