@@ -1,0 +1,328 @@
+#!/usr/bin/env python
+"""Benchmark of the leaf-parallel evaluation path on B200.
+
+One "step" = one leaf batch through the hot path: Gomoku 15x15 positions ->
+bf16 input planes (encoder kernel) -> 10 x 64 residual tower + policy / value
+heads.  Headline metric: network leaf evaluations per second.
+
+  value     all ranks' evaluations / max-over-ranks device time, inputs (move
+            histories) already resident in HBM, outputs left in HBM.
+  e2e       the same through the host-buffer call a user makes
+            (ob200_net_infer_gomoku): host -> device copies of the histories
+            and device -> host copies of policy + value inside the timed region.
+  roofline  the dominant kernel (3x3 convolution, tensor-core bound): algorithmic
+            FLOPs of one launch / its average duration, against the measured
+            bf16 peak; timed live on a ping-pong loop of the very kernel.
+  selection batched PUCT selection + virtual-loss apply + revert over 65,536
+            nodes x 225 children (HBM bound), timed in the same run.
+  cpu_baseline  the reference's own CPU code (oracle/_ref: libtorch forward +
+            GomokuState encoder; else the oracle port) on a bounded sample.
+
+`--impl reference` times that CPU path alone with the same JSON keys.
+Multi-GPU: one process per GPU (torchrun), independent replicas, no data-path
+collective; per-GPU counters are summed after the timed region.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from omoknuni_small_b200 import synth  # noqa: E402
+
+NET = dict(board_size=15, input_channels=17, filters=64, blocks=10, policy_size=225, policy_head_ch=2,
+           value_head_ch=1, value_hidden=256)
+SEL_NODES, SEL_CHILDREN = 65536, 225
+METRIC, UNIT = "nn_leaf_evals_per_sec", "evals/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_burst=p["bf16_tflops"], bf16_sustained=p.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_burst=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.stop = index, [], threading.Event()
+        self.thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self.stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                self.rows.append([c.strip() for c in out.strip().split(",")])
+            except Exception:
+                pass
+            self.stop.wait(0.2)
+
+    def __enter__(self):
+        self.thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop.set()
+        self.thread.join(timeout=6)
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 7 and r[3 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_baseline(steps, warmup, sample_b=256):
+    """The reference's CPU path on a bounded sample: encode + forward of `sample_b` positions per step."""
+    from oracle import capi as oc, net_ref
+    shapes = synth.net_tensor_shapes(NET["board_size"], NET["input_channels"], NET["filters"], NET["blocks"],
+                                     NET["policy_size"], NET["policy_head_ch"], NET["value_head_ch"])
+    w = synth.make_weights(shapes, seed=42, init="kaiming_normal")
+    games, hist, nh, tm = synth.make_gomoku_games(sample_b, 15, seed=1000)
+    cores = os.cpu_count() or 1
+    kind = "reference" if (oc.have_ref_net() and oc.have_ref_tree()) else "port"
+    times = []
+    if kind == "reference":
+        # The reference class hard-codes 32-channel heads; the benchmark network has 2 / 1, so the
+        # reference class runs the tower it shares with the benchmark network and its own heads.
+        net = oc.RefNet(17, 15, NET["blocks"], 64, 225, seed=42)
+        for k, a in w.items():
+            if k.startswith(("input_", "res_blocks")):
+                net.set(k, a)
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            planes, _ = oc.ref_gomoku_encode_batch(games, 15, threads=cores)
+            net.forward(np.ascontiguousarray(planes[:, :17]), threads=cores)
+            if i >= warmup:
+                times.append(time.perf_counter() - t0)
+        what = (f"{sample_b} positions/step: reference GomokuState::getEnhancedTensorRepresentation (OpenMP) + "
+                f"ResNetModel::forward (libtorch CPU fp32, 32/32 heads), {cores} threads")
+    else:
+        for i in range(warmup + steps):
+            t0 = time.perf_counter()
+            planes = oc.gomoku_encode(hist, nh, tm, 15, 17, threads=cores)
+            net_ref.forward(w, planes, threads=cores)
+            if i >= warmup:
+                times.append(time.perf_counter() - t0)
+        what = f"{sample_b} positions/step: oracle port (C encoder + torch CPU fp32 forward), {cores} threads"
+    sec = float(np.mean(times))
+    return {"value": sample_b / sec, "unit": UNIT, "cores": cores, "kind": kind, "sample": what}, sec
+
+
+def selection_cpu_baseline(n_nodes=4096):
+    """MCTSNode::selectChild + applyVirtualLoss + revertVirtualLoss on real reference nodes (or the port)."""
+    from oracle import capi as oc
+    t = synth.make_selection_tree(n_nodes, SEL_CHILDREN, seed=7)
+    cores = os.cpu_count() or 1
+    if oc.have_ref_tree():
+        _, _, _, secs = oc.ref_select(t, repeats=5, threads=cores)
+        return {"value": n_nodes * 5 / secs, "unit": "selections/s", "cores": cores, "kind": "reference",
+                "sample": f"{n_nodes} parents x 225 children, 5 passes, real MCTSNode objects, OpenMP over parents"}
+    t0 = time.perf_counter()
+    for _ in range(5):
+        s = oc.puct_select(t, apply_vl=True, threads=cores)
+        oc.vl_revert(t, s, 3)
+    return {"value": n_nodes * 5 / (time.perf_counter() - t0), "unit": "selections/s", "cores": cores, "kind": "port",
+            "sample": f"{n_nodes} parents x 225 children, 5 passes, flat-array port"}
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base, sec = cpu_baseline(args.steps, max(1, min(args.warmup, 2)))
+    line = {"metric": METRIC, "value": base["value"], "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "gomoku15x15 leaf batch: encode + resnet 10x64 forward", "sample_batch": 256},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def gpu_arm(args):
+    import torch
+    from omoknuni_small_b200 import capi
+    import ctypes as C
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    capi.lib()                       # fails loudly when the CUDA library is missing
+    B, K, W = args.batch, args.steps, max(args.warmup, 3)
+    peaks = measured_peaks()
+    shapes = synth.net_tensor_shapes(NET["board_size"], NET["input_channels"], NET["filters"], NET["blocks"],
+                                     NET["policy_size"], NET["policy_head_ch"], NET["value_head_ch"])
+    w = synth.make_weights(shapes, seed=42, init="kaiming_normal")
+    net = capi.Net(17, 15, NET["blocks"], 64, 225, NET["policy_head_ch"], NET["value_head_ch"], 256, B, local).load(w)
+    games, hist, nh, tm = synth.make_gomoku_games(B, 15, seed=1000 + rank)
+    d_hist, d_nh, d_tm = (torch.from_numpy(a).to(dev) for a in (hist, nh, tm))
+    assert net.stride_positions() == capi.board_positions(15, B)
+    d_policy = torch.empty((B, 225), dtype=torch.float32, device=dev)
+    d_value = torch.empty(B, dtype=torch.float32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > 126 MB L2
+
+    def step_resident():
+        bt = capi.encode_gomoku(d_hist, d_nh, d_tm, 15, 17, net.input_tensor_channels())
+        net.forward_device(bt, B, d_policy, d_value, capi.OUT_PROBS)
+
+    def timed(fn, n, per_iter_flush=True):
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for s, e in ev:
+            if per_iter_flush:
+                flush.zero_()
+            s.record()
+            fn()
+            e.record()
+        torch.cuda.synchronize()
+        return [s.elapsed_time(e) for s, e in ev]
+
+    for _ in range(W):
+        step_resident()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    with sampler:
+        # ---- headline: K steps, device resident ----
+        barrier()
+        c0 = capi.counters()["kernel_launches"]
+        ms = timed(step_resident, K)
+        barrier()
+        launches = capi.counters()["kernel_launches"] - c0
+        total_ms = float(sum(ms))
+        # ---- e2e: host buffers through the public call ----
+        for _ in range(2):
+            net.infer_gomoku(hist, nh, tm)
+        e2e_s = 0.0
+        for _ in range(K):
+            flush.zero_()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            net.infer_gomoku(hist, nh, tm)
+            e2e_s += time.perf_counter() - t0
+        # ---- the dominant kernel alone: 64 -> 64 conv with residual + ReLU ----
+        rng = np.random.default_rng(0)
+        wp = torch.from_numpy(capi.pack_conv3x3(rng.normal(0, 0.04, (64, 64, 3, 3)).astype(np.float32), None, 64).view(np.int16)).to(dev)
+        bias = torch.zeros(64, device=dev)
+        n_el = int(capi.lib().ob200_board_tensor_bytes(15, B, 64)) // 2
+        bufs = [torch.zeros(n_el, dtype=torch.int16, device=dev) for _ in range(3)]
+        reps = 20
+
+        def conv_loop():
+            for i in range(reps):
+                capi.conv3x3(bufs[i % 3], wp, bias, bufs[(i + 2) % 3], B, 15, 64, 64, True, out=bufs[(i + 1) % 3])
+        conv_loop()
+        conv_ms = float(np.mean(timed(conv_loop, 5))) / reps
+        # ---- batched PUCT selection + virtual loss, 65,536 x 225 ----
+        t = synth.make_selection_tree(SEL_NODES, SEL_CHILDREN, seed=7 + rank)
+        dt = capi.DeviceTree(t, dev)
+        sel = torch.empty(SEL_NODES, dtype=torch.int32, device=dev)
+
+        def sel_pass():
+            dt.select(None, 1.5, 3, True, out=sel)
+            dt.vl_revert(sel, 3)
+
+        def sel_only():
+            dt.select(None, 1.5, 3, True, out=sel)
+        for _ in range(3):
+            sel_pass()
+        sel_ms = float(np.mean(timed(sel_pass, max(K, 10))))
+        dt.vl_revert(sel, 3)
+        selk_ms = float(np.mean(timed(sel_only, max(K, 10))))
+        torch.cuda.synchronize()
+    assert capi.device_error_code() == 0, "a kernel gave up on a bounded wait"
+
+    times = torch.tensor([total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        cnt = torch.tensor([capi.counters()["evals"]], dtype=torch.int64, device=dev)
+        dist.all_reduce(cnt)                     # the only cross-GPU step: summing per-GPU counters
+    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms = times.tolist()
+    if rank == 0:
+        flops_eval = synth.net_flops_per_eval(15, 17, 64, NET["blocks"], 225, NET["policy_head_ch"], NET["value_head_ch"])
+        value = world * B * K / (total_ms * 1e-3)
+        conv_flops = 2.0 * 225 * 9 * 64 * 64 * B
+        conv_tf = conv_flops / (conv_ms * 1e-3) / 1e12
+        sel_bytes = synth.selection_bytes_per_node(SEL_CHILDREN) * SEL_NODES
+        selk_bytes = sel_bytes - 16 * SEL_NODES      # the select kernel alone: without the revert's read-modify-write
+        clocks = sampler.summary()
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "gomoku15x15 leaf batch: encode + resnet 10x64 (2/1-channel heads) forward",
+                       "leaf_batch_per_gpu": B, "l2": "flushed between timed steps (256 MB write)",
+                       "replicas": world, "weights": "kaiming-normal seed 42, BN identity"},
+            "e2e": {"value": world * B * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": B * 34,
+                    "d2h_bytes_per_step": B * 226 * 4},
+            "gpu_launches": int(launches),
+            "tower_tflops": value / world * flops_eval / 1e12,
+            "roofline": {"kernel": "conv3x3_kernel<8> (64->64, residual+ReLU)", "bound": "tensor", "achieved": conv_tf,
+                         "peak": peaks["bf16_burst"], "unit": "TFLOP/s", "frac": conv_tf / peaks["bf16_burst"],
+                         "frac_of_sustained": conv_tf / peaks["bf16_sustained"] if peaks["bf16_sustained"] else None,
+                         "peak_source": peaks["source"] + " (burst: kernel timed alone)", "us_per_launch": conv_ms * 1e3,
+                         "traffic": None},
+            "selection": {"value": SEL_NODES / (sel_ms * 1e-3), "unit": "node selections/s (select + VL apply + VL revert)",
+                          "nodes": SEL_NODES, "children": SEL_CHILDREN, "ms_per_pass": sel_ms,
+                          "roofline": {"kernel": "puct_select_kernel", "bound": "hbm",
+                                       "achieved": selk_bytes / (selk_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                                       "unit": "GB/s", "frac": selk_bytes / (selk_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                       "peak_source": peaks["source"], "us_per_launch": selk_ms * 1e3, "traffic": None},
+                          "pass_gbs": sel_bytes / (sel_ms * 1e-3) / 1e9},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            base, _ = cpu_baseline(3, 1)
+            line["cpu_baseline"] = base
+            line["selection"]["cpu_baseline"] = selection_cpu_baseline()
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=1024, help="leaf batch per GPU")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()
