@@ -8,7 +8,7 @@
 // MCTSNode::selectChild (reference src/mcts/mcts_node.cpp:143-167), so no
 // FMA contraction or fast-math can change a comparison.  The argmax is a
 // shuffle butterfly whose combine rule keeps the lowest slot on equal scores.
-#include "common.h"
+#include "internal.h"
 #include <cfloat>
 
 namespace ob200 {
@@ -19,8 +19,6 @@ constexpr int kWarpsPerBlock = 8;
 struct Best {
     float score;   // best score seen with strict '>' starting from -inf
     int idx;       // its slot, -1 when nothing compared greater than -inf
-    int min_n;     // fewest visits among existing slots (fallback)
-    int min_idx;   // its slot, -1 when the row has no slot
 };
 
 __device__ __forceinline__ float puct_score(int n, float w, float p, int vl, float explore) {
@@ -31,11 +29,13 @@ __device__ __forceinline__ float puct_score(int n, float w, float p, int vl, flo
     return __fadd_rn(q, u);
 }
 
-__device__ __forceinline__ void consider(Best& b, int slot, int n, float w, float p, int vl,
+// Branch-free per slot: a slot that does not exist scores -inf, which the strict
+// '>' never takes (the reference never sees such a slot at all).
+__device__ __forceinline__ void consider(Best& b, int slot, bool legal, int n, float w, float p, int vl,
                                          float explore) {
-    const float s = puct_score(n, w, p, vl, explore);
+    float s = puct_score(n, w, p, vl, explore);
+    s = legal ? s : -INFINITY;
     if (s > b.score) { b.score = s; b.idx = slot; }
-    if (n < b.min_n) { b.min_n = n; b.min_idx = slot; }
 }
 
 __device__ __forceinline__ Best warp_combine(Best b) {
@@ -43,16 +43,31 @@ __device__ __forceinline__ Best warp_combine(Best b) {
     for (int off = 16; off > 0; off >>= 1) {
         const float os = __shfl_xor_sync(0xffffffffu, b.score, off);
         const int oi = __shfl_xor_sync(0xffffffffu, b.idx, off);
-        const int on = __shfl_xor_sync(0xffffffffu, b.min_n, off);
-        const int om = __shfl_xor_sync(0xffffffffu, b.min_idx, off);
         if (oi >= 0 && (b.idx < 0 || os > b.score || (os == b.score && oi < b.idx))) {
             b.score = os; b.idx = oi;
         }
-        if (om >= 0 && (b.min_idx < 0 || on < b.min_n || (on == b.min_n && om < b.min_idx))) {
-            b.min_n = on; b.min_idx = om;
-        }
     }
     return b;
+}
+
+// The reference's fallback when no score compared greater than -inf (all NaN or
+// -inf): the least-visited existing child, first one on ties
+// (src/mcts/mcts_node.cpp:173-181).  Rare, so it is a second scan of N only.
+__device__ __noinline__ int least_visited_row(const ob200_tree_view& t, int node, int lane) {
+    const int32_t* N = t.N + (size_t)node * t.pitch;
+    const uint32_t* mask = t.legal_bits + (size_t)node * t.mask_words;
+    int mn = INT_MAX, mi = -1;
+    for (int s = lane; s < t.n_children; s += 32)
+        if ((mask[s >> 5] >> (s & 31)) & 1u) {
+            const int n = N[s];
+            if (n < mn) { mn = n; mi = s; }
+        }
+    for (int off = 16; off > 0; off >>= 1) {
+        const int on = __shfl_xor_sync(0xffffffffu, mn, off);
+        const int om = __shfl_xor_sync(0xffffffffu, mi, off);
+        if (om >= 0 && (mi < 0 || on < mn || (on == mn && om < mi))) { mn = on; mi = om; }
+    }
+    return mi;
 }
 
 // Scans one row with the whole warp.  kStream: N/W/P are read with streaming
@@ -69,46 +84,39 @@ __device__ __forceinline__ int select_row(const ob200_tree_view& t, int node, fl
     const uint32_t* __restrict__ mask = t.legal_bits + (size_t)node * t.mask_words;
     const float explore = __fmul_rn(c_puct, __fsqrt_rn((float)t.node_visits[node]));
 
-    Best b{-INFINITY, -1, INT_MAX, -1};
+    Best b{-INFINITY, -1};
     for (int v0 = 0; v0 < nvec; v0 += 64) {
-        // two independent load rounds in flight per lane
+        // two independent load rounds in flight per lane; out-of-range lanes re-read vector 0
+        // with an empty mask, so that the arithmetic below has no branches
         const int va = v0 + lane, vb = v0 + 32 + lane;
         const bool ha = va < nvec, hb = vb < nvec;
-        int4 na, nb, la, lb; float4 wa, wb, pa, pb; uint32_t ma = 0, mb = 0;
-        if (ha) {
-            na = kStream ? __ldcs(N4 + va) : __ldcg(N4 + va);
-            wa = kStream ? __ldcs(W4 + va) : __ldcg(W4 + va);
-            pa = kStream ? __ldcs(P4 + va) : __ldcg(P4 + va);
-            la = __ldcg(V4 + va);
-            ma = (__ldg(mask + (va >> 3)) >> ((va & 7) * 4)) & 0xFu;
-        }
-        if (hb) {
-            nb = kStream ? __ldcs(N4 + vb) : __ldcg(N4 + vb);
-            wb = kStream ? __ldcs(W4 + vb) : __ldcg(W4 + vb);
-            pb = kStream ? __ldcs(P4 + vb) : __ldcg(P4 + vb);
-            lb = __ldcg(V4 + vb);
-            mb = (__ldg(mask + (vb >> 3)) >> ((vb & 7) * 4)) & 0xFu;
-        }
-        if (ha && ma) {
-            const int s = va * 4;
-            if (ma & 1u) consider(b, s + 0, na.x, wa.x, pa.x, la.x, explore);
-            if (ma & 2u) consider(b, s + 1, na.y, wa.y, pa.y, la.y, explore);
-            if (ma & 4u) consider(b, s + 2, na.z, wa.z, pa.z, la.z, explore);
-            if (ma & 8u) consider(b, s + 3, na.w, wa.w, pa.w, la.w, explore);
-        }
-        if (hb && mb) {
-            const int s = vb * 4;
-            if (mb & 1u) consider(b, s + 0, nb.x, wb.x, pb.x, lb.x, explore);
-            if (mb & 2u) consider(b, s + 1, nb.y, wb.y, pb.y, lb.y, explore);
-            if (mb & 4u) consider(b, s + 2, nb.z, wb.z, pb.z, lb.z, explore);
-            if (mb & 8u) consider(b, s + 3, nb.w, wb.w, pb.w, lb.w, explore);
-        }
+        const int ia = ha ? va : 0, ib = hb ? vb : 0;
+        const int4 na = kStream ? __ldcs(N4 + ia) : __ldcg(N4 + ia);
+        const float4 wa = kStream ? __ldcs(W4 + ia) : __ldcg(W4 + ia);
+        const float4 pa = kStream ? __ldcs(P4 + ia) : __ldcg(P4 + ia);
+        const int4 la = __ldcg(V4 + ia);
+        const int4 nb = kStream ? __ldcs(N4 + ib) : __ldcg(N4 + ib);
+        const float4 wb = kStream ? __ldcs(W4 + ib) : __ldcg(W4 + ib);
+        const float4 pb = kStream ? __ldcs(P4 + ib) : __ldcg(P4 + ib);
+        const int4 lb = __ldcg(V4 + ib);
+        const uint32_t ma = ha ? (__ldg(mask + (ia >> 3)) >> ((ia & 7) * 4)) & 0xFu : 0u;
+        const uint32_t mb = hb ? (__ldg(mask + (ib >> 3)) >> ((ib & 7) * 4)) & 0xFu : 0u;
+        const int sa = va * 4, sb = vb * 4;
+        consider(b, sa + 0, ma & 1u, na.x, wa.x, pa.x, la.x, explore);
+        consider(b, sa + 1, ma & 2u, na.y, wa.y, pa.y, la.y, explore);
+        consider(b, sa + 2, ma & 4u, na.z, wa.z, pa.z, la.z, explore);
+        consider(b, sa + 3, ma & 8u, na.w, wa.w, pa.w, la.w, explore);
+        consider(b, sb + 0, mb & 1u, nb.x, wb.x, pb.x, lb.x, explore);
+        consider(b, sb + 1, mb & 2u, nb.y, wb.y, pb.y, lb.y, explore);
+        consider(b, sb + 2, mb & 4u, nb.z, wb.z, pb.z, lb.z, explore);
+        consider(b, sb + 3, mb & 8u, nb.w, wb.w, pb.w, lb.w, explore);
     }
     b = warp_combine(b);
-    return b.idx >= 0 ? b.idx : b.min_idx;
+    if (b.idx < 0) return least_visited_row(t, node, lane);
+    return b.idx;
 }
 
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
 puct_select_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids, int n, float c_puct,
                    int vl_value, int apply_vl, int32_t* __restrict__ sel_out) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -120,6 +128,113 @@ puct_select_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids, int 
     if (lane == 0) {
         sel_out[warp] = sel;
         if (sel >= 0 && apply_vl && vl_value > 0) atomicAdd(t.VL + (size_t)node * t.pitch + sel, vl_value);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Staged variant for rows of up to 256 slots: a persistent grid, every warp
+// walks its own list of nodes and keeps a two-deep ring of rows in shared
+// memory, filled by 1-D bulk async copies (one per array row, completion on an
+// mbarrier).  The copies of the next node are in flight while the current one
+// is scored from shared memory, so HBM latency is hidden by the ring instead of
+// by occupancy, and the registers are free for the arithmetic.
+// ---------------------------------------------------------------------------
+constexpr int kStagedWarps = 24;
+constexpr int kStagedDepth = 2;
+constexpr int kStagedMaxPitch = 256;
+constexpr uint32_t kStagedSpin = 1u << 24;
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kStagedSpin; ++i) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void row_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(kStagedWarps * 32, 1)
+puct_select_staged_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids, int n, float c_puct,
+                          int vl_value, int apply_vl, int32_t* __restrict__ sel_out, int* error_word) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row_bytes = t.pitch * 4, mask_bytes = t.mask_words * 4;
+    const int stage_bytes = (4 * row_bytes + mask_bytes + 127) & ~127;
+    uint8_t* ring = smem + (size_t)warp * kStagedDepth * stage_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kStagedWarps * kStagedDepth * stage_bytes) + warp * kStagedDepth;
+    if (lane == 0) {
+        for (int d = 0; d < kStagedDepth; ++d)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_u32(bars + d)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
+    const int total_warps = gridDim.x * kStagedWarps;
+    const int first = blockIdx.x * kStagedWarps + warp;
+    const int nvec = t.pitch >> 2;
+
+    auto fetch = [&](int i, int stage) {       // lane 0 only
+        const int node = node_ids ? node_ids[i] : i;
+        if (node < 0 || node >= t.n_nodes) return;     // nothing to copy; the consumer skips it too
+        const uint32_t bar = s_u32(bars + stage);
+        const uint32_t dst = s_u32(ring + (size_t)stage * stage_bytes);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(4 * row_bytes + mask_bytes)) : "memory");
+        const size_t off = (size_t)node * t.pitch;
+        row_copy(dst, t.N + off, row_bytes, bar);
+        row_copy(dst + row_bytes, t.W + off, row_bytes, bar);
+        row_copy(dst + 2 * row_bytes, t.P + off, row_bytes, bar);
+        row_copy(dst + 3 * row_bytes, t.VL + off, row_bytes, bar);
+        row_copy(dst + 4 * row_bytes, t.legal_bits + (size_t)node * t.mask_words, mask_bytes, bar);
+    };
+
+    if (first < n && lane == 0) fetch(first, 0);
+    uint32_t phase_bits = 0;                   // one parity bit per stage
+    int k = 0;
+    for (int i = first; i < n; i += total_warps, ++k) {
+        const int stage = k % kStagedDepth;
+        const int nxt = i + total_warps;
+        __syncwarp();                           // every lane is done reading the stage about to be refilled
+        if (nxt < n && lane == 0) fetch(nxt, (k + 1) % kStagedDepth);
+        const int node = node_ids ? node_ids[i] : i;
+        int sel = -1;
+        if (node >= 0 && node < t.n_nodes) {
+            const float explore = __fmul_rn(c_puct, __fsqrt_rn((float)__ldg(t.node_visits + node)));
+            if (!bar_wait(s_u32(bars + stage), (phase_bits >> stage) & 1u)) {
+                if (lane == 0) atomicExch(error_word, 4);
+                break;
+            }
+            phase_bits ^= 1u << stage;
+            const uint8_t* st = ring + (size_t)stage * stage_bytes;
+            const int4* N4 = reinterpret_cast<const int4*>(st);
+            const float4* W4 = reinterpret_cast<const float4*>(st + row_bytes);
+            const float4* P4 = reinterpret_cast<const float4*>(st + 2 * row_bytes);
+            const int4* V4 = reinterpret_cast<const int4*>(st + 3 * row_bytes);
+            const uint32_t* mask = reinterpret_cast<const uint32_t*>(st + 4 * row_bytes);
+            Best b{-INFINITY, -1};
+            for (int v = lane; v < nvec; v += 32) {
+                const int4 nn = N4[v]; const float4 ww = W4[v]; const float4 pp = P4[v]; const int4 ll = V4[v];
+                const uint32_t m = (mask[v >> 3] >> ((v & 7) * 4)) & 0xFu;
+                const int s0 = v * 4;
+                consider(b, s0 + 0, m & 1u, nn.x, ww.x, pp.x, ll.x, explore);
+                consider(b, s0 + 1, m & 2u, nn.y, ww.y, pp.y, ll.y, explore);
+                consider(b, s0 + 2, m & 4u, nn.z, ww.z, pp.z, ll.z, explore);
+                consider(b, s0 + 3, m & 8u, nn.w, ww.w, pp.w, ll.w, explore);
+            }
+            b = warp_combine(b);
+            sel = b.idx >= 0 ? b.idx : least_visited_row(t, node, lane);
+        }
+        if (lane == 0) {
+            sel_out[i] = sel;
+            if (sel >= 0 && apply_vl && vl_value > 0) atomicAdd(t.VL + (size_t)node * t.pitch + sel, vl_value);
+        }
     }
 }
 
@@ -270,10 +385,31 @@ int ob200_launch_puct_select(const ob200_tree_view* tree, const int32_t* node_id
     if (n < 0 || (!node_ids && n > tree->n_nodes) || !sel_out)
         return set_error(OB200_ERR_INVALID, "ob200_launch_puct_select: bad n (%d) or null output", n);
     if (int rc = require_device()) return rc;
-    const int blocks = (n + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    puct_select_kernel<<<blocks, kWarpsPerBlock * 32, 0, as_stream(stream)>>>(*tree, node_ids, n, c_puct, vl_value,
-                                                                             apply_vl, sel_out);
-    OB200_LAUNCHED("puct_select_kernel");
+    if (tree->pitch <= kStagedMaxPitch && (tree->mask_words & 3) == 0 && n >= 1024) {
+        // rows small enough to ring-buffer in shared memory: persistent staged kernel
+        int dev = 0, sms = 0;
+        OB200_CUDA_OK(cudaGetDevice(&dev));
+        OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        const int stage_bytes = (4 * tree->pitch * 4 + tree->mask_words * 4 + 127) & ~127;
+        const int smem = kStagedWarps * kStagedDepth * stage_bytes + kStagedWarps * kStagedDepth * 8;
+        static bool configured[64] = {false};
+        if (dev >= 0 && dev < 64 && !configured[dev]) {
+            OB200_CUDA_OK(cudaFuncSetAttribute(puct_select_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               kStagedWarps * kStagedDepth * ((4 * kStagedMaxPitch * 4 + 64 * 4 + 127) & ~127) + kStagedWarps * kStagedDepth * 8));
+            configured[dev] = true;
+        }
+        int* errw = device_error_word();
+        if (!errw) return set_error(OB200_ERR_CUDA, "ob200_launch_puct_select: cannot resolve the device error word");
+        const int want = (n + kStagedWarps - 1) / kStagedWarps;
+        puct_select_staged_kernel<<<want < sms ? want : sms, kStagedWarps * 32, smem, as_stream(stream)>>>(
+            *tree, node_ids, n, c_puct, vl_value, apply_vl, sel_out, errw);
+        OB200_LAUNCHED("puct_select_staged_kernel");
+    } else {
+        const int blocks = (n + kWarpsPerBlock - 1) / kWarpsPerBlock;
+        puct_select_kernel<<<blocks, kWarpsPerBlock * 32, 0, as_stream(stream)>>>(*tree, node_ids, n, c_puct, vl_value,
+                                                                                 apply_vl, sel_out);
+        OB200_LAUNCHED("puct_select_kernel");
+    }
     counters().selections.fetch_add((uint64_t)n, std::memory_order_relaxed);
     return OB200_OK;
 }

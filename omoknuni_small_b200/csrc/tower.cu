@@ -16,7 +16,7 @@
 //     all 9 taps; zero columns/rows/guards in the tensor are the padding.
 // Weights (BatchNorm folded, bf16) stay resident in shared memory for the
 // whole launch.  Warp 0 produces (bulk copies), warp 1 issues the MMAs, warps
-// 2-5 run the epilogue (TMEM -> registers, + bias, + residual, ReLU, zero the
+// 2-9 (two warpgroups on alternate tiles) run the epilogue (TMEM -> registers, + bias, + residual, ReLU, zero the
 // padding positions, bf16, 16-byte coalesced stores).  Four shared-memory
 // stages and four TMEM accumulators decouple the three roles.
 //
@@ -38,7 +38,8 @@ constexpr int kChunkBytes = kTileRows * 16;             // 3072
 constexpr int kStages = 4;
 constexpr int kAccStages = 4;
 constexpr int kTmemCols = kAccStages * kCout;           // 256 (power of two)
-constexpr int kThreads = 192;
+constexpr int kEpiGroups = 2;           // epilogue warpgroups, alternating tiles
+constexpr int kThreads = 64 + 128 * kEpiGroups;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct ConvParams {
@@ -224,12 +225,35 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const ConvParams p
         }
     } else {
         // ---------------- epilogue: TMEM -> registers -> global ----------------
+        // Two warpgroups take alternate tiles.  A thread owns one position (TMEM lane) and
+        // all 64 channels; the residual is fetched before the wait on the accumulator so
+        // that its latency hides behind the MMAs of the tile.
         const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+        const int group = (warp - 2) >> 2;
         const int row = q * 32 + lane;
-        int it = 0;
-        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+        const uint8_t* __restrict__ resid = p.residual;
+        uint8_t* __restrict__ outp = p.out;
+        const int P = (int)p.P;
+        int it = group;
+        for (int tile = blockIdx.x + group * gridDim.x; tile < p.num_tiles; tile += kEpiGroups * gridDim.x, it += kEpiGroups) {
             const int a = it % kAccStages;
             const uint32_t pa = (uint32_t)(it / kAccStages) & 1u;
+            const int pos = tile * kTileM + row;
+            bool valid = pos < P;
+            if (valid) {
+                const int rr = pos % p.slots;
+                valid = (rr / p.GP < p.S) && (rr % p.GP < p.S);
+            }
+            const long long rec = (long long)OB200_GUARD + pos;
+            uint4 rs[kCout / 8];
+            if (resid != nullptr && valid) {
+#pragma unroll
+                for (int c = 0; c < kCout / 8; ++c)
+                    rs[c] = __ldg(reinterpret_cast<const uint4*>(resid + ((long long)c * p.PT + rec) * 16));
+            } else {
+#pragma unroll
+                for (int c = 0; c < kCout / 8; ++c) rs[c] = make_uint4(0u, 0u, 0u, 0u);
+            }
             if (!mbar_wait(accfull_bar(a), pa, abort_flag)) {
                 *abort_flag = 1; atomicExch(p.error, 3); break;
             }
@@ -242,40 +266,24 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const ConvParams p
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(accempty_bar(a));
-
-            const long long pos = (long long)tile * kTileM + row;
-            bool valid = pos < p.P;
-            if (valid) {
-                const int rr = (int)(pos % p.slots);
-                valid = (rr / p.GP < p.S) && (rr % p.GP < p.S);
-            }
-            const long long rec = (long long)OB200_GUARD + pos;
 #pragma unroll
             for (int c = 0; c < kCout / 8; ++c) {
-                Pack8 o;
+                uint4 o = make_uint4(0u, 0u, 0u, 0u);
                 if (valid) {
-                    float v[8];
+                    const uint32_t rw[4] = {rs[c].x, rs[c].y, rs[c].z, rs[c].w};
+                    uint32_t ow[4];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[c * 8 + j]) + bias_s[c * 8 + j];
-                    if (p.residual) {
-                        const Pack8 rs = *reinterpret_cast<const Pack8*>(p.residual + ((long long)c * p.PT + rec) * 16);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float2 f = __bfloat1622float2(rs.v[j]);
-                            v[2 * j] += f.x; v[2 * j + 1] += f.y;
-                        }
+                    for (int j = 0; j < 4; ++j) {
+                        // bf16 -> fp32 is a 16-bit shift
+                        float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bias_s[c * 8 + 2 * j] + __uint_as_float(rw[j] << 16);
+                        float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bias_s[c * 8 + 2 * j + 1] + __uint_as_float(rw[j] & 0xFFFF0000u);
+                        if (p.relu) { v0 = fmaxf(v0, 0.0f); v1 = fmaxf(v1, 0.0f); }
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                        ow[j] = *reinterpret_cast<const uint32_t*>(&h);
                     }
-                    if (p.relu) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.0f);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) o.v[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) o.v[j] = __floats2bfloat162_rn(0.0f, 0.0f);
+                    o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                 }
-                *reinterpret_cast<Pack8*>(p.out + ((long long)c * p.PT + rec) * 16) = o;
+                *reinterpret_cast<uint4*>(outp + ((long long)c * p.PT + rec) * 16) = o;
             }
         }
     }

@@ -68,6 +68,31 @@ def test_select_edge_cases(api, oracle):
     dt.select(torch.zeros(0, dtype=torch.int32, device="cuda"))
 
 
+def test_select_staged_path_with_node_ids(api, oracle):
+    """Launches of >= 1024 entries on rows of <= 256 slots take the shared-memory staged
+    kernel: node list with repeats and out-of-range ids, with and without virtual loss."""
+    import torch
+    t = synth.make_selection_tree(2048, 225, seed=23)
+    t["legal_bits"][5] = 0
+    t["W"][9, :225] = np.nan
+    rng = np.random.default_rng(4)
+    ids = rng.integers(0, 2048, 5000).astype(np.int32)
+    ids[17], ids[18], ids[19], ids[20] = -1, 2048, 5, 9
+    dt = api.DeviceTree(t)
+    sel = dt.select(torch.from_numpy(ids).cuda(), c_puct=1.5, vl_value=3, apply_vl=False).cpu().numpy()
+    want = np.full(len(ids), -1, np.int32)
+    ok = (ids >= 0) & (ids < 2048)
+    want[ok] = oracle.puct_select(synth.copy_tree(t), ids[ok], c_puct=1.5, vl_value=3, apply_vl=False)
+    assert np.array_equal(sel, want)
+    assert api.device_error_code() == 0
+    # distinct nodes with virtual loss applied: state matches the oracle exactly
+    ids = rng.permutation(2048)[:1500].astype(np.int32)
+    ref = synth.copy_tree(t)
+    sel = dt.select(torch.from_numpy(ids).cuda(), c_puct=1.5, vl_value=3, apply_vl=True).cpu().numpy()
+    assert np.array_equal(sel, oracle.puct_select(ref, ids, c_puct=1.5, vl_value=3, apply_vl=True))
+    assert np.array_equal(dt.host("VL"), ref["VL"])
+
+
 def test_vl_revert_clamps_at_zero(api, oracle):
     import torch
     t = synth.make_selection_tree(128, 225, seed=22, vl_max=2)
