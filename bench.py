@@ -186,7 +186,6 @@ def gpu_arm(args):
     net = capi.Net(17, 15, NET["blocks"], 64, 225, NET["policy_head_ch"], NET["value_head_ch"], 256, B, local).load(w)
     games, hist, nh, tm = synth.make_gomoku_games(B, 15, seed=1000 + rank)
     d_hist, d_nh, d_tm = (torch.from_numpy(a).to(dev) for a in (hist, nh, tm))
-    assert net.stride_positions() == capi.board_positions(15, B)
     d_policy = torch.empty((B, 225), dtype=torch.float32, device=dev)
     d_value = torch.empty(B, dtype=torch.float32, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > 126 MB L2

@@ -154,17 +154,19 @@ int ob200_launch_traverse(const ob200_tree_view* tree, const int32_t* roots, int
 /* ------------------------------------------------------------------------- *
  *  Board tensors: the activation format of the encoder and the network.
  *
- *  bf16, channels-last blocked by 8 ("NHWC8"): element (channel c, board b,
- *  row y, column x) lives at
- *        ((c / 8) * PT + G + b * slots + y * GP + x) * 8 + (c % 8)
+ *  bf16, NHWC: element (channel c, board b, row y, column x) of a tensor with C
+ *  channels lives at
+ *        (G + b * slots + y * GP + x) * C + c
  *  with GP = board_size + 1 (one zero column after each row), slots = GP * GP
  *  (one zero row after each board), G = OB200_GUARD zero positions before the
- *  first and after the last board, and PT = 2 * G + roundup(B * slots, 128).
- *  The zero column / row / guards are the 3x3 convolution's padding; every
- *  producer writes them as zero.
+ *  first and after the last board; the tensor has PT = 2 * G +
+ *  roundup(B * slots, 128) positions.  The zero column / row / guards are the
+ *  3x3 convolution's padding; every producer writes them as zero.  With C = 64
+ *  one position is one 128-byte row, which is what the tensor-core kernel's
+ *  TMA boxes and 128-byte-swizzled shared-memory tiles are built on.
  * ------------------------------------------------------------------------- */
 #define OB200_GUARD 32
-/* Positions per channel block (PT above) for a batch of B boards. */
+/* Positions (PT above) of a board tensor for a batch of B boards. */
 int64_t ob200_board_tensor_positions(int32_t board_size, int32_t B);
 /* Bytes of a board tensor with `channels` channels (rounded up to 8). */
 int64_t ob200_board_tensor_bytes(int32_t board_size, int32_t B, int32_t channels);
@@ -205,17 +207,19 @@ int ob200_launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int
  * Replaces one conv + BatchNorm2d + relu (+ residual add) group of
  * ResNetResidualBlock::forward / ResNetModel::forward
  * (src/nn/resnet_model.cpp:43-49,150).  `packed_w` comes from
- * ob200_pack_conv3x3_weights.  in: cin channels (multiple of 16), out and
- * residual: cout channels; cout must be 64 in this build. */
+ * ob200_pack_conv3x3_weights.  in, out and residual are 64-channel board
+ * tensors of B boards (cin = cout = 64 in this build; a layer with fewer real
+ * input channels, like the stem, runs with zero weights on the rest). */
 int ob200_launch_conv3x3(const void* in, const void* packed_w, const float* bias,
                          const void* residual, void* out, int32_t B, int32_t board_size,
                          int32_t cin, int32_t cout, int32_t relu, ob200_stream stream);
-/* Bytes of the packed bf16 weight image for (cin, cout). */
+/* Bytes of the packed bf16 weight image for (cin, cout); 0 when unsupported. */
 int64_t ob200_packed_conv3x3_bytes(int32_t cin, int32_t cout);
 /* Host helper: fp32 OIHW weights [cout][cin_real][3][3] scaled per output
  * channel by scale[cout] (the folded BatchNorm factor; NULL = 1) -> packed
  * bf16 image for cin >= cin_real input channels (extra channels get zero
- * weights).  Output is HOST memory of ob200_packed_conv3x3_bytes(cin, cout). */
+ * weights).  Output is HOST memory of ob200_packed_conv3x3_bytes(cin, cout);
+ * copy it to the device for ob200_launch_conv3x3. */
 int ob200_pack_conv3x3_weights(const float* w_oihw, const float* scale, int32_t cout,
                                int32_t cin_real, int32_t cin, void* packed_out);
 
@@ -273,19 +277,17 @@ int ob200_net_infer_gomoku(ob200_net* net, const int16_t* history, const uint8_t
                            const uint8_t* to_move, int32_t B, float* policy_out,
                            float* value_out, int32_t out_kind);
 /* DEVICE in, DEVICE out, asynchronous on `stream`: input is a board tensor of
- * ob200_net_input_tensor_channels() channels whose channel blocks are
- * ob200_net_stride_positions() positions apart (B <= max_batch boards in it). */
+ * ob200_net_input_tensor_channels() channels holding B <= max_batch boards
+ * (ob200_board_tensor_bytes(board_size, B, channels) bytes, 16-byte aligned). */
 int ob200_net_forward_device(ob200_net* net, const void* input_board_tensor, int32_t B,
                              float* policy_out, float* value_out, int32_t out_kind,
                              ob200_stream stream);
 /* Device pointer of the tower's output board tensor of the last forward
  * (filters channels), for tests. */
 const void* ob200_net_debug_tower_output(ob200_net* net);
-/* Layout of the handle's own board tensors, which ob200_net_forward_device
- * expects of its input: positions between channel blocks (sized once for
- * max_batch, so that one buffer serves every batch size) and the channel
- * count of the input tensor (input_channels rounded up to 32 or 64). */
-int64_t ob200_net_stride_positions(ob200_net* net);
+/* Channel count of the input board tensor ob200_net_forward_device expects
+ * (64: the stem runs on the same 64-channel kernel as the tower, with zero
+ * weights for the channels beyond input_channels). */
 int32_t ob200_net_input_tensor_channels(ob200_net* net);
 
 /* Reads and clears the current device's error word, which a kernel raises when

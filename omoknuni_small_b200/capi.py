@@ -74,7 +74,6 @@ SIGNATURES = {
     "ob200_net_forward_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
                                            C.c_void_p]),
     "ob200_net_debug_tower_output": (C.c_void_p, [C.c_void_p]),
-    "ob200_net_stride_positions": (C.c_int64, [C.c_void_p]),
     "ob200_net_input_tensor_channels": (C.c_int32, [C.c_void_p]),
     "ob200_device_error_code": (C.c_int, [C.POINTER(C.c_int32)]),
     "ob200_get_counters": (C.c_int, [C.POINTER(Counters)]),
@@ -190,42 +189,39 @@ def board_positions(board_size, B):
     return int(lib().ob200_board_tensor_positions(board_size, B))
 
 
-def board_tensor_to_planes(bt_u16, board_size, B, channels, stride_positions=None):
-    """bf16 board tensor (numpy uint16 view, flat) -> fp32 planes [B, channels, S, S]
-    plus a flag telling whether every padding / guard element covered by the
-    batch is zero.  Host-side helper for tests."""
+def board_tensor_to_planes(bt_u16, board_size, B, channels):
+    """bf16 NHWC board tensor (numpy uint16 view, flat, `channels` rounded up to 8
+    per position) -> fp32 planes [B, channels, S, S] plus a flag telling whether
+    every padding / guard element is zero.  Host-side helper for tests."""
     S, GP = board_size, board_size + 1
     slots = GP * GP
     PT = board_positions(S, B)
-    stride = stride_positions or PT
-    chunks = (channels + 7) // 8
-    a = np.asarray(bt_u16).reshape(-1)[: chunks * stride * 8].reshape(chunks, stride, 8)[:, :PT]
+    Cp = (channels + 7) // 8 * 8
+    a = np.asarray(bt_u16).reshape(-1)[: PT * Cp].reshape(PT, Cp)
     f = (a.astype(np.uint32) << 16).view(np.float32)
-    body = f[:, GUARD:GUARD + B * slots].reshape(chunks, B, GP, GP, 8)
-    planes = body[:, :, :S, :S, :].transpose(1, 0, 4, 2, 3).reshape(B, chunks * 8, S, S)[:, :channels]
-    pad_zero = (not f[:, :GUARD].any() and not f[:, GUARD + B * slots:].any()
-                and not body[:, :, S, :, :].any() and not body[:, :, :, S, :].any())
+    body = f[GUARD:GUARD + B * slots].reshape(B, GP, GP, Cp)
+    planes = body[:, :S, :S, :channels].transpose(0, 3, 1, 2)
+    pad_zero = (not f[:GUARD].any() and not f[GUARD + B * slots:].any()
+                and not body[:, S, :, :].any() and not body[:, :, S, :].any())
     return np.ascontiguousarray(planes), bool(pad_zero)
 
 
-def planes_to_board_tensor_host(planes, out_channels, stride_positions=None):
-    """fp32 planes [B, C, S, S] -> bf16 board tensor as a flat numpy uint16 array
-    (round to nearest even), the host-side twin of the device conversion."""
+def planes_to_board_tensor_host(planes, out_channels):
+    """fp32 planes [B, C, S, S] -> bf16 NHWC board tensor as a flat numpy uint16
+    array (round to nearest even), the host-side twin of the device conversion."""
     B, Cc, S, _ = planes.shape
     GP = S + 1
     PT = board_positions(S, B)
-    stride = stride_positions or PT
-    chunks = out_channels // 8
-    full = np.zeros((chunks * 8, B, GP, GP), np.float32)
-    full[:Cc, :, :S, :S] = planes.transpose(1, 0, 2, 3)
+    full = np.zeros((B, GP, GP, out_channels), np.float32)
+    full[:, :S, :S, :Cc] = planes.transpose(0, 2, 3, 1)
     u = full.view(np.uint32)
     r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
-    out = np.zeros((chunks, stride, 8), np.uint16)
-    out[:, GUARD:GUARD + B * GP * GP, :] = r.reshape(chunks, 8, B * GP * GP).transpose(0, 2, 1)
+    out = np.zeros((PT, out_channels), np.uint16)
+    out[GUARD:GUARD + B * GP * GP] = r.reshape(B * GP * GP, out_channels)
     return out.reshape(-1)
 
 
-def encode_gomoku(history, n_hist, to_move, board_size=15, planes=19, out_channels=32):
+def encode_gomoku(history, n_hist, to_move, board_size=15, planes=19, out_channels=64):
     """Device tensors in (int16 [B,16], uint8 [B], uint8 [B]) -> bf16 board tensor
     (torch int16 tensor holding the bf16 bits)."""
     import torch
@@ -246,7 +242,7 @@ def planes_to_board_tensor(planes, out_channels):
     return out
 
 
-def pack_conv3x3(w_oihw, scale, cin):
+def pack_conv3x3(w_oihw, scale, cin=64):
     """fp32 [cout, cin_real, 3, 3] (+ per-output-channel scale or None) -> packed
     bf16 image as numpy uint16."""
     w = np.ascontiguousarray(w_oihw, np.float32)
@@ -258,7 +254,7 @@ def pack_conv3x3(w_oihw, scale, cin):
     return out
 
 
-def conv3x3(x_bt, packed_w, bias, residual_bt, B, board_size, cin, cout=64, relu=True, out=None):
+def conv3x3(x_bt, packed_w, bias, residual_bt, B, board_size, cin=64, cout=64, relu=True, out=None):
     """One conv layer on device board tensors (torch int16 tensors with bf16 bits)."""
     import torch
     if out is None:
@@ -312,9 +308,6 @@ class Net:
                                            tm.ctypes.data_as(C.c_void_p), B, pol.ctypes.data_as(C.c_void_p),
                                            val.ctypes.data_as(C.c_void_p), out_kind))
         return pol, val
-
-    def stride_positions(self):
-        return int(lib().ob200_net_stride_positions(self.h))
 
     def input_tensor_channels(self):
         return int(lib().ob200_net_input_tensor_channels(self.h))

@@ -81,7 +81,7 @@ int64_t ob200_board_tensor_positions(int32_t board_size, int32_t B) {
 }
 int64_t ob200_board_tensor_bytes(int32_t board_size, int32_t B, int32_t channels) {
     if (board_size <= 0 || B < 0 || channels <= 0) return 0;
-    return ob200::board_geom(board_size, B).PT * (int64_t)((channels + 7) / 8) * 16;
+    return ob200::board_geom(board_size, B).PT * (int64_t)((channels + 7) / 8 * 8) * 2;
 }
 
 }  // extern "C"

@@ -1,12 +1,12 @@
 // Leaf state -> bf16 board tensor (sm_100a).
 //
-// Output format (see "Board tensors" in omoknuni_b200.h): channels blocked by
-// 8, positions on a (S+1) x (S+1) grid per board whose last column / row are
-// zero, guard positions before and after.  One thread produces one position of
-// one channel block: a single 16-byte store, consecutive threads write
-// consecutive 16-byte words, so every warp writes 512 contiguous bytes.  The
-// kernels also write the zero padding, so the output needs no memset.
-#include "common.h"
+// Output format (see "Board tensors" in omoknuni_b200.h): NHWC, positions on a
+// (S+1) x (S+1) grid per board whose last column / row are zero, guard
+// positions before and after.  One thread produces 8 channels of one position:
+// a single 16-byte store; consecutive threads write consecutive 16-byte words,
+// so every warp writes 512 contiguous bytes.  The kernels also write the zero
+// padding, so the output needs no memset.
+#include "internal.h"
 #include <cuda_bf16.h>
 
 namespace ob200 {
@@ -23,13 +23,12 @@ struct alignas(16) Pack8 { __nv_bfloat16 v[8]; };
 __global__ void __launch_bounds__(256)
 encode_gomoku_kernel(const int16_t* __restrict__ history, const uint8_t* __restrict__ n_hist,
                      const uint8_t* __restrict__ to_move, int B, int S, int planes, int chunks,
-                     long long cover, long long stride, Pack8* __restrict__ out) {
-    // cover = positions written per channel block (guards included), stride = positions
-    // between channel blocks of the destination (>= cover)
+                     long long cover, Pack8* __restrict__ out) {
+    // cover = positions written (guards included); chunks = channels / 8
     const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= cover * chunks) return;
-    const int chunk = (int)(gid / cover);
-    const long long p = gid % cover - OB200_GUARD;
+    const int chunk = (int)(gid % chunks);
+    const long long p = gid / chunks - OB200_GUARD;
     const int GP = S + 1, slots = GP * GP;
     Pack8 o;
 #pragma unroll
@@ -56,16 +55,16 @@ encode_gomoku_kernel(const int16_t* __restrict__ history, const uint8_t* __restr
             }
         }
     }
-    out[(long long)chunk * stride + (p + OB200_GUARD)] = o;
+    out[gid] = o;
 }
 
 __global__ void __launch_bounds__(256)
 planes_to_board_tensor_kernel(const float* __restrict__ planes, int B, int C, int S, int chunks,
-                              long long cover, long long stride, Pack8* __restrict__ out) {
+                              long long cover, Pack8* __restrict__ out) {
     const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= cover * chunks) return;
-    const int chunk = (int)(gid / cover);
-    const long long p = gid % cover - OB200_GUARD;
+    const int chunk = (int)(gid % chunks);
+    const long long p = gid / chunks - OB200_GUARD;
     const int GP = S + 1, slots = GP * GP;
     Pack8 o;
 #pragma unroll
@@ -81,16 +80,14 @@ planes_to_board_tensor_kernel(const float* __restrict__ planes, int B, int C, in
             }
         }
     }
-    out[(long long)chunk * stride + (p + OB200_GUARD)] = o;
+    out[gid] = o;
 }
 
 }  // namespace
 
-// stride_positions: positions between channel blocks of the destination; 0 = the
-// compact tensor for exactly B boards.
 int launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, const uint8_t* to_move,
                          int32_t B, int32_t board_size, int32_t planes, int32_t out_channels,
-                         void* board_tensor_out, long long stride_positions, cudaStream_t stream) {
+                         void* board_tensor_out, cudaStream_t stream) {
     if (!history || !n_hist || !to_move || !board_tensor_out || B < 0)
         return set_error(OB200_ERR_INVALID, "ob200_launch_encode_gomoku: null pointer or negative batch");
     if (planes != 17 && planes != 19)
@@ -103,17 +100,14 @@ int launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, const ui
     const BoardGeom g = board_geom(board_size, B);
     const int chunks = out_channels / 8;
     const long long total = g.PT * chunks;
-    const long long stride = stride_positions ? stride_positions : g.PT;
-    if (stride < g.PT) return set_error(OB200_ERR_INVALID, "encode: destination stride smaller than the batch needs");
     encode_gomoku_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-        history, n_hist, to_move, B, board_size, planes, chunks, g.PT, stride, reinterpret_cast<Pack8*>(board_tensor_out));
+        history, n_hist, to_move, B, board_size, planes, chunks, g.PT, reinterpret_cast<Pack8*>(board_tensor_out));
     OB200_LAUNCHED("encode_gomoku_kernel");
     return OB200_OK;
 }
 
 int launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C, int32_t board_size,
-                                  int32_t out_channels, void* board_tensor_out, long long stride_positions,
-                                  cudaStream_t stream) {
+                                  int32_t out_channels, void* board_tensor_out, cudaStream_t stream) {
     if (!planes_nchw || !board_tensor_out || B < 0 || C <= 0)
         return set_error(OB200_ERR_INVALID, "ob200_launch_planes_to_board_tensor: bad arguments");
     if (board_size < 1 || board_size > 31 || out_channels <= 0 || (out_channels & 7))
@@ -123,10 +117,8 @@ int launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C
     const BoardGeom g = board_geom(board_size, B);
     const int chunks = out_channels / 8;
     const long long total = g.PT * chunks;
-    const long long stride = stride_positions ? stride_positions : g.PT;
-    if (stride < g.PT) return set_error(OB200_ERR_INVALID, "planes_to_board_tensor: destination stride smaller than the batch needs");
     planes_to_board_tensor_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-        planes_nchw, B, C, board_size, chunks, g.PT, stride, reinterpret_cast<Pack8*>(board_tensor_out));
+        planes_nchw, B, C, board_size, chunks, g.PT, reinterpret_cast<Pack8*>(board_tensor_out));
     OB200_LAUNCHED("planes_to_board_tensor_kernel");
     return OB200_OK;
 }
@@ -140,13 +132,13 @@ extern "C" {
 int ob200_launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, const uint8_t* to_move,
                                int32_t B, int32_t board_size, int32_t planes, int32_t out_channels,
                                void* board_tensor_out, ob200_stream stream) {
-    return launch_encode_gomoku(history, n_hist, to_move, B, board_size, planes, out_channels, board_tensor_out, 0,
+    return launch_encode_gomoku(history, n_hist, to_move, B, board_size, planes, out_channels, board_tensor_out,
                                 as_stream(stream));
 }
 
 int ob200_launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C, int32_t board_size,
                                         int32_t out_channels, void* board_tensor_out, ob200_stream stream) {
-    return launch_planes_to_board_tensor(planes_nchw, B, C, board_size, out_channels, board_tensor_out, 0,
+    return launch_planes_to_board_tensor(planes_nchw, B, C, board_size, out_channels, board_tensor_out,
                                          as_stream(stream));
 }
 

@@ -11,7 +11,7 @@
 //                      each weight is used for 8 boards.
 //   softmax_kernel     in-place softmax over a row.
 //   value_out_kernel   value_fc2 + tanh (one warp per board).
-#include "common.h"
+#include "internal.h"
 #include <cuda_bf16.h>
 
 namespace ob200 {
@@ -25,7 +25,7 @@ struct alignas(16) Pack8 { __nv_bfloat162 v[4]; };
 
 // One thread per real board cell; w_s holds [HC][64] folded weights.
 __global__ void __launch_bounds__(128)
-head_conv_kernel(const uint8_t* __restrict__ tower, long long PT, const float* __restrict__ w,
+head_conv_kernel(const uint8_t* __restrict__ tower, const float* __restrict__ w,
                  const float* __restrict__ bias, int HC, int pc, float* __restrict__ hp,
                  float* __restrict__ hv, int B, int S) {
     extern __shared__ float w_s[];  // HC*64 weights then HC biases
@@ -41,7 +41,7 @@ head_conv_kernel(const uint8_t* __restrict__ tower, long long PT, const float* _
     float a[64];
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
-        const Pack8 v = *reinterpret_cast<const Pack8*>(tower + ((long long)c * PT + rec) * 16);
+        const Pack8 v = *reinterpret_cast<const Pack8*>(tower + rec * 128 + c * 16);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float2 f = __bfloat1622float2(v.v[j]);
@@ -136,11 +136,11 @@ value_out_kernel(const float* __restrict__ hidden, const float* __restrict__ w2,
 
 }  // namespace
 
-int launch_head_conv(const void* tower, long long PT, const float* w, const float* bias, int HC, int pc,
+int launch_head_conv(const void* tower, const float* w, const float* bias, int HC, int pc,
                      float* hp, float* hv, int B, int S, cudaStream_t st) {
     const long long total = (long long)B * S * S;
     const size_t smem = (size_t)(HC * 64 + HC) * sizeof(float);
-    head_conv_kernel<<<(unsigned)((total + 127) / 128), 128, smem, st>>>(static_cast<const uint8_t*>(tower), PT, w, bias,
+    head_conv_kernel<<<(unsigned)((total + 127) / 128), 128, smem, st>>>(static_cast<const uint8_t*>(tower), w, bias,
                                                                         HC, pc, hp, hv, B, S);
     OB200_LAUNCHED("head_conv_kernel");
     return OB200_OK;

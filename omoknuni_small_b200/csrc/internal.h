@@ -6,15 +6,19 @@ namespace ob200 {
 
 int launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, const uint8_t* to_move, int32_t B,
                          int32_t board_size, int32_t planes, int32_t out_channels, void* board_tensor_out,
-                         long long stride_positions, cudaStream_t stream);
+                         cudaStream_t stream);
 int launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C, int32_t board_size,
-                                  int32_t out_channels, void* board_tensor_out, long long stride_positions,
-                                  cudaStream_t stream);
-int launch_conv3x3(const void* in, const void* packed_w, const float* bias, const void* residual, void* out, int B,
-                   int S, int cin, int cout, int relu, long long stride_positions, cudaStream_t st);
+                                  int32_t out_channels, void* board_tensor_out, cudaStream_t stream);
+// Opaque storage of a CUtensorMap (128 bytes, 64-byte aligned) so that only the convolution's
+// translation unit needs the driver API header.
+struct alignas(64) BoardTensorMap { unsigned char opaque[128]; };
+int make_board_tensor_map(const void* base, long long rows, int box_rows, BoardTensorMap* out);
+int conv_halo_rows(int S);
+int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* packed_w,
+                        const float* bias, const void* residual, int B, int S, int relu, cudaStream_t st);
 int* device_error_word();
 
-int launch_head_conv(const void* tower, long long PT, const float* w, const float* bias, int HC, int pc, float* hp,
+int launch_head_conv(const void* tower, const float* w, const float* bias, int HC, int pc, float* hp,
                      float* hv, int B, int S, cudaStream_t st);
 int launch_fc(const float* in, const float* WT, const float* bias, float* out, int B, int K, int Nout, int relu,
               cudaStream_t st);

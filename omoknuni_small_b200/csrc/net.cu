@@ -14,8 +14,9 @@
 
 struct ob200_net {
     ob200_net_config cfg{};
-    int cin_pad = 0;                // stem input channels of the board tensor (32 or 64)
-    long long stride = 0;           // positions between channel blocks (sized for max_batch)
+    int cin_pad = 64;               // channels of the input board tensor (the stem runs on the 64-channel kernel)
+    long long rows = 0;             // positions per board tensor (sized for max_batch)
+    ob200::BoardTensorMap in_map_load{}, act_load[3]{}, act_store[3]{};
     std::map<std::string, std::vector<float>> host;  // tensors as given
     bool finalized = false;
     std::mutex mu;                  // calls on one handle are serialised
@@ -139,8 +140,8 @@ int ob200_net_create(const ob200_net_config* cfg, ob200_net** out) {
     if (int rc = require_device()) return rc;
     ob200_net* n = new ob200_net;
     n->cfg = *cfg;
-    n->cin_pad = cfg->input_channels <= 32 ? 32 : 64;
-    n->stride = board_geom(cfg->board_size, cfg->max_batch).PT;
+    n->cin_pad = 64;
+    n->rows = board_geom(cfg->board_size, cfg->max_batch).PT;
     *out = n;
     return OB200_OK;
 }
@@ -208,11 +209,18 @@ int ob200_net_finalize(ob200_net* n) {
     if (int rc = upload(n, &n->w2, *f2w)) return rc;
     n->b2 = (*f2b)[0];
     // activations (zeroed once: guards and padding stay zero for the handle's lifetime)
-    const size_t rec = (size_t)n->stride * 16;  // bytes per channel block
+    const size_t tensor_bytes = (size_t)n->rows * 128;   // 64 channels x bf16 per position
+    const int box_in = 128 + 2 * conv_halo_rows(c.board_size);
     uint8_t* p8 = nullptr;
-    if (int rc = dev_alloc(n, &p8, rec * (n->cin_pad / 8), true)) return rc;
+    if (int rc = dev_alloc(n, &p8, tensor_bytes, true)) return rc;
     n->act_in = p8;
-    for (int i = 0; i < 3; ++i) { if (int rc = dev_alloc(n, &p8, rec * (F / 8), true)) return rc; n->act[i] = p8; }
+    if (int rc = make_board_tensor_map(p8, n->rows, box_in, &n->in_map_load)) return rc;
+    for (int i = 0; i < 3; ++i) {
+        if (int rc = dev_alloc(n, &p8, tensor_bytes, true)) return rc;
+        n->act[i] = p8;
+        if (int rc = make_board_tensor_map(p8, n->rows, box_in, &n->act_load[i])) return rc;
+        if (int rc = make_board_tensor_map(p8, n->rows, 128, &n->act_store[i])) return rc;
+    }
     const size_t MB = c.max_batch;
     if (int rc = dev_alloc(n, &n->hp, MB * Kp, false)) return rc;
     if (int rc = dev_alloc(n, &n->hv, MB * Kv, false)) return rc;
@@ -242,26 +250,22 @@ int ob200_net_finalize(ob200_net* n) {
 namespace ob200 {
 namespace {
 
-// Tower + heads on device buffers. `input` is a board tensor of cin_pad channels
-// whose channel blocks are `in_stride` positions apart.
-int forward_device(ob200_net* n, const void* input, long long in_stride, int B, float* policy_out, float* value_out,
+// Tower + heads on device buffers.  `in_map` covers a 64-channel board tensor holding the
+// B input boards.
+int forward_device(ob200_net* n, const BoardTensorMap& in_map, int B, float* policy_out, float* value_out,
                    int out_kind, cudaStream_t st) {
     const ob200_net_config& c = n->cfg;
-    const int S = c.board_size, F = c.filters;
-    // The stem reads `input` with its own stride; everything after uses the handle's stride.
-    // launch_conv3x3 takes one stride for all tensors, so the stem input must share it.
-    if (in_stride != n->stride)
-        return set_error(OB200_ERR_INVALID, "forward: input tensor stride %lld != handle stride %lld", in_stride, n->stride);
-    void *x = n->act[0], *y = n->act[1], *z = n->act[2];
-    if (int rc = launch_conv3x3(input, n->conv_w[0], n->conv_b[0], nullptr, x, B, S, n->cin_pad, F, 1, n->stride, st)) return rc;
+    const int S = c.board_size;
+    int x = 0, y = 1, z = 2;
+    if (int rc = launch_conv3x3_maps(in_map, n->act_store[x], n->conv_w[0], n->conv_b[0], nullptr, B, S, 1, st)) return rc;
     for (int i = 0; i < c.blocks; ++i) {
-        if (int rc = launch_conv3x3(x, n->conv_w[1 + 2 * i], n->conv_b[1 + 2 * i], nullptr, y, B, S, F, F, 1, n->stride, st)) return rc;
-        if (int rc = launch_conv3x3(y, n->conv_w[2 + 2 * i], n->conv_b[2 + 2 * i], x, z, B, S, F, F, 1, n->stride, st)) return rc;
+        if (int rc = launch_conv3x3_maps(n->act_load[x], n->act_store[y], n->conv_w[1 + 2 * i], n->conv_b[1 + 2 * i], nullptr, B, S, 1, st)) return rc;
+        if (int rc = launch_conv3x3_maps(n->act_load[y], n->act_store[z], n->conv_w[2 + 2 * i], n->conv_b[2 + 2 * i], n->act[x], B, S, 1, st)) return rc;
         std::swap(x, z);
     }
-    n->tower_out = x;
+    n->tower_out = n->act[x];
     const int S2 = S * S, pc = c.policy_head_ch, vc = c.value_head_ch;
-    if (int rc = launch_head_conv(x, n->stride, n->head_w, n->head_b, pc + vc, pc, n->hp, n->hv, B, S, st)) return rc;
+    if (int rc = launch_head_conv(n->act[x], n->head_w, n->head_b, pc + vc, pc, n->hp, n->hv, B, S, st)) return rc;
     if (int rc = launch_fc(n->hp, n->WpT, n->bp, policy_out, B, pc * S2, c.policy_size, 0, st)) return rc;
     if (out_kind == OB200_OUT_PROBS)
         if (int rc = launch_softmax(policy_out, B, c.policy_size, st)) return rc;
@@ -321,8 +325,8 @@ int ob200_net_infer_planes(ob200_net* n, const float* planes, int32_t B, int32_t
     for (int b = 0; b < B; ++b)
         std::memcpy(n->h_planes + (size_t)b * used * S2, planes + (size_t)b * C * S2, (size_t)used * S2 * sizeof(float));
     OB200_CUDA_OK(cudaMemcpyAsync(n->d_planes, n->h_planes, (size_t)B * used * S2 * sizeof(float), cudaMemcpyHostToDevice, n->stream));
-    if (int rc = launch_planes_to_board_tensor(n->d_planes, B, used, c.board_size, n->cin_pad, n->act_in, n->stride, n->stream)) return rc;
-    if (int rc = forward_device(n, n->act_in, n->stride, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
+    if (int rc = launch_planes_to_board_tensor(n->d_planes, B, used, c.board_size, n->cin_pad, n->act_in, n->stream)) return rc;
+    if (int rc = forward_device(n, n->in_map_load, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
     return finish_host_call(n, B, policy_out, value_out);
 }
 
@@ -343,8 +347,8 @@ int ob200_net_infer_gomoku(ob200_net* n, const int16_t* history, const uint8_t* 
     OB200_CUDA_OK(cudaMemcpyAsync(n->d_nhist, n->h_nhist, (size_t)B, cudaMemcpyHostToDevice, n->stream));
     OB200_CUDA_OK(cudaMemcpyAsync(n->d_tomove, n->h_tomove, (size_t)B, cudaMemcpyHostToDevice, n->stream));
     if (int rc = launch_encode_gomoku(n->d_hist, n->d_nhist, n->d_tomove, B, c.board_size, c.input_channels, n->cin_pad,
-                                      n->act_in, n->stride, n->stream)) return rc;
-    if (int rc = forward_device(n, n->act_in, n->stride, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
+                                      n->act_in, n->stream)) return rc;
+    if (int rc = forward_device(n, n->in_map_load, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
     return finish_host_call(n, B, policy_out, value_out);
 }
 
@@ -353,11 +357,13 @@ int ob200_net_forward_device(ob200_net* n, const void* input_board_tensor, int32
     if (int rc = check_call(n, B, input_board_tensor, policy_out, value_out, out_kind, "ob200_net_forward_device")) return rc;
     std::lock_guard<std::mutex> lk(n->mu);
     OB200_CUDA_OK(cudaSetDevice(n->cfg.device));
-    return forward_device(n, input_board_tensor, n->stride, B, policy_out, value_out, out_kind, as_stream(stream));
+    BoardTensorMap in_map;
+    if (int rc = make_board_tensor_map(input_board_tensor, board_geom(n->cfg.board_size, B).PT,
+                                       128 + 2 * conv_halo_rows(n->cfg.board_size), &in_map)) return rc;
+    return forward_device(n, in_map, B, policy_out, value_out, out_kind, as_stream(stream));
 }
 
 const void* ob200_net_debug_tower_output(ob200_net* n) { return n ? n->tower_out : nullptr; }
-int64_t ob200_net_stride_positions(ob200_net* n) { return n ? n->stride : 0; }
 int32_t ob200_net_input_tensor_channels(ob200_net* n) { return n ? n->cin_pad : 0; }
 
 }  // extern "C"

@@ -2,28 +2,30 @@
 // 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM), sm_100a.
 //
 // GEMM view: M = board positions (128 per tile), N = 64 output channels,
-// K = 9 taps x C_in.  Activations are board tensors (channels blocked by 8,
-// positions on a padded (S+1)x(S+1) grid, see omoknuni_b200.h), so that
-//   * a tile plus its halo is, per channel block, ONE contiguous run of
-//     16-byte position records: the producer warp fetches it with a handful
-//     of 1-D bulk async copies (cp.async.bulk, completion on an mbarrier);
-//   * in shared memory the run is already the tensor core's no-swizzle
-//     K-major layout (8 positions x 16 bytes = one 128-byte core matrix,
-//     next 8 positions 128 bytes further, next channel block one run
-//     further), so every tap of the 3x3 stencil is the SAME buffer read
-//     through a matrix descriptor whose start address is shifted by
-//     (dy*(S+1)+dx) records.  The tile is brought on chip once and used by
-//     all 9 taps; zero columns/rows/guards in the tensor are the padding.
-// Weights (BatchNorm folded, bf16) stay resident in shared memory for the
-// whole launch.  Warp 0 produces (bulk copies), warp 1 issues the MMAs, warps
-// 2-9 (two warpgroups on alternate tiles) run the epilogue (TMEM -> registers, + bias, + residual, ReLU, zero the
-// padding positions, bf16, 16-byte coalesced stores).  Four shared-memory
-// stages and four TMEM accumulators decouple the three roles.
+// K = 9 taps x 64 input channels.  Activations are bf16 NHWC board tensors
+// (see omoknuni_b200.h): one position = 64 channels = one 128-byte row, boards
+// laid on a padded (S+1) x (S+1) grid whose extra column / row and the guard
+// rows are zero, so that
+//   * a tile plus its halo is one 2-D TMA box (64 channels x rows) that lands
+//     in shared memory in the tensor core's 128-byte-swizzled K-major layout;
+//   * every tap of the stencil is the SAME shared-memory tile read through a
+//     matrix descriptor whose start address is moved by (dy*(S+1)+dx) rows
+//     (the 128-byte swizzle is a function of the shared-memory address, so a
+//     row-shifted start reads the same bytes TMA wrote).  A tile is fetched
+//     once and used by all 9 taps; the zero rows / columns of the tensor are
+//     the convolution's padding.
+// Weights (BatchNorm folded, bf16, pre-swizzled on the host) stay resident in
+// shared memory for the whole launch.  Warp 0 produces (TMA loads), warp 1
+// issues the MMAs, warps 2-17 (two groups of 8 warps on alternate tiles) run the
+// epilogue: TMEM -> registers, + bias, + residual, ReLU, zero the padding
+// positions, bf16, swizzled staging tile in shared memory, one TMA store.
 //
 // Every wait on an mbarrier is bounded; when one runs out the CTA raises the
-// error word, leaves its loops, frees its TMEM and returns.
-#include "common.h"
+// device error word, leaves its loops, frees its TMEM and returns.
+#include "internal.h"
+#include <cuda.h>
 #include <cuda_bf16.h>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -31,29 +33,33 @@ namespace ob200 {
 namespace {
 
 constexpr int kTileM = 128;             // positions per tile
-constexpr int kCout = 64;               // output channels (GEMM N)
-constexpr int kHaloMax = OB200_GUARD;   // smem rows kept before / after a tile
-constexpr int kTileRows = kTileM + 2 * kHaloMax;       // 192 records per channel block
-constexpr int kChunkBytes = kTileRows * 16;             // 3072
-constexpr int kStages = 4;
+constexpr int kC = 64;                  // channels in and out (GEMM N and K per tap)
+constexpr int kRowBytes = kC * 2;       // one position
+constexpr int kHaloMax = OB200_GUARD;   // halo rows kept before / after a tile, at most
+constexpr int kStageBytes = (kTileM + 2 * kHaloMax) * kRowBytes;   // 24,576
+constexpr int kWBytes = 9 * kC * kRowBytes;                        // 73,728
+constexpr int kOutBytes = kTileM * kRowBytes;                      // 16,384
+constexpr int kStages = 3;
 constexpr int kAccStages = 4;
-constexpr int kTmemCols = kAccStages * kCout;           // 256 (power of two)
-constexpr int kEpiGroups = 2;           // epilogue warpgroups, alternating tiles
-constexpr int kThreads = 64 + 128 * kEpiGroups;
+constexpr int kTmemCols = kAccStages * kC;                         // 256 (power of two)
+constexpr int kEpiGroups = 2;
+constexpr int kEpiWarps = 8;             // per group: 4 TMEM lane quadrants x 2 halves of the 64 channels
+constexpr int kThreads = 64 + 32 * kEpiWarps * kEpiGroups;
+constexpr int kNumBars = 2 * kStages + 2 * kAccStages + 1;
+constexpr int kSmemBytes = kWBytes + kStages * kStageBytes + kEpiGroups * kOutBytes + kNumBars * 8 + kC * 4 + 16 + 1024;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct ConvParams {
-    const uint8_t* in;        // board tensor, cin channels
-    const uint8_t* w;         // packed weights
+    const uint8_t* w;         // packed, pre-swizzled weights
     const float* bias;        // [64]
-    const uint8_t* residual;  // board tensor, 64 channels, or null
-    uint8_t* out;             // board tensor, 64 channels
+    const uint8_t* residual;  // board tensor or null
     int* error;               // device error word (0 = fine)
-    long long PT;             // positions per channel block incl. guards
-    long long P;              // real positions = B * slots
+    int P;                    // real positions = B * slots
     int num_tiles;
     int S, GP, slots;
+    int halo;                 // halo rows of the TMA box (multiple of 8, >= GP + 1)
     int relu;
+    int dbg;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -70,7 +76,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
-        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
@@ -78,10 +84,7 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_test(bar, parity)) return true;
-        if (i > 64) {
-            __nanosleep(32);
-            if ((i & 1023) == 0 && *abort_flag) return false;
-        }
+        if ((i & 255) == 255 && *abort_flag) return false;
     }
     return false;
 }
@@ -90,24 +93,36 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-
-// Shared-memory matrix descriptor, no swizzle, K-major: core matrices of
-// 8 rows x 16 bytes stored as 128 contiguous bytes; `lbo` = bytes between the
-// two K-adjacent core matrices of one MMA (K = 16), `sbo` = bytes between
-// 8-row groups along M / N.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
-           ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46);
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes,
+// 8-row groups 1024 bytes apart (stride byte offset); the leading byte offset is
+// not used by swizzled K-major layouts and is encoded as 1.  The swizzle is a
+// function of the shared-memory address itself (16-byte chunk index XOR address
+// bits 7-9), so a descriptor may start at any 128-byte row of a tile that TMA
+// wrote with the same swizzle; the base-offset field stays 0 (measured: a
+// non-zero base offset on a row-shifted start gives wrong products).
+// Split in two words so that the issuing thread only adds to the low one.
+constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
 // kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128, N = 64.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kCout >> 3) << 17) |
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kC >> 3) << 17) |
                             ((uint32_t)(kTileM >> 4) << 24);
 
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t accumulate) {
     asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate) : "memory");
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "mov.b64 da, {%1, %3};\nmov.b64 db, {%2, %3};\n"
+        "setp.ne.b32 p, %5, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(kIdesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -123,38 +138,42 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void group_bar(int id) {   // the threads of one epilogue group
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(32 * kEpiWarps) : "memory");
+}
 
-struct alignas(16) Pack8 { __nv_bfloat162 v[4]; };
-
-template <int CC>  // input channel blocks of 8 (8 for 64 channels, 4 for the 32-channel stem)
-__global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const ConvParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int kWBytes = 9 * CC * kCout * 16;
-    constexpr int kStageBytes = CC * kChunkBytes;
+__global__ void __launch_bounds__(kThreads, 1)
+conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
+               const ConvParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // swizzled tiles need 1024-byte aligned bases
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* w_s = smem;
-    uint8_t* a_s = smem + kWBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(a_s + kStages * kStageBytes);
-    // bars: [0,4) full, [4,8) empty, [8,12) accumulator full, [12,16) accumulator empty, 16 weights
-    float* bias_s = reinterpret_cast<float*>(bars + 17);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bias_s + kCout);
+    uint8_t* a_s = w_s + kWBytes;
+    uint8_t* o_s = a_s + kStages * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(o_s + kEpiGroups * kOutBytes);
+    float* bias_s = reinterpret_cast<float*>(bars + kNumBars);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bias_s + kC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
-    auto empty_bar = [&](int s) { return bar0 + 8u * (4 + s); };
-    auto accfull_bar = [&](int a) { return bar0 + 8u * (8 + a); };
-    auto accempty_bar = [&](int a) { return bar0 + 8u * (12 + a); };
-    const uint32_t w_bar = bar0 + 8u * 16;
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+    auto accfull_bar = [&](int a) { return bar0 + 8u * (2 * kStages + a); };
+    auto accempty_bar = [&](int a) { return bar0 + 8u * (2 * kStages + kAccStages + a); };
+    const uint32_t w_bar = bar0 + 8u * (2 * kStages + 2 * kAccStages);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < kAccStages; ++a) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), 4); }
+        for (int a = 0; a < kAccStages; ++a) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), kEpiWarps); }
         mbar_init(w_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&in_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&out_map) : "memory");
     }
-    if (threadIdx.x < kCout) bias_s[threadIdx.x] = p.bias[threadIdx.x];
+    if (threadIdx.x < kC) bias_s[threadIdx.x] = p.bias[threadIdx.x];
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
@@ -165,14 +184,12 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const ConvParams p
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    const int halo = p.GP + 1;
-    const uint32_t chunk_copy_bytes = (uint32_t)(kTileM + 2 * halo) * 16u;
-
     if (warp == 0) {
-        // ---------------- producer: bulk copies global -> shared ----------------
+        // ---------------- producer: TMA loads global -> shared ----------------
         if (lane == 0) {
             mbar_arrive_expect_tx(w_bar, (uint32_t)kWBytes);
             bulk_g2s(smem_u32(w_s), p.w, (uint32_t)kWBytes, w_bar);
+            const uint32_t box_bytes = (uint32_t)(kTileM + 2 * p.halo) * kRowBytes;
             int it = 0;
             for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
                 const int s = it % kStages;
@@ -180,13 +197,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const ConvParams p
                 if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) {
                     *abort_flag = 1; atomicExch(p.error, 1); break;
                 }
-                mbar_arrive_expect_tx(full_bar(s), chunk_copy_bytes * CC);
-                const long long first = (long long)OB200_GUARD + (long long)tile * kTileM - halo;
-                const uint32_t dst0 = smem_u32(a_s + s * kStageBytes) + (uint32_t)(kHaloMax - halo) * 16u;
-#pragma unroll
-                for (int c = 0; c < CC; ++c)
-                    bulk_g2s(dst0 + c * kChunkBytes, p.in + ((long long)c * p.PT + first) * 16, chunk_copy_bytes,
-                             full_bar(s));
+                mbar_arrive_expect_tx(full_bar(s), box_bytes);
+                tma_load_2d(smem_u32(a_s + s * kStageBytes), &in_map, 0, OB200_GUARD + tile * kTileM - p.halo, full_bar(s));
             }
         }
     } else if (warp == 1) {
@@ -194,6 +206,14 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const ConvParams p
         if (lane == 0) {
             bool ok = mbar_wait(w_bar, 0, abort_flag);
             if (!ok) { *abort_flag = 1; atomicExch(p.error, 2); }
+            // Everything that does not change from tile to tile is prepared once: the issuing
+            // thread is a single warp lane, so each MMA must cost it a handful of integer
+            // instructions, not a descriptor rebuild.
+            const uint32_t w_lo = desc_lo(smem_u32(w_s));
+            int tap_off[9];
+#pragma unroll
+            for (int tap = 0; tap < 9; ++tap)
+                tap_off[tap] = (p.halo + (tap / 3 - 1) * p.GP + (tap % 3 - 1)) * (kRowBytes >> 4);
             int it = 0;
             for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
                 const int s = it % kStages, a = it % kAccStages;
@@ -202,72 +222,77 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const ConvParams p
                     *abort_flag = 1; atomicExch(p.error, 2); break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_base = smem_u32(a_s + s * kStageBytes) + (uint32_t)kHaloMax * 16u;
-                const uint32_t w_base = smem_u32(w_s);
-                const uint32_t d_tmem = tmem_base + (uint32_t)a * kCout;
-                uint32_t acc = 0;
+                const uint32_t a_lo = desc_lo(smem_u32(a_s + s * kStageBytes));
+                const uint32_t d_tmem = tmem_base + (uint32_t)a * kC;
 #pragma unroll
                 for (int tap = 0; tap < 9; ++tap) {
-                    const int shift = (tap / 3 - 1) * p.GP + (tap % 3 - 1);
+                    if ((p.dbg & 1) && tap > 0) break;
+                    if ((p.dbg & 8) && tap > 3) break;
 #pragma unroll
-                    for (int ks = 0; ks < CC / 2; ++ks) {
-                        const uint64_t ad = make_desc(a_base + (uint32_t)(2 * ks) * kChunkBytes + (uint32_t)(shift * 16),
-                                                      kChunkBytes, 128);
-                        const uint64_t bd = make_desc(w_base + (uint32_t)((tap * CC + 2 * ks) * kCout * 16),
-                                                      kCout * 16, 128);
-                        umma(d_tmem, ad, bd, acc);
-                        acc = 1;
-                    }
+                    for (int ks = 0; ks < kC / 16; ++ks)
+                        umma(d_tmem, a_lo + (uint32_t)(tap_off[tap] + ks * 2),
+                             w_lo + (uint32_t)(tap * (kC * kRowBytes >> 4) + ks * 2), (tap | ks) ? 1u : 0u);
                 }
                 umma_commit(empty_bar(s));      // smem stage free once these MMAs have read it
                 umma_commit(accfull_bar(a));    // accumulator ready for the epilogue
             }
         }
     } else {
-        // ---------------- epilogue: TMEM -> registers -> global ----------------
-        // Two warpgroups take alternate tiles.  A thread owns one position (TMEM lane) and
-        // all 64 channels; the residual is fetched before the wait on the accumulator so
-        // that its latency hides behind the MMAs of the tile.
-        const int q = warp & 3;                 // TMEM lane quadrant this warp may read
-        const int group = (warp - 2) >> 2;
+        // ---------------- epilogue: TMEM -> registers -> shared -> TMA store ----------------
+        // Two groups of 8 warps take alternate tiles.  Within a group a warp owns one TMEM
+        // lane quadrant (32 positions; fixed by warp id % 4) and one half of the 64 channels,
+        // so a thread handles 32 channels of one position: the per-tile latency of one
+        // thread's instruction stream, not its throughput, is what paces a group.  The
+        // residual is fetched before the wait on the accumulator so that its latency hides
+        // behind the MMAs of the tile.
+        const int ew = warp - 2;                 // 0 .. 15
+        const int group = ew / kEpiWarps;
+        const int half = (ew % kEpiWarps) >> 2;  // channels [32*half, 32*half + 32)
+        const int q = warp & 3;                  // TMEM lane quadrant this warp may read
         const int row = q * 32 + lane;
+        const bool leader = (ew % kEpiWarps) == 0 && lane == 0;
         const uint8_t* __restrict__ resid = p.residual;
-        uint8_t* __restrict__ outp = p.out;
-        const int P = (int)p.P;
+        uint8_t* stage_out = o_s + group * kOutBytes;
+        const uint32_t stage_out_u32 = smem_u32(stage_out);
+        float bias_r[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) bias_r[j] = bias_s[half * 32 + j];
         int it = group;
         for (int tile = blockIdx.x + group * gridDim.x; tile < p.num_tiles; tile += kEpiGroups * gridDim.x, it += kEpiGroups) {
             const int a = it % kAccStages;
             const uint32_t pa = (uint32_t)(it / kAccStages) & 1u;
             const int pos = tile * kTileM + row;
-            bool valid = pos < P;
+            bool valid = pos < p.P;
             if (valid) {
                 const int rr = pos % p.slots;
                 valid = (rr / p.GP < p.S) && (rr % p.GP < p.S);
             }
-            const long long rec = (long long)OB200_GUARD + pos;
-            uint4 rs[kCout / 8];
+            uint4 rs[4];
             if (resid != nullptr && valid) {
+                const uint4* src = reinterpret_cast<const uint4*>(resid + (size_t)(OB200_GUARD + pos) * kRowBytes) + half * 4;
 #pragma unroll
-                for (int c = 0; c < kCout / 8; ++c)
-                    rs[c] = __ldg(reinterpret_cast<const uint4*>(resid + ((long long)c * p.PT + rec) * 16));
+                for (int c = 0; c < 4; ++c) rs[c] = __ldg(src + c);
             } else {
 #pragma unroll
-                for (int c = 0; c < kCout / 8; ++c) rs[c] = make_uint4(0u, 0u, 0u, 0u);
+                for (int c = 0; c < 4; ++c) rs[c] = make_uint4(0u, 0u, 0u, 0u);
             }
             if (!mbar_wait(accfull_bar(a), pa, abort_flag)) {
                 *abort_flag = 1; atomicExch(p.error, 3); break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t r[64];
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)a * kCout;
-            tmem_ld32(taddr, r);
-            tmem_ld32(taddr + 32, r + 32);
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kC + half * 32), r);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(accempty_bar(a));
+            if (p.dbg & 2) continue;
+
+            // the previous store of this group must have finished reading the staging tile
+            if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            group_bar(1 + 2 * group);
 #pragma unroll
-            for (int c = 0; c < kCout / 8; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 uint4 o = make_uint4(0u, 0u, 0u, 0u);
                 if (valid) {
                     const uint32_t rw[4] = {rs[c].x, rs[c].y, rs[c].z, rs[c].w};
@@ -275,23 +300,30 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const ConvParams p
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         // bf16 -> fp32 is a 16-bit shift
-                        float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bias_s[c * 8 + 2 * j] + __uint_as_float(rw[j] << 16);
-                        float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bias_s[c * 8 + 2 * j + 1] + __uint_as_float(rw[j] & 0xFFFF0000u);
+                        float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bias_r[c * 8 + 2 * j] + __uint_as_float(rw[j] << 16);
+                        float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bias_r[c * 8 + 2 * j + 1] + __uint_as_float(rw[j] & 0xFFFF0000u);
                         if (p.relu) { v0 = fmaxf(v0, 0.0f); v1 = fmaxf(v1, 0.0f); }
                         const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
                         ow[j] = *reinterpret_cast<const uint32_t*>(&h);
                     }
                     o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                 }
-                *reinterpret_cast<uint4*>(outp + ((long long)c * p.PT + rec) * 16) = o;
+                // 128-byte swizzle of the staging tile: 16-byte chunk k of row r sits at chunk k ^ (r % 8)
+                *reinterpret_cast<uint4*>(stage_out + row * kRowBytes + (((half * 4 + c) ^ (row & 7)) << 4)) = o;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            group_bar(2 + 2 * group);
+            if (leader) {
+                tma_store_2d(&out_map, 0, OB200_GUARD + tile * kTileM, stage_out_u32);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
         }
+        if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     // ---------------- teardown ----------------
     if (*abort_flag) {
-        // give bulk copies that may still be in flight time to land before the CTA's
-        // shared memory is released
+        // give copies that may still be in flight time to land before the shared memory is released
         for (int i = 0; i < 64; ++i) __nanosleep(2000);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -299,11 +331,6 @@ __global__ void __launch_bounds__(kThreads, 1) conv3x3_kernel(const ConvParams p
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
     }
-}
-
-template <int CC>
-constexpr int conv_smem_bytes() {
-    return 9 * CC * kCout * 16 + kStages * CC * kChunkBytes + 17 * 8 + kCout * 4 + 16;
 }
 
 inline uint16_t f32_to_bf16_rne(float f) {
@@ -334,48 +361,67 @@ int* device_error_word() {
     return cached[dev];
 }
 
-template <int CC>
-static int launch_conv(const ConvParams& p, cudaStream_t st) {
+// 2-D tensor map over a board tensor: inner dimension the 64 channels of a position
+// (128 bytes), outer dimension `rows` positions; boxes of 64 x box_rows, 128-byte swizzle.
+int make_board_tensor_map(const void* base, long long rows, int box_rows, BoardTensorMap* out) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn)
+            return set_error(OB200_ERR_CUDA, "cannot resolve cuTensorMapEncodeTiled from the driver");
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    static_assert(sizeof(BoardTensorMap) == sizeof(CUtensorMap), "tensor map size");
+    if (((uintptr_t)base & 15) || rows <= 0 || box_rows <= 0 || box_rows > 256)
+        return set_error(OB200_ERR_INVALID, "board tensor map: base must be 16-byte aligned, box rows in [1,256]");
+    const cuuint64_t dims[2] = {(cuuint64_t)kC, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)kRowBytes};
+    const cuuint32_t box[2] = {(cuuint32_t)kC, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(OB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return OB200_OK;
+}
+
+int conv_halo_rows(int S) { return (S + 2 + 7) / 8 * 8; }
+
+int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* packed_w,
+                        const float* bias, const void* residual, int B, int S, int relu, cudaStream_t st) {
+    if (!packed_w || !bias || B <= 0) return set_error(OB200_ERR_INVALID, "conv3x3: null pointer or empty batch");
+    if (S < 1 || conv_halo_rows(S) > kHaloMax)
+        return set_error(OB200_ERR_UNSUPPORTED, "conv3x3: board_size %d outside [1, %d]", S, kHaloMax - 2);
+    if (((uintptr_t)packed_w | (uintptr_t)residual) & 15)
+        return set_error(OB200_ERR_INVALID, "conv3x3: tensors must be 16-byte aligned");
+    if (int rc = require_device()) return rc;
     static bool configured[64] = {false};
     int dev = 0;
     OB200_CUDA_OK(cudaGetDevice(&dev));
-    constexpr int smem = conv_smem_bytes<CC>();
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        OB200_CUDA_OK(cudaFuncSetAttribute(conv3x3_kernel<CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        OB200_CUDA_OK(cudaFuncSetAttribute(conv3x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         configured[dev] = true;
     }
     int sms = 0;
     OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    const int grid = p.num_tiles < sms ? p.num_tiles : sms;   // one persistent CTA per SM
-    conv3x3_kernel<CC><<<grid, kThreads, smem, st>>>(p);
-    OB200_LAUNCHED("conv3x3_kernel");
-    return OB200_OK;
-}
-
-// stride_positions: positions between channel blocks of all three tensors; 0 = the
-// compact tensors for exactly B boards.
-int launch_conv3x3(const void* in, const void* packed_w, const float* bias, const void* residual, void* out,
-                   int B, int S, int cin, int cout, int relu, long long stride_positions, cudaStream_t st) {
-    if (!in || !packed_w || !bias || !out || B <= 0)
-        return set_error(OB200_ERR_INVALID, "conv3x3: null pointer or empty batch");
-    if (cout != kCout || (cin != 32 && cin != 64))
-        return set_error(OB200_ERR_UNSUPPORTED, "conv3x3: this build covers cout = 64 and cin in {32, 64}; got cin %d cout %d",
-                         cin, cout);
-    if (S < 1 || S + 2 > kHaloMax)
-        return set_error(OB200_ERR_UNSUPPORTED, "conv3x3: board_size %d outside [1, %d]", S, kHaloMax - 2);
-    if (((uintptr_t)in | (uintptr_t)packed_w | (uintptr_t)out | (uintptr_t)residual) & 15)
-        return set_error(OB200_ERR_INVALID, "conv3x3: tensors must be 16-byte aligned");
-    if (int rc = require_device()) return rc;
     const BoardGeom g = board_geom(S, B);
     ConvParams p;
-    p.in = static_cast<const uint8_t*>(in); p.w = static_cast<const uint8_t*>(packed_w); p.bias = bias;
-    p.residual = static_cast<const uint8_t*>(residual); p.out = static_cast<uint8_t*>(out);
+    p.w = static_cast<const uint8_t*>(packed_w); p.bias = bias; p.residual = static_cast<const uint8_t*>(residual);
     p.error = device_error_word();
     if (!p.error) return set_error(OB200_ERR_CUDA, "conv3x3: cannot resolve the device error word");
-    if (stride_positions && stride_positions < g.PT)
-        return set_error(OB200_ERR_INVALID, "conv3x3: tensor stride smaller than the batch needs");
-    p.PT = stride_positions ? stride_positions : g.PT; p.P = g.P; p.num_tiles = (int)(g.Ppad / kTileM); p.S = S; p.GP = g.GP; p.slots = g.slots; p.relu = relu;
-    return cin == 64 ? launch_conv<8>(p, st) : launch_conv<4>(p, st);
+    p.P = (int)g.P; p.num_tiles = (int)(g.Ppad / kTileM); p.S = S; p.GP = g.GP; p.slots = g.slots;
+    p.halo = conv_halo_rows(S); p.relu = relu;
+    { static int dbg = -1; if (dbg < 0) { const char* e = std::getenv("OB200_CONV_DEBUG"); dbg = e ? std::atoi(e) : 0; } p.dbg = dbg; }
+    const int grid = p.num_tiles < sms ? p.num_tiles : sms;   // one persistent CTA per SM
+    conv3x3_kernel<<<grid, kThreads, kSmemBytes, st>>>(*reinterpret_cast<const CUtensorMap*>(&in_map),
+                                                       *reinterpret_cast<const CUtensorMap*>(&out_map), p);
+    OB200_LAUNCHED("conv3x3_kernel");
+    return OB200_OK;
 }
 
 }  // namespace ob200
@@ -387,38 +433,44 @@ extern "C" {
 int ob200_launch_conv3x3(const void* in, const void* packed_w, const float* bias, const void* residual,
                          void* out, int32_t B, int32_t board_size, int32_t cin, int32_t cout, int32_t relu,
                          ob200_stream stream) {
-    return launch_conv3x3(in, packed_w, bias, residual, out, B, board_size, cin, cout, relu, 0, as_stream(stream));
+    if (!in || !out || B <= 0) return set_error(OB200_ERR_INVALID, "ob200_launch_conv3x3: null pointer or empty batch");
+    if (cin != kC || cout != kC)
+        return set_error(OB200_ERR_UNSUPPORTED, "ob200_launch_conv3x3: this build covers 64 -> 64 channels; got %d -> %d", cin, cout);
+    if (board_size < 1 || conv_halo_rows(board_size) > kHaloMax)
+        return set_error(OB200_ERR_UNSUPPORTED, "ob200_launch_conv3x3: board_size %d outside [1, %d]", board_size, kHaloMax - 2);
+    const BoardGeom g = board_geom(board_size, B);
+    BoardTensorMap im, om;
+    if (int rc = make_board_tensor_map(in, g.PT, kTileM + 2 * conv_halo_rows(board_size), &im)) return rc;
+    if (int rc = make_board_tensor_map(out, g.PT, kTileM, &om)) return rc;
+    return launch_conv3x3_maps(im, om, packed_w, bias, residual, B, board_size, relu, as_stream(stream));
 }
 
 int64_t ob200_packed_conv3x3_bytes(int32_t cin, int32_t cout) {
-    if (cin <= 0 || cout <= 0 || (cin & 7)) return 0;
-    return (int64_t)9 * cin * cout * 2;
+    if (cin != kC || cout != kC) return 0;
+    return (int64_t)kWBytes;
 }
 
-// Packed image: [tap = ky*3+kx][cin/8][cout][8] bf16 — per tap and per block
-// of 8 input channels, `cout` rows of 16 bytes: the K-major no-swizzle
-// operand layout of the tensor core with the output channel as the row.
+// Packed image: [tap = ky*3+kx][cout][cin] bf16, one 128-byte row per output channel and
+// tap, its 16-byte chunks (8 input channels) permuted by the 128-byte swizzle
+// (chunk j of row r stored at chunk j ^ (r % 8)) — the K-major shared-memory operand
+// layout of the tensor core, ready for a plain bulk copy.
 int ob200_pack_conv3x3_weights(const float* w_oihw, const float* scale, int32_t cout, int32_t cin_real,
                                int32_t cin, void* packed_out) {
-    if (!w_oihw || !packed_out || cout <= 0 || cin_real <= 0 || cin < cin_real || (cin & 7))
-        return set_error(OB200_ERR_INVALID, "ob200_pack_conv3x3_weights: bad arguments (cout %d, cin_real %d, cin %d)",
+    if (!w_oihw || !packed_out || cout != kC || cin != kC || cin_real <= 0 || cin_real > cin)
+        return set_error(OB200_ERR_INVALID, "ob200_pack_conv3x3_weights: this build packs cout = 64, cin = 64 (cin_real <= 64); got cout %d, cin_real %d, cin %d",
                          cout, cin_real, cin);
     uint16_t* o = static_cast<uint16_t*>(packed_out);
-    const int chunks = cin / 8;
     for (int tap = 0; tap < 9; ++tap)
-        for (int cb = 0; cb < chunks; ++cb)
-            for (int co = 0; co < cout; ++co)
-                for (int j = 0; j < 8; ++j) {
-                    const int ci = cb * 8 + j;
-                    float v = 0.0f;
-                    if (ci < cin_real) v = w_oihw[((size_t)co * cin_real + ci) * 9 + tap] * (scale ? scale[co] : 1.0f);
-                    o[(((size_t)tap * chunks + cb) * cout + co) * 8 + j] = f32_to_bf16_rne(v);
-                }
+        for (int co = 0; co < kC; ++co)
+            for (int ci = 0; ci < kC; ++ci) {
+                float v = 0.0f;
+                if (ci < cin_real) v = w_oihw[((size_t)co * cin_real + ci) * 9 + tap] * (scale ? scale[co] : 1.0f);
+                const size_t byte = (size_t)tap * kC * kRowBytes + (size_t)co * kRowBytes + ((((ci >> 3) ^ (co & 7))) << 4) + (ci & 7) * 2;
+                o[byte / 2] = f32_to_bf16_rne(v);
+            }
     return OB200_OK;
 }
 
-/* Reads and clears the device error word of the current device (synchronises
- * the device).  0 = no kernel gave up on a wait. */
 int ob200_device_error_code(int32_t* code_out) {
     if (!code_out) return set_error(OB200_ERR_INVALID, "ob200_device_error_code: null output");
     if (int rc = require_device()) return rc;

@@ -40,7 +40,7 @@ def test_pure_host_helpers(lib):
     # 15x15 boards live on a 16x16 grid: 256 positions per board + 2 x 32 guards
     assert lib.ob200_board_tensor_positions(15, 4) == 4 * 256 + 64
     assert lib.ob200_board_tensor_positions(19, 1) == 512 + 64   # 400 rounded up to 128s
-    assert lib.ob200_board_tensor_bytes(15, 4, 17) == (4 * 256 + 64) * 3 * 16
+    assert lib.ob200_board_tensor_bytes(15, 4, 17) == (4 * 256 + 64) * 24 * 2
     assert lib.ob200_packed_conv3x3_bytes(64, 64) == 9 * 64 * 64 * 2
 
 
@@ -50,12 +50,15 @@ def test_weight_packing_layout(lib):
     rng = np.random.default_rng(0)
     w = rng.integers(-8, 8, (64, 17, 3, 3)).astype(np.float32)      # exactly representable in bf16
     scale = np.full(64, 0.5, np.float32)
-    packed = capi.pack_conv3x3(w, scale, 32).reshape(9, 4, 64, 8)
+    packed = capi.pack_conv3x3(w, scale, 64).reshape(9, 64, 8, 8)    # [tap][cout][16-byte chunk][8]
     vals = (packed.astype(np.uint32) << 16).view(np.float32)
     for tap in (0, 4, 8):
-        for ci in (0, 7, 8, 16):
-            assert np.array_equal(vals[tap, ci // 8, :, ci % 8], w[:, ci, tap // 3, tap % 3] * 0.5)
-    assert not vals[:, 2:, :, :][:, :, :, 1:].any() and not vals[:, 3].any()   # channels >= 17 are zero
+        for co in (0, 5, 63):
+            row = np.empty(64, np.float32)
+            for chunk in range(8):                                    # undo the 128-byte swizzle
+                row[chunk * 8:(chunk + 1) * 8] = vals[tap, co, chunk ^ (co % 8)]
+            assert np.array_equal(row[:17], w[co, :, tap // 3, tap % 3] * 0.5)
+            assert not row[17:].any()                                 # channels >= 17 carry zero weights
 
 
 @pytest.mark.skipif(os.path.exists("/dev/nvidiactl"), reason="a GPU is present")

@@ -15,7 +15,7 @@ def api(lib):
     return capi
 
 
-def run_encode(api, hist, nh, tm, S, planes, out_channels=32):
+def run_encode(api, hist, nh, tm, S, planes, out_channels=64):
     import torch
     bt = api.encode_gomoku(torch.from_numpy(hist).cuda(), torch.from_numpy(nh).cuda(), torch.from_numpy(tm).cuda(), S,
                            planes, out_channels)
@@ -55,7 +55,7 @@ def test_planes_to_board_tensor_round_trip(api):
     import torch
     x = synth.make_stone_planes(33, 15, 17, seed=6)
     x[:, 3] *= 0.37                                           # a non-binary plane: must match host rounding to bf16
-    bt = api.planes_to_board_tensor(torch.from_numpy(x).cuda(), 32)
+    bt = api.planes_to_board_tensor(torch.from_numpy(x).cuda(), 64)
     torch.cuda.synchronize()
     got = bt.cpu().numpy().view(np.uint16)
-    assert np.array_equal(got, api.planes_to_board_tensor_host(x, 32))
+    assert np.array_equal(got, api.planes_to_board_tensor_host(x, 64))
