@@ -6,9 +6,9 @@
 //                      in the reference's flatten order c * S*S + y * S + x
 //                      (src/nn/resnet_model.cpp:183,209 view({B,-1}) on NCHW).
 //   fc_kernel          out[b][j] = act(sum_i in[b][i] * WT[i][j] + bias[j]);
-//                      a CTA owns 8 boards x 256 outputs, the weight matrix is
-//                      stored transposed so that threads read it coalesced and
-//                      each weight is used for 8 boards.
+//                      a CTA owns 8 boards x 64 outputs split in 4 K-slices, the
+//                      weight matrix is stored transposed so that threads read
+//                      it coalesced and each weight is used for 8 boards.
 //   softmax_kernel     in-place softmax over a row.
 //   value_out_kernel   value_fc2 + tanh (one warp per board).
 #include "internal.h"
@@ -59,12 +59,18 @@ head_conv_kernel(const uint8_t* __restrict__ tower, const float* __restrict__ w,
     }
 }
 
+// A CTA owns 8 boards x 64 outputs; its 256 threads are 4 K-slices x 64 outputs, so a
+// thread walks a quarter of the inner dimension with 8 accumulators (one weight load
+// feeds 8 boards) and the slices are summed through shared memory.  Small tiles give a
+// grid of several CTAs per SM, which is what hides the L2 latency of the weight reads.
 __global__ void __launch_bounds__(kFcThreads)
 fc_kernel(const float* __restrict__ in, const float* __restrict__ WT, const float* __restrict__ bias,
           float* __restrict__ out, int B, int K, int Nout, int relu) {
     __shared__ float in_s[kFcBoards][kFcKTile];
+    __shared__ float red[3][kFcBoards][64];
     const int b0 = blockIdx.x * kFcBoards;
-    const int j = blockIdx.y * kFcThreads + threadIdx.x;
+    const int jl = threadIdx.x & 63, slice = threadIdx.x >> 6;
+    const int j = blockIdx.y * 64 + jl;
     float acc[kFcBoards];
 #pragma unroll
     for (int g = 0; g < kFcBoards; ++g) acc[g] = 0.0f;
@@ -77,19 +83,28 @@ fc_kernel(const float* __restrict__ in, const float* __restrict__ WT, const floa
         }
         __syncthreads();
         if (j < Nout) {
-            for (int i = 0; i < kt; ++i) {
-                const float wv = __ldg(WT + (size_t)(k0 + i) * Nout + j);
+            const int per = (kt + 3) / 4;
+            const int i0 = slice * per, i1 = min(kt, i0 + per);
+            const float* wp = WT + (size_t)k0 * Nout + j;
+#pragma unroll 4
+            for (int i = i0; i < i1; ++i) {
+                const float wv = __ldg(wp + (size_t)i * Nout);
 #pragma unroll
                 for (int g = 0; g < kFcBoards; ++g) acc[g] = fmaf(in_s[g][i], wv, acc[g]);
             }
         }
     }
-    if (j < Nout) {
+    if (slice > 0) {
+#pragma unroll
+        for (int g = 0; g < kFcBoards; ++g) red[slice - 1][g][jl] = acc[g];
+    }
+    __syncthreads();
+    if (slice == 0 && j < Nout) {
         const float bj = bias[j];
 #pragma unroll
         for (int g = 0; g < kFcBoards; ++g)
             if (b0 + g < B) {
-                float v = acc[g] + bj;
+                float v = acc[g] + red[0][g][jl] + red[1][g][jl] + red[2][g][jl] + bj;
                 if (relu) v = fmaxf(v, 0.0f);
                 out[(size_t)(b0 + g) * Nout + j] = v;
             }
@@ -148,7 +163,7 @@ int launch_head_conv(const void* tower, const float* w, const float* bias, int H
 
 int launch_fc(const float* in, const float* WT, const float* bias, float* out, int B, int K, int Nout, int relu,
               cudaStream_t st) {
-    dim3 grid((B + kFcBoards - 1) / kFcBoards, (Nout + kFcThreads - 1) / kFcThreads);
+    dim3 grid((B + kFcBoards - 1) / kFcBoards, (Nout + 63) / 64);
     fc_kernel<<<grid, kFcThreads, 0, st>>>(in, WT, bias, out, B, K, Nout, relu);
     OB200_LAUNCHED("fc_kernel");
     return OB200_OK;

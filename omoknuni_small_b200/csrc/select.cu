@@ -131,6 +131,37 @@ puct_select_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids, int 
     }
 }
 
+// Cheap bracket of the score: one MUFU reciprocal per division instead of an IEEE
+// divide.  rcp.approx is within 1 ulp, so with q~ = val * rcp(ev), u~ = (p*explore) *
+// rcp(1 + ev) and m = |q~| + |u~| the exact score s (the reference's fp32 expression)
+// satisfies |s - s~| < 2^-21 * m; kBracket = 2^-19 leaves a factor 4.  The staged kernel
+// uses the bracket to find the few slots that can hold the maximum and evaluates only
+// those with the exact expression, so the selected index is still bit-exact:
+//   T = max over slots of (s~ - kBracket*m) <= max s,   and the reference's choice i*
+//   (first slot attaining max s) has s~ + kBracket*m >= s_i* >= T, as has every slot tied
+//   with it; the exact pass over { s~ + kBracket*m >= T } in slot order therefore sees
+//   i* and everything that could beat or tie it.  NaN brackets compare false (never a
+//   candidate, as NaN scores are never selected) and are ignored by the maximum.
+constexpr float kBracket = 1.9073486328125e-06f;   // 2^-19
+
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+__device__ __forceinline__ void bracket(int n, float w, float p, int vl, float explore, bool legal, float& lo,
+                                        float& hi) {
+    const int ev = n + vl;
+    const float evf = (float)ev;
+    const float q = ev > 0 ? __fmul_rn(__fsub_rn(w, (float)vl), rcp_approx(evf)) : 0.0f;
+    const float u = __fmul_rn(__fmul_rn(p, explore), rcp_approx(__fadd_rn(1.0f, evf)));
+    const float s = __fadd_rn(q, u);
+    const float m = __fadd_rn(fabsf(q), fabsf(u));
+    lo = legal ? fmaf(-kBracket, m, s) : -INFINITY;
+    hi = legal ? fmaf(kBracket, m, s) : -INFINITY;
+}
+
 // ---------------------------------------------------------------------------
 // Staged variant for rows of up to 256 slots: a persistent grid, every warp
 // walks its own list of nodes and keeps a two-deep ring of rows in shared
@@ -218,15 +249,39 @@ puct_select_staged_kernel(ob200_tree_view t, const int32_t* __restrict__ node_id
             const float4* P4 = reinterpret_cast<const float4*>(st + 2 * row_bytes);
             const int4* V4 = reinterpret_cast<const int4*>(st + 3 * row_bytes);
             const uint32_t* mask = reinterpret_cast<const uint32_t*>(st + 4 * row_bytes);
+            // pass 1: brackets of this lane's slots (rows of <= 256 slots: two vectors a lane)
+            float hi[8];
+            float lane_lo = -INFINITY;
+            uint32_t legal8 = 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int v = lane + 32 * h;
+                const bool in = v < nvec;
+                const int vi = in ? v : 0;
+                const int4 nn = N4[vi]; const float4 ww = W4[vi]; const float4 pp = P4[vi]; const int4 ll = V4[vi];
+                const uint32_t m = in ? (mask[vi >> 3] >> ((vi & 7) * 4)) & 0xFu : 0u;
+                legal8 |= m << (4 * h);
+                float lo;
+                bracket(nn.x, ww.x, pp.x, ll.x, explore, m & 1u, lo, hi[4 * h + 0]); lane_lo = fmaxf(lane_lo, lo);
+                bracket(nn.y, ww.y, pp.y, ll.y, explore, m & 2u, lo, hi[4 * h + 1]); lane_lo = fmaxf(lane_lo, lo);
+                bracket(nn.z, ww.z, pp.z, ll.z, explore, m & 4u, lo, hi[4 * h + 2]); lane_lo = fmaxf(lane_lo, lo);
+                bracket(nn.w, ww.w, pp.w, ll.w, explore, m & 8u, lo, hi[4 * h + 3]); lane_lo = fmaxf(lane_lo, lo);
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) lane_lo = fmaxf(lane_lo, __shfl_xor_sync(0xffffffffu, lane_lo, off));
+            // pass 2: exact scores of the slots whose bracket reaches the best lower bound
             Best b{-INFINITY, -1};
-            for (int v = lane; v < nvec; v += 32) {
-                const int4 nn = N4[v]; const float4 ww = W4[v]; const float4 pp = P4[v]; const int4 ll = V4[v];
-                const uint32_t m = (mask[v >> 3] >> ((v & 7) * 4)) & 0xFu;
-                const int s0 = v * 4;
-                consider(b, s0 + 0, m & 1u, nn.x, ww.x, pp.x, ll.x, explore);
-                consider(b, s0 + 1, m & 2u, nn.y, ww.y, pp.y, ll.y, explore);
-                consider(b, s0 + 2, m & 4u, nn.z, ww.z, pp.z, ll.z, explore);
-                consider(b, s0 + 3, m & 8u, nn.w, ww.w, pp.w, ll.w, explore);
+            const int32_t* Ns = reinterpret_cast<const int32_t*>(N4);
+            const float* Ws = reinterpret_cast<const float*>(W4);
+            const float* Ps = reinterpret_cast<const float*>(P4);
+            const int32_t* Vs = reinterpret_cast<const int32_t*>(V4);
+#pragma unroll
+            for (int k2 = 0; k2 < 8; ++k2) {
+                if (((legal8 >> k2) & 1u) && hi[k2] >= lane_lo) {
+                    const int slot = (lane + 32 * (k2 >> 2)) * 4 + (k2 & 3);
+                    const float sc = puct_score(Ns[slot], Ws[slot], Ps[slot], Vs[slot], explore);
+                    if (sc > b.score) { b.score = sc; b.idx = slot; }
+                }
             }
             b = warp_combine(b);
             sel = b.idx >= 0 ? b.idx : least_visited_row(t, node, lane);

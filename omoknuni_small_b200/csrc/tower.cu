@@ -16,7 +16,7 @@
 //     the convolution's padding.
 // Weights (BatchNorm folded, bf16, pre-swizzled on the host) stay resident in
 // shared memory for the whole launch.  Warp 0 produces (TMA loads), warp 1
-// issues the MMAs, warps 2-17 (two groups of 8 warps on alternate tiles) run the
+// issues the MMAs, warps 2-9 (two groups of 4 warps on alternate tiles) run the
 // epilogue: TMEM -> registers, + bias, + residual, ReLU, zero the padding
 // positions, bf16, swizzled staging tile in shared memory, one TMA store.
 //
@@ -43,7 +43,8 @@ constexpr int kStages = 3;
 constexpr int kAccStages = 4;
 constexpr int kTmemCols = kAccStages * kC;                         // 256 (power of two)
 constexpr int kEpiGroups = 2;
-constexpr int kEpiWarps = 8;             // per group: 4 TMEM lane quadrants x 2 halves of the 64 channels
+constexpr int kEpiWarps = 4;             // per group: 4 TMEM lane quadrants x (kEpiWarps / 4) slices of the 64 channels
+constexpr int kChPerThread = kC / (kEpiWarps / 4);   // channels one epilogue thread handles
 constexpr int kThreads = 64 + 32 * kEpiWarps * kEpiGroups;
 constexpr int kNumBars = 2 * kStages + 2 * kAccStages + 1;
 constexpr int kSmemBytes = kWBytes + kStages * kStageBytes + kEpiGroups * kOutBytes + kNumBars * 8 + kC * 4 + 16 + 1024;
@@ -57,9 +58,8 @@ struct ConvParams {
     int P;                    // real positions = B * slots
     int num_tiles;
     int S, GP, slots;
-    int halo;                 // halo rows of the TMA box (multiple of 8, >= GP + 1)
+    int halo;                 // halo rows of the TMA box (GP + 1)
     int relu;
-    int dbg;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -183,12 +183,18 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    // Programmatic dependent launch: the next layer's CTAs may start their own prologue
+    // (barriers, TMEM, weights) as soon as SMs free up; what depends on the previous
+    // kernel's output (activation loads, residual loads, output stores) sits behind
+    // griddepcontrol.wait below.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         // ---------------- producer: TMA loads global -> shared ----------------
         if (lane == 0) {
             mbar_arrive_expect_tx(w_bar, (uint32_t)kWBytes);
             bulk_g2s(smem_u32(w_s), p.w, (uint32_t)kWBytes, w_bar);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             const uint32_t box_bytes = (uint32_t)(kTileM + 2 * p.halo) * kRowBytes;
             int it = 0;
             for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
@@ -226,8 +232,6 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
                 const uint32_t d_tmem = tmem_base + (uint32_t)a * kC;
 #pragma unroll
                 for (int tap = 0; tap < 9; ++tap) {
-                    if ((p.dbg & 1) && tap > 0) break;
-                    if ((p.dbg & 8) && tap > 3) break;
 #pragma unroll
                     for (int ks = 0; ks < kC / 16; ++ks)
                         umma(d_tmem, a_lo + (uint32_t)(tap_off[tap] + ks * 2),
@@ -239,24 +243,22 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
         }
     } else {
         // ---------------- epilogue: TMEM -> registers -> shared -> TMA store ----------------
-        // Two groups of 8 warps take alternate tiles.  Within a group a warp owns one TMEM
-        // lane quadrant (32 positions; fixed by warp id % 4) and one half of the 64 channels,
-        // so a thread handles 32 channels of one position: the per-tile latency of one
-        // thread's instruction stream, not its throughput, is what paces a group.  The
-        // residual is fetched before the wait on the accumulator so that its latency hides
-        // behind the MMAs of the tile.
-        const int ew = warp - 2;                 // 0 .. 15
+        // Groups of kEpiWarps warps take alternate tiles.  Within a group a warp owns one TMEM
+        // lane quadrant (32 positions; fixed by warp id % 4) and one slice of the 64 channels.
+        // The residual is fetched before the wait on the accumulator so that its latency
+        // hides behind the MMAs of the tile.
+        const int ew = warp - 2;
         const int group = ew / kEpiWarps;
-        const int half = (ew % kEpiWarps) >> 2;  // channels [32*half, 32*half + 32)
-        const int q = warp & 3;                  // TMEM lane quadrant this warp may read
+        const int slice = (ew % kEpiWarps) >> 2;     // channels [kChPerThread*slice, +kChPerThread)
+        const int q = warp & 3;                      // TMEM lane quadrant this warp may read
         const int row = q * 32 + lane;
         const bool leader = (ew % kEpiWarps) == 0 && lane == 0;
+        constexpr int kChunks = kChPerThread / 8;    // 16-byte chunks per thread
         const uint8_t* __restrict__ resid = p.residual;
         uint8_t* stage_out = o_s + group * kOutBytes;
         const uint32_t stage_out_u32 = smem_u32(stage_out);
-        float bias_r[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) bias_r[j] = bias_s[half * 32 + j];
+        const float* bias_t = bias_s + slice * kChPerThread;
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         int it = group;
         for (int tile = blockIdx.x + group * gridDim.x; tile < p.num_tiles; tile += kEpiGroups * gridDim.x, it += kEpiGroups) {
             const int a = it % kAccStages;
@@ -267,32 +269,33 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
                 const int rr = pos % p.slots;
                 valid = (rr / p.GP < p.S) && (rr % p.GP < p.S);
             }
-            uint4 rs[4];
+            uint4 rs[kChunks];
             if (resid != nullptr && valid) {
-                const uint4* src = reinterpret_cast<const uint4*>(resid + (size_t)(OB200_GUARD + pos) * kRowBytes) + half * 4;
+                const uint4* src = reinterpret_cast<const uint4*>(resid + (size_t)(OB200_GUARD + pos) * kRowBytes) + slice * kChunks;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) rs[c] = __ldg(src + c);
+                for (int c = 0; c < kChunks; ++c) rs[c] = __ldg(src + c);
             } else {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) rs[c] = make_uint4(0u, 0u, 0u, 0u);
+                for (int c = 0; c < kChunks; ++c) rs[c] = make_uint4(0u, 0u, 0u, 0u);
             }
             if (!mbar_wait(accfull_bar(a), pa, abort_flag)) {
                 *abort_flag = 1; atomicExch(p.error, 3); break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t r[32];
-            tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kC + half * 32), r);
+            uint32_t r[kChPerThread];
+#pragma unroll
+            for (int h = 0; h < kChPerThread / 32; ++h)
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kC + slice * kChPerThread + h * 32), r + h * 32);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(accempty_bar(a));
-            if (p.dbg & 2) continue;
 
             // the previous store of this group must have finished reading the staging tile
             if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             group_bar(1 + 2 * group);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < kChunks; ++c) {
                 uint4 o = make_uint4(0u, 0u, 0u, 0u);
                 if (valid) {
                     const uint32_t rw[4] = {rs[c].x, rs[c].y, rs[c].z, rs[c].w};
@@ -300,16 +303,16 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         // bf16 -> fp32 is a 16-bit shift
-                        float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bias_r[c * 8 + 2 * j] + __uint_as_float(rw[j] << 16);
-                        float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bias_r[c * 8 + 2 * j + 1] + __uint_as_float(rw[j] & 0xFFFF0000u);
+                        float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bias_t[c * 8 + 2 * j] + __uint_as_float(rw[j] << 16);
+                        float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bias_t[c * 8 + 2 * j + 1] + __uint_as_float(rw[j] & 0xFFFF0000u);
                         if (p.relu) { v0 = fmaxf(v0, 0.0f); v1 = fmaxf(v1, 0.0f); }
-                        const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-                        ow[j] = *reinterpret_cast<const uint32_t*>(&h);
+                        const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+                        ow[j] = *reinterpret_cast<const uint32_t*>(&h2);
                     }
                     o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                 }
                 // 128-byte swizzle of the staging tile: 16-byte chunk k of row r sits at chunk k ^ (r % 8)
-                *reinterpret_cast<uint4*>(stage_out + row * kRowBytes + (((half * 4 + c) ^ (row & 7)) << 4)) = o;
+                *reinterpret_cast<uint4*>(stage_out + row * kRowBytes + (((slice * kChunks + c) ^ (row & 7)) << 4)) = o;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             group_bar(2 + 2 * group);
@@ -390,7 +393,7 @@ int make_board_tensor_map(const void* base, long long rows, int box_rows, BoardT
     return OB200_OK;
 }
 
-int conv_halo_rows(int S) { return (S + 2 + 7) / 8 * 8; }
+int conv_halo_rows(int S) { return S + 2; }   // |dy*(S+1)+dx| <= S+2 rows before / after a tile
 
 int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* packed_w,
                         const float* bias, const void* residual, int B, int S, int relu, cudaStream_t st) {
@@ -416,10 +419,15 @@ int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_
     if (!p.error) return set_error(OB200_ERR_CUDA, "conv3x3: cannot resolve the device error word");
     p.P = (int)g.P; p.num_tiles = (int)(g.Ppad / kTileM); p.S = S; p.GP = g.GP; p.slots = g.slots;
     p.halo = conv_halo_rows(S); p.relu = relu;
-    { static int dbg = -1; if (dbg < 0) { const char* e = std::getenv("OB200_CONV_DEBUG"); dbg = e ? std::atoi(e) : 0; } p.dbg = dbg; }
     const int grid = p.num_tiles < sms ? p.num_tiles : sms;   // one persistent CTA per SM
-    conv3x3_kernel<<<grid, kThreads, kSmemBytes, st>>>(*reinterpret_cast<const CUtensorMap*>(&in_map),
-                                                       *reinterpret_cast<const CUtensorMap*>(&out_map), p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv3x3_kernel, *reinterpret_cast<const CUtensorMap*>(&in_map),
+                                     *reinterpret_cast<const CUtensorMap*>(&out_map), p));
     OB200_LAUNCHED("conv3x3_kernel");
     return OB200_OK;
 }
