@@ -35,7 +35,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-from omoknuni_small_b200 import synth  # noqa: E402
+from omoknuni_small_b200 import replicas, synth  # noqa: E402
 
 NET = dict(board_size=15, input_channels=17, filters=64, blocks=10, policy_size=225, policy_head_ch=2,
            value_head_ch=1, value_hidden=256)
@@ -162,9 +162,7 @@ def gpu_arm(args):
     from omoknuni_small_b200 import capi
     import ctypes as C
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
+    rank, world, local = replicas.rank_info()
     torch.cuda.set_device(local)
     dev = f"cuda:{local}"
     dist = None
@@ -184,7 +182,7 @@ def gpu_arm(args):
                                      NET["policy_size"], NET["policy_head_ch"], NET["value_head_ch"])
     w = synth.make_weights(shapes, seed=42, init="kaiming_normal")
     net = capi.Net(17, 15, NET["blocks"], 64, 225, NET["policy_head_ch"], NET["value_head_ch"], 256, B, local).load(w)
-    games, hist, nh, tm = synth.make_gomoku_games(B, 15, seed=1000 + rank)
+    games, hist, nh, tm = synth.make_gomoku_games(B, 15, seed=replicas.shard_seed(1000, rank))
     d_hist, d_nh, d_tm = (torch.from_numpy(a).to(dev) for a in (hist, nh, tm))
     d_policy = torch.empty((B, 225), dtype=torch.float32, device=dev)
     d_value = torch.empty(B, dtype=torch.float32, device=dev)
@@ -241,7 +239,7 @@ def gpu_arm(args):
         conv_loop()
         conv_ms = float(np.mean(timed(conv_loop, 5))) / reps
         # ---- batched PUCT selection + virtual loss, 65,536 x 225 ----
-        t = synth.make_selection_tree(SEL_NODES, SEL_CHILDREN, seed=7 + rank)
+        t = synth.make_selection_tree(SEL_NODES, SEL_CHILDREN, seed=replicas.shard_seed(7, rank))
         dt = capi.DeviceTree(t, dev)
         sel = torch.empty(SEL_NODES, dtype=torch.int32, device=dev)
 
@@ -253,21 +251,28 @@ def gpu_arm(args):
             dt.select(None, 1.5, 3, True, out=sel)
         for _ in range(3):
             sel_pass()
-        sel_ms = float(np.mean(timed(sel_pass, max(K, 10))))
-        dt.vl_revert(sel, 3)
-        selk_ms = float(np.mean(timed(sel_only, max(K, 10))))
+        # one pass reads 240 MB, more than the 126 MB L2, so passes run back to back unflushed
+        sel_reps = 10
+
+        def sel_pass_loop():
+            for _ in range(sel_reps):
+                sel_pass()
+
+        def sel_only_loop():
+            for _ in range(sel_reps):
+                sel_only()
+        sel_ms = float(np.mean(timed(sel_pass_loop, 5, per_iter_flush=False))) / sel_reps
+        selk_ms = float(np.mean(timed(sel_only_loop, 5, per_iter_flush=False))) / sel_reps
+        dt.t["VL"].copy_(torch.from_numpy(t["VL"]).to(dev))
         torch.cuda.synchronize()
     assert capi.device_error_code() == 0, "a kernel gave up on a bounded wait"
 
-    times = torch.tensor([total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms], dtype=torch.float64, device=dev)
-    if dist is not None:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-        cnt = torch.tensor([capi.counters()["evals"]], dtype=torch.int64, device=dev)
-        dist.all_reduce(cnt)                     # the only cross-GPU step: summing per-GPU counters
-    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms = times.tolist()
+    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms = replicas.max_over_ranks(
+        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms], dev)
+    totals = replicas.sum_counters(dist, capi.counters(), dev)   # the only cross-GPU step: per-GPU counters summed
     if rank == 0:
         flops_eval = synth.net_flops_per_eval(15, 17, 64, NET["blocks"], 225, NET["policy_head_ch"], NET["value_head_ch"])
-        value = world * B * K / (total_ms * 1e-3)
+        value = replicas.aggregate_throughput(B, K, world, total_ms)
         conv_flops = 2.0 * 225 * 9 * 64 * 64 * B
         conv_tf = conv_flops / (conv_ms * 1e-3) / 1e12
         sel_bytes = synth.selection_bytes_per_node(SEL_CHILDREN) * SEL_NODES
@@ -282,16 +287,16 @@ def gpu_arm(args):
                        "replicas": world, "weights": "kaiming-normal seed 42, BN identity"},
             "e2e": {"value": world * B * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": B * 34,
                     "d2h_bytes_per_step": B * 226 * 4},
-            "gpu_launches": int(launches),
+            "gpu_launches": int(launches), "counters_all_gpus": totals,
             "tower_tflops": value / world * flops_eval / 1e12,
-            "roofline": {"kernel": "conv3x3_kernel<8> (64->64, residual+ReLU)", "bound": "tensor", "achieved": conv_tf,
+            "roofline": {"kernel": "conv3x3_kernel (64->64, residual+ReLU)", "bound": "tensor", "achieved": conv_tf,
                          "peak": peaks["bf16_burst"], "unit": "TFLOP/s", "frac": conv_tf / peaks["bf16_burst"],
                          "frac_of_sustained": conv_tf / peaks["bf16_sustained"] if peaks["bf16_sustained"] else None,
                          "peak_source": peaks["source"] + " (burst: kernel timed alone)", "us_per_launch": conv_ms * 1e3,
                          "traffic": None},
             "selection": {"value": SEL_NODES / (sel_ms * 1e-3), "unit": "node selections/s (select + VL apply + VL revert)",
                           "nodes": SEL_NODES, "children": SEL_CHILDREN, "ms_per_pass": sel_ms,
-                          "roofline": {"kernel": "puct_select_kernel", "bound": "hbm",
+                          "roofline": {"kernel": "puct_select_staged_kernel", "bound": "hbm",
                                        "achieved": selk_bytes / (selk_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                                        "unit": "GB/s", "frac": selk_bytes / (selk_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                                        "peak_source": peaks["source"], "us_per_launch": selk_ms * 1e3, "traffic": None},

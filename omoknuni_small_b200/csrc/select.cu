@@ -53,11 +53,9 @@ __device__ __forceinline__ Best warp_combine(Best b) {
 // The reference's fallback when no score compared greater than -inf (all NaN or
 // -inf): the least-visited existing child, first one on ties
 // (src/mcts/mcts_node.cpp:173-181).  Rare, so it is a second scan of N only.
-__device__ __noinline__ int least_visited_row(const ob200_tree_view& t, int node, int lane) {
-    const int32_t* N = t.N + (size_t)node * t.pitch;
-    const uint32_t* mask = t.legal_bits + (size_t)node * t.mask_words;
+__device__ __noinline__ int least_visited_row(const int32_t* N, const uint32_t* mask, int n_children, int lane) {
     int mn = INT_MAX, mi = -1;
-    for (int s = lane; s < t.n_children; s += 32)
+    for (int s = lane; s < n_children; s += 32)
         if ((mask[s >> 5] >> (s & 31)) & 1u) {
             const int n = N[s];
             if (n < mn) { mn = n; mi = s; }
@@ -112,7 +110,8 @@ __device__ __forceinline__ int select_row(const ob200_tree_view& t, int node, fl
         consider(b, sb + 3, mb & 8u, nb.w, wb.w, pb.w, lb.w, explore);
     }
     b = warp_combine(b);
-    if (b.idx < 0) return least_visited_row(t, node, lane);
+    if (b.idx < 0)
+        return least_visited_row(t.N + (size_t)node * t.pitch, t.legal_bits + (size_t)node * t.mask_words, t.n_children, lane);
     return b.idx;
 }
 
@@ -164,14 +163,14 @@ __device__ __forceinline__ void bracket(int n, float w, float p, int vl, float e
 
 // ---------------------------------------------------------------------------
 // Staged variant for rows of up to 256 slots: a persistent grid, every warp
-// walks its own list of nodes and keeps a two-deep ring of rows in shared
+// walks its own list of nodes and keeps a three-deep ring of rows in shared
 // memory, filled by 1-D bulk async copies (one per array row, completion on an
-// mbarrier).  The copies of the next node are in flight while the current one
+// mbarrier).  The copies of the next two nodes are in flight while the current one
 // is scored from shared memory, so HBM latency is hidden by the ring instead of
 // by occupancy, and the registers are free for the arithmetic.
 // ---------------------------------------------------------------------------
-constexpr int kStagedWarps = 24;
-constexpr int kStagedDepth = 2;
+constexpr int kStagedWarps = 20;
+constexpr int kStagedDepth = 3;
 constexpr int kStagedMaxPitch = 256;
 constexpr uint32_t kStagedSpin = 1u << 24;
 
@@ -180,7 +179,8 @@ __device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cv
 __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < kStagedSpin; ++i) {
         uint32_t ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        // the hint lets the hardware park the thread for up to ~1 us instead of spinning
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 1000;\nselp.u32 %0, 1, 0, p;\n}"
                      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
     }
@@ -212,32 +212,55 @@ puct_select_staged_kernel(ob200_tree_view t, const int32_t* __restrict__ node_id
     const int first = blockIdx.x * kStagedWarps + warp;
     const int nvec = t.pitch >> 2;
 
-    auto fetch = [&](int i, int stage) {       // lane 0 only
+    // Lanes 0-4 each issue one of the five row copies of a node; lane 0 also posts the byte
+    // count (a copy that completes before the count is posted only drives the pending byte
+    // count negative; the phase cannot complete before lane 0's arrival).
+    auto fetch = [&](int i, int stage) {       // call with lanes 0-4
         const int node = node_ids ? node_ids[i] : i;
         if (node < 0 || node >= t.n_nodes) return;     // nothing to copy; the consumer skips it too
         const uint32_t bar = s_u32(bars + stage);
         const uint32_t dst = s_u32(ring + (size_t)stage * stage_bytes);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(4 * row_bytes + mask_bytes)) : "memory");
+        if (lane == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(4 * row_bytes + mask_bytes)) : "memory");
         const size_t off = (size_t)node * t.pitch;
-        row_copy(dst, t.N + off, row_bytes, bar);
-        row_copy(dst + row_bytes, t.W + off, row_bytes, bar);
-        row_copy(dst + 2 * row_bytes, t.P + off, row_bytes, bar);
-        row_copy(dst + 3 * row_bytes, t.VL + off, row_bytes, bar);
-        row_copy(dst + 4 * row_bytes, t.legal_bits + (size_t)node * t.mask_words, mask_bytes, bar);
+        const void* src = lane == 0 ? (const void*)(t.N + off) : lane == 1 ? (const void*)(t.W + off)
+                        : lane == 2 ? (const void*)(t.P + off) : lane == 3 ? (const void*)(t.VL + off)
+                                    : (const void*)(t.legal_bits + (size_t)node * t.mask_words);
+        row_copy(dst + lane * row_bytes, src, lane == 4 ? mask_bytes : row_bytes, bar);
     };
 
-    if (first < n && lane == 0) fetch(first, 0);
+    // node id and node visit count travel in a small register queue, loaded when the
+    // node's rows are requested, so that no global load sits between a full barrier and
+    // the arithmetic
+    int q_node[kStagedDepth - 1], q_visits[kStagedDepth - 1];
+    auto lookup = [&](int i, int& node, int& visits) {
+        node = -1; visits = 0;
+        if (i < n) {
+            node = node_ids ? __ldg(node_ids + i) : i;
+            if (node < 0 || node >= t.n_nodes) node = -1;
+            else visits = __ldg(t.node_visits + node);
+        }
+    };
+#pragma unroll
+    for (int d = 0; d < kStagedDepth - 1; ++d) {
+        lookup(first + d * total_warps, q_node[d], q_visits[d]);
+        if (first + d * total_warps < n && lane < 5) fetch(first + d * total_warps, d);
+    }
     uint32_t phase_bits = 0;                   // one parity bit per stage
     int k = 0;
     for (int i = first; i < n; i += total_warps, ++k) {
         const int stage = k % kStagedDepth;
-        const int nxt = i + total_warps;
+        const int nxt = i + (kStagedDepth - 1) * total_warps;
         __syncwarp();                           // every lane is done reading the stage about to be refilled
-        if (nxt < n && lane == 0) fetch(nxt, (k + 1) % kStagedDepth);
-        const int node = node_ids ? node_ids[i] : i;
+        if (nxt < n && lane < 5) fetch(nxt, (k + kStagedDepth - 1) % kStagedDepth);
+        const int node = q_node[0];
+        const int visits = q_visits[0];
+#pragma unroll
+        for (int d = 0; d + 1 < kStagedDepth - 1; ++d) { q_node[d] = q_node[d + 1]; q_visits[d] = q_visits[d + 1]; }
+        lookup(nxt, q_node[kStagedDepth - 2], q_visits[kStagedDepth - 2]);
         int sel = -1;
-        if (node >= 0 && node < t.n_nodes) {
-            const float explore = __fmul_rn(c_puct, __fsqrt_rn((float)__ldg(t.node_visits + node)));
+        if (node >= 0) {
+            const float explore = __fmul_rn(c_puct, __fsqrt_rn((float)visits));
             if (!bar_wait(s_u32(bars + stage), (phase_bits >> stage) & 1u)) {
                 if (lane == 0) atomicExch(error_word, 4);
                 break;
@@ -269,22 +292,36 @@ puct_select_staged_kernel(ob200_tree_view t, const int32_t* __restrict__ node_id
             }
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) lane_lo = fmaxf(lane_lo, __shfl_xor_sync(0xffffffffu, lane_lo, off));
-            // pass 2: exact scores of the slots whose bracket reaches the best lower bound
-            Best b{-INFINITY, -1};
-            const int32_t* Ns = reinterpret_cast<const int32_t*>(N4);
-            const float* Ws = reinterpret_cast<const float*>(W4);
-            const float* Ps = reinterpret_cast<const float*>(P4);
-            const int32_t* Vs = reinterpret_cast<const int32_t*>(V4);
+            // pass 2: the slots whose bracket reaches the best lower bound.  Usually there is
+            // exactly one, and with a finite bound it is the answer without any exact score.
+            uint32_t cand = 0;
 #pragma unroll
-            for (int k2 = 0; k2 < 8; ++k2) {
-                if (((legal8 >> k2) & 1u) && hi[k2] >= lane_lo) {
-                    const int slot = (lane + 32 * (k2 >> 2)) * 4 + (k2 & 3);
-                    const float sc = puct_score(Ns[slot], Ws[slot], Ps[slot], Vs[slot], explore);
-                    if (sc > b.score) { b.score = sc; b.idx = slot; }
+            for (int k2 = 0; k2 < 8; ++k2) cand |= (uint32_t)(((legal8 >> k2) & 1u) && hi[k2] >= lane_lo) << k2;
+            const uint32_t lanes_with = __ballot_sync(0xffffffffu, cand != 0);
+            const uint32_t lanes_multi = __ballot_sync(0xffffffffu, (cand & (cand - 1)) != 0);
+            Best b{-INFINITY, -1};
+            if (__popc(lanes_with) == 1 && lanes_multi == 0 && lane_lo > -INFINITY) {
+                const int k2 = __ffs(cand) - 1;                       // valid on the owning lane only
+                const int slot = (lane + 32 * (k2 >> 2)) * 4 + (k2 & 3);
+                b.idx = __shfl_sync(0xffffffffu, slot, __ffs(lanes_with) - 1);
+            } else {
+                const int32_t* Ns = reinterpret_cast<const int32_t*>(N4);
+                const float* Ws = reinterpret_cast<const float*>(W4);
+                const float* Ps = reinterpret_cast<const float*>(P4);
+                const int32_t* Vs = reinterpret_cast<const int32_t*>(V4);
+#pragma unroll
+                for (int k2 = 0; k2 < 8; ++k2) {
+                    if ((cand >> k2) & 1u) {
+                        const int slot = (lane + 32 * (k2 >> 2)) * 4 + (k2 & 3);
+                        const float sc = puct_score(Ns[slot], Ws[slot], Ps[slot], Vs[slot], explore);
+                        if (sc > b.score) { b.score = sc; b.idx = slot; }
+                    }
                 }
+                b = warp_combine(b);
             }
-            b = warp_combine(b);
-            sel = b.idx >= 0 ? b.idx : least_visited_row(t, node, lane);
+            sel = b.idx >= 0 ? b.idx
+                             : least_visited_row(t.N + (size_t)node * t.pitch, t.legal_bits + (size_t)node * t.mask_words,
+                                                 t.n_children, lane);
         }
         if (lane == 0) {
             sel_out[i] = sel;
@@ -440,18 +477,18 @@ int ob200_launch_puct_select(const ob200_tree_view* tree, const int32_t* node_id
     if (n < 0 || (!node_ids && n > tree->n_nodes) || !sel_out)
         return set_error(OB200_ERR_INVALID, "ob200_launch_puct_select: bad n (%d) or null output", n);
     if (int rc = require_device()) return rc;
-    if (tree->pitch <= kStagedMaxPitch && (tree->mask_words & 3) == 0 && n >= 1024) {
+    const int stage_bytes = (4 * tree->pitch * 4 + tree->mask_words * 4 + 127) & ~127;
+    const int staged_smem = kStagedWarps * kStagedDepth * stage_bytes + kStagedWarps * kStagedDepth * 8;
+    if (tree->pitch <= kStagedMaxPitch && (tree->mask_words & 3) == 0 && n >= 1024 && staged_smem <= 227 * 1024) {
         // rows small enough to ring-buffer in shared memory: persistent staged kernel
         int dev = 0, sms = 0;
         OB200_CUDA_OK(cudaGetDevice(&dev));
         OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        const int stage_bytes = (4 * tree->pitch * 4 + tree->mask_words * 4 + 127) & ~127;
-        const int smem = kStagedWarps * kStagedDepth * stage_bytes + kStagedWarps * kStagedDepth * 8;
-        static bool configured[64] = {false};
-        if (dev >= 0 && dev < 64 && !configured[dev]) {
-            OB200_CUDA_OK(cudaFuncSetAttribute(puct_select_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               kStagedWarps * kStagedDepth * ((4 * kStagedMaxPitch * 4 + 64 * 4 + 127) & ~127) + kStagedWarps * kStagedDepth * 8));
-            configured[dev] = true;
+        const int smem = staged_smem;
+        static int configured[64] = {0};
+        if (dev >= 0 && dev < 64 && configured[dev] < smem) {
+            OB200_CUDA_OK(cudaFuncSetAttribute(puct_select_staged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            configured[dev] = smem;
         }
         int* errw = device_error_word();
         if (!errw) return set_error(OB200_ERR_CUDA, "ob200_launch_puct_select: cannot resolve the device error word");
