@@ -1,0 +1,171 @@
+// Drop-in for the reference project's network class: implements
+// alphazero::nn::NeuralNetwork (reference include/nn/neural_network.h:20-147)
+// on top of the C ABI in include/omoknuni_b200.h.  Header-only; compile it
+// inside the reference project (it needs the reference's own headers) and link
+// libomoknuni_b200.so.  No libtorch.
+//
+// Behaviour kept from alphazero::nn::ResNetModel (reference
+// src/nn/resnet_model.cpp):
+//   * constructor arguments in the same order (:51-53), plus the two head
+//     widths the reference hard-codes as 32 (:81,:90);
+//   * inference() returns one NetworkOutput per state, policy = softmax
+//     probabilities over the whole action space, value in [-1, 1] (:752-763);
+//   * a null state contributes all-zero planes (:412-416);
+//   * any failure returns a uniform policy and value 0 for every state
+//     (:610-623, :801-810) — inference() never throws;
+//   * getInputShape() = {channels, board, board}, getPolicySize() (:866-873).
+// Weights enter by the reference's parameter names (setTensor) or from a flat
+// file written by save().
+#pragma once
+
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "nn/neural_network.h"   // reference header
+#include "omoknuni_b200.h"
+
+namespace omoknuni_b200 {
+
+class B200Network : public alphazero::nn::NeuralNetwork {
+public:
+    B200Network(int64_t input_channels, int64_t board_size, int64_t num_res_blocks = 10, int64_t num_filters = 64,
+                int64_t policy_size = 0, int policy_head_ch = 32, int value_head_ch = 32, int max_batch = 1024,
+                int device = 0) {
+        cfg_.board_size = (int32_t)board_size;
+        cfg_.input_channels = (int32_t)input_channels;
+        cfg_.filters = (int32_t)num_filters;
+        cfg_.blocks = (int32_t)num_res_blocks;
+        cfg_.policy_size = (int32_t)(policy_size ? policy_size : board_size * board_size);
+        cfg_.policy_head_ch = policy_head_ch;
+        cfg_.value_head_ch = value_head_ch;
+        cfg_.value_hidden = 256;
+        cfg_.max_batch = max_batch;
+        cfg_.device = device;
+        if (ob200_net_create(&cfg_, &net_) != OB200_OK) {
+            std::fprintf(stderr, "[B200Network] %s\n", ob200_last_error());
+            net_ = nullptr;
+        }
+    }
+    ~B200Network() override { ob200_net_destroy(net_); }
+    B200Network(const B200Network&) = delete;
+    B200Network& operator=(const B200Network&) = delete;
+
+    bool ok() const { return net_ != nullptr; }
+
+    // One tensor under the reference module's name, e.g. "res_blocks.3.bn1.running_var".
+    bool setTensor(const std::string& name, const float* data, int64_t numel) {
+        if (!net_) return false;
+        kept_.push_back({name, std::vector<float>(data, data + numel)});
+        return report(ob200_net_set_tensor(net_, name.c_str(), data, numel));
+    }
+    bool finalize() { return net_ && report(ob200_net_finalize(net_)) && (ready_ = true); }
+
+    std::vector<alphazero::mcts::NetworkOutput> inference(
+        const std::vector<std::unique_ptr<alphazero::core::IGameState>>& states) override {
+        const size_t n = states.size();
+        const int A = cfg_.policy_size;
+        std::vector<alphazero::mcts::NetworkOutput> out(n);
+        for (auto& o : out) { o.policy.assign(A, 1.0f / (float)A); o.value = 0.0f; }   // the reference's default outputs
+        if (n == 0 || !net_ || !ready_) return out;
+        try {
+            std::vector<float> policy((size_t)cfg_.max_batch * A), value(cfg_.max_batch);
+            for (size_t first = 0; first < n; first += (size_t)cfg_.max_batch) {
+                const int B = (int)std::min(n - first, (size_t)cfg_.max_batch);
+                const bool gomoku = allGomoku(states, first, B) && (cfg_.input_channels == 17 || cfg_.input_channels == 19);
+                int rc;
+                if (gomoku) {
+                    // Gomoku: the device encoder needs only the last 16 moves and the side to move
+                    std::vector<int16_t> hist((size_t)B * 16, (int16_t)-1);
+                    std::vector<uint8_t> nh(B, 0), tm(B, 2);
+                    for (int b = 0; b < B; ++b) {
+                        const auto& st = states[first + b];
+                        if (!st) continue;                                  // null state: zero planes
+                        const std::vector<int> mv = st->getMoveHistory();
+                        const int k = (int)std::min<size_t>(16, mv.size());
+                        for (int i = 0; i < k; ++i) hist[(size_t)b * 16 + i] = (int16_t)mv[mv.size() - 1 - i];
+                        nh[b] = (uint8_t)k;
+                        tm[b] = (uint8_t)st->getCurrentPlayer();
+                    }
+                    rc = ob200_net_infer_gomoku(net_, hist.data(), nh.data(), tm.data(), B, policy.data(), value.data(),
+                                                OB200_OUT_PROBS);
+                } else {
+                    // any other game: the state's own planes, as prepareInputTensor gathers them (:258-260, :410-494)
+                    const int S = cfg_.board_size, C = cfg_.input_channels;
+                    std::vector<float> planes((size_t)B * C * S * S, 0.0f);
+                    for (int b = 0; b < B; ++b) {
+                        const auto& st = states[first + b];
+                        if (!st) continue;
+                        const auto t = (C == 3) ? st->getTensorRepresentation() : st->getEnhancedTensorRepresentation();
+                        for (int c = 0; c < C && c < (int)t.size(); ++c)
+                            for (int r = 0; r < S && r < (int)t[c].size(); ++r)
+                                std::memcpy(&planes[(((size_t)b * C + c) * S + r) * S], t[c][r].data(),
+                                            sizeof(float) * std::min<size_t>(S, t[c][r].size()));
+                    }
+                    rc = ob200_net_infer_planes(net_, planes.data(), B, C, policy.data(), value.data(), OB200_OUT_PROBS);
+                }
+                if (rc != OB200_OK) { report(rc); continue; }               // this slice keeps the default outputs
+                for (int b = 0; b < B; ++b) {
+                    out[first + b].policy.assign(policy.begin() + (size_t)b * A, policy.begin() + (size_t)(b + 1) * A);
+                    out[first + b].value = value[b];
+                }
+            }
+        } catch (...) {
+            // as the reference: swallow and keep the defaults
+        }
+        return out;
+    }
+
+    // Flat weight file: repeated { uint32 name_len, name, uint64 numel, float data[numel] }.
+    void save(const std::string& path) override {
+        std::FILE* f = std::fopen(path.c_str(), "wb");
+        if (!f) return;
+        for (const auto& t : kept_) {
+            const uint32_t len = (uint32_t)t.name.size();
+            const uint64_t numel = t.data.size();
+            std::fwrite(&len, 4, 1, f); std::fwrite(t.name.data(), 1, len, f);
+            std::fwrite(&numel, 8, 1, f); std::fwrite(t.data.data(), 4, numel, f);
+        }
+        std::fclose(f);
+    }
+    void load(const std::string& path) override {
+        std::FILE* f = std::fopen(path.c_str(), "rb");
+        if (!f) return;
+        uint32_t len; uint64_t numel;
+        while (std::fread(&len, 4, 1, f) == 1 && len < 4096) {
+            std::string name(len, '\0');
+            if (std::fread(&name[0], 1, len, f) != len || std::fread(&numel, 8, 1, f) != 1) break;
+            std::vector<float> data(numel);
+            if (std::fread(data.data(), 4, numel, f) != numel) break;
+            setTensor(name, data.data(), (int64_t)numel);
+        }
+        std::fclose(f);
+        finalize();
+    }
+    std::vector<int64_t> getInputShape() const override { return {cfg_.input_channels, cfg_.board_size, cfg_.board_size}; }
+    int64_t getPolicySize() const override { return cfg_.policy_size; }
+
+private:
+    struct Kept { std::string name; std::vector<float> data; };
+
+    static bool allGomoku(const std::vector<std::unique_ptr<alphazero::core::IGameState>>& s, size_t first, int B) {
+        for (int b = 0; b < B; ++b)
+            if (s[first + b] && s[first + b]->getGameType() != alphazero::core::GameType::GOMOKU) return false;
+        return true;
+    }
+    bool report(int rc) {
+        if (rc != OB200_OK) std::fprintf(stderr, "[B200Network] %s\n", ob200_last_error());
+        return rc == OB200_OK;
+    }
+
+    ob200_net_config cfg_{};
+    ob200_net* net_ = nullptr;
+    bool ready_ = false;
+    std::vector<Kept> kept_;
+};
+
+}  // namespace omoknuni_b200
