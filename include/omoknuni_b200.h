@@ -285,6 +285,30 @@ int ob200_net_forward_device(ob200_net* net, const void* input_board_tensor, int
 /* Device pointer of the tower's output board tensor of the last forward
  * (filters channels), for tests. */
 const void* ob200_net_debug_tower_output(ob200_net* net);
+/* The value head alone, for callers that must never allocate.  (No counterpart in
+ * the reference: its value head runs inside ResNetModel::forward on libtorch's
+ * caching allocator.)  Meant for search threads in the middle of a self-play loop
+ * and for processes whose device memory is budgeted once at start-up: a cudaMalloc
+ * there synchronises the whole device and stalls every other engine's stream, or
+ * simply fails when the budget is spent.  This call allocates nothing, on the
+ * device or the host: the two intermediates of the value head (1x1-convolution
+ * activations and the hidden layer) live in one array compiled into the library,
+ * 2 MiB per GPU, held by every GPU that loads the library until the process ends.
+ *   tower_board_tensor : DEVICE, 64-channel board tensor of B boards (the tower's
+ *       output, e.g. ob200_net_debug_tower_output after a forward);
+ *   value_out : DEVICE, B floats, tanh values; weights come from the handle.
+ * Limit: B * (value_head_ch * S * S + value_hidden) <= the capacity below (in
+ * floats; 524,288 = batch 1089 for the 15x15, 1-channel head); more returns
+ * OB200_ERR_TOO_LARGE.  The first call on each device looks the array's address up;
+ * make that first call outside any stream capture.  All calls on a device share the
+ * array, which keeps whatever the last call left: nothing needs clearing because each
+ * launch overwrites what the next one reads, but two calls whose kernels overlap on
+ * the GPU (different streams, no ordering) race on it — order them.  Asynchronous on
+ * `stream`; results are identical to the value output of ob200_net_forward_device. */
+int ob200_net_value_head_noalloc(ob200_net* net, const void* tower_board_tensor, int32_t B,
+                                 float* value_out, ob200_stream stream);
+int64_t ob200_value_head_noalloc_capacity(void);
+
 /* Channel count of the input board tensor ob200_net_forward_device expects
  * (64: the stem runs on the same 64-channel kernel as the tower, with zero
  * weights for the channels beyond input_channels). */

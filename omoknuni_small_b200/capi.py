@@ -75,6 +75,8 @@ SIGNATURES = {
                                            C.c_void_p]),
     "ob200_net_debug_tower_output": (C.c_void_p, [C.c_void_p]),
     "ob200_net_input_tensor_channels": (C.c_int32, [C.c_void_p]),
+    "ob200_net_value_head_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
+    "ob200_value_head_noalloc_capacity": (C.c_int64, []),
     "ob200_device_error_code": (C.c_int, [C.POINTER(C.c_int32)]),
     "ob200_get_counters": (C.c_int, [C.POINTER(Counters)]),
     "ob200_reset_counters": (None, []),
@@ -318,6 +320,11 @@ class Net:
 
     def tower_output_ptr(self):
         return lib().ob200_net_debug_tower_output(self.h)
+
+    def value_head_noalloc(self, tower_ptr, B, value_out):
+        """Value head from a tower output already on the device, using only the
+        library's built-in scratch array (no allocation anywhere)."""
+        check(lib().ob200_net_value_head_noalloc(self.h, C.c_void_p(tower_ptr), B, _ptr(value_out), _stream()))
 
     def close(self):
         if self.h:

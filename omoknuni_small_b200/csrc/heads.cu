@@ -13,6 +13,7 @@
 //   value_out_kernel   value_fc2 + tanh (one warp per board).
 #include "internal.h"
 #include <cuda_bf16.h>
+#include <mutex>
 
 namespace ob200 {
 namespace {
@@ -179,6 +180,53 @@ int launch_value_out(const float* hidden, const float* w2, float b2, int H, int 
     value_out_kernel<<<(B * 32 + 255) / 256, 256, 0, st>>>(hidden, w2, b2, H, B, value);
     OB200_LAUNCHED("value_out_kernel");
     return OB200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Value head without any allocation.  The two intermediates of the value head
+// (the 1x1-convolution activations and the hidden layer) live in this
+// file-scope device array instead of buffers obtained from cudaMalloc.  Every
+// GPU that loads the library holds the 2 MiB until the process exits.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticScratchFloats = size_t(1) << 19;
+static __device__ __align__(256) float g_value_head_scratch[kStaticScratchFloats];
+
+size_t value_head_static_capacity() { return kStaticScratchFloats; }
+
+// In host code the array's name is only a stand-in for the symbol: its device address
+// is asked from the runtime once per device, with that device current.
+static int value_head_scratch_ptr(float** out) {
+    static std::mutex mu;
+    static float* cached[64] = {nullptr};
+    int dev = 0;
+    OB200_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return set_error(OB200_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lk(mu);
+    if (!cached[dev]) {
+        void* ptr = nullptr;
+        OB200_CUDA_OK(cudaGetSymbolAddress(&ptr, g_value_head_scratch));
+        cached[dev] = static_cast<float*>(ptr);
+    }
+    *out = cached[dev];
+    return OB200_OK;
+}
+
+int launch_value_head_static(const void* tower, const float* vw, const float* vb, int vc, const float* W1T,
+                             const float* b1, const float* w2, float b2, int H, int B, int S, float* value_out,
+                             cudaStream_t st) {
+    const size_t need = (size_t)B * ((size_t)vc * S * S + (size_t)H);
+    if (need > kStaticScratchFloats)
+        return set_error(OB200_ERR_TOO_LARGE,
+                         "value head without allocation: batch %d needs %zu scratch floats (%d x %d x %d + %d per board), the static array holds %zu",
+                         B, need, vc, S, S, H, kStaticScratchFloats);
+    float* scratch = nullptr;
+    if (int rc = value_head_scratch_ptr(&scratch)) return rc;
+    float* hv = scratch;                                  // [B][vc * S * S]
+    float* hidden = scratch + (size_t)B * vc * S * S;     // [B][H]
+    // every element read below is written first by the launch before it: nothing needs clearing
+    if (int rc = launch_head_conv(tower, vw, vb, vc, 0, hv, hv, B, S, st)) return rc;
+    if (int rc = launch_fc(hv, W1T, b1, hidden, B, vc * S * S, H, 1, st)) return rc;
+    return launch_value_out(hidden, w2, b2, H, B, value_out, st);
 }
 
 }  // namespace ob200

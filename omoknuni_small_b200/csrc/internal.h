@@ -24,5 +24,9 @@ int launch_fc(const float* in, const float* WT, const float* bias, float* out, i
               cudaStream_t st);
 int launch_softmax(float* x, int B, int A, cudaStream_t st);
 int launch_value_out(const float* hidden, const float* w2, float b2, int H, int B, float* value, cudaStream_t st);
+int launch_value_head_static(const void* tower, const float* vw, const float* vb, int vc, const float* W1T,
+                             const float* b1, const float* w2, float b2, int H, int B, int S, float* value_out,
+                             cudaStream_t st);
+size_t value_head_static_capacity();
 
 }  // namespace ob200

@@ -364,6 +364,22 @@ int ob200_net_forward_device(ob200_net* n, const void* input_board_tensor, int32
 }
 
 const void* ob200_net_debug_tower_output(ob200_net* n) { return n ? n->tower_out : nullptr; }
+
+int ob200_net_value_head_noalloc(ob200_net* n, const void* tower_board_tensor, int32_t B, float* value_out,
+                                 ob200_stream stream) {
+    if (!n || !tower_board_tensor || !value_out)
+        return set_error(OB200_ERR_INVALID, "ob200_net_value_head_noalloc: null argument");
+    if (!n->finalized) return set_error(OB200_ERR_STATE, "ob200_net_value_head_noalloc: weights not finalised");
+    if (B < 1) return set_error(OB200_ERR_INVALID, "ob200_net_value_head_noalloc: batch %d", B);
+    if (int rc = require_device()) return rc;
+    const ob200_net_config& c = n->cfg;
+    const int pc = c.policy_head_ch;
+    return launch_value_head_static(tower_board_tensor, n->head_w + (size_t)pc * c.filters, n->head_b + pc,
+                                    c.value_head_ch, n->W1T, n->b1, n->w2, n->b2, c.value_hidden, B, c.board_size,
+                                    value_out, as_stream(stream));
+}
+
+int64_t ob200_value_head_noalloc_capacity(void) { return (int64_t)value_head_static_capacity(); }
 int32_t ob200_net_input_tensor_channels(ob200_net* n) { return n ? n->cin_pad : 0; }
 
 }  // extern "C"
