@@ -2,9 +2,8 @@
 //
 // Output format (see "Board tensors" in omoknuni_b200.h): NHWC, positions on a
 // (S+1) x (S+1) grid per board whose last column / row are zero, guard
-// positions before and after.  One thread produces 8 channels of one position:
-// a single 16-byte store; consecutive threads write consecutive 16-byte words,
-// so every warp writes 512 contiguous bytes.  The kernels also write the zero
+// positions before and after.  A thread produces one position (its 16-byte
+// channel blocks one after the other); the kernels also write the zero
 // padding, so the output needs no memset.
 #include "internal.h"
 #include <cuda_bf16.h>
@@ -23,39 +22,47 @@ struct alignas(16) Pack8 { __nv_bfloat16 v[8]; };
 __global__ void __launch_bounds__(256)
 encode_gomoku_kernel(const int16_t* __restrict__ history, const uint8_t* __restrict__ n_hist,
                      const uint8_t* __restrict__ to_move, int B, int S, int planes, int chunks,
-                     long long cover, Pack8* __restrict__ out) {
-    // cover = positions written (guards included); chunks = channels / 8
-    const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (gid >= cover * chunks) return;
-    const int chunk = (int)(gid % chunks);
-    const long long p = gid / chunks - OB200_GUARD;
+                     int cover, Pack8* __restrict__ out) {
+    // cover = positions written (guards included); chunks = channels / 8.
+    // One thread per position writes all its chunks; only the first three can be non-zero.
+    const int pidx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pidx >= cover) return;
+    const int p = pidx - OB200_GUARD;
     const int GP = S + 1, slots = GP * GP;
-    Pack8 o;
+    int cell = -1, b = 0;
+    if (p >= 0 && p < B * slots) {
+        b = p / slots;
+        const int r = p - b * slots;
+        const int y = r / GP, x = r - y * GP;
+        if (y < S && x < S) cell = y * S + x;
+    }
+    Pack8 zero;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o.v[j] = __float2bfloat16(0.0f);
-    if (p >= 0 && p < (long long)B * slots) {
-        const int b = (int)(p / slots), r = (int)(p % slots);
-        const int y = r / GP, x = r % GP;
-        if (y < S && x < S) {
-            const int cell = y * S + x;
-            const int nh = n_hist[b];
+    for (int j = 0; j < 8; ++j) zero.v[j] = __float2bfloat16(0.0f);
+    Pack8* dst = out + (size_t)pidx * chunks;
+    if (cell < 0) {
+        for (int c = 0; c < chunks; ++c) dst[c] = zero;
+        return;
+    }
+    const int nh = n_hist[b];
+    const int16_t* h = history + (size_t)b * 16;
+    const float colour = (planes > 16 && to_move[b] == 1) ? 1.0f : 0.0f;
+    for (int c = 0; c < chunks; ++c) {
+        Pack8 o = zero;
+        if (c < 2) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const int plane = chunk * 8 + j;
-                float v = 0.0f;
-                if (plane < 16) {
-                    const int k = (plane & 1) ? plane - 1 : plane + 1;
-                    if (k < nh && history[(size_t)b * 16 + k] == cell) v = 1.0f;
-                } else if (plane == 16 && planes > 16) {
-                    v = (to_move[b] == 1) ? 1.0f : 0.0f;
-                }
-                // planes 17 / 18 (attack / defense): zero, as the reference's CPU code
-                // yields for every legal move (src/utils/attack_defense_module.cpp:96-154).
-                o.v[j] = __float2bfloat16(v);
+                const int plane = c * 8 + j;
+                const int k = (plane & 1) ? plane - 1 : plane + 1;
+                if (k < nh && h[k] == cell) o.v[j] = __float2bfloat16(1.0f);
             }
+        } else if (c == 2) {
+            // plane 16: colour.  Planes 17 / 18 (attack / defense): zero, as the reference's CPU
+            // code yields for every legal move (src/utils/attack_defense_module.cpp:96-154).
+            o.v[0] = __float2bfloat16(colour);
         }
+        dst[c] = o;
     }
-    out[gid] = o;
 }
 
 __global__ void __launch_bounds__(256)
@@ -99,9 +106,9 @@ int launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, const ui
     if (int rc = require_device()) return rc;
     const BoardGeom g = board_geom(board_size, B);
     const int chunks = out_channels / 8;
-    const long long total = g.PT * chunks;
-    encode_gomoku_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-        history, n_hist, to_move, B, board_size, planes, chunks, g.PT, reinterpret_cast<Pack8*>(board_tensor_out));
+    if (g.PT > 0x7fffffffLL / 2) return set_error(OB200_ERR_TOO_LARGE, "encode: batch too large");
+    encode_gomoku_kernel<<<(unsigned)((g.PT + 255) / 256), 256, 0, stream>>>(
+        history, n_hist, to_move, B, board_size, planes, chunks, (int)g.PT, reinterpret_cast<Pack8*>(board_tensor_out));
     OB200_LAUNCHED("encode_gomoku_kernel");
     return OB200_OK;
 }

@@ -67,7 +67,7 @@ head_conv_kernel(const uint8_t* __restrict__ tower, const float* __restrict__ w,
 __global__ void __launch_bounds__(kFcThreads)
 fc_kernel(const float* __restrict__ in, const float* __restrict__ WT, const float* __restrict__ bias,
           float* __restrict__ out, int B, int K, int Nout, int relu) {
-    __shared__ float in_s[kFcBoards][kFcKTile];
+    __shared__ __align__(16) float in_s[kFcBoards][kFcKTile];
     __shared__ float red[3][kFcBoards][64];
     const int b0 = blockIdx.x * kFcBoards;
     const int jl = threadIdx.x & 63, slice = threadIdx.x >> 6;
@@ -84,11 +84,24 @@ fc_kernel(const float* __restrict__ in, const float* __restrict__ WT, const floa
         }
         __syncthreads();
         if (j < Nout) {
-            const int per = (kt + 3) / 4;
+            // slices are multiples of 4 wide so that the staged inputs are read as float4:
+            // one shared-memory load feeds 4 multiply-adds (the loop is otherwise bound by
+            // shared-memory instruction issue)
+            const int per = ((kt + 3) / 4 + 3) & ~3;
             const int i0 = slice * per, i1 = min(kt, i0 + per);
             const float* wp = WT + (size_t)k0 * Nout + j;
-#pragma unroll 4
-            for (int i = i0; i < i1; ++i) {
+            int i = i0;
+            for (; i + 4 <= i1; i += 4) {
+                const float w0 = __ldg(wp + (size_t)i * Nout), w1 = __ldg(wp + (size_t)(i + 1) * Nout);
+                const float w2 = __ldg(wp + (size_t)(i + 2) * Nout), w3 = __ldg(wp + (size_t)(i + 3) * Nout);
+#pragma unroll
+                for (int g = 0; g < kFcBoards; ++g) {
+                    const float4 x = *reinterpret_cast<const float4*>(&in_s[g][i]);
+                    acc[g] = fmaf(x.x, w0, acc[g]); acc[g] = fmaf(x.y, w1, acc[g]);
+                    acc[g] = fmaf(x.z, w2, acc[g]); acc[g] = fmaf(x.w, w3, acc[g]);
+                }
+            }
+            for (; i < i1; ++i) {
                 const float wv = __ldg(wp + (size_t)i * Nout);
 #pragma unroll
                 for (int g = 0; g < kFcBoards; ++g) acc[g] = fmaf(in_s[g][i], wv, acc[g]);
