@@ -264,11 +264,23 @@ def gpu_arm(args):
         sel_ms = float(np.mean(timed(sel_pass_loop, 5, per_iter_flush=False))) / sel_reps
         selk_ms = float(np.mean(timed(sel_only_loop, 5, per_iter_flush=False))) / sel_reps
         dt.t["VL"].copy_(torch.from_numpy(t["VL"]).to(dev))
+        # ---- leaf-parallel MCTS: 64 games, 800 simulations per move, leaf batch = B ----
+        n_trees, sims = 64, 800
+        openings, _, _, _ = synth.make_gomoku_games(n_trees, 15, seed=replicas.shard_seed(100, rank), max_moves=20)
+        search = capi.Search(net, n_trees=n_trees, sims_per_move=sims, leaf_batch=B, max_depth=64, c_puct=1.5,
+                             virtual_loss=3, dirichlet_alpha=0.3, dirichlet_epsilon=0.25, value_sign=1, seed=rank)
+        search.run(openings)                                   # warm-up move
+        mcts_ms, mcts_sims, mcts_evals, mcts_moves = 0.0, 0, 0, max(2, min(K, 5))
+        for _ in range(mcts_moves):
+            flush.zero_()
+            torch.cuda.synchronize()
+            _, _, st = search.run(openings)
+            mcts_ms += st["device_ms"]; mcts_sims += st["simulations"]; mcts_evals += st["evaluations"]
         torch.cuda.synchronize()
     assert capi.device_error_code() == 0, "a kernel gave up on a bounded wait"
 
-    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms = replicas.max_over_ranks(
-        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms], dev)
+    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms = replicas.max_over_ranks(
+        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms], dev)
     totals = replicas.sum_counters(dist, capi.counters(), dev)   # the only cross-GPU step: per-GPU counters summed
     if rank == 0:
         flops_eval = synth.net_flops_per_eval(15, 17, 64, NET["blocks"], 225, NET["policy_head_ch"], NET["value_head_ch"])
@@ -293,14 +305,25 @@ def gpu_arm(args):
                          "peak": peaks["bf16_burst"], "unit": "TFLOP/s", "frac": conv_tf / peaks["bf16_burst"],
                          "frac_of_sustained": conv_tf / peaks["bf16_sustained"] if peaks["bf16_sustained"] else None,
                          "peak_source": peaks["source"] + " (burst: kernel timed alone)", "us_per_launch": conv_ms * 1e3,
-                         "traffic": None},
+                         # DRAM bytes per launch from the ncu capture at batch 512 (cold cache: input +
+                         # residual from DRAM, output left in L2), scaled by the boards processed
+                         "traffic": 31.63e6 * B / 512.0, "traffic_unit": "bytes/launch",
+                         "traffic_source": "profiles/conv3x3_kernel_gomoku15_batch512.md (scaled by batch)"},
             "selection": {"value": SEL_NODES / (sel_ms * 1e-3), "unit": "node selections/s (select + VL apply + VL revert)",
                           "nodes": SEL_NODES, "children": SEL_CHILDREN, "ms_per_pass": sel_ms,
                           "roofline": {"kernel": "puct_select_staged_kernel", "bound": "hbm",
                                        "achieved": selk_bytes / (selk_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                                        "unit": "GB/s", "frac": selk_bytes / (selk_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                                       "peak_source": peaks["source"], "us_per_launch": selk_ms * 1e3, "traffic": None},
+                                       "peak_source": peaks["source"], "us_per_launch": selk_ms * 1e3,
+                                       "algorithmic_bytes": selk_bytes, "traffic": 246.8e6, "traffic_unit": "bytes/launch",
+                                       "traffic_source": "profiles/puct_select_staged_kernel_65536x225.md"},
                           "pass_gbs": sel_bytes / (sel_ms * 1e-3) / 1e9},
+            "mcts": {"value": world * mcts_sims / (mcts_ms * 1e-3), "unit": "simulations/s",
+                     "leaf_evals_per_sec": world * mcts_evals / (mcts_ms * 1e-3),
+                     "config": {"games_per_gpu": 64, "sims_per_move": 800, "leaf_batch": B, "c_puct": 1.5, "virtual_loss": 3,
+                                "dirichlet": [0.3, 0.25], "openings": "seeded random, 0-20 stones", "moves_timed": mcts_moves,
+                                "transposition_table": "not built yet"},
+                     "ms_per_move": mcts_ms / mcts_moves, "timing": "CUDA events around each move, inside the library"},
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu:

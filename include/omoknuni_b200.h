@@ -320,6 +320,71 @@ int32_t ob200_net_input_tensor_channels(ob200_net* net);
  * check it themselves and return OB200_ERR_TIMEOUT. */
 int ob200_device_error_code(int32_t* code_out);
 
+/* ------------------------------------------------------------------------- *
+ *  Leaf-parallel search, Gomoku, device-resident trees.
+ *  Replaces MCTSEngine::runSearch / executeBatchedTreeSearch
+ *  (src/mcts/mcts_engine_search.cpp:347-406,
+ *  src/mcts/mcts_engine_batch_tree_simple.cpp:14-301) for a group of
+ *  independent games on one GPU, together with MCTSNode::expand
+ *  (src/mcts/mcts_node.cpp:238-436), addDirichletNoise
+ *  (src/mcts/mcts_engine_eval.cpp:83-110) and getActionProbabilities
+ *  (src/mcts/mcts_engine_tree.cpp:389-465).
+ *
+ *  Per move and per tree: the root is created from the game's move list and
+ *  evaluated once (priors = network policy, optionally mixed with Dirichlet
+ *  noise); then rounds of { descend leaf_batch / n_trees simulations per tree
+ *  with virtual loss (ob200_launch_traverse), rebuild each leaf's position from
+ *  the path, detect five-in-a-row / full board, encode, network forward, expand
+ *  (one new node per leaf edge, priors = clamp(policy), no renormalisation),
+ *  back up with virtual-loss revert } until sims_per_move simulations per tree
+ *  are done.  No host synchronisation inside a move.
+ *  Where the reference leaves things open or racy this defines them:
+ *  children are in action order (the reference shuffles them); simulations of a
+ *  tree inside a round run in sequence; a leaf reached twice in a round is
+ *  expanded once and backed up twice; a terminal leaf takes the game result
+ *  (-1 for the side to move after a five-in-a-row, 0 for a full board) instead
+ *  of the network value (the reference's batched loop asks the network even
+ *  then; its serial loop uses the result); value_sign = +1 adds the leaf value
+ *  to the leaf edge as the reference's batched loop does, -1 is negamax.
+ * ------------------------------------------------------------------------- */
+typedef struct ob200_search ob200_search;
+
+typedef struct ob200_search_config {
+    int32_t n_trees;            /* concurrent games on this GPU                    */
+    int32_t sims_per_move;      /* simulations per tree per move (800)             */
+    int32_t leaf_batch;         /* leaves per network call, multiple of n_trees    */
+    int32_t max_depth;          /* longest path recorded (<= 64)                   */
+    float c_puct;               /* MCTSSettings::exploration_constant              */
+    int32_t virtual_loss;       /* MCTSSettings::virtual_loss (3)                  */
+    float dirichlet_alpha;      /* 0.3                                             */
+    float dirichlet_epsilon;    /* 0.25; 0 disables the root noise                 */
+    int32_t value_sign;         /* +1 reference batched loop, -1 negamax           */
+    uint64_t seed;              /* root-noise generator                            */
+} ob200_search_config;
+
+typedef struct ob200_search_stats {
+    int64_t simulations;        /* all trees, this call                            */
+    int64_t evaluations;        /* positions sent to the network (roots included)  */
+    int64_t nodes;              /* nodes allocated, all trees                      */
+    int64_t terminal_leaves;    /* simulations that ended in a finished game       */
+    double device_ms;           /* device time of the call (CUDA events)           */
+} ob200_search_stats;
+
+/* `net` must be a finalised 15x15 Gomoku network with max_batch >= leaf_batch;
+ * the search borrows it (destroy the search first). */
+int ob200_search_create(ob200_net* net, const ob200_search_config* cfg, ob200_search** out);
+void ob200_search_destroy(ob200_search* s);
+/* One move for every tree.  HOST buffers.  moves[t * moves_stride + i], i in
+ * [0, n_moves[t]): the game so far (BLACK first), legal and unfinished.
+ * pi_out [n_trees][225]: visit counts -> (n / n_max)^(1/T) normalised, one-hot
+ * argmax for temperature < 0.01; visits_out [n_trees][225] may be NULL. */
+int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_moves, int32_t moves_stride,
+                     float temperature, float* pi_out, int32_t* visits_out, ob200_search_stats* stats);
+/* Test hooks: device pointers of the search's tree view and node counter, and a
+ * synchronous device-to-host copy for reading them. */
+int ob200_search_debug_tree(ob200_search* s, ob200_tree_view* view_out, int32_t* nodes_used_out);
+int ob200_copy_to_host(void* dst_host, const void* src_device, int64_t bytes);
+
 /* Per-device counters for the end-of-run reduction (the only cross-GPU step;
  * it replaces the MCTSStats fields total_evaluations / total_batches_processed,
  * include/mcts/mcts_engine.h:154-197). */

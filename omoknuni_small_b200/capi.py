@@ -33,6 +33,17 @@ class NetConfig(C.Structure):
                                           "policy_head_ch", "value_head_ch", "value_hidden", "max_batch", "device")]
 
 
+class SearchConfig(C.Structure):
+    _fields_ = [("n_trees", C.c_int32), ("sims_per_move", C.c_int32), ("leaf_batch", C.c_int32), ("max_depth", C.c_int32),
+                ("c_puct", C.c_float), ("virtual_loss", C.c_int32), ("dirichlet_alpha", C.c_float),
+                ("dirichlet_epsilon", C.c_float), ("value_sign", C.c_int32), ("seed", C.c_uint64)]
+
+
+class SearchStats(C.Structure):
+    _fields_ = [("simulations", C.c_int64), ("evaluations", C.c_int64), ("nodes", C.c_int64),
+                ("terminal_leaves", C.c_int64), ("device_ms", C.c_double)]
+
+
 class Counters(C.Structure):
     _fields_ = [(k, C.c_uint64) for k in ("evals", "batches", "selections", "backups", "kernel_launches")]
 
@@ -78,6 +89,12 @@ SIGNATURES = {
     "ob200_net_value_head_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "ob200_value_head_noalloc_capacity": (C.c_int64, []),
     "ob200_device_error_code": (C.c_int, [C.POINTER(C.c_int32)]),
+    "ob200_search_create": (C.c_int, [C.c_void_p, C.POINTER(SearchConfig), C.POINTER(C.c_void_p)]),
+    "ob200_search_destroy": (None, [C.c_void_p]),
+    "ob200_search_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_float, C.c_void_p, C.c_void_p,
+                                   C.POINTER(SearchStats)]),
+    "ob200_search_debug_tree": (C.c_int, [C.c_void_p, C.POINTER(TreeView), C.POINTER(C.c_int32)]),
+    "ob200_copy_to_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
     "ob200_get_counters": (C.c_int, [C.POINTER(Counters)]),
     "ob200_reset_counters": (None, []),
 }
@@ -329,6 +346,66 @@ class Net:
     def close(self):
         if self.h:
             lib().ob200_net_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---- leaf-parallel search ---------------------------------------------------------
+class Search:
+    """Leaf-parallel MCTS over a group of Gomoku games on one GPU (host-side mirror of
+    MCTSEngine::search for many games at once)."""
+
+    def __init__(self, net, n_trees=64, sims_per_move=800, leaf_batch=1024, max_depth=64, c_puct=1.5, virtual_loss=3,
+                 dirichlet_alpha=0.3, dirichlet_epsilon=0.25, value_sign=1, seed=0):
+        self.net = net                       # keep the network alive
+        self.cfg = SearchConfig(n_trees, sims_per_move, leaf_batch, max_depth, c_puct, virtual_loss, dirichlet_alpha,
+                                dirichlet_epsilon, value_sign, seed)
+        self.h = C.c_void_p()
+        check(lib().ob200_search_create(net.h, C.byref(self.cfg), C.byref(self.h)))
+
+    def run(self, move_lists, temperature=1.0):
+        """move_lists: one sequence of actions per tree.  Returns (pi [T,225], visits [T,225], stats dict)."""
+        T = self.cfg.n_trees
+        assert len(move_lists) == T
+        stride = max(1, max(len(m) for m in move_lists))
+        moves = np.full((T, stride), -1, np.int16)
+        n = np.zeros(T, np.int32)
+        for t, m in enumerate(move_lists):
+            moves[t, :len(m)] = m
+            n[t] = len(m)
+        pi = np.zeros((T, 225), np.float32)
+        visits = np.zeros((T, 225), np.int32)
+        st = SearchStats()
+        check(lib().ob200_search_run(self.h, moves.ctypes.data_as(C.c_void_p), n.ctypes.data_as(C.c_void_p), stride,
+                                     temperature, pi.ctypes.data_as(C.c_void_p), visits.ctypes.data_as(C.c_void_p),
+                                     C.byref(st)))
+        return pi, visits, {k: getattr(st, k) for k, _ in SearchStats._fields_}
+
+    def tree(self):
+        """Host copies of the search's tree arrays (for tests): dict of numpy arrays + nodes used."""
+        v = TreeView()
+        used = C.c_int32(0)
+        check(lib().ob200_search_debug_tree(self.h, C.byref(v), C.byref(used)))
+        n, pitch, mw = used.value, v.pitch, v.mask_words
+
+        def pull(ptr, count, dtype):
+            a = np.empty(count, dtype)
+            check(lib().ob200_copy_to_host(a.ctypes.data_as(C.c_void_p), C.c_void_p(ptr), a.nbytes))
+            return a
+        return {"N": pull(v.N, n * pitch, np.int32).reshape(n, pitch), "W": pull(v.W, n * pitch, np.float32).reshape(n, pitch),
+                "P": pull(v.P, n * pitch, np.float32).reshape(n, pitch), "VL": pull(v.VL, n * pitch, np.int32).reshape(n, pitch),
+                "child_node": pull(v.child_node, n * pitch, np.int32).reshape(n, pitch),
+                "legal_bits": pull(v.legal_bits, n * mw, np.uint32).reshape(n, mw),
+                "node_visits": pull(v.node_visits, n, np.int32), "n_children": v.n_children, "nodes": n}
+
+    def close(self):
+        if self.h:
+            lib().ob200_search_destroy(self.h)
             self.h = C.c_void_p()
 
     def __del__(self):

@@ -308,6 +308,20 @@ int finish_host_call(ob200_net* n, int B, float* policy_out, float* value_out) {
 }  // namespace
 }  // namespace ob200
 
+namespace ob200 {
+// For the search loop: forward on a device input tensor, probabilities out, no locking
+// beyond the handle's (the search is the handle's only user while it runs).
+int net_forward_for_search(ob200_net* n, const void* input_bt, int B, float* policy, float* value, cudaStream_t st) {
+    if (!n || !n->finalized) return set_error(OB200_ERR_STATE, "search: the network is not finalised");
+    std::lock_guard<std::mutex> lk(n->mu);
+    BoardTensorMap in_map;
+    if (int rc = make_board_tensor_map(input_bt, board_geom(n->cfg.board_size, B).PT,
+                                       128 + 2 * conv_halo_rows(n->cfg.board_size), &in_map)) return rc;
+    return forward_device(n, in_map, B, policy, value, OB200_OUT_PROBS, st);
+}
+const ob200_net_config* net_config(ob200_net* n) { return (n && n->finalized) ? &n->cfg : nullptr; }
+}  // namespace ob200
+
 extern "C" {
 
 int ob200_net_infer_planes(ob200_net* n, const float* planes, int32_t B, int32_t C, float* policy_out,

@@ -1,0 +1,405 @@
+// Leaf-parallel MCTS for Gomoku with device-resident trees: the search loop
+// around the selection, encoder and network kernels.  Host code only enqueues;
+// nothing inside a move waits for the GPU.
+//
+// Takes the place of MCTSEngine::executeBatchedTreeSearch (reference
+// src/mcts/mcts_engine_batch_tree_simple.cpp:14-301) for a group of independent
+// games, of MCTSNode::expand (src/mcts/mcts_node.cpp:238-436: one child per
+// legal move), addDirichletNoise (src/mcts/mcts_engine_eval.cpp:83-110) and
+// getActionProbabilities (src/mcts/mcts_engine_tree.cpp:389-465).
+//
+// Tree layout: one ob200_tree_view over a pool of nodes shared by all trees;
+// node t (< n_trees) is the root of tree t; a node's child slot is the board
+// cell of the move (slot == action), its existence bit says the cell is empty.
+#include "internal.h"
+#include <cmath>
+#include <cstring>
+#include <random>
+#include <vector>
+
+struct ob200_search {
+    ob200_search_config cfg{};
+    ob200_net* net = nullptr;
+    int S = 15, A = 225, pitch = 228, mask_words = 8;
+    int max_nodes = 0, sims_per_round = 0;     // per tree
+    ob200_tree_view tv{};                      // device arrays
+    int32_t* n_used = nullptr;                 // device node counter
+    int32_t* term_count = nullptr;             // device counter of terminal leaves
+    uint32_t* root_stones = nullptr;           // [n_trees][2][8]: BLACK, WHITE bitmaps
+    int16_t* root_hist = nullptr;              // [n_trees][16] k-th most recent move
+    uint8_t *root_nh = nullptr, *root_tm = nullptr;
+    int32_t* root_count = nullptr;             // stones on the board at the root
+    int32_t *roots = nullptr, *paths = nullptr, *path_len = nullptr;
+    int16_t* leaf_hist = nullptr; uint8_t *leaf_nh = nullptr, *leaf_tm = nullptr;
+    float *leaf_value = nullptr, *term_value = nullptr;   // term_value: NaN = not terminal
+    float *policy = nullptr, *value = nullptr, *noise = nullptr;
+    void* input_bt = nullptr;                  // encoder output for leaf_batch boards
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    uint64_t moves_done = 0;
+    std::vector<void*> owned;
+};
+
+namespace ob200 {
+namespace {
+
+constexpr int kMaxDepth = 64;
+
+__device__ __forceinline__ bool bit(const uint32_t* m, int i) { return (m[i >> 5] >> (i & 31)) & 1u; }
+
+// Roots: existence mask = empty cells, statistics zero, no children yet.
+__global__ void init_roots_kernel(ob200_tree_view t, const uint32_t* __restrict__ stones, int n_trees,
+                                  int32_t* n_used, int32_t* term_count) {
+    const int tree = blockIdx.x;
+    const uint32_t* st = stones + (size_t)tree * 16;
+    const size_t row = (size_t)tree * t.pitch;
+    for (int s = threadIdx.x; s < t.pitch; s += blockDim.x) {
+        t.N[row + s] = 0; t.W[row + s] = 0.0f; t.VL[row + s] = 0; t.P[row + s] = 0.0f;
+        t.child_node[row + s] = -1;
+    }
+    for (int w = threadIdx.x; w < t.mask_words; w += blockDim.x) {
+        uint32_t occupied = st[w] | st[8 + w];
+        uint32_t valid = 0xFFFFFFFFu;
+        if ((w + 1) * 32 > t.n_children) valid = (w * 32 >= t.n_children) ? 0u : ((1u << (t.n_children - w * 32)) - 1u);
+        t.legal_bits[(size_t)tree * t.mask_words + w] = ~occupied & valid;
+    }
+    if (threadIdx.x == 0) {
+        t.node_visits[tree] = 0;
+        if (tree == 0) { *n_used = n_trees; *term_count = 0; }
+    }
+}
+
+// P = (1 - eps) * P + eps * noise on the existing root children
+// (MCTSEngine::addDirichletNoise, src/mcts/mcts_engine_eval.cpp:83-110).
+__global__ void mix_noise_kernel(ob200_tree_view t, const float* __restrict__ noise, float eps) {
+    const int tree = blockIdx.x;
+    const size_t row = (size_t)tree * t.pitch;
+    const uint32_t* m = t.legal_bits + (size_t)tree * t.mask_words;
+    for (int s = threadIdx.x; s < t.n_children; s += blockDim.x)
+        if (bit(m, s)) t.P[row + s] = (1.0f - eps) * t.P[row + s] + eps * noise[(size_t)tree * t.pitch + s];
+}
+
+// One thread per simulation: the leaf position from root + path.
+//   history (k-th most recent move), side to move, and whether the game is over:
+//   five or more in a row through the last move for the player who made it
+//   (freestyle rules), or a full board.
+__global__ void leaf_prepare_kernel(const int32_t* __restrict__ paths, const int32_t* __restrict__ path_len,
+                                    int n_sims, int sims_per_tree, int max_depth, int S,
+                                    const uint32_t* __restrict__ root_stones, const int16_t* __restrict__ root_hist,
+                                    const uint8_t* __restrict__ root_nh, const uint8_t* __restrict__ root_tm,
+                                    const int32_t* __restrict__ root_count, int16_t* __restrict__ leaf_hist,
+                                    uint8_t* __restrict__ leaf_nh, uint8_t* __restrict__ leaf_tm,
+                                    float* __restrict__ term_value, int32_t* term_count) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_sims) return;
+    const int tree = i / sims_per_tree;
+    int len = path_len[i];
+    if (len > max_depth) len = max_depth;
+    const int32_t* p = paths + (size_t)i * max_depth * 2;
+    const int rtm = root_tm[tree], rnh = root_nh[tree];
+    const int tm = (len & 1) ? 3 - rtm : rtm;
+    int nh = 0;
+    for (int k = 0; k < 16; ++k) {
+        int mv = -1;
+        if (k < len) mv = p[2 * (len - 1 - k) + 1];
+        else if (k - len < rnh) mv = root_hist[(size_t)tree * 16 + (k - len)];
+        leaf_hist[(size_t)i * 16 + k] = (int16_t)mv;
+        if (mv >= 0) nh = k + 1;
+    }
+    leaf_nh[i] = (uint8_t)nh;
+    leaf_tm[i] = (uint8_t)tm;
+    float tv = nanf("");
+    if (len > 0) {
+        const int mover = 3 - tm;                              // who made the last move
+        const uint32_t* st = root_stones + (size_t)tree * 16 + (mover - 1) * 8;
+        const int last = p[2 * (len - 1) + 1];
+        const int r0 = last / S, c0 = last % S;
+        auto has = [&](int r, int c) {
+            if (r < 0 || r >= S || c < 0 || c >= S) return false;
+            const int cell = r * S + c;
+            if (bit(st, cell)) return true;
+            for (int d = len - 1; d >= 0; d -= 2)              // the mover's moves on the path
+                if (p[2 * d + 1] == cell) return true;
+            return false;
+        };
+        const int dr[4] = {0, 1, 1, 1}, dc[4] = {1, 0, 1, -1};
+        bool win = false;
+        for (int dir = 0; dir < 4 && !win; ++dir) {
+            int run = 1;
+            for (int k = 1; k < 5 && has(r0 + k * dr[dir], c0 + k * dc[dir]); ++k) ++run;
+            for (int k = 1; k < 5 && has(r0 - k * dr[dir], c0 - k * dc[dir]); ++k) ++run;
+            win = run >= 5;
+        }
+        if (win) tv = -1.0f;                                    // the side to move has lost
+        else if (root_count[tree] + len >= S * S) tv = 0.0f;    // full board
+    }
+    term_value[i] = tv;
+    if (tv == tv) atomicAdd(term_count, 1);
+}
+
+// One warp per simulation: create the node behind the leaf edge (once per edge)
+// with priors from the network policy, and choose the value to back up.
+__global__ void __launch_bounds__(256)
+expand_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const int32_t* __restrict__ path_len,
+              int n_sims, int max_depth, const float* __restrict__ policy, int policy_size,
+              const float* __restrict__ value, const float* __restrict__ term_value, float value_sign,
+              int max_nodes, int32_t* n_used, float* __restrict__ leaf_value) {
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (i >= n_sims) return;
+    int len = path_len[i];
+    if (len > max_depth) len = max_depth;
+    const float tv = term_value[i];
+    const bool terminal = tv == tv;
+    if (lane == 0) leaf_value[i] = value_sign * (terminal ? tv : value[i]);
+    if (len == 0 || terminal) return;
+    const int32_t* p = paths + (size_t)i * max_depth * 2;
+    const int parent = p[2 * (len - 1)], slot = p[2 * (len - 1) + 1];
+    const size_t e = (size_t)parent * t.pitch + slot;
+    int id = -1;
+    if (lane == 0 && atomicCAS(t.child_node + e, -1, -2) == -1) {     // first simulation on this edge claims it
+        id = atomicAdd(n_used, 1);
+        if (id >= max_nodes) {                                        // pool exhausted: the edge stays a leaf
+            atomicSub(n_used, 1);
+            atomicExch(t.child_node + e, -1);
+            id = -1;
+        }
+    }
+    id = __shfl_sync(0xffffffffu, id, 0);
+    if (id < 0) return;     // another simulation of this round creates the node (or nobody can)
+    const size_t row = (size_t)id * t.pitch;
+    const uint32_t* pm = t.legal_bits + (size_t)parent * t.mask_words;
+    uint32_t* cm = t.legal_bits + (size_t)id * t.mask_words;
+    for (int w = lane; w < t.mask_words; w += 32) cm[w] = pm[w] & ~((w == (slot >> 5)) ? (1u << (slot & 31)) : 0u);
+    __syncwarp();
+    const float* pol = policy + (size_t)i * policy_size;
+    for (int s = lane; s < t.pitch; s += 32) {
+        float pr = 0.0f;
+        if (s < t.n_children && bit(pm, s) && s != slot) pr = fminf(1.0f, fmaxf(0.0f, pol[s]));
+        t.N[row + s] = 0; t.W[row + s] = 0.0f; t.VL[row + s] = 0; t.P[row + s] = pr;
+        t.child_node[row + s] = -1;
+    }
+    if (lane == 0) {
+        t.node_visits[id] = 0;
+        __threadfence();
+        atomicExch(t.child_node + e, id);
+    }
+}
+
+}  // namespace
+}  // namespace ob200
+
+// Accessors of the network handle that the search needs (defined in net.cu).
+namespace ob200 {
+int net_forward_for_search(ob200_net* n, const void* input_bt, int B, float* policy, float* value, cudaStream_t st);
+const ob200_net_config* net_config(ob200_net* n);
+}
+
+using namespace ob200;
+
+namespace {
+
+template <typename T>
+int salloc(ob200_search* s, T** out, size_t count) {
+    void* p = nullptr;
+    OB200_CUDA_OK(cudaMalloc(&p, count * sizeof(T)));
+    s->owned.push_back(p);
+    *out = static_cast<T*>(p);
+    return OB200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ob200_search_create(ob200_net* net, const ob200_search_config* cfg, ob200_search** out) {
+    if (!net || !cfg || !out) return set_error(OB200_ERR_INVALID, "ob200_search_create: null argument");
+    *out = nullptr;
+    const ob200_net_config* nc = net_config(net);
+    if (!nc) return set_error(OB200_ERR_STATE, "ob200_search_create: the network is not finalised");
+    if (nc->board_size != 15 || nc->policy_size != 225 || (nc->input_channels != 17 && nc->input_channels != 19))
+        return set_error(OB200_ERR_UNSUPPORTED, "ob200_search_create: the search is built for 15x15 Gomoku networks (17 or 19 planes, 225 moves)");
+    if (cfg->n_trees < 1 || cfg->sims_per_move < 1 || cfg->leaf_batch < cfg->n_trees || cfg->leaf_batch % cfg->n_trees ||
+        cfg->leaf_batch > nc->max_batch || cfg->max_depth < 1 || cfg->max_depth > kMaxDepth || cfg->virtual_loss < 0 ||
+        (cfg->value_sign != 1 && cfg->value_sign != -1) || cfg->dirichlet_epsilon < 0 || cfg->dirichlet_epsilon > 1)
+        return set_error(OB200_ERR_INVALID,
+                         "ob200_search_create: need leaf_batch a multiple of n_trees and <= the network's max_batch (%d), max_depth in [1,%d], value_sign +-1",
+                         nc->max_batch, kMaxDepth);
+    OB200_CUDA_OK(cudaSetDevice(nc->device));
+    if (int rc = require_device()) return rc;
+    ob200_search* s = new ob200_search;
+    s->cfg = *cfg; s->net = net;
+    s->sims_per_round = cfg->leaf_batch / cfg->n_trees;
+    const int rounds = (cfg->sims_per_move + s->sims_per_round - 1) / s->sims_per_round;
+    s->max_nodes = cfg->n_trees * (1 + rounds * s->sims_per_round);     // every simulation adds at most one node
+    const size_t edges = (size_t)s->max_nodes * s->pitch;
+    const int T = cfg->n_trees, L = cfg->leaf_batch;
+    int rc = OB200_OK;
+    auto A_ = [&](int r) { if (!rc) rc = r; };
+    A_(salloc(s, &s->tv.N, edges)); A_(salloc(s, &s->tv.W, edges)); A_(salloc(s, &s->tv.P, edges));
+    A_(salloc(s, &s->tv.VL, edges)); A_(salloc(s, &s->tv.child_node, edges));
+    A_(salloc(s, &s->tv.legal_bits, (size_t)s->max_nodes * s->mask_words));
+    A_(salloc(s, &s->tv.node_visits, (size_t)s->max_nodes));
+    A_(salloc(s, &s->n_used, 1)); A_(salloc(s, &s->term_count, 1));
+    A_(salloc(s, &s->root_stones, (size_t)T * 16)); A_(salloc(s, &s->root_hist, (size_t)T * 16));
+    A_(salloc(s, &s->root_nh, (size_t)T)); A_(salloc(s, &s->root_tm, (size_t)T)); A_(salloc(s, &s->root_count, (size_t)T));
+    A_(salloc(s, &s->roots, (size_t)T));
+    A_(salloc(s, &s->paths, (size_t)L * cfg->max_depth * 2)); A_(salloc(s, &s->path_len, (size_t)L));
+    A_(salloc(s, &s->leaf_hist, (size_t)L * 16)); A_(salloc(s, &s->leaf_nh, (size_t)L)); A_(salloc(s, &s->leaf_tm, (size_t)L));
+    A_(salloc(s, &s->leaf_value, (size_t)L)); A_(salloc(s, &s->term_value, (size_t)L));
+    A_(salloc(s, &s->policy, (size_t)L * s->A)); A_(salloc(s, &s->value, (size_t)L));
+    A_(salloc(s, &s->noise, (size_t)T * s->pitch));
+    uint8_t* bt = nullptr;
+    A_(salloc(s, &bt, (size_t)ob200_board_tensor_bytes(15, L, 64)));
+    s->input_bt = bt;
+    if (rc) { ob200_search_destroy(s); return rc; }
+    s->tv.n_nodes = s->max_nodes; s->tv.n_children = s->A; s->tv.pitch = s->pitch; s->tv.mask_words = s->mask_words;
+    std::vector<int32_t> roots(T);
+    for (int t = 0; t < T; ++t) roots[t] = t;
+    OB200_CUDA_OK(cudaMemcpy(s->roots, roots.data(), T * sizeof(int32_t), cudaMemcpyHostToDevice));
+    OB200_CUDA_OK(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+    OB200_CUDA_OK(cudaEventCreate(&s->ev0)); OB200_CUDA_OK(cudaEventCreate(&s->ev1));
+    *out = s;
+    return OB200_OK;
+}
+
+void ob200_search_destroy(ob200_search* s) {
+    if (!s) return;
+    if (s->stream) { cudaStreamSynchronize(s->stream); cudaStreamDestroy(s->stream); }
+    if (s->ev0) cudaEventDestroy(s->ev0);
+    if (s->ev1) cudaEventDestroy(s->ev1);
+    for (void* p : s->owned) cudaFree(p);
+    delete s;
+}
+
+int ob200_search_debug_tree(ob200_search* s, ob200_tree_view* view_out, int32_t* nodes_used_out) {
+    if (!s || !view_out) return set_error(OB200_ERR_INVALID, "ob200_search_debug_tree: null argument");
+    *view_out = s->tv;
+    if (nodes_used_out) OB200_CUDA_OK(cudaMemcpy(nodes_used_out, s->n_used, sizeof(int32_t), cudaMemcpyDeviceToHost));
+    return OB200_OK;
+}
+
+int ob200_copy_to_host(void* dst_host, const void* src_device, int64_t bytes) {
+    if (!dst_host || !src_device || bytes < 0) return set_error(OB200_ERR_INVALID, "ob200_copy_to_host: bad argument");
+    OB200_CUDA_OK(cudaMemcpy(dst_host, src_device, (size_t)bytes, cudaMemcpyDeviceToHost));
+    return OB200_OK;
+}
+
+int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_moves, int32_t moves_stride,
+                     float temperature, float* pi_out, int32_t* visits_out, ob200_search_stats* stats) {
+    if (!s || !moves || !n_moves || !pi_out || moves_stride < 0)
+        return set_error(OB200_ERR_INVALID, "ob200_search_run: null argument");
+    const ob200_search_config& c = s->cfg;
+    const int T = c.n_trees, L = c.leaf_batch, S = s->S, A = s->A;
+    const ob200_net_config* nc = net_config(s->net);
+    OB200_CUDA_OK(cudaSetDevice(nc->device));
+    // ---- roots from the move lists (host) ----
+    std::vector<uint32_t> stones((size_t)T * 16, 0u);
+    std::vector<int16_t> hist((size_t)T * 16, (int16_t)-1);
+    std::vector<uint8_t> nh(T), tm(T);
+    std::vector<int32_t> count(T);
+    for (int t = 0; t < T; ++t) {
+        const int n = n_moves[t];
+        if (n < 0 || n > moves_stride || n >= A)
+            return set_error(OB200_ERR_INVALID, "ob200_search_run: tree %d has %d moves (stride %d, board %d cells)", t, n, moves_stride, A);
+        for (int i = 0; i < n; ++i) {
+            const int mv = moves[(size_t)t * moves_stride + i];
+            if (mv < 0 || mv >= A) return set_error(OB200_ERR_INVALID, "ob200_search_run: tree %d move %d out of range", t, mv);
+            uint32_t& w = stones[(size_t)t * 16 + (i & 1) * 8 + (mv >> 5)];
+            if (((stones[(size_t)t * 16 + (mv >> 5)] | stones[(size_t)t * 16 + 8 + (mv >> 5)]) >> (mv & 31)) & 1u)
+                return set_error(OB200_ERR_INVALID, "ob200_search_run: tree %d plays cell %d twice", t, mv);
+            w |= 1u << (mv & 31);
+        }
+        const int k = n < 16 ? n : 16;
+        for (int i = 0; i < k; ++i) hist[(size_t)t * 16 + i] = moves[(size_t)t * moves_stride + n - 1 - i];
+        nh[t] = (uint8_t)k; tm[t] = (uint8_t)((n & 1) ? 2 : 1); count[t] = n;
+    }
+    cudaStream_t st = s->stream;
+    OB200_CUDA_OK(cudaMemcpyAsync(s->root_stones, stones.data(), stones.size() * 4, cudaMemcpyHostToDevice, st));
+    OB200_CUDA_OK(cudaMemcpyAsync(s->root_hist, hist.data(), hist.size() * 2, cudaMemcpyHostToDevice, st));
+    OB200_CUDA_OK(cudaMemcpyAsync(s->root_nh, nh.data(), T, cudaMemcpyHostToDevice, st));
+    OB200_CUDA_OK(cudaMemcpyAsync(s->root_tm, tm.data(), T, cudaMemcpyHostToDevice, st));
+    OB200_CUDA_OK(cudaMemcpyAsync(s->root_count, count.data(), T * 4, cudaMemcpyHostToDevice, st));
+    // root noise: Gamma(alpha, 1) per existing child, normalised (addDirichletNoise, :83-110)
+    std::vector<float> noise;
+    if (c.dirichlet_epsilon > 0.0f) {
+        noise.assign((size_t)T * s->pitch, 0.0f);
+        std::mt19937_64 rng(c.seed + 0x9E3779B97F4A7C15ull * (s->moves_done + 1));
+        std::gamma_distribution<float> gamma(c.dirichlet_alpha, 1.0f);
+        for (int t = 0; t < T; ++t) {
+            double sum = 0.0;
+            for (int a = 0; a < A; ++a) {
+                const bool occ = ((stones[(size_t)t * 16 + (a >> 5)] | stones[(size_t)t * 16 + 8 + (a >> 5)]) >> (a & 31)) & 1u;
+                if (!occ) { const float g = gamma(rng); noise[(size_t)t * s->pitch + a] = g; sum += g; }
+            }
+            if (sum > 0) for (int a = 0; a < A; ++a) noise[(size_t)t * s->pitch + a] = (float)(noise[(size_t)t * s->pitch + a] / sum);
+        }
+        OB200_CUDA_OK(cudaMemcpyAsync(s->noise, noise.data(), noise.size() * 4, cudaMemcpyHostToDevice, st));
+    }
+    OB200_CUDA_OK(cudaEventRecord(s->ev0, st));
+    // ---- roots: create, evaluate, priors (+ noise) ----
+    init_roots_kernel<<<T, 128, 0, st>>>(s->tv, s->root_stones, T, s->n_used, s->term_count);
+    OB200_LAUNCHED("init_roots_kernel");
+    if (int rc = launch_encode_gomoku(s->root_hist, s->root_nh, s->root_tm, T, S, nc->input_channels, 64, s->input_bt, st)) return rc;
+    if (int rc = net_forward_for_search(s->net, s->input_bt, T, s->policy, s->value, st)) return rc;
+    if (int rc = ob200_launch_set_priors(&s->tv, s->roots, T, s->policy, A, nullptr, st)) return rc;
+    if (c.dirichlet_epsilon > 0.0f) {
+        mix_noise_kernel<<<T, 128, 0, st>>>(s->tv, s->noise, c.dirichlet_epsilon);
+        OB200_LAUNCHED("mix_noise_kernel");
+    }
+    // ---- rounds ----
+    const int rounds = (c.sims_per_move + s->sims_per_round - 1) / s->sims_per_round;
+    for (int r = 0; r < rounds; ++r) {
+        if (int rc = ob200_launch_traverse(&s->tv, s->roots, T, s->sims_per_round, c.c_puct, c.virtual_loss, c.max_depth,
+                                           s->paths, s->path_len, st)) return rc;
+        leaf_prepare_kernel<<<(L + 127) / 128, 128, 0, st>>>(s->paths, s->path_len, L, s->sims_per_round, c.max_depth, S,
+                                                            s->root_stones, s->root_hist, s->root_nh, s->root_tm,
+                                                            s->root_count, s->leaf_hist, s->leaf_nh, s->leaf_tm,
+                                                            s->term_value, s->term_count);
+        OB200_LAUNCHED("leaf_prepare_kernel");
+        if (int rc = launch_encode_gomoku(s->leaf_hist, s->leaf_nh, s->leaf_tm, L, S, nc->input_channels, 64, s->input_bt, st)) return rc;
+        if (int rc = net_forward_for_search(s->net, s->input_bt, L, s->policy, s->value, st)) return rc;
+        expand_kernel<<<(L * 32 + 255) / 256, 256, 0, st>>>(s->tv, s->paths, s->path_len, L, c.max_depth, s->policy, A,
+                                                           s->value, s->term_value, (float)c.value_sign, s->max_nodes,
+                                                           s->n_used, s->leaf_value);
+        OB200_LAUNCHED("expand_kernel");
+        if (int rc = ob200_launch_backup(&s->tv, s->paths, s->path_len, s->leaf_value, L, c.max_depth, c.virtual_loss, st)) return rc;
+    }
+    OB200_CUDA_OK(cudaEventRecord(s->ev1, st));
+    // ---- results: root visit counts -> pi (getActionProbabilities, src/mcts/mcts_engine_tree.cpp:389-465) ----
+    std::vector<int32_t> rootN((size_t)T * s->pitch);
+    int32_t used = 0, terms = 0;
+    OB200_CUDA_OK(cudaMemcpyAsync(rootN.data(), s->tv.N, rootN.size() * 4, cudaMemcpyDeviceToHost, st));
+    OB200_CUDA_OK(cudaMemcpyAsync(&used, s->n_used, 4, cudaMemcpyDeviceToHost, st));
+    OB200_CUDA_OK(cudaMemcpyAsync(&terms, s->term_count, 4, cudaMemcpyDeviceToHost, st));
+    int err = 0;
+    int* errw = device_error_word();
+    if (errw) OB200_CUDA_OK(cudaMemcpyAsync(&err, errw, 4, cudaMemcpyDeviceToHost, st));
+    OB200_CUDA_OK(cudaStreamSynchronize(st));
+    if (err) {
+        cudaMemsetAsync(errw, 0, 4, st); cudaStreamSynchronize(st);
+        return set_error(OB200_ERR_TIMEOUT, "a kernel gave up on a bounded wait (code %d) during the search", err);
+    }
+    for (int t = 0; t < T; ++t) {
+        const int32_t* n = rootN.data() + (size_t)t * s->pitch;
+        float* pi = pi_out + (size_t)t * A;
+        int nmax = 0, amax = -1;
+        for (int a = 0; a < A; ++a) { if (visits_out) visits_out[(size_t)t * A + a] = n[a]; if (n[a] > nmax) { nmax = n[a]; amax = a; } }
+        std::memset(pi, 0, sizeof(float) * A);
+        if (nmax <= 0) continue;
+        if (temperature < 0.01f) { pi[amax] = 1.0f; continue; }
+        double sum = 0.0;
+        for (int a = 0; a < A; ++a) if (n[a] > 0) { pi[a] = std::pow((float)n[a] / (float)nmax, 1.0f / temperature); sum += pi[a]; }
+        for (int a = 0; a < A; ++a) pi[a] = (float)(pi[a] / sum);
+    }
+    s->moves_done++;
+    if (stats) {
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, s->ev0, s->ev1);
+        stats->simulations = (int64_t)rounds * L;
+        stats->evaluations = (int64_t)rounds * L + T;
+        stats->nodes = used; stats->terminal_leaves = terms; stats->device_ms = ms;
+    }
+    return OB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,102 @@
+"""The leaf-parallel search loop on the device.  Whole-search results cannot be compared
+with the reference bit for bit (the reference shuffles children and races on virtual loss),
+so — like the reference's own engine tests (tests/mcts/mcts_engine_test.cpp:143-157) — the
+checks are invariants: visit conservation, legality, virtual loss back to zero, consistent
+expansion, probabilities that sum to one, and game-result handling on a forced win."""
+import numpy as np
+import pytest
+
+from omoknuni_small_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def net(lib):
+    from omoknuni_small_b200 import capi
+    shapes = synth.net_tensor_shapes(15, 17, 64, 2, 225, 2, 1)
+    w = synth.make_weights(shapes, seed=9, init="torch_default", bn="random")
+    return capi.Net(17, 15, 2, 64, 225, 2, 1, 256, 256).load(w)
+
+
+def legal_of(mask_row, n=225):
+    return np.unpackbits(mask_row.view(np.uint8), bitorder="little")[:n].astype(bool)
+
+
+def test_search_invariants(net):
+    from omoknuni_small_b200 import capi
+    T, sims = 16, 96
+    games, _, _, _ = synth.make_gomoku_games(T, 15, seed=5, max_moves=20)
+    s = capi.Search(net, n_trees=T, sims_per_move=sims, leaf_batch=128, max_depth=32, c_puct=1.5, virtual_loss=3,
+                    dirichlet_epsilon=0.25, seed=1)
+    pi, visits, st = s.run(games, temperature=1.0)
+    assert st["simulations"] == T * sims and st["evaluations"] == T * sims + T
+    assert capi.device_error_code() == 0
+    tr = s.tree()
+    n = tr["nodes"]
+    assert T < n <= T * (sims + 1) and st["nodes"] == n
+    assert not tr["VL"].any(), "virtual loss must be back to zero after the backups"
+    for t in range(T):
+        occupied = np.zeros(225, bool)
+        occupied[games[t]] = True
+        assert np.array_equal(legal_of(tr["legal_bits"][t]), ~occupied)          # root children = empty cells
+        assert visits[t].sum() == sims and tr["node_visits"][t] == sims          # every simulation passes the root once
+        assert not visits[t][occupied].any()
+        assert abs(pi[t].sum() - 1) < 1e-5 and not pi[t][occupied].any()
+        assert np.array_equal(visits[t], tr["N"][t, :225])
+    # structure: a child's existence mask is its parent's minus the move, its visits are its edge's
+    child = tr["child_node"][:, :225]
+    assert child.max() < n and (child >= -1).all()
+    parents, slots = np.nonzero(child >= 0)
+    for p, a in zip(parents[:400], slots[:400]):
+        c = child[p, a]
+        lp, lc = legal_of(tr["legal_bits"][p]), legal_of(tr["legal_bits"][c])
+        assert lp[a] and not lc[a] and np.array_equal(np.delete(lp, a), np.delete(lc, a))
+        assert tr["node_visits"][c] == tr["N"][p, a]
+        assert tr["N"][c, :225].sum() <= tr["N"][p, a] - 1                       # the visit(s) that created it stop at the edge
+        assert not tr["P"][c, :225][~lc].any() and (tr["P"][c, :225] >= 0).all() and (tr["P"][c, :225] <= 1).all()
+    assert len(np.unique(child[child >= 0])) == (child >= 0).sum() == n - T       # one edge per non-root node
+    # a second move on the same handle starts from fresh trees
+    pi2, visits2, st2 = s.run(games, temperature=0.0)
+    assert (visits2.sum(1) == sims).all() and ((pi2 == 1).sum(1) == 1).all() and (pi2.sum(1) == 1).all()
+    assert np.array_equal(pi2.argmax(1), visits2.argmax(1))
+
+
+def test_search_takes_the_win_and_counts_terminals(net):
+    """BLACK to move with an open four: the completing move ends the game.  With negamax signs the
+    result (+1 for the mover) must pull the visits onto the winning cells.  (Priors are flat, so
+    every child is tried once before the win is found; a winning edge carries virtual loss while a
+    round is in flight, so it takes about one visit per round after that.)"""
+    from omoknuni_small_b200 import capi
+    # black: (7,3) (7,4) (7,5) (7,6); white scattered; black to move -> (7,2) or (7,7) wins
+    black = [7 * 15 + c for c in (3, 4, 5, 6)]
+    white = [0, 14, 210, 224]
+    moves = [m for pair in zip(black, white) for m in pair]
+    T = 4
+    s = capi.Search(net, n_trees=T, sims_per_move=768, leaf_batch=64, max_depth=16, c_puct=1.5, virtual_loss=3,
+                    dirichlet_epsilon=0.0, value_sign=-1, seed=3)
+    pi, visits, st = s.run([moves] * T, temperature=0.0)
+    wins = {7 * 15 + 2, 7 * 15 + 7}
+    assert st["terminal_leaves"] > 0
+    for t in range(T):
+        assert int(visits[t].argmax()) in wins, visits[t].argmax()
+        assert min(visits[t][w] for w in wins) >= 20
+        others = np.delete(visits[t], list(wins))
+        assert others.max() < min(visits[t][w] for w in wins)
+    tr = s.tree()
+    for t in range(T):                                   # a finished game is never expanded
+        for w in wins:
+            assert tr["child_node"][t, w] == -1
+            if tr["N"][t, w]:
+                assert tr["W"][t, w] == tr["N"][t, w]    # every visit backed up the game result +1
+
+
+def test_search_argument_errors(net):
+    from omoknuni_small_b200 import capi
+    with pytest.raises(capi.Error):
+        capi.Search(net, n_trees=3, leaf_batch=64)                   # leaf_batch not a multiple of n_trees
+    with pytest.raises(capi.Error):
+        capi.Search(net, n_trees=64, leaf_batch=1024)                # beyond the network's max_batch (256)
+    s = capi.Search(net, n_trees=2, sims_per_move=8, leaf_batch=8)
+    with pytest.raises(capi.Error):
+        s.run([[5, 5], [1]])                                         # a cell played twice
