@@ -52,6 +52,7 @@ def lib():
         L.oracle_traverse.argtypes = [_i32, _f32, _f32, _i32, _u32, _i32, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                       C.c_int, _i32, C.c_int, C.c_int, C.c_float, C.c_int, C.c_int, _i32, _i32]
         L.oracle_gomoku_encode_batch.argtypes = [_i16, _u8, _u8, C.c_int, C.c_int, C.c_int, _f32, C.c_int]
+        L.oracle_gomoku_result.argtypes = [_i16, C.c_int, C.c_int]
         _lib = L
     return _lib
 
@@ -132,6 +133,12 @@ def gomoku_encode(history, n_hist, to_move, board_size=15, planes=19, threads=0)
     return out
 
 
+def gomoku_result(moves, board_size=15):
+    """0 ongoing, 1 BLACK won, 2 WHITE won, 3 draw, judged on the last move (freestyle rules)."""
+    mv = np.ascontiguousarray(moves, np.int16)
+    return int(lib().oracle_gomoku_result(mv, len(mv), board_size))
+
+
 # ---- the reference's own classes (oracle/_ref) --------------------------------
 _ref_tree = None
 _ref_net = None
@@ -164,6 +171,7 @@ def ref_tree():
         L.ref_vl_ops.argtypes = [C.c_int, _i32, C.c_int, _i32]
         L.ref_backup_path.argtypes = [C.c_int, _i32, _f32, _i32, C.c_float, C.c_int, _f32]
         L.ref_gomoku_encode.argtypes = [C.c_int, _i32, C.c_int, C.c_void_p, C.c_void_p]
+        L.ref_gomoku_result.argtypes = [C.c_int, _i32, C.c_int]
         L.ref_gomoku_encode_batch.restype = C.c_double
         L.ref_gomoku_encode_batch.argtypes = [C.c_int, C.c_int, _i64, _i32, _f32, C.c_int]
         _ref_tree = L
@@ -228,6 +236,11 @@ def ref_gomoku_planes(moves, board_size=15):
     if tm < 0:
         raise ValueError("illegal move in list")
     return p19, p3, tm
+
+
+def ref_gomoku_result(moves, board_size=15):
+    mv = np.ascontiguousarray(moves, np.int32)
+    return int(ref_tree().ref_gomoku_result(board_size, mv, len(mv)))
 
 
 def ref_gomoku_encode_batch(move_lists, board_size=15, threads=0):

@@ -7,7 +7,7 @@
  *
  * Pinned against the reference's own classes compiled from its sources
  * (oracle/_ref, see oracle/Makefile) by tests/golden/make_golden.py and
- * tests/test_oracle_vs_reference.py, and against the known-answer cases of
+ * tests/test_oracle.py, and against the known-answer cases of
  * the reference's unit tests (tests/mcts/mcts_node_test.cpp:237-298,
  * tests/mcts/virtual_loss_test.cpp:160-224,282-308).
  *
@@ -228,4 +228,36 @@ void oracle_gomoku_encode_batch(const int16_t* history, const uint8_t* n_hist,
     for (int b = 0; b < B; ++b)
         oracle_gomoku_encode(history + (size_t)b * 16, n_hist[b], to_move[b], S, planes,
                              out + (size_t)b * planes * S * S);
+}
+
+/* Game result after a move list on an S x S freestyle Gomoku board (BLACK first):
+ * 0 = ongoing, 1 = BLACK won, 2 = WHITE won, 3 = draw (full board).
+ * GomokuState::refresh_winner_cache (src/games/gomoku/gomoku_state.cpp:792-860) checks
+ * only the last move, for the player who made it, with
+ * GomokuRules::is_five_in_a_row(action, player, allow_overline = true) for freestyle
+ * (src/games/gomoku/gomoku_rules.cpp:71-100: a line of length >= 5 through the stone in
+ * any of 4 directions); isTerminal (:131-156) adds the stalemate of a full board. */
+int oracle_gomoku_result(const int16_t* moves, int n, int S) {
+    signed char board[32 * 32];
+    memset(board, 0, sizeof(board));
+    for (int i = 0; i < n; ++i) board[moves[i]] = (signed char)(1 + (i & 1));
+    if (n == 0) return 0;
+    const int last = moves[n - 1], who = board[last];
+    const int r0 = last / S, c0 = last % S;
+    static const int DR[4] = {1, 0, 1, 1}, DC[4] = {0, 1, 1, -1};
+    for (int d = 0; d < 4; ++d) {
+        int len = 1;
+        for (int k = 1;; ++k) {
+            const int r = r0 + k * DR[d], c = c0 + k * DC[d];
+            if (r < 0 || r >= S || c < 0 || c >= S || board[r * S + c] != who) break;
+            ++len;
+        }
+        for (int k = 1;; ++k) {
+            const int r = r0 - k * DR[d], c = c0 - k * DC[d];
+            if (r < 0 || r >= S || c < 0 || c >= S || board[r * S + c] != who) break;
+            ++len;
+        }
+        if (len >= 5) return who;
+    }
+    return n >= S * S ? 3 : 0;
 }

@@ -241,4 +241,21 @@ double ref_gomoku_encode_batch(int board_size, int n_states, const int64_t* row_
     return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
 }
 
+// Game result the reference reports after playing `moves` (all but the last must leave the
+// game unfinished): 0 ongoing, 1 BLACK won, 2 WHITE won, 3 draw, -1 illegal move list.
+int ref_gomoku_result(int board_size, const int32_t* moves, int n_moves) {
+    alphazero::games::gomoku::GomokuState st(board_size, false, false, 0, false);
+    for (int i = 0; i < n_moves; ++i) {
+        if (st.isTerminal() || !st.isLegalMove(moves[i])) return -1;
+        st.makeMove(moves[i]);
+    }
+    if (!st.isTerminal()) return 0;
+    switch (st.getGameResult()) {
+        case GameResult::WIN_PLAYER1: return 1;
+        case GameResult::WIN_PLAYER2: return 2;
+        case GameResult::DRAW: return 3;
+        default: return 0;
+    }
+}
+
 }  // extern "C"

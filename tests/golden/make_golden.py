@@ -8,6 +8,7 @@ Inputs come from omoknuni_small_b200.synth with fixed seeds; the fixtures store
 the inputs' checksums and the reference's outputs:
   select_golden.npz  MCTSNode::selectChild + applyVirtualLoss + revertVirtualLoss
   encode_golden.npz  GomokuState::getEnhancedTensorRepresentation (bit-packed)
+  result_golden.npz  GomokuState::isTerminal / getGameResult after one more move
   net_golden.npz     ResNetModel::forward (log-softmax policy, value): (a) a tiny
                      model with the reference's own libtorch default
                      initialisation, its weights stored here rounded to fp16
@@ -89,11 +90,30 @@ def make_net():
     np.savez_compressed(os.path.join(HERE, "net_golden.npz"), **out)
 
 
+def make_results():
+    """Game results of the reference's GomokuState for unfinished games extended by one move."""
+    rng = np.random.default_rng(5)
+    games, _, _, _ = synth.make_gomoku_games(120, 15, seed=606, max_moves=140)
+    flat, ptr, res = [], [0], []
+    for g in games:
+        occ = set(int(x) for x in g)
+        for a in rng.permutation(225)[:12]:
+            if int(a) in occ:
+                continue
+            mv = [int(x) for x in g] + [int(a)]
+            flat += mv
+            ptr.append(len(flat))
+            res.append(capi.ref_gomoku_result(mv))
+    np.savez_compressed(os.path.join(HERE, "result_golden.npz"), moves=np.asarray(flat, np.int16),
+                        row_ptr=np.asarray(ptr, np.int64), result=np.asarray(res, np.int8))
+
+
 if __name__ == "__main__":
     if not (capi.have_ref_tree() and capi.have_ref_net()):
         sys.exit("oracle/_ref is not built: run `make -C oracle ref` where the reference checkout exists")
     make_select()
     make_encode()
     make_net()
+    make_results()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))

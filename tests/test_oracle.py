@@ -105,6 +105,28 @@ def test_encoder_matches_reference_golden(oracle):
     assert np.array_equal(oracle.gomoku_encode(hist, nh, tm, 15, 17), planes[:, :17])
 
 
+def test_game_result_matches_reference_golden(oracle):
+    g = np.load(os.path.join(GOLD, "result_golden.npz"))
+    ptr, mv = g["row_ptr"], g["moves"]
+    got = [oracle.gomoku_result(mv[ptr[i]:ptr[i + 1]]) for i in range(len(ptr) - 1)]
+    assert np.array_equal(np.asarray(got, np.int8), g["result"])
+    assert (g["result"] != 0).sum() >= 10                        # the fixture does contain finished games
+
+
+def test_game_result_known_cases(oracle):
+    def interleave(black, white):
+        return [m for pair in zip(black, white) for m in pair]
+    far = [200, 202, 204, 206, 208, 210]
+    assert oracle.gomoku_result(interleave([0, 1, 2, 3, 4], far)[:-1]) == 1            # five in a row
+    assert oracle.gomoku_result(interleave([0, 1, 2, 4, 5, 3], far)[:-1]) == 1         # six: overline wins in freestyle
+    assert oracle.gomoku_result(interleave([0, 16, 32, 48, 64], far)[:-1]) == 1        # diagonal
+    assert oracle.gomoku_result(interleave([14, 28, 42, 56, 70], far)[:-1]) == 1       # anti-diagonal
+    assert oracle.gomoku_result(interleave([0, 1, 2, 3], far)) == 0                     # four is not enough
+    assert oracle.gomoku_result(interleave(far, [0, 15, 30, 45, 60])) == 2             # WHITE, vertical
+    assert oracle.gomoku_result([11, 12, 13, 14, 15][:0]) == 0                          # empty game
+    assert oracle.gomoku_result(interleave([10, 11, 12, 13, 14 + 15], far)[:-1]) == 0  # no wrap over the board edge
+
+
 def load_net_golden_a():
     g = np.load(os.path.join(GOLD, "net_golden.npz"))
     cin, S, blocks, F, A, pc, vc = [int(v) for v in g["a_cfg"]]
@@ -182,6 +204,25 @@ def test_encoder_live_against_gomokustate(oracle):
     games, hist, nh, tm = synth.make_gomoku_games(16, 9, seed=10, max_moves=30)
     ref, _ = oracle.ref_gomoku_encode_batch(games, 9)
     assert np.array_equal(oracle.gomoku_encode(hist, nh, tm, 9, 19), ref)
+
+
+def test_game_result_live_against_gomokustate(oracle):
+    _need_ref(oracle, "tree")
+    rng = np.random.default_rng(8)
+    games, _, _, _ = synth.make_gomoku_games(60, 15, seed=707, max_moves=150)
+    n_done = 0
+    for g in games:
+        occ = set(int(x) for x in g)
+        for a in rng.permutation(225)[:20]:
+            if int(a) in occ:
+                continue
+            mv = [int(x) for x in g] + [int(a)]
+            r = oracle.ref_gomoku_result(mv)
+            assert r == oracle.gomoku_result(mv)
+            n_done += r != 0
+    assert n_done > 0
+    six = [0, 200, 1, 202, 2, 204, 4, 206, 5, 208, 3]
+    assert oracle.ref_gomoku_result(six) == oracle.gomoku_result(six) == 1
 
 
 def test_network_live_against_resnetmodel(oracle):

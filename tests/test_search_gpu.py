@@ -91,6 +91,43 @@ def test_search_takes_the_win_and_counts_terminals(net):
                 assert tr["W"][t, w] == tr["N"][t, w]    # every visit backed up the game result +1
 
 
+def test_terminal_edges_match_the_oracle_rule(net, oracle):
+    """After every root child has been tried, the root edges the device treated as finished
+    games (never expanded) must be exactly the moves the oracle's rule — pinned to the
+    reference's GomokuState on the CPU — calls a win, for roots with threats in all four
+    directions, at the board edge, and an overline."""
+    from omoknuni_small_b200 import capi
+
+    def interleave(black, white):
+        return [m for pair in zip(black, white) for m in pair]
+    far = [200, 217, 204, 221, 208, 223]
+    roots = [
+        interleave([7 * 15 + c for c in (3, 4, 5, 6)], far[:4]),                 # horizontal open four (BLACK to move)
+        interleave([r * 15 + 2 for r in (1, 2, 3, 4)], far[:4]),                 # vertical
+        interleave([0, 16, 32, 48], [1, 2, 3, 4]),                               # diagonal from the corner
+        interleave([14, 28, 42, 56], [1, 2, 3, 5]),                              # anti-diagonal from the corner
+        interleave([0, 1, 2, 4, 5], far[:5]),                                    # gap: filling it makes six
+        interleave(far[:5], [7 * 15 + c for c in (8, 9, 10, 11)] + [100])[:-1],  # WHITE to move with four
+        interleave([10, 11, 12, 13], far[:4]),                                   # four ending at the right edge
+        [112],                                                                   # no threat at all
+    ]
+    T = len(roots)
+    # a huge exploration constant makes the search try every root child before it settles
+    s = capi.Search(net, n_trees=T, sims_per_move=640, leaf_batch=16 * T, max_depth=8, c_puct=200.0, virtual_loss=3,
+                    dirichlet_epsilon=0.0, value_sign=-1, seed=0)
+    _, visits, st = s.run(roots, temperature=1.0)
+    tr = s.tree()
+    for t, root in enumerate(roots):
+        occ = set(root)
+        want = {a for a in range(225) if a not in occ and oracle.gomoku_result(list(root) + [a]) != 0}
+        tried = {a for a in range(225) if tr["N"][t, a] > 0}
+        assert tried == set(range(225)) - occ, "every legal root move is tried with this exploration constant"
+        got = {a for a in tried if tr["child_node"][t, a] < 0}
+        assert got == want, (t, sorted(got), sorted(want))
+        for a in want:
+            assert tr["W"][t, a] == tr["N"][t, a]                # each visit backed up the result
+
+
 def test_search_argument_errors(net):
     from omoknuni_small_b200 import capi
     with pytest.raises(capi.Error):
