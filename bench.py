@@ -268,7 +268,8 @@ def gpu_arm(args):
         n_trees, sims = 64, 800
         openings, _, _, _ = synth.make_gomoku_games(n_trees, 15, seed=replicas.shard_seed(100, rank), max_moves=20)
         search = capi.Search(net, n_trees=n_trees, sims_per_move=sims, leaf_batch=B, max_depth=64, c_puct=1.5,
-                             virtual_loss=3, dirichlet_alpha=0.3, dirichlet_epsilon=0.25, value_sign=1, seed=rank)
+                             virtual_loss=3, dirichlet_alpha=0.3, dirichlet_epsilon=0.25, value_sign=1,
+                             transposition_table=True, seed=rank)
         search.run(openings)                                   # warm-up move
         mcts_ms, mcts_sims, mcts_evals, mcts_moves = 0.0, 0, 0, max(2, min(K, 5))
         for _ in range(mcts_moves):
@@ -276,6 +277,7 @@ def gpu_arm(args):
             torch.cuda.synchronize()
             _, _, st = search.run(openings)
             mcts_ms += st["device_ms"]; mcts_sims += st["simulations"]; mcts_evals += st["evaluations"]
+            mcts_nodes = st["nodes"]
         torch.cuda.synchronize()
     assert capi.device_error_code() == 0, "a kernel gave up on a bounded wait"
 
@@ -322,7 +324,7 @@ def gpu_arm(args):
                      "leaf_evals_per_sec": world * mcts_evals / (mcts_ms * 1e-3),
                      "config": {"games_per_gpu": 64, "sims_per_move": 800, "leaf_batch": B, "c_puct": 1.5, "virtual_loss": 3,
                                 "dirichlet": [0.3, 0.25], "openings": "seeded random, 0-20 stones", "moves_timed": mcts_moves,
-                                "transposition_table": "not built yet"},
+                                "transposition_table": "on (device table, Zobrist keys)", "nodes_per_move": mcts_nodes},
                      "ms_per_move": mcts_ms / mcts_moves, "timing": "CUDA events around each move, inside the library"},
             "clocks": clocks,
         }

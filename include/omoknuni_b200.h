@@ -346,6 +346,13 @@ int ob200_device_error_code(int32_t* code_out);
  *  of the network value (the reference's batched loop asks the network even
  *  then; its serial loop uses the result); value_sign = +1 adds the leaf value
  *  to the leaf edge as the reference's batched loop does, -1 is negamax.
+ *  Transposition table (replaces PHMapTranspositionTable,
+ *  src/mcts/phmap_transposition_table.cpp, as the batched loop uses it,
+ *  mcts_engine_batch_tree_simple.cpp:117-162): when a leaf edge is expanded and
+ *  a node with the same Zobrist key (stones + side to move, as
+ *  GomokuState::compute_hash_signature_internal) already exists in this move's
+ *  trees, the edge is pointed at
+ *  that node instead of a new one, so the subtree and its statistics are shared.
  * ------------------------------------------------------------------------- */
 typedef struct ob200_search ob200_search;
 
@@ -359,7 +366,8 @@ typedef struct ob200_search_config {
     float dirichlet_alpha;      /* 0.3                                             */
     float dirichlet_epsilon;    /* 0.25; 0 disables the root noise                 */
     int32_t value_sign;         /* +1 reference batched loop, -1 negamax           */
-    uint64_t seed;              /* root-noise generator                            */
+    int32_t use_transposition_table; /* MCTSSettings::use_transposition_table      */
+    uint64_t seed;              /* root-noise generator, Zobrist keys              */
 } ob200_search_config;
 
 typedef struct ob200_search_stats {

@@ -36,7 +36,8 @@ class NetConfig(C.Structure):
 class SearchConfig(C.Structure):
     _fields_ = [("n_trees", C.c_int32), ("sims_per_move", C.c_int32), ("leaf_batch", C.c_int32), ("max_depth", C.c_int32),
                 ("c_puct", C.c_float), ("virtual_loss", C.c_int32), ("dirichlet_alpha", C.c_float),
-                ("dirichlet_epsilon", C.c_float), ("value_sign", C.c_int32), ("seed", C.c_uint64)]
+                ("dirichlet_epsilon", C.c_float), ("value_sign", C.c_int32), ("use_transposition_table", C.c_int32),
+                ("seed", C.c_uint64)]
 
 
 class SearchStats(C.Structure):
@@ -361,10 +362,10 @@ class Search:
     MCTSEngine::search for many games at once)."""
 
     def __init__(self, net, n_trees=64, sims_per_move=800, leaf_batch=1024, max_depth=64, c_puct=1.5, virtual_loss=3,
-                 dirichlet_alpha=0.3, dirichlet_epsilon=0.25, value_sign=1, seed=0):
+                 dirichlet_alpha=0.3, dirichlet_epsilon=0.25, value_sign=1, transposition_table=False, seed=0):
         self.net = net                       # keep the network alive
         self.cfg = SearchConfig(n_trees, sims_per_move, leaf_batch, max_depth, c_puct, virtual_loss, dirichlet_alpha,
-                                dirichlet_epsilon, value_sign, seed)
+                                dirichlet_epsilon, value_sign, int(transposition_table), seed)
         self.h = C.c_void_p()
         check(lib().ob200_search_create(net.h, C.byref(self.cfg), C.byref(self.h)))
 

@@ -33,6 +33,11 @@ struct ob200_search {
     int16_t* leaf_hist = nullptr; uint8_t *leaf_nh = nullptr, *leaf_tm = nullptr;
     float *leaf_value = nullptr, *term_value = nullptr;   // term_value: NaN = not terminal
     float *policy = nullptr, *value = nullptr, *noise = nullptr;
+    // transposition table: Zobrist keys of positions -> node id (open addressing)
+    unsigned long long *zobrist = nullptr, *node_hash = nullptr, *tt_key = nullptr;
+    int32_t* tt_val = nullptr;
+    int tt_size = 0;                           // power of two; 0 = table off
+    std::vector<unsigned long long> zobrist_host;
     void* input_bt = nullptr;                  // encoder output for leaf_batch boards
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -143,7 +148,9 @@ __global__ void __launch_bounds__(256)
 expand_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const int32_t* __restrict__ path_len,
               int n_sims, int max_depth, const float* __restrict__ policy, int policy_size,
               const float* __restrict__ value, const float* __restrict__ term_value, float value_sign,
-              int max_nodes, int32_t* n_used, float* __restrict__ leaf_value) {
+              int max_nodes, int32_t* n_used, float* __restrict__ leaf_value, int sims_per_tree,
+              const uint8_t* __restrict__ root_tm, const unsigned long long* __restrict__ zobrist,
+              unsigned long long* node_hash, unsigned long long* tt_key, int32_t* tt_val, int tt_size) {
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (i >= n_sims) return;
     int len = path_len[i];
@@ -155,17 +162,41 @@ expand_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const int32_
     const int32_t* p = paths + (size_t)i * max_depth * 2;
     const int parent = p[2 * (len - 1)], slot = p[2 * (len - 1) + 1];
     const size_t e = (size_t)parent * t.pitch + slot;
-    int id = -1;
+    int id = -1, tt_slot = -1;
+    unsigned long long h = 0;
     if (lane == 0 && atomicCAS(t.child_node + e, -1, -2) == -1) {     // first simulation on this edge claims it
-        id = atomicAdd(n_used, 1);
-        if (id >= max_nodes) {                                        // pool exhausted: the edge stays a leaf
-            atomicSub(n_used, 1);
-            atomicExch(t.child_node + e, -1);
-            id = -1;
+        bool shared = false;
+        if (tt_size > 0) {
+            // Zobrist key of the position behind the edge: the parent's key, the mover's stone, the
+            // side to move flipped (GomokuState::compute_hash_signature_internal keys the board and
+            // the player, not the move order: src/games/gomoku/gomoku_state.cpp:947-958)
+            const int rtm = root_tm[i / sims_per_tree];
+            const int mover = ((len - 1) & 1) ? 3 - rtm : rtm;
+            h = node_hash[parent] ^ zobrist[(mover - 1) * 225 + slot] ^ zobrist[450];
+            if (h == 0) h = 1;
+            unsigned idx = (unsigned)(h >> 17) & (unsigned)(tt_size - 1);
+            for (int tries = 0; tries < 64; ++tries, idx = (idx + 1) & (unsigned)(tt_size - 1)) {
+                unsigned long long k = tt_key[idx];
+                if (k == 0) k = atomicCAS(tt_key + idx, 0ull, h);       // try to take the empty slot
+                if (k == 0) { tt_slot = (int)idx; break; }               // ours: filled in once the node exists
+                if (k == h) {                                            // same position reached before
+                    const int other = *reinterpret_cast<volatile int32_t*>(tt_val + idx);
+                    if (other >= 0) { atomicExch(t.child_node + e, other); shared = true; }
+                    break;                                               // (or being created right now: no sharing)
+                }
+            }
+        }
+        if (!shared) {
+            id = atomicAdd(n_used, 1);
+            if (id >= max_nodes) {                                    // pool exhausted: the edge stays a leaf
+                atomicSub(n_used, 1);
+                atomicExch(t.child_node + e, -1);
+                id = -1;
+            }
         }
     }
     id = __shfl_sync(0xffffffffu, id, 0);
-    if (id < 0) return;     // another simulation of this round creates the node (or nobody can)
+    if (id < 0) return;     // another simulation of the same batch creates the node, it is shared, or nobody can
     const size_t row = (size_t)id * t.pitch;
     const uint32_t* pm = t.legal_bits + (size_t)parent * t.mask_words;
     uint32_t* cm = t.legal_bits + (size_t)id * t.mask_words;
@@ -180,8 +211,10 @@ expand_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const int32_
     }
     if (lane == 0) {
         t.node_visits[id] = 0;
+        if (tt_size > 0) node_hash[id] = h;
         __threadfence();
         atomicExch(t.child_node + e, id);
+        if (tt_slot >= 0) atomicExch(tt_val + tt_slot, id);          // visible to later transpositions
     }
 }
 
@@ -248,6 +281,12 @@ int ob200_search_create(ob200_net* net, const ob200_search_config* cfg, ob200_se
     A_(salloc(s, &s->leaf_value, (size_t)L)); A_(salloc(s, &s->term_value, (size_t)L));
     A_(salloc(s, &s->policy, (size_t)L * s->A)); A_(salloc(s, &s->value, (size_t)L));
     A_(salloc(s, &s->noise, (size_t)T * s->pitch));
+    if (cfg->use_transposition_table) {
+        s->tt_size = 1;
+        while (s->tt_size < 2 * s->max_nodes) s->tt_size <<= 1;
+        A_(salloc(s, &s->zobrist, 451)); A_(salloc(s, &s->node_hash, (size_t)s->max_nodes));
+        A_(salloc(s, &s->tt_key, (size_t)s->tt_size)); A_(salloc(s, &s->tt_val, (size_t)s->tt_size));
+    }
     uint8_t* bt = nullptr;
     A_(salloc(s, &bt, (size_t)ob200_board_tensor_bytes(15, L, 64)));
     s->input_bt = bt;
@@ -256,6 +295,17 @@ int ob200_search_create(ob200_net* net, const ob200_search_config* cfg, ob200_se
     std::vector<int32_t> roots(T);
     for (int t = 0; t < T; ++t) roots[t] = t;
     OB200_CUDA_OK(cudaMemcpy(s->roots, roots.data(), T * sizeof(int32_t), cudaMemcpyHostToDevice));
+    if (s->tt_size) {
+        // Zobrist keys: splitmix64 stream from the seed; [0,225) BLACK stones, [225,450) WHITE, [450] side to move
+        s->zobrist_host.resize(451);
+        unsigned long long x = cfg->seed ^ 0xD1B54A32D192ED03ull;
+        for (auto& z : s->zobrist_host) {
+            x += 0x9E3779B97F4A7C15ull;
+            unsigned long long v = x;
+            v = (v ^ (v >> 30)) * 0xBF58476D1CE4E5B9ull; v = (v ^ (v >> 27)) * 0x94D049BB133111EBull; z = v ^ (v >> 31);
+        }
+        OB200_CUDA_OK(cudaMemcpy(s->zobrist, s->zobrist_host.data(), 451 * 8, cudaMemcpyHostToDevice));
+    }
     OB200_CUDA_OK(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
     OB200_CUDA_OK(cudaEventCreate(&s->ev0)); OB200_CUDA_OK(cudaEventCreate(&s->ev1));
     *out = s;
@@ -335,6 +385,17 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
         }
         OB200_CUDA_OK(cudaMemcpyAsync(s->noise, noise.data(), noise.size() * 4, cudaMemcpyHostToDevice, st));
     }
+    if (s->tt_size) {
+        std::vector<unsigned long long> rh(T, 0ull);
+        for (int t = 0; t < T; ++t) {
+            for (int i = 0; i < n_moves[t]; ++i) rh[t] ^= s->zobrist_host[(i & 1) * 225 + moves[(size_t)t * moves_stride + i]];
+            if (n_moves[t] & 1) rh[t] ^= s->zobrist_host[450];
+            rh[t] ^= 0x9E3779B97F4A7C15ull * (unsigned long long)(t + 1);   // per-game salt: games do not share nodes
+        }
+        OB200_CUDA_OK(cudaMemcpyAsync(s->node_hash, rh.data(), (size_t)T * 8, cudaMemcpyHostToDevice, st));
+        OB200_CUDA_OK(cudaMemsetAsync(s->tt_key, 0, (size_t)s->tt_size * 8, st));
+        OB200_CUDA_OK(cudaMemsetAsync(s->tt_val, 0xFF, (size_t)s->tt_size * 4, st));
+    }
     OB200_CUDA_OK(cudaEventRecord(s->ev0, st));
     // ---- roots: create, evaluate, priors (+ noise) ----
     init_roots_kernel<<<T, 128, 0, st>>>(s->tv, s->root_stones, T, s->n_used, s->term_count);
@@ -360,7 +421,8 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
         if (int rc = net_forward_for_search(s->net, s->input_bt, L, s->policy, s->value, st)) return rc;
         expand_kernel<<<(L * 32 + 255) / 256, 256, 0, st>>>(s->tv, s->paths, s->path_len, L, c.max_depth, s->policy, A,
                                                            s->value, s->term_value, (float)c.value_sign, s->max_nodes,
-                                                           s->n_used, s->leaf_value);
+                                                           s->n_used, s->leaf_value, s->sims_per_round, s->root_tm,
+                                                           s->zobrist, s->node_hash, s->tt_key, s->tt_val, s->tt_size);
         OB200_LAUNCHED("expand_kernel");
         if (int rc = ob200_launch_backup(&s->tv, s->paths, s->path_len, s->leaf_value, L, c.max_depth, c.virtual_loss, st)) return rc;
     }

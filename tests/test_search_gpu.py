@@ -128,6 +128,46 @@ def test_terminal_edges_match_the_oracle_rule(net, oracle):
             assert tr["W"][t, a] == tr["N"][t, a]                # each visit backed up the result
 
 
+def test_transposition_table_shares_nodes(net):
+    """With the table on, a position reached by two move orders is one node: fewer nodes for the
+    same simulations, edges outnumber nodes, and every edge still leads to the position it names."""
+    from omoknuni_small_b200 import capi
+    T, sims = 8, 640
+    games, _, _, _ = synth.make_gomoku_games(T, 15, seed=12, max_moves=10)
+    out = {}
+    for tt in (False, True):
+        s = capi.Search(net, n_trees=T, sims_per_move=sims, leaf_batch=64, max_depth=32, c_puct=1.5, virtual_loss=3,
+                        dirichlet_epsilon=0.0, transposition_table=tt, seed=4)
+        _, visits, st = s.run(games)
+        tr = s.tree()
+        assert (visits.sum(1) == sims).all() and not tr["VL"].any()
+        out[tt] = (st["nodes"], tr)
+    n_off, _ = out[False]
+    n_on, tr = out[True]
+    assert n_on < n_off, (n_on, n_off)
+    child = tr["child_node"][:, :225]
+    parents, slots = np.nonzero(child >= 0)
+    assert len(parents) > n_on - T                                  # some node has more than one parent edge
+    incoming = np.zeros(n_on, np.int64)
+    for p, a in zip(parents, slots):
+        c = child[p, a]
+        lp, lc = legal_of(tr["legal_bits"][p]), legal_of(tr["legal_bits"][c])
+        assert lp[a] and not lc[a] and np.array_equal(np.delete(lp, a), np.delete(lc, a))   # same stones either way
+        incoming[c] += tr["N"][p, a]
+    assert np.array_equal(incoming[T:], tr["node_visits"][T:])      # a shared node counts the visits of all its parents
+    # games keep their own trees: a node is reachable from one root only
+    owner = np.full(n_on, -1)
+    owner[:T] = np.arange(T)
+    frontier = list(range(T))
+    while frontier:
+        p = frontier.pop()
+        for c in child[p][child[p] >= 0]:
+            assert owner[c] in (-1, owner[p])
+            if owner[c] < 0:
+                owner[c] = owner[p]
+                frontier.append(c)
+
+
 def test_search_argument_errors(net):
     from omoknuni_small_b200 import capi
     with pytest.raises(capi.Error):
