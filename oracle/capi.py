@@ -268,6 +268,7 @@ class RefNet:
             L.ref_net_get.argtypes = [C.c_void_p, C.c_char_p, _f32, C.c_int64]
             L.ref_net_set.restype = C.c_int64
             L.ref_net_set.argtypes = [C.c_void_p, C.c_char_p, _f32, C.c_int64]
+            L.ref_net_save.argtypes = [C.c_void_p, C.c_char_p]
             L.ref_net_forward.restype = C.c_double
             L.ref_net_forward.argtypes = [C.c_void_p, _f32, C.c_int, C.c_int, _f32, _f32, C.c_int, C.c_int]
             _ref_net = L
@@ -294,6 +295,11 @@ class RefNet:
         a = np.ascontiguousarray(arr, np.float32).ravel()
         if self.L.ref_net_set(self.h, name.encode(), a, a.size) != a.size:
             raise KeyError(f"{name}: unknown or size mismatch")
+
+    def save(self, path):
+        """ResNetModel::save: the reference's checkpoint file."""
+        if self.L.ref_net_save(self.h, str(path).encode()) != 0:
+            raise RuntimeError("reference save failed")
 
     def forward(self, x, threads=0, repeats=1):
         """x [B,C,S,S] fp32 -> (log-softmax policy [B,A], value [B], seconds per forward)."""

@@ -98,5 +98,10 @@ double ref_net_forward(void* h, const float* x, int B, int C, float* logp_out, f
     }
 }
 int ref_net_threads() { return at::get_num_threads(); }
+// ResNetModel::save (src/nn/resnet_model.cpp:813-828): the checkpoint format of the reference.
+int ref_net_save(void* h, const char* path) {
+    try { static_cast<Net*>(h)->m->save(path); return 0; } catch (const std::exception& e) {
+        fprintf(stderr, "ref_net_save: %s\n", e.what()); return -1; }
+}
 
 }  // extern "C"
