@@ -168,6 +168,29 @@ def test_transposition_table_shares_nodes(net):
                 frontier.append(c)
 
 
+def test_self_play_records(net, tmp_path, oracle):
+    """Games advance together to the end; every record has the reference's fields, legal moves,
+    one policy per move, and the result the oracle's rule gives for its move list."""
+    import json
+    from omoknuni_small_b200 import capi, selfplay
+    s = capi.Search(net, n_trees=8, sims_per_move=32, leaf_batch=64, max_depth=16, dirichlet_epsilon=0.25, seed=2)
+    sp = selfplay.SelfPlay(s, temperature_threshold=4, max_moves=24, seed=5, out_dir=str(tmp_path))
+    recs = sp.generate_games(10)
+    assert len(recs) == 10 and len(list(tmp_path.glob("game_*.json"))) >= 10
+    for rec in recs:
+        assert set(rec) >= {"game_type", "board_size", "winner", "total_time_ms", "game_id", "moves", "policies"}
+        mv = rec["moves"]
+        assert len(mv) == len(rec["policies"]) <= 24 and len(set(mv)) == len(mv)
+        assert all(len(p) == 225 and abs(sum(p) - 1) < 1e-4 for p in rec["policies"])
+        assert all(rec["policies"][i][mv[i]] > 0 for i in range(len(mv)))
+        res = oracle.gomoku_result(mv)
+        assert rec["winner"] == (res if res in (1, 2) else 0)
+        assert all(oracle.gomoku_result(mv[:k]) == 0 for k in range(1, len(mv)))     # no move after the end
+        assert json.load(open(tmp_path / f"game_{rec['game_id']}.json"))["moves"] == mv
+    for mv in ([112], [0, 1, 2, 3, 4, 5, 6, 7, 8], list(range(0, 18))):
+        assert selfplay.gomoku_result(mv) == oracle.gomoku_result(mv)
+
+
 def test_search_argument_errors(net):
     from omoknuni_small_b200 import capi
     with pytest.raises(capi.Error):
