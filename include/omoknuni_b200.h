@@ -187,7 +187,8 @@ int64_t ob200_board_tensor_bytes(int32_t board_size, int32_t B, int32_t channels
  *       attack / defense planes, which the reference's CPU code computes as
  *       zero for every legal move (it scores the board without the candidate
  *       stone against itself).
- * All pointers are device pointers. */
+ * All pointers are device pointers; history must be 16-byte aligned (each
+ * board's 16 entries are read as two 16-byte words). */
 int ob200_launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist,
                                const uint8_t* to_move, int32_t B, int32_t board_size,
                                int32_t planes, int32_t out_channels, void* board_tensor_out,

@@ -2,16 +2,19 @@
 //
 // Output format (see "Board tensors" in omoknuni_b200.h): NHWC, positions on a
 // (S+1) x (S+1) grid per board whose last column / row are zero, guard
-// positions before and after.  A thread produces one position (its 16-byte
-// channel blocks one after the other); the kernels also write the zero
-// padding, so the output needs no memset.
+// positions before and after.  Stores are 16 bytes wide, consecutive threads
+// consecutive addresses; the kernels also write the zero padding, so the output
+// needs no memset.
 #include "internal.h"
 #include <cuda_bf16.h>
+#include <mutex>
 
 namespace ob200 {
 namespace {
 
 struct alignas(16) Pack8 { __nv_bfloat16 v[8]; };
+constexpr size_t kMaxBoardSmem = 200 * 1024;   // a board's block must fit a CTA's shared memory
+constexpr int kMaxDevices = 64;
 
 // Gomoku planes from the move history; reference semantics in
 // GomokuState::getEnhancedTensorRepresentation
@@ -19,49 +22,116 @@ struct alignas(16) Pack8 { __nv_bfloat16 v[8]; };
 // the opponent's for even k and the side to move's for odd k; plane 2i holds
 // the side to move's i-th most recent stone, plane 2i+1 the opponent's.
 // Hence plane p takes move k = p + 1 (p even) or p - 1 (p odd).
-__global__ void __launch_bounds__(256)
+constexpr int kEncThreads = 128;
+__global__ void __launch_bounds__(kEncThreads)
 encode_gomoku_kernel(const int16_t* __restrict__ history, const uint8_t* __restrict__ n_hist,
                      const uint8_t* __restrict__ to_move, int B, int S, int planes, int chunks,
-                     int cover, Pack8* __restrict__ out) {
-    // cover = positions written (guards included); chunks = channels / 8.
-    // One thread per position writes all its chunks; only the first three can be non-zero.
-    const int pidx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (pidx >= cover) return;
+                     int chunk_shift, int cover, Pack8* __restrict__ out) {
+    // cover = positions written (guards included); chunks = channels / 8 (chunk_shift = log2 when it
+    // is a power of two, else -1).  Phase 1: a thread works out the 24 plane channels of one
+    // position.  Phase 2: the block writes its 128 positions as 16-byte stores, consecutive threads
+    // consecutive addresses; channels past 24 are zero.
+    __shared__ Pack8 stage[kEncThreads][3];
+    const int base = blockIdx.x * kEncThreads;
+    const int pidx = base + threadIdx.x;
+    Pack8 o[3];
+#pragma unroll
+    for (int c = 0; c < 3; ++c)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[c].v[j] = __float2bfloat16(0.0f);
     const int p = pidx - OB200_GUARD;
     const int GP = S + 1, slots = GP * GP;
-    int cell = -1, b = 0;
     if (p >= 0 && p < B * slots) {
-        b = p / slots;
-        const int r = p - b * slots;
+        const int b = p / slots, r = p - b * slots;
         const int y = r / GP, x = r - y * GP;
-        if (y < S && x < S) cell = y * S + x;
+        if (y < S && x < S) {
+            const int cell = y * S + x;
+            const int nh = n_hist[b];
+            // the board's 16 history entries as two 16-byte loads (the launcher checks alignment)
+            const uint4* h4 = reinterpret_cast<const uint4*>(history + (size_t)b * 16);
+            const uint4 ha = __ldg(h4), hb = __ldg(h4 + 1);
+            const uint32_t hw[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+#pragma unroll
+            for (int plane = 0; plane < 16; ++plane) {
+                const int k = (plane & 1) ? plane - 1 : plane + 1;
+                const int hk = (int)(int16_t)((k & 1) ? (hw[k >> 1] >> 16) : (hw[k >> 1] & 0xffffu));
+                if (k < nh && hk == cell) o[plane >> 3].v[plane & 7] = __float2bfloat16(1.0f);
+            }
+            // plane 16: colour.  Planes 17 / 18 (attack / defense): zero, as the reference's CPU
+            // code yields for every legal move (src/utils/attack_defense_module.cpp:96-154).
+            if (planes > 16 && to_move[b] == 1) o[2].v[0] = __float2bfloat16(1.0f);
+        }
     }
+#pragma unroll
+    for (int c = 0; c < 3; ++c) stage[threadIdx.x][c] = o[c];
+    __syncthreads();
+    const int n_pos = min(kEncThreads, cover - base);
+    const int n = n_pos * chunks;
     Pack8 zero;
 #pragma unroll
     for (int j = 0; j < 8; ++j) zero.v[j] = __float2bfloat16(0.0f);
-    Pack8* dst = out + (size_t)pidx * chunks;
-    if (cell < 0) {
-        for (int c = 0; c < chunks; ++c) dst[c] = zero;
+    Pack8* dst = out + (size_t)base * chunks;
+    for (int idx = threadIdx.x; idx < n; idx += kEncThreads) {
+        const int pl = chunk_shift >= 0 ? idx >> chunk_shift : idx / chunks;
+        const int ch = idx - pl * chunks;
+        dst[idx] = ch < 3 ? stage[pl][ch] : zero;
+    }
+}
+
+// The same planes, a CTA per board: the board's (S+1)^2 x C block of the tensor is built in
+// shared memory (zero fill, then one 2-byte store per history stone and per cell of the colour
+// plane) and leaves as one bulk copy.  Blocks B and B + 1 zero the guard positions before the
+// first and after the last board.
+__global__ void __launch_bounds__(256)
+encode_gomoku_board_kernel(const int16_t* __restrict__ history, const uint8_t* __restrict__ n_hist,
+                           const uint8_t* __restrict__ to_move, int B, int S, int planes, int C, int cover,
+                           uint8_t* __restrict__ out) {
+    extern __shared__ __align__(128) uint8_t board_s[];
+    const int GP = S + 1, slots = GP * GP, S2 = S * S;
+    const int row_bytes = C * 2;
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    if ((int)blockIdx.x >= B) {
+        const long long first = (int)blockIdx.x == B ? 0 : (long long)OB200_GUARD + (long long)B * slots;
+        const long long last = (int)blockIdx.x == B ? OB200_GUARD : cover;
+        uint4* o16 = reinterpret_cast<uint4*>(out);
+        for (long long i = first * row_bytes / 16 + threadIdx.x; i < last * row_bytes / 16; i += blockDim.x) o16[i] = z;
         return;
     }
-    const int nh = n_hist[b];
-    const int16_t* h = history + (size_t)b * 16;
-    const float colour = (planes > 16 && to_move[b] == 1) ? 1.0f : 0.0f;
-    for (int c = 0; c < chunks; ++c) {
-        Pack8 o = zero;
-        if (c < 2) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int plane = c * 8 + j;
-                const int k = (plane & 1) ? plane - 1 : plane + 1;
-                if (k < nh && h[k] == cell) o.v[j] = __float2bfloat16(1.0f);
+    const int bytes = slots * row_bytes;
+    uint4* s16 = reinterpret_cast<uint4*>(board_s);
+    for (int i = threadIdx.x; i < bytes / 16; i += blockDim.x) s16[i] = z;
+    __syncthreads();
+    const int b = blockIdx.x;
+    __nv_bfloat16* sb = reinterpret_cast<__nv_bfloat16*>(board_s);
+    const __nv_bfloat16 one = __float2bfloat16(1.0f);
+    if (threadIdx.x < 16) {
+        const int plane = threadIdx.x;
+        const int k = (plane & 1) ? plane - 1 : plane + 1;
+        if (k < (int)n_hist[b]) {
+            const int cell = history[(size_t)b * 16 + k];
+            if (cell >= 0 && cell < S2) {
+                const int y = cell / S, x = cell - y * S;
+                sb[(y * GP + x) * C + plane] = one;
             }
-        } else if (c == 2) {
-            // plane 16: colour.  Planes 17 / 18 (attack / defense): zero, as the reference's CPU
-            // code yields for every legal move (src/utils/attack_defense_module.cpp:96-154).
-            o.v[0] = __float2bfloat16(colour);
         }
-        dst[c] = o;
+    }
+    // plane 16: colour.  Planes 17 / 18 (attack / defense) stay zero, as the reference's CPU code
+    // yields for every legal move (src/utils/attack_defense_module.cpp:96-154).
+    if (planes > 16 && to_move[b] == 1) {
+        for (int cell = threadIdx.x; cell < S2; cell += blockDim.x) {
+            const int y = cell / S, x = cell - y * S;
+            sb[(y * GP + x) * C + 16] = one;
+        }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> bulk copy engine
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint8_t* dst = out + ((size_t)OB200_GUARD + (size_t)b * slots) * row_bytes;
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                     "r"((uint32_t)__cvta_generic_to_shared(board_s)), "r"((uint32_t)bytes)
+                     : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // shared memory read before the CTA ends
     }
 }
 
@@ -103,12 +173,38 @@ int launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, const ui
         return set_error(OB200_ERR_INVALID,
                          "ob200_launch_encode_gomoku: board_size %d must be in [5,31] and out_channels %d a multiple of 8 >= planes",
                          board_size, out_channels);
+    if (reinterpret_cast<uintptr_t>(history) & 15)
+        return set_error(OB200_ERR_INVALID, "ob200_launch_encode_gomoku: history must be 16-byte aligned");
     if (int rc = require_device()) return rc;
     const BoardGeom g = board_geom(board_size, B);
     const int chunks = out_channels / 8;
-    if (g.PT > 0x7fffffffLL / 2) return set_error(OB200_ERR_TOO_LARGE, "encode: batch too large");
-    encode_gomoku_kernel<<<(unsigned)((g.PT + 255) / 256), 256, 0, stream>>>(
-        history, n_hist, to_move, B, board_size, planes, chunks, (int)g.PT, reinterpret_cast<Pack8*>(board_tensor_out));
+    if (g.PT * chunks > 0x7fffffffLL) return set_error(OB200_ERR_TOO_LARGE, "encode: batch too large");
+    const size_t board_bytes = (size_t)(board_size + 1) * (board_size + 1) * out_channels * 2;
+    if (board_bytes <= kMaxBoardSmem) {
+        // one CTA per board, the board's block staged in shared memory
+        static std::once_flag once[kMaxDevices];
+        int dev = 0;
+        OB200_CUDA_OK(cudaGetDevice(&dev));
+        if (dev >= 0 && dev < kMaxDevices)
+            std::call_once(once[dev], [] {
+                cudaFuncSetAttribute(encode_gomoku_board_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)kMaxBoardSmem);
+            });
+        else if (board_bytes > 48 * 1024)
+            OB200_CUDA_OK(cudaFuncSetAttribute(encode_gomoku_board_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)kMaxBoardSmem));
+        encode_gomoku_board_kernel<<<(unsigned)(B + 2), 256, board_bytes, stream>>>(
+            history, n_hist, to_move, B, board_size, planes, out_channels, (int)g.PT,
+            static_cast<uint8_t*>(board_tensor_out));
+        OB200_LAUNCHED("encode_gomoku_board_kernel");
+        return OB200_OK;
+    }
+    int chunk_shift = -1;
+    for (int sft = 0; sft < 8; ++sft)
+        if ((1 << sft) == chunks) chunk_shift = sft;
+    encode_gomoku_kernel<<<(unsigned)((g.PT + kEncThreads - 1) / kEncThreads), kEncThreads, 0, stream>>>(
+        history, n_hist, to_move, B, board_size, planes, chunks, chunk_shift, (int)g.PT,
+        reinterpret_cast<Pack8*>(board_tensor_out));
     OB200_LAUNCHED("encode_gomoku_kernel");
     return OB200_OK;
 }

@@ -6,9 +6,8 @@
 //                      in the reference's flatten order c * S*S + y * S + x
 //                      (src/nn/resnet_model.cpp:183,209 view({B,-1}) on NCHW).
 //   fc_kernel          out[b][j] = act(sum_i in[b][i] * WT[i][j] + bias[j]);
-//                      a CTA owns 8 boards x 64 outputs split in 4 K-slices, the
-//                      weight matrix is stored transposed so that threads read
-//                      it coalesced and each weight is used for 8 boards.
+//                      register-tiled (32 boards x 64 outputs per CTA, 4 x 4 per
+//                      thread, cp.async pipeline), weight matrix stored transposed.
 //   softmax_kernel     in-place softmax over a row.
 //   value_out_kernel   value_fc2 + tanh (one warp per board).
 #include "internal.h"
@@ -18,110 +17,185 @@
 namespace ob200 {
 namespace {
 
-constexpr int kFcBoards = 8;
-constexpr int kFcThreads = 256;
-constexpr int kFcKTile = 512;
-
 struct alignas(16) Pack8 { __nv_bfloat162 v[4]; };
 
-// One thread per real board cell; w_s holds [HC][64] folded weights.
-__global__ void __launch_bounds__(128)
+// A warp takes 32 consecutive positions of the board tensor (pad positions included, their
+// results are dropped).  Eight lanes share a position: lane = 8 * (position within a group of 4)
+// + channel block, so a warp-wide 16-byte load covers 4 positions x 128 contiguous bytes and the
+// 8 loads of a warp are issued back to back.  Each lane multiplies its 8 channels into a head
+// channel's partial sum, three shuffle steps add the 8 lanes, and lane (sub, blk) keeps the sum of
+// group blk: after 8 groups every lane owns one position and stores once per head channel.
+// HCT > 0: that many head channels, the lane's weights held in registers; HCT == 0: any number,
+// weights read from shared memory.
+constexpr int kHeadThreads = 128;
+template <int HCT>
+__global__ void __launch_bounds__(kHeadThreads)
 head_conv_kernel(const uint8_t* __restrict__ tower, const float* __restrict__ w,
                  const float* __restrict__ bias, int HC, int pc, float* __restrict__ hp,
                  float* __restrict__ hv, int B, int S) {
-    extern __shared__ float w_s[];  // HC*64 weights then HC biases
-    for (int i = threadIdx.x; i < HC * 64; i += blockDim.x) w_s[i] = w[i];
-    for (int i = threadIdx.x; i < HC; i += blockDim.x) w_s[HC * 64 + i] = bias[i];
-    __syncthreads();
-    const int S2 = S * S, GP = S + 1;
-    const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (gid >= (long long)B * S2) return;
-    const int b = (int)(gid / S2), cell = (int)(gid % S2);
-    const int y = cell / S, x = cell % S;
-    const long long rec = (long long)OB200_GUARD + (long long)b * GP * GP + y * GP + x;
-    float a[64];
+    extern __shared__ float w_s[];  // HCT == 0: [HC][64] folded weights then [HC] biases
+    const int lane = threadIdx.x & 31, sub = lane >> 3, blk = lane & 7;
+    constexpr int kRegCh = HCT > 0 ? HCT : 1;
+    float wreg[kRegCh][8], breg[kRegCh];
+    if (HCT > 0) {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        const Pack8 v = *reinterpret_cast<const Pack8*>(tower + rec * 128 + c * 16);
+        for (int h = 0; h < kRegCh; ++h) {
+            breg[h] = bias[h];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) wreg[h][k] = w[h * 64 + blk * 8 + k];
+        }
+    } else {
+        for (int i = threadIdx.x; i < HC * 64; i += blockDim.x) w_s[i] = w[i];
+        for (int i = threadIdx.x; i < HC; i += blockDim.x) w_s[HC * 64 + i] = bias[i];
+        __syncthreads();
+    }
+    const int hc = HCT > 0 ? HCT : HC;
+    const int S2 = S * S, GP = S + 1, slots = GP * GP, vc = hc - pc;
+    const int total = B * slots;
+    const int p0 = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 32;
+    if (p0 >= total) return;
+    // the tensor's trailing guard positions make the (at most 31) positions past the end readable
+    const uint8_t* src = tower + ((size_t)OB200_GUARD + p0 + sub) * 128 + blk * 16;
+    float a[8][8];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const Pack8 v = *reinterpret_cast<const Pack8*>(src + (size_t)it * 4 * 128);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float2 f = __bfloat1622float2(v.v[j]);
-            a[c * 8 + 2 * j] = f.x; a[c * 8 + 2 * j + 1] = f.y;
+            a[it][2 * j] = f.x; a[it][2 * j + 1] = f.y;
         }
     }
-    const int vc = HC - pc;
-    for (int h = 0; h < HC; ++h) {
-        float s = 0.0f;
+    // this lane's own position: group blk, member sub
+    const int p = p0 + blk * 4 + sub;
+    const int b = p / slots, r = p - b * slots;
+    const int y = r / GP, x = r - y * GP;
+    const bool real = p < total && y < S && x < S;
+    const int cell = y * S + x;
+    auto one_channel = [&](int h, const float (&wk)[8], float bh) {
+        float keep = 0.0f;
 #pragma unroll
-        for (int k = 0; k < 64; ++k) s = fmaf(a[k], w_s[h * 64 + k], s);
-        s = fmaxf(s + w_s[HC * 64 + h], 0.0f);
-        if (h < pc) hp[((size_t)b * pc + h) * S2 + cell] = s;
-        else hv[((size_t)b * vc + (h - pc)) * S2 + cell] = s;
+        for (int it = 0; it < 8; ++it) {
+            float s = a[it][0] * wk[0];
+#pragma unroll
+            for (int k = 1; k < 8; ++k) s = fmaf(a[it][k], wk[k], s);
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            keep = (it == blk) ? s : keep;
+        }
+        if (real) {
+            const float o = fmaxf(keep + bh, 0.0f);
+            if (h < pc) hp[((size_t)b * pc + h) * S2 + cell] = o;
+            else hv[((size_t)b * vc + (h - pc)) * S2 + cell] = o;
+        }
+    };
+    if (HCT > 0) {
+#pragma unroll
+        for (int h = 0; h < kRegCh; ++h) one_channel(h, wreg[h], breg[h]);
+    } else {
+        for (int h = 0; h < hc; ++h) {
+            const float4* wr = reinterpret_cast<const float4*>(w_s + h * 64 + blk * 8);
+            const float4 w0 = wr[0], w1 = wr[1];
+            const float wk[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            one_channel(h, wk, w_s[hc * 64 + h]);
+        }
     }
 }
 
-// A CTA owns 8 boards x 64 outputs; its 256 threads are 4 K-slices x 64 outputs, so a
-// thread walks a quarter of the inner dimension with 8 accumulators (one weight load
-// feeds 8 boards) and the slices are summed through shared memory.  Small tiles give a
-// grid of several CTAs per SM, which is what hides the L2 latency of the weight reads.
-__global__ void __launch_bounds__(kFcThreads)
+// out[b][j] = act(sum_i in[b][i] * WT[i][j] + bias[j]).  Register-tiled: a CTA owns 32 boards x
+// 64 outputs, a thread 4 boards x 4 outputs.  The 256 threads form two groups of 128 that each
+// take half of the inner dimension and run their own 3-stage cp.async pipeline of 16-deep tiles
+// (operands read back from shared memory as float4: 2 shared loads feed 16 multiply-adds); the
+// second group's sums pass through shared memory to the first, which applies bias / ReLU.
+constexpr int kFcTileB = 32, kFcTileN = 64, kFcTileK = 16, kFcStages = 3, kFcAPitch = kFcTileB + 4;
+struct FcStage {
+    float a[kFcTileK][kFcAPitch];   // inputs, k-major; the pad spreads the staging writes over banks
+    float b[kFcTileK][kFcTileN];    // weights
+};
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+                 : "memory");
+}
+__global__ void __launch_bounds__(256)
 fc_kernel(const float* __restrict__ in, const float* __restrict__ WT, const float* __restrict__ bias,
           float* __restrict__ out, int B, int K, int Nout, int relu) {
-    __shared__ __align__(16) float in_s[kFcBoards][kFcKTile];
-    __shared__ float red[3][kFcBoards][64];
-    const int b0 = blockIdx.x * kFcBoards;
-    const int jl = threadIdx.x & 63, slice = threadIdx.x >> 6;
-    const int j = blockIdx.y * 64 + jl;
-    float acc[kFcBoards];
+    __shared__ __align__(16) FcStage st[2][kFcStages];
+    const int half = threadIdx.x >> 7, t = threadIdx.x & 127;
+    const int b0 = blockIdx.x * kFcTileB, n0 = blockIdx.y * kFcTileN;
+    const int tb = (t >> 4) * 4, tn = (t & 15) * 4;   // 8 x 16 threads
+    const int tiles = (K + kFcTileK - 1) / kFcTileK, split = (tiles + 1) / 2;
+    const int first = half ? split : 0, last = half ? tiles : split;
+    float acc[4][4];
 #pragma unroll
-    for (int g = 0; g < kFcBoards; ++g) acc[g] = 0.0f;
-    for (int k0 = 0; k0 < K; k0 += kFcKTile) {
-        const int kt = min(kFcKTile, K - k0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < kFcBoards * kt; idx += kFcThreads) {
-            const int g = idx / kt, i = idx % kt;
-            in_s[g][i] = (b0 + g < B) ? in[(size_t)(b0 + g) * K + k0 + i] : 0.0f;
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+    auto issue = [&](int tile, int slot) {
+        if (tile < last) {
+            FcStage& s = st[half][slot];
+            const int k0 = tile * kFcTileK;
+#pragma unroll
+            for (int r = 0; r < (kFcTileK * kFcTileB) / 128; ++r) {
+                const int idx = t + r * 128;
+                const int bb = idx / kFcTileK, kk = idx - bb * kFcTileK;   // threads walk k: rows of `in`
+                const int gb = b0 + bb, gk = k0 + kk;
+                if (gb < B && gk < K) cp_async4(&s.a[kk][bb], in + (size_t)gb * K + gk);
+                else s.a[kk][bb] = 0.0f;
+            }
+#pragma unroll
+            for (int r = 0; r < (kFcTileK * kFcTileN) / 128; ++r) {
+                const int idx = t + r * 128;
+                const int kk = idx / kFcTileN, nn = idx - kk * kFcTileN;
+                const int gk = k0 + kk, gn = n0 + nn;
+                if (gk < K && gn < Nout) cp_async4(&s.b[kk][nn], WT + (size_t)gk * Nout + gn);
+                else s.b[kk][nn] = 0.0f;
+            }
         }
-        __syncthreads();
-        if (j < Nout) {
-            // slices are multiples of 4 wide so that the staged inputs are read as float4:
-            // one shared-memory load feeds 4 multiply-adds (the loop is otherwise bound by
-            // shared-memory instruction issue)
-            const int per = ((kt + 3) / 4 + 3) & ~3;
-            const int i0 = slice * per, i1 = min(kt, i0 + per);
-            const float* wp = WT + (size_t)k0 * Nout + j;
-            int i = i0;
-            for (; i + 4 <= i1; i += 4) {
-                const float w0 = __ldg(wp + (size_t)i * Nout), w1 = __ldg(wp + (size_t)(i + 1) * Nout);
-                const float w2 = __ldg(wp + (size_t)(i + 2) * Nout), w3 = __ldg(wp + (size_t)(i + 3) * Nout);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
 #pragma unroll
-                for (int g = 0; g < kFcBoards; ++g) {
-                    const float4 x = *reinterpret_cast<const float4*>(&in_s[g][i]);
-                    acc[g] = fmaf(x.x, w0, acc[g]); acc[g] = fmaf(x.y, w1, acc[g]);
-                    acc[g] = fmaf(x.z, w2, acc[g]); acc[g] = fmaf(x.w, w3, acc[g]);
-                }
-            }
-            for (; i < i1; ++i) {
-                const float wv = __ldg(wp + (size_t)i * Nout);
+    for (int s = 0; s < kFcStages - 1; ++s) issue(first + s, s);
+    for (int tile = first; tile < last; ++tile) {
+        const int slot = (tile - first) % kFcStages;
+        asm volatile("cp.async.wait_group %0;" ::"n"(kFcStages - 2) : "memory");
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");   // tile landed; previous slot free
+        issue(tile + kFcStages - 1, (slot + kFcStages - 1) % kFcStages);
+        const FcStage& s = st[half][slot];
 #pragma unroll
-                for (int g = 0; g < kFcBoards; ++g) acc[g] = fmaf(in_s[g][i], wv, acc[g]);
-            }
+        for (int kk = 0; kk < kFcTileK; ++kk) {
+            const float4 av = *reinterpret_cast<const float4*>(&s.a[kk][tb]);
+            const float4 bv = *reinterpret_cast<const float4*>(&s.b[kk][tn]);
+            const float aa[4] = {av.x, av.y, av.z, av.w}, bb[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(aa[i], bb[j], acc[i][j]);
         }
     }
-    if (slice > 0) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    float* red = reinterpret_cast<float*>(&st[0][0]);   // 128 x 16 floats, reusing the stages
+    if (half) {
 #pragma unroll
-        for (int g = 0; g < kFcBoards; ++g) red[slice - 1][g][jl] = acc[g];
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) red[(i * 4 + j) * 128 + t] = acc[i][j];
     }
     __syncthreads();
-    if (slice == 0 && j < Nout) {
-        const float bj = bias[j];
+    if (half) return;
 #pragma unroll
-        for (int g = 0; g < kFcBoards; ++g)
-            if (b0 + g < B) {
-                float v = acc[g] + red[0][g][jl] + red[1][g][jl] + red[2][g][jl] + bj;
-                if (relu) v = fmaxf(v, 0.0f);
-                out[(size_t)(b0 + g) * Nout + j] = v;
-            }
+    for (int i = 0; i < 4; ++i) {
+        const int gb = b0 + tb + i;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tn + j;
+            if (gb >= B || gn >= Nout) continue;
+            float v = acc[i][j] + red[(i * 4 + j) * 128 + t] + bias[gn];
+            if (relu) v = fmaxf(v, 0.0f);
+            out[(size_t)gb * Nout + gn] = v;
+        }
     }
 }
 
@@ -167,18 +241,26 @@ value_out_kernel(const float* __restrict__ hidden, const float* __restrict__ w2,
 
 int launch_head_conv(const void* tower, const float* w, const float* bias, int HC, int pc,
                      float* hp, float* hv, int B, int S, cudaStream_t st) {
-    const long long total = (long long)B * S * S;
-    const size_t smem = (size_t)(HC * 64 + HC) * sizeof(float);
-    head_conv_kernel<<<(unsigned)((total + 127) / 128), 128, smem, st>>>(static_cast<const uint8_t*>(tower), w, bias,
-                                                                        HC, pc, hp, hv, B, S);
+    const long long total = (long long)B * (S + 1) * (S + 1);   // positions, one warp per 32
+    const unsigned grid = (unsigned)((total + kHeadThreads - 1) / kHeadThreads);
+    const uint8_t* t = static_cast<const uint8_t*>(tower);
+    switch (HC) {
+        case 1: head_conv_kernel<1><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S); break;
+        case 2: head_conv_kernel<2><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S); break;
+        case 3: head_conv_kernel<3><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S); break;
+        case 4: head_conv_kernel<4><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S); break;
+        default:
+            head_conv_kernel<0><<<grid, kHeadThreads, (size_t)(HC * 64 + HC) * sizeof(float), st>>>(t, w, bias, HC, pc,
+                                                                                                   hp, hv, B, S);
+    }
     OB200_LAUNCHED("head_conv_kernel");
     return OB200_OK;
 }
 
 int launch_fc(const float* in, const float* WT, const float* bias, float* out, int B, int K, int Nout, int relu,
               cudaStream_t st) {
-    dim3 grid((B + kFcBoards - 1) / kFcBoards, (Nout + 63) / 64);
-    fc_kernel<<<grid, kFcThreads, 0, st>>>(in, WT, bias, out, B, K, Nout, relu);
+    dim3 grid((B + kFcTileB - 1) / kFcTileB, (Nout + kFcTileN - 1) / kFcTileN);
+    fc_kernel<<<grid, 256, 0, st>>>(in, WT, bias, out, B, K, Nout, relu);
     OB200_LAUNCHED("fc_kernel");
     return OB200_OK;
 }
