@@ -364,9 +364,9 @@ int* device_error_word() {
     return cached[dev];
 }
 
-// 2-D tensor map over a board tensor: inner dimension the 64 channels of a position
-// (128 bytes), outer dimension `rows` positions; boxes of 64 x box_rows, 128-byte swizzle.
-int make_board_tensor_map(const void* base, long long rows, int box_rows, BoardTensorMap* out) {
+// 2-D tensor map over a board tensor: inner dimension the `channels` channels of a position,
+// outer dimension `rows` positions; boxes of 64 channels (128 bytes) x box_rows, 128-byte swizzle.
+int make_board_tensor_map(const void* base, long long rows, int box_rows, BoardTensorMap* out, int channels) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -379,10 +379,11 @@ int make_board_tensor_map(const void* base, long long rows, int box_rows, BoardT
         encode = reinterpret_cast<EncodeFn>(fn);
     }
     static_assert(sizeof(BoardTensorMap) == sizeof(CUtensorMap), "tensor map size");
-    if (((uintptr_t)base & 15) || rows <= 0 || box_rows <= 0 || box_rows > 256)
-        return set_error(OB200_ERR_INVALID, "board tensor map: base must be 16-byte aligned, box rows in [1,256]");
-    const cuuint64_t dims[2] = {(cuuint64_t)kC, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)kRowBytes};
+    if (((uintptr_t)base & 15) || rows <= 0 || box_rows <= 0 || box_rows > 256 || channels < kC || channels % kC)
+        return set_error(OB200_ERR_INVALID,
+                         "board tensor map: base must be 16-byte aligned, box rows in [1,256], channels a multiple of 64");
+    const cuuint64_t dims[2] = {(cuuint64_t)channels, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)channels * 2};
     const cuuint32_t box[2] = {(cuuint32_t)kC, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = encode(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
@@ -442,8 +443,18 @@ int ob200_launch_conv3x3(const void* in, const void* packed_w, const float* bias
                          void* out, int32_t B, int32_t board_size, int32_t cin, int32_t cout, int32_t relu,
                          ob200_stream stream) {
     if (!in || !out || B <= 0) return set_error(OB200_ERR_INVALID, "ob200_launch_conv3x3: null pointer or empty batch");
+    if (conv_wide_covers(cin, cout)) {
+        if (board_size < 1 || conv_halo_rows(board_size) > kHaloMax)
+            return set_error(OB200_ERR_UNSUPPORTED, "ob200_launch_conv3x3: board_size %d outside [1, %d]", board_size, kHaloMax - 2);
+        const BoardGeom gw = board_geom(board_size, B);
+        BoardTensorMap wim, wom;
+        if (int rc = make_board_tensor_map(in, gw.PT, conv_wide_box_rows(), &wim, cin)) return rc;
+        if (int rc = make_board_tensor_map(out, gw.PT, kTileM, &wom, cout)) return rc;
+        return launch_conv_wide_maps(wim, wom, packed_w, bias, residual, B, board_size, cin, cout, 9, relu, as_stream(stream));
+    }
     if (cin != kC || cout != kC)
-        return set_error(OB200_ERR_UNSUPPORTED, "ob200_launch_conv3x3: this build covers 64 -> 64 channels; got %d -> %d", cin, cout);
+        return set_error(OB200_ERR_UNSUPPORTED,
+                         "ob200_launch_conv3x3: covered shapes are 64 -> 64 and {64,128,192,256} -> {128,256}; got %d -> %d", cin, cout);
     if (board_size < 1 || conv_halo_rows(board_size) > kHaloMax)
         return set_error(OB200_ERR_UNSUPPORTED, "ob200_launch_conv3x3: board_size %d outside [1, %d]", board_size, kHaloMax - 2);
     const BoardGeom g = board_geom(board_size, B);
@@ -454,6 +465,7 @@ int ob200_launch_conv3x3(const void* in, const void* packed_w, const float* bias
 }
 
 int64_t ob200_packed_conv3x3_bytes(int32_t cin, int32_t cout) {
+    if (conv_wide_covers(cin, cout)) return (int64_t)conv_wide_packed_bytes(cin, cout, 9);
     if (cin != kC || cout != kC) return 0;
     return (int64_t)kWBytes;
 }
@@ -464,8 +476,9 @@ int64_t ob200_packed_conv3x3_bytes(int32_t cin, int32_t cout) {
 // layout of the tensor core, ready for a plain bulk copy.
 int ob200_pack_conv3x3_weights(const float* w_oihw, const float* scale, int32_t cout, int32_t cin_real,
                                int32_t cin, void* packed_out) {
+    if (conv_wide_covers(cin, cout)) return conv_wide_pack(w_oihw, scale, cout, cin_real, cin, 9, packed_out);
     if (!w_oihw || !packed_out || cout != kC || cin != kC || cin_real <= 0 || cin_real > cin)
-        return set_error(OB200_ERR_INVALID, "ob200_pack_conv3x3_weights: this build packs cout = 64, cin = 64 (cin_real <= 64); got cout %d, cin_real %d, cin %d",
+        return set_error(OB200_ERR_INVALID, "ob200_pack_conv3x3_weights: covered shapes are 64 -> 64 and {64,128,192,256} -> {128,256}; got cout %d, cin_real %d, cin %d",
                          cout, cin_real, cin);
     uint16_t* o = static_cast<uint16_t*>(packed_out);
     for (int tap = 0; tap < 9; ++tap)

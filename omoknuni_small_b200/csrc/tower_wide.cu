@@ -1,0 +1,470 @@
+// 3x3 (or 1x1) convolution for towers of 128 / 256 channels as an implicit GEMM
+// on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM), sm_100a.
+//
+// GEMM view of one work unit: M = 256 board positions (two 128-row MMA tiles),
+// N = 128 output channels, K = taps x C_in.  Activations are bf16 NHWC board
+// tensors (see omoknuni_b200.h) read in 64-channel slices: a slice of a position
+// is one 128-byte row, so a unit's positions plus the stencil halo arrive as two
+// 2-D TMA boxes (64 channels x 160 rows) in the tensor core's 128-byte-swizzled
+// K-major layout, and every tap is the same shared-memory tile read through a
+// matrix descriptor whose start is moved by (dy*(S+1)+dx) rows.  With 128 or 256
+// channels a layer's weights (288 KB / 1.1 MB) do not fit in shared memory: they
+// stream from L2 as 16 KB blocks (128 output channels x 64 input channels of one
+// tap, pre-swizzled on the host) through a 6-deep ring; each block feeds the MMAs
+// of both tiles of the unit, which halves the weight traffic per position, and
+// N = 128 keeps the shared-memory operand reads of an MMA (8 KB) within what the
+// tensor core consumes per instruction.
+//
+// Warp 0 loads activations, warp 2 loads weights, warp 1 issues the MMAs, warps
+// 4-11 (one group of 4 per tile of the unit) run the epilogue: TMEM -> registers,
+// + bias, + residual, ReLU, zero the padding positions, bf16, swizzled staging
+// tile, TMA store - 64 channels at a time.  Accumulators are double-buffered
+// (2 units x 2 tiles x 128 columns = all 512 TMEM columns), so the epilogue of a
+// unit overlaps the MMAs of the next.
+//
+// Every wait on an mbarrier is bounded; when one runs out the CTA raises the
+// device error word, leaves its loops, frees its TMEM and returns.
+#include "internal.h"
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cstring>
+
+namespace ob200 {
+namespace {
+
+constexpr int kTileM = 128;              // positions per MMA tile
+constexpr int kUnitTiles = 2;            // tiles per work unit
+constexpr int kN = 128;                  // output channels per work unit
+constexpr int kSlice = 64;               // input channels per K slice
+constexpr int kRowBytes = kSlice * 2;    // one position of one slice
+constexpr int kBoxRows = 160;            // rows per activation TMA box; two boxes per stage
+constexpr int kAStageBytes = 2 * kBoxRows * kRowBytes;   // 40,960: 256 positions + 2 x 32 halo rows
+constexpr int kAStages = 2;
+constexpr int kBStageBytes = kN * kRowBytes;              // 16,384
+constexpr int kBStages = 6;
+constexpr int kOutBytes = kTileM * kRowBytes;             // 16,384: 64 output channels of a tile
+constexpr int kEpiGroups = kUnitTiles;
+constexpr int kAccStages = 2;
+constexpr int kTmemCols = kAccStages * kUnitTiles * kN;   // 512
+constexpr int kThreads = 128 + 128 * kEpiGroups;          // warps 0-3 roles, 4-11 epilogue
+constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kAccStages;
+constexpr int kMaxCout = 256;
+constexpr int kSmemBytes = kAStages * kAStageBytes + kBStages * kBStageBytes + kEpiGroups * kOutBytes +
+                           kNumBars * 8 + kMaxCout * 4 + 16 + 1024;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+struct WideParams {
+    const uint8_t* w;         // packed weights: [n_half][k_slice][tap] blocks of 128 x 64, pre-swizzled
+    const float* bias;        // [cout]
+    const uint8_t* residual;  // board tensor of cout channels, or null
+    int* error;               // device error word (0 = fine)
+    int P;                    // real positions = B * slots
+    int num_tiles;            // 128-position tiles
+    int m_units;              // ceil(num_tiles / 2)
+    int n_halves;             // cout / 128
+    int k_slices;             // cin / 64
+    int taps;                 // 9 or 1
+    int cout;
+    int S, GP, slots;
+    int halo;                 // rows before the unit's first position in a stage
+    int relu;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if ((i & 255) == 255 && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle (rows of 128 bytes, 8-row groups
+// 1024 bytes apart, base offset 0: the swizzle is a function of the shared-memory address, so
+// a descriptor may start at any 128-byte row of a tile TMA wrote with the same swizzle).
+constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
+// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128, N = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kN >> 3) << 17) |
+                            ((uint32_t)(kTileM >> 4) << 24);
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "mov.b64 da, {%1, %3};\nmov.b64 db, {%2, %3};\n"
+        "setp.ne.b32 p, %5, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(kIdesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void group_bar(int id) {   // the 128 threads of one epilogue group
+    asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
+                 const WideParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // swizzled tiles need 1024-byte aligned bases
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* a_s = smem;
+    uint8_t* b_s = a_s + kAStages * kAStageBytes;
+    uint8_t* o_s = b_s + kBStages * kBStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(o_s + kEpiGroups * kOutBytes);
+    float* bias_s = reinterpret_cast<float*>(bars + kNumBars);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bias_s + kMaxCout);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar0 = smem_u32(bars);
+    auto afull_bar = [&](int s) { return bar0 + 8u * s; };
+    auto aempty_bar = [&](int s) { return bar0 + 8u * (kAStages + s); };
+    auto bfull_bar = [&](int s) { return bar0 + 8u * (2 * kAStages + s); };
+    auto bempty_bar = [&](int s) { return bar0 + 8u * (2 * kAStages + kBStages + s); };
+    auto accfull_bar = [&](int a) { return bar0 + 8u * (2 * kAStages + 2 * kBStages + a); };
+    auto accempty_bar = [&](int a) { return bar0 + 8u * (2 * kAStages + 2 * kBStages + kAccStages + a); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kAStages; ++s) { mbar_init(afull_bar(s), 1); mbar_init(aempty_bar(s), 1); }
+        for (int s = 0; s < kBStages; ++s) { mbar_init(bfull_bar(s), 1); mbar_init(bempty_bar(s), 1); }
+        for (int a = 0; a < kAccStages; ++a) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), 4 * kEpiGroups); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&in_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&out_map) : "memory");
+    }
+    for (int i = threadIdx.x; i < p.cout; i += kThreads) bias_s[i] = p.bias[i];
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    // Programmatic dependent launch: what reads or writes activations sits behind
+    // griddepcontrol.wait; the weight ring may fill while the previous layer drains.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const int num_units = p.m_units * p.n_halves;
+
+    if (warp == 0) {
+        // ---------------- activation producer ----------------
+        if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            int it = 0;
+            for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+                const int mu = u / p.n_halves;
+                const int row0 = OB200_GUARD + mu * (kUnitTiles * kTileM) - p.halo;
+                bool ok = true;
+                for (int kc = 0; kc < p.k_slices; ++kc, ++it) {
+                    const int s = it % kAStages;
+                    const uint32_t ph = (uint32_t)(it / kAStages) & 1u;
+                    if (!mbar_wait(aempty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(afull_bar(s), (uint32_t)kAStageBytes);
+                    const uint32_t dst = smem_u32(a_s + s * kAStageBytes);
+                    tma_load_2d(dst, &in_map, kc * kSlice, row0, afull_bar(s));
+                    tma_load_2d(dst + kBoxRows * kRowBytes, &in_map, kc * kSlice, row0 + kBoxRows, afull_bar(s));
+                }
+                if (!ok) { *abort_flag = 1; atomicExch(p.error, 1); break; }
+            }
+        }
+    } else if (warp == 2) {
+        // ---------------- weight producer ----------------
+        if (lane == 0) {
+            int jt = 0;
+            for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+                const int nh = u % p.n_halves;
+                const uint8_t* src = p.w + (size_t)nh * p.k_slices * p.taps * kBStageBytes;
+                const int blocks = p.k_slices * p.taps;
+                bool ok = true;
+                for (int j = 0; j < blocks; ++j, ++jt) {
+                    const int s = jt % kBStages;
+                    const uint32_t ph = (uint32_t)(jt / kBStages) & 1u;
+                    if (!mbar_wait(bempty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(bfull_bar(s), (uint32_t)kBStageBytes);
+                    bulk_g2s(smem_u32(b_s + s * kBStageBytes), src + (size_t)j * kBStageBytes, (uint32_t)kBStageBytes,
+                             bfull_bar(s));
+                }
+                if (!ok) { *abort_flag = 1; atomicExch(p.error, 4); break; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int tap_off[9];
+#pragma unroll
+            for (int tap = 0; tap < 9; ++tap) {
+                const int dy = p.taps == 9 ? tap / 3 - 1 : 0, dx = p.taps == 9 ? tap % 3 - 1 : 0;
+                tap_off[tap] = (p.halo + dy * p.GP + dx) * (kRowBytes >> 4);
+            }
+            int it = 0, jt = 0, ut = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; ok && u < num_units; u += gridDim.x, ++ut) {
+                const int mu = u / p.n_halves;
+                const int tiles_here = (p.num_tiles - mu * kUnitTiles) < kUnitTiles ? (p.num_tiles - mu * kUnitTiles) : kUnitTiles;
+                const int a = ut % kAccStages;
+                const uint32_t pa = (uint32_t)(ut / kAccStages) & 1u;
+                if (!mbar_wait(accempty_bar(a), pa ^ 1u, abort_flag)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_tmem = tmem_base + (uint32_t)(a * kUnitTiles * kN);
+                for (int kc = 0; ok && kc < p.k_slices; ++kc, ++it) {
+                    const int sa = it % kAStages;
+                    if (!mbar_wait(afull_bar(sa), (uint32_t)(it / kAStages) & 1u, abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_lo = desc_lo(smem_u32(a_s + sa * kAStageBytes));
+                    for (int tap = 0; tap < p.taps; ++tap, ++jt) {
+                        const int sb = jt % kBStages;
+                        if (!mbar_wait(bfull_bar(sb), (uint32_t)(jt / kBStages) & 1u, abort_flag)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t b_lo = desc_lo(smem_u32(b_s + sb * kBStageBytes));
+                        for (int t = 0; t < tiles_here; ++t) {
+                            const uint32_t at = a_lo + (uint32_t)(tap_off[tap] + t * kTileM * (kRowBytes >> 4));
+#pragma unroll
+                            for (int ks = 0; ks < kSlice / 16; ++ks)
+                                umma(d_tmem + (uint32_t)(t * kN), at + (uint32_t)(ks * 2), b_lo + (uint32_t)(ks * 2),
+                                     (kc | tap | ks) ? 1u : 0u);
+                        }
+                        umma_commit(bempty_bar(sb));    // weight block free once these MMAs have read it
+                    }
+                    if (ok) umma_commit(aempty_bar(sa));   // activation stage free
+                }
+                if (ok) umma_commit(accfull_bar(a));       // accumulators ready for the epilogue
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(p.error, 2); }
+        }
+    } else if (warp >= 4) {
+        // ---------------- epilogue: TMEM -> registers -> shared -> TMA store ----------------
+        // Group g (4 warps) owns tile g of every unit; a warp owns one TMEM lane quadrant
+        // (fixed by warp id % 4), a thread one position and all 128 output channels, 64 at a time.
+        const int ew = warp - 4;
+        const int group = ew >> 2;
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const bool leader = (ew & 3) == 0 && lane == 0;
+        const uint8_t* __restrict__ resid = p.residual;
+        uint8_t* stage_out = o_s + group * kOutBytes;
+        const uint32_t stage_out_u32 = smem_u32(stage_out);
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        int ut = 0;
+        for (int u = blockIdx.x; u < num_units; u += gridDim.x, ++ut) {
+            const int mu = u / p.n_halves, nh = u % p.n_halves;
+            const int a = ut % kAccStages;
+            const uint32_t pa = (uint32_t)(ut / kAccStages) & 1u;
+            const int tile = mu * kUnitTiles + group;
+            const bool active = tile < p.num_tiles;
+            const int pos = tile * kTileM + row;
+            bool valid = active && pos < p.P;
+            if (valid) {
+                const int rr = pos % p.slots;
+                valid = (rr / p.GP < p.S) && (rr % p.GP < p.S);
+            }
+            // the residual is fetched before the wait on the accumulator so that its latency
+            // hides behind the MMAs of the unit
+            uint4 rs[16];
+            if (resid != nullptr && valid) {
+                const uint4* src = reinterpret_cast<const uint4*>(resid + ((size_t)(OB200_GUARD + pos) * p.cout + (size_t)nh * kN) * 2);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) rs[c] = __ldg(src + c);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 16; ++c) rs[c] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (!mbar_wait(accfull_bar(a), pa, abort_flag)) {
+                *abort_flag = 1; atomicExch(p.error, 3); break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (!active) {   // a unit with one tile: nothing to read, release the accumulator
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(accempty_bar(a));
+                continue;
+            }
+            const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kUnitTiles * kN + group * kN);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t r[64];
+                tmem_ld32(t_acc + (uint32_t)(half * 64), r);
+                tmem_ld32(t_acc + (uint32_t)(half * 64 + 32), r + 32);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (half == 1) {
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(accempty_bar(a));
+                }
+                // the previous store of this group must have finished reading the staging tile
+                if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                group_bar(1 + 2 * group);
+                const float* bias_t = bias_s + nh * kN + half * 64;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    uint4 o = make_uint4(0u, 0u, 0u, 0u);
+                    if (valid) {
+                        const uint4 rv = rs[half * 8 + c];
+                        const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+                        uint32_t ow[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            // bf16 -> fp32 is a 16-bit shift
+                            float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bias_t[c * 8 + 2 * j] + __uint_as_float(rw[j] << 16);
+                            float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bias_t[c * 8 + 2 * j + 1] + __uint_as_float(rw[j] & 0xFFFF0000u);
+                            if (p.relu) { v0 = fmaxf(v0, 0.0f); v1 = fmaxf(v1, 0.0f); }
+                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
+                            ow[j] = *reinterpret_cast<const uint32_t*>(&h2);
+                        }
+                        o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                    }
+                    // 128-byte swizzle of the staging tile: 16-byte chunk k of row r sits at chunk k ^ (r % 8)
+                    *reinterpret_cast<uint4*>(stage_out + row * kRowBytes + ((c ^ (row & 7)) << 4)) = o;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                group_bar(2 + 2 * group);
+                if (leader) {
+                    tma_store_2d(&out_map, nh * kN + half * 64, OB200_GUARD + tile * kTileM, stage_out_u32);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+            }
+        }
+        if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+
+    // ---------------- teardown ----------------
+    if (*abort_flag) {
+        // give copies that may still be in flight time to land before the shared memory is released
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
+    }
+}
+
+inline uint16_t f32_to_bf16_rne(float f) {
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40);  // NaN
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+
+}  // namespace
+
+bool conv_wide_covers(int cin, int cout) {
+    return cin >= kSlice && cin <= 256 && cin % kSlice == 0 && (cout == 128 || cout == 256);
+}
+int conv_wide_box_rows() { return kBoxRows; }
+
+int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* packed_w,
+                          const float* bias, const void* residual, int B, int S, int cin, int cout, int taps, int relu,
+                          cudaStream_t st) {
+    if (!packed_w || !bias || B <= 0) return set_error(OB200_ERR_INVALID, "conv (wide): null pointer or empty batch");
+    if (!conv_wide_covers(cin, cout) || (taps != 9 && taps != 1))
+        return set_error(OB200_ERR_UNSUPPORTED, "conv (wide): %d -> %d channels with %d taps is not covered", cin, cout, taps);
+    if (S < 1 || conv_halo_rows(S) > OB200_GUARD)
+        return set_error(OB200_ERR_UNSUPPORTED, "conv (wide): board_size %d outside [1, %d]", S, OB200_GUARD - 2);
+    if (((uintptr_t)packed_w | (uintptr_t)residual) & 15)
+        return set_error(OB200_ERR_INVALID, "conv (wide): tensors must be 16-byte aligned");
+    if (int rc = require_device()) return rc;
+    static bool configured[64] = {false};
+    int dev = 0;
+    OB200_CUDA_OK(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        OB200_CUDA_OK(cudaFuncSetAttribute(conv_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        configured[dev] = true;
+    }
+    int sms = 0;
+    OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const BoardGeom g = board_geom(S, B);
+    WideParams p;
+    p.w = static_cast<const uint8_t*>(packed_w); p.bias = bias; p.residual = static_cast<const uint8_t*>(residual);
+    p.error = device_error_word();
+    if (!p.error) return set_error(OB200_ERR_CUDA, "conv (wide): cannot resolve the device error word");
+    p.P = (int)g.P; p.num_tiles = (int)(g.Ppad / kTileM); p.m_units = (p.num_tiles + kUnitTiles - 1) / kUnitTiles;
+    p.n_halves = cout / kN; p.k_slices = cin / kSlice; p.taps = taps; p.cout = cout;
+    p.S = S; p.GP = g.GP; p.slots = g.slots;
+    p.halo = taps == 9 ? conv_halo_rows(S) : 0; p.relu = relu;
+    const int units = p.m_units * p.n_halves;
+    const int grid = units < sms ? units : sms;   // one persistent CTA per SM
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv_wide_kernel, *reinterpret_cast<const CUtensorMap*>(&in_map),
+                                     *reinterpret_cast<const CUtensorMap*>(&out_map), p));
+    OB200_LAUNCHED("conv_wide_kernel");
+    return OB200_OK;
+}
+
+size_t conv_wide_packed_bytes(int cin, int cout, int taps) { return (size_t)taps * cin * cout * 2; }
+
+// Packed image: blocks [n_half][k_slice][tap] of 128 output channels x 64 input channels, bf16,
+// one 128-byte row per output channel, its 16-byte chunks (8 input channels) permuted by the
+// 128-byte swizzle (chunk j of row r stored at chunk j ^ (r % 8)): the K-major shared-memory
+// operand layout of the tensor core, ready for plain bulk copies in the order the kernel
+// consumes them.  w: [cout][cin_real][taps] fp32 (OIHW), scale: per output channel or null.
+int conv_wide_pack(const float* w, const float* scale, int cout, int cin_real, int cin, int taps, void* packed_out) {
+    if (!w || !packed_out || !conv_wide_covers(cin, cout) || cin_real <= 0 || cin_real > cin || (taps != 9 && taps != 1))
+        return set_error(OB200_ERR_INVALID, "conv (wide) pack: cout %d, cin_real %d, cin %d, taps %d not covered", cout,
+                         cin_real, cin, taps);
+    uint16_t* o = static_cast<uint16_t*>(packed_out);
+    const int KS = cin / kSlice;
+    for (int co = 0; co < cout; ++co)
+        for (int ci = 0; ci < cin; ++ci)
+            for (int tap = 0; tap < taps; ++tap) {
+                float v = 0.0f;
+                if (ci < cin_real) v = w[((size_t)co * cin_real + ci) * taps + tap] * (scale ? scale[co] : 1.0f);
+                const int nh = co / kN, col = co % kN, kc = ci / kSlice, cil = ci % kSlice;
+                const size_t block = ((size_t)nh * KS + kc) * taps + tap;
+                const size_t byte = block * kBStageBytes + (size_t)col * kRowBytes + ((((cil >> 3) ^ (col & 7))) << 4) + (cil & 7) * 2;
+                o[byte / 2] = f32_to_bf16_rne(v);
+            }
+    return OB200_OK;
+}
+
+}  // namespace ob200

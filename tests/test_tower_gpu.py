@@ -29,33 +29,33 @@ def bf16_round(a):
     return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
 
 
-def conv_case(api, B, S, cin_real, cin, residual, relu, seed):
+def conv_case(api, B, S, cin_real, cin, residual, relu, seed, cout=64):
     import torch
     import torch.nn.functional as F
     rng = np.random.default_rng(seed)
     x = bf16_round(rng.normal(0, 1, (B, cin_real, S, S)).astype(np.float32))
-    w = bf16_round(rng.normal(0, 0.1, (64, cin_real, 3, 3)).astype(np.float32))
-    bias = rng.normal(0, 0.5, 64).astype(np.float32)
-    res = bf16_round(rng.normal(0, 1, (B, 64, S, S)).astype(np.float32)) if residual else None
+    w = bf16_round(rng.normal(0, 0.1, (cout, cin_real, 3, 3)).astype(np.float32))
+    bias = rng.normal(0, 0.5, cout).astype(np.float32)
+    res = bf16_round(rng.normal(0, 1, (B, cout, S, S)).astype(np.float32)) if residual else None
     y = F.conv2d(torch.from_numpy(x), torch.from_numpy(w), padding=1).numpy() + bias[None, :, None, None]
     if residual:
         y = y + res
     if relu:
         y = np.maximum(y, 0)
     xd = torch.from_numpy(api.planes_to_board_tensor_host(x, cin).view(np.int16)).cuda()
-    rd = torch.from_numpy(api.planes_to_board_tensor_host(res, 64).view(np.int16)).cuda() if residual else None
+    rd = torch.from_numpy(api.planes_to_board_tensor_host(res, cout).view(np.int16)).cuda() if residual else None
     wd = torch.from_numpy(api.pack_conv3x3(w, None, cin).view(np.int16)).cuda()
     bd = torch.from_numpy(bias).cuda()
     # pre-fill the output with a pattern: the kernel must overwrite padding positions with zero
-    out = torch.full((int(api.lib().ob200_board_tensor_bytes(S, B, 64)) // 2,), 0x3F80, dtype=torch.int16, device="cuda")
+    out = torch.full((int(api.lib().ob200_board_tensor_bytes(S, B, cout)) // 2,), 0x3F80, dtype=torch.int16, device="cuda")
     PT = api.board_positions(S, B)
-    o2 = out.view(PT, 64)
+    o2 = out.view(PT, cout)
     o2[:api.GUARD] = 0
     o2[PT - api.GUARD:] = 0
-    api.conv3x3(xd, wd, bd, rd, B, S, cin, 64, relu, out=out)
+    api.conv3x3(xd, wd, bd, rd, B, S, cin, cout, relu, out=out)
     torch.cuda.synchronize()
     assert api.device_error_code() == 0
-    got, pad_zero = api.board_tensor_to_planes(out.cpu().numpy().view(np.uint16), S, B, 64)
+    got, pad_zero = api.board_tensor_to_planes(out.cpu().numpy().view(np.uint16), S, B, cout)
     return got, y, pad_zero
 
 
@@ -73,6 +73,26 @@ def test_conv3x3_layer(api, B, S, cin_real, cin, residual, relu):
     got, want, pad_zero = conv_case(api, B, S, cin_real, cin, residual, relu, seed=B * 100 + S)
     err = np.abs(got - want)
     tol = np.abs(want) * 2.0 ** -8 + 1e-5
+    bad = np.argwhere(err > tol)
+    assert bad.size == 0, f"{len(bad)} of {err.size} elements off; first {bad[:5].tolist()}; max err {err.max():.4g}"
+    assert pad_zero, "padding / guard positions of the output are not zero"
+
+
+@pytest.mark.parametrize("B,S,cin_real,cin,cout,residual,relu", [
+    (1, 15, 128, 128, 128, False, False),
+    (2, 19, 128, 128, 128, True, True),      # Go tower layer
+    (3, 19, 17, 64, 128, False, True),       # Go stem: 17 planes in a 64-channel tensor
+    (40, 19, 128, 128, 128, True, True),     # 125 tiles: the last work unit holds a single tile
+    (5, 8, 119, 128, 256, False, True),      # chess stem: 119 planes in a 128-channel tensor
+    (6, 8, 256, 256, 256, True, True),       # chess tower layer: two 128-channel halves
+    (700, 8, 256, 256, 256, True, True),     # 444 work units: every CTA loops, all rings wrap
+    (300, 19, 128, 128, 128, True, True),    # 938 tiles
+])
+def test_conv3x3_layer_wide(api, B, S, cin_real, cin, cout, residual, relu):
+    """Towers of 128 / 256 channels (streamed-weight kernel)."""
+    got, want, pad_zero = conv_case(api, B, S, cin_real, cin, residual, relu, seed=B * 100 + S + cout, cout=cout)
+    err = np.abs(got - want)
+    tol = np.abs(want) * 2.0 ** -8 + 1e-4
     bad = np.argwhere(err > tol)
     assert bad.size == 0, f"{len(bad)} of {err.size} elements off; first {bad[:5].tolist()}; max err {err.max():.4g}"
     assert pad_zero, "padding / guard positions of the output are not zero"
