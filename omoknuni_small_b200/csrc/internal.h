@@ -14,18 +14,19 @@ int launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C
 struct alignas(64) BoardTensorMap { unsigned char opaque[128]; };
 int make_board_tensor_map(const void* base, long long rows, int box_rows, BoardTensorMap* out, int channels = 64);
 int conv_halo_rows(int S);
-int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* packed_w,
-                        const float* bias, const void* residual, int B, int S, int relu, cudaStream_t st);
+// res_map: the residual tensor through a 128-row-box map (a store map of that buffer), or null
+int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const BoardTensorMap* res_map,
+                        const void* packed_w, const float* bias, int B, int S, int relu, cudaStream_t st);
 int* device_error_word();
 // Towers of 128 / 256 channels (tower_wide.cu): cin a multiple of 64 up to 256, cout 128 or 256,
 // taps 9 (3x3) or 1 (1x1).  in_map: boxes of conv_wide_box_rows() rows over a cin-channel tensor;
-// out_map: boxes of 128 rows over a cout-channel tensor.
+// out_map / res_map (residual, or null): boxes of 128 rows over a cout-channel tensor.
 bool conv_wide_covers(int cin, int cout);
 int conv_wide_box_rows();
 size_t conv_wide_packed_bytes(int cin, int cout, int taps);
 int conv_wide_pack(const float* w, const float* scale, int cout, int cin_real, int cin, int taps, void* packed_out);
-int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* packed_w,
-                          const float* bias, const void* residual, int B, int S, int cin, int cout, int taps, int relu,
+int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const BoardTensorMap* res_map,
+                          const void* packed_w, const float* bias, int B, int S, int cin, int cout, int taps, int relu,
                           cudaStream_t st);
 
 int launch_head_conv(const void* tower, const float* w, const float* bias, int HC, int pc, float* hp,

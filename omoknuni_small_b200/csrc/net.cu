@@ -257,10 +257,10 @@ int forward_device(ob200_net* n, const BoardTensorMap& in_map, int B, float* pol
     const ob200_net_config& c = n->cfg;
     const int S = c.board_size;
     int x = 0, y = 1, z = 2;
-    if (int rc = launch_conv3x3_maps(in_map, n->act_store[x], n->conv_w[0], n->conv_b[0], nullptr, B, S, 1, st)) return rc;
+    if (int rc = launch_conv3x3_maps(in_map, n->act_store[x], nullptr, n->conv_w[0], n->conv_b[0], B, S, 1, st)) return rc;
     for (int i = 0; i < c.blocks; ++i) {
-        if (int rc = launch_conv3x3_maps(n->act_load[x], n->act_store[y], n->conv_w[1 + 2 * i], n->conv_b[1 + 2 * i], nullptr, B, S, 1, st)) return rc;
-        if (int rc = launch_conv3x3_maps(n->act_load[y], n->act_store[z], n->conv_w[2 + 2 * i], n->conv_b[2 + 2 * i], n->act[x], B, S, 1, st)) return rc;
+        if (int rc = launch_conv3x3_maps(n->act_load[x], n->act_store[y], nullptr, n->conv_w[1 + 2 * i], n->conv_b[1 + 2 * i], B, S, 1, st)) return rc;
+        if (int rc = launch_conv3x3_maps(n->act_load[y], n->act_store[z], &n->act_store[x], n->conv_w[2 + 2 * i], n->conv_b[2 + 2 * i], B, S, 1, st)) return rc;
         std::swap(x, z);
     }
     n->tower_out = n->act[x];

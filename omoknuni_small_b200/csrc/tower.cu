@@ -17,8 +17,9 @@
 // Weights (BatchNorm folded, bf16, pre-swizzled on the host) stay resident in
 // shared memory for the whole launch.  Warp 0 produces (TMA loads), warp 1
 // issues the MMAs, warps 2-9 (two groups of 4 warps on alternate tiles) run the
-// epilogue: TMEM -> registers, + bias, + residual, ReLU, zero the padding
-// positions, bf16, swizzled staging tile in shared memory, one TMA store.
+// epilogue: TMEM -> registers, + bias, + residual (brought into the staging tile
+// by TMA), ReLU, zero the padding positions, bf16, swizzled staging tile in
+// shared memory, one TMA store.
 //
 // Every wait on an mbarrier is bounded; when one runs out the CTA raises the
 // device error word, leaves its loops, frees its TMEM and returns.
@@ -46,14 +47,14 @@ constexpr int kEpiGroups = 2;
 constexpr int kEpiWarps = 4;             // per group: 4 TMEM lane quadrants x (kEpiWarps / 4) slices of the 64 channels
 constexpr int kChPerThread = kC / (kEpiWarps / 4);   // channels one epilogue thread handles
 constexpr int kThreads = 64 + 32 * kEpiWarps * kEpiGroups;
-constexpr int kNumBars = 2 * kStages + 2 * kAccStages + 1;
+constexpr int kNumBars = 2 * kStages + 2 * kAccStages + 1 + kEpiGroups;
 constexpr int kSmemBytes = kWBytes + kStages * kStageBytes + kEpiGroups * kOutBytes + kNumBars * 8 + kC * 4 + 16 + 1024;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct ConvParams {
     const uint8_t* w;         // packed, pre-swizzled weights
     const float* bias;        // [64]
-    const uint8_t* residual;  // board tensor or null
+    int has_residual;         // the residual tensor map is live
     int* error;               // device error word (0 = fine)
     int P;                    // real positions = B * slots
     int num_tiles;
@@ -144,7 +145,7 @@ __device__ __forceinline__ void group_bar(int id) {   // the threads of one epil
 
 __global__ void __launch_bounds__(kThreads, 1)
 conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
-               const ConvParams p) {
+               const __grid_constant__ CUtensorMap res_map, const ConvParams p) {
     extern __shared__ uint8_t smem_raw[];
     // swizzled tiles need 1024-byte aligned bases
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -163,15 +164,18 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
     auto accfull_bar = [&](int a) { return bar0 + 8u * (2 * kStages + a); };
     auto accempty_bar = [&](int a) { return bar0 + 8u * (2 * kStages + kAccStages + a); };
     const uint32_t w_bar = bar0 + 8u * (2 * kStages + 2 * kAccStages);
+    auto res_bar = [&](int g) { return bar0 + 8u * (2 * kStages + 2 * kAccStages + 1 + g); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < kAccStages; ++a) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), kEpiWarps); }
         mbar_init(w_bar, 1);
+        for (int g = 0; g < kEpiGroups; ++g) mbar_init(res_bar(g), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&in_map) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&out_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&res_map) : "memory");
     }
     if (threadIdx.x < kC) bias_s[threadIdx.x] = p.bias[threadIdx.x];
     if (warp == 1) {
@@ -245,8 +249,9 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
         // ---------------- epilogue: TMEM -> registers -> shared -> TMA store ----------------
         // Groups of kEpiWarps warps take alternate tiles.  Within a group a warp owns one TMEM
         // lane quadrant (32 positions; fixed by warp id % 4) and one slice of the 64 channels.
-        // The residual is fetched before the wait on the accumulator so that its latency
-        // hides behind the MMAs of the tile.
+        // With a residual, TMA loads the residual's tile into the group's staging tile while the
+        // tile's MMAs run; a thread then reads its own row, adds, and writes the result back in
+        // place before the TMA store.
         const int ew = warp - 2;
         const int group = ew / kEpiWarps;
         const int slice = (ew % kEpiWarps) >> 2;     // channels [kChPerThread*slice, +kChPerThread)
@@ -254,10 +259,11 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
         const int row = q * 32 + lane;
         const bool leader = (ew % kEpiWarps) == 0 && lane == 0;
         constexpr int kChunks = kChPerThread / 8;    // 16-byte chunks per thread
-        const uint8_t* __restrict__ resid = p.residual;
+        const bool has_res = p.has_residual != 0;
         uint8_t* stage_out = o_s + group * kOutBytes;
         const uint32_t stage_out_u32 = smem_u32(stage_out);
         const float* bias_t = bias_s + slice * kChPerThread;
+        uint32_t res_phase = 0;
         asm volatile("griddepcontrol.wait;" ::: "memory");
         int it = group;
         for (int tile = blockIdx.x + group * gridDim.x; tile < p.num_tiles; tile += kEpiGroups * gridDim.x, it += kEpiGroups) {
@@ -269,14 +275,13 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
                 const int rr = pos % p.slots;
                 valid = (rr / p.GP < p.S) && (rr % p.GP < p.S);
             }
-            uint4 rs[kChunks];
-            if (resid != nullptr && valid) {
-                const uint4* src = reinterpret_cast<const uint4*>(resid + (size_t)(OB200_GUARD + pos) * kRowBytes) + slice * kChunks;
-#pragma unroll
-                for (int c = 0; c < kChunks; ++c) rs[c] = __ldg(src + c);
-            } else {
-#pragma unroll
-                for (int c = 0; c < kChunks; ++c) rs[c] = make_uint4(0u, 0u, 0u, 0u);
+            if (leader) {
+                // the previous store of this group must have finished reading the staging tile
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                if (has_res) {
+                    mbar_arrive_expect_tx(res_bar(group), (uint32_t)kOutBytes);
+                    tma_load_2d(stage_out_u32, &res_map, 0, OB200_GUARD + tile * kTileM, res_bar(group));
+                }
             }
             if (!mbar_wait(accfull_bar(a), pa, abort_flag)) {
                 *abort_flag = 1; atomicExch(p.error, 3); break;
@@ -291,14 +296,22 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(accempty_bar(a));
 
-            // the previous store of this group must have finished reading the staging tile
-            if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-            group_bar(1 + 2 * group);
+            if (has_res) {
+                if (!mbar_wait(res_bar(group), res_phase, abort_flag)) {
+                    *abort_flag = 1; atomicExch(p.error, 5); break;
+                }
+                res_phase ^= 1u;
+            } else {
+                group_bar(1 + 2 * group);   // after the leader's wait above: the staging tile is free
+            }
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) {
+                // 128-byte swizzle of the staging tile: 16-byte chunk k of row r sits at chunk k ^ (r % 8)
+                uint4* slot = reinterpret_cast<uint4*>(stage_out + row * kRowBytes + (((slice * kChunks + c) ^ (row & 7)) << 4));
                 uint4 o = make_uint4(0u, 0u, 0u, 0u);
                 if (valid) {
-                    const uint32_t rw[4] = {rs[c].x, rs[c].y, rs[c].z, rs[c].w};
+                    const uint4 rv = has_res ? *slot : make_uint4(0u, 0u, 0u, 0u);
+                    const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
                     uint32_t ow[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -311,8 +324,7 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
                     }
                     o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                 }
-                // 128-byte swizzle of the staging tile: 16-byte chunk k of row r sits at chunk k ^ (r % 8)
-                *reinterpret_cast<uint4*>(stage_out + row * kRowBytes + (((slice * kChunks + c) ^ (row & 7)) << 4)) = o;
+                *slot = o;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             group_bar(2 + 2 * group);
@@ -396,13 +408,12 @@ int make_board_tensor_map(const void* base, long long rows, int box_rows, BoardT
 
 int conv_halo_rows(int S) { return S + 2; }   // |dy*(S+1)+dx| <= S+2 rows before / after a tile
 
-int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* packed_w,
-                        const float* bias, const void* residual, int B, int S, int relu, cudaStream_t st) {
+int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const BoardTensorMap* res_map,
+                        const void* packed_w, const float* bias, int B, int S, int relu, cudaStream_t st) {
     if (!packed_w || !bias || B <= 0) return set_error(OB200_ERR_INVALID, "conv3x3: null pointer or empty batch");
     if (S < 1 || conv_halo_rows(S) > kHaloMax)
         return set_error(OB200_ERR_UNSUPPORTED, "conv3x3: board_size %d outside [1, %d]", S, kHaloMax - 2);
-    if (((uintptr_t)packed_w | (uintptr_t)residual) & 15)
-        return set_error(OB200_ERR_INVALID, "conv3x3: tensors must be 16-byte aligned");
+    if ((uintptr_t)packed_w & 15) return set_error(OB200_ERR_INVALID, "conv3x3: weights must be 16-byte aligned");
     if (int rc = require_device()) return rc;
     static bool configured[64] = {false};
     int dev = 0;
@@ -415,7 +426,7 @@ int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_
     OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const BoardGeom g = board_geom(S, B);
     ConvParams p;
-    p.w = static_cast<const uint8_t*>(packed_w); p.bias = bias; p.residual = static_cast<const uint8_t*>(residual);
+    p.w = static_cast<const uint8_t*>(packed_w); p.bias = bias; p.has_residual = res_map != nullptr;
     p.error = device_error_word();
     if (!p.error) return set_error(OB200_ERR_CUDA, "conv3x3: cannot resolve the device error word");
     p.P = (int)g.P; p.num_tiles = (int)(g.Ppad / kTileM); p.S = S; p.GP = g.GP; p.slots = g.slots;
@@ -428,7 +439,8 @@ int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv3x3_kernel, *reinterpret_cast<const CUtensorMap*>(&in_map),
-                                     *reinterpret_cast<const CUtensorMap*>(&out_map), p));
+                                     *reinterpret_cast<const CUtensorMap*>(&out_map),
+                                     *reinterpret_cast<const CUtensorMap*>(res_map ? res_map : &out_map), p));
     OB200_LAUNCHED("conv3x3_kernel");
     return OB200_OK;
 }
@@ -450,7 +462,11 @@ int ob200_launch_conv3x3(const void* in, const void* packed_w, const float* bias
         BoardTensorMap wim, wom;
         if (int rc = make_board_tensor_map(in, gw.PT, conv_wide_box_rows(), &wim, cin)) return rc;
         if (int rc = make_board_tensor_map(out, gw.PT, kTileM, &wom, cout)) return rc;
-        return launch_conv_wide_maps(wim, wom, packed_w, bias, residual, B, board_size, cin, cout, 9, relu, as_stream(stream));
+        BoardTensorMap wrm;
+        if (residual)
+            if (int rc = make_board_tensor_map(residual, gw.PT, kTileM, &wrm, cout)) return rc;
+        return launch_conv_wide_maps(wim, wom, residual ? &wrm : nullptr, packed_w, bias, B, board_size, cin, cout, 9, relu,
+                                     as_stream(stream));
     }
     if (cin != kC || cout != kC)
         return set_error(OB200_ERR_UNSUPPORTED,
@@ -461,7 +477,10 @@ int ob200_launch_conv3x3(const void* in, const void* packed_w, const float* bias
     BoardTensorMap im, om;
     if (int rc = make_board_tensor_map(in, g.PT, kTileM + 2 * conv_halo_rows(board_size), &im)) return rc;
     if (int rc = make_board_tensor_map(out, g.PT, kTileM, &om)) return rc;
-    return launch_conv3x3_maps(im, om, packed_w, bias, residual, B, board_size, relu, as_stream(stream));
+    BoardTensorMap rm;
+    if (residual)
+        if (int rc = make_board_tensor_map(residual, g.PT, kTileM, &rm)) return rc;
+    return launch_conv3x3_maps(im, om, residual ? &rm : nullptr, packed_w, bias, B, board_size, relu, as_stream(stream));
 }
 
 int64_t ob200_packed_conv3x3_bytes(int32_t cin, int32_t cout) {

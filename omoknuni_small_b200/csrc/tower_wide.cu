@@ -10,17 +10,17 @@
 // matrix descriptor whose start is moved by (dy*(S+1)+dx) rows.  With 128 or 256
 // channels a layer's weights (288 KB / 1.1 MB) do not fit in shared memory: they
 // stream from L2 as 16 KB blocks (128 output channels x 64 input channels of one
-// tap, pre-swizzled on the host) through a 6-deep ring; each block feeds the MMAs
+// tap, pre-swizzled on the host) through a 4-deep ring; each block feeds the MMAs
 // of both tiles of the unit, which halves the weight traffic per position, and
 // N = 128 keeps the shared-memory operand reads of an MMA (8 KB) within what the
 // tensor core consumes per instruction.
 //
 // Warp 0 loads activations, warp 2 loads weights, warp 1 issues the MMAs, warps
 // 4-11 (one group of 4 per tile of the unit) run the epilogue: TMEM -> registers,
-// + bias, + residual, ReLU, zero the padding positions, bf16, swizzled staging
-// tile, TMA store - 64 channels at a time.  Accumulators are double-buffered
-// (2 units x 2 tiles x 128 columns = all 512 TMEM columns), so the epilogue of a
-// unit overlaps the MMAs of the next.
+// + bias, + residual (brought into the staging tile by TMA), ReLU, zero the
+// padding positions, bf16, swizzled staging tile, TMA store - 64 channels at a
+// time.  Accumulators are double-buffered (2 units x 2 tiles x 128 columns = all
+// 512 TMEM columns), so the epilogue of a unit overlaps the MMAs of the next.
 //
 // Every wait on an mbarrier is bounded; when one runs out the CTA raises the
 // device error word, leaves its loops, frees its TMEM and returns.
@@ -41,22 +41,22 @@ constexpr int kBoxRows = 160;            // rows per activation TMA box; two box
 constexpr int kAStageBytes = 2 * kBoxRows * kRowBytes;   // 40,960: 256 positions + 2 x 32 halo rows
 constexpr int kAStages = 2;
 constexpr int kBStageBytes = kN * kRowBytes;              // 16,384
-constexpr int kBStages = 6;
+constexpr int kBStages = 4;
 constexpr int kOutBytes = kTileM * kRowBytes;             // 16,384: 64 output channels of a tile
 constexpr int kEpiGroups = kUnitTiles;
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = kAccStages * kUnitTiles * kN;   // 512
 constexpr int kThreads = 128 + 128 * kEpiGroups;          // warps 0-3 roles, 4-11 epilogue
-constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kAccStages;
+constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kAccStages + kEpiGroups;
 constexpr int kMaxCout = 256;
-constexpr int kSmemBytes = kAStages * kAStageBytes + kBStages * kBStageBytes + kEpiGroups * kOutBytes +
+constexpr int kSmemBytes = kAStages * kAStageBytes + kBStages * kBStageBytes + kEpiGroups * 2 * kOutBytes +
                            kNumBars * 8 + kMaxCout * 4 + 16 + 1024;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct WideParams {
     const uint8_t* w;         // packed weights: [n_half][k_slice][tap] blocks of 128 x 64, pre-swizzled
     const float* bias;        // [cout]
-    const uint8_t* residual;  // board tensor of cout channels, or null
+    int has_residual;         // the residual tensor map is live
     int* error;               // device error word (0 = fine)
     int P;                    // real positions = B * slots
     int num_tiles;            // 128-position tiles
@@ -145,14 +145,14 @@ __device__ __forceinline__ void group_bar(int id) {   // the 128 threads of one 
 
 __global__ void __launch_bounds__(kThreads, 1)
 conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
-                 const WideParams p) {
+                 const __grid_constant__ CUtensorMap res_map, const WideParams p) {
     extern __shared__ uint8_t smem_raw[];
     // swizzled tiles need 1024-byte aligned bases
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* a_s = smem;
     uint8_t* b_s = a_s + kAStages * kAStageBytes;
     uint8_t* o_s = b_s + kBStages * kBStageBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(o_s + kEpiGroups * kOutBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(o_s + kEpiGroups * 2 * kOutBytes);
     float* bias_s = reinterpret_cast<float*>(bars + kNumBars);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bias_s + kMaxCout);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -165,15 +165,18 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
     auto bempty_bar = [&](int s) { return bar0 + 8u * (2 * kAStages + kBStages + s); };
     auto accfull_bar = [&](int a) { return bar0 + 8u * (2 * kAStages + 2 * kBStages + a); };
     auto accempty_bar = [&](int a) { return bar0 + 8u * (2 * kAStages + 2 * kBStages + kAccStages + a); };
+    auto res_bar = [&](int g) { return bar0 + 8u * (2 * kAStages + 2 * kBStages + 2 * kAccStages + g); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kAStages; ++s) { mbar_init(afull_bar(s), 1); mbar_init(aempty_bar(s), 1); }
         for (int s = 0; s < kBStages; ++s) { mbar_init(bfull_bar(s), 1); mbar_init(bempty_bar(s), 1); }
         for (int a = 0; a < kAccStages; ++a) { mbar_init(accfull_bar(a), 1); mbar_init(accempty_bar(a), 4 * kEpiGroups); }
+        for (int g = 0; g < kEpiGroups; ++g) mbar_init(res_bar(g), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&in_map) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&out_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&res_map) : "memory");
     }
     for (int i = threadIdx.x; i < p.cout; i += kThreads) bias_s[i] = p.bias[i];
     if (warp == 1) {
@@ -280,14 +283,18 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
         // ---------------- epilogue: TMEM -> registers -> shared -> TMA store ----------------
         // Group g (4 warps) owns tile g of every unit; a warp owns one TMEM lane quadrant
         // (fixed by warp id % 4), a thread one position and all 128 output channels, 64 at a time.
+        // The group has one staging tile per 64-channel half.  With a residual, TMA loads the
+        // residual's two halves into the staging tiles while the unit's MMAs run; a thread then
+        // reads its own row, adds, and writes the result back in place before the TMA store.
         const int ew = warp - 4;
         const int group = ew >> 2;
         const int q = warp & 3;
         const int row = q * 32 + lane;
         const bool leader = (ew & 3) == 0 && lane == 0;
-        const uint8_t* __restrict__ resid = p.residual;
-        uint8_t* stage_out = o_s + group * kOutBytes;
+        const bool has_res = p.has_residual != 0;
+        uint8_t* stage_out = o_s + group * 2 * kOutBytes;
         const uint32_t stage_out_u32 = smem_u32(stage_out);
+        uint32_t res_phase = 0;
         asm volatile("griddepcontrol.wait;" ::: "memory");
         int ut = 0;
         for (int u = blockIdx.x; u < num_units; u += gridDim.x, ++ut) {
@@ -302,16 +309,14 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                 const int rr = pos % p.slots;
                 valid = (rr / p.GP < p.S) && (rr % p.GP < p.S);
             }
-            // the residual is fetched before the wait on the accumulator so that its latency
-            // hides behind the MMAs of the unit
-            uint4 rs[16];
-            if (resid != nullptr && valid) {
-                const uint4* src = reinterpret_cast<const uint4*>(resid + ((size_t)(OB200_GUARD + pos) * p.cout + (size_t)nh * kN) * 2);
-#pragma unroll
-                for (int c = 0; c < 16; ++c) rs[c] = __ldg(src + c);
-            } else {
-#pragma unroll
-                for (int c = 0; c < 16; ++c) rs[c] = make_uint4(0u, 0u, 0u, 0u);
+            if (active && leader) {
+                // the previous stores of this group must have finished reading the staging tiles
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                if (has_res) {
+                    mbar_arrive_expect_tx(res_bar(group), (uint32_t)(2 * kOutBytes));
+                    tma_load_2d(stage_out_u32, &res_map, nh * kN, OB200_GUARD + tile * kTileM, res_bar(group));
+                    tma_load_2d(stage_out_u32 + kOutBytes, &res_map, nh * kN + 64, OB200_GUARD + tile * kTileM, res_bar(group));
+                }
             }
             if (!mbar_wait(accfull_bar(a), pa, abort_flag)) {
                 *abort_flag = 1; atomicExch(p.error, 3); break;
@@ -322,6 +327,14 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                 __syncwarp();
                 if (lane == 0) mbar_arrive(accempty_bar(a));
                 continue;
+            }
+            if (has_res) {
+                if (!mbar_wait(res_bar(group), res_phase, abort_flag)) {
+                    *abort_flag = 1; atomicExch(p.error, 5); break;
+                }
+                res_phase ^= 1u;
+            } else {
+                group_bar(1 + 2 * group);   // after the leader's wait above: staging tiles are free
             }
             const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kUnitTiles * kN + group * kN);
 #pragma unroll
@@ -335,15 +348,15 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                     __syncwarp();
                     if (lane == 0) mbar_arrive(accempty_bar(a));
                 }
-                // the previous store of this group must have finished reading the staging tile
-                if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                group_bar(1 + 2 * group);
                 const float* bias_t = bias_s + nh * kN + half * 64;
+                uint8_t* my_row = stage_out + half * kOutBytes + row * kRowBytes;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
+                    // 128-byte swizzle of the staging tile: 16-byte chunk k of row r sits at chunk k ^ (r % 8)
+                    uint4* slot = reinterpret_cast<uint4*>(my_row + ((c ^ (row & 7)) << 4));
                     uint4 o = make_uint4(0u, 0u, 0u, 0u);
                     if (valid) {
-                        const uint4 rv = rs[half * 8 + c];
+                        const uint4 rv = has_res ? *slot : make_uint4(0u, 0u, 0u, 0u);
                         const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
                         uint32_t ow[4];
 #pragma unroll
@@ -357,13 +370,12 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                         }
                         o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                     }
-                    // 128-byte swizzle of the staging tile: 16-byte chunk k of row r sits at chunk k ^ (r % 8)
-                    *reinterpret_cast<uint4*>(stage_out + row * kRowBytes + ((c ^ (row & 7)) << 4)) = o;
+                    *slot = o;
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 group_bar(2 + 2 * group);
                 if (leader) {
-                    tma_store_2d(&out_map, nh * kN + half * 64, OB200_GUARD + tile * kTileM, stage_out_u32);
+                    tma_store_2d(&out_map, nh * kN + half * 64, OB200_GUARD + tile * kTileM, stage_out_u32 + half * kOutBytes);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
@@ -398,16 +410,15 @@ bool conv_wide_covers(int cin, int cout) {
 }
 int conv_wide_box_rows() { return kBoxRows; }
 
-int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* packed_w,
-                          const float* bias, const void* residual, int B, int S, int cin, int cout, int taps, int relu,
+int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const BoardTensorMap* res_map,
+                          const void* packed_w, const float* bias, int B, int S, int cin, int cout, int taps, int relu,
                           cudaStream_t st) {
     if (!packed_w || !bias || B <= 0) return set_error(OB200_ERR_INVALID, "conv (wide): null pointer or empty batch");
     if (!conv_wide_covers(cin, cout) || (taps != 9 && taps != 1))
         return set_error(OB200_ERR_UNSUPPORTED, "conv (wide): %d -> %d channels with %d taps is not covered", cin, cout, taps);
     if (S < 1 || conv_halo_rows(S) > OB200_GUARD)
         return set_error(OB200_ERR_UNSUPPORTED, "conv (wide): board_size %d outside [1, %d]", S, OB200_GUARD - 2);
-    if (((uintptr_t)packed_w | (uintptr_t)residual) & 15)
-        return set_error(OB200_ERR_INVALID, "conv (wide): tensors must be 16-byte aligned");
+    if ((uintptr_t)packed_w & 15) return set_error(OB200_ERR_INVALID, "conv (wide): weights must be 16-byte aligned");
     if (int rc = require_device()) return rc;
     static bool configured[64] = {false};
     int dev = 0;
@@ -420,7 +431,7 @@ int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& ou
     OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const BoardGeom g = board_geom(S, B);
     WideParams p;
-    p.w = static_cast<const uint8_t*>(packed_w); p.bias = bias; p.residual = static_cast<const uint8_t*>(residual);
+    p.w = static_cast<const uint8_t*>(packed_w); p.bias = bias; p.has_residual = res_map != nullptr;
     p.error = device_error_word();
     if (!p.error) return set_error(OB200_ERR_CUDA, "conv (wide): cannot resolve the device error word");
     p.P = (int)g.P; p.num_tiles = (int)(g.Ppad / kTileM); p.m_units = (p.num_tiles + kUnitTiles - 1) / kUnitTiles;
@@ -436,7 +447,8 @@ int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& ou
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv_wide_kernel, *reinterpret_cast<const CUtensorMap*>(&in_map),
-                                     *reinterpret_cast<const CUtensorMap*>(&out_map), p));
+                                     *reinterpret_cast<const CUtensorMap*>(&out_map),
+                                     *reinterpret_cast<const CUtensorMap*>(res_map ? res_map : &out_map), p));
     OB200_LAUNCHED("conv_wide_kernel");
     return OB200_OK;
 }
