@@ -13,7 +13,7 @@ int launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C
 // translation unit needs the driver API header.
 struct alignas(64) BoardTensorMap { unsigned char opaque[128]; };
 int make_board_tensor_map(const void* base, long long rows, int box_rows, BoardTensorMap* out, int channels = 64);
-int conv_halo_rows(int S);
+int conv_halo_rows(int S);   // 64-channel kernel: load boxes have 128 + 2 * conv_halo_rows(S) rows
 // res_map: the residual tensor through a 128-row-box map (a store map of that buffer), or null
 int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const BoardTensorMap* res_map,
                         const void* packed_w, const float* bias, int B, int S, int relu, cudaStream_t st);

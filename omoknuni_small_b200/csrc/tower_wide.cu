@@ -10,7 +10,7 @@
 // matrix descriptor whose start is moved by (dy*(S+1)+dx) rows.  With 128 or 256
 // channels a layer's weights (288 KB / 1.1 MB) do not fit in shared memory: they
 // stream from L2 as 16 KB blocks (128 output channels x 64 input channels of one
-// tap, pre-swizzled on the host) through a 4-deep ring; each block feeds the MMAs
+// tap, pre-swizzled on the host) through a 6-deep ring; each block feeds the MMAs
 // of both tiles of the unit, which halves the weight traffic per position, and
 // N = 128 keeps the shared-memory operand reads of an MMA (8 KB) within what the
 // tensor core consumes per instruction.
@@ -41,7 +41,7 @@ constexpr int kBoxRows = 160;            // rows per activation TMA box; two box
 constexpr int kAStageBytes = 2 * kBoxRows * kRowBytes;   // 40,960: 256 positions + 2 x 32 halo rows
 constexpr int kAStages = 2;
 constexpr int kBStageBytes = kN * kRowBytes;              // 16,384
-constexpr int kBStages = 4;
+constexpr int kBStages = 6;
 constexpr int kOutBytes = kTileM * kRowBytes;             // 16,384: 64 output channels of a tile
 constexpr int kEpiGroups = kUnitTiles;
 constexpr int kAccStages = 2;
@@ -49,7 +49,7 @@ constexpr int kTmemCols = kAccStages * kUnitTiles * kN;   // 512
 constexpr int kThreads = 128 + 128 * kEpiGroups;          // warps 0-3 roles, 4-11 epilogue
 constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kAccStages + kEpiGroups;
 constexpr int kMaxCout = 256;
-constexpr int kSmemBytes = kAStages * kAStageBytes + kBStages * kBStageBytes + kEpiGroups * 2 * kOutBytes +
+constexpr int kSmemBytes = kAStages * kAStageBytes + kBStages * kBStageBytes + kEpiGroups * kOutBytes +
                            kNumBars * 8 + kMaxCout * 4 + 16 + 1024;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
@@ -63,7 +63,6 @@ struct WideParams {
     int m_units;              // ceil(num_tiles / 2)
     int n_halves;             // cout / 128
     int k_slices;             // cin / 64
-    int taps;                 // 9 or 1
     int cout;
     int S, GP, slots;
     int halo;                 // rows before the unit's first position in a stage
@@ -143,6 +142,7 @@ __device__ __forceinline__ void group_bar(int id) {   // the 128 threads of one 
     asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory");
 }
 
+template <int TAPS>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
                  const __grid_constant__ CUtensorMap res_map, const WideParams p) {
@@ -152,7 +152,7 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
     uint8_t* a_s = smem;
     uint8_t* b_s = a_s + kAStages * kAStageBytes;
     uint8_t* o_s = b_s + kBStages * kBStageBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(o_s + kEpiGroups * 2 * kOutBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(o_s + kEpiGroups * kOutBytes);
     float* bias_s = reinterpret_cast<float*>(bars + kNumBars);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bias_s + kMaxCout);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -221,8 +221,8 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
             int jt = 0;
             for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
                 const int nh = u % p.n_halves;
-                const uint8_t* src = p.w + (size_t)nh * p.k_slices * p.taps * kBStageBytes;
-                const int blocks = p.k_slices * p.taps;
+                const uint8_t* src = p.w + (size_t)nh * p.k_slices * TAPS * kBStageBytes;
+                const int blocks = p.k_slices * TAPS;
                 bool ok = true;
                 for (int j = 0; j < blocks; ++j, ++jt) {
                     const int s = jt % kBStages;
@@ -237,45 +237,53 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
+        // One thread issues; the loop over taps, tiles and 16-channel steps is unrolled with
+        // compile-time offsets and ring positions are kept as counters, because every integer
+        // instruction between two MMAs of this thread is time the tensor core waits.
         if (lane == 0) {
-            int tap_off[9];
+            int tap_off[TAPS];
 #pragma unroll
-            for (int tap = 0; tap < 9; ++tap) {
-                const int dy = p.taps == 9 ? tap / 3 - 1 : 0, dx = p.taps == 9 ? tap % 3 - 1 : 0;
+            for (int tap = 0; tap < TAPS; ++tap) {
+                const int dy = TAPS == 9 ? tap / 3 - 1 : 0, dx = TAPS == 9 ? tap % 3 - 1 : 0;
                 tap_off[tap] = (p.halo + dy * p.GP + dx) * (kRowBytes >> 4);
             }
-            int it = 0, jt = 0, ut = 0;
+            const uint32_t a_base = desc_lo(smem_u32(a_s)), b_base = desc_lo(smem_u32(b_s));
+            int sa = 0, sb = 0, acc = 0;
+            uint32_t pha = 0, phb = 0, phacc = 0;
             bool ok = true;
-            for (int u = blockIdx.x; ok && u < num_units; u += gridDim.x, ++ut) {
+            for (int u = blockIdx.x; ok && u < num_units; u += gridDim.x) {
                 const int mu = u / p.n_halves;
-                const int tiles_here = (p.num_tiles - mu * kUnitTiles) < kUnitTiles ? (p.num_tiles - mu * kUnitTiles) : kUnitTiles;
-                const int a = ut % kAccStages;
-                const uint32_t pa = (uint32_t)(ut / kAccStages) & 1u;
-                if (!mbar_wait(accempty_bar(a), pa ^ 1u, abort_flag)) { ok = false; break; }
+                const bool two = p.num_tiles - mu * kUnitTiles >= kUnitTiles;
+                if (!mbar_wait(accempty_bar(acc), phacc ^ 1u, abort_flag)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t d_tmem = tmem_base + (uint32_t)(a * kUnitTiles * kN);
-                for (int kc = 0; ok && kc < p.k_slices; ++kc, ++it) {
-                    const int sa = it % kAStages;
-                    if (!mbar_wait(afull_bar(sa), (uint32_t)(it / kAStages) & 1u, abort_flag)) { ok = false; break; }
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kUnitTiles * kN);
+                for (int kc = 0; ok && kc < p.k_slices; ++kc) {
+                    if (!mbar_wait(afull_bar(sa), pha, abort_flag)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_lo = desc_lo(smem_u32(a_s + sa * kAStageBytes));
-                    for (int tap = 0; tap < p.taps; ++tap, ++jt) {
-                        const int sb = jt % kBStages;
-                        if (!mbar_wait(bfull_bar(sb), (uint32_t)(jt / kBStages) & 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t a_lo = a_base + (uint32_t)(sa * (kAStageBytes >> 4));
+#pragma unroll
+                    for (int tap = 0; tap < TAPS; ++tap) {
+                        if (!mbar_wait(bfull_bar(sb), phb, abort_flag)) { ok = false; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const uint32_t b_lo = desc_lo(smem_u32(b_s + sb * kBStageBytes));
-                        for (int t = 0; t < tiles_here; ++t) {
-                            const uint32_t at = a_lo + (uint32_t)(tap_off[tap] + t * kTileM * (kRowBytes >> 4));
+                        const uint32_t b_lo = b_base + (uint32_t)(sb * (kBStageBytes >> 4));
+                        const uint32_t at = a_lo + (uint32_t)tap_off[tap];
+#pragma unroll
+                        for (int ks = 0; ks < kSlice / 16; ++ks)
+                            umma(d_tmem, at + (uint32_t)(ks * 2), b_lo + (uint32_t)(ks * 2), (tap | ks) ? 1u : (uint32_t)(kc != 0));
+                        if (two) {
 #pragma unroll
                             for (int ks = 0; ks < kSlice / 16; ++ks)
-                                umma(d_tmem + (uint32_t)(t * kN), at + (uint32_t)(ks * 2), b_lo + (uint32_t)(ks * 2),
-                                     (kc | tap | ks) ? 1u : 0u);
+                                umma(d_tmem + (uint32_t)kN, at + (uint32_t)(kTileM * (kRowBytes >> 4) + ks * 2),
+                                     b_lo + (uint32_t)(ks * 2), (tap | ks) ? 1u : (uint32_t)(kc != 0));
                         }
                         umma_commit(bempty_bar(sb));    // weight block free once these MMAs have read it
+                        if (++sb == kBStages) { sb = 0; phb ^= 1u; }
                     }
                     if (ok) umma_commit(aempty_bar(sa));   // activation stage free
+                    if (++sa == kAStages) { sa = 0; pha ^= 1u; }
                 }
-                if (ok) umma_commit(accfull_bar(a));       // accumulators ready for the epilogue
+                if (ok) umma_commit(accfull_bar(acc));     // accumulators ready for the epilogue
+                if (++acc == kAccStages) { acc = 0; phacc ^= 1u; }
             }
             if (!ok) { *abort_flag = 1; atomicExch(p.error, 2); }
         }
@@ -283,16 +291,17 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
         // ---------------- epilogue: TMEM -> registers -> shared -> TMA store ----------------
         // Group g (4 warps) owns tile g of every unit; a warp owns one TMEM lane quadrant
         // (fixed by warp id % 4), a thread one position and all 128 output channels, 64 at a time.
-        // The group has one staging tile per 64-channel half.  With a residual, TMA loads the
-        // residual's two halves into the staging tiles while the unit's MMAs run; a thread then
-        // reads its own row, adds, and writes the result back in place before the TMA store.
+        // The group has one staging tile (128 positions x 64 channels).  With a residual, TMA loads
+        // the residual's 64-channel half into the staging tile (the first half while the unit's
+        // MMAs run); a thread then reads its own row, adds, and writes the result back in place
+        // before the TMA store.
         const int ew = warp - 4;
         const int group = ew >> 2;
         const int q = warp & 3;
         const int row = q * 32 + lane;
         const bool leader = (ew & 3) == 0 && lane == 0;
         const bool has_res = p.has_residual != 0;
-        uint8_t* stage_out = o_s + group * 2 * kOutBytes;
+        uint8_t* stage_out = o_s + group * kOutBytes;
         const uint32_t stage_out_u32 = smem_u32(stage_out);
         uint32_t res_phase = 0;
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -310,12 +319,11 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                 valid = (rr / p.GP < p.S) && (rr % p.GP < p.S);
             }
             if (active && leader) {
-                // the previous stores of this group must have finished reading the staging tiles
+                // the previous store of this group must have finished reading the staging tile
                 asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 if (has_res) {
-                    mbar_arrive_expect_tx(res_bar(group), (uint32_t)(2 * kOutBytes));
+                    mbar_arrive_expect_tx(res_bar(group), (uint32_t)kOutBytes);
                     tma_load_2d(stage_out_u32, &res_map, nh * kN, OB200_GUARD + tile * kTileM, res_bar(group));
-                    tma_load_2d(stage_out_u32 + kOutBytes, &res_map, nh * kN + 64, OB200_GUARD + tile * kTileM, res_bar(group));
                 }
             }
             if (!mbar_wait(accfull_bar(a), pa, abort_flag)) {
@@ -328,17 +336,18 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                 if (lane == 0) mbar_arrive(accempty_bar(a));
                 continue;
             }
-            if (has_res) {
-                if (!mbar_wait(res_bar(group), res_phase, abort_flag)) {
-                    *abort_flag = 1; atomicExch(p.error, 5); break;
-                }
-                res_phase ^= 1u;
-            } else {
-                group_bar(1 + 2 * group);   // after the leader's wait above: staging tiles are free
-            }
             const uint32_t t_acc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kUnitTiles * kN + group * kN);
+            bool ok = true;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
+                if (half == 1 && leader) {
+                    // second half: the store of the first must have read the staging tile
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    if (has_res) {
+                        mbar_arrive_expect_tx(res_bar(group), (uint32_t)kOutBytes);
+                        tma_load_2d(stage_out_u32, &res_map, nh * kN + 64, OB200_GUARD + tile * kTileM, res_bar(group));
+                    }
+                }
                 uint32_t r[64];
                 tmem_ld32(t_acc + (uint32_t)(half * 64), r);
                 tmem_ld32(t_acc + (uint32_t)(half * 64 + 32), r + 32);
@@ -348,8 +357,14 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                     __syncwarp();
                     if (lane == 0) mbar_arrive(accempty_bar(a));
                 }
+                if (has_res) {
+                    if (!mbar_wait(res_bar(group), res_phase, abort_flag)) { ok = false; break; }
+                    res_phase ^= 1u;
+                } else {
+                    group_bar(1 + 2 * group);   // after the leader's wait: the staging tile is free
+                }
                 const float* bias_t = bias_s + nh * kN + half * 64;
-                uint8_t* my_row = stage_out + half * kOutBytes + row * kRowBytes;
+                uint8_t* my_row = stage_out + row * kRowBytes;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     // 128-byte swizzle of the staging tile: 16-byte chunk k of row r sits at chunk k ^ (r % 8)
@@ -375,10 +390,11 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 group_bar(2 + 2 * group);
                 if (leader) {
-                    tma_store_2d(&out_map, nh * kN + half * 64, OB200_GUARD + tile * kTileM, stage_out_u32 + half * kOutBytes);
+                    tma_store_2d(&out_map, nh * kN + half * 64, OB200_GUARD + tile * kTileM, stage_out_u32);
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
+            if (!ok) { *abort_flag = 1; atomicExch(p.error, 5); break; }
         }
         if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
@@ -416,7 +432,7 @@ int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& ou
     if (!packed_w || !bias || B <= 0) return set_error(OB200_ERR_INVALID, "conv (wide): null pointer or empty batch");
     if (!conv_wide_covers(cin, cout) || (taps != 9 && taps != 1))
         return set_error(OB200_ERR_UNSUPPORTED, "conv (wide): %d -> %d channels with %d taps is not covered", cin, cout, taps);
-    if (S < 1 || conv_halo_rows(S) > OB200_GUARD)
+    if (S < 1 || S + 2 > OB200_GUARD)
         return set_error(OB200_ERR_UNSUPPORTED, "conv (wide): board_size %d outside [1, %d]", S, OB200_GUARD - 2);
     if ((uintptr_t)packed_w & 15) return set_error(OB200_ERR_INVALID, "conv (wide): weights must be 16-byte aligned");
     if (int rc = require_device()) return rc;
@@ -424,7 +440,8 @@ int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& ou
     int dev = 0;
     OB200_CUDA_OK(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        OB200_CUDA_OK(cudaFuncSetAttribute(conv_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        OB200_CUDA_OK(cudaFuncSetAttribute(conv_wide_kernel<9>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        OB200_CUDA_OK(cudaFuncSetAttribute(conv_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
         configured[dev] = true;
     }
     int sms = 0;
@@ -435,9 +452,9 @@ int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& ou
     p.error = device_error_word();
     if (!p.error) return set_error(OB200_ERR_CUDA, "conv (wide): cannot resolve the device error word");
     p.P = (int)g.P; p.num_tiles = (int)(g.Ppad / kTileM); p.m_units = (p.num_tiles + kUnitTiles - 1) / kUnitTiles;
-    p.n_halves = cout / kN; p.k_slices = cin / kSlice; p.taps = taps; p.cout = cout;
+    p.n_halves = cout / kN; p.k_slices = cin / kSlice; p.cout = cout;
     p.S = S; p.GP = g.GP; p.slots = g.slots;
-    p.halo = taps == 9 ? conv_halo_rows(S) : 0; p.relu = relu;
+    p.halo = taps == 9 ? S + 2 : 0; p.relu = relu;   // |dy*(S+1)+dx| <= S+2 rows before / after a unit
     const int units = p.m_units * p.n_halves;
     const int grid = units < sms ? units : sms;   // one persistent CTA per SM
     cudaLaunchConfig_t cfg = {};
@@ -446,9 +463,11 @@ int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& ou
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv_wide_kernel, *reinterpret_cast<const CUtensorMap*>(&in_map),
-                                     *reinterpret_cast<const CUtensorMap*>(&out_map),
-                                     *reinterpret_cast<const CUtensorMap*>(res_map ? res_map : &out_map), p));
+    const CUtensorMap& im = *reinterpret_cast<const CUtensorMap*>(&in_map);
+    const CUtensorMap& om = *reinterpret_cast<const CUtensorMap*>(&out_map);
+    const CUtensorMap& rm = *reinterpret_cast<const CUtensorMap*>(res_map ? res_map : &out_map);
+    if (taps == 9) OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv_wide_kernel<9>, im, om, rm, p));
+    else OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv_wide_kernel<1>, im, om, rm, p));
     OB200_LAUNCHED("conv_wide_kernel");
     return OB200_OK;
 }
