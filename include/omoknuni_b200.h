@@ -234,7 +234,7 @@ typedef struct ob200_net ob200_net;
 typedef struct ob200_net_config {
     int32_t board_size;       /* S: 15 for Gomoku                              */
     int32_t input_channels;   /* C_in of the stem (17, 19, 3, ...)             */
-    int32_t filters;          /* tower width; 64 in this build                 */
+    int32_t filters;          /* tower width: 64, 128 or 256                   */
     int32_t blocks;           /* residual blocks                               */
     int32_t policy_size;      /* A: policy outputs                             */
     int32_t policy_head_ch;   /* channels of the policy 1x1 conv (reference 32)*/
@@ -242,7 +242,19 @@ typedef struct ob200_net_config {
     int32_t value_hidden;     /* width of value_fc1 (reference 256)            */
     int32_t max_batch;        /* largest batch any call will pass              */
     int32_t device;           /* CUDA device ordinal                           */
+    int32_t policy_kind;      /* OB200_POLICY_FC (the reference's head) or
+                                 OB200_POLICY_CONV_PLANES                       */
 } ob200_net_config;
+
+/* Policy head kinds.  FC: 1x1 conv to policy_head_ch channels + BatchNorm + ReLU
+ * + policy_fc, as ResNetModel (src/nn/resnet_model.cpp:81-88,:178-188).
+ * CONV_PLANES (no counterpart in the reference; the shape of the chess
+ * configuration): 1x1 convolution with bias to policy_head_ch planes, logits =
+ * the planes flattened in NCHW order (index = plane * S^2 + cell), policy_size
+ * = policy_head_ch * S^2; tensors "policy_conv.weight" [planes][filters][1][1]
+ * and "policy_conv.bias" [planes]; filters 128 or 256 only. */
+#define OB200_POLICY_FC 0
+#define OB200_POLICY_CONV_PLANES 1
 
 int ob200_net_create(const ob200_net_config* cfg, ob200_net** out);
 void ob200_net_destroy(ob200_net* net);

@@ -28,9 +28,13 @@ class TreeView(C.Structure):
                 ("n_nodes", C.c_int32), ("n_children", C.c_int32), ("pitch", C.c_int32), ("mask_words", C.c_int32)]
 
 
+POLICY_FC, POLICY_CONV_PLANES = 0, 1
+
+
 class NetConfig(C.Structure):
     _fields_ = [(k, C.c_int32) for k in ("board_size", "input_channels", "filters", "blocks", "policy_size",
-                                          "policy_head_ch", "value_head_ch", "value_hidden", "max_batch", "device")]
+                                          "policy_head_ch", "value_head_ch", "value_hidden", "max_batch", "device",
+                                          "policy_kind")]
 
 
 class SearchConfig(C.Structure):
@@ -292,9 +296,9 @@ class Net:
     under the same names, inference on host buffers)."""
 
     def __init__(self, input_channels, board_size, blocks, filters, policy_size, policy_head_ch=32, value_head_ch=32,
-                 value_hidden=256, max_batch=1024, device=0):
+                 value_hidden=256, max_batch=1024, device=0, policy_kind=POLICY_FC):
         self.cfg = NetConfig(board_size, input_channels, filters, blocks, policy_size or board_size * board_size,
-                             policy_head_ch, value_head_ch, value_hidden, max_batch, device)
+                             policy_head_ch, value_head_ch, value_hidden, max_batch, device, policy_kind)
         self.h = C.c_void_p()
         check(lib().ob200_net_create(C.byref(self.cfg), C.byref(self.h)))
         self.policy_size = self.cfg.policy_size

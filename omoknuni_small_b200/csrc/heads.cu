@@ -21,64 +21,58 @@ struct alignas(16) Pack8 { __nv_bfloat162 v[4]; };
 
 // A warp takes 32 consecutive positions of the board tensor (pad positions included, their
 // results are dropped).  Eight lanes share a position: lane = 8 * (position within a group of 4)
-// + channel block, so a warp-wide 16-byte load covers 4 positions x 128 contiguous bytes and the
-// 8 loads of a warp are issued back to back.  Each lane multiplies its 8 channels into a head
-// channel's partial sum, three shuffle steps add the 8 lanes, and lane (sub, blk) keeps the sum of
-// group blk: after 8 groups every lane owns one position and stores once per head channel.
-// HCT > 0: that many head channels, the lane's weights held in registers; HCT == 0: any number,
-// weights read from shared memory.
+// + channel block, so a warp-wide 16-byte load covers 4 positions x 128 contiguous bytes of one
+// 64-channel slice and the 8 loads of a warp are issued back to back.  Each lane multiplies its
+// 8 channels (per slice) into a head channel's partial sum, three shuffle steps add the 8 lanes,
+// and lane (sub, blk) keeps the sum of group blk: after 8 groups every lane owns one position and
+// stores once per head channel.  C = tower channels (a multiple of 64).
+// HCT > 0: that many head channels, partial sums of all of them held in registers while the
+// slices stream by; HCT == 0: any number, weights in shared memory, one head channel at a time.
 constexpr int kHeadThreads = 128;
 template <int HCT>
 __global__ void __launch_bounds__(kHeadThreads)
 head_conv_kernel(const uint8_t* __restrict__ tower, const float* __restrict__ w,
                  const float* __restrict__ bias, int HC, int pc, float* __restrict__ hp,
-                 float* __restrict__ hv, int B, int S) {
-    extern __shared__ float w_s[];  // HCT == 0: [HC][64] folded weights then [HC] biases
+                 float* __restrict__ hv, int B, int S, int C) {
+    extern __shared__ float w_s[];  // HCT == 0: [HC][C] folded weights then [HC] biases
     const int lane = threadIdx.x & 31, sub = lane >> 3, blk = lane & 7;
-    constexpr int kRegCh = HCT > 0 ? HCT : 1;
-    float wreg[kRegCh][8], breg[kRegCh];
-    if (HCT > 0) {
-#pragma unroll
-        for (int h = 0; h < kRegCh; ++h) {
-            breg[h] = bias[h];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) wreg[h][k] = w[h * 64 + blk * 8 + k];
-        }
-    } else {
-        for (int i = threadIdx.x; i < HC * 64; i += blockDim.x) w_s[i] = w[i];
-        for (int i = threadIdx.x; i < HC; i += blockDim.x) w_s[HC * 64 + i] = bias[i];
+    if (HCT == 0) {
+        for (int i = threadIdx.x; i < HC * C; i += blockDim.x) w_s[i] = w[i];
+        for (int i = threadIdx.x; i < HC; i += blockDim.x) w_s[HC * C + i] = bias[i];
         __syncthreads();
     }
     const int hc = HCT > 0 ? HCT : HC;
     const int S2 = S * S, GP = S + 1, slots = GP * GP, vc = hc - pc;
     const int total = B * slots;
+    const int slices = C >> 6;
+    const size_t row_bytes = (size_t)C * 2;
     const int p0 = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * 32;
     if (p0 >= total) return;
     // the tensor's trailing guard positions make the (at most 31) positions past the end readable
-    const uint8_t* src = tower + ((size_t)OB200_GUARD + p0 + sub) * 128 + blk * 16;
+    const uint8_t* src = tower + ((size_t)OB200_GUARD + p0 + sub) * row_bytes + blk * 16;
     float a[8][8];
+    auto load_slice = [&](int sl) {
 #pragma unroll
-    for (int it = 0; it < 8; ++it) {
-        const Pack8 v = *reinterpret_cast<const Pack8*>(src + (size_t)it * 4 * 128);
+        for (int it = 0; it < 8; ++it) {
+            const Pack8 v = *reinterpret_cast<const Pack8*>(src + (size_t)it * 4 * row_bytes + (size_t)sl * 128);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(v.v[j]);
-            a[it][2 * j] = f.x; a[it][2 * j + 1] = f.y;
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(v.v[j]);
+                a[it][2 * j] = f.x; a[it][2 * j + 1] = f.y;
+            }
         }
-    }
+    };
     // this lane's own position: group blk, member sub
     const int p = p0 + blk * 4 + sub;
     const int b = p / slots, r = p - b * slots;
     const int y = r / GP, x = r - y * GP;
     const bool real = p < total && y < S && x < S;
     const int cell = y * S + x;
-    auto one_channel = [&](int h, const float (&wk)[8], float bh) {
+    auto finish = [&](int h, const float (&part)[8], float bh) {
         float keep = 0.0f;
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
-            float s = a[it][0] * wk[0];
-#pragma unroll
-            for (int k = 1; k < 8; ++k) s = fmaf(a[it][k], wk[k], s);
+            float s = part[it];
             s += __shfl_xor_sync(0xffffffffu, s, 1);
             s += __shfl_xor_sync(0xffffffffu, s, 2);
             s += __shfl_xor_sync(0xffffffffu, s, 4);
@@ -91,14 +85,44 @@ head_conv_kernel(const uint8_t* __restrict__ tower, const float* __restrict__ w,
         }
     };
     if (HCT > 0) {
+        constexpr int kRegCh = HCT > 0 ? HCT : 1;
+        float part[kRegCh][8];
 #pragma unroll
-        for (int h = 0; h < kRegCh; ++h) one_channel(h, wreg[h], breg[h]);
+        for (int h = 0; h < kRegCh; ++h)
+#pragma unroll
+            for (int it = 0; it < 8; ++it) part[h][it] = 0.0f;
+        for (int sl = 0; sl < slices; ++sl) {
+            load_slice(sl);
+#pragma unroll
+            for (int h = 0; h < kRegCh; ++h) {
+                const float4* wr = reinterpret_cast<const float4*>(w + (size_t)h * C + sl * 64 + blk * 8);
+                const float4 w0 = __ldg(wr), w1 = __ldg(wr + 1);
+                const float wk[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int it = 0; it < 8; ++it)
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) part[h][it] = fmaf(a[it][k], wk[k], part[h][it]);
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < kRegCh; ++h) finish(h, part[h], __ldg(bias + h));
     } else {
+        if (slices == 1) load_slice(0);
         for (int h = 0; h < hc; ++h) {
-            const float4* wr = reinterpret_cast<const float4*>(w_s + h * 64 + blk * 8);
-            const float4 w0 = wr[0], w1 = wr[1];
-            const float wk[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-            one_channel(h, wk, w_s[hc * 64 + h]);
+            float part[8];
+#pragma unroll
+            for (int it = 0; it < 8; ++it) part[it] = 0.0f;
+            for (int sl = 0; sl < slices; ++sl) {
+                if (slices > 1) load_slice(sl);   // re-read per head channel (L1 / L2 hits)
+                const float4* wr = reinterpret_cast<const float4*>(w_s + (size_t)h * C + sl * 64 + blk * 8);
+                const float4 w0 = wr[0], w1 = wr[1];
+                const float wk[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int it = 0; it < 8; ++it)
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) part[it] = fmaf(a[it][k], wk[k], part[it]);
+            }
+            finish(h, part, w_s[hc * C + h]);
         }
     }
 }
@@ -240,18 +264,24 @@ value_out_kernel(const float* __restrict__ hidden, const float* __restrict__ w2,
 }  // namespace
 
 int launch_head_conv(const void* tower, const float* w, const float* bias, int HC, int pc,
-                     float* hp, float* hv, int B, int S, cudaStream_t st) {
+                     float* hp, float* hv, int B, int S, cudaStream_t st, int C) {
+    if (C < 64 || C % 64) return set_error(OB200_ERR_INVALID, "head conv: tower channels %d not a multiple of 64", C);
     const long long total = (long long)B * (S + 1) * (S + 1);   // positions, one warp per 32
     const unsigned grid = (unsigned)((total + kHeadThreads - 1) / kHeadThreads);
     const uint8_t* t = static_cast<const uint8_t*>(tower);
     switch (HC) {
-        case 1: head_conv_kernel<1><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S); break;
-        case 2: head_conv_kernel<2><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S); break;
-        case 3: head_conv_kernel<3><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S); break;
-        case 4: head_conv_kernel<4><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S); break;
-        default:
-            head_conv_kernel<0><<<grid, kHeadThreads, (size_t)(HC * 64 + HC) * sizeof(float), st>>>(t, w, bias, HC, pc,
-                                                                                                   hp, hv, B, S);
+        case 1: head_conv_kernel<1><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C); break;
+        case 2: head_conv_kernel<2><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C); break;
+        case 3: head_conv_kernel<3><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C); break;
+        case 4: head_conv_kernel<4><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C); break;
+        default: {
+            const size_t smem = (size_t)(HC * C + HC) * sizeof(float);
+            if (smem > 200 * 1024)
+                return set_error(OB200_ERR_UNSUPPORTED, "head conv: %d head channels x %d tower channels exceed shared memory", HC, C);
+            if (smem > 48 * 1024)
+                OB200_CUDA_OK(cudaFuncSetAttribute(head_conv_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            head_conv_kernel<0><<<grid, kHeadThreads, smem, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C);
+        }
     }
     OB200_LAUNCHED("head_conv_kernel");
     return OB200_OK;

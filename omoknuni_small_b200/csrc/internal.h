@@ -21,16 +21,18 @@ int* device_error_word();
 // Towers of 128 / 256 channels (tower_wide.cu): cin a multiple of 64 up to 256, cout 128 or 256,
 // taps 9 (3x3) or 1 (1x1).  in_map: boxes of conv_wide_box_rows() rows over a cin-channel tensor;
 // out_map / res_map (residual, or null): boxes of 128 rows over a cout-channel tensor.
+// out_f32 (optional): fp32 [positions][cout] output by plain stores instead of the bf16 tensor.
 bool conv_wide_covers(int cin, int cout);
 int conv_wide_box_rows();
 size_t conv_wide_packed_bytes(int cin, int cout, int taps);
 int conv_wide_pack(const float* w, const float* scale, int cout, int cin_real, int cin, int taps, void* packed_out);
 int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const BoardTensorMap* res_map,
                           const void* packed_w, const float* bias, int B, int S, int cin, int cout, int taps, int relu,
-                          cudaStream_t st);
+                          cudaStream_t st, float* out_f32 = nullptr);
 
+// C: channels of the tower board tensor (a multiple of 64); w: [HC][C]
 int launch_head_conv(const void* tower, const float* w, const float* bias, int HC, int pc, float* hp,
-                     float* hv, int B, int S, cudaStream_t st);
+                     float* hv, int B, int S, cudaStream_t st, int C = 64);
 int launch_fc(const float* in, const float* WT, const float* bias, float* out, int B, int K, int Nout, int relu,
               cudaStream_t st);
 int launch_softmax(float* x, int B, int A, cudaStream_t st);

@@ -5,6 +5,7 @@
 // Takes the place of alphazero::nn::ResNetModel (reference
 // src/nn/resnet_model.cpp:51-237 construction + forward, :594-811 inference).
 #include "internal.h"
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <map>
@@ -14,7 +15,9 @@
 
 struct ob200_net {
     ob200_net_config cfg{};
-    int cin_pad = 64;               // channels of the input board tensor (the stem runs on the 64-channel kernel)
+    int cin_pad = 64;               // channels of the input board tensor (input_channels rounded up to 64)
+    bool wide = false;              // filters 128 / 256: the streamed-weight kernel; 64: the resident-weight kernel
+    int box_in = 0;                 // rows of a load box of the tower kernel in use
     long long rows = 0;             // positions per board tensor (sized for max_batch)
     ob200::BoardTensorMap in_map_load{}, act_load[3]{}, act_store[3]{};
     std::map<std::string, std::vector<float>> host;  // tensors as given
@@ -32,6 +35,8 @@ struct ob200_net {
     float *WpT = nullptr, *bp = nullptr, *W1T = nullptr, *b1 = nullptr, *w2 = nullptr;
     float b2 = 0.0f;
     float *hp = nullptr, *hv = nullptr, *hidden = nullptr;
+    // device: policy as convolution planes (policy_kind 1): 1x1 convolution on the tensor cores
+    void* pol_w = nullptr; float* pol_b = nullptr; float* pol_planes = nullptr; int pol_cout = 0;
     // device + pinned host staging of the host-buffer calls
     float *d_planes = nullptr, *d_policy = nullptr, *d_value = nullptr;
     int16_t* d_hist = nullptr; uint8_t *d_nhist = nullptr, *d_tomove = nullptr;
@@ -114,6 +119,37 @@ int add_conv(ob200_net* n, const std::string& conv, const std::string& bn, int c
     return OB200_OK;
 }
 
+// One tower layer on the kernel that covers the handle's width.
+int tower_conv(ob200_net* n, const BoardTensorMap& in_map, int cin, const BoardTensorMap& out_map,
+               const BoardTensorMap* res_map, int layer, int B, cudaStream_t st) {
+    const ob200_net_config& c = n->cfg;
+    if (n->wide)
+        return launch_conv_wide_maps(in_map, out_map, res_map, n->conv_w[layer], n->conv_b[layer], B, c.board_size, cin,
+                                     c.filters, 9, 1, st);
+    return launch_conv3x3_maps(in_map, out_map, res_map, n->conv_w[layer], n->conv_b[layer], B, c.board_size, 1, st);
+}
+
+// Load map over a caller's input board tensor holding B boards.
+int input_map(ob200_net* n, const void* input_bt, int B, BoardTensorMap* out) {
+    return make_board_tensor_map(input_bt, board_geom(n->cfg.board_size, B).PT, n->box_in, out, n->cin_pad);
+}
+
+// logits[b][plane * S2 + cell] = planes[(G + b * slots + y * GP + x)][plane]: the fp32 output of the
+// policy 1x1 convolution, gathered into the NCHW-flattened order of a convolutional policy head.
+__global__ void __launch_bounds__(256)
+policy_planes_gather_kernel(const float* __restrict__ planes, int pitch, int n_planes, int B, int S,
+                            float* __restrict__ logits) {
+    const int S2 = S * S, GP = S + 1;
+    const long long total = (long long)B * n_planes * S2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int cell = (int)(i % S2);
+        const long long t = i / S2;
+        const int plane = (int)(t % n_planes), b = (int)(t / n_planes);
+        const int y = cell / S, x = cell - y * S;
+        logits[i] = planes[((size_t)OB200_GUARD + (size_t)b * GP * GP + y * GP + x) * pitch + plane];
+    }
+}
+
 }  // namespace
 }  // namespace ob200
 
@@ -128,11 +164,21 @@ int ob200_net_create(const ob200_net_config* cfg, ob200_net** out) {
         cfg->policy_size < 1 || cfg->policy_head_ch < 1 || cfg->value_head_ch < 1 || cfg->value_hidden < 1 ||
         cfg->max_batch < 1)
         return set_error(OB200_ERR_INVALID, "ob200_net_create: bad configuration value");
-    if (cfg->filters != 64)
-        return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_create: this build's tower kernel covers filters = 64, got %d",
+    if (cfg->filters != 64 && cfg->filters != 128 && cfg->filters != 256)
+        return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_create: the tower kernels cover filters = 64, 128, 256; got %d",
                          cfg->filters);
-    if (cfg->input_channels > 64)
-        return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_create: input_channels %d > 64", cfg->input_channels);
+    if (cfg->input_channels > (cfg->filters == 64 ? 64 : 256))
+        return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_create: input_channels %d too many for filters %d",
+                         cfg->input_channels, cfg->filters);
+    if (cfg->policy_kind != OB200_POLICY_FC && cfg->policy_kind != OB200_POLICY_CONV_PLANES)
+        return set_error(OB200_ERR_INVALID, "ob200_net_create: bad policy_kind %d", cfg->policy_kind);
+    if (cfg->policy_kind == OB200_POLICY_CONV_PLANES) {
+        if (cfg->filters == 64)
+            return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_create: the convolutional policy head needs filters 128 or 256");
+        if (cfg->policy_size != cfg->policy_head_ch * cfg->board_size * cfg->board_size || cfg->policy_head_ch > 256)
+            return set_error(OB200_ERR_INVALID,
+                             "ob200_net_create: convolutional policy head: policy_size must be policy_head_ch * board_size^2, at most 256 planes");
+    }
     if (cudaSetDevice(cfg->device) != cudaSuccess) {
         cudaGetLastError();
         return set_error(OB200_ERR_NO_DEVICE, "ob200_net_create: CUDA device %d is not available (there is no CPU path)", cfg->device);
@@ -140,7 +186,9 @@ int ob200_net_create(const ob200_net_config* cfg, ob200_net** out) {
     if (int rc = require_device()) return rc;
     ob200_net* n = new ob200_net;
     n->cfg = *cfg;
-    n->cin_pad = 64;
+    n->cin_pad = (cfg->input_channels + 63) / 64 * 64;
+    n->wide = cfg->filters != 64;
+    n->box_in = n->wide ? conv_wide_box_rows() : 128 + 2 * conv_halo_rows(cfg->board_size);
     n->rows = board_geom(cfg->board_size, cfg->max_batch).PT;
     *out = n;
     return OB200_OK;
@@ -180,49 +228,72 @@ int ob200_net_finalize(ob200_net* n) {
         if (int rc = add_conv(n, p + "conv2", p + "bn2", F, F)) return rc;
     }
     // heads: 1x1 convolutions with BatchNorm folded, policy rows first
-    const std::vector<float>*pw, *vw, *fcw, *fcb, *f1w, *f1b, *f2w, *f2b;
-    if (int rc = need(n, "policy_conv.weight", (size_t)pc * F, &pw)) return rc;
+    const bool planes_policy = c.policy_kind == OB200_POLICY_CONV_PLANES;
+    const int pch = planes_policy ? 0 : pc;        // policy channels that go through the small head kernel
+    const std::vector<float>*pw = nullptr, *vw, *fcw, *fcb, *f1w, *f1b, *f2w, *f2b;
+    if (!planes_policy)
+        if (int rc = need(n, "policy_conv.weight", (size_t)pc * F, &pw)) return rc;
     if (int rc = need(n, "value_conv.weight", (size_t)vc * F, &vw)) return rc;
     std::vector<float> ps, pb, vs, vb;
-    if (int rc = bn_fold(n, "policy_bn", pc, ps, pb)) return rc;
+    if (!planes_policy)
+        if (int rc = bn_fold(n, "policy_bn", pc, ps, pb)) return rc;
     if (int rc = bn_fold(n, "value_bn", vc, vs, vb)) return rc;
-    std::vector<float> hw((size_t)(pc + vc) * F), hb(pc + vc);
-    for (int h = 0; h < pc; ++h) { for (int k = 0; k < F; ++k) hw[(size_t)h * F + k] = (*pw)[(size_t)h * F + k] * ps[h]; hb[h] = pb[h]; }
-    for (int h = 0; h < vc; ++h) { for (int k = 0; k < F; ++k) hw[(size_t)(pc + h) * F + k] = (*vw)[(size_t)h * F + k] * vs[h]; hb[pc + h] = vb[h]; }
+    std::vector<float> hw((size_t)(pch + vc) * F), hb(pch + vc);
+    for (int h = 0; h < pch; ++h) { for (int k = 0; k < F; ++k) hw[(size_t)h * F + k] = (*pw)[(size_t)h * F + k] * ps[h]; hb[h] = pb[h]; }
+    for (int h = 0; h < vc; ++h) { for (int k = 0; k < F; ++k) hw[(size_t)(pch + h) * F + k] = (*vw)[(size_t)h * F + k] * vs[h]; hb[pch + h] = vb[h]; }
     if (int rc = upload(n, &n->head_w, hw)) return rc;
     if (int rc = upload(n, &n->head_b, hb)) return rc;
     // fully connected layers, stored transposed ([in][out]) for coalesced reads
     const int Kp = pc * S2, Kv = vc * S2, A = c.policy_size, H = c.value_hidden;
-    if (int rc = need(n, "policy_fc.weight", (size_t)A * Kp, &fcw)) return rc;
-    if (int rc = need(n, "policy_fc.bias", (size_t)A, &fcb)) return rc;
+    if (planes_policy) {
+        // policy planes: 1x1 convolution with bias, no BatchNorm, no ReLU, run on the tensor cores with the
+        // plane count padded to 128 / 256 output channels
+        const std::vector<float>*cw, *cb;
+        if (int rc = need(n, "policy_conv.weight", (size_t)pc * F, &cw)) return rc;
+        if (int rc = need(n, "policy_conv.bias", (size_t)pc, &cb)) return rc;
+        n->pol_cout = pc <= 128 ? 128 : 256;
+        std::vector<float> wpad((size_t)n->pol_cout * F, 0.0f), bpad(n->pol_cout, 0.0f);
+        std::copy(cw->begin(), cw->end(), wpad.begin());
+        std::copy(cb->begin(), cb->end(), bpad.begin());
+        std::vector<uint16_t> packed(conv_wide_packed_bytes(F, n->pol_cout, 1) / 2);
+        if (int rc = conv_wide_pack(wpad.data(), nullptr, n->pol_cout, F, F, 1, packed.data())) return rc;
+        uint16_t* dw = nullptr;
+        if (int rc = upload(n, &dw, packed)) return rc;
+        n->pol_w = dw;
+        if (int rc = upload(n, &n->pol_b, bpad)) return rc;
+        if (int rc = dev_alloc(n, &n->pol_planes, (size_t)n->rows * n->pol_cout, false)) return rc;
+    } else {
+        if (int rc = need(n, "policy_fc.weight", (size_t)A * Kp, &fcw)) return rc;
+        if (int rc = need(n, "policy_fc.bias", (size_t)A, &fcb)) return rc;
+        std::vector<float> wpt((size_t)Kp * A);
+        for (int j = 0; j < A; ++j) for (int i = 0; i < Kp; ++i) wpt[(size_t)i * A + j] = (*fcw)[(size_t)j * Kp + i];
+        if (int rc = upload(n, &n->WpT, wpt)) return rc;
+        if (int rc = upload(n, &n->bp, *fcb)) return rc;
+    }
     if (int rc = need(n, "value_fc1.weight", (size_t)H * Kv, &f1w)) return rc;
     if (int rc = need(n, "value_fc1.bias", (size_t)H, &f1b)) return rc;
     if (int rc = need(n, "value_fc2.weight", (size_t)H, &f2w)) return rc;
     if (int rc = need(n, "value_fc2.bias", 1, &f2b)) return rc;
-    std::vector<float> wpt((size_t)Kp * A), w1t((size_t)Kv * H);
-    for (int j = 0; j < A; ++j) for (int i = 0; i < Kp; ++i) wpt[(size_t)i * A + j] = (*fcw)[(size_t)j * Kp + i];
+    std::vector<float> w1t((size_t)Kv * H);
     for (int j = 0; j < H; ++j) for (int i = 0; i < Kv; ++i) w1t[(size_t)i * H + j] = (*f1w)[(size_t)j * Kv + i];
-    if (int rc = upload(n, &n->WpT, wpt)) return rc;
-    if (int rc = upload(n, &n->bp, *fcb)) return rc;
     if (int rc = upload(n, &n->W1T, w1t)) return rc;
     if (int rc = upload(n, &n->b1, *f1b)) return rc;
     if (int rc = upload(n, &n->w2, *f2w)) return rc;
     n->b2 = (*f2b)[0];
     // activations (zeroed once: guards and padding stay zero for the handle's lifetime)
-    const size_t tensor_bytes = (size_t)n->rows * 128;   // 64 channels x bf16 per position
-    const int box_in = 128 + 2 * conv_halo_rows(c.board_size);
+    const int box_store = 128;
     uint8_t* p8 = nullptr;
-    if (int rc = dev_alloc(n, &p8, tensor_bytes, true)) return rc;
+    if (int rc = dev_alloc(n, &p8, (size_t)n->rows * n->cin_pad * 2, true)) return rc;
     n->act_in = p8;
-    if (int rc = make_board_tensor_map(p8, n->rows, box_in, &n->in_map_load)) return rc;
+    if (int rc = make_board_tensor_map(p8, n->rows, n->box_in, &n->in_map_load, n->cin_pad)) return rc;
     for (int i = 0; i < 3; ++i) {
-        if (int rc = dev_alloc(n, &p8, tensor_bytes, true)) return rc;
+        if (int rc = dev_alloc(n, &p8, (size_t)n->rows * F * 2, true)) return rc;
         n->act[i] = p8;
-        if (int rc = make_board_tensor_map(p8, n->rows, box_in, &n->act_load[i])) return rc;
-        if (int rc = make_board_tensor_map(p8, n->rows, 128, &n->act_store[i])) return rc;
+        if (int rc = make_board_tensor_map(p8, n->rows, n->box_in, &n->act_load[i], F)) return rc;
+        if (int rc = make_board_tensor_map(p8, n->rows, box_store, &n->act_store[i], F)) return rc;
     }
     const size_t MB = c.max_batch;
-    if (int rc = dev_alloc(n, &n->hp, MB * Kp, false)) return rc;
+    if (int rc = dev_alloc(n, &n->hp, MB * (planes_policy ? 1 : Kp), false)) return rc;
     if (int rc = dev_alloc(n, &n->hv, MB * Kv, false)) return rc;
     if (int rc = dev_alloc(n, &n->hidden, MB * H, false)) return rc;
     if (int rc = dev_alloc(n, &n->d_policy, MB * A, false)) return rc;
@@ -250,23 +321,34 @@ int ob200_net_finalize(ob200_net* n) {
 namespace ob200 {
 namespace {
 
-// Tower + heads on device buffers.  `in_map` covers a 64-channel board tensor holding the
-// B input boards.
+// Tower + heads on device buffers.  `in_map` covers a board tensor of cin_pad channels holding
+// the B input boards.
 int forward_device(ob200_net* n, const BoardTensorMap& in_map, int B, float* policy_out, float* value_out,
                    int out_kind, cudaStream_t st) {
     const ob200_net_config& c = n->cfg;
     const int S = c.board_size;
+    const int F = c.filters;
     int x = 0, y = 1, z = 2;
-    if (int rc = launch_conv3x3_maps(in_map, n->act_store[x], nullptr, n->conv_w[0], n->conv_b[0], B, S, 1, st)) return rc;
+    if (int rc = tower_conv(n, in_map, n->cin_pad, n->act_store[x], nullptr, 0, B, st)) return rc;
     for (int i = 0; i < c.blocks; ++i) {
-        if (int rc = launch_conv3x3_maps(n->act_load[x], n->act_store[y], nullptr, n->conv_w[1 + 2 * i], n->conv_b[1 + 2 * i], B, S, 1, st)) return rc;
-        if (int rc = launch_conv3x3_maps(n->act_load[y], n->act_store[z], &n->act_store[x], n->conv_w[2 + 2 * i], n->conv_b[2 + 2 * i], B, S, 1, st)) return rc;
+        if (int rc = tower_conv(n, n->act_load[x], F, n->act_store[y], nullptr, 1 + 2 * i, B, st)) return rc;
+        if (int rc = tower_conv(n, n->act_load[y], F, n->act_store[z], &n->act_store[x], 2 + 2 * i, B, st)) return rc;
         std::swap(x, z);
     }
     n->tower_out = n->act[x];
     const int S2 = S * S, pc = c.policy_head_ch, vc = c.value_head_ch;
-    if (int rc = launch_head_conv(n->act[x], n->head_w, n->head_b, pc + vc, pc, n->hp, n->hv, B, S, st)) return rc;
-    if (int rc = launch_fc(n->hp, n->WpT, n->bp, policy_out, B, pc * S2, c.policy_size, 0, st)) return rc;
+    if (c.policy_kind == OB200_POLICY_CONV_PLANES) {
+        if (int rc = launch_conv_wide_maps(n->act_load[x], n->act_load[x], nullptr, n->pol_w, n->pol_b, B, S, F, n->pol_cout, 1, 0,
+                                           st, n->pol_planes)) return rc;
+        const long long total = (long long)B * pc * S2;
+        policy_planes_gather_kernel<<<(unsigned)std::min<long long>((total + 255) / 256, 148 * 16), 256, 0, st>>>(
+            n->pol_planes, n->pol_cout, pc, B, S, policy_out);
+        OB200_LAUNCHED("policy_planes_gather_kernel");
+        if (int rc = launch_head_conv(n->act[x], n->head_w, n->head_b, vc, 0, n->hv, n->hv, B, S, st, F)) return rc;
+    } else {
+        if (int rc = launch_head_conv(n->act[x], n->head_w, n->head_b, pc + vc, pc, n->hp, n->hv, B, S, st, F)) return rc;
+        if (int rc = launch_fc(n->hp, n->WpT, n->bp, policy_out, B, pc * S2, c.policy_size, 0, st)) return rc;
+    }
     if (out_kind == OB200_OUT_PROBS)
         if (int rc = launch_softmax(policy_out, B, c.policy_size, st)) return rc;
     if (int rc = launch_fc(n->hv, n->W1T, n->b1, n->hidden, B, vc * S2, c.value_hidden, 1, st)) return rc;
@@ -315,8 +397,7 @@ int net_forward_for_search(ob200_net* n, const void* input_bt, int B, float* pol
     if (!n || !n->finalized) return set_error(OB200_ERR_STATE, "search: the network is not finalised");
     std::lock_guard<std::mutex> lk(n->mu);
     BoardTensorMap in_map;
-    if (int rc = make_board_tensor_map(input_bt, board_geom(n->cfg.board_size, B).PT,
-                                       128 + 2 * conv_halo_rows(n->cfg.board_size), &in_map)) return rc;
+    if (int rc = input_map(n, input_bt, B, &in_map)) return rc;
     return forward_device(n, in_map, B, policy, value, OB200_OUT_PROBS, st);
 }
 const ob200_net_config* net_config(ob200_net* n) { return (n && n->finalized) ? &n->cfg : nullptr; }
@@ -372,8 +453,7 @@ int ob200_net_forward_device(ob200_net* n, const void* input_board_tensor, int32
     std::lock_guard<std::mutex> lk(n->mu);
     OB200_CUDA_OK(cudaSetDevice(n->cfg.device));
     BoardTensorMap in_map;
-    if (int rc = make_board_tensor_map(input_board_tensor, board_geom(n->cfg.board_size, B).PT,
-                                       128 + 2 * conv_halo_rows(n->cfg.board_size), &in_map)) return rc;
+    if (int rc = input_map(n, input_board_tensor, B, &in_map)) return rc;
     return forward_device(n, in_map, B, policy_out, value_out, out_kind, as_stream(stream));
 }
 
@@ -387,7 +467,9 @@ int ob200_net_value_head_noalloc(ob200_net* n, const void* tower_board_tensor, i
     if (B < 1) return set_error(OB200_ERR_INVALID, "ob200_net_value_head_noalloc: batch %d", B);
     if (int rc = require_device()) return rc;
     const ob200_net_config& c = n->cfg;
-    const int pc = c.policy_head_ch;
+    const int pc = c.policy_kind == OB200_POLICY_CONV_PLANES ? 0 : c.policy_head_ch;
+    if (c.filters != 64)
+        return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_value_head_noalloc: covers towers of 64 filters");
     return launch_value_head_static(tower_board_tensor, n->head_w + (size_t)pc * c.filters, n->head_b + pc,
                                     c.value_head_ch, n->W1T, n->b1, n->w2, n->b2, c.value_hidden, B, c.board_size,
                                     value_out, as_stream(stream));

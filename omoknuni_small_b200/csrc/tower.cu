@@ -224,15 +224,15 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
 #pragma unroll
             for (int tap = 0; tap < 9; ++tap)
                 tap_off[tap] = (p.halo + (tap / 3 - 1) * p.GP + (tap % 3 - 1)) * (kRowBytes >> 4);
-            int it = 0;
-            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x, ++it) {
-                const int s = it % kStages, a = it % kAccStages;
-                const uint32_t ph = (uint32_t)(it / kStages) & 1u, pa = (uint32_t)(it / kAccStages) & 1u;
+            const uint32_t a_base = desc_lo(smem_u32(a_s));
+            int s = 0, a = 0;
+            uint32_t ph = 0, pa = 0;
+            for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
                 if (!mbar_wait(accempty_bar(a), pa ^ 1u, abort_flag) || !mbar_wait(full_bar(s), ph, abort_flag)) {
                     *abort_flag = 1; atomicExch(p.error, 2); break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_lo = desc_lo(smem_u32(a_s + s * kStageBytes));
+                const uint32_t a_lo = a_base + (uint32_t)(s * (kStageBytes >> 4));
                 const uint32_t d_tmem = tmem_base + (uint32_t)a * kC;
 #pragma unroll
                 for (int tap = 0; tap < 9; ++tap) {
@@ -243,6 +243,8 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
                 }
                 umma_commit(empty_bar(s));      // smem stage free once these MMAs have read it
                 umma_commit(accfull_bar(a));    // accumulator ready for the epilogue
+                if (++s == kStages) { s = 0; ph ^= 1u; }
+                if (++a == kAccStages) { a = 0; pa ^= 1u; }
             }
         }
     } else {

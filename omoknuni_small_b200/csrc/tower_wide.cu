@@ -57,6 +57,7 @@ struct WideParams {
     const uint8_t* w;         // packed weights: [n_half][k_slice][tap] blocks of 128 x 64, pre-swizzled
     const float* bias;        // [cout]
     int has_residual;         // the residual tensor map is live
+    float* out_f32;           // when set: results as fp32 [positions][cout] by plain stores, no bf16 tensor
     int* error;               // device error word (0 = fine)
     int P;                    // real positions = B * slots
     int num_tiles;            // 128-position tiles
@@ -357,6 +358,24 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                     __syncwarp();
                     if (lane == 0) mbar_arrive(accempty_bar(a));
                 }
+                if (p.out_f32 != nullptr) {
+                    // fp32 output (policy planes): the thread's 64 channels are 256 contiguous bytes
+                    float4* dst = reinterpret_cast<float4*>(p.out_f32 + (size_t)(OB200_GUARD + pos) * p.cout + nh * kN + half * 64);
+                    const float* bias_f = bias_s + nh * kN + half * 64;
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        if (valid) {
+                            o.x = __uint_as_float(r[4 * c]) + bias_f[4 * c];
+                            o.y = __uint_as_float(r[4 * c + 1]) + bias_f[4 * c + 1];
+                            o.z = __uint_as_float(r[4 * c + 2]) + bias_f[4 * c + 2];
+                            o.w = __uint_as_float(r[4 * c + 3]) + bias_f[4 * c + 3];
+                            if (p.relu) { o.x = fmaxf(o.x, 0.0f); o.y = fmaxf(o.y, 0.0f); o.z = fmaxf(o.z, 0.0f); o.w = fmaxf(o.w, 0.0f); }
+                        }
+                        dst[c] = o;
+                    }
+                    continue;
+                }
                 if (has_res) {
                     if (!mbar_wait(res_bar(group), res_phase, abort_flag)) { ok = false; break; }
                     res_phase ^= 1u;
@@ -428,7 +447,7 @@ int conv_wide_box_rows() { return kBoxRows; }
 
 int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const BoardTensorMap* res_map,
                           const void* packed_w, const float* bias, int B, int S, int cin, int cout, int taps, int relu,
-                          cudaStream_t st) {
+                          cudaStream_t st, float* out_f32) {
     if (!packed_w || !bias || B <= 0) return set_error(OB200_ERR_INVALID, "conv (wide): null pointer or empty batch");
     if (!conv_wide_covers(cin, cout) || (taps != 9 && taps != 1))
         return set_error(OB200_ERR_UNSUPPORTED, "conv (wide): %d -> %d channels with %d taps is not covered", cin, cout, taps);
@@ -449,6 +468,8 @@ int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& ou
     const BoardGeom g = board_geom(S, B);
     WideParams p;
     p.w = static_cast<const uint8_t*>(packed_w); p.bias = bias; p.has_residual = res_map != nullptr;
+    p.out_f32 = out_f32;
+    if (out_f32 && res_map) return set_error(OB200_ERR_INVALID, "conv (wide): fp32 output takes no residual");
     p.error = device_error_word();
     if (!p.error) return set_error(OB200_ERR_CUDA, "conv (wide): cannot resolve the device error word");
     p.P = (int)g.P; p.num_tiles = (int)(g.Ppad / kTileM); p.m_units = (p.num_tiles + kUnitTiles - 1) / kUnitTiles;

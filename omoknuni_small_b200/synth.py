@@ -135,9 +135,11 @@ def make_stone_planes(B, board_size=15, channels=17, seed=1000, max_stones=100, 
 
 
 def net_tensor_shapes(board_size, input_channels, filters, blocks, policy_size, policy_head_ch=32,
-                      value_head_ch=32, value_hidden=256):
+                      value_head_ch=32, value_hidden=256, policy_planes=False):
     """Names and shapes of the reference module's parameters and buffers
-    (reference src/nn/resnet_model.cpp:51-102), in registration order."""
+    (reference src/nn/resnet_model.cpp:51-102), in registration order.
+    policy_planes: the convolutional policy head (1x1 convolution with bias to
+    policy_head_ch planes, no BatchNorm, no FC) instead of the reference's."""
     S2 = board_size * board_size
     out = []
 
@@ -153,9 +155,12 @@ def net_tensor_shapes(board_size, input_channels, filters, blocks, policy_size, 
         out.append((f"res_blocks.{i}.conv2.weight", (filters, filters, 3, 3)))
         bn(f"res_blocks.{i}.bn2", filters)
     out.append(("policy_conv.weight", (policy_head_ch, filters, 1, 1)))
-    bn("policy_bn", policy_head_ch)
-    out.append(("policy_fc.weight", (policy_size, policy_head_ch * S2)))
-    out.append(("policy_fc.bias", (policy_size,)))
+    if policy_planes:
+        out.append(("policy_conv.bias", (policy_head_ch,)))
+    else:
+        bn("policy_bn", policy_head_ch)
+        out.append(("policy_fc.weight", (policy_size, policy_head_ch * S2)))
+        out.append(("policy_fc.bias", (policy_size,)))
     out.append(("value_conv.weight", (value_head_ch, filters, 1, 1)))
     bn("value_bn", value_head_ch)
     out.append(("value_fc1.weight", (value_hidden, value_head_ch * S2)))

@@ -44,8 +44,11 @@ def forward(weights, planes, blocks=None, threads=0, return_tower=False):
             y = _bn(F.conv2d(y, w[p + "conv2.weight"], padding=1), w, p + "bn2")
             x = F.relu(y + x)
         tower = x
-        pol = F.relu(_bn(F.conv2d(x, w["policy_conv.weight"]), w, "policy_bn"))               # :178
-        logits = F.linear(pol.reshape(pol.shape[0], -1), w["policy_fc.weight"], w["policy_fc.bias"])  # :183-188
+        if "policy_fc.weight" in w:
+            pol = F.relu(_bn(F.conv2d(x, w["policy_conv.weight"]), w, "policy_bn"))               # :178
+            logits = F.linear(pol.reshape(pol.shape[0], -1), w["policy_fc.weight"], w["policy_fc.bias"])  # :183-188
+        else:   # convolutional policy head (not in the reference): planes flattened in NCHW order
+            logits = F.conv2d(x, w["policy_conv.weight"], w["policy_conv.bias"]).reshape(x.shape[0], -1)
         val = F.relu(_bn(F.conv2d(x, w["value_conv.weight"]), w, "value_bn"))                 # :204
         val = F.relu(F.linear(val.reshape(val.shape[0], -1), w["value_fc1.weight"], w["value_fc1.bias"]))  # :214
         val = torch.tanh(F.linear(val, w["value_fc2.weight"], w["value_fc2.bias"]))          # :219
@@ -99,9 +102,12 @@ def forward_bf16(weights, planes, blocks=None):
             y = _bf16(F.relu(F.conv2d(x, _bf16(wf), padding=1) + b[None, :, None, None]))
             wf, b = fold(p + "conv2", p + "bn2")
             x = _bf16(F.relu(F.conv2d(y, _bf16(wf), padding=1) + b[None, :, None, None] + x))
-        wf, b = fold("policy_conv", "policy_bn")
-        pol = F.relu(F.conv2d(x, wf) + b[None, :, None, None])
-        logits = F.linear(pol.reshape(pol.shape[0], -1), w["policy_fc.weight"], w["policy_fc.bias"])
+        if "policy_fc.weight" in w:
+            wf, b = fold("policy_conv", "policy_bn")
+            pol = F.relu(F.conv2d(x, wf) + b[None, :, None, None])
+            logits = F.linear(pol.reshape(pol.shape[0], -1), w["policy_fc.weight"], w["policy_fc.bias"])
+        else:   # convolutional policy head: bf16 weights on the tensor cores, fp32 accumulate and output
+            logits = F.conv2d(x, _bf16(w["policy_conv.weight"]), w["policy_conv.bias"]).reshape(x.shape[0], -1)
         wf, b = fold("value_conv", "value_bn")
         val = F.relu(F.conv2d(x, wf) + b[None, :, None, None])
         val = F.relu(F.linear(val.reshape(val.shape[0], -1), w["value_fc1.weight"], w["value_fc1.bias"]))

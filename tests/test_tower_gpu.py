@@ -99,78 +99,69 @@ def test_conv3x3_layer_wide(api, B, S, cin_real, cin, cout, residual, relu):
 
 
 def make_net(api, w, cfg, max_batch):
-    return api.Net(cfg["cin"], cfg["S"], cfg["blocks"], cfg["F"], cfg["A"], cfg["pc"], cfg["vc"], 256, max_batch).load(w)
+    return api.Net(cfg["cin"], cfg["S"], cfg["blocks"], cfg["F"], cfg["A"], cfg["pc"], cfg["vc"], 256, max_batch,
+                   policy_kind=cfg.get("kind", 0)).load(w)
 
 
-def test_network_matches_reference_golden_default_init(api):
-    """The reference module with its own libtorch initialisation (fixture (a))."""
+def mixed_planes(B, S, C, scalar_planes, seed):
+    """Binary planes (p = 0.1) followed by `scalar_planes` planes uniform in [0, 1]."""
+    rng = np.random.default_rng(seed)
+    x = (rng.random((B, C, S, S)) < 0.1).astype(np.float32)
+    if scalar_planes:
+        x[:, C - scalar_planes:] = rng.random((B, scalar_planes, S, S)).astype(np.float32)
+    return x
+
+
+WIDE_NETS = [
+    # Go 19x19 shape: 128 filters, policy 362, 2 / 1-channel heads
+    ("go19_f128", dict(cin=17, S=19, blocks=4, F=128, A=362, pc=2, vc=1), 12, 0),
+    # the reference's own head widths on a 128-filter tower
+    ("go19_f128_heads32", dict(cin=17, S=19, blocks=2, F=128, A=362, pc=32, vc=32), 5, 0),
+    # 15x15 with 256 filters and 19 planes
+    ("gomoku15_f256", dict(cin=19, S=15, blocks=2, F=256, A=225, pc=2, vc=1), 9, 0),
+    # chess shape: 119 planes (7 real-valued), 256 filters, 73 policy planes -> 4672 logits
+    ("chess8_f256_planes", dict(cin=119, S=8, blocks=3, F=256, A=4672, pc=73, vc=1, kind=1), 37, 7),
+    ("chess8_f128_planes", dict(cin=119, S=8, blocks=2, F=128, A=4672, pc=73, vc=1, kind=1), 6, 7),
+]
+
+
+@pytest.mark.parametrize("name,cfg,B,scalar", WIDE_NETS, ids=[n[0] for n in WIDE_NETS])
+def test_network_wide_towers(api, name, cfg, B, scalar):
+    """Towers of 128 / 256 filters (streamed-weight kernel), FC and convolution-plane policy
+    heads, against the fp32 forward; libtorch-default initialisation with random BatchNorm."""
     from oracle import net_ref
-    cfg, w, x, logp, value = load_net_golden_a()
-    net = make_net(api, w, cfg, 16)
+    shapes = synth.net_tensor_shapes(cfg["S"], cfg["cin"], cfg["F"], cfg["blocks"], cfg["A"], cfg["pc"], cfg["vc"],
+                                     policy_planes=cfg.get("kind", 0) == 1)
+    w = synth.make_weights(shapes, seed=11, init="torch_default", bn="random")
+    x = mixed_planes(B, cfg["S"], cfg["cin"], scalar, seed=2000 + B)
+    ref_logits, ref_v = net_ref.forward(w, x)
+    net = make_net(api, w, cfg, B + 3)
     logits, v = net.infer_planes(x, api.OUT_LOGITS)
-    assert np.abs(net_ref.log_softmax(logits) - logp).max() <= POLICY_TOL
-    assert np.abs(v - value).max() <= VALUE_TOL
-    probs, v2 = net.infer_planes(x, api.OUT_PROBS)
-    assert np.abs(probs - np.exp(logp)).max() <= 1e-3 and np.allclose(probs.sum(1), 1, atol=1e-5)
-    assert np.array_equal(v, v2)
+    assert logits.shape == ref_logits.shape
+    assert np.abs(logits - ref_logits).max() <= POLICY_TOL, np.abs(logits - ref_logits).max()
+    assert np.abs(v - ref_v).max() <= VALUE_TOL
+    probs, _ = net.infer_planes(x, api.OUT_PROBS)
+    assert np.abs(probs - net_ref.softmax(ref_logits)).max() <= 1e-3 and np.allclose(probs.sum(1), 1, atol=1e-5)
 
 
-def test_network_matches_reference_golden_15x15(api):
-    """15x15, 10 blocks, reference 32/32 heads, seeded weights + random BatchNorm (fixture (b))."""
+def test_network_wide_tower_full_depth(api):
+    """Go shape at the benchmark's depth (20 blocks x 128 filters, 41 tensor-core layers in a row)
+    with the libtorch-default initialisation and random BatchNorm statistics, at the standard
+    tolerances.  (Kaiming-normal weights with identity BatchNorm double the residual stream's
+    variance per block: over 20 blocks the logits reach the hundreds and tanh saturates, which
+    tests nothing.)"""
     from oracle import net_ref
-    w, x, logp, value = load_net_golden_b()
-    cfg = dict(cin=17, S=15, blocks=10, F=64, A=225, pc=32, vc=32)
+    cfg = dict(cin=17, S=19, blocks=20, F=128, A=362, pc=2, vc=1)
+    shapes = synth.net_tensor_shapes(19, 17, 128, 20, 362, 2, 1)
+    w = synth.make_weights(shapes, seed=43, init="torch_default", bn="random")
+    x = mixed_planes(6, 19, 17, 0, seed=77)
+    ref_logits, ref_v = net_ref.forward(w, x)
     net = make_net(api, w, cfg, 8)
     logits, v = net.infer_planes(x, api.OUT_LOGITS)
-    assert np.abs(net_ref.log_softmax(logits) - logp).max() <= POLICY_TOL
-    assert np.abs(v - value).max() <= VALUE_TOL
-
-
-@pytest.mark.parametrize("heads", [(2, 1), (32, 32)])
-def test_network_torch_default_init_benchmark_shape(api, heads):
-    """Benchmark network shape with the distribution the reference's C++ model is born with."""
-    from oracle import net_ref
-    shapes = synth.net_tensor_shapes(15, 17, 64, 10, 225, heads[0], heads[1])
-    w = synth.make_weights(shapes, seed=3, init="torch_default", bn="identity")
-    x = synth.make_stone_planes(64, 15, 17, seed=1001)
-    ref_logits, ref_v = net_ref.forward(w, x)
-    net = make_net(api, w, dict(cin=17, S=15, blocks=10, F=64, A=225, pc=heads[0], vc=heads[1]), 64)
-    logits, v = net.infer_planes(x, api.OUT_LOGITS)
-    assert np.abs(logits - ref_logits).max() <= POLICY_TOL
-    assert np.abs(v - ref_v).max() <= VALUE_TOL
-
-
-def test_network_kaiming_normal_benchmark_weights(api):
-    """The benchmark's weights (Kaiming-normal convolutions with ReLU gain, identity BatchNorm,
-    2/1-channel heads).  With this initialisation the residual stream doubles in variance per
-    block, and ANY pipeline that stores activations in bf16 (8 significant bits, 21 layers)
-    lands about 0.1 (logits) / 0.02 (value) away from fp32: the fp32-arithmetic emulation of
-    bf16 storage (oracle/net_ref.forward_bf16) is that far from fp32 itself, and two bf16
-    implementations differ from each other by a similar amount because one flipped rounding
-    early on is amplified by the later layers.  The kernels' own arithmetic is held to a tight
-    bound by test_conv3x3_layer; here the device's gap to fp32 must not exceed the emulation's
-    gap by more than half, and the preferred move must agree wherever fp32's margin is clear."""
-    from oracle import net_ref
-    shapes = synth.net_tensor_shapes(15, 17, 64, 10, 225, 2, 1)
-    w = synth.make_weights(shapes, seed=42, init="kaiming_normal", bn="identity")
-    x = synth.make_stone_planes(256, 15, 17, seed=1000)
-    ref_logits, ref_v = net_ref.forward(w, x)
-    emu_logits, emu_v = net_ref.forward_bf16(w, x)
-    net = make_net(api, w, dict(cin=17, S=15, blocks=10, F=64, A=225, pc=2, vc=1), 256)
-    logits, v = net.infer_planes(x, api.OUT_LOGITS)
-    k_err, kv_err = np.abs(logits - emu_logits).max(), np.abs(v - emu_v).max()
     f_err, fv_err = np.abs(logits - ref_logits).max(), np.abs(v - ref_v).max()
-    e_err = np.abs(emu_logits - ref_logits).max()
-    print(f"kaiming-normal: max|logit| {np.abs(ref_logits).max():.2f}; device vs bf16 emulation {k_err:.4f} / {kv_err:.4f}; "
-          f"device vs fp32 {f_err:.4f} / {fv_err:.4f}; bf16 emulation vs fp32 {e_err:.4f}")
-    ev_err = np.abs(emu_v - ref_v).max()
-    assert f_err <= 1.5 * e_err + POLICY_TOL and fv_err <= 1.5 * ev_err + VALUE_TOL
-    assert k_err <= 2 * e_err and kv_err <= 2 * ev_err + VALUE_TOL
-    # the preferred move agrees wherever the fp32 margin exceeds twice the gap
-    order = np.argsort(ref_logits, 1)
-    rows = np.arange(len(order))
-    margin = ref_logits[rows, order[:, -1]] - ref_logits[rows, order[:, -2]]
-    assert (logits.argmax(1) == order[:, -1])[margin > 2 * f_err].all()
+    print(f"go 20x128: max|logit| {np.abs(ref_logits).max():.3f}, max|value| {np.abs(ref_v).max():.3f}; device vs fp32 {f_err:.5f} / {fv_err:.5f}")
+    assert np.abs(ref_logits).max() > 0.05          # the comparison is not vacuous
+    assert f_err <= POLICY_TOL and fv_err <= VALUE_TOL
 
 
 def test_gomoku_inference_end_to_end(api, oracle):
@@ -207,4 +198,4 @@ def test_inference_argument_errors(api):
         net.infer_planes(np.zeros((5, 17, 15, 15), np.float32))
     assert e.value.code == 7                                   # beyond max_batch
     with pytest.raises(api.Error):
-        api.Net(17, 15, 1, 128, 225)                           # tower width outside this build
+        api.Net(17, 15, 1, 96, 225)                            # tower width outside this build
