@@ -157,6 +157,71 @@ def reference_arm(args):
     print(json.dumps(line))
 
 
+WIDE_NETS = [
+    dict(name="go19x19 resnet 20x128, policy FC 362 (2/1-channel heads)", S=19, cin=17, F=128, blocks=20, A=362, pc=2, vc=1,
+         kind=0, B=2048, scalar=0),
+    dict(name="chess8x8 resnet 20x256, 119 planes, 73 policy planes (4672 logits)", S=8, cin=119, F=256, blocks=20, A=4672,
+         pc=73, vc=1, kind=1, B=4096, scalar=7),
+]
+
+
+def time_wide_net(capi, torch, wc, dev, local, rank, flush, timed, steps):
+    """Forward of one wide-tower configuration on a device-resident input board tensor, and its
+    dominant kernel (F -> F convolution with residual) alone."""
+    S, F, B = wc["S"], wc["F"], wc["B"]
+    shapes = synth.net_tensor_shapes(S, wc["cin"], F, wc["blocks"], wc["A"], wc["pc"], wc["vc"], policy_planes=wc["kind"] == 1)
+    w = synth.make_weights(shapes, seed=42, init="torch_default", bn="random")
+    net = capi.Net(wc["cin"], S, wc["blocks"], F, wc["A"], wc["pc"], wc["vc"], 256, B, local, policy_kind=wc["kind"]).load(w)
+    rng = np.random.default_rng(replicas.shard_seed(3000, rank))
+    planes = (rng.random((B, wc["cin"], S, S)) < 0.1).astype(np.float32)
+    if wc["scalar"]:
+        planes[:, wc["cin"] - wc["scalar"]:] = rng.random((B, wc["scalar"], S, S)).astype(np.float32)
+    bt = capi.planes_to_board_tensor(torch.from_numpy(planes).to(dev), net.input_tensor_channels())
+    pol = torch.empty((B, wc["A"]), dtype=torch.float32, device=dev)
+    val = torch.empty(B, dtype=torch.float32, device=dev)
+
+    def fwd():
+        net.forward_device(bt, B, pol, val, capi.OUT_PROBS)
+    for _ in range(3):
+        fwd()
+    ms = float(np.mean(timed(fwd, steps)))
+    rngw = np.random.default_rng(0)
+    wp = torch.from_numpy(capi.pack_conv3x3(rngw.normal(0, 0.03, (F, F, 3, 3)).astype(np.float32), None, F).view(np.int16)).to(dev)
+    bias = torch.zeros(F, device=dev)
+    n_el = int(capi.lib().ob200_board_tensor_bytes(S, B, F)) // 2
+    bufs = [torch.zeros(n_el, dtype=torch.int16, device=dev) for _ in range(3)]
+    reps = 10
+
+    def conv_loop():
+        for i in range(reps):
+            capi.conv3x3(bufs[i % 3], wp, bias, bufs[(i + 2) % 3], B, S, F, F, True, out=bufs[(i + 1) % 3])
+    conv_loop()
+    conv_ms = float(np.mean(timed(conv_loop, 3))) / reps
+    net.close()
+    return dict(cfg=wc, ms=ms, conv_ms=conv_ms)
+
+
+def wide_report(wr, world, peaks):
+    wc = wr["cfg"]
+    S2 = wc["S"] * wc["S"]
+    if wc["kind"] == 1:     # convolutional policy head: 1x1 convolution to the planes, no FC
+        flops = (synth.net_flops_per_eval(wc["S"], wc["cin"], wc["F"], wc["blocks"], 0, 0, wc["vc"])
+                 + 2 * S2 * wc["F"] * wc["pc"])
+    else:
+        flops = synth.net_flops_per_eval(wc["S"], wc["cin"], wc["F"], wc["blocks"], wc["A"], wc["pc"], wc["vc"])
+    conv_tf = 2.0 * S2 * 9 * wc["F"] * wc["F"] * wc["B"] / (wr["conv_ms"] * 1e-3) / 1e12
+    evals = world * wc["B"] / (wr["ms"] * 1e-3)
+    return {"workload": wc["name"], "batch_per_gpu": wc["B"], "value": evals, "unit": UNIT, "ms_per_step": wr["ms"],
+            "tower_tflops": evals / world * flops / 1e12, "flops_per_eval": flops,
+            "weights": "libtorch-default init seed 42, random BatchNorm", "input": "device-resident board tensor",
+            "roofline": {"kernel": f"conv_wide_kernel ({wc['F']}->{wc['F']}, residual+ReLU)", "bound": "tensor",
+                         "achieved": conv_tf, "peak": peaks["bf16_burst"], "unit": "TFLOP/s",
+                         "frac": conv_tf / peaks["bf16_burst"],
+                         "frac_of_sustained": conv_tf / peaks["bf16_sustained"] if peaks["bf16_sustained"] else None,
+                         "us_per_launch": wr["conv_ms"] * 1e3,
+                         "flops": "real board cells only; the padded (S+1)^2 grid the kernel computes is not counted"}}
+
+
 def gpu_arm(args):
     import torch
     from omoknuni_small_b200 import capi
@@ -279,10 +344,19 @@ def gpu_arm(args):
             mcts_ms += st["device_ms"]; mcts_sims += st["simulations"]; mcts_evals += st["evaluations"]
             mcts_nodes = st["nodes"]
         torch.cuda.synchronize()
+        search.close()
+        # ---- the wider towers (parity-test configurations timed for their roofline): Go 19x19 20x128 at
+        # batch 2048, chess 8x8 20x256 with 73 policy planes at batch 4096; forward on a resident input ----
+        wide = []
+        for wc in WIDE_NETS:
+            wide.append(time_wide_net(capi, torch, wc, dev, local, rank, flush, timed, min(K, 5)))
     assert capi.device_error_code() == 0, "a kernel gave up on a bounded wait"
 
-    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms = replicas.max_over_ranks(
-        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms], dev)
+    reduced = replicas.max_over_ranks(
+        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
+    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms = reduced[:6]
+    for i, wr in enumerate(wide):
+        wr["ms"], wr["conv_ms"] = reduced[6 + 2 * i], reduced[7 + 2 * i]
     totals = replicas.sum_counters(dist, capi.counters(), dev)   # the only cross-GPU step: per-GPU counters summed
     if rank == 0:
         flops_eval = synth.net_flops_per_eval(15, 17, 64, NET["blocks"], 225, NET["policy_head_ch"], NET["value_head_ch"])
@@ -326,6 +400,7 @@ def gpu_arm(args):
                                 "dirichlet": [0.3, 0.25], "openings": "seeded random, 0-20 stones", "moves_timed": mcts_moves,
                                 "transposition_table": "on (device table, Zobrist keys)", "nodes_per_move": mcts_nodes},
                      "ms_per_move": mcts_ms / mcts_moves, "timing": "CUDA events around each move, inside the library"},
+            "wide_towers": [wide_report(wr, world, peaks) for wr in wide],
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu:
