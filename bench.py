@@ -222,6 +222,32 @@ def wide_report(wr, world, peaks):
                          "flops": "real board cells only; the padded (S+1)^2 grid the kernel computes is not counted"}}
 
 
+def wide_only(args):
+    """Only the wide-tower section, single GPU: one JSON line with its entries."""
+    import torch
+    from omoknuni_small_b200 import capi
+    torch.cuda.set_device(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")
+
+    def timed(fn, n, per_iter_flush=True):
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for s, e in ev:
+            if per_iter_flush:
+                flush.zero_()
+            s.record()
+            fn()
+            e.record()
+        torch.cuda.synchronize()
+        return [s.elapsed_time(e) for s, e in ev]
+    peaks = measured_peaks()
+    out = []
+    for wc in WIDE_NETS:
+        wc = dict(wc, B=args.wide_batch or wc["B"])
+        out.append(wide_report(time_wide_net(capi, torch, wc, "cuda:0", 0, 0, flush, timed, max(1, min(args.steps, 5))), 1, peaks))
+    assert capi.device_error_code() == 0, "a kernel gave up on a bounded wait"
+    print(json.dumps({"wide_towers": out}))
+
+
 def gpu_arm(args):
     import torch
     from omoknuni_small_b200 import capi
@@ -421,9 +447,14 @@ def main():
     ap.add_argument("--batch", type=int, default=1024, help="leaf batch per GPU")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--wide-only", action="store_true",
+                    help="time only the Go / chess towers (a short run for profiling; not the contract line)")
+    ap.add_argument("--wide-batch", type=int, default=0, help="with --wide-only: batch for both towers")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
+    elif args.wide_only:
+        wide_only(args)
     else:
         gpu_arm(args)
 
