@@ -141,7 +141,10 @@ int ob200_launch_set_priors(const ob200_tree_view* tree, const int32_t* node_ids
  * selection above followed by VL += vl_value on the chosen edge, so that
  * simulation k sees the virtual loss of simulations < k of the same tree.
  * Descent stops at an edge whose child_node is -1 (leaf to expand) or after
- * max_depth steps.  paths_out [n_trees*sims_per_tree][max_depth][2],
+ * max_depth steps.  (The simulations of a tree overlap as a wavefront, one
+ * level apart; the result is that of running them one after another as long
+ * as every node is reached at a single depth below its root, which holds for
+ * trees and for games in which every move adds a stone.)  paths_out [n_trees*sims_per_tree][max_depth][2],
  * path_len_out [n_trees*sims_per_tree].
  * Replaces phase 1 of MCTSEngine::executeBatchedTreeSearch
  * (src/mcts/mcts_engine_batch_tree_simple.cpp:73-185) and

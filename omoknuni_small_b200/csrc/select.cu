@@ -413,38 +413,65 @@ set_priors_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids, int n
     }
 }
 
-// One warp per tree, simulations of a tree in sequence so that each sees the
-// virtual loss left by the ones before it.
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+// One CTA per tree.  Simulations of a tree are ordered: simulation k must see the virtual loss
+// that simulations < k left on every edge it scores.  They still overlap as a wavefront: the CTA
+// advances in steps, a simulation takes one level per step, and simulation k starts at least one
+// step after simulation k - 1, so when k scores the edges at depth d, every earlier simulation
+// has already passed depth d (virtual loss is per edge, and edges below depth d do not enter the
+// scores at depth d).  sims + depth steps instead of sims x depth.  The order is the sequential
+// one as long as a node is reached at one depth only (a tree; a game in which every move adds a
+// stone): two simulations can then never be at the same node in the same step.
+constexpr int kTravWarps = 16;
+__global__ void __launch_bounds__(kTravWarps * 32)
 traverse_kernel(ob200_tree_view t, const int32_t* __restrict__ roots, int n_trees,
                 int sims_per_tree, float c_puct, int vl_value, int max_depth,
                 int32_t* __restrict__ paths_out, int32_t* __restrict__ path_len_out) {
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (warp >= n_trees) return;
-    const int root = roots[warp];
-    for (int k = 0; k < sims_per_tree; ++k) {
-        const size_t sim = (size_t)warp * sims_per_tree + k;
-        int32_t* path = paths_out + sim * max_depth * 2;
-        int node = root, depth = 0;
-        while (depth < max_depth && node >= 0 && node < t.n_nodes) {
-            const int sel = select_row<false>(t, node, c_puct, lane);
-            if (sel < 0) break;
-            int next = -1;
-            if (lane == 0) {
-                const size_t e = (size_t)node * t.pitch + sel;
-                if (vl_value > 0) atomicAdd(t.VL + e, vl_value);
-                path[2 * depth] = node;
-                path[2 * depth + 1] = sel;
-                next = t.child_node ? __ldcg(t.child_node + e) : -1;
-            }
-            __threadfence();
-            next = __shfl_sync(0xffffffffu, next, 0);
-            ++depth;
-            node = next;
+    __shared__ int n_started, n_finished;
+    const int tree = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) { n_started = 0; n_finished = 0; }
+    __syncthreads();
+    const int root = roots[tree];
+    int k = -1;            // simulation this warp is running, -1 = idle
+    int my_next = warp;    // next simulation this warp owns (k = warp mod kTravWarps)
+    int depth = 0, node = -1;
+    while (true) {
+        const int started = n_started, finished = n_finished;
+        if (finished >= sims_per_tree) break;
+        bool start_now = false;
+        if (k < 0 && my_next == started && my_next < sims_per_tree) {
+            k = my_next; my_next += kTravWarps; depth = 0; node = root; start_now = true;
         }
-        if (lane == 0) path_len_out[sim] = depth;
-        __syncwarp();
+        __syncthreads();   // every warp has read the counters before any warp updates them
+        if (k >= 0) {
+            const size_t sim = (size_t)tree * sims_per_tree + k;
+            bool done = true;
+            if (depth < max_depth && node >= 0 && node < t.n_nodes) {
+                const int sel = select_row<false>(t, node, c_puct, lane);
+                if (sel >= 0) {
+                    int next = -1;
+                    if (lane == 0) {
+                        const size_t e = (size_t)node * t.pitch + sel;
+                        if (vl_value > 0) atomicAdd(t.VL + e, vl_value);
+                        int32_t* path = paths_out + sim * max_depth * 2;
+                        path[2 * depth] = node;
+                        path[2 * depth + 1] = sel;
+                        next = t.child_node ? __ldcg(t.child_node + e) : -1;
+                    }
+                    __threadfence();
+                    next = __shfl_sync(0xffffffffu, next, 0);
+                    ++depth;
+                    node = next;
+                    done = !(depth < max_depth && node >= 0 && node < t.n_nodes);
+                }
+            }
+            if (lane == 0) {
+                if (done) { path_len_out[sim] = depth; atomicAdd(&n_finished, 1); }
+                if (start_now) atomicAdd(&n_started, 1);
+            }
+            if (done) k = -1;
+        }
+        __syncthreads();
     }
 }
 
@@ -566,8 +593,8 @@ int ob200_launch_traverse(const ob200_tree_view* tree, const int32_t* roots, int
         return set_error(OB200_ERR_INVALID, "ob200_launch_traverse: bad arguments");
     if (int rc = require_device()) return rc;
     if (n_trees == 0) return OB200_OK;
-    // one warp per block: trees are few and latency-bound, so spread them over the SMs
-    traverse_kernel<<<n_trees, 32, 0, as_stream(stream)>>>(*tree, roots, n_trees, sims_per_tree, c_puct,
+    // one CTA per tree: trees are few and latency-bound, so spread them over the SMs
+    traverse_kernel<<<n_trees, kTravWarps * 32, 0, as_stream(stream)>>>(*tree, roots, n_trees, sims_per_tree, c_puct,
                                                                           vl_value, max_depth, paths_out, path_len_out);
     OB200_LAUNCHED("traverse_kernel");
     counters().selections.fetch_add((uint64_t)n_trees * sims_per_tree, std::memory_order_relaxed);

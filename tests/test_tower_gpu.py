@@ -164,6 +164,77 @@ def test_network_wide_tower_full_depth(api):
     assert f_err <= POLICY_TOL and fv_err <= VALUE_TOL
 
 
+def test_network_matches_reference_golden_default_init(api):
+    """The reference module with its own libtorch initialisation (fixture (a))."""
+    from oracle import net_ref
+    cfg, w, x, logp, value = load_net_golden_a()
+    net = make_net(api, w, cfg, 16)
+    logits, v = net.infer_planes(x, api.OUT_LOGITS)
+    assert np.abs(net_ref.log_softmax(logits) - logp).max() <= POLICY_TOL
+    assert np.abs(v - value).max() <= VALUE_TOL
+    probs, v2 = net.infer_planes(x, api.OUT_PROBS)
+    assert np.abs(probs - np.exp(logp)).max() <= 1e-3 and np.allclose(probs.sum(1), 1, atol=1e-5)
+    assert np.array_equal(v, v2)
+
+
+def test_network_matches_reference_golden_15x15(api):
+    """15x15, 10 blocks, reference 32/32 heads, seeded weights + random BatchNorm (fixture (b))."""
+    from oracle import net_ref
+    w, x, logp, value = load_net_golden_b()
+    cfg = dict(cin=17, S=15, blocks=10, F=64, A=225, pc=32, vc=32)
+    net = make_net(api, w, cfg, 8)
+    logits, v = net.infer_planes(x, api.OUT_LOGITS)
+    assert np.abs(net_ref.log_softmax(logits) - logp).max() <= POLICY_TOL
+    assert np.abs(v - value).max() <= VALUE_TOL
+
+
+@pytest.mark.parametrize("heads", [(2, 1), (32, 32)])
+def test_network_torch_default_init_benchmark_shape(api, heads):
+    """Benchmark network shape with the distribution the reference's C++ model is born with."""
+    from oracle import net_ref
+    shapes = synth.net_tensor_shapes(15, 17, 64, 10, 225, heads[0], heads[1])
+    w = synth.make_weights(shapes, seed=3, init="torch_default", bn="identity")
+    x = synth.make_stone_planes(64, 15, 17, seed=1001)
+    ref_logits, ref_v = net_ref.forward(w, x)
+    net = make_net(api, w, dict(cin=17, S=15, blocks=10, F=64, A=225, pc=heads[0], vc=heads[1]), 64)
+    logits, v = net.infer_planes(x, api.OUT_LOGITS)
+    assert np.abs(logits - ref_logits).max() <= POLICY_TOL
+    assert np.abs(v - ref_v).max() <= VALUE_TOL
+
+
+def test_network_kaiming_normal_benchmark_weights(api):
+    """The benchmark's weights (Kaiming-normal convolutions with ReLU gain, identity BatchNorm,
+    2/1-channel heads).  With this initialisation the residual stream doubles in variance per
+    block, and ANY pipeline that stores activations in bf16 (8 significant bits, 21 layers)
+    lands about 0.1 (logits) / 0.02 (value) away from fp32: the fp32-arithmetic emulation of
+    bf16 storage (oracle/net_ref.forward_bf16) is that far from fp32 itself, and two bf16
+    implementations differ from each other by a similar amount because one flipped rounding
+    early on is amplified by the later layers.  The kernels' own arithmetic is held to a tight
+    bound by test_conv3x3_layer; here the device's gap to fp32 must not exceed the emulation's
+    gap by more than half, and the preferred move must agree wherever fp32's margin is clear."""
+    from oracle import net_ref
+    shapes = synth.net_tensor_shapes(15, 17, 64, 10, 225, 2, 1)
+    w = synth.make_weights(shapes, seed=42, init="kaiming_normal", bn="identity")
+    x = synth.make_stone_planes(256, 15, 17, seed=1000)
+    ref_logits, ref_v = net_ref.forward(w, x)
+    emu_logits, emu_v = net_ref.forward_bf16(w, x)
+    net = make_net(api, w, dict(cin=17, S=15, blocks=10, F=64, A=225, pc=2, vc=1), 256)
+    logits, v = net.infer_planes(x, api.OUT_LOGITS)
+    k_err, kv_err = np.abs(logits - emu_logits).max(), np.abs(v - emu_v).max()
+    f_err, fv_err = np.abs(logits - ref_logits).max(), np.abs(v - ref_v).max()
+    e_err = np.abs(emu_logits - ref_logits).max()
+    print(f"kaiming-normal: max|logit| {np.abs(ref_logits).max():.2f}; device vs bf16 emulation {k_err:.4f} / {kv_err:.4f}; "
+          f"device vs fp32 {f_err:.4f} / {fv_err:.4f}; bf16 emulation vs fp32 {e_err:.4f}")
+    ev_err = np.abs(emu_v - ref_v).max()
+    assert f_err <= 1.5 * e_err + POLICY_TOL and fv_err <= 1.5 * ev_err + VALUE_TOL
+    assert k_err <= 2 * e_err and kv_err <= 2 * ev_err + VALUE_TOL
+    # the preferred move agrees wherever the fp32 margin exceeds twice the gap
+    order = np.argsort(ref_logits, 1)
+    rows = np.arange(len(order))
+    margin = ref_logits[rows, order[:, -1]] - ref_logits[rows, order[:, -2]]
+    assert (logits.argmax(1) == order[:, -1])[margin > 2 * f_err].all()
+
+
 def test_gomoku_inference_end_to_end(api, oracle):
     """Host move histories -> encoder -> tower -> heads, against oracle encoder + fp32 forward,
     including a batch smaller than max_batch after a larger one (buffer reuse)."""
