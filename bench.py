@@ -40,6 +40,7 @@ from omoknuni_small_b200 import replicas, synth  # noqa: E402
 NET = dict(board_size=15, input_channels=17, filters=64, blocks=10, policy_size=225, policy_head_ch=2,
            value_head_ch=1, value_hidden=256)
 SEL_NODES, SEL_CHILDREN = 65536, 225
+SELW_NODES, SELW_CHILDREN = 2048, 4672      # chess-wide child rows (154 MB per pass)
 METRIC, UNIT = "nn_leaf_evals_per_sec", "evals/s"
 
 
@@ -307,14 +308,20 @@ def gpu_arm(args):
         launches = capi.counters()["kernel_launches"] - c0
         total_ms = float(sum(ms))
         # ---- e2e: host buffers through the public call ----
+        # inputs and outputs in page-locked host memory, allocated once (as an engine would keep them)
+        pin = [torch.from_numpy(a).pin_memory() for a in (hist, nh, tm)]
+        p_hist, p_nh, p_tm = (t_.numpy() for t_ in pin)
+        out_pol = torch.empty((B, 225), dtype=torch.float32).pin_memory()
+        out_val = torch.empty(B, dtype=torch.float32).pin_memory()
+        outs = (out_pol.numpy(), out_val.numpy())
         for _ in range(2):
-            net.infer_gomoku(hist, nh, tm)
+            net.infer_gomoku(p_hist, p_nh, p_tm, out=outs)
         e2e_s = 0.0
         for _ in range(K):
             flush.zero_()
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            net.infer_gomoku(hist, nh, tm)
+            net.infer_gomoku(p_hist, p_nh, p_tm, out=outs)
             e2e_s += time.perf_counter() - t0
         # ---- the dominant kernel alone: 64 -> 64 conv with residual + ReLU ----
         rng = np.random.default_rng(0)
@@ -355,6 +362,18 @@ def gpu_arm(args):
         sel_ms = float(np.mean(timed(sel_pass_loop, 5, per_iter_flush=False))) / sel_reps
         selk_ms = float(np.mean(timed(sel_only_loop, 5, per_iter_flush=False))) / sel_reps
         dt.t["VL"].copy_(torch.from_numpy(t["VL"]).to(dev))
+        # ---- the same pass over chess-wide rows: 2,048 nodes x 4,672 children (154 MB per pass) ----
+        tw = synth.make_selection_tree(SELW_NODES, SELW_CHILDREN, seed=replicas.shard_seed(9, rank))
+        dtw = capi.DeviceTree(tw, dev)
+        selw = torch.empty(SELW_NODES, dtype=torch.int32, device=dev)
+
+        def selw_loop():
+            for _ in range(5):
+                dtw.select(None, 1.5, 3, True, out=selw)
+                dtw.vl_revert(selw, 3)
+        selw_loop()
+        selw_ms = float(np.mean(timed(selw_loop, 3, per_iter_flush=False))) / 5
+        del dtw, tw
         # ---- leaf-parallel MCTS: 64 games, 800 simulations per move, leaf batch = B ----
         n_trees, sims = 64, 800
         openings, _, _, _ = synth.make_gomoku_games(n_trees, 15, seed=replicas.shard_seed(100, rank), max_moves=20)
@@ -379,10 +398,10 @@ def gpu_arm(args):
     assert capi.device_error_code() == 0, "a kernel gave up on a bounded wait"
 
     reduced = replicas.max_over_ranks(
-        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
-    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms = reduced[:6]
+        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
+    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms = reduced[:7]
     for i, wr in enumerate(wide):
-        wr["ms"], wr["conv_ms"] = reduced[6 + 2 * i], reduced[7 + 2 * i]
+        wr["ms"], wr["conv_ms"] = reduced[7 + 2 * i], reduced[8 + 2 * i]
     totals = replicas.sum_counters(dist, capi.counters(), dev)   # the only cross-GPU step: per-GPU counters summed
     if rank == 0:
         flops_eval = synth.net_flops_per_eval(15, 17, 64, NET["blocks"], 225, NET["policy_head_ch"], NET["value_head_ch"])
@@ -419,7 +438,12 @@ def gpu_arm(args):
                                        "peak_source": peaks["source"], "us_per_launch": selk_ms * 1e3,
                                        "algorithmic_bytes": selk_bytes, "traffic": 246.8e6, "traffic_unit": "bytes/launch",
                                        "traffic_source": "profiles/puct_select_staged_kernel_65536x225.md"},
-                          "pass_gbs": sel_bytes / (sel_ms * 1e-3) / 1e9},
+                          "pass_gbs": sel_bytes / (sel_ms * 1e-3) / 1e9,
+                          "wide_rows": {"nodes": SELW_NODES, "children": SELW_CHILDREN, "ms_per_pass": selw_ms,
+                                        "value": SELW_NODES / (selw_ms * 1e-3), "unit": "node selections/s (select + VL apply + VL revert)",
+                                        "kernel": "puct_select_kernel (one warp per node, 128-bit streaming loads)",
+                                        "achieved_gbs": synth.selection_bytes_per_node(SELW_CHILDREN) * SELW_NODES / (selw_ms * 1e-3) / 1e9,
+                                        "frac_of_hbm": synth.selection_bytes_per_node(SELW_CHILDREN) * SELW_NODES / (selw_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}},
             "mcts": {"value": world * mcts_sims / (mcts_ms * 1e-3), "unit": "simulations/s",
                      "leaf_evals_per_sec": world * mcts_evals / (mcts_ms * 1e-3),
                      "config": {"games_per_gpu": 64, "sims_per_move": 800, "leaf_batch": B, "c_puct": 1.5, "virtual_loss": 3,

@@ -321,13 +321,20 @@ class Net:
                                            val.ctypes.data_as(C.c_void_p), out_kind))
         return pol, val
 
-    def infer_gomoku(self, history, n_hist, to_move, out_kind=OUT_PROBS):
+    def infer_gomoku(self, history, n_hist, to_move, out_kind=OUT_PROBS, out=None):
+        """out: optional (policy [B, A] float32, value [B] float32) numpy arrays to fill; arrays in
+        page-locked memory are written by the copy engine directly."""
         h = np.ascontiguousarray(history, np.int16)
         nh = np.ascontiguousarray(n_hist, np.uint8)
         tm = np.ascontiguousarray(to_move, np.uint8)
         B = h.shape[0]
-        pol = np.empty((B, self.policy_size), np.float32)
-        val = np.empty(B, np.float32)
+        if out is not None:
+            pol, val = out
+            assert pol.dtype == np.float32 and val.dtype == np.float32 and pol.flags.c_contiguous and val.flags.c_contiguous
+            assert pol.shape == (B, self.policy_size) and val.shape == (B,)
+        else:
+            pol = np.empty((B, self.policy_size), np.float32)
+            val = np.empty(B, np.float32)
         check(lib().ob200_net_infer_gomoku(self.h, h.ctypes.data_as(C.c_void_p), nh.ctypes.data_as(C.c_void_p),
                                            tm.ctypes.data_as(C.c_void_p), B, pol.ctypes.data_as(C.c_void_p),
                                            val.ctypes.data_as(C.c_void_p), out_kind))

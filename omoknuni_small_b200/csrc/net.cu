@@ -42,6 +42,7 @@ struct ob200_net {
     int16_t* d_hist = nullptr; uint8_t *d_nhist = nullptr, *d_tomove = nullptr;
     float *h_planes = nullptr, *h_policy = nullptr, *h_value = nullptr;
     int16_t* h_hist = nullptr; uint8_t *h_nhist = nullptr, *h_tomove = nullptr;
+    int* h_err = nullptr;           // pinned landing word for the device error code
     size_t planes_capacity = 0;     // floats per staging buffer
     std::vector<void*> owned_dev, owned_host;
 };
@@ -309,6 +310,8 @@ int ob200_net_finalize(ob200_net* n) {
     if (int rc = host_alloc(n, &n->h_hist, MB * 16)) return rc;
     if (int rc = host_alloc(n, &n->h_nhist, MB)) return rc;
     if (int rc = host_alloc(n, &n->h_tomove, MB)) return rc;
+    if (int rc = host_alloc(n, &n->h_err, 1)) return rc;
+    *n->h_err = 0;
     OB200_CUDA_OK(cudaStreamCreateWithFlags(&n->stream, cudaStreamNonBlocking));
     OB200_CUDA_OK(cudaDeviceSynchronize());
     n->host.clear();
@@ -368,22 +371,35 @@ int check_call(ob200_net* n, int B, const void* a, const void* b, const void* c,
     return OB200_OK;
 }
 
-// Copies results back, waits, and reports a kernel that gave up on a wait.
+bool is_pinned_host(const void* p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+    return a.type == cudaMemoryTypeHost;
+}
+
+// Copies results back, waits, and reports a kernel that gave up on a wait.  Outputs the caller
+// keeps in page-locked memory are written by the copy engine directly; pageable ones go through
+// the handle's pinned staging buffers.
 int finish_host_call(ob200_net* n, int B, float* policy_out, float* value_out) {
     const size_t A = n->cfg.policy_size;
-    OB200_CUDA_OK(cudaMemcpyAsync(n->h_policy, n->d_policy, (size_t)B * A * sizeof(float), cudaMemcpyDeviceToHost, n->stream));
-    OB200_CUDA_OK(cudaMemcpyAsync(n->h_value, n->d_value, (size_t)B * sizeof(float), cudaMemcpyDeviceToHost, n->stream));
+    const bool direct = is_pinned_host(policy_out) && is_pinned_host(value_out);
+    float* pol_dst = direct ? policy_out : n->h_policy;
+    float* val_dst = direct ? value_out : n->h_value;
+    OB200_CUDA_OK(cudaMemcpyAsync(pol_dst, n->d_policy, (size_t)B * A * sizeof(float), cudaMemcpyDeviceToHost, n->stream));
+    OB200_CUDA_OK(cudaMemcpyAsync(val_dst, n->d_value, (size_t)B * sizeof(float), cudaMemcpyDeviceToHost, n->stream));
     int* errw = device_error_word();
-    int err = 0;
-    if (errw) OB200_CUDA_OK(cudaMemcpyAsync(&err, errw, sizeof(int), cudaMemcpyDeviceToHost, n->stream));
+    if (errw) OB200_CUDA_OK(cudaMemcpyAsync(n->h_err, errw, sizeof(int), cudaMemcpyDeviceToHost, n->stream));
     OB200_CUDA_OK(cudaStreamSynchronize(n->stream));
+    const int err = errw ? *n->h_err : 0;
     if (err) {
         cudaMemsetAsync(errw, 0, sizeof(int), n->stream);
         cudaStreamSynchronize(n->stream);
         return set_error(OB200_ERR_TIMEOUT, "a tower kernel gave up on a bounded wait (role code %d); outputs are not valid", err);
     }
-    std::memcpy(policy_out, n->h_policy, (size_t)B * A * sizeof(float));
-    std::memcpy(value_out, n->h_value, (size_t)B * sizeof(float));
+    if (!direct) {
+        std::memcpy(policy_out, n->h_policy, (size_t)B * A * sizeof(float));
+        std::memcpy(value_out, n->h_value, (size_t)B * sizeof(float));
+    }
     return OB200_OK;
 }
 
