@@ -162,6 +162,89 @@ __device__ __forceinline__ void bracket(int n, float w, float p, int vl, float e
 }
 
 // ---------------------------------------------------------------------------
+// Wide rows (chess: 4,672 children = 75 KB of statistics per node): one CTA per
+// node.  Pass 1: every thread brackets its slots (16-byte loads, upper bounds
+// kept in shared memory) and the CTA takes the best lower bound T.  Pass 2: the
+// few slots whose upper bound reaches T are re-read (they are still in L2) and
+// scored with the exact expression; ties go to the lowest slot.  Same argument
+// for bit-exactness as above.
+// ---------------------------------------------------------------------------
+constexpr int kWideThreads = 256;
+constexpr int kWideMinPitch = 1024;
+__global__ void __launch_bounds__(kWideThreads)
+puct_select_wide_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids, int n, float c_puct,
+                        int vl_value, int apply_vl, int32_t* __restrict__ sel_out) {
+    extern __shared__ __align__(16) float hi_s[];          // [pitch] upper bounds, -inf for slots that do not exist
+    __shared__ float red_f[kWideThreads / 32];
+    __shared__ int red_i[kWideThreads / 32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nvec = t.pitch >> 2;
+    for (int i = blockIdx.x; i < n; i += gridDim.x) {
+        int node = node_ids ? node_ids[i] : i;
+        if (node < 0 || node >= t.n_nodes) {
+            if (threadIdx.x == 0) sel_out[i] = -1;
+            continue;
+        }
+        const size_t row = (size_t)node * t.pitch;
+        const int4* N4 = reinterpret_cast<const int4*>(t.N + row);
+        const float4* W4 = reinterpret_cast<const float4*>(t.W + row);
+        const float4* P4 = reinterpret_cast<const float4*>(t.P + row);
+        const int4* V4 = reinterpret_cast<const int4*>(t.VL + row);
+        const uint32_t* mask = t.legal_bits + (size_t)node * t.mask_words;
+        const float explore = __fmul_rn(c_puct, __fsqrt_rn((float)t.node_visits[node]));
+        float lo_best = -INFINITY;
+        for (int v = threadIdx.x; v < nvec; v += kWideThreads) {
+            const int4 nn = __ldcg(N4 + v); const float4 ww = __ldcg(W4 + v); const float4 pp = __ldcg(P4 + v);
+            const int4 ll = __ldcg(V4 + v);
+            const uint32_t m = (__ldg(mask + (v >> 3)) >> ((v & 7) * 4)) & 0xFu;
+            float lo; float4 h;
+            bracket(nn.x, ww.x, pp.x, ll.x, explore, m & 1u, lo, h.x); lo_best = fmaxf(lo_best, lo);
+            bracket(nn.y, ww.y, pp.y, ll.y, explore, m & 2u, lo, h.y); lo_best = fmaxf(lo_best, lo);
+            bracket(nn.z, ww.z, pp.z, ll.z, explore, m & 4u, lo, h.z); lo_best = fmaxf(lo_best, lo);
+            bracket(nn.w, ww.w, pp.w, ll.w, explore, m & 8u, lo, h.w); lo_best = fmaxf(lo_best, lo);
+            reinterpret_cast<float4*>(hi_s)[v] = h;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) lo_best = fmaxf(lo_best, __shfl_xor_sync(0xffffffffu, lo_best, off));
+        if (lane == 0) red_f[warp] = lo_best;
+        __syncthreads();
+        float T = red_f[0];
+#pragma unroll
+        for (int w = 1; w < kWideThreads / 32; ++w) T = fmaxf(T, red_f[w]);
+        Best b{-INFINITY, -1};
+        for (int v = threadIdx.x; v < nvec; v += kWideThreads) {
+            const float4 h = reinterpret_cast<const float4*>(hi_s)[v];
+            const float he[4] = {h.x, h.y, h.z, h.w};
+            const uint32_t m = (__ldg(mask + (v >> 3)) >> ((v & 7) * 4)) & 0xFu;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (((m >> e) & 1u) && he[e] >= T) {
+                    const int slot = v * 4 + e;
+                    const float sc = puct_score(__ldcg(t.N + row + slot), __ldcg(t.W + row + slot), __ldcg(t.P + row + slot),
+                                                __ldcg(t.VL + row + slot), explore);
+                    if (sc > b.score) { b.score = sc; b.idx = slot; }
+                }
+            }
+        }
+        b = warp_combine(b);
+        __syncthreads();                       // red_f has been read by everyone
+        if (lane == 0) { red_f[warp] = b.score; red_i[warp] = b.idx; }
+        __syncthreads();
+        if (warp == 0) {
+            Best c{-INFINITY, -1};
+            if (lane < kWideThreads / 32) { c.score = red_f[lane]; c.idx = red_i[lane]; }
+            c = warp_combine(c);
+            int sel = c.idx >= 0 ? c.idx : least_visited_row(t.N + row, mask, t.n_children, lane);
+            if (lane == 0) {
+                sel_out[i] = sel;
+                if (sel >= 0 && apply_vl && vl_value > 0) atomicAdd(t.VL + row + sel, vl_value);
+            }
+        }
+        __syncthreads();                       // shared memory is reused by the next node
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Staged variant for rows of up to 256 slots: a persistent grid, every warp
 // walks its own list of nodes and keeps a three-deep ring of rows in shared
 // memory, filled by 1-D bulk async copies (one per array row, completion on an
@@ -523,6 +606,18 @@ int ob200_launch_puct_select(const ob200_tree_view* tree, const int32_t* node_id
         puct_select_staged_kernel<<<want < sms ? want : sms, kStagedWarps * 32, smem, as_stream(stream)>>>(
             *tree, node_ids, n, c_puct, vl_value, apply_vl, sel_out, errw);
         OB200_LAUNCHED("puct_select_staged_kernel");
+    } else if (tree->pitch >= kWideMinPitch && (size_t)tree->pitch * 4 <= 160 * 1024) {
+        // chess-wide rows: a CTA per node
+        int dev = 0, sms = 0;
+        OB200_CUDA_OK(cudaGetDevice(&dev));
+        OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        const int smem = tree->pitch * 4;
+        if (smem > 48 * 1024)
+            OB200_CUDA_OK(cudaFuncSetAttribute(puct_select_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        const int want = sms * 8;
+        puct_select_wide_kernel<<<n < want ? n : want, kWideThreads, smem, as_stream(stream)>>>(
+            *tree, node_ids, n, c_puct, vl_value, apply_vl, sel_out);
+        OB200_LAUNCHED("puct_select_wide_kernel");
     } else {
         const int blocks = (n + kWarpsPerBlock - 1) / kWarpsPerBlock;
         puct_select_kernel<<<blocks, kWarpsPerBlock * 32, 0, as_stream(stream)>>>(*tree, node_ids, n, c_puct, vl_value,

@@ -68,6 +68,38 @@ def test_select_edge_cases(api, oracle):
     dt.select(torch.zeros(0, dtype=torch.int32, device="cuda"))
 
 
+def test_select_wide_rows_edge_cases(api, oracle):
+    """Chess-wide rows (4,672 slots) take the CTA-per-node kernel: the same edge cases, a node
+    list with repeats and out-of-range ids, more nodes than CTAs."""
+    import torch
+    nc = 4672
+    t = synth.make_selection_tree(1500, nc, seed=31)
+    t["legal_bits"][0] = 0                                  # node without children -> -1
+    t["legal_bits"][1] = 0; t["legal_bits"][1, (nc - 1) >> 5] = 1 << ((nc - 1) & 31)   # one child: the last slot
+    t["P"][2] = 0; t["N"][2] = 0; t["W"][2] = 0; t["VL"][2] = 0   # all scores equal -> lowest legal slot
+    t["W"][3, :nc] = np.nan                                 # no score compares greater -> least visited
+    t["W"][4, :nc] = -np.inf
+    t["node_visits"][5] = 0                                 # unvisited parent: exploration term is 0
+    t["VL"][6] = 1000                                       # large virtual loss everywhere
+    t["P"][7, :nc] = 1.0 / nc; t["N"][7] = 3; t["W"][7] = 1.5; t["VL"][7] = 0   # a wide tie at a non-zero score
+    ref = synth.copy_tree(t)
+    rng = np.random.default_rng(5)
+    ids = np.concatenate([np.array([0, 1, 2, 3, 4, 5, 6, 7, 7, 1499, 1], np.int32),
+                          rng.integers(0, 1500, 1400).astype(np.int32)])
+    ids[20], ids[21] = -1, 1500
+    dt = api.DeviceTree(t)
+    sel = dt.select(torch.from_numpy(ids).cuda(), c_puct=1.5, vl_value=3, apply_vl=False).cpu().numpy()
+    want = np.full(len(ids), -1, np.int32)
+    ok = (ids >= 0) & (ids < 1500)
+    want[ok] = oracle.puct_select(ref, ids[ok], c_puct=1.5, vl_value=3, apply_vl=False)
+    assert np.array_equal(sel, want)
+    assert sel[0] == -1 and sel[1] == nc - 1
+    # with virtual loss applied, whole tree
+    sel2 = dt.select(c_puct=1.5, vl_value=3, apply_vl=True).cpu().numpy()
+    sel2_ref = oracle.puct_select(ref, c_puct=1.5, vl_value=3, apply_vl=True)
+    assert np.array_equal(sel2, sel2_ref) and np.array_equal(dt.host("VL"), ref["VL"])
+
+
 def test_select_staged_path_with_node_ids(api, oracle):
     """Launches of >= 1024 entries on rows of <= 256 slots take the shared-memory staged
     kernel: node list with repeats and out-of-range ids, with and without virtual loss."""
