@@ -260,6 +260,8 @@ def gpu_arm(args):
     dist = None
     if world > 1:
         import torch.distributed as dist
+        # stdout carries the one JSON line: NCCL's own banner / debug lines go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device(dev))
 
     def barrier():
