@@ -18,6 +18,13 @@ int conv_halo_rows(int S);   // 64-channel kernel: load boxes have 128 + 2 * con
 int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const BoardTensorMap* res_map,
                         const void* packed_w, const float* bias, int B, int S, int relu, cudaStream_t st);
 int* device_error_word();
+// The whole 64-filter tower as one cooperative launch (tower_fused.cu).
+size_t tower_fused_layer_bytes();
+void tower_fused_fill_layer(void* dst, const BoardTensorMap* in_map, const BoardTensorMap& out_map,
+                            const BoardTensorMap* res_map, const void* w, const float* bias);
+size_t tower_fused_smem_bytes(int S, int n_layers);   // 0: does not fit
+int launch_conv_tower(const BoardTensorMap& stem_in_map, const void* layers_dev, int n_layers, int* flags, int tiles_pitch,
+                      int* done, int epoch, int B, int S, cudaStream_t st);
 // Towers of 128 / 256 channels (tower_wide.cu): cin a multiple of 64 up to 256, cout 128 or 256,
 // taps 9 (3x3) or 1 (1x1).  in_map: boxes of conv_wide_box_rows() rows over a cin-channel tensor;
 // out_map / res_map (residual, or null): boxes of 128 rows over a cout-channel tensor.

@@ -7,6 +7,7 @@
 #include "internal.h"
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -30,6 +31,9 @@ struct ob200_net {
     void* act_in = nullptr;         // cin_pad channels
     void* act[3] = {nullptr, nullptr, nullptr};      // filters channels each
     const void* tower_out = nullptr;
+    // the fused tower (64 filters): per-layer descriptors and tile flags on the device
+    void* fused_layers = nullptr; int *fused_flags = nullptr, *fused_done = nullptr; int fused_pitch = 0, fused_epoch = 0, fused_final = 0;
+    bool fused = false;
     // device: heads
     float *head_w = nullptr, *head_b = nullptr;      // [pc+vc][64], [pc+vc]
     float *WpT = nullptr, *bp = nullptr, *W1T = nullptr, *b1 = nullptr, *w2 = nullptr;
@@ -293,6 +297,30 @@ int ob200_net_finalize(ob200_net* n) {
         if (int rc = make_board_tensor_map(p8, n->rows, n->box_in, &n->act_load[i], F)) return rc;
         if (int rc = make_board_tensor_map(p8, n->rows, box_store, &n->act_store[i], F)) return rc;
     }
+    if (!n->wide && tower_fused_smem_bytes(c.board_size, 1 + 2 * c.blocks) != 0) {
+        // one cooperative launch for the whole tower: layer descriptors with the buffer rotation of
+        // forward_device baked in, and one "tile stored" flag per layer and tile
+        const char* env = std::getenv("OB200_TOWER_FUSED");
+        const int L = 1 + 2 * c.blocks;
+        std::vector<unsigned char> host(tower_fused_layer_bytes() * L);
+        int x = 0, y = 1, z = 2;
+        tower_fused_fill_layer(host.data(), nullptr, n->act_store[x], nullptr, n->conv_w[0], n->conv_b[0]);
+        for (int i = 0; i < c.blocks; ++i) {
+            tower_fused_fill_layer(host.data() + tower_fused_layer_bytes() * (1 + 2 * i), &n->act_load[x], n->act_store[y], nullptr,
+                                   n->conv_w[1 + 2 * i], n->conv_b[1 + 2 * i]);
+            tower_fused_fill_layer(host.data() + tower_fused_layer_bytes() * (2 + 2 * i), &n->act_load[y], n->act_store[z],
+                                   &n->act_store[x], n->conv_w[2 + 2 * i], n->conv_b[2 + 2 * i]);
+            std::swap(x, z);
+        }
+        n->fused_final = x;
+        unsigned char* dl = nullptr;
+        if (int rc = upload(n, &dl, host)) return rc;
+        n->fused_layers = dl;
+        n->fused_pitch = (int)(board_geom(c.board_size, c.max_batch).Ppad / 128);
+        if (int rc = dev_alloc(n, &n->fused_flags, (size_t)L * n->fused_pitch, true)) return rc;
+        if (int rc = dev_alloc(n, &n->fused_done, (size_t)L, true)) return rc;
+        n->fused = !(env && env[0] == '0');
+    }
     const size_t MB = c.max_batch;
     if (int rc = dev_alloc(n, &n->hp, MB * (planes_policy ? 1 : Kp), false)) return rc;
     if (int rc = dev_alloc(n, &n->hv, MB * Kv, false)) return rc;
@@ -332,11 +360,26 @@ int forward_device(ob200_net* n, const BoardTensorMap& in_map, int B, float* pol
     const int S = c.board_size;
     const int F = c.filters;
     int x = 0, y = 1, z = 2;
-    if (int rc = tower_conv(n, in_map, n->cin_pad, n->act_store[x], nullptr, 0, B, st)) return rc;
-    for (int i = 0; i < c.blocks; ++i) {
-        if (int rc = tower_conv(n, n->act_load[x], F, n->act_store[y], nullptr, 1 + 2 * i, B, st)) return rc;
-        if (int rc = tower_conv(n, n->act_load[y], F, n->act_store[z], &n->act_store[x], 2 + 2 * i, B, st)) return rc;
-        std::swap(x, z);
+    bool done = false;
+    // The fused tower keeps two activation tiles in flight per CTA, which covers L2 latency but not
+    // DRAM latency: it is used while the three rotating activation tensors stay resident in L2
+    // (40 MB each at most; 15x15 boards: up to 1,220 per batch).  Larger batches run layer by layer.
+    const bool l2_resident = (size_t)board_geom(S, B).PT * 128 <= ((size_t)40 << 20);
+    if (n->fused && l2_resident) {
+        if (++n->fused_epoch == 0) ++n->fused_epoch;   // flags start at zero: epoch 0 is never used
+        const int rc = launch_conv_tower(in_map, n->fused_layers, 1 + 2 * c.blocks, n->fused_flags, n->fused_pitch,
+                                         n->fused_done, n->fused_epoch, B, S, st);
+        if (rc == OB200_OK) { done = true; x = n->fused_final; }
+        else if (rc == OB200_ERR_UNSUPPORTED) n->fused = false;   // not launchable here: layer by layer from now on
+        else return rc;
+    }
+    if (!done) {
+        if (int rc = tower_conv(n, in_map, n->cin_pad, n->act_store[x], nullptr, 0, B, st)) return rc;
+        for (int i = 0; i < c.blocks; ++i) {
+            if (int rc = tower_conv(n, n->act_load[x], F, n->act_store[y], nullptr, 1 + 2 * i, B, st)) return rc;
+            if (int rc = tower_conv(n, n->act_load[y], F, n->act_store[z], &n->act_store[x], 2 + 2 * i, B, st)) return rc;
+            std::swap(x, z);
+        }
     }
     n->tower_out = n->act[x];
     const int S2 = S * S, pc = c.policy_head_ch, vc = c.value_head_ch;

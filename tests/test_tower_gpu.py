@@ -235,6 +235,30 @@ def test_network_kaiming_normal_benchmark_weights(api):
     assert (logits.argmax(1) == order[:, -1])[margin > 2 * f_err].all()
 
 
+@pytest.mark.parametrize("B", [3, 300, 1100])
+def test_fused_tower_equals_layer_by_layer(api, monkeypatch, B):
+    """The single-launch tower (CTAs walk the layers, tiles hand over through flags) and the
+    launch-per-layer path run the same arithmetic: outputs must be bit-identical.  Batches with
+    fewer tiles than CTAs, a few tiles per CTA, and 15 tiles per CTA."""
+    shapes = synth.net_tensor_shapes(15, 17, 64, 10, 225, 2, 1)
+    w = synth.make_weights(shapes, seed=5, init="torch_default", bn="random")
+    x = synth.make_stone_planes(B, 15, 17, seed=4000 + B)
+    outs = []
+    for fused in ("1", "0"):
+        monkeypatch.setenv("OB200_TOWER_FUSED", fused)
+        net = make_net(api, w, dict(cin=17, S=15, blocks=10, F=64, A=225, pc=2, vc=1), B)
+        before = api.counters()["kernel_launches"]
+        logits, v = net.infer_planes(x, api.OUT_LOGITS)
+        launches = api.counters()["kernel_launches"] - before
+        logits2, v2 = net.infer_planes(x, api.OUT_LOGITS)          # flags of the first call must not leak into the second
+        assert np.array_equal(logits, logits2) and np.array_equal(v, v2)
+        outs.append((logits, v, launches))
+        net.close()
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+    assert outs[0][2] == outs[1][2] - 20                           # 1 tower launch instead of 21
+    assert api.device_error_code() == 0
+
+
 def test_gomoku_inference_end_to_end(api, oracle):
     """Host move histories -> encoder -> tower -> heads, against oracle encoder + fp32 forward,
     including a batch smaller than max_batch after a larger one (buffer reuse)."""
