@@ -325,7 +325,18 @@ def gpu_arm(args):
             t0 = time.perf_counter()
             net.infer_gomoku(p_hist, p_nh, p_tm, out=outs)
             e2e_s += time.perf_counter() - t0
-        # ---- the dominant kernel alone: 64 -> 64 conv with residual + ReLU ----
+        # ---- the dominant kernel alone: the whole tower (one cooperative launch at this batch) ----
+        bt_in = capi.encode_gomoku(d_hist, d_nh, d_tm, 15, 17, net.input_tensor_channels())
+        tower_reps = 5
+
+        def tower_loop():
+            for _ in range(tower_reps):
+                net.tower_device(bt_in, B)
+        tower_loop()
+        c_t0 = capi.counters()["kernel_launches"]
+        tower_ms = float(np.mean(timed(tower_loop, 5))) / tower_reps
+        tower_launches = (capi.counters()["kernel_launches"] - c_t0) // (5 * tower_reps)
+        # ---- one layer as its own launch: 64 -> 64 conv with residual + ReLU ----
         rng = np.random.default_rng(0)
         wp = torch.from_numpy(capi.pack_conv3x3(rng.normal(0, 0.04, (64, 64, 3, 3)).astype(np.float32), None, 64).view(np.int16)).to(dev)
         bias = torch.zeros(64, device=dev)
@@ -400,16 +411,18 @@ def gpu_arm(args):
     assert capi.device_error_code() == 0, "a kernel gave up on a bounded wait"
 
     reduced = replicas.max_over_ranks(
-        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
-    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms = reduced[:7]
+        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
+    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms = reduced[:8]
     for i, wr in enumerate(wide):
-        wr["ms"], wr["conv_ms"] = reduced[7 + 2 * i], reduced[8 + 2 * i]
+        wr["ms"], wr["conv_ms"] = reduced[8 + 2 * i], reduced[9 + 2 * i]
     totals = replicas.sum_counters(dist, capi.counters(), dev)   # the only cross-GPU step: per-GPU counters summed
     if rank == 0:
         flops_eval = synth.net_flops_per_eval(15, 17, 64, NET["blocks"], 225, NET["policy_head_ch"], NET["value_head_ch"])
         value = replicas.aggregate_throughput(B, K, world, total_ms)
         conv_flops = 2.0 * 225 * 9 * 64 * 64 * B
         conv_tf = conv_flops / (conv_ms * 1e-3) / 1e12
+        tower_flops = (2.0 * 225 * 9 * 17 * 64 + NET["blocks"] * 2 * 2.0 * 225 * 9 * 64 * 64) * B
+        tower_tf = tower_flops / (tower_ms * 1e-3) / 1e12
         sel_bytes = synth.selection_bytes_per_node(SEL_CHILDREN) * SEL_NODES
         selk_bytes = sel_bytes - 16 * SEL_NODES      # the select kernel alone: without the revert's read-modify-write
         clocks = sampler.summary()
@@ -424,13 +437,24 @@ def gpu_arm(args):
                     "d2h_bytes_per_step": B * 226 * 4},
             "gpu_launches": int(launches), "counters_all_gpus": totals,
             "tower_tflops": value / world * flops_eval / 1e12,
-            "roofline": {"kernel": "conv3x3_kernel (64->64, residual+ReLU)", "bound": "tensor", "achieved": conv_tf,
+            "roofline": {"kernel": ("conv_tower_kernel (stem + 20 convolutions 64->64 in one launch)" if tower_launches == 1
+                                    else "conv3x3_kernel x 21 (one launch per layer)"),
+                         "bound": "tensor", "achieved": tower_tf, "peak": peaks["bf16_burst"], "unit": "TFLOP/s",
+                         "frac": tower_tf / peaks["bf16_burst"],
+                         "frac_of_sustained": tower_tf / peaks["bf16_sustained"] if peaks["bf16_sustained"] else None,
+                         "peak_source": peaks["source"] + " (burst: kernel timed alone)", "us_per_launch": tower_ms * 1e3,
+                         "launches_per_tower": int(tower_launches), "flops_per_launch": tower_flops,
+                         # DRAM bytes: with the L2 flushed before the loop the first layer reads the input tensor
+                         # from DRAM; every later layer works out of L2 (3 x 33.6 MB of activations at batch 1024)
+                         "traffic": None},
+            "roofline_conv_layer": {"kernel": "conv3x3_kernel (64->64, residual+ReLU), one layer as its own launch",
+                         "bound": "tensor", "achieved": conv_tf,
                          "peak": peaks["bf16_burst"], "unit": "TFLOP/s", "frac": conv_tf / peaks["bf16_burst"],
                          "frac_of_sustained": conv_tf / peaks["bf16_sustained"] if peaks["bf16_sustained"] else None,
                          "peak_source": peaks["source"] + " (burst: kernel timed alone)", "us_per_launch": conv_ms * 1e3,
                          # DRAM bytes per launch from the ncu capture at batch 512 (cold cache: input +
                          # residual from DRAM, output left in L2), scaled by the boards processed
-                         "traffic": 31.63e6 * B / 512.0, "traffic_unit": "bytes/launch",
+                         "traffic": 33.66e6 * B / 512.0, "traffic_unit": "bytes/launch",
                          "traffic_source": "profiles/conv3x3_kernel_gomoku15_batch512.md (scaled by batch)"},
             "selection": {"value": SEL_NODES / (sel_ms * 1e-3), "unit": "node selections/s (select + VL apply + VL revert)",
                           "nodes": SEL_NODES, "children": SEL_CHILDREN, "ms_per_pass": sel_ms,

@@ -301,6 +301,11 @@ int ob200_net_forward_device(ob200_net* net, const void* input_board_tensor, int
 /* Device pointer of the tower's output board tensor of the last forward
  * (filters channels), for tests. */
 const void* ob200_net_debug_tower_output(ob200_net* net);
+/* The residual tower alone (stem + blocks), DEVICE in, asynchronous on `stream`;
+ * the result is the board tensor ob200_net_debug_tower_output() points at.
+ * For measurement and for callers that run their own heads. */
+int ob200_net_tower_device(ob200_net* net, const void* input_board_tensor, int32_t B,
+                           ob200_stream stream);
 /* The value head alone, for callers that must never allocate.  (No counterpart in
  * the reference: its value head runs inside ResNetModel::forward on libtorch's
  * caching allocator.)  Meant for search threads in the middle of a self-play loop

@@ -90,6 +90,7 @@ SIGNATURES = {
     "ob200_net_forward_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
                                            C.c_void_p]),
     "ob200_net_debug_tower_output": (C.c_void_p, [C.c_void_p]),
+    "ob200_net_tower_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "ob200_net_input_tensor_channels": (C.c_int32, [C.c_void_p]),
     "ob200_net_value_head_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "ob200_value_head_noalloc_capacity": (C.c_int64, []),
@@ -346,6 +347,10 @@ class Net:
     def forward_device(self, input_bt, B, policy_out, value_out, out_kind=OUT_PROBS):
         check(lib().ob200_net_forward_device(self.h, _ptr(input_bt), B, _ptr(policy_out), _ptr(value_out), out_kind,
                                              _stream()))
+
+    def tower_device(self, input_bt, B):
+        """The residual tower alone on a device input tensor (asynchronous)."""
+        check(lib().ob200_net_tower_device(self.h, _ptr(input_bt), B, _stream()))
 
     def tower_output_ptr(self):
         return lib().ob200_net_debug_tower_output(self.h)

@@ -354,8 +354,8 @@ namespace {
 
 // Tower + heads on device buffers.  `in_map` covers a board tensor of cin_pad channels holding
 // the B input boards.
-int forward_device(ob200_net* n, const BoardTensorMap& in_map, int B, float* policy_out, float* value_out,
-                   int out_kind, cudaStream_t st) {
+// The tower alone; returns the index of the activation buffer that holds its output in *out_buf.
+int tower_device(ob200_net* n, const BoardTensorMap& in_map, int B, int* out_buf, cudaStream_t st) {
     const ob200_net_config& c = n->cfg;
     const int S = c.board_size;
     const int F = c.filters;
@@ -382,6 +382,17 @@ int forward_device(ob200_net* n, const BoardTensorMap& in_map, int B, float* pol
         }
     }
     n->tower_out = n->act[x];
+    *out_buf = x;
+    return OB200_OK;
+}
+
+int forward_device(ob200_net* n, const BoardTensorMap& in_map, int B, float* policy_out, float* value_out,
+                   int out_kind, cudaStream_t st) {
+    const ob200_net_config& c = n->cfg;
+    const int S = c.board_size;
+    const int F = c.filters;
+    int x = 0;
+    if (int rc = tower_device(n, in_map, B, &x, st)) return rc;
     const int S2 = S * S, pc = c.policy_head_ch, vc = c.value_head_ch;
     if (c.policy_kind == OB200_POLICY_CONV_PLANES) {
         if (int rc = launch_conv_wide_maps(n->act_load[x], n->act_load[x], nullptr, n->pol_w, n->pol_b, B, S, F, n->pol_cout, 1, 0,
@@ -517,6 +528,19 @@ int ob200_net_forward_device(ob200_net* n, const void* input_board_tensor, int32
 }
 
 const void* ob200_net_debug_tower_output(ob200_net* n) { return n ? n->tower_out : nullptr; }
+
+int ob200_net_tower_device(ob200_net* n, const void* input_board_tensor, int32_t B, ob200_stream stream) {
+    if (!n || !input_board_tensor) return set_error(OB200_ERR_INVALID, "ob200_net_tower_device: null argument");
+    if (!n->finalized) return set_error(OB200_ERR_STATE, "ob200_net_tower_device: weights not finalised");
+    if (B < 1 || B > n->cfg.max_batch)
+        return set_error(OB200_ERR_TOO_LARGE, "ob200_net_tower_device: batch %d outside [1, max_batch %d]", B, n->cfg.max_batch);
+    std::lock_guard<std::mutex> lk(n->mu);
+    OB200_CUDA_OK(cudaSetDevice(n->cfg.device));
+    BoardTensorMap in_map;
+    if (int rc = input_map(n, input_board_tensor, B, &in_map)) return rc;
+    int x = 0;
+    return tower_device(n, in_map, B, &x, as_stream(stream));
+}
 
 int ob200_net_value_head_noalloc(ob200_net* n, const void* tower_board_tensor, int32_t B, float* value_out,
                                  ob200_stream stream) {
