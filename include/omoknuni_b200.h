@@ -340,6 +340,10 @@ int32_t ob200_net_input_tensor_channels(ob200_net* net);
  * runs out: 0 = none.  Synchronises the device.  The host-buffer calls above
  * check it themselves and return OB200_ERR_TIMEOUT. */
 int ob200_device_error_code(int32_t* code_out);
+/* Test hook for that path: one thread waits on a barrier nobody arrives at,
+ * gives up after spin_limit polls (microseconds) and raises the error word with
+ * code 9.  Nothing faults or hangs; the context stays usable. */
+int ob200_debug_bounded_wait(int32_t spin_limit, ob200_stream stream);
 
 /* ------------------------------------------------------------------------- *
  *  Leaf-parallel search, Gomoku, device-resident trees.

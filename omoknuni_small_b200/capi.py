@@ -89,6 +89,7 @@ SIGNATURES = {
                                          C.c_void_p, C.c_int32]),
     "ob200_net_forward_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
                                            C.c_void_p]),
+    "ob200_debug_bounded_wait": (C.c_int, [C.c_int32, C.c_void_p]),
     "ob200_net_debug_tower_output": (C.c_void_p, [C.c_void_p]),
     "ob200_net_tower_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "ob200_net_input_tensor_channels": (C.c_int32, [C.c_void_p]),

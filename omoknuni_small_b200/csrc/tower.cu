@@ -513,6 +513,28 @@ int ob200_pack_conv3x3_weights(const float* w_oihw, const float* scale, int32_t 
     return OB200_OK;
 }
 
+// A wait that nothing will ever satisfy, with a small limit: the same bounded-wait-then-report
+// path the kernels take when a copy or a tensor-core completion never arrives.
+__global__ void bounded_wait_probe_kernel(int* error_word, int limit) {
+    __shared__ __align__(8) uint64_t bar;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    bool done = false;
+    for (int i = 0; i < limit && !done; ++i) done = mbar_test(smem_u32(&bar), 0);
+    if (!done) atomicExch(error_word, 9);
+}
+
+int ob200_debug_bounded_wait(int32_t spin_limit, ob200_stream stream) {
+    if (spin_limit < 1 || spin_limit > (1 << 20))
+        return set_error(OB200_ERR_INVALID, "ob200_debug_bounded_wait: spin_limit %d outside [1, 2^20]", spin_limit);
+    if (int rc = require_device()) return rc;
+    int* w = device_error_word();
+    if (!w) return set_error(OB200_ERR_CUDA, "cannot resolve the device error word");
+    bounded_wait_probe_kernel<<<1, 1, 0, as_stream(stream)>>>(w, spin_limit);
+    OB200_LAUNCHED("bounded_wait_probe_kernel");
+    return OB200_OK;
+}
+
 int ob200_device_error_code(int32_t* code_out) {
     if (!code_out) return set_error(OB200_ERR_INVALID, "ob200_device_error_code: null output");
     if (int rc = require_device()) return rc;

@@ -68,6 +68,23 @@ def test_select_edge_cases(api, oracle):
     dt.select(torch.zeros(0, dtype=torch.int32, device="cuda"))
 
 
+def test_select_full_size_pass(api, oracle):
+    """The benchmark's full size, 65,536 nodes x 225 children: selection, virtual loss apply and
+    revert equal the oracle node for node, and the pass leaves the tree as it found it."""
+    import torch
+    t = synth.make_selection_tree(65536, 225, seed=7)
+    ref = synth.copy_tree(t)
+    dt = api.DeviceTree(t)
+    sel = dt.select(c_puct=1.5, vl_value=3, apply_vl=True)
+    sel_ref = oracle.puct_select(ref, c_puct=1.5, vl_value=3, apply_vl=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(sel.cpu().numpy(), sel_ref)
+    assert np.array_equal(dt.host("VL"), ref["VL"])
+    dt.vl_revert(sel, 3)
+    assert np.array_equal(dt.host("VL"), t["VL"])
+    assert api.device_error_code() == 0
+
+
 def test_select_wide_rows_edge_cases(api, oracle):
     """Chess-wide rows (4,672 slots) take the CTA-per-node kernel: the same edge cases, a node
     list with repeats and out-of-range ids, more nodes than CTAs."""

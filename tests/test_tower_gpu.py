@@ -276,6 +276,47 @@ def test_gomoku_inference_end_to_end(api, oracle):
         assert np.allclose(probs.sum(1), 1, atol=1e-5) and (probs >= 0).all()
 
 
+def test_bounded_wait_reports_and_context_survives(api):
+    """A device-side wait that runs out raises the error word (no trap, no hang); the host reads
+    and clears it, the host-buffer inference call turns it into OB200_ERR_TIMEOUT, and the
+    context keeps working."""
+    import torch
+    from oracle import net_ref
+    shapes = synth.net_tensor_shapes(15, 17, 64, 2, 225, 2, 1)
+    w = synth.make_weights(shapes, seed=2, init="torch_default")
+    net = api.Net(17, 15, 2, 64, 225, 2, 1, 256, 8).load(w)
+    x = synth.make_stone_planes(8, 15, 17, seed=5)
+    good, _ = net.infer_planes(x, api.OUT_LOGITS)
+    assert api.device_error_code() == 0
+    api.check(api.lib().ob200_debug_bounded_wait(2000, None))
+    assert api.device_error_code() == 9          # reported ...
+    assert api.device_error_code() == 0          # ... and cleared by the read
+    api.check(api.lib().ob200_debug_bounded_wait(2000, None))
+    torch.cuda.synchronize()                     # the handle's own stream does not wait for the default stream
+    with pytest.raises(api.Error) as e:          # the inference call notices it on its own
+        net.infer_planes(x, api.OUT_LOGITS)
+    assert e.value.code == 6
+    again, _ = net.infer_planes(x, api.OUT_LOGITS)
+    assert np.array_equal(good, again) and api.device_error_code() == 0
+    ref_logits, _ = net_ref.forward(w, x)
+    assert np.abs(again - ref_logits).max() <= POLICY_TOL
+
+
+@pytest.mark.parametrize("F,blocks,B", [(64, 10, 1024), (128, 3, 600)])
+def test_network_batch_invariance(api, F, blocks, B):
+    """Size-independent property at the benchmark's batch: a position's outputs do not depend on
+    what else is in the batch, nor on where its tiles fall (whole batch vs uneven chunks, bit for bit)."""
+    shapes = synth.net_tensor_shapes(15, 17, F, blocks, 225, 2, 1)
+    w = synth.make_weights(shapes, seed=6, init="torch_default", bn="random")
+    x = synth.make_stone_planes(B, 15, 17, seed=6000)
+    net = make_net(api, w, dict(cin=17, S=15, blocks=blocks, F=F, A=225, pc=2, vc=1), B)
+    logits, v = net.infer_planes(x, api.OUT_LOGITS)
+    cuts = [0, 1, 130, 131 + B // 3, B]
+    parts = [net.infer_planes(x[a:b], api.OUT_LOGITS) for a, b in zip(cuts[:-1], cuts[1:])]
+    assert np.array_equal(logits, np.concatenate([p[0] for p in parts]))
+    assert np.array_equal(v, np.concatenate([p[1] for p in parts]))
+
+
 def test_inference_argument_errors(api):
     shapes = synth.net_tensor_shapes(15, 17, 64, 1, 225, 2, 1)
     w = synth.make_weights(shapes, seed=1, init="torch_default")
