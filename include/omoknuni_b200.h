@@ -197,6 +197,23 @@ int ob200_launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist,
                                int32_t planes, int32_t out_channels, void* board_tensor_out,
                                ob200_stream stream);
 
+/* Go state -> the reference's 10 input planes, written as a bf16 board tensor of
+ * `out_channels` (a multiple of 8, >= 10) channels.  Replaces
+ * GoState::getEnhancedTensorRepresentation (src/games/go/go_state.cpp:596-704)
+ * with the CPU code of computeAttackDefensePlanes (:1306-1476): planes 0 / 1
+ * black / white stones, 2 all ones iff black is to move, 3 / 4 min(1, liberties /
+ * 10) of the black / white group on its stones, 5 ko point, 6 / 7 distance to
+ * the nearer edge over S/2, 8 / 9 capture / liberty-defense scores of the legal
+ * cells.  Values are the reference's fp32 values rounded to bf16.
+ *   stones [B][S*S] : 0 empty, 1 black, 2 white;  ko_point [B] : cell or -1;
+ *   to_move [B] : 1 black, 2 white;  legal_bits [B][ceil(S*S/32)] : bit p set
+ *   iff cell p is in GoState::getLegalMoves() (the rules - suicide, ko,
+ *   superko - stay with the caller, which needs the legal moves anyway).
+ * All pointers are device pointers.  board_size <= 30. */
+int ob200_launch_encode_go(const int8_t* stones, const int32_t* ko_point, const uint8_t* to_move,
+                           const uint32_t* legal_bits, int32_t B, int32_t board_size,
+                           int32_t out_channels, void* board_tensor_out, ob200_stream stream);
+
 /* fp32 planes [B][C][S][S] (NCHW, device) -> bf16 board tensor of out_channels
  * channels; channels >= C are zero.  The reference feeds such planes from
  * IGameState::getTensorRepresentation / getEnhancedTensorRepresentation

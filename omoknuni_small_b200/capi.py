@@ -74,6 +74,7 @@ SIGNATURES = {
     "ob200_board_tensor_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
     "ob200_launch_encode_gomoku": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                              C.c_int32, C.c_void_p, C.c_void_p]),
+    "ob200_launch_encode_go": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p, C.c_void_p]),
     "ob200_launch_planes_to_board_tensor": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                                       C.c_void_p]),
     "ob200_launch_conv3x3": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
@@ -256,6 +257,18 @@ def encode_gomoku(history, n_hist, to_move, board_size=15, planes=19, out_channe
     out = torch.empty(nbytes // 2, dtype=torch.int16, device=history.device)
     check(lib().ob200_launch_encode_gomoku(_ptr(history), _ptr(n_hist), _ptr(to_move), B, board_size, planes,
                                            out_channels, _ptr(out), _stream()))
+    return out
+
+
+def encode_go(stones, ko_point, to_move, legal_bits, board_size, out_channels=64):
+    """Device tensors in (int8 [B,S*S], int32 [B], uint8 [B], int32 [B,ceil(S*S/32)] bit masks)
+    -> bf16 board tensor (int16 view) with the reference's 10 Go planes."""
+    import torch
+    B = stones.shape[0]
+    nbytes = int(lib().ob200_board_tensor_bytes(board_size, B, out_channels))
+    out = torch.empty(nbytes // 2, dtype=torch.int16, device=stones.device)
+    check(lib().ob200_launch_encode_go(_ptr(stones), _ptr(ko_point), _ptr(to_move), _ptr(legal_bits), B, board_size,
+                                       out_channels, _ptr(out), _stream()))
     return out
 
 

@@ -135,6 +135,133 @@ encode_gomoku_board_kernel(const int16_t* __restrict__ history, const uint8_t* _
     }
 }
 
+// Go planes (GoState::getEnhancedTensorRepresentation, src/games/go/go_state.cpp:596-704, with the
+// CPU code of computeAttackDefensePlanes, :1306-1476), a CTA per board:
+//   0 black stones, 1 white stones, 2 all ones iff black is to move, 3 / 4 min(1, liberties / 10) of
+//   the black / white group on its stones, 5 ko point, 6 / 7 distance to the nearer edge over S/2,
+//   8 min(1, capture / 5), 9 min(1, defense) on the legal cells.
+// Groups: every stone starts as its own label; labels fall to the minimum over same-coloured
+// neighbours and are compressed (label = label[label]) until nothing changes, which takes a few
+// rounds per board rather than one per stone of the longest chain.  Liberties: every empty cell
+// adds one to each distinct group beside it.  The board's (S+1)^2 x C block of the tensor is built
+// in shared memory and leaves as one bulk copy, as in encode_gomoku_board_kernel.
+constexpr int kGoThreads = 256;
+constexpr int kGoMaxCells = 31 * 31;
+__global__ void __launch_bounds__(kGoThreads)
+encode_go_kernel(const int8_t* __restrict__ stones, const int32_t* __restrict__ ko_point,
+                 const uint8_t* __restrict__ to_move, const uint32_t* __restrict__ legal_bits, int legal_words,
+                 int B, int S, int C, int cover, uint8_t* __restrict__ out) {
+    extern __shared__ __align__(128) uint8_t board_s[];
+    __shared__ int label[kGoMaxCells];
+    __shared__ int gsize[kGoMaxCells];
+    __shared__ int glibs[kGoMaxCells];
+    __shared__ int8_t st[kGoMaxCells];
+    const int GP = S + 1, slots = GP * GP, S2 = S * S;
+    const int row_bytes = C * 2;
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    if ((int)blockIdx.x >= B) {
+        const long long first = (int)blockIdx.x == B ? 0 : (long long)OB200_GUARD + (long long)B * slots;
+        const long long last = (int)blockIdx.x == B ? OB200_GUARD : cover;
+        uint4* o16 = reinterpret_cast<uint4*>(out);
+        for (long long i = first * row_bytes / 16 + threadIdx.x; i < last * row_bytes / 16; i += blockDim.x) o16[i] = z;
+        return;
+    }
+    const int b = blockIdx.x;
+    const int bytes = slots * row_bytes;
+    uint4* s16 = reinterpret_cast<uint4*>(board_s);
+    for (int i = threadIdx.x; i < bytes / 16; i += blockDim.x) s16[i] = z;
+    for (int p = threadIdx.x; p < S2; p += blockDim.x) {
+        const int8_t v = stones[(size_t)b * S2 + p];
+        st[p] = v; label[p] = v ? p : -1; gsize[p] = 0; glibs[p] = 0;
+    }
+    __syncthreads();
+    // ---- groups ----
+    for (int round = 0; round < S2; ++round) {
+        int changed = 0;
+        for (int p = threadIdx.x; p < S2; p += blockDim.x) {
+            if (!st[p]) continue;
+            const int x = p % S, y = p / S;
+            int m = label[p];
+            if (y > 0 && st[p - S] == st[p]) m = min(m, label[p - S]);
+            if (x + 1 < S && st[p + 1] == st[p]) m = min(m, label[p + 1]);
+            if (y + 1 < S && st[p + S] == st[p]) m = min(m, label[p + S]);
+            if (x > 0 && st[p - 1] == st[p]) m = min(m, label[p - 1]);
+            m = min(m, label[m]);                        // compress: labels only ever decrease, a stale read is still valid
+            if (m < label[p]) { label[p] = m; changed = 1; }
+        }
+        if (!__syncthreads_or(changed)) break;
+    }
+    // every label now names the lowest cell of its group (a fixed point of the rule above)
+    for (int p = threadIdx.x; p < S2; p += blockDim.x)
+        if (st[p]) atomicAdd(&gsize[label[p]], 1);
+    for (int e = threadIdx.x; e < S2; e += blockDim.x) {
+        if (st[e]) continue;
+        const int x = e % S, y = e / S;
+        int seen[4], ns = 0;
+        const int nb[4] = {y > 0 ? e - S : -1, x + 1 < S ? e + 1 : -1, y + 1 < S ? e + S : -1, x > 0 ? e - 1 : -1};
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+            if (nb[d] < 0 || !st[nb[d]]) continue;
+            const int g = label[nb[d]];
+            bool dup = false;
+            for (int k = 0; k < ns; ++k) dup |= seen[k] == g;
+            if (!dup) { seen[ns++] = g; atomicAdd(&glibs[g], 1); }
+        }
+    }
+    __syncthreads();
+    // ---- planes ----
+    __nv_bfloat16* sb = reinterpret_cast<__nv_bfloat16*>(board_s);
+    const __nv_bfloat16 one = __float2bfloat16(1.0f);
+    const int mover = to_move[b];
+    const int ko = ko_point[b];
+    const float half = fmaxf(1.0f, __fdiv_rn((float)S, 2.0f));
+    for (int p = threadIdx.x; p < S2; p += blockDim.x) {
+        const int x = p % S, y = p / S;
+        __nv_bfloat16* o = sb + (size_t)(y * GP + x) * C;
+        const int s = st[p];
+        if (s == 1) o[0] = one;
+        if (s == 2) o[1] = one;
+        if (mover == 1) o[2] = one;
+        if (s) o[s == 1 ? 3 : 4] = __float2bfloat16(fminf(1.0f, __fdiv_rn((float)glibs[label[p]], 10.0f)));
+        if (p == ko) o[5] = one;
+        o[6] = __float2bfloat16(fminf(1.0f, fmaxf(0.0f, __fdiv_rn((float)min(x, S - 1 - x), half))));
+        o[7] = __float2bfloat16(fminf(1.0f, fmaxf(0.0f, __fdiv_rn((float)min(y, S - 1 - y), half))));
+        if ((legal_bits[(size_t)b * legal_words + (p >> 5)] >> (p & 31)) & 1u) {
+            const int nb[4] = {y > 0 ? p - S : -1, x + 1 < S ? p + 1 : -1, y + 1 < S ? p + S : -1, x > 0 ? p - 1 : -1};
+            float capture = 0.0f, defense = 0.0f;
+            int empty_adj = 0, friendly_adj = 0;
+#pragma unroll
+            for (int d = 0; d < 4; ++d) {
+                if (nb[d] < 0) continue;
+                const int q = nb[d], sq = st[q];
+                if (!sq) { ++empty_adj; continue; }
+                const int g = label[q];
+                if (sq != mover) {
+                    const int left = glibs[g] - (s == 0 ? 1 : 0);   // liberties other than the move itself
+                    if (left == 0) capture = __fadd_rn(capture, (float)gsize[g]);
+                    else if (left == 1) capture = __fadd_rn(capture, __fmul_rn((float)gsize[g], 0.5f));
+                } else {
+                    ++friendly_adj;
+                    if (glibs[g] <= 2) defense = __fadd_rn(defense, __fmul_rn(__fsub_rn(3.0f, (float)glibs[g]), 0.5f));
+                }
+            }
+            if (friendly_adj >= 2 && empty_adj <= 1) defense = __fadd_rn(defense, 0.3f);
+            o[8] = __float2bfloat16(fminf(1.0f, __fdiv_rn(capture, 5.0f)));
+            o[9] = __float2bfloat16(fminf(1.0f, defense));
+        }
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint8_t* dst = out + ((size_t)OB200_GUARD + (size_t)b * slots) * row_bytes;
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                     "r"((uint32_t)__cvta_generic_to_shared(board_s)), "r"((uint32_t)bytes)
+                     : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    }
+}
+
 __global__ void __launch_bounds__(256)
 planes_to_board_tensor_kernel(const float* __restrict__ planes, int B, int C, int S, int chunks,
                               long long cover, Pack8* __restrict__ out) {
@@ -209,6 +336,30 @@ int launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, const ui
     return OB200_OK;
 }
 
+int launch_encode_go(const int8_t* stones, const int32_t* ko_point, const uint8_t* to_move, const uint32_t* legal_bits,
+                     int32_t B, int32_t board_size, int32_t out_channels, void* board_tensor_out, cudaStream_t stream) {
+    if (!stones || !ko_point || !to_move || !legal_bits || !board_tensor_out || B < 0)
+        return set_error(OB200_ERR_INVALID, "ob200_launch_encode_go: null pointer or negative batch");
+    if (board_size < 2 || board_size > 30 || out_channels < 10 || (out_channels & 7))
+        return set_error(OB200_ERR_INVALID,
+                         "ob200_launch_encode_go: board_size %d must be in [2,30] and out_channels %d a multiple of 8 >= 10",
+                         board_size, out_channels);
+    if (int rc = require_device()) return rc;
+    const BoardGeom g = board_geom(board_size, B);
+    const size_t board_bytes = (size_t)(board_size + 1) * (board_size + 1) * out_channels * 2;
+    if (board_bytes > kMaxBoardSmem - 16 * 1024)
+        return set_error(OB200_ERR_UNSUPPORTED, "ob200_launch_encode_go: a %dx%d board with %d channels does not fit shared memory",
+                         board_size, board_size, out_channels);
+    if (board_bytes > 32 * 1024)
+        OB200_CUDA_OK(cudaFuncSetAttribute(encode_go_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)board_bytes));
+    const int legal_words = (board_size * board_size + 31) / 32;
+    encode_go_kernel<<<(unsigned)(B + 2), kGoThreads, board_bytes, stream>>>(
+        stones, ko_point, to_move, legal_bits, legal_words, B, board_size, out_channels, (int)g.PT,
+        static_cast<uint8_t*>(board_tensor_out));
+    OB200_LAUNCHED("encode_go_kernel");
+    return OB200_OK;
+}
+
 int launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C, int32_t board_size,
                                   int32_t out_channels, void* board_tensor_out, cudaStream_t stream) {
     if (!planes_nchw || !board_tensor_out || B < 0 || C <= 0)
@@ -237,6 +388,13 @@ int ob200_launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, co
                                void* board_tensor_out, ob200_stream stream) {
     return launch_encode_gomoku(history, n_hist, to_move, B, board_size, planes, out_channels, board_tensor_out,
                                 as_stream(stream));
+}
+
+int ob200_launch_encode_go(const int8_t* stones, const int32_t* ko_point, const uint8_t* to_move,
+                           const uint32_t* legal_bits, int32_t B, int32_t board_size, int32_t out_channels,
+                           void* board_tensor_out, ob200_stream stream) {
+    return launch_encode_go(stones, ko_point, to_move, legal_bits, B, board_size, out_channels, board_tensor_out,
+                            as_stream(stream));
 }
 
 int ob200_launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C, int32_t board_size,

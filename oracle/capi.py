@@ -133,6 +133,19 @@ def gomoku_encode(history, n_hist, to_move, board_size=15, planes=19, threads=0)
     return out
 
 
+def go_encode(stones, ko_point, to_move, legal):
+    """stones [B,S,S] int8 (0 empty, 1 black, 2 white), ko_point [B] int32 (-1 none), to_move [B] u8,
+    legal [B,S,S] u8 -> planes [B, 10, S, S] fp32."""
+    stones = np.ascontiguousarray(stones, np.int8)
+    B, S = stones.shape[0], stones.shape[1]
+    out = np.empty((B, 10, S, S), np.float32)
+    lib().oracle_go_encode_batch(stones.ctypes.data_as(C.c_void_p), np.ascontiguousarray(ko_point, np.int32).ctypes.data_as(C.c_void_p),
+                                 np.ascontiguousarray(to_move, np.uint8).ctypes.data_as(C.c_void_p),
+                                 np.ascontiguousarray(legal, np.uint8).ctypes.data_as(C.c_void_p), B, S,
+                                 out.ctypes.data_as(C.c_void_p))
+    return out
+
+
 def gomoku_result(moves, board_size=15):
     """0 ongoing, 1 BLACK won, 2 WHITE won, 3 draw, judged on the last move (freestyle rules)."""
     mv = np.ascontiguousarray(moves, np.int16)
@@ -174,6 +187,8 @@ def ref_tree():
         L.ref_gomoku_result.argtypes = [C.c_int, _i32, C.c_int]
         L.ref_gomoku_encode_batch.restype = C.c_double
         L.ref_gomoku_encode_batch.argtypes = [C.c_int, C.c_int, _i64, _i32, _f32, C.c_int]
+        if hasattr(L, "ref_go_encode"):
+            L.ref_go_encode.argtypes = [C.c_int, C.c_void_p, C.c_int] + [C.c_void_p] * 5
         _ref_tree = L
     return _ref_tree
 
@@ -250,6 +265,41 @@ def ref_gomoku_encode_batch(move_lists, board_size=15, threads=0):
     out = np.zeros((len(move_lists), 19, board_size, board_size), np.float32)
     secs = ref_tree().ref_gomoku_encode_batch(board_size, len(move_lists), row_ptr, flat, out, threads)
     return out, secs
+
+
+def ref_go_encode(moves, board_size):
+    """The reference's GoState after `moves` (cell indices, -1 = pass): dict with stones [S,S] int8,
+    ko_point, to_move, legal [S,S] u8 and planes [10,S,S] fp32; None when the move list is illegal."""
+    S, S2 = board_size, board_size * board_size
+    m = np.ascontiguousarray(moves, np.int32)
+    stones = np.zeros(S2, np.int8); legal = np.zeros(S2, np.uint8); planes = np.zeros(10 * S2, np.float32)
+    ko = C.c_int32(); tm = C.c_int32()
+    n = ref_tree().ref_go_encode(S, m.ctypes.data_as(C.c_void_p), len(m), stones.ctypes.data_as(C.c_void_p), C.byref(ko),
+                                 C.byref(tm), legal.ctypes.data_as(C.c_void_p), planes.ctypes.data_as(C.c_void_p))
+    if n != 10:
+        return None
+    return dict(stones=stones.reshape(S, S), ko_point=ko.value, to_move=tm.value, legal=legal.reshape(S, S),
+                planes=planes.reshape(10, S, S))
+
+
+def random_go_games(n_games, board_size, seed, max_moves):
+    """Seeded random legal play on the reference's GoState (passes with probability 0.03); one
+    position per game, after a random number of moves.  Returns a list of ref_go_encode dicts."""
+    rng = np.random.default_rng(seed)
+    out = []
+    for _ in range(n_games):
+        target = int(rng.integers(0, max_moves + 1))
+        moves = []
+        st = ref_go_encode(moves, board_size)
+        while len(moves) < target:
+            cand = np.flatnonzero(st["legal"].reshape(-1))
+            mv = -1 if (len(cand) == 0 or rng.random() < 0.03) else int(rng.choice(cand))
+            nxt = ref_go_encode(moves + [mv], board_size)
+            if nxt is None:
+                break
+            moves.append(mv); st = nxt
+        out.append(st)
+    return out
 
 
 class RefNet:

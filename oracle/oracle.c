@@ -261,3 +261,107 @@ int oracle_gomoku_result(const int16_t* moves, int n, int S) {
     }
     return n >= S * S ? 3 : 0;
 }
+
+/* Go planes, as GoState::getEnhancedTensorRepresentation (src/games/go/go_state.cpp:596-704)
+ * with the CPU code of computeAttackDefensePlanes (:1306-1476).  Inputs are what the state
+ * holds: stones (0 empty, 1 black, 2 white), the ko point (or -1), the side to move and the
+ * legal cells (GoState::getLegalMoves, :227-265: not suicide, not the ko point, no superko
+ * repetition - rule logic that stays with the caller).  planes: [10][S][S]
+ *   0 black stones, 1 white stones (getTensorRepresentation, :557-594), 2 all ones iff black is
+ *   to move; 3 / 4 min(1, liberties / 10) of the black / white group on its stones (:608-660);
+ *   5 ko point (:666-674); 6 / 7 min(x, S-1-x) / (S/2), the same for y (:677-694);
+ *   8 min(1, capture / 5), 9 min(1, defense) on the legal cells (:1349-1471):
+ *     capture += size (group left without liberty other than the move) or 0.5 * size (one left),
+ *       once per adjacent enemy STONE (a group touching the move twice counts twice);
+ *     defense += (3 - liberties) * 0.5 for each adjacent friendly stone whose group has <= 2
+ *       liberties; += 0.3 when >= 2 adjacent cells are friendly and <= 1 is empty.
+ * Adjacent cells in the order of getAdjacentPositions (:1170-1186): up, right, down, left. */
+void oracle_go_encode(const signed char* stones, int ko_point, int to_move, const unsigned char* legal, int S,
+                      float* planes) {
+    const int S2 = S * S;
+    static const int DX[4] = {0, 1, 0, -1}, DY[4] = {-1, 0, 1, 0};
+    int label[32 * 32], gsize[32 * 32], glibs[32 * 32], stack[32 * 32];
+    memset(planes, 0, sizeof(float) * 10 * S2);
+    for (int p = 0; p < S2; ++p) { label[p] = -1; gsize[p] = 0; glibs[p] = 0; }
+    /* groups: flood fill, label = lowest cell of the group */
+    for (int p = 0; p < S2; ++p) {
+        if (stones[p] == 0 || label[p] >= 0) continue;
+        int top = 0, n = 0;
+        stack[top++] = p; label[p] = p;
+        while (top) {
+            const int c = stack[--top];
+            ++n;
+            const int x = c % S, y = c / S;
+            for (int d = 0; d < 4; ++d) {
+                const int nx = x + DX[d], ny = y + DY[d];
+                if (nx < 0 || nx >= S || ny < 0 || ny >= S) continue;
+                const int q = ny * S + nx;
+                if (stones[q] == stones[p] && label[q] < 0) { label[q] = p; stack[top++] = q; }
+            }
+        }
+        gsize[p] = n;
+    }
+    /* liberties: an empty cell counts once for every distinct group beside it */
+    for (int e = 0; e < S2; ++e) {
+        if (stones[e] != 0) continue;
+        int seen[4], ns = 0;
+        const int x = e % S, y = e / S;
+        for (int d = 0; d < 4; ++d) {
+            const int nx = x + DX[d], ny = y + DY[d];
+            if (nx < 0 || nx >= S || ny < 0 || ny >= S) continue;
+            const int q = ny * S + nx;
+            if (stones[q] == 0) continue;
+            int dup = 0;
+            for (int k = 0; k < ns; ++k) dup |= seen[k] == label[q];
+            if (!dup) { seen[ns++] = label[q]; ++glibs[label[q]]; }
+        }
+    }
+    const float half = (float)S / 2.0f > 1.0f ? (float)S / 2.0f : 1.0f;
+    for (int p = 0; p < S2; ++p) {
+        const int x = p % S, y = p / S;
+        if (stones[p] == 1) planes[0 * S2 + p] = 1.0f;
+        if (stones[p] == 2) planes[1 * S2 + p] = 1.0f;
+        planes[2 * S2 + p] = to_move == 1 ? 1.0f : 0.0f;
+        if (stones[p] != 0) {
+            const float v = (float)glibs[label[p]] / 10.0f;
+            planes[(stones[p] == 1 ? 3 : 4) * S2 + p] = v < 1.0f ? v : 1.0f;
+        }
+        float dx = (float)(x < S - 1 - x ? x : S - 1 - x) / half, dy = (float)(y < S - 1 - y ? y : S - 1 - y) / half;
+        planes[6 * S2 + p] = dx < 0.0f ? 0.0f : dx > 1.0f ? 1.0f : dx;
+        planes[7 * S2 + p] = dy < 0.0f ? 0.0f : dy > 1.0f ? 1.0f : dy;
+    }
+    if (ko_point >= 0 && ko_point < S2) planes[5 * S2 + ko_point] = 1.0f;
+    for (int m = 0; m < S2; ++m) {
+        if (!legal[m]) continue;
+        const int x = m % S, y = m / S;
+        float capture = 0.0f, defense = 0.0f;
+        int empty_adj = 0, friendly_adj = 0;
+        for (int d = 0; d < 4; ++d) {
+            const int nx = x + DX[d], ny = y + DY[d];
+            if (nx < 0 || nx >= S || ny < 0 || ny >= S) continue;
+            const int q = ny * S + nx, st = stones[q];
+            if (st == 0) { ++empty_adj; continue; }
+            const int g = label[q];
+            if (st != to_move) {
+                /* liberties of the group other than the move itself (the move is empty and adjacent) */
+                const int left = glibs[g] - (stones[m] == 0 ? 1 : 0);
+                if (left == 0) capture += (float)gsize[g] * 1.0f;
+                else if (left == 1) capture += (float)gsize[g] * 0.5f;
+            } else {
+                ++friendly_adj;
+                if (glibs[g] <= 2) defense += (3.0f - (float)glibs[g]) * 0.5f;
+            }
+        }
+        if (friendly_adj >= 2 && empty_adj <= 1) defense += 0.3f;
+        const float a = capture / 5.0f;
+        planes[8 * S2 + m] = a < 1.0f ? a : 1.0f;
+        planes[9 * S2 + m] = defense < 1.0f ? defense : 1.0f;
+    }
+}
+
+void oracle_go_encode_batch(const signed char* stones, const int* ko_point, const unsigned char* to_move,
+                            const unsigned char* legal, int B, int S, float* planes) {
+    for (int b = 0; b < B; ++b)
+        oracle_go_encode(stones + (size_t)b * S * S, ko_point[b], to_move[b], legal + (size_t)b * S * S, S,
+                         planes + (size_t)b * 10 * S * S);
+}

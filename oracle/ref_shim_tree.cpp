@@ -23,6 +23,7 @@
 #include "core/igamestate.h"
 #include "mcts/mcts_node.h"
 #include "games/gomoku/gomoku_state.h"
+#include "games/go/go_state.h"
 
 namespace {
 
@@ -256,6 +257,42 @@ int ref_gomoku_result(int board_size, const int32_t* moves, int n_moves) {
         case GameResult::DRAW: return 3;
         default: return 0;
     }
+}
+
+// Real GoState (Chinese rules, positional superko as the constructor's defaults): play
+// `n_moves` actions (cell index y*S+x, or -1 for a pass) from the empty board, then export what a
+// device encoder takes (stones 0/1/2, ko point or -1, side to move, legal cells as bytes; the
+// pass move is always legal and not listed) and getEnhancedTensorRepresentation()
+// (src/games/go/go_state.cpp:596-704: 10 planes) into planes10[10*S*S].  Any output may be
+// null.  Returns the number of planes, or -1 on an illegal move / finished game.
+int ref_go_encode(int board_size, const int32_t* moves, int n_moves, int8_t* stones, int32_t* ko_point,
+                  int32_t* to_move, uint8_t* legal, float* planes10) {
+    alphazero::games::go::GoState st(board_size);
+    for (int i = 0; i < n_moves; ++i) {
+        if (st.isTerminal() || !st.isLegalMove(moves[i])) return -1;
+        st.makeMove(moves[i]);
+    }
+    const int S = board_size, S2 = S * S;
+    if (stones) for (int p = 0; p < S2; ++p) stones[p] = (int8_t)st.getStone(p);
+    if (ko_point) *ko_point = st.getKoPoint();
+    if (to_move) *to_move = st.getCurrentPlayer();
+    if (legal) {
+        std::memset(legal, 0, S2);
+        for (int m : st.getLegalMoves()) if (m >= 0 && m < S2) legal[m] = 1;
+    }
+    int planes = 0;
+    if (planes10) {
+        // a fresh copy, as the engine encodes node states it has just cloned: the copy constructor
+        // starts with empty group / tensor caches (src/games/go/go_state.cpp:140-178); the state that
+        // played the moves can hold groups cached before its last captures
+        alphazero::games::go::GoState fresh(st);
+        auto t = fresh.getEnhancedTensorRepresentation();
+        planes = (int)t.size();
+        for (size_t c = 0; c < t.size() && c < 10; ++c)
+            for (int r = 0; r < S; ++r)
+                std::memcpy(planes10 + (c * S + r) * S, t[c][r].data(), sizeof(float) * S);
+    }
+    return planes;
 }
 
 }  // extern "C"

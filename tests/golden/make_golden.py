@@ -9,6 +9,10 @@ the inputs' checksums and the reference's outputs:
   select_golden.npz  MCTSNode::selectChild + applyVirtualLoss + revertVirtualLoss
   encode_golden.npz  GomokuState::getEnhancedTensorRepresentation (bit-packed)
   result_golden.npz  GomokuState::isTerminal / getGameResult after one more move
+  go_golden.npz      GoState (stones, ko point, side to move, legal cells) and its
+                     getEnhancedTensorRepresentation planes after seeded random
+                     legal play, 9x9 and 19x19 (`python make_golden.py go` makes
+                     only this one)
   net_golden.npz     ResNetModel::forward (log-softmax policy, value): (a) a tiny
                      model with the reference's own libtorch default
                      initialisation, its weights stored here rounded to fp16
@@ -108,12 +112,29 @@ def make_results():
                         row_ptr=np.asarray(ptr, np.int64), result=np.asarray(res, np.int8))
 
 
+def make_go():
+    """Positions of the reference's GoState with the planes its encoder gives for them."""
+    out = {}
+    for tag, S, n, max_moves, seed in (("s9", 9, 48, 110, 909), ("s19", 19, 6, 260, 919)):
+        gs = capi.random_go_games(n, S, seed=seed, max_moves=max_moves)
+        out[tag + "_stones"] = np.stack([g["stones"] for g in gs]).astype(np.int8)
+        out[tag + "_ko"] = np.array([g["ko_point"] for g in gs], np.int32)
+        out[tag + "_to_move"] = np.array([g["to_move"] for g in gs], np.uint8)
+        out[tag + "_legal"] = np.packbits(np.stack([g["legal"] for g in gs]).reshape(n, -1), axis=1)
+        out[tag + "_planes"] = np.stack([g["planes"] for g in gs]).astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, "go_golden.npz"), **out)
+
+
 if __name__ == "__main__":
     if not (capi.have_ref_tree() and capi.have_ref_net()):
         sys.exit("oracle/_ref is not built: run `make -C oracle ref` where the reference checkout exists")
+    if sys.argv[1:] == ["go"]:
+        make_go()
+        sys.exit(0)
     make_select()
     make_encode()
     make_net()
     make_results()
+    make_go()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 from omoknuni_small_b200 import synth
-from test_oracle import load_encode_golden
+from test_oracle import load_encode_golden, load_go_golden
 
 pytestmark = pytest.mark.gpu
 
@@ -59,3 +59,58 @@ def test_planes_to_board_tensor_round_trip(api):
     torch.cuda.synchronize()
     got = bt.cpu().numpy().view(np.uint16)
     assert np.array_equal(got, api.planes_to_board_tensor_host(x, 64))
+
+
+def bf16_round(a):
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
+
+
+def pack_legal(legal):
+    """[B,S,S] 0/1 -> int32 words, bit p of a board = cell p (little-endian bit order)."""
+    B = legal.shape[0]
+    flat = legal.reshape(B, -1).astype(np.uint8)
+    words = (flat.shape[1] + 31) // 32
+    padded = np.zeros((B, words * 32), np.uint8)
+    padded[:, :flat.shape[1]] = flat
+    return np.packbits(padded, axis=1, bitorder="little").view(np.uint32).astype(np.uint32).view(np.int32).reshape(B, words)
+
+
+def run_encode_go(api, stones, ko, tm, legal, out_channels=64):
+    import torch
+    B, S = stones.shape[0], stones.shape[1]
+    bt = api.encode_go(torch.from_numpy(np.ascontiguousarray(stones.reshape(B, -1), np.int8)).cuda(),
+                       torch.from_numpy(np.ascontiguousarray(ko, np.int32)).cuda(),
+                       torch.from_numpy(np.ascontiguousarray(tm, np.uint8)).cuda(),
+                       torch.from_numpy(pack_legal(legal)).cuda(), S, out_channels)
+    torch.cuda.synchronize()
+    return api.board_tensor_to_planes(bt.cpu().numpy().view(np.uint16), S, B, out_channels)
+
+
+@pytest.mark.parametrize("tag", ["s9", "s19"])
+def test_encode_go_matches_reference_golden(api, tag):
+    """The reference's GoState planes, rounded to bf16 (liberty fractions and edge distances are not
+    bf16-exact; stones, colour, ko are)."""
+    stones, ko, tm, legal, planes = load_go_golden(tag)
+    got, pad_zero = run_encode_go(api, stones, ko, tm, legal)
+    assert pad_zero
+    assert np.array_equal(got[:, :10], bf16_round(planes))
+    assert not got[:, 10:].any()
+
+
+@pytest.mark.parametrize("B,S,fill,seed", [(300, 19, 0.45, 1), (64, 19, 0.9, 2), (50, 13, 0.6, 3), (200, 9, 0.7, 4),
+                                           (3, 19, 0.0, 5), (2, 5, 1.0, 6), (5, 30, 0.5, 7)])
+def test_encode_go_matches_oracle(api, oracle, B, S, fill, seed):
+    """Random boards (not necessarily reachable: long chains, one-cell eyes, full and empty boards)
+    with random legal subsets of the empty cells, against the C restatement."""
+    rng = np.random.default_rng(seed)
+    stones = (rng.random((B, S, S)) < fill) * rng.integers(1, 3, (B, S, S))
+    stones = stones.astype(np.int8)
+    stones[0, :, S // 2] = 1                                  # a chain across the whole board
+    legal = ((stones == 0) & (rng.random((B, S, S)) < 0.8)).astype(np.uint8)
+    empty = [np.flatnonzero(stones[b].reshape(-1) == 0) for b in range(B)]
+    ko = np.array([int(rng.choice(e)) if len(e) and rng.random() < 0.3 else -1 for e in empty], np.int32)
+    tm = rng.integers(1, 3, B).astype(np.uint8)
+    got, pad_zero = run_encode_go(api, stones, ko, tm, legal, 16 if S == 30 else 64)
+    want = oracle.go_encode(stones, ko, tm, legal)
+    assert pad_zero and np.array_equal(got[:, :10], bf16_round(want))

@@ -105,6 +105,24 @@ def test_encoder_matches_reference_golden(oracle):
     assert np.array_equal(oracle.gomoku_encode(hist, nh, tm, 15, 17), planes[:, :17])
 
 
+def load_go_golden(tag):
+    """Positions of the reference's GoState and its planes (tests/golden/make_golden.py): stones
+    [n,S,S] int8, ko [n] int32, to_move [n] u8, legal [n,S,S] u8, planes [n,10,S,S] fp32."""
+    g = np.load(os.path.join(GOLD, "go_golden.npz"))
+    stones = g[tag + "_stones"]
+    n, S = stones.shape[0], stones.shape[1]
+    legal = np.unpackbits(g[tag + "_legal"], axis=1)[:, :S * S].reshape(n, S, S)
+    return stones, g[tag + "_ko"], g[tag + "_to_move"], legal, g[tag + "_planes"]
+
+
+@pytest.mark.parametrize("tag", ["s9", "s19"])
+def test_go_encoder_matches_reference_golden(oracle, tag):
+    stones, ko, tm, legal, planes = load_go_golden(tag)
+    assert (ko >= 0).any() or tag == "s19"            # the 9x9 set holds positions with a ko point
+    assert (planes[:, 8] > 0).any() and (planes[:, 9] > 0).any() and (planes[:, 3] > 0).any()
+    assert np.array_equal(oracle.go_encode(stones, ko, tm, legal), planes)
+
+
 def test_game_result_matches_reference_golden(oracle):
     g = np.load(os.path.join(GOLD, "result_golden.npz"))
     ptr, mv = g["row_ptr"], g["moves"]
@@ -204,6 +222,16 @@ def test_encoder_live_against_gomokustate(oracle):
     games, hist, nh, tm = synth.make_gomoku_games(16, 9, seed=10, max_moves=30)
     ref, _ = oracle.ref_gomoku_encode_batch(games, 9)
     assert np.array_equal(oracle.gomoku_encode(hist, nh, tm, 9, 19), ref)
+
+
+def test_go_encoder_live_against_gostate(oracle):
+    """The C restatement against GoState::getEnhancedTensorRepresentation on fresh random games."""
+    _need_ref(oracle, "tree")
+    gs = oracle.random_go_games(16, 9, seed=4242, max_moves=90) + oracle.random_go_games(2, 13, seed=4243, max_moves=120)
+    for g in gs:
+        got = oracle.go_encode(g["stones"][None], np.array([g["ko_point"]], np.int32), np.array([g["to_move"]], np.uint8),
+                               g["legal"][None])[0]
+        assert np.array_equal(got, g["planes"])
 
 
 def test_game_result_live_against_gomokustate(oracle):
