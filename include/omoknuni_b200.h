@@ -197,6 +197,26 @@ int ob200_launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist,
                                int32_t planes, int32_t out_channels, void* board_tensor_out,
                                ob200_stream stream);
 
+/* Chess state -> the reference's 20 input planes, written as a bf16 board
+ * tensor (board_size 8) of `out_channels` (a multiple of 8, >= 24) channels.
+ * Replaces ChessState::getEnhancedTensorRepresentation
+ * (src/games/chess/chess_state.cpp:745-826) with the CPU code of
+ * computeAttackDefensePlanes (:1753-1803).  Square = rank * 8 + file.
+ *   pieces [B][64] : 0 empty, else 1..6 = pawn, knight, bishop, rook, queen,
+ *       king, + 8 for black;
+ *   meta [B][6] : side to move (1 white, 2 black), castling bits (1 WK, 2 WQ,
+ *       4 BK, 8 BQ), en passant square or -1, halfmove clock, chess960 (0/1),
+ *       how often the position has occurred (the repetition plane is that / 3);
+ *   legal_to [B][2] : 64-bit set of the destination squares of the legal moves
+ *       (move generation stays with the caller).
+ * Planes: 0-5 white P N B R Q K, 6-11 black, 12 side to move, 13 castling,
+ * 14 en passant, 15 halfmove / 100, 16 chess960, 17 repetition, 18 / 19 value
+ * of enemy / own pieces around each legal destination.  Values are the
+ * reference's fp32 values rounded to bf16.  All pointers are device pointers. */
+int ob200_launch_encode_chess(const int8_t* pieces, const int32_t* meta, const uint32_t* legal_to,
+                              int32_t B, int32_t out_channels, void* board_tensor_out,
+                              ob200_stream stream);
+
 /* Go state -> the reference's 10 input planes, written as a bf16 board tensor of
  * `out_channels` (a multiple of 8, >= 10) channels.  Replaces
  * GoState::getEnhancedTensorRepresentation (src/games/go/go_state.cpp:596-704)

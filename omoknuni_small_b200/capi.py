@@ -75,6 +75,7 @@ SIGNATURES = {
     "ob200_launch_encode_gomoku": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                              C.c_int32, C.c_void_p, C.c_void_p]),
     "ob200_launch_encode_go": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p, C.c_void_p]),
+    "ob200_launch_encode_chess": (C.c_int, [C.c_void_p] * 3 + [C.c_int32] * 2 + [C.c_void_p, C.c_void_p]),
     "ob200_launch_planes_to_board_tensor": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                                       C.c_void_p]),
     "ob200_launch_conv3x3": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
@@ -269,6 +270,17 @@ def encode_go(stones, ko_point, to_move, legal_bits, board_size, out_channels=64
     out = torch.empty(nbytes // 2, dtype=torch.int16, device=stones.device)
     check(lib().ob200_launch_encode_go(_ptr(stones), _ptr(ko_point), _ptr(to_move), _ptr(legal_bits), B, board_size,
                                        out_channels, _ptr(out), _stream()))
+    return out
+
+
+def encode_chess(pieces, meta, legal_to, out_channels=64):
+    """Device tensors in (int8 [B,64], int32 [B,6], int32 [B,2] bit masks) -> bf16 board tensor
+    (int16 view, board_size 8) with the reference's 20 chess planes."""
+    import torch
+    B = pieces.shape[0]
+    nbytes = int(lib().ob200_board_tensor_bytes(8, B, out_channels))
+    out = torch.empty(nbytes // 2, dtype=torch.int16, device=pieces.device)
+    check(lib().ob200_launch_encode_chess(_ptr(pieces), _ptr(meta), _ptr(legal_to), B, out_channels, _ptr(out), _stream()))
     return out
 
 

@@ -262,6 +262,76 @@ encode_go_kernel(const int8_t* __restrict__ stones, const int32_t* __restrict__ 
     }
 }
 
+// Chess planes (ChessState::getEnhancedTensorRepresentation, src/games/chess/chess_state.cpp:745-826,
+// with the CPU code of computeAttackDefensePlanes, :1753-1803), a CTA of 64 threads per board, one
+// thread per square (square = rank * 8 + file): 0-5 white P N B R Q K, 6-11 black, 12 ones iff white
+// to move, 13 0.25 per castling right, 14 en passant square, 15 min(1, halfmove / 100), 16 chess960,
+// 17 clamp(occurrences / 3, 0, 1), 18 / 19 on every legal destination min(1, sum / 10) of the values
+// (1, 3, 3, 5, 9, 100) of the enemy / own pieces on the 8 squares around it.
+__global__ void __launch_bounds__(64)
+encode_chess_kernel(const int8_t* __restrict__ pieces, const int32_t* __restrict__ meta,
+                    const uint32_t* __restrict__ legal_to, int B, int C, int cover, uint8_t* __restrict__ out) {
+    extern __shared__ __align__(128) uint8_t board_s[];
+    __shared__ int8_t pc_s[64];
+    constexpr int S = 8, GP = 9, slots = 81;
+    const int row_bytes = C * 2;
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    if ((int)blockIdx.x >= B) {
+        const long long first = (int)blockIdx.x == B ? 0 : (long long)OB200_GUARD + (long long)B * slots;
+        const long long last = (int)blockIdx.x == B ? OB200_GUARD : cover;
+        uint4* o16 = reinterpret_cast<uint4*>(out);
+        for (long long i = first * row_bytes / 16 + threadIdx.x; i < last * row_bytes / 16; i += blockDim.x) o16[i] = z;
+        return;
+    }
+    const int b = blockIdx.x, sq = threadIdx.x;
+    const int bytes = slots * row_bytes;
+    uint4* s16 = reinterpret_cast<uint4*>(board_s);
+    for (int i = threadIdx.x; i < bytes / 16; i += blockDim.x) s16[i] = z;
+    const int pc = pieces[(size_t)b * 64 + sq];
+    pc_s[sq] = (int8_t)pc;
+    const int32_t* m = meta + (size_t)b * 6;
+    const int mover = m[0], castling_bits = m[1], ep = m[2], halfmove = m[3], chess960 = m[4], reps = m[5];
+    __syncthreads();
+    const int r0 = sq >> 3, c0 = sq & 7;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(board_s) + (size_t)(r0 * GP + c0) * C;
+    const __nv_bfloat16 one = __float2bfloat16(1.0f);
+    if (pc) o[(pc & 7) - 1 + ((pc & 8) ? 6 : 0)] = one;
+    if (mover == 1) o[12] = one;
+    o[13] = __float2bfloat16(0.25f * (float)__popc(castling_bits & 15));
+    if (sq == ep) o[14] = one;
+    o[15] = __float2bfloat16(fminf(1.0f, __fdiv_rn((float)halfmove, 100.0f)));
+    if (chess960) o[16] = one;
+    o[17] = __float2bfloat16(fminf(1.0f, fmaxf(0.0f, __fdiv_rn((float)reps, 3.0f))));
+    if ((legal_to[(size_t)b * 2 + (sq >> 5)] >> (sq & 31)) & 1u) {
+        float attack = 0.0f, defense = 0.0f;
+#pragma unroll
+        for (int dr = -1; dr <= 1; ++dr)
+#pragma unroll
+            for (int dc = -1; dc <= 1; ++dc) {
+                if (!dr && !dc) continue;
+                const int r = r0 + dr, c = c0 + dc;
+                if (r < 0 || r >= S || c < 0 || c >= S) continue;
+                const int q = pc_s[r * 8 + c];
+                if (!q) continue;
+                const int t = q & 7;
+                const float v = t == 1 ? 1.0f : t <= 3 ? 3.0f : t == 4 ? 5.0f : t == 5 ? 9.0f : 100.0f;
+                if (((q & 8) ? 2 : 1) != mover) attack = __fadd_rn(attack, v); else defense = __fadd_rn(defense, v);
+            }
+        o[18] = __float2bfloat16(fminf(1.0f, __fdiv_rn(attack, 10.0f)));
+        o[19] = __float2bfloat16(fminf(1.0f, __fdiv_rn(defense, 10.0f)));
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint8_t* dst = out + ((size_t)OB200_GUARD + (size_t)b * slots) * row_bytes;
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                     "r"((uint32_t)__cvta_generic_to_shared(board_s)), "r"((uint32_t)bytes)
+                     : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    }
+}
+
 __global__ void __launch_bounds__(256)
 planes_to_board_tensor_kernel(const float* __restrict__ planes, int B, int C, int S, int chunks,
                               long long cover, Pack8* __restrict__ out) {
@@ -360,6 +430,21 @@ int launch_encode_go(const int8_t* stones, const int32_t* ko_point, const uint8_
     return OB200_OK;
 }
 
+int launch_encode_chess(const int8_t* pieces, const int32_t* meta, const uint32_t* legal_to, int32_t B,
+                        int32_t out_channels, void* board_tensor_out, cudaStream_t stream) {
+    if (!pieces || !meta || !legal_to || !board_tensor_out || B < 0)
+        return set_error(OB200_ERR_INVALID, "ob200_launch_encode_chess: null pointer or negative batch");
+    if (out_channels < 20 || (out_channels & 7) || out_channels > 256)
+        return set_error(OB200_ERR_INVALID, "ob200_launch_encode_chess: out_channels %d must be a multiple of 8 in [24, 256]", out_channels);
+    if (int rc = require_device()) return rc;
+    const BoardGeom g = board_geom(8, B);
+    const size_t board_bytes = (size_t)81 * out_channels * 2;
+    encode_chess_kernel<<<(unsigned)(B + 2), 64, board_bytes, stream>>>(pieces, meta, legal_to, B, out_channels, (int)g.PT,
+                                                                         static_cast<uint8_t*>(board_tensor_out));
+    OB200_LAUNCHED("encode_chess_kernel");
+    return OB200_OK;
+}
+
 int launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C, int32_t board_size,
                                   int32_t out_channels, void* board_tensor_out, cudaStream_t stream) {
     if (!planes_nchw || !board_tensor_out || B < 0 || C <= 0)
@@ -395,6 +480,11 @@ int ob200_launch_encode_go(const int8_t* stones, const int32_t* ko_point, const 
                            void* board_tensor_out, ob200_stream stream) {
     return launch_encode_go(stones, ko_point, to_move, legal_bits, B, board_size, out_channels, board_tensor_out,
                             as_stream(stream));
+}
+
+int ob200_launch_encode_chess(const int8_t* pieces, const int32_t* meta, const uint32_t* legal_to, int32_t B,
+                              int32_t out_channels, void* board_tensor_out, ob200_stream stream) {
+    return launch_encode_chess(pieces, meta, legal_to, B, out_channels, board_tensor_out, as_stream(stream));
 }
 
 int ob200_launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C, int32_t board_size,

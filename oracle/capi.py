@@ -146,6 +146,18 @@ def go_encode(stones, ko_point, to_move, legal):
     return out
 
 
+def chess_encode(pieces, meta, legal_to):
+    """pieces [B,64] int8, meta [B,6] int32, legal_to [B,2] uint32 -> planes [B, 20, 8, 8] fp32
+    (field meanings: oracle_chess_encode in oracle.c)."""
+    pieces = np.ascontiguousarray(pieces, np.int8)
+    B = pieces.shape[0]
+    out = np.empty((B, 20, 8, 8), np.float32)
+    lib().oracle_chess_encode_batch(pieces.ctypes.data_as(C.c_void_p), np.ascontiguousarray(meta, np.int32).ctypes.data_as(C.c_void_p),
+                                    np.ascontiguousarray(legal_to, np.uint32).ctypes.data_as(C.c_void_p), B,
+                                    out.ctypes.data_as(C.c_void_p))
+    return out
+
+
 def gomoku_result(moves, board_size=15):
     """0 ongoing, 1 BLACK won, 2 WHITE won, 3 draw, judged on the last move (freestyle rules)."""
     mv = np.ascontiguousarray(moves, np.int16)
@@ -300,6 +312,25 @@ def random_go_games(n_games, board_size, seed, max_moves):
             moves.append(mv); st = nxt
         out.append(st)
     return out
+
+
+def ref_chess_positions(n, seed, max_plies):
+    """n positions of the reference's ChessState after seeded random legal play: pieces [n,64] int8,
+    meta [n,6] int32, legal_to [n,2] uint32, planes [n,20,8,8] fp32.  meta[:,5] (how often the position
+    has occurred) is not readable through the reference's public interface: it is recovered from the
+    reference's own repetition plane (plane 17 = occurrences / 3)."""
+    f = ref_tree().ref_chess_random_encode
+    f.restype = C.c_int
+    f.argtypes = [C.c_uint64, C.c_int] + [C.c_void_p] * 4
+    rng = np.random.default_rng(seed)
+    pieces = np.zeros((n, 64), np.int8); meta = np.zeros((n, 6), np.int32); legal = np.zeros((n, 2), np.uint32)
+    planes = np.zeros((n, 20, 8, 8), np.float32)
+    for i in range(n):
+        r = f(int(rng.integers(1, 1 << 40)), int(rng.integers(0, max_plies + 1)), pieces[i].ctypes.data, meta[i].ctypes.data,
+              legal[i].ctypes.data, planes[i].ctypes.data)
+        assert r >= 0
+        meta[i, 5] = int(round(float(planes[i, 17, 0, 0]) * 3))
+    return pieces, meta, legal, planes
 
 
 class RefNet:

@@ -365,3 +365,59 @@ void oracle_go_encode_batch(const signed char* stones, const int* ko_point, cons
         oracle_go_encode(stones + (size_t)b * S * S, ko_point[b], to_move[b], legal + (size_t)b * S * S, S,
                          planes + (size_t)b * 10 * S * S);
 }
+
+/* Chess planes, as ChessState::getEnhancedTensorRepresentation (src/games/chess/chess_state.cpp:
+ * 745-826) with the CPU code of computeAttackDefensePlanes (:1753-1803).  Square = rank * 8 + file
+ * (:408-410).  pieces[64]: 0 empty, else type 1..6 (pawn, knight, bishop, rook, queen, king), + 8 for
+ * black.  meta: {side to move (1 white, 2 black), castling bits (1 WK, 2 WQ, 4 BK, 8 BQ), en passant
+ * square or -1, halfmove clock, chess960, times the position has occurred}.  legal_to: the 64-bit set
+ * of destination squares of the legal moves (move generation stays with the caller).
+ * planes [20][8][8]: 0-5 white P N B R Q K, 6-11 black (getTensorRepresentation, :692-740);
+ *   12 ones iff white to move; 13 0.25 per castling right; 14 en passant square; 15 min(1,
+ *   halfmove / 100); 16 chess960; 17 clamp(occurrences / 3, 0, 1); 18 / 19 on every legal
+ *   destination: min(1, sum / 10) of the values (1, 3, 3, 5, 9, 100) of the enemy / own pieces on the
+ *   8 squares around it. */
+void oracle_chess_encode(const signed char* pieces, const int* meta, const unsigned int* legal_to, float* planes) {
+    static const float VAL[7] = {0.0f, 1.0f, 3.0f, 3.0f, 5.0f, 9.0f, 100.0f};
+    memset(planes, 0, sizeof(float) * 20 * 64);
+    const int mover = meta[0];
+    float castling = 0.0f;
+    for (int k = 0; k < 4; ++k) if (meta[1] & (1 << k)) castling += 0.25f;
+    float half = (float)meta[3] / 100.0f; if (half > 1.0f) half = 1.0f;
+    float rep = (float)meta[5] / 3.0f; rep = rep < 0.0f ? 0.0f : rep > 1.0f ? 1.0f : rep;
+    for (int sq = 0; sq < 64; ++sq) {
+        const int pc = pieces[sq];
+        if (pc) planes[((pc & 7) - 1 + (pc & 8 ? 6 : 0)) * 64 + sq] = 1.0f;
+        planes[12 * 64 + sq] = mover == 1 ? 1.0f : 0.0f;
+        planes[13 * 64 + sq] = castling;
+        planes[15 * 64 + sq] = half;
+        planes[16 * 64 + sq] = meta[4] ? 1.0f : 0.0f;
+        planes[17 * 64 + sq] = rep;
+    }
+    if (meta[2] >= 0 && meta[2] < 64) planes[14 * 64 + meta[2]] = 1.0f;
+    for (int sq = 0; sq < 64; ++sq) {
+        if (!((legal_to[sq >> 5] >> (sq & 31)) & 1u)) continue;
+        const int r0 = sq / 8, c0 = sq % 8;
+        float attack = 0.0f, defense = 0.0f;
+        for (int dr = -1; dr <= 1; ++dr)
+            for (int dc = -1; dc <= 1; ++dc) {
+                if (!dr && !dc) continue;
+                const int r = r0 + dr, c = c0 + dc;
+                if (r < 0 || r >= 8 || c < 0 || c >= 8) continue;
+                const int pc = pieces[r * 8 + c];
+                if (!pc) continue;
+                const int color = pc & 8 ? 2 : 1;
+                if (color != mover) attack += VAL[pc & 7]; else defense += VAL[pc & 7];
+            }
+        const float a = attack / 10.0f, d = defense / 10.0f;
+        planes[18 * 64 + sq] = a < 1.0f ? a : 1.0f;
+        planes[19 * 64 + sq] = d < 1.0f ? d : 1.0f;
+    }
+}
+
+void oracle_chess_encode_batch(const signed char* pieces, const int* meta, const unsigned int* legal_to, int B,
+                               float* planes) {
+    for (int b = 0; b < B; ++b)
+        oracle_chess_encode(pieces + (size_t)b * 64, meta + (size_t)b * 6, legal_to + (size_t)b * 2,
+                            planes + (size_t)b * 20 * 64);
+}

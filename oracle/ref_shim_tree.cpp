@@ -24,6 +24,8 @@
 #include "mcts/mcts_node.h"
 #include "games/gomoku/gomoku_state.h"
 #include "games/go/go_state.h"
+#include "games/chess/chess_state.h"
+#include "games/chess/chess_types.h"
 
 namespace {
 
@@ -293,6 +295,49 @@ int ref_go_encode(int board_size, const int32_t* moves, int n_moves, int8_t* sto
                 std::memcpy(planes10 + (c * S + r) * S, t[c][r].data(), sizeof(float) * S);
     }
     return planes;
+}
+
+// Real ChessState: `n_plies` random legal moves (LCG on `seed`) from the start position, then
+// export what a device encoder takes - pieces[64] (0 empty, else type 1..6 = P N B R Q K, + 8 for
+// black), meta[6] = {side to move (1 white, 2 black), castling bits (1 WK, 2 WQ, 4 BK, 8 BQ),
+// en passant square or -1, halfmove clock, chess960, 0}, legal_to[2] = the 64-bit set of
+// destination squares of the legal moves - and getEnhancedTensorRepresentation()
+// (src/games/chess/chess_state.cpp:745-826: 20 planes) of a fresh copy into planes20[20*64].
+// Returns the number of plies actually played (the game may end early), or -1 on error.
+int ref_chess_random_encode(uint64_t seed, int n_plies, int8_t* pieces, int32_t* meta, uint32_t* legal_to,
+                            float* planes20) {
+    using namespace alphazero::games::chess;
+    ChessState st;
+    uint64_t x = seed * 6364136223846793005ULL + 1442695040888963407ULL;
+    int played = 0;
+    for (; played < n_plies; ++played) {
+        if (st.isTerminal()) break;
+        auto legal = st.getLegalMoves();
+        if (legal.empty()) break;
+        x = x * 6364136223846793005ULL + 1442695040888963407ULL;
+        st.makeMove(legal[(x >> 33) % legal.size()]);
+    }
+    ChessState fresh(st);
+    for (int sq = 0; sq < 64; ++sq) {
+        const Piece p = fresh.getPiece(sq);
+        pieces[sq] = p.type == PieceType::NONE ? 0 : (int8_t)((int)p.type + (p.color == PieceColor::BLACK ? 8 : 0));
+    }
+    const CastlingRights cr = fresh.getCastlingRights();
+    meta[0] = fresh.getCurrentPlayer();
+    meta[1] = (cr.white_kingside ? 1 : 0) | (cr.white_queenside ? 2 : 0) | (cr.black_kingside ? 4 : 0) | (cr.black_queenside ? 8 : 0);
+    meta[2] = fresh.getEnPassantSquare();
+    meta[3] = fresh.getHalfmoveClock();
+    meta[4] = fresh.isChess960() ? 1 : 0;
+    meta[5] = 0;
+    legal_to[0] = legal_to[1] = 0;
+    for (const auto& m : fresh.generateLegalMoves())
+        if (m.to_square >= 0 && m.to_square < 64) legal_to[m.to_square >> 5] |= 1u << (m.to_square & 31);
+    auto t = fresh.getEnhancedTensorRepresentation();
+    if (t.size() != 20) return -1;
+    for (size_t c = 0; c < 20; ++c)
+        for (int r = 0; r < 8; ++r)
+            std::memcpy(planes20 + (c * 8 + r) * 8, t[c][r].data(), sizeof(float) * 8);
+    return played;
 }
 
 }  // extern "C"

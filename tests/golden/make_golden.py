@@ -13,6 +13,9 @@ the inputs' checksums and the reference's outputs:
                      getEnhancedTensorRepresentation planes after seeded random
                      legal play, 9x9 and 19x19 (`python make_golden.py go` makes
                      only this one)
+  chess_golden.npz   ChessState (pieces, side to move, castling, en passant, clocks,
+                     legal destinations) and its getEnhancedTensorRepresentation
+                     planes after seeded random legal play (`make_golden.py chess`)
   net_golden.npz     ResNetModel::forward (log-softmax policy, value): (a) a tiny
                      model with the reference's own libtorch default
                      initialisation, its weights stored here rounded to fp16
@@ -125,16 +128,26 @@ def make_go():
     np.savez_compressed(os.path.join(HERE, "go_golden.npz"), **out)
 
 
+def make_chess():
+    pieces, meta, legal, planes = capi.ref_chess_positions(160, seed=64, max_plies=140)
+    np.savez_compressed(os.path.join(HERE, "chess_golden.npz"), pieces=pieces, meta=meta, legal_to=legal,
+                        planes=planes)
+
+
 if __name__ == "__main__":
     if not (capi.have_ref_tree() and capi.have_ref_net()):
         sys.exit("oracle/_ref is not built: run `make -C oracle ref` where the reference checkout exists")
     if sys.argv[1:] == ["go"]:
         make_go()
         sys.exit(0)
+    if sys.argv[1:] == ["chess"]:
+        make_chess()
+        sys.exit(0)
     make_select()
     make_encode()
     make_net()
     make_results()
     make_go()
+    make_chess()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 from omoknuni_small_b200 import synth
-from test_oracle import load_encode_golden, load_go_golden
+from test_oracle import load_chess_golden, load_encode_golden, load_go_golden
 
 pytestmark = pytest.mark.gpu
 
@@ -114,3 +114,34 @@ def test_encode_go_matches_oracle(api, oracle, B, S, fill, seed):
     got, pad_zero = run_encode_go(api, stones, ko, tm, legal, 16 if S == 30 else 64)
     want = oracle.go_encode(stones, ko, tm, legal)
     assert pad_zero and np.array_equal(got[:, :10], bf16_round(want))
+
+
+def run_encode_chess(api, pieces, meta, legal_to, out_channels=64):
+    import torch
+    B = pieces.shape[0]
+    bt = api.encode_chess(torch.from_numpy(np.ascontiguousarray(pieces, np.int8)).cuda(),
+                          torch.from_numpy(np.ascontiguousarray(meta, np.int32)).cuda(),
+                          torch.from_numpy(np.ascontiguousarray(legal_to, np.uint32).view(np.int32)).cuda(), out_channels)
+    torch.cuda.synchronize()
+    return api.board_tensor_to_planes(bt.cpu().numpy().view(np.uint16), 8, B, out_channels)
+
+
+def test_encode_chess_matches_reference_golden(api):
+    pieces, meta, legal_to, planes = load_chess_golden()
+    got, pad_zero = run_encode_chess(api, pieces, meta, legal_to, 128)
+    assert pad_zero
+    assert np.array_equal(got[:, :20], bf16_round(planes))
+    assert not got[:, 20:].any()
+
+
+@pytest.mark.parametrize("B,C,seed", [(1, 24, 1), (700, 128, 2), (4096, 64, 3)])
+def test_encode_chess_matches_oracle(api, oracle, B, C, seed):
+    """Random boards and state words (not necessarily reachable: clocks beyond 100, up to 5
+    occurrences, chess960, any en passant square, random destination sets)."""
+    rng = np.random.default_rng(seed)
+    pieces = ((rng.random((B, 64)) < 0.4) * (rng.integers(1, 7, (B, 64)) + 8 * rng.integers(0, 2, (B, 64)))).astype(np.int8)
+    meta = np.stack([rng.integers(1, 3, B), rng.integers(0, 16, B), rng.integers(-1, 64, B), rng.integers(0, 160, B),
+                     rng.integers(0, 2, B), rng.integers(0, 6, B)], axis=1).astype(np.int32)
+    legal_to = rng.integers(0, 1 << 32, (B, 2), dtype=np.uint64).astype(np.uint32)
+    got, pad_zero = run_encode_chess(api, pieces, meta, legal_to, C)
+    assert pad_zero and np.array_equal(got[:, :20], bf16_round(oracle.chess_encode(pieces, meta, legal_to)))

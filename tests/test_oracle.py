@@ -123,6 +123,18 @@ def test_go_encoder_matches_reference_golden(oracle, tag):
     assert np.array_equal(oracle.go_encode(stones, ko, tm, legal), planes)
 
 
+def load_chess_golden():
+    """Positions of the reference's ChessState and its planes (tests/golden/make_golden.py)."""
+    g = np.load(os.path.join(GOLD, "chess_golden.npz"))
+    return g["pieces"], g["meta"], g["legal_to"], g["planes"]
+
+
+def test_chess_encoder_matches_reference_golden(oracle):
+    pieces, meta, legal_to, planes = load_chess_golden()
+    assert (meta[:, 2] >= 0).any() and len(np.unique(meta[:, 1])) > 4 and set(np.unique(meta[:, 0])) == {1, 2}
+    assert np.array_equal(oracle.chess_encode(pieces, meta, legal_to), planes)
+
+
 def test_game_result_matches_reference_golden(oracle):
     g = np.load(os.path.join(GOLD, "result_golden.npz"))
     ptr, mv = g["row_ptr"], g["moves"]
@@ -232,6 +244,13 @@ def test_go_encoder_live_against_gostate(oracle):
         got = oracle.go_encode(g["stones"][None], np.array([g["ko_point"]], np.int32), np.array([g["to_move"]], np.uint8),
                                g["legal"][None])[0]
         assert np.array_equal(got, g["planes"])
+
+
+def test_chess_encoder_live_against_chessstate(oracle):
+    """The C restatement against ChessState::getEnhancedTensorRepresentation on fresh random games."""
+    _need_ref(oracle, "tree")
+    pieces, meta, legal_to, planes = oracle.ref_chess_positions(60, seed=777, max_plies=200)
+    assert np.array_equal(oracle.chess_encode(pieces, meta, legal_to), planes)
 
 
 def test_game_result_live_against_gomokustate(oracle):
