@@ -336,6 +336,23 @@ def gpu_arm(args):
         c_t0 = capi.counters()["kernel_launches"]
         tower_ms = float(np.mean(timed(tower_loop, 5))) / tower_reps
         tower_launches = (capi.counters()["kernel_launches"] - c_t0) // (5 * tower_reps)
+        # ---- the same network at the other batch sizes of the configurations (256: configs[0]; 4096) ----
+        sweep = []
+        if not args.no_sweep:
+            net_sw = capi.Net(17, 15, NET["blocks"], 64, 225, NET["policy_head_ch"], NET["value_head_ch"], 256, 4096, local).load(w)
+            for Bs in (256, 4096):
+                _, h_s, n_s, t_s = synth.make_gomoku_games(Bs, 15, seed=replicas.shard_seed(2000 + Bs, rank))
+                dhs, dns, dts = (torch.from_numpy(a).to(dev) for a in (h_s, n_s, t_s))
+                pol_s = torch.empty((Bs, 225), dtype=torch.float32, device=dev)
+                val_s = torch.empty(Bs, dtype=torch.float32, device=dev)
+
+                def step_s():
+                    bts = capi.encode_gomoku(dhs, dns, dts, 15, 17, net_sw.input_tensor_channels())
+                    net_sw.forward_device(bts, Bs, pol_s, val_s, capi.OUT_PROBS)
+                for _ in range(3):
+                    step_s()
+                sweep.append((Bs, float(np.mean(timed(step_s, 5)))))
+            net_sw.close()
         # ---- one layer as its own launch: 64 -> 64 conv with residual + ReLU ----
         rng = np.random.default_rng(0)
         wp = torch.from_numpy(capi.pack_conv3x3(rng.normal(0, 0.04, (64, 64, 3, 3)).astype(np.float32), None, 64).view(np.int16)).to(dev)
@@ -411,10 +428,11 @@ def gpu_arm(args):
     assert capi.device_error_code() == 0, "a kernel gave up on a bounded wait"
 
     reduced = replicas.max_over_ranks(
-        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
+        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms] + [m for _, m in sweep] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
     total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms = reduced[:8]
+    sweep = [(bs, reduced[8 + i]) for i, (bs, _) in enumerate(sweep)]
     for i, wr in enumerate(wide):
-        wr["ms"], wr["conv_ms"] = reduced[8 + 2 * i], reduced[9 + 2 * i]
+        wr["ms"], wr["conv_ms"] = reduced[8 + len(sweep) + 2 * i], reduced[9 + len(sweep) + 2 * i]
     totals = replicas.sum_counters(dist, capi.counters(), dev)   # the only cross-GPU step: per-GPU counters summed
     if rank == 0:
         flops_eval = synth.net_flops_per_eval(15, 17, 64, NET["blocks"], 225, NET["policy_head_ch"], NET["value_head_ch"])
@@ -477,6 +495,8 @@ def gpu_arm(args):
                                 "dirichlet": [0.3, 0.25], "openings": "seeded random, 0-20 stones", "moves_timed": mcts_moves,
                                 "transposition_table": "on (device table, Zobrist keys)", "nodes_per_move": mcts_nodes},
                      "ms_per_move": mcts_ms / mcts_moves, "timing": "CUDA events around each move, inside the library"},
+            "batch_sweep": [{"leaf_batch_per_gpu": bs, "ms_per_step": m, "value": world * bs / (m * 1e-3), "unit": UNIT,
+                             "tower_tflops": bs / (m * 1e-3) * flops_eval / 1e12} for bs, m in sweep],
             "wide_towers": [wide_report(wr, world, peaks) for wr in wide],
             "clocks": clocks,
         }
@@ -498,6 +518,7 @@ def main():
     ap.add_argument("--batch", type=int, default=1024, help="leaf batch per GPU")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the batch 256 / 4096 runs of the same network")
     ap.add_argument("--wide-only", action="store_true",
                     help="time only the Go / chess towers (a short run for profiling; not the contract line)")
     ap.add_argument("--wide-batch", type=int, default=0, help="with --wide-only: batch for both towers")
