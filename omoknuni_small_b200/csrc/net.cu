@@ -33,7 +33,8 @@ struct ob200_net {
     const void* tower_out = nullptr;
     // the fused tower (64 filters): per-layer descriptors and tile flags on the device
     void* fused_layers = nullptr; int *fused_flags = nullptr, *fused_done = nullptr; int fused_pitch = 0, fused_epoch = 0, fused_final = 0;
-    bool fused = false;
+    bool fused = false, fused_forced = false;   // forced: OB200_TOWER_FUSED=2 (tests: every batch size)
+    int sm_count = 148;
     // device: heads
     float *head_w = nullptr, *head_b = nullptr;      // [pc+vc][64], [pc+vc]
     float *WpT = nullptr, *bp = nullptr, *W1T = nullptr, *b1 = nullptr, *w2 = nullptr;
@@ -320,6 +321,10 @@ int ob200_net_finalize(ob200_net* n) {
         if (int rc = dev_alloc(n, &n->fused_flags, (size_t)L * n->fused_pitch, true)) return rc;
         if (int rc = dev_alloc(n, &n->fused_done, (size_t)L, true)) return rc;
         n->fused = !(env && env[0] == '0');
+        n->fused_forced = env && env[0] == '2';
+        int dev = 0;
+        OB200_CUDA_OK(cudaGetDevice(&dev));
+        OB200_CUDA_OK(cudaDeviceGetAttribute(&n->sm_count, cudaDevAttrMultiProcessorCount, dev));
     }
     const size_t MB = c.max_batch;
     if (int rc = dev_alloc(n, &n->hp, MB * (planes_policy ? 1 : Kp), false)) return rc;
@@ -361,11 +366,16 @@ int tower_device(ob200_net* n, const BoardTensorMap& in_map, int B, int* out_buf
     const int F = c.filters;
     int x = 0, y = 1, z = 2;
     bool done = false;
-    // The fused tower keeps two activation tiles in flight per CTA, which covers L2 latency but not
-    // DRAM latency: it is used while the three rotating activation tensors stay resident in L2
-    // (40 MB each at most; 15x15 boards: up to 1,220 per batch).  Larger batches run layer by layer.
-    const bool l2_resident = (size_t)board_geom(S, B).PT * 128 <= ((size_t)40 << 20);
-    if (n->fused && l2_resident) {
+    // The fused tower pays off in a window of batch sizes (measured, 15x15: 4.5 % faster at 1,024 boards,
+    // equal at 512, 45 % slower at 64, 19 % slower at 4,096).  Below about 8 tiles per CTA and layer the
+    // hand-over of tiles through flags in global memory (store complete -> flag -> poll, about 3 us per
+    // layer on the critical path) costs more than a kernel boundary; and it keeps two activation tiles
+    // in flight per CTA, which covers L2 latency but not DRAM latency, so the three rotating
+    // activation tensors must stay resident in L2 (40 MB each at most; 15x15 boards: 1,220 per batch).
+    const BoardGeom bg = board_geom(S, B);
+    const bool l2_resident = (size_t)bg.PT * 128 <= ((size_t)40 << 20);
+    const bool enough_tiles = bg.Ppad / 128 >= 8LL * n->sm_count;
+    if (n->fused && (n->fused_forced || (l2_resident && enough_tiles))) {
         if (++n->fused_epoch == 0) ++n->fused_epoch;   // flags start at zero: epoch 0 is never used
         const int rc = launch_conv_tower(in_map, n->fused_layers, 1 + 2 * c.blocks, n->fused_flags, n->fused_pitch,
                                          n->fused_done, n->fused_epoch, B, S, st);

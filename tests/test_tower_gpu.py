@@ -244,7 +244,7 @@ def test_fused_tower_equals_layer_by_layer(api, monkeypatch, B):
     w = synth.make_weights(shapes, seed=5, init="torch_default", bn="random")
     x = synth.make_stone_planes(B, 15, 17, seed=4000 + B)
     outs = []
-    for fused in ("1", "0"):
+    for fused in ("2", "0"):      # 2: the single launch at every batch size, 0: never
         monkeypatch.setenv("OB200_TOWER_FUSED", fused)
         net = make_net(api, w, dict(cin=17, S=15, blocks=10, F=64, A=225, pc=2, vc=1), B)
         before = api.counters()["kernel_launches"]
