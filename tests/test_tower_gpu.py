@@ -259,6 +259,24 @@ def test_fused_tower_equals_layer_by_layer(api, monkeypatch, B):
     assert api.device_error_code() == 0
 
 
+@pytest.mark.parametrize("S,blocks,B,cin,fused", [(9, 0, 5, 3, "1"), (5, 1, 17, 17, "2"), (30, 1, 3, 19, "2"),
+                                                    (19, 2, 70, 17, "2"), (19, 2, 70, 17, "0"), (7, 3, 1, 64, "2")])
+def test_network_odd_shapes(api, monkeypatch, S, blocks, B, cin, fused):
+    """Board sizes from 5 to 30, a tower without blocks, 3 / 64 input planes, single boards; with the
+    single-launch tower forced on ("2") and off ("0")."""
+    from oracle import net_ref
+    monkeypatch.setenv("OB200_TOWER_FUSED", fused)
+    A = S * S
+    shapes = synth.net_tensor_shapes(S, cin, 64, blocks, A, 2, 1)
+    w = synth.make_weights(shapes, seed=S + blocks, init="torch_default", bn="random")
+    x = mixed_planes(B, S, cin, 0, seed=50 + S)
+    ref_logits, ref_v = net_ref.forward(w, x, blocks=blocks)
+    net = make_net(api, w, dict(cin=cin, S=S, blocks=blocks, F=64, A=A, pc=2, vc=1), B)
+    logits, v = net.infer_planes(x, api.OUT_LOGITS)
+    assert np.abs(logits - ref_logits).max() <= POLICY_TOL and np.abs(v - ref_v).max() <= VALUE_TOL
+    assert api.device_error_code() == 0
+
+
 def test_gomoku_inference_end_to_end(api, oracle):
     """Host move histories -> encoder -> tower -> heads, against oracle encoder + fp32 forward,
     including a batch smaller than max_batch after a larger one (buffer reuse)."""
