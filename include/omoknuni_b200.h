@@ -197,6 +197,16 @@ int ob200_launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist,
                                int32_t planes, int32_t out_channels, void* board_tensor_out,
                                ob200_stream stream);
 
+/* Gomoku board -> the reference's 3-plane representation, for networks built
+ * with 3 input channels (src/nn/resnet_model.cpp:258-260).  Replaces
+ * GomokuState::getTensorRepresentation (src/games/gomoku/gomoku_state.cpp:184-208):
+ * channel 0 the stones of the side to move, 1 the opponent's, 2 all ones iff
+ * BLACK is to move.  stones [B][S*S]: 0 empty, 1 black, 2 white; to_move [B]:
+ * 1 BLACK, 2 WHITE; out_channels a multiple of 8.  Device pointers. */
+int ob200_launch_encode_gomoku3(const int8_t* stones, const uint8_t* to_move, int32_t B,
+                                int32_t board_size, int32_t out_channels, void* board_tensor_out,
+                                ob200_stream stream);
+
 /* Chess state -> the reference's 20 input planes, written as a bf16 board
  * tensor (board_size 8) of `out_channels` (a multiple of 8, >= 24) channels.
  * Replaces ChessState::getEnhancedTensorRepresentation

@@ -75,6 +75,7 @@ SIGNATURES = {
     "ob200_launch_encode_gomoku": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                              C.c_int32, C.c_void_p, C.c_void_p]),
     "ob200_launch_encode_go": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p, C.c_void_p]),
+    "ob200_launch_encode_gomoku3": (C.c_int, [C.c_void_p, C.c_void_p] + [C.c_int32] * 3 + [C.c_void_p, C.c_void_p]),
     "ob200_launch_encode_chess": (C.c_int, [C.c_void_p] * 3 + [C.c_int32] * 2 + [C.c_void_p, C.c_void_p]),
     "ob200_launch_planes_to_board_tensor": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                                       C.c_void_p]),
@@ -270,6 +271,16 @@ def encode_go(stones, ko_point, to_move, legal_bits, board_size, out_channels=64
     out = torch.empty(nbytes // 2, dtype=torch.int16, device=stones.device)
     check(lib().ob200_launch_encode_go(_ptr(stones), _ptr(ko_point), _ptr(to_move), _ptr(legal_bits), B, board_size,
                                        out_channels, _ptr(out), _stream()))
+    return out
+
+
+def encode_gomoku3(stones, to_move, board_size, out_channels=64):
+    """Device tensors in (int8 [B,S*S], uint8 [B]) -> bf16 board tensor with the 3-plane representation."""
+    import torch
+    B = stones.shape[0]
+    nbytes = int(lib().ob200_board_tensor_bytes(board_size, B, out_channels))
+    out = torch.empty(nbytes // 2, dtype=torch.int16, device=stones.device)
+    check(lib().ob200_launch_encode_gomoku3(_ptr(stones), _ptr(to_move), B, board_size, out_channels, _ptr(out), _stream()))
     return out
 
 

@@ -332,6 +332,34 @@ encode_chess_kernel(const int8_t* __restrict__ pieces, const int32_t* __restrict
     }
 }
 
+// The 3-plane Gomoku representation (GomokuState::getTensorRepresentation,
+// src/games/gomoku/gomoku_state.cpp:184-208): channel 0 the stones of the side to move, 1 the
+// opponent's, 2 ones iff BLACK is to move.  One thread per (position, 8-channel block).
+__global__ void __launch_bounds__(256)
+encode_gomoku3_kernel(const int8_t* __restrict__ stones, const uint8_t* __restrict__ to_move, int B, int S, int chunks,
+                      long long cover, Pack8* __restrict__ out) {
+    const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= cover * chunks) return;
+    const long long pidx = gid / chunks;
+    const int chunk = (int)(gid - pidx * chunks);
+    Pack8 o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o.v[j] = __float2bfloat16(0.0f);
+    const long long p = pidx - OB200_GUARD;
+    const int GP = S + 1, slots = GP * GP;
+    if (chunk == 0 && p >= 0 && p < (long long)B * slots) {
+        const int b = (int)(p / slots), r = (int)(p - (long long)b * slots);
+        const int y = r / GP, x = r - y * GP;
+        if (y < S && x < S) {
+            const int st = stones[(size_t)b * S * S + y * S + x], me = to_move[b];
+            if (st == me) o.v[0] = __float2bfloat16(1.0f);
+            else if (st != 0) o.v[1] = __float2bfloat16(1.0f);
+            if (me == 1) o.v[2] = __float2bfloat16(1.0f);
+        }
+    }
+    out[gid] = o;
+}
+
 __global__ void __launch_bounds__(256)
 planes_to_board_tensor_kernel(const float* __restrict__ planes, int B, int C, int S, int chunks,
                               long long cover, Pack8* __restrict__ out) {
@@ -445,6 +473,23 @@ int launch_encode_chess(const int8_t* pieces, const int32_t* meta, const uint32_
     return OB200_OK;
 }
 
+int launch_encode_gomoku3(const int8_t* stones, const uint8_t* to_move, int32_t B, int32_t board_size, int32_t out_channels,
+                          void* board_tensor_out, cudaStream_t stream) {
+    if (!stones || !to_move || !board_tensor_out || B < 0)
+        return set_error(OB200_ERR_INVALID, "ob200_launch_encode_gomoku3: null pointer or negative batch");
+    if (board_size < 1 || board_size > 31 || out_channels < 8 || (out_channels & 7))
+        return set_error(OB200_ERR_INVALID, "ob200_launch_encode_gomoku3: bad board_size %d / out_channels %d", board_size,
+                         out_channels);
+    if (int rc = require_device()) return rc;
+    const BoardGeom g = board_geom(board_size, B);
+    const int chunks = out_channels / 8;
+    const long long total = g.PT * chunks;
+    encode_gomoku3_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(stones, to_move, B, board_size, chunks, g.PT,
+                                                                              reinterpret_cast<Pack8*>(board_tensor_out));
+    OB200_LAUNCHED("encode_gomoku3_kernel");
+    return OB200_OK;
+}
+
 int launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C, int32_t board_size,
                                   int32_t out_channels, void* board_tensor_out, cudaStream_t stream) {
     if (!planes_nchw || !board_tensor_out || B < 0 || C <= 0)
@@ -480,6 +525,11 @@ int ob200_launch_encode_go(const int8_t* stones, const int32_t* ko_point, const 
                            void* board_tensor_out, ob200_stream stream) {
     return launch_encode_go(stones, ko_point, to_move, legal_bits, B, board_size, out_channels, board_tensor_out,
                             as_stream(stream));
+}
+
+int ob200_launch_encode_gomoku3(const int8_t* stones, const uint8_t* to_move, int32_t B, int32_t board_size,
+                                int32_t out_channels, void* board_tensor_out, ob200_stream stream) {
+    return launch_encode_gomoku3(stones, to_move, B, board_size, out_channels, board_tensor_out, as_stream(stream));
 }
 
 int ob200_launch_encode_chess(const int8_t* pieces, const int32_t* meta, const uint32_t* legal_to, int32_t B,

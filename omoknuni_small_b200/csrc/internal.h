@@ -9,6 +9,8 @@ int launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, const ui
                          cudaStream_t stream);
 int launch_encode_go(const int8_t* stones, const int32_t* ko_point, const uint8_t* to_move, const uint32_t* legal_bits,
                      int32_t B, int32_t board_size, int32_t out_channels, void* board_tensor_out, cudaStream_t stream);
+int launch_encode_gomoku3(const int8_t* stones, const uint8_t* to_move, int32_t B, int32_t board_size, int32_t out_channels,
+                          void* board_tensor_out, cudaStream_t stream);
 int launch_encode_chess(const int8_t* pieces, const int32_t* meta, const uint32_t* legal_to, int32_t B,
                         int32_t out_channels, void* board_tensor_out, cudaStream_t stream);
 int launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C, int32_t board_size,

@@ -133,6 +133,24 @@ def gomoku_encode(history, n_hist, to_move, board_size=15, planes=19, threads=0)
     return out
 
 
+def gomoku_planes3(stones, to_move):
+    """stones [B,S,S] int8 (0 empty, 1 black, 2 white), to_move [B] u8 -> planes [B, 3, S, S] fp32."""
+    stones = np.ascontiguousarray(stones, np.int8)
+    B, S = stones.shape[0], stones.shape[1]
+    out = np.empty((B, 3, S, S), np.float32)
+    lib().oracle_gomoku_planes3_batch(stones.ctypes.data_as(C.c_void_p), np.ascontiguousarray(to_move, np.uint8).ctypes.data_as(C.c_void_p),
+                                      B, S, out.ctypes.data_as(C.c_void_p))
+    return out
+
+
+def stones_from_moves(moves, board_size):
+    """Board of a Gomoku game given as its move list (black moves first): [S,S] int8 and the side to move."""
+    st = np.zeros(board_size * board_size, np.int8)
+    for i, m in enumerate(moves):
+        st[int(m)] = 1 + (i & 1)
+    return st.reshape(board_size, board_size), 1 + (len(moves) & 1)
+
+
 def go_encode(stones, ko_point, to_move, legal):
     """stones [B,S,S] int8 (0 empty, 1 black, 2 white), ko_point [B] int32 (-1 none), to_move [B] u8,
     legal [B,S,S] u8 -> planes [B, 10, S, S] fp32."""

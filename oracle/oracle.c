@@ -421,3 +421,18 @@ void oracle_chess_encode_batch(const signed char* pieces, const int* meta, const
         oracle_chess_encode(pieces + (size_t)b * 64, meta + (size_t)b * 6, legal_to + (size_t)b * 2,
                             planes + (size_t)b * 20 * 64);
 }
+
+/* The 3-plane Gomoku representation, GomokuState::getTensorRepresentation
+ * (src/games/gomoku/gomoku_state.cpp:184-208), used when the network takes 3 input channels
+ * (src/nn/resnet_model.cpp:258-260): plane 0 the stones of the side to move, plane 1 the
+ * opponent's, plane 2 all ones iff BLACK (1) is to move.  stones: 0 empty, 1 black, 2 white. */
+void oracle_gomoku_planes3_batch(const signed char* stones, const unsigned char* to_move, int B, int S, float* planes) {
+    const int S2 = S * S;
+    for (int b = 0; b < B; ++b)
+        for (int p = 0; p < S2; ++p) {
+            const int st = stones[(size_t)b * S2 + p], me = to_move[b];
+            planes[((size_t)b * 3 + 0) * S2 + p] = st == me ? 1.0f : 0.0f;
+            planes[((size_t)b * 3 + 1) * S2 + p] = (st != 0 && st != me) ? 1.0f : 0.0f;
+            planes[((size_t)b * 3 + 2) * S2 + p] = me == 1 ? 1.0f : 0.0f;
+        }
+}

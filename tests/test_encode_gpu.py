@@ -145,3 +145,16 @@ def test_encode_chess_matches_oracle(api, oracle, B, C, seed):
     legal_to = rng.integers(0, 1 << 32, (B, 2), dtype=np.uint64).astype(np.uint32)
     got, pad_zero = run_encode_chess(api, pieces, meta, legal_to, C)
     assert pad_zero and np.array_equal(got[:, :20], bf16_round(oracle.chess_encode(pieces, meta, legal_to)))
+
+
+@pytest.mark.parametrize("B,S,C", [(257, 15, 64), (3, 9, 8), (40, 19, 128)])
+def test_encode_gomoku3_matches_oracle(api, oracle, B, S, C):
+    """The 3-plane representation (side to move / opponent / colour) from board arrays."""
+    import torch
+    games, _, _, _ = synth.make_gomoku_games(B, S, seed=B, max_moves=S * S // 2)
+    boards = [oracle.stones_from_moves(g, S) for g in games]
+    stones = np.stack([b[0] for b in boards]); tm = np.array([b[1] for b in boards], np.uint8)
+    bt = api.encode_gomoku3(torch.from_numpy(stones.reshape(B, -1)).cuda(), torch.from_numpy(tm).cuda(), S, C)
+    torch.cuda.synchronize()
+    got, pad_zero = api.board_tensor_to_planes(bt.cpu().numpy().view(np.uint16), S, B, C)
+    assert pad_zero and np.array_equal(got[:, :3], oracle.gomoku_planes3(stones, tm)) and not got[:, 3:].any()

@@ -253,6 +253,17 @@ def test_chess_encoder_live_against_chessstate(oracle):
     assert np.array_equal(oracle.chess_encode(pieces, meta, legal_to), planes)
 
 
+def test_gomoku_planes3_live_against_gomokustate(oracle):
+    """The 3-plane representation against GomokuState::getTensorRepresentation."""
+    _need_ref(oracle, "tree")
+    games, _, _, _ = synth.make_gomoku_games(40, 15, seed=31, max_moves=120)
+    for g in games[:40]:
+        st, tm = oracle.stones_from_moves(g, 15)
+        _, p3, tm_ref = oracle.ref_gomoku_planes(g, 15)
+        assert tm == tm_ref
+        assert np.array_equal(oracle.gomoku_planes3(st[None], np.array([tm], np.uint8))[0], p3)
+
+
 def test_game_result_live_against_gomokustate(oracle):
     _need_ref(oracle, "tree")
     rng = np.random.default_rng(8)
