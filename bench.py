@@ -23,6 +23,8 @@ Multi-GPU: one process per GPU (torchrun), independent replicas, no data-path
 collective; per-GPU counters are summed after the timed region.
 """
 import argparse
+import contextlib
+import io
 import json
 import os
 import subprocess
@@ -143,6 +145,13 @@ def selection_cpu_baseline(n_nodes=4096):
             "sample": f"{n_nodes} parents x 225 children, 5 passes, flat-array port"}
 
 
+def arm_config(B, world):
+    """The workload both arms report."""
+    return {"workload": "gomoku15x15 leaf batch: encode + resnet 10x64 (2/1-channel heads) forward",
+            "leaf_batch_per_gpu": B, "l2": "flushed between timed steps (256 MB write)",
+            "replicas": world, "weights": "kaiming-normal seed 42, BN identity"}
+
+
 def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -151,7 +160,8 @@ def reference_arm(args):
     line = {"metric": METRIC, "value": base["value"], "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "gomoku15x15 leaf batch: encode + resnet 10x64 forward", "sample_batch": 256},
+            "config": dict(arm_config(args.batch, args.gpus), sample_batch=256,
+                           note="the reference class hard-codes 32/32-channel heads; one step = a 256-position sample of the leaf batch"),
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -260,8 +270,6 @@ def gpu_arm(args):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        # stdout carries the one JSON line: NCCL's own banner / debug lines go to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device(dev))
 
     def barrier():
@@ -448,9 +456,7 @@ def gpu_arm(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "gomoku15x15 leaf batch: encode + resnet 10x64 (2/1-channel heads) forward",
-                       "leaf_batch_per_gpu": B, "l2": "flushed between timed steps (256 MB write)",
-                       "replicas": world, "weights": "kaiming-normal seed 42, BN identity"},
+            "config": arm_config(B, world),
             "e2e": {"value": world * B * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": B * 34,
                     "d2h_bytes_per_step": B * 226 * 4},
             "gpu_launches": int(launches), "counters_all_gpus": totals,
@@ -523,12 +529,29 @@ def main():
                     help="time only the Go / chess towers (a short run for profiling; not the contract line)")
     ap.add_argument("--wide-batch", type=int, default=0, help="with --wide-only: batch for both towers")
     args = ap.parse_args()
-    if args.impl == "reference":
-        reference_arm(args)
-    elif args.wide_only:
-        wide_only(args)
-    else:
-        gpu_arm(args)
+    # stdout carries the one JSON line and nothing else: while the benchmark runs, file descriptor 1
+    # points at stderr (libraries such as NCCL print banners with printf), and print() is given the
+    # real stdout back only for the result line
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    result = io.StringIO()
+    try:
+        with contextlib.redirect_stdout(result):
+            if args.impl == "reference":
+                reference_arm(args)
+            elif args.wide_only:
+                wide_only(args)
+            else:
+                gpu_arm(args)
+    finally:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
+    out = result.getvalue()
+    if out:
+        sys.stdout.write(out)
+        sys.stdout.flush()
 
 
 if __name__ == "__main__":
