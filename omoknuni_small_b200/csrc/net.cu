@@ -375,7 +375,11 @@ int tower_device(ob200_net* n, const BoardTensorMap& in_map, int B, int* out_buf
     const BoardGeom bg = board_geom(S, B);
     const bool l2_resident = (size_t)bg.PT * 128 <= ((size_t)40 << 20);
     const bool enough_tiles = bg.Ppad / 128 >= 8LL * n->sm_count;
-    if (n->fused && (n->fused_forced || (l2_resident && enough_tiles))) {
+    // The tile flags carry a per-launch epoch kept on the host: a launch replayed from a captured
+    // graph would see its own earlier flags, so a capturing stream gets the per-layer kernels.
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &capturing) != cudaSuccess) { cudaGetLastError(); capturing = cudaStreamCaptureStatusNone; }
+    if (n->fused && capturing == cudaStreamCaptureStatusNone && (n->fused_forced || (l2_resident && enough_tiles))) {
         if (++n->fused_epoch == 0) ++n->fused_epoch;   // flags start at zero: epoch 0 is never used
         const int rc = launch_conv_tower(in_map, n->fused_layers, 1 + 2 * c.blocks, n->fused_flags, n->fused_pitch,
                                          n->fused_done, n->fused_epoch, B, S, st);

@@ -277,6 +277,42 @@ def test_network_odd_shapes(api, monkeypatch, S, blocks, B, cin, fused):
     assert api.device_error_code() == 0
 
 
+def test_forward_device_in_a_captured_graph(api):
+    """ob200_net_forward_device captured into a CUDA graph and replayed on new inputs gives what
+    direct calls give (the single-launch tower keeps a per-launch epoch on the host, so a capturing
+    stream must get the per-layer kernels)."""
+    import torch
+    B = 700                                            # a batch at which direct calls use the single launch
+    shapes = synth.net_tensor_shapes(15, 17, 64, 4, 225, 2, 1)
+    w = synth.make_weights(shapes, seed=9, init="torch_default", bn="random")
+    net = make_net(api, w, dict(cin=17, S=15, blocks=4, F=64, A=225, pc=2, vc=1), B)
+    xs = [synth.make_stone_planes(B, 15, 17, seed=7000 + i) for i in range(3)]
+    bts = [api.planes_to_board_tensor(torch.from_numpy(x).cuda(), net.input_tensor_channels()) for x in xs]
+    pol = torch.empty((B, 225), dtype=torch.float32, device="cuda")
+    val = torch.empty(B, dtype=torch.float32, device="cuda")
+    direct = []
+    for bt in bts:
+        net.forward_device(bt, B, pol, val, api.OUT_LOGITS)
+        torch.cuda.synchronize()
+        direct.append((pol.cpu().numpy().copy(), val.cpu().numpy().copy()))
+    static_in = bts[0].clone()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        net.forward_device(static_in, B, pol, val, api.OUT_LOGITS)      # warm-up outside capture
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(g):
+        net.forward_device(static_in, B, pol, val, api.OUT_LOGITS)
+    for bt, (p_ref, v_ref) in zip(bts, direct):
+        static_in.copy_(bt)
+        g.replay()
+        g.replay()                                     # a second replay must not see the first one's state
+        torch.cuda.synchronize()
+        assert np.array_equal(pol.cpu().numpy(), p_ref) and np.array_equal(val.cpu().numpy(), v_ref)
+    assert api.device_error_code() == 0
+
+
 def test_gomoku_inference_end_to_end(api, oracle):
     """Host move histories -> encoder -> tower -> heads, against oracle encoder + fp32 forward,
     including a batch smaller than max_batch after a larger one (buffer reuse)."""
