@@ -31,6 +31,14 @@ void tower_fused_fill_layer(void* dst, const BoardTensorMap* in_map, const Board
 size_t tower_fused_smem_bytes(int S, int n_layers);   // 0: does not fit
 int launch_conv_tower(const BoardTensorMap& stem_in_map, const void* layers_dev, int n_layers, int* flags, int tiles_pitch,
                       int* done, int epoch, int B, int S, cudaStream_t st);
+// The 64-filter tower with the boards resident in shared memory (tower_resident.cu): boards up to
+// 15x15, one ordinary launch.  in_map / out_map: boxes of tower_resident_box_rows(S) rows.
+size_t tower_resident_layer_bytes();
+void tower_resident_fill_layer(void* dst, const void* w, const float* bias, int has_res);
+int tower_resident_box_rows(int S);
+size_t tower_resident_smem_bytes(int S, int n_layers);   // 0: does not fit
+int launch_conv_tower_resident(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* layers_dev,
+                               int n_layers, int B, int S, cudaStream_t st);
 // Towers of 128 / 256 channels (tower_wide.cu): cin a multiple of 64 up to 256, cout 128 or 256,
 // taps 9 (3x3) or 1 (1x1).  in_map: boxes of conv_wide_box_rows() rows over a cin-channel tensor;
 // out_map / res_map (residual, or null): boxes of 128 rows over a cout-channel tensor.

@@ -36,6 +36,9 @@ struct ob200_net {
     // the fused tower (64 filters): per-layer descriptors and tile flags on the device
     void* fused_layers = nullptr; int *fused_flags = nullptr, *fused_done = nullptr; int fused_pitch = 0, fused_epoch = 0, fused_final = 0;
     bool fused = false, fused_forced = false;   // forced: OB200_TOWER_FUSED=2 (tests: every batch size)
+    // the board-resident tower (64 filters, boards up to 15x15): layer descriptors, whole-board boxes
+    void* resident_layers = nullptr; bool resident = false;
+    ob200::BoardTensorMap in_map_board{}, out_map_board{};
     int sm_count = 148;
     // device: heads
     float *head_w = nullptr, *head_b = nullptr;      // [pc+vc][64], [pc+vc]
@@ -138,8 +141,8 @@ int tower_conv(ob200_net* n, const BoardTensorMap& in_map, int cin, const BoardT
 }
 
 // Load map over a caller's input board tensor holding B boards.
-int input_map(ob200_net* n, const void* input_bt, int B, BoardTensorMap* out) {
-    return make_board_tensor_map(input_bt, board_geom(n->cfg.board_size, B).PT, n->box_in, out, n->cin_pad);
+int input_map(ob200_net* n, const void* input_bt, int B, int box_rows, BoardTensorMap* out) {
+    return make_board_tensor_map(input_bt, board_geom(n->cfg.board_size, B).PT, box_rows, out, n->cin_pad);
 }
 
 // logits[b][plane * S2 + cell] = planes[(G + b * slots + y * GP + x)][plane]: the fp32 output of the
@@ -331,6 +334,23 @@ int ob200_net_finalize(ob200_net* n) {
         OB200_CUDA_OK(cudaGetDevice(&dev));
         OB200_CUDA_OK(cudaDeviceGetAttribute(&n->sm_count, cudaDevAttrMultiProcessorCount, dev));
     }
+    if (!n->wide && n->cin_pad == 64 && tower_resident_smem_bytes(c.board_size, 1 + 2 * c.blocks) != 0) {
+        // boards stay in shared memory through all the layers: one ordinary launch, whole-board boxes
+        const char* env = std::getenv("OB200_TOWER_RESIDENT");
+        const int L = 1 + 2 * c.blocks;
+        std::vector<unsigned char> host(tower_resident_layer_bytes() * L);
+        for (int l = 0; l < L; ++l)
+            tower_resident_fill_layer(host.data() + tower_resident_layer_bytes() * l, n->conv_w[l], n->conv_b[l], l >= 2 && !(l & 1));
+        unsigned char* dl = nullptr;
+        if (int rc = upload(n, &dl, host)) return rc;
+        n->resident_layers = dl;
+        const int box = tower_resident_box_rows(c.board_size);
+        if (int rc = make_board_tensor_map(n->act_in, n->rows, box, &n->in_map_board, n->cin_pad)) return rc;
+        if (int rc = make_board_tensor_map(n->act[0], n->rows, box, &n->out_map_board, F)) return rc;
+        // on unless switched off; an explicit choice about the single-launch tower (OB200_TOWER_FUSED, used by
+        // tests and comparisons to pick one of the other two paths) also switches it off unless it is asked for
+        n->resident = env ? env[0] != '0' : std::getenv("OB200_TOWER_FUSED") == nullptr;
+    }
     const size_t MB = c.max_batch;
     if (int rc = dev_alloc(n, &n->hp, MB * (planes_policy ? 1 : Kp), false)) return rc;
     if (int rc = dev_alloc(n, &n->hv, MB * Kv, false)) return rc;
@@ -365,15 +385,30 @@ int ob200_net_finalize(ob200_net* n) {
 namespace ob200 {
 namespace {
 
-// Tower + heads on device buffers.  `in_map` covers a board tensor of cin_pad channels holding
-// the B input boards.
 // The tower alone; returns the index of the activation buffer that holds its output in *out_buf.
-int tower_device(ob200_net* n, const BoardTensorMap& in_map, int B, int* out_buf, cudaStream_t st) {
+// `input_bt`: a board tensor of cin_pad channels holding the B input boards (the handle's own staging
+// tensor or a caller's).
+int tower_device(ob200_net* n, const void* input_bt, int B, int* out_buf, cudaStream_t st) {
     const ob200_net_config& c = n->cfg;
     const int S = c.board_size;
     const int F = c.filters;
     int x = 0, y = 1, z = 2;
     bool done = false;
+    const bool own_input = input_bt == n->act_in;
+    if (n->resident) {
+        BoardTensorMap board_map;
+        if (!own_input)
+            if (int rc = input_map(n, input_bt, B, tower_resident_box_rows(S), &board_map)) return rc;
+        const int rc = launch_conv_tower_resident(own_input ? n->in_map_board : board_map, n->out_map_board, n->resident_layers,
+                                                  1 + 2 * c.blocks, B, S, st);
+        if (rc == OB200_OK) { done = true; x = 0; }
+        else if (rc == OB200_ERR_UNSUPPORTED) n->resident = false;
+        else return rc;
+    }
+    BoardTensorMap conv_map;
+    if (!done && !own_input)
+        if (int rc = input_map(n, input_bt, B, n->box_in, &conv_map)) return rc;
+    const BoardTensorMap& in_map = own_input ? n->in_map_load : conv_map;
     // The fused tower pays off in a window of batch sizes (measured, 15x15: 4.5 % faster at 1,024 boards,
     // equal at 512, 45 % slower at 64, 19 % slower at 4,096).  Below about 8 tiles per CTA and layer the
     // hand-over of tiles through flags in global memory (store complete -> flag -> poll, about 3 us per
@@ -387,7 +422,7 @@ int tower_device(ob200_net* n, const BoardTensorMap& in_map, int B, int* out_buf
     // graph would see its own earlier flags, so a capturing stream gets the per-layer kernels.
     cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(st, &capturing) != cudaSuccess) { cudaGetLastError(); capturing = cudaStreamCaptureStatusNone; }
-    if (n->fused && capturing == cudaStreamCaptureStatusNone && (n->fused_forced || (l2_resident && enough_tiles))) {
+    if (!done && n->fused && capturing == cudaStreamCaptureStatusNone && (n->fused_forced || (l2_resident && enough_tiles))) {
         if (++n->fused_epoch == 0) ++n->fused_epoch;   // flags start at zero: epoch 0 is never used
         const int rc = launch_conv_tower(in_map, n->fused_layers, 1 + 2 * c.blocks, n->fused_flags, n->fused_pitch,
                                          n->fused_done, n->fused_epoch, B, S, st);
@@ -408,13 +443,13 @@ int tower_device(ob200_net* n, const BoardTensorMap& in_map, int B, int* out_buf
     return OB200_OK;
 }
 
-int forward_device(ob200_net* n, const BoardTensorMap& in_map, int B, float* policy_out, float* value_out,
+int forward_device(ob200_net* n, const void* input_bt, int B, float* policy_out, float* value_out,
                    int out_kind, cudaStream_t st) {
     const ob200_net_config& c = n->cfg;
     const int S = c.board_size;
     const int F = c.filters;
     int x = 0;
-    if (int rc = tower_device(n, in_map, B, &x, st)) return rc;
+    if (int rc = tower_device(n, input_bt, B, &x, st)) return rc;
     const int S2 = S * S, pc = c.policy_head_ch, vc = c.value_head_ch;
     if (c.policy_kind == OB200_POLICY_CONV_PLANES) {
         if (int rc = launch_conv_wide_maps(n->act_load[x], n->act_load[x], nullptr, n->pol_w, n->pol_b, B, S, F, n->pol_cout, 1, 0,
@@ -501,9 +536,7 @@ namespace ob200 {
 int net_forward_for_search(ob200_net* n, const void* input_bt, int B, float* policy, float* value, cudaStream_t st) {
     if (!n || !n->finalized) return set_error(OB200_ERR_STATE, "search: the network is not finalised");
     std::lock_guard<std::mutex> lk(n->mu);
-    BoardTensorMap in_map;
-    if (int rc = input_map(n, input_bt, B, &in_map)) return rc;
-    return forward_device(n, in_map, B, policy, value, OB200_OUT_PROBS, st);
+    return forward_device(n, input_bt, B, policy, value, OB200_OUT_PROBS, st);
 }
 const ob200_net_config* net_config(ob200_net* n) { return (n && n->finalized) ? &n->cfg : nullptr; }
 }  // namespace ob200
@@ -526,7 +559,7 @@ int ob200_net_infer_planes(ob200_net* n, const float* planes, int32_t B, int32_t
         std::memcpy(n->h_planes + (size_t)b * used * S2, planes + (size_t)b * C * S2, (size_t)used * S2 * sizeof(float));
     OB200_CUDA_OK(cudaMemcpyAsync(n->d_planes, n->h_planes, (size_t)B * used * S2 * sizeof(float), cudaMemcpyHostToDevice, n->stream));
     if (int rc = launch_planes_to_board_tensor(n->d_planes, B, used, c.board_size, n->cin_pad, n->act_in, n->stream)) return rc;
-    if (int rc = forward_device(n, n->in_map_load, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
+    if (int rc = forward_device(n, n->act_in, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
     return finish_host_call(n, B, policy_out, value_out);
 }
 
@@ -548,7 +581,7 @@ int ob200_net_infer_gomoku(ob200_net* n, const int16_t* history, const uint8_t* 
     OB200_CUDA_OK(cudaMemcpyAsync(n->d_tomove, n->h_tomove, (size_t)B, cudaMemcpyHostToDevice, n->stream));
     if (int rc = launch_encode_gomoku(n->d_hist, n->d_nhist, n->d_tomove, B, c.board_size, c.input_channels, n->cin_pad,
                                       n->act_in, n->stream)) return rc;
-    if (int rc = forward_device(n, n->in_map_load, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
+    if (int rc = forward_device(n, n->act_in, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
     return finish_host_call(n, B, policy_out, value_out);
 }
 
@@ -557,9 +590,7 @@ int ob200_net_forward_device(ob200_net* n, const void* input_board_tensor, int32
     if (int rc = check_call(n, B, input_board_tensor, policy_out, value_out, out_kind, "ob200_net_forward_device")) return rc;
     std::lock_guard<std::mutex> lk(n->mu);
     OB200_CUDA_OK(cudaSetDevice(n->cfg.device));
-    BoardTensorMap in_map;
-    if (int rc = input_map(n, input_board_tensor, B, &in_map)) return rc;
-    return forward_device(n, in_map, B, policy_out, value_out, out_kind, as_stream(stream));
+    return forward_device(n, input_board_tensor, B, policy_out, value_out, out_kind, as_stream(stream));
 }
 
 const void* ob200_net_debug_tower_output(ob200_net* n) { return n ? n->tower_out : nullptr; }
@@ -571,10 +602,8 @@ int ob200_net_tower_device(ob200_net* n, const void* input_board_tensor, int32_t
         return set_error(OB200_ERR_TOO_LARGE, "ob200_net_tower_device: batch %d outside [1, max_batch %d]", B, n->cfg.max_batch);
     std::lock_guard<std::mutex> lk(n->mu);
     OB200_CUDA_OK(cudaSetDevice(n->cfg.device));
-    BoardTensorMap in_map;
-    if (int rc = input_map(n, input_board_tensor, B, &in_map)) return rc;
     int x = 0;
-    return tower_device(n, in_map, B, &x, as_stream(stream));
+    return tower_device(n, input_board_tensor, B, &x, as_stream(stream));
 }
 
 int ob200_net_value_head_noalloc(ob200_net* n, const void* tower_board_tensor, int32_t B, float* value_out,

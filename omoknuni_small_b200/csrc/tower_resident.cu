@@ -1,0 +1,431 @@
+// The 64-filter residual tower with the boards RESIDENT in shared memory (sm_100a).
+//
+// A board of up to 15x15 cells is at most 256 padded positions x 64 channels = 32 KB in bf16, and a
+// 3x3 convolution never looks outside its own board (the padded row / column around every board is
+// zero).  So a CTA can take a board through ALL the layers without the activations ever leaving the
+// SM: two buffers per board (x: block input / residual / block output, y: the middle of a block),
+// the layer's output written by the epilogue threads straight into the 128-byte-swizzled layout the
+// next layer's MMA descriptors read.  Per tile that removes the TMA load of the input box, the TMA
+// load of the residual, the staging tile and the TMA store - 85 KB of shared-memory traffic that
+// otherwise competes with the tensor cores' operand reads - and every hand-over through global
+// memory.  What is left is the MMA issue rate (128x64x16 tcgen05.mma: 48 cycles each, 36 per tile).
+//
+//   * Two boards are in flight per CTA: while board A's layer-l accumulators are drained and written
+//     back as layer l+1's input, the tensor cores run board B's layer l.  TMEM holds both boards'
+//     accumulators for two consecutive layers (2 x 2 boards x 2 tiles x 64 columns = 512).
+//   * Weights stream from L2 through a one-layer ring of three 24 KB blocks (three taps each): the
+//     MMAs of a board go tap by tap (both tiles of a tap back to back), a block is handed back by a
+//     tcgen05.commit after the round's last board has used it, and the loader refills it with the
+//     same taps of the next layer - more than one board-layer (1.9 us) ahead of their first use.
+//   * Boards are assigned statically: CTA c takes boards c, c + grid, c + 2 grid, ... two at a time.
+//     The first input of a board arrives by TMA into y, the tower's output leaves by TMA from x.
+// There is no communication between CTAs, so this is an ordinary launch (and may be captured in a
+// graph).  Every wait is bounded; a thread that gives up raises the device error word.
+#include "internal.h"
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cstring>
+
+namespace ob200 {
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kC = 64;
+constexpr int kRowBytes = kC * 2;
+constexpr int kTapBytes = kC * kRowBytes;            // 8,192: one tap of one layer
+constexpr int kSlotRows = 256;                       // rows reserved per board
+constexpr int kGuardRows = 24;                       // zero rows before / between / after the two boards (>= S + 2)
+constexpr int kBufRows = 3 * kGuardRows + 2 * kSlotRows;     // 584
+constexpr int kBufBytes = kBufRows * kRowBytes;      // 74,752
+constexpr int kTmemCols = 512;
+constexpr int kEpiWarps = 8;                         // two groups of four: group g drains tile g of the board
+constexpr int kThreads = 64 + 32 * kEpiWarps;        // warp 0: MMA issue, warp 1: weight loader, warps 2-9: epilogue
+constexpr int kWGroups = 3;                          // the weight ring is handed over in groups of three taps
+constexpr int kWGroupBytes = 3 * kTapBytes;          // 24,576
+constexpr int kNumBars = 2 + 2 + 2 + kWGroups + kWGroups + 2 + 2;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+struct alignas(32) ResidentLayer {
+    const uint8_t* w;         // packed weights (ob200_pack_conv3x3_weights): 9 taps x 8 KB
+    const float* bias;        // [64]
+    int has_res;
+    int pad_[3];
+};
+
+struct ResidentParams {
+    const ResidentLayer* layers;
+    int n_layers;
+    int B, S, GP, slots;
+    int* error;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if ((i & 255) == 255 && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
+}
+constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kC >> 3) << 17) |
+                            ((uint32_t)(kTileM >> 4) << 24);
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+        "mov.b64 da, {%1, %3};\nmov.b64 db, {%2, %3};\n"
+        "setp.ne.b32 p, %5, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(kIdesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+
+// relu(v) rounded to bf16, two at a time (lo in the low half)
+__device__ __forceinline__ uint32_t relu_bf16x2(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+// One 128-byte row of a layer's output: relu(accumulator + bias [+ residual, which is the row's old content]).
+// 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8).
+template <bool RES>
+__device__ __forceinline__ void store_row(uint8_t* dst_row, int row, const uint32_t* r, const float* bias_t) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        uint4* slot = reinterpret_cast<uint4*>(dst_row + ((c ^ (row & 7)) << 4));
+        const float4 b0 = *reinterpret_cast<const float4*>(bias_t + c * 8), b1 = *reinterpret_cast<const float4*>(bias_t + c * 8 + 4);
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        uint32_t rw[4] = {0u, 0u, 0u, 0u};
+        if (RES) { const uint4 rv = *slot; rw[0] = rv.x; rw[1] = rv.y; rw[2] = rv.z; rw[3] = rv.w; }
+        uint32_t ow[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bb[2 * j];
+            float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bb[2 * j + 1];
+            if (RES) { v0 += __uint_as_float(rw[j] << 16); v1 += __uint_as_float(rw[j] & 0xFFFF0000u); }
+            ow[j] = relu_bf16x2(v0, v1);
+        }
+        *slot = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+__device__ __forceinline__ void store_zero_row(uint8_t* dst_row) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(dst_row)[c] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+// T: 128-row tiles per board (1 for boards up to 10x10, 2 up to 15x15).
+template <int T>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
+                           const ResidentParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* x_s = smem;                                   // [guard][board 0][guard][board 1][guard]
+    uint8_t* y_s = x_s + kBufBytes;
+    uint8_t* w_s = y_s + kBufBytes;                        // nine tap blocks of the current / next layer
+    float* bias_s = reinterpret_cast<float*>(w_s + 9 * kTapBytes);   // [n_layers][64]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(bias_s + p.n_layers * kC);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar0 = smem_u32(bars);
+    auto in_full = [&](int bd) { return bar0 + 8u * bd; };               // the board's first input has landed in y
+    auto act_ready = [&](int bd) { return bar0 + 8u * (2 + bd); };       // the previous layer's output is written
+    auto acc_full = [&](int bd) { return bar0 + 8u * (4 + bd); };        // the board's MMAs of this layer are complete
+    auto w_full = [&](int g) { return bar0 + 8u * (6 + g); };
+    auto w_empty = [&](int g) { return bar0 + 8u * (6 + kWGroups + g); };
+    auto out_written = [&](int bd) { return bar0 + 8u * (6 + 2 * kWGroups + bd); };    // the tower's output is complete in x
+    auto x_free = [&](int bd) { return bar0 + 8u * (8 + 2 * kWGroups + bd); };         // the output store has read x
+
+    if (threadIdx.x == 0) {
+        for (int bd = 0; bd < 2; ++bd) {
+            mbar_init(in_full(bd), 1); mbar_init(act_ready(bd), 4 * T); mbar_init(acc_full(bd), 1);
+            mbar_init(out_written(bd), 4 * T); mbar_init(x_free(bd), 1);
+        }
+        for (int g = 0; g < kWGroups; ++g) { mbar_init(w_full(g), 1); mbar_init(w_empty(g), 1); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&in_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&out_map) : "memory");
+    }
+    // guards, and the rows of a slot beyond the board, are zero for the kernel's lifetime
+    for (int i = threadIdx.x; i < 2 * kBufBytes / 16; i += kThreads) reinterpret_cast<uint4*>(x_s)[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = threadIdx.x; i < p.n_layers * kC; i += kThreads) bias_s[i] = p.layers[i / kC].bias[i % kC];
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the zeros -> reads by the tensor cores / TMA
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    // this CTA's boards: blockIdx.x, + gridDim.x, ...; two per round
+    const int n_my = ((int)blockIdx.x < p.B) ? (p.B - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int rounds = (n_my + 1) / 2;
+    const int L = p.n_layers;
+    auto board_of = [&](int round, int bd) { return (int)blockIdx.x + (2 * round + bd) * (int)gridDim.x; };
+    auto slot_off = [&](int bd) { return (uint32_t)((kGuardRows + bd * (kSlotRows + kGuardRows)) * kRowBytes); };
+
+    if (warp == 1) {
+        // ---------------- weight loader ----------------
+        // constants of the network: may start before the kernels ahead of this one in the stream are complete
+        if (lane == 0) {
+            const int total = rounds * L;
+            bool ok = true;
+            for (int it = 0; ok && it < total; ++it) {
+                const uint8_t* src = p.layers[it % L].w;
+                for (int g = 0; g < kWGroups; ++g) {
+                    if (it > 0 && !mbar_wait(w_empty(g), (uint32_t)(it - 1) & 1u, abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(w_full(g), (uint32_t)kWGroupBytes);
+                    bulk_g2s(smem_u32(w_s + g * kWGroupBytes), src + (size_t)g * kWGroupBytes, (uint32_t)kWGroupBytes, w_full(g));
+                }
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(p.error, 4); }
+        }
+    } else if (warp == 0) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int tap_off[9];
+#pragma unroll
+            for (int tap = 0; tap < 9; ++tap) tap_off[tap] = ((tap / 3) * p.GP + (tap % 3)) * (kRowBytes >> 4);
+            // descriptor of the row GP + 1 rows above a board's first row (tap 0 of position 0), per buffer and board
+            const uint32_t a_base_x = desc_lo(smem_u32(x_s) + slot_off(0) - (uint32_t)((p.GP + 1) * kRowBytes));
+            const uint32_t a_base_y = desc_lo(smem_u32(y_s) + slot_off(0) - (uint32_t)((p.GP + 1) * kRowBytes));
+            const uint32_t w_lo = desc_lo(smem_u32(w_s));
+            uint32_t ready_cnt[2] = {0u, 0u};
+            bool ok = true;
+            int it = 0;
+            for (int round = 0; ok && round < rounds; ++round) {
+                const int nb = n_my - 2 * round >= 2 ? 2 : 1;
+                for (int l = 0; ok && l < L; ++l, ++it) {
+                    const uint32_t a_layer = (l == 0 || !(l & 1)) ? a_base_y : a_base_x;   // stem and second convolutions read y, first ones x
+                    // unrolled over the two boards: "first board" is then a compile-time fact in each copy, and every
+                    // instruction between two MMAs costs issue time
+#pragma unroll
+                    for (int bd = 0; bd < 2; ++bd) {
+                        if (bd >= nb) break;
+                        if (l == 0) {
+                            if (!mbar_wait(in_full(bd), (uint32_t)round & 1u, abort_flag)) { ok = false; break; }
+                        } else {
+                            if (!mbar_wait(act_ready(bd), ready_cnt[bd] & 1u, abort_flag)) { ok = false; break; }
+                            ++ready_cnt[bd];
+                        }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t a_lo = a_layer + (uint32_t)(bd * ((kSlotRows + kGuardRows) * kRowBytes >> 4));
+                        const uint32_t d_tmem = tmem_base + (uint32_t)((it & 1) * 256 + bd * 128);
+                        const bool first_board = bd == 0, last_board = bd == nb - 1;
+#pragma unroll
+                        for (int tap = 0; tap < 9; ++tap) {
+                            // the issuing thread pays for every instruction between two MMAs (a wait costs about
+                            // 50 cycles, a commit 25, an MMA 48): weights are waited for and handed back three taps at a time
+                            if (first_board && tap % 3 == 0 && !mbar_wait(w_full(tap / 3), (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
+#pragma unroll
+                            for (int tile = 0; tile < T; ++tile) {
+#pragma unroll
+                                for (int ks = 0; ks < kC / 16; ++ks)
+                                    umma(d_tmem + (uint32_t)(tile * kC),
+                                         a_lo + (uint32_t)(tile * (kTileM * kRowBytes >> 4) + tap_off[tap] + ks * 2),
+                                         w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), (tap | ks) ? 1u : 0u);
+                            }
+                            if (last_board && tap % 3 == 2) umma_commit(w_empty(tap / 3));   // the round's boards are through with these taps
+                        }
+                        if (!ok) break;
+                        umma_commit(acc_full(bd));
+                    }
+                }
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(p.error, 2); }
+        }
+    } else if (warp - 2 < 4 * T) {
+        // ---------------- epilogue: TMEM -> registers -> the next layer's input rows ----------------
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // inputs come from the kernels ahead in the stream
+        const int group = (warp - 2) >> 2;
+        const int q = warp & 3;                          // TMEM lane quadrant this warp may read
+        const int row = group * kTileM + q * 32 + lane;  // row within the board's slot
+        const bool valid = row < p.slots && (row / p.GP < p.S) && (row % p.GP < p.S);
+        const bool elected = warp == 2 && lane == 0;     // issues the boards' loads and stores
+        const uint32_t in_bytes = (uint32_t)p.slots * kRowBytes;
+        bool ok = true;
+        if (elected)
+            for (int bd = 0; bd < 2 && bd < n_my; ++bd) {
+                mbar_arrive_expect_tx(in_full(bd), in_bytes);
+                tma_load_2d(smem_u32(y_s) + slot_off(bd), &in_map, 0, OB200_GUARD + board_of(0, bd) * p.slots, in_full(bd));
+            }
+        uint32_t full_cnt0 = 0u, full_cnt1 = 0u;
+        int it = 0;
+        for (int round = 0; ok && round < rounds; ++round) {
+            const int nb = n_my - 2 * round >= 2 ? 2 : 1;
+            for (int l = 0; ok && l < L; ++l, ++it) {
+                const bool has_res = p.layers[l].has_res != 0;
+                const bool to_x = l == 0 || !(l & 1);
+                const float* bias_t = bias_s + l * kC;
+                for (int bd = 0; bd < nb; ++bd) {
+                    // every wait's outcome is voted on, so that a warp gives up as a whole (the TMEM loads below
+                    // need all 32 lanes; the elected lane may come late from its store)
+                    bool good = mbar_wait(acc_full(bd), (bd ? full_cnt1 : full_cnt0) & 1u, abort_flag);
+                    if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+                    if (bd) ++full_cnt1; else ++full_cnt0;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    uint32_t r[kC];
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((it & 1) * 256 + bd * 128 + group * kC);
+                    tmem_ld32(taddr, r);
+                    tmem_ld32(taddr + 32, r + 32);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (l == 0 && round > 0) {
+                        // x still holds the previous round's output until its store has read it
+                        if (elected) {
+                            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                            mbar_arrive(x_free(bd));
+                        }
+                        good = mbar_wait(x_free(bd), (uint32_t)(round - 1) & 1u, abort_flag);
+                        if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+                    }
+                    uint8_t* dst_row = (to_x ? x_s : y_s) + slot_off(bd) + row * kRowBytes;
+                    if (!valid) store_zero_row(dst_row);
+                    else if (has_res) store_row<true>(dst_row, row, r, bias_t);
+                    else store_row<false>(dst_row, row, r, bias_t);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // rows -> the tensor cores' / the store's reads
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (l + 1 < L) {
+                        if (lane == 0) mbar_arrive(act_ready(bd));
+                    } else {
+                        if (lane == 0) mbar_arrive(out_written(bd));
+                        if (elected) good = mbar_wait(out_written(bd), (uint32_t)round & 1u, abort_flag);
+                        if (elected && good) {
+                            tma_store_2d(&out_map, 0, OB200_GUARD + board_of(round, bd) * p.slots, smem_u32(x_s) + slot_off(bd));
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                            // y is free (the last layer's MMAs are complete) and so are the accumulators (every warp has
+                            // drained them): the board's successor may come in
+                            if (2 * (round + 1) + bd < n_my) {
+                                mbar_arrive_expect_tx(in_full(bd), in_bytes);
+                                tma_load_2d(smem_u32(y_s) + slot_off(bd), &in_map, 0, OB200_GUARD + board_of(round + 1, bd) * p.slots,
+                                            in_full(bd));
+                            }
+                        }
+                        if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+                    }
+                }
+            }
+        }
+        if (elected) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the output stores are complete
+        if (!ok) { *abort_flag = 1; atomicExch(p.error, 3); }
+    }
+
+    // ---------------- teardown ----------------
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);    // copies in flight into shared memory land first
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
+    }
+}
+
+}  // namespace
+
+size_t tower_resident_layer_bytes() { return sizeof(ResidentLayer); }
+
+void tower_resident_fill_layer(void* dst, const void* w, const float* bias, int has_res) {
+    ResidentLayer d;
+    std::memset(&d, 0, sizeof(d));
+    d.w = static_cast<const uint8_t*>(w); d.bias = bias; d.has_res = has_res;
+    std::memcpy(dst, &d, sizeof(d));
+}
+
+// Rows of the load / store boxes: one whole board.
+int tower_resident_box_rows(int S) { return (S + 1) * (S + 1); }
+
+// Shared memory the kernel needs, or 0 when the board or the depth does not fit.
+size_t tower_resident_smem_bytes(int S, int n_layers) {
+    if (S < 1 || (S + 1) * (S + 1) > kSlotRows || S + 2 > kGuardRows || n_layers < 1) return 0;
+    const size_t total = 2 * (size_t)kBufBytes + 9 * (size_t)kTapBytes + (size_t)n_layers * kC * 4 + kNumBars * 8 + 16 + 1024;
+    return total <= 232448 ? total : 0;
+}
+
+// The whole tower in one ordinary launch.  in_map / out_map: boxes of tower_resident_box_rows(S)
+// rows over the 64-channel input tensor and the output tensor; layers_dev: n_layers descriptors on
+// the device.
+int launch_conv_tower_resident(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* layers_dev,
+                               int n_layers, int B, int S, cudaStream_t st) {
+    if (!layers_dev || n_layers < 1 || B <= 0) return set_error(OB200_ERR_INVALID, "resident tower: bad arguments");
+    const size_t smem = tower_resident_smem_bytes(S, n_layers);
+    if (!smem) return set_error(OB200_ERR_UNSUPPORTED, "resident tower: board size %d / %d layers do not fit shared memory", S, n_layers);
+    if (int rc = require_device()) return rc;
+    int dev = 0, sms = 0;
+    OB200_CUDA_OK(cudaGetDevice(&dev));
+    OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int slots = (S + 1) * (S + 1);
+    const bool two_tiles = slots > kTileM;
+    static size_t configured[64][2] = {{0, 0}};
+    if (dev >= 0 && dev < 64 && configured[dev][two_tiles] < smem) {
+        if (two_tiles) OB200_CUDA_OK(cudaFuncSetAttribute(conv_tower_resident_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        else OB200_CUDA_OK(cudaFuncSetAttribute(conv_tower_resident_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[dev][two_tiles] = smem;
+    }
+    ResidentParams p;
+    p.layers = static_cast<const ResidentLayer*>(layers_dev); p.n_layers = n_layers; p.B = B; p.S = S; p.GP = S + 1; p.slots = slots;
+    p.error = device_error_word();
+    if (!p.error) return set_error(OB200_ERR_CUDA, "resident tower: cannot resolve the device error word");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(B < sms ? B : sms); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    const CUtensorMap& im = *reinterpret_cast<const CUtensorMap*>(&in_map);
+    const CUtensorMap& om = *reinterpret_cast<const CUtensorMap*>(&out_map);
+    if (two_tiles) OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv_tower_resident_kernel<2>, im, om, p));
+    else OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv_tower_resident_kernel<1>, im, om, p));
+    OB200_LAUNCHED("conv_tower_resident_kernel");
+    return OB200_OK;
+}
+
+}  // namespace ob200

@@ -235,6 +235,43 @@ def test_network_kaiming_normal_benchmark_weights(api):
     assert (logits.argmax(1) == order[:, -1])[margin > 2 * f_err].all()
 
 
+def pick_tower(monkeypatch, which):
+    """Pins the tower path a network handle created afterwards will use: "layers" (a launch per
+    layer), "fused" (one cooperative launch, tiles handed over through flags) or "resident" (one
+    launch, boards kept in shared memory)."""
+    if which == "resident":
+        monkeypatch.delenv("OB200_TOWER_FUSED", raising=False)
+        monkeypatch.setenv("OB200_TOWER_RESIDENT", "1")
+    else:
+        monkeypatch.setenv("OB200_TOWER_RESIDENT", "0")
+        monkeypatch.setenv("OB200_TOWER_FUSED", "2" if which == "fused" else "0")
+
+
+@pytest.mark.parametrize("S,blocks,B", [(15, 1, 1), (15, 1, 2), (15, 2, 3), (9, 2, 5), (10, 1, 40), (11, 1, 40), (13, 4, 700),
+                                        (15, 3, 150), (15, 10, 300), (15, 10, 1024)])
+def test_resident_tower_equals_layer_by_layer(api, monkeypatch, S, blocks, B):
+    """The board-resident tower (activations never leave shared memory) runs the same arithmetic in
+    the same order as the launch-per-layer path: outputs must be bit-identical.  One and two
+    boards per CTA, an odd number of boards per CTA, boards of one tile (up to 10x10) and of two."""
+    shapes = synth.net_tensor_shapes(S, 17, 64, blocks, S * S, 2, 1)
+    w = synth.make_weights(shapes, seed=5, init="torch_default", bn="random")
+    x = synth.make_stone_planes(B, S, 17, seed=4000 + B)
+    outs = []
+    for which in ("resident", "layers"):
+        pick_tower(monkeypatch, which)
+        net = make_net(api, w, dict(cin=17, S=S, blocks=blocks, F=64, A=S * S, pc=2, vc=1), B)
+        before = api.counters()["kernel_launches"]
+        logits, v = net.infer_planes(x, api.OUT_LOGITS)
+        launches = api.counters()["kernel_launches"] - before
+        logits2, v2 = net.infer_planes(x, api.OUT_LOGITS)
+        assert np.array_equal(logits, logits2) and np.array_equal(v, v2)
+        outs.append((logits, v, launches))
+        net.close()
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+    assert outs[0][2] == outs[1][2] - 2 * blocks                   # 1 tower launch instead of 1 + 2 * blocks
+    assert api.device_error_code() == 0
+
+
 @pytest.mark.parametrize("B", [3, 300, 1100])
 def test_fused_tower_equals_layer_by_layer(api, monkeypatch, B):
     """The single-launch tower (CTAs walk the layers, tiles hand over through flags) and the
@@ -244,8 +281,8 @@ def test_fused_tower_equals_layer_by_layer(api, monkeypatch, B):
     w = synth.make_weights(shapes, seed=5, init="torch_default", bn="random")
     x = synth.make_stone_planes(B, 15, 17, seed=4000 + B)
     outs = []
-    for fused in ("2", "0"):      # 2: the single launch at every batch size, 0: never
-        monkeypatch.setenv("OB200_TOWER_FUSED", fused)
+    for which in ("fused", "layers"):
+        pick_tower(monkeypatch, which)
         net = make_net(api, w, dict(cin=17, S=15, blocks=10, F=64, A=225, pc=2, vc=1), B)
         before = api.counters()["kernel_launches"]
         logits, v = net.infer_planes(x, api.OUT_LOGITS)
@@ -259,13 +296,45 @@ def test_fused_tower_equals_layer_by_layer(api, monkeypatch, B):
     assert api.device_error_code() == 0
 
 
-@pytest.mark.parametrize("S,blocks,B,cin,fused", [(9, 0, 5, 3, "1"), (5, 1, 17, 17, "2"), (30, 1, 3, 19, "2"),
-                                                    (19, 2, 70, 17, "2"), (19, 2, 70, 17, "0"), (7, 3, 1, 64, "2")])
-def test_network_odd_shapes(api, monkeypatch, S, blocks, B, cin, fused):
-    """Board sizes from 5 to 30, a tower without blocks, 3 / 64 input planes, single boards; with the
-    single-launch tower forced on ("2") and off ("0")."""
+@pytest.mark.parametrize("which,B,iters", [("fused", 1024, 400), ("fused", 700, 200), ("resident", 1024, 400),
+                                           ("resident", 301, 200)])
+def test_single_launch_tower_repeats_bit_identically(api, monkeypatch, which, B, iters):
+    """Hundreds of back-to-back single-launch towers on one input: every result equals the first
+    (a tile read before its producer wrote it, or a flag left over from an earlier launch, would
+    show up as a different output sooner or later)."""
+    import torch
+    pick_tower(monkeypatch, which)
+    shapes = synth.net_tensor_shapes(15, 17, 64, 10, 225, 2, 1)
+    w = synth.make_weights(shapes, seed=42, init="kaiming_normal")
+    net = api.Net(17, 15, 10, 64, 225, 2, 1, 256, B).load(w)
+    _, hist, nh, tm = synth.make_gomoku_games(B, 15, seed=B)
+    dh, dn, dt = (torch.from_numpy(a).cuda() for a in (hist, nh, tm))
+    bt = api.encode_gomoku(dh, dn, dt, 15, 17, 64)
+    pol = torch.empty((B, 225), device="cuda")
+    val = torch.empty(B, device="cuda")
+    net.forward_device(bt, B, pol, val, api.OUT_LOGITS)
+    torch.cuda.synchronize()
+    p0, v0 = pol.clone(), val.clone()
+    different = torch.zeros((), dtype=torch.int64, device="cuda")
+    for _ in range(iters):
+        net.forward_device(bt, B, pol, val, api.OUT_LOGITS)
+        different += (pol != p0).any() | (val != v0).any()
+    torch.cuda.synchronize()
+    net.close()
+    assert int(different) == 0
+    assert api.device_error_code() == 0
+
+
+@pytest.mark.parametrize("S,blocks,B,cin,which", [(9, 0, 5, 3, "fused"), (5, 1, 17, 17, "fused"), (30, 1, 3, 19, "fused"),
+                                                    (19, 2, 70, 17, "fused"), (19, 2, 70, 17, "layers"), (7, 3, 1, 64, "fused"),
+                                                    (9, 0, 5, 3, "resident"), (5, 1, 17, 17, "resident"), (7, 3, 1, 64, "resident"),
+                                                    (15, 2, 149, 19, "resident"), (19, 1, 9, 17, "resident")])
+def test_network_odd_shapes(api, monkeypatch, S, blocks, B, cin, which):
+    """Board sizes from 5 to 30, a tower without blocks, 3 / 64 input planes, single boards; on each of
+    the three tower paths (a 19x19 board does not fit the board-resident one, which then hands over to
+    the others)."""
     from oracle import net_ref
-    monkeypatch.setenv("OB200_TOWER_FUSED", fused)
+    pick_tower(monkeypatch, which)
     A = S * S
     shapes = synth.net_tensor_shapes(S, cin, 64, blocks, A, 2, 1)
     w = synth.make_weights(shapes, seed=S + blocks, init="torch_default", bn="random")
