@@ -333,7 +333,7 @@ def gpu_arm(args):
             t0 = time.perf_counter()
             net.infer_gomoku(p_hist, p_nh, p_tm, out=outs)
             e2e_s += time.perf_counter() - t0
-        # ---- the dominant kernel alone: the whole tower (one cooperative launch at this batch) ----
+        # ---- the dominant kernel alone: the whole tower (one launch) ----
         bt_in = capi.encode_gomoku(d_hist, d_nh, d_tm, 15, 17, net.input_tensor_channels())
         tower_reps = 5
 
@@ -344,6 +344,7 @@ def gpu_arm(args):
         c_t0 = capi.counters()["kernel_launches"]
         tower_ms = float(np.mean(timed(tower_loop, 5))) / tower_reps
         tower_launches = (capi.counters()["kernel_launches"] - c_t0) // (5 * tower_reps)
+        tower_path = net.tower_path()     # 2: boards resident in shared memory, 1: cooperative launch, 0: a launch per layer
         # ---- the same network at the other batch sizes of the configurations (256: configs[0]; 4096) ----
         sweep = []
         if not args.no_sweep:
@@ -461,8 +462,9 @@ def gpu_arm(args):
                     "d2h_bytes_per_step": B * 226 * 4},
             "gpu_launches": int(launches), "counters_all_gpus": totals,
             "tower_tflops": value / world * flops_eval / 1e12,
-            "roofline": {"kernel": ("conv_tower_kernel (stem + 20 convolutions 64->64 in one launch)" if tower_launches == 1
-                                    else "conv3x3_kernel x 21 (one launch per layer)"),
+            "roofline": {"kernel": {2: "conv_tower_resident_kernel (stem + 20 convolutions 64->64 in one launch, boards resident in shared memory)",
+                                    1: "conv_tower_kernel (stem + 20 convolutions 64->64 in one cooperative launch)",
+                                    0: "conv3x3_kernel x 21 (one launch per layer)"}.get(tower_path, "?"),
                          "bound": "tensor", "achieved": tower_tf, "peak": peaks["bf16_burst"], "unit": "TFLOP/s",
                          "frac": tower_tf / peaks["bf16_burst"],
                          "frac_of_sustained": tower_tf / peaks["bf16_sustained"] if peaks["bf16_sustained"] else None,

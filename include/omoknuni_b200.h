@@ -348,6 +348,14 @@ int ob200_net_forward_device(ob200_net* net, const void* input_board_tensor, int
 /* Device pointer of the tower's output board tensor of the last forward
  * (filters channels), for tests. */
 const void* ob200_net_debug_tower_output(ob200_net* net);
+/* Which tower path the last forward took, for tests and measurements:
+ * 0 one launch per layer, 1 one cooperative launch (tiles handed over through
+ * flags), 2 one launch with the boards resident in shared memory; -1 before the
+ * first forward.  Environment, read when a handle is finalised:
+ * OB200_TOWER_RESIDENT=0 switches path 2 off; OB200_TOWER_FUSED=0 / 2 switches
+ * path 1 off / forces it at every batch size (and, unless OB200_TOWER_RESIDENT=1,
+ * switches path 2 off). */
+int32_t ob200_net_debug_tower_path(ob200_net* net);
 /* The residual tower alone (stem + blocks), DEVICE in, asynchronous on `stream`;
  * the result is the board tensor ob200_net_debug_tower_output() points at.
  * For measurement and for callers that run their own heads. */

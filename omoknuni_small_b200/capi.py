@@ -94,6 +94,7 @@ SIGNATURES = {
                                            C.c_void_p]),
     "ob200_debug_bounded_wait": (C.c_int, [C.c_int32, C.c_void_p]),
     "ob200_net_debug_tower_output": (C.c_void_p, [C.c_void_p]),
+    "ob200_net_debug_tower_path": (C.c_int32, [C.c_void_p]),
     "ob200_net_tower_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "ob200_net_input_tensor_channels": (C.c_int32, [C.c_void_p]),
     "ob200_net_value_head_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
@@ -391,6 +392,10 @@ class Net:
 
     def tower_output_ptr(self):
         return lib().ob200_net_debug_tower_output(self.h)
+
+    def tower_path(self):
+        """0 launch per layer, 1 one cooperative launch, 2 boards resident in shared memory (last forward)."""
+        return int(lib().ob200_net_debug_tower_path(self.h))
 
     def value_head_noalloc(self, tower_ptr, B, value_out):
         """Value head from a tower output already on the device, using only the

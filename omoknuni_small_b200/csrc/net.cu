@@ -33,6 +33,7 @@ struct ob200_net {
     void* act_in = nullptr;         // cin_pad channels
     void* act[3] = {nullptr, nullptr, nullptr};      // filters channels each
     const void* tower_out = nullptr;
+    int tower_path = -1;            // path of the last forward: 0 per layer, 1 cooperative launch, 2 board-resident
     // the fused tower (64 filters): per-layer descriptors and tile flags on the device
     void* fused_layers = nullptr; int *fused_flags = nullptr, *fused_done = nullptr; int fused_pitch = 0, fused_epoch = 0, fused_final = 0;
     bool fused = false, fused_forced = false;   // forced: OB200_TOWER_FUSED=2 (tests: every batch size)
@@ -401,7 +402,7 @@ int tower_device(ob200_net* n, const void* input_bt, int B, int* out_buf, cudaSt
             if (int rc = input_map(n, input_bt, B, tower_resident_box_rows(S), &board_map)) return rc;
         const int rc = launch_conv_tower_resident(own_input ? n->in_map_board : board_map, n->out_map_board, n->resident_layers,
                                                   1 + 2 * c.blocks, B, S, st);
-        if (rc == OB200_OK) { done = true; x = 0; }
+        if (rc == OB200_OK) { done = true; x = 0; n->tower_path = 2; }
         else if (rc == OB200_ERR_UNSUPPORTED) n->resident = false;
         else return rc;
     }
@@ -426,11 +427,12 @@ int tower_device(ob200_net* n, const void* input_bt, int B, int* out_buf, cudaSt
         if (++n->fused_epoch == 0) ++n->fused_epoch;   // flags start at zero: epoch 0 is never used
         const int rc = launch_conv_tower(in_map, n->fused_layers, 1 + 2 * c.blocks, n->fused_flags, n->fused_pitch,
                                          n->fused_done, n->fused_epoch, B, S, st);
-        if (rc == OB200_OK) { done = true; x = n->fused_final; }
+        if (rc == OB200_OK) { done = true; x = n->fused_final; n->tower_path = 1; }
         else if (rc == OB200_ERR_UNSUPPORTED) n->fused = false;   // not launchable here: layer by layer from now on
         else return rc;
     }
     if (!done) {
+        n->tower_path = 0;
         if (int rc = tower_conv(n, in_map, n->cin_pad, n->act_store[x], nullptr, 0, B, st)) return rc;
         for (int i = 0; i < c.blocks; ++i) {
             if (int rc = tower_conv(n, n->act_load[x], F, n->act_store[y], nullptr, 1 + 2 * i, B, st)) return rc;
@@ -594,6 +596,7 @@ int ob200_net_forward_device(ob200_net* n, const void* input_board_tensor, int32
 }
 
 const void* ob200_net_debug_tower_output(ob200_net* n) { return n ? n->tower_out : nullptr; }
+int32_t ob200_net_debug_tower_path(ob200_net* n) { return n ? n->tower_path : -1; }
 
 int ob200_net_tower_device(ob200_net* n, const void* input_board_tensor, int32_t B, ob200_stream stream) {
     if (!n || !input_board_tensor) return set_error(OB200_ERR_INVALID, "ob200_net_tower_device: null argument");

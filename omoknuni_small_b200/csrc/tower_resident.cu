@@ -10,17 +10,23 @@
 // otherwise competes with the tensor cores' operand reads - and every hand-over through global
 // memory.  What is left is the MMA issue rate (128x64x16 tcgen05.mma: 48 cycles each, 36 per tile).
 //
-//   * Two boards are in flight per CTA: while board A's layer-l accumulators are drained and written
-//     back as layer l+1's input, the tensor cores run board B's layer l.  TMEM holds both boards'
-//     accumulators for two consecutive layers (2 x 2 boards x 2 tiles x 64 columns = 512).
+//   * Two boards are in flight per CTA, each with its own MMA-issuing warp: while board 0's layer-l
+//     accumulators are drained and written back as layer l+1's input, the tensor cores run board 1's
+//     layer l (board 1 runs two thirds of a layer behind board 0).  The thread that issues
+//     tcgen05.mma pays for every instruction between two MMAs and waits at every layer boundary; with
+//     two issuers the tensor cores always have the other board's MMAs to take.  TMEM holds both
+//     boards' accumulators for two consecutive layers (2 x 2 boards x 2 tiles x 64 columns = 512).
 //   * Weights stream from L2 through a one-layer ring of three 24 KB blocks (three taps each): the
 //     MMAs of a board go tap by tap (both tiles of a tap back to back), a block is handed back by a
-//     tcgen05.commit after the round's last board has used it, and the loader refills it with the
-//     same taps of the next layer - more than one board-layer (1.9 us) ahead of their first use.
+//     tcgen05.commit of each board's issuer, and the loader refills it with the same taps of the
+//     next layer when both have come in.
 //   * Boards are assigned statically: CTA c takes boards c, c + grid, c + 2 grid, ... two at a time.
 //     The first input of a board arrives by TMA into y, the tower's output leaves by TMA from x.
 // There is no communication between CTAs, so this is an ordinary launch (and may be captured in a
 // graph).  Every wait is bounded; a thread that gives up raises the device error word.
+// Measured (15x15, 21 layers, B200): 8,000-8,400 cycles per layer for a pair of boards (four tiles), against
+// 6,912 for the MMAs alone; 370 us for 1,024 boards (932 TFLOP/s) and 1,327 us for 4,096 (1,039 TFLOP/s)
+// where a launch per layer takes 432 / 1,650 us; 74-84 us for 1 to 148 boards (93-140 us per layer-launches).
 #include "internal.h"
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -39,10 +45,11 @@ constexpr int kBufRows = 3 * kGuardRows + 2 * kSlotRows;     // 584
 constexpr int kBufBytes = kBufRows * kRowBytes;      // 74,752
 constexpr int kTmemCols = 512;
 constexpr int kEpiWarps = 8;                         // two groups of four: group g drains tile g of the board
-constexpr int kThreads = 64 + 32 * kEpiWarps;        // warp 0: MMA issue, warp 1: weight loader, warps 2-9: epilogue
+constexpr int kThreads = 64 + 32 * kEpiWarps + 32;   // warps 0, 1: MMA issue for board 0 / 1, warps 2-9: epilogue, warp 10: weight loader
+constexpr int kStaggerTap = 6;                       // board 1 starts a layer when board 0 has issued this tap of it
 constexpr int kWGroups = 3;                          // the weight ring is handed over in groups of three taps
 constexpr int kWGroupBytes = 3 * kTapBytes;          // 24,576
-constexpr int kNumBars = 2 + 2 + 2 + kWGroups + kWGroups + 2 + 2;
+constexpr int kNumBars = 2 + 2 + 2 + kWGroups + kWGroups + 2 + 2 + 1;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct alignas(32) ResidentLayer {
@@ -155,6 +162,34 @@ __device__ __forceinline__ void store_zero_row(uint8_t* dst_row) {
     for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(dst_row)[c] = make_uint4(0u, 0u, 0u, 0u);
 }
 
+// The MMAs of one board and layer: 9 taps x T tiles x 4 k-steps, tap-outer so that a block of three taps
+// is handed back to the loader as early as possible.  ALONE: the round has a single board, whose issuer
+// hands the weight blocks back twice (the loader counts two boards).  SIGNAL: board 0 of a pair tells
+// board 1's issuer when it has issued tap kStaggerTap.  Everything that can be is a compile-time fact:
+// every instruction between two MMAs costs the issuing thread time.
+template <int T, bool ALONE, bool SIGNAL>
+__device__ __forceinline__ bool issue_board_layer(uint32_t d_tmem, uint32_t a_lo, uint32_t w_lo, const int (&tap_off)[9],
+                                                  uint32_t w_full0, uint32_t w_empty0, uint32_t stagger, uint32_t parity,
+                                                  volatile int* abort_flag) {
+#pragma unroll
+    for (int tap = 0; tap < 9; ++tap) {
+        if (tap % 3 == 0 && !mbar_wait(w_full0 + 8u * (tap / 3), parity, abort_flag)) return false;
+#pragma unroll
+        for (int tile = 0; tile < T; ++tile) {
+#pragma unroll
+            for (int ks = 0; ks < kC / 16; ++ks)
+                umma(d_tmem + (uint32_t)(tile * kC), a_lo + (uint32_t)(tile * (kTileM * kRowBytes >> 4) + tap_off[tap] + ks * 2),
+                     w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), (tap | ks) ? 1u : 0u);
+        }
+        if (tap % 3 == 2) {
+            umma_commit(w_empty0 + 8u * (tap / 3));
+            if (ALONE) umma_commit(w_empty0 + 8u * (tap / 3));
+        }
+        if (SIGNAL && tap == kStaggerTap) mbar_arrive(stagger);
+    }
+    return true;
+}
+
 // T: 128-row tiles per board (1 for boards up to 10x10, 2 up to 15x15).
 template <int T>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -179,13 +214,15 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
     auto w_empty = [&](int g) { return bar0 + 8u * (6 + kWGroups + g); };
     auto out_written = [&](int bd) { return bar0 + 8u * (6 + 2 * kWGroups + bd); };    // the tower's output is complete in x
     auto x_free = [&](int bd) { return bar0 + 8u * (8 + 2 * kWGroups + bd); };         // the output store has read x
+    const uint32_t stagger = bar0 + 8u * (10 + 2 * kWGroups);                          // board 0 is far enough into the layer
 
     if (threadIdx.x == 0) {
         for (int bd = 0; bd < 2; ++bd) {
             mbar_init(in_full(bd), 1); mbar_init(act_ready(bd), 4 * T); mbar_init(acc_full(bd), 1);
             mbar_init(out_written(bd), 4 * T); mbar_init(x_free(bd), 1);
         }
-        for (int g = 0; g < kWGroups; ++g) { mbar_init(w_full(g), 1); mbar_init(w_empty(g), 1); }
+        for (int g = 0; g < kWGroups; ++g) { mbar_init(w_full(g), 1); mbar_init(w_empty(g), 2); }
+        mbar_init(stagger, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&in_map) : "memory");
@@ -212,7 +249,7 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
     auto board_of = [&](int round, int bd) { return (int)blockIdx.x + (2 * round + bd) * (int)gridDim.x; };
     auto slot_off = [&](int bd) { return (uint32_t)((kGuardRows + bd * (kSlotRows + kGuardRows)) * kRowBytes); };
 
-    if (warp == 1) {
+    if (warp == 10) {
         // ---------------- weight loader ----------------
         // constants of the network: may start before the kernels ahead of this one in the stream are complete
         if (lane == 0) {
@@ -220,7 +257,11 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
             bool ok = true;
             for (int it = 0; ok && it < total; ++it) {
                 const uint8_t* src = p.layers[it % L].w;
+                // a block comes back from both boards' issuers; in a round with a single board (the last one, when the
+                // CTA's board count is odd) the loader stands in for the missing issuer
+                const bool prev_alone = it > 0 && (n_my & 1) && (it - 1) / L == rounds - 1;
                 for (int g = 0; g < kWGroups; ++g) {
+                    if (prev_alone) mbar_arrive(w_empty(g));
                     if (it > 0 && !mbar_wait(w_empty(g), (uint32_t)(it - 1) & 1u, abort_flag)) { ok = false; break; }
                     mbar_arrive_expect_tx(w_full(g), (uint32_t)kWGroupBytes);
                     bulk_g2s(smem_u32(w_s + g * kWGroupBytes), src + (size_t)g * kWGroupBytes, (uint32_t)kWGroupBytes, w_full(g));
@@ -228,56 +269,62 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
             }
             if (!ok) { *abort_flag = 1; atomicExch(p.error, 4); }
         }
-    } else if (warp == 0) {
-        // ---------------- MMA issuer ----------------
+    } else if (warp < 2) {
+        // ---------------- MMA issuers: warp 0 for board 0, warp 1 for board 1 ----------------
+        // The issuing thread pays for every instruction between two MMAs (an MMA holds it 48 cycles, a wait
+        // about 50, a commit 25), and at a layer boundary it waits for the epilogue.  With one issuer per
+        // board the tensor cores take the other board's MMAs meanwhile.  Board 1 runs two thirds of a layer
+        // behind board 0 (it starts a layer when board 0 has issued tap kStaggerTap), so that one board's MMAs
+        // cover the other's epilogue; both hand the weight blocks back, and the loader waits for both.
         if (lane == 0) {
+            const int bd = warp;
             int tap_off[9];
 #pragma unroll
             for (int tap = 0; tap < 9; ++tap) tap_off[tap] = ((tap / 3) * p.GP + (tap % 3)) * (kRowBytes >> 4);
-            // descriptor of the row GP + 1 rows above a board's first row (tap 0 of position 0), per buffer and board
-            const uint32_t a_base_x = desc_lo(smem_u32(x_s) + slot_off(0) - (uint32_t)((p.GP + 1) * kRowBytes));
-            const uint32_t a_base_y = desc_lo(smem_u32(y_s) + slot_off(0) - (uint32_t)((p.GP + 1) * kRowBytes));
+            // descriptor of the row GP + 1 rows above the board's first row (tap 0 of position 0), per buffer
+            const uint32_t a_base_x = desc_lo(smem_u32(x_s) + slot_off(bd) - (uint32_t)((p.GP + 1) * kRowBytes));
+            const uint32_t a_base_y = desc_lo(smem_u32(y_s) + slot_off(bd) - (uint32_t)((p.GP + 1) * kRowBytes));
             const uint32_t w_lo = desc_lo(smem_u32(w_s));
-            uint32_t ready_cnt[2] = {0u, 0u};
+            uint32_t ready_cnt = 0u, stagger_cnt = 0u;
             bool ok = true;
             int it = 0;
             for (int round = 0; ok && round < rounds; ++round) {
                 const int nb = n_my - 2 * round >= 2 ? 2 : 1;
+                if (bd >= nb) break;                    // a single board in the last round: issuer 1 is done
                 for (int l = 0; ok && l < L; ++l, ++it) {
-                    const uint32_t a_layer = (l == 0 || !(l & 1)) ? a_base_y : a_base_x;   // stem and second convolutions read y, first ones x
-                    // unrolled over the two boards: "first board" is then a compile-time fact in each copy, and every
-                    // instruction between two MMAs costs issue time
-#pragma unroll
-                    for (int bd = 0; bd < 2; ++bd) {
-                        if (bd >= nb) break;
-                        if (l == 0) {
-                            if (!mbar_wait(in_full(bd), (uint32_t)round & 1u, abort_flag)) { ok = false; break; }
-                        } else {
-                            if (!mbar_wait(act_ready(bd), ready_cnt[bd] & 1u, abort_flag)) { ok = false; break; }
-                            ++ready_cnt[bd];
-                        }
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const uint32_t a_lo = a_layer + (uint32_t)(bd * ((kSlotRows + kGuardRows) * kRowBytes >> 4));
-                        const uint32_t d_tmem = tmem_base + (uint32_t)((it & 1) * 256 + bd * 128);
-                        const bool first_board = bd == 0, last_board = bd == nb - 1;
-#pragma unroll
-                        for (int tap = 0; tap < 9; ++tap) {
-                            // the issuing thread pays for every instruction between two MMAs (a wait costs about
-                            // 50 cycles, a commit 25, an MMA 48): weights are waited for and handed back three taps at a time
-                            if (first_board && tap % 3 == 0 && !mbar_wait(w_full(tap / 3), (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
-#pragma unroll
-                            for (int tile = 0; tile < T; ++tile) {
-#pragma unroll
-                                for (int ks = 0; ks < kC / 16; ++ks)
-                                    umma(d_tmem + (uint32_t)(tile * kC),
-                                         a_lo + (uint32_t)(tile * (kTileM * kRowBytes >> 4) + tap_off[tap] + ks * 2),
-                                         w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), (tap | ks) ? 1u : 0u);
-                            }
-                            if (last_board && tap % 3 == 2) umma_commit(w_empty(tap / 3));   // the round's boards are through with these taps
-                        }
-                        if (!ok) break;
-                        umma_commit(acc_full(bd));
+                    const uint32_t a_lo = (l == 0 || !(l & 1)) ? a_base_y : a_base_x;   // stem and second convolutions read y, first ones x
+                    if (l == 0) {
+                        if (!mbar_wait(in_full(bd), (uint32_t)round & 1u, abort_flag)) { ok = false; break; }
+                    } else {
+                        if (!mbar_wait(act_ready(bd), ready_cnt & 1u, abort_flag)) { ok = false; break; }
+                        ++ready_cnt;
                     }
+                    if (bd == 1) {
+                        if (!mbar_wait(stagger, stagger_cnt & 1u, abort_flag)) { ok = false; break; }
+                        ++stagger_cnt;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t d_tmem = tmem_base + (uint32_t)((it & 1) * 256 + bd * 128);
+#pragma unroll
+                    for (int tap = 0; tap < 9; ++tap) {
+                        if (tap % 3 == 0) {
+                            if (!mbar_wait(w_full(tap / 3), (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
+                        }
+#pragma unroll
+                        for (int tile = 0; tile < T; ++tile) {
+#pragma unroll
+                            for (int ks = 0; ks < kC / 16; ++ks)
+                                umma(d_tmem + (uint32_t)(tile * kC),
+                                     a_lo + (uint32_t)(tile * (kTileM * kRowBytes >> 4) + tap_off[tap] + ks * 2),
+                                     w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), (tap | ks) ? 1u : 0u);
+                        }
+                        if (tap % 3 == 2) {
+                            umma_commit(w_empty(tap / 3));
+                        }
+                        if (tap == kStaggerTap && bd == 0) mbar_arrive(stagger);
+                    }
+                    if (!ok) break;
+                    umma_commit(acc_full(bd));
                 }
             }
             if (!ok) { *abort_flag = 1; atomicExch(p.error, 2); }

@@ -265,6 +265,7 @@ def test_resident_tower_equals_layer_by_layer(api, monkeypatch, S, blocks, B):
         launches = api.counters()["kernel_launches"] - before
         logits2, v2 = net.infer_planes(x, api.OUT_LOGITS)
         assert np.array_equal(logits, logits2) and np.array_equal(v, v2)
+        assert net.tower_path() == (2 if which == "resident" else 0)
         outs.append((logits, v, launches))
         net.close()
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
