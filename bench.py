@@ -470,10 +470,13 @@ def gpu_arm(args):
                          "frac_of_sustained": tower_tf / peaks["bf16_sustained"] if peaks["bf16_sustained"] else None,
                          "peak_source": peaks["source"] + " (burst: kernel timed alone)", "us_per_launch": tower_ms * 1e3,
                          "launches_per_tower": int(tower_launches), "flops_per_launch": tower_flops,
-                         # DRAM bytes per launch from the ncu capture at batch 512 (the input tensor and the weights
-                         # are read, every later layer works out of L2), scaled by the boards processed
-                         "traffic": 21.05e6 * B / 512.0, "traffic_unit": "bytes/launch",
-                         "traffic_source": "profiles/conv_tower_kernel_gomoku15_batch512.md (scaled by batch)"},
+                         # DRAM bytes per launch from the ncu captures at batch 512, scaled by the boards processed: the
+                         # input tensor and the weights are read; the board-resident tower writes nothing back to DRAM
+                         # (its output stays in L2), the cooperative-launch tower works out of L2 after the first layer
+                         "traffic": {2: 18.38e6, 1: 21.05e6}.get(tower_path, 21 * 33.66e6) * B / 512.0, "traffic_unit": "bytes/launch",
+                         "traffic_source": {2: "profiles/conv_tower_resident_kernel_gomoku15_batch512.md (scaled by batch)",
+                                            1: "profiles/conv_tower_kernel_gomoku15_batch512.md (scaled by batch)"}.get(
+                                                tower_path, "profiles/conv3x3_kernel_gomoku15_batch512.md (21 launches, scaled by batch)")},
             "roofline_conv_layer": {"kernel": "conv3x3_kernel (64->64, residual+ReLU), one layer as its own launch",
                          "bound": "tensor", "achieved": conv_tf,
                          "peak": peaks["bf16_burst"], "unit": "TFLOP/s", "frac": conv_tf / peaks["bf16_burst"],
