@@ -389,7 +389,8 @@ namespace {
 // The tower alone; returns the index of the activation buffer that holds its output in *out_buf.
 // `input_bt`: a board tensor of cin_pad channels holding the B input boards (the handle's own staging
 // tensor or a caller's).
-int tower_device(ob200_net* n, const void* input_bt, int B, int* out_buf, cudaStream_t st) {
+// heads_done (optional): the caller wants the heads' 1x1 convolutions too; set when the tower kernel took them along.
+int tower_device(ob200_net* n, const void* input_bt, int B, int* out_buf, cudaStream_t st, bool* heads_done = nullptr) {
     const ob200_net_config& c = n->cfg;
     const int S = c.board_size;
     const int F = c.filters;
@@ -400,9 +401,13 @@ int tower_device(ob200_net* n, const void* input_bt, int B, int* out_buf, cudaSt
         BoardTensorMap board_map;
         if (!own_input)
             if (int rc = input_map(n, input_bt, B, tower_resident_box_rows(S), &board_map)) return rc;
+        // the heads' 1x1 convolutions ride along when they are few (FC policy head: policy + value channels)
+        const int hc = c.policy_head_ch + c.value_head_ch;
+        const bool with_heads = heads_done && c.policy_kind != OB200_POLICY_CONV_PLANES && hc <= tower_resident_head_channels_max();
         const int rc = launch_conv_tower_resident(own_input ? n->in_map_board : board_map, n->out_map_board, n->resident_layers,
-                                                  1 + 2 * c.blocks, B, S, st);
-        if (rc == OB200_OK) { done = true; x = 0; n->tower_path = 2; }
+                                                  1 + 2 * c.blocks, B, S, st, n->head_w, n->head_b, with_heads ? hc : 0,
+                                                  with_heads ? c.policy_head_ch : 0, n->hp, n->hv);
+        if (rc == OB200_OK) { done = true; x = 0; n->tower_path = 2; if (heads_done) *heads_done = with_heads; }
         else if (rc == OB200_ERR_UNSUPPORTED) n->resident = false;
         else return rc;
     }
@@ -451,7 +456,8 @@ int forward_device(ob200_net* n, const void* input_bt, int B, float* policy_out,
     const int S = c.board_size;
     const int F = c.filters;
     int x = 0;
-    if (int rc = tower_device(n, input_bt, B, &x, st)) return rc;
+    bool heads_done = false;
+    if (int rc = tower_device(n, input_bt, B, &x, st, &heads_done)) return rc;
     const int S2 = S * S, pc = c.policy_head_ch, vc = c.value_head_ch;
     if (c.policy_kind == OB200_POLICY_CONV_PLANES) {
         if (int rc = launch_conv_wide_maps(n->act_load[x], n->act_load[x], nullptr, n->pol_w, n->pol_b, B, S, F, n->pol_cout, 1, 0,
@@ -461,7 +467,7 @@ int forward_device(ob200_net* n, const void* input_bt, int B, float* policy_out,
             n->pol_planes, n->pol_cout, pc, B, S, policy_out);
         OB200_LAUNCHED("policy_planes_gather_kernel");
         if (int rc = launch_head_conv(n->act[x], n->head_w, n->head_b, vc, 0, n->hv, n->hv, B, S, st, F)) return rc;
-    } else {
+    } else if (!heads_done) {
         if (int rc = launch_head_conv(n->act[x], n->head_w, n->head_b, pc + vc, pc, n->hp, n->hv, B, S, st, F)) return rc;
     }
     // the two heads are independent from here on: the value head (FC + FC/tanh) runs on a second

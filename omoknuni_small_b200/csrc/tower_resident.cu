@@ -59,11 +59,20 @@ struct alignas(32) ResidentLayer {
     int pad_[3];
 };
 
+constexpr int kHeadMax = 4;                          // head channels the last epilogue can take along
+
 struct ResidentParams {
     const ResidentLayer* layers;
     int n_layers;
     int B, S, GP, slots;
     int* error;
+    // optional: the heads' 1x1 convolutions (+ folded BatchNorm, ReLU) on the tower's output, done by the last
+    // layer's epilogue while the row is at hand.  head_ch == 0: none.
+    const float* head_w;      // [head_ch][64]
+    const float* head_b;      // [head_ch]
+    int head_ch, head_pc;     // channels in all, and how many of them belong to the policy head
+    float* hp;                // [B][head_pc][S*S]
+    float* hv;                // [B][head_ch - head_pc][S*S]
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -157,6 +166,39 @@ __device__ __forceinline__ void store_row(uint8_t* dst_row, int row, const uint3
         *slot = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
+// The heads' 1x1 convolutions for one position, from the row just written (bf16, as the head kernel would
+// read it from the tower's output tensor).  Same order of additions as head_conv_kernel: eight partial sums
+// over eight consecutive channels each, added as ((0+1)+(2+3))+((4+5)+(6+7)), then the bias, then ReLU.
+__device__ __noinline__ void head_row(const uint8_t* row_ptr, int row, const float* head_s, int head_ch, int head_pc,
+                                      int board, int S, int GP, float* hp, float* hv) {
+    float a[kC];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const uint4 v = *reinterpret_cast<const uint4*>(row_ptr + ((c ^ (row & 7)) << 4));
+        const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            a[c * 8 + 2 * j] = __uint_as_float(w4[j] << 16);
+            a[c * 8 + 2 * j + 1] = __uint_as_float(w4[j] & 0xFFFF0000u);
+        }
+    }
+    const int y = row / GP, x = row - y * GP, S2 = S * S, cell = y * S + x;
+    for (int h = 0; h < head_ch; ++h) {
+        const float* wh = head_s + h * kC;
+        float part[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc = fmaf(a[j * 8 + k], wh[j * 8 + k], acc);
+            part[j] = acc;
+        }
+        const float sum = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
+        const float o = fmaxf(sum + head_s[kHeadMax * kC + h], 0.0f);
+        if (h < head_pc) hp[((size_t)board * head_pc + h) * S2 + cell] = o;
+        else hv[((size_t)board * (head_ch - head_pc) + (h - head_pc)) * S2 + cell] = o;
+    }
+}
 __device__ __forceinline__ void store_zero_row(uint8_t* dst_row) {
 #pragma unroll
     for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(dst_row)[c] = make_uint4(0u, 0u, 0u, 0u);
@@ -201,7 +243,8 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
     uint8_t* y_s = x_s + kBufBytes;
     uint8_t* w_s = y_s + kBufBytes;                        // nine tap blocks of the current / next layer
     float* bias_s = reinterpret_cast<float*>(w_s + 9 * kTapBytes);   // [n_layers][64]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(bias_s + p.n_layers * kC);
+    float* head_s = bias_s + p.n_layers * kC;                        // [kHeadMax][64] weights, [kHeadMax] biases
+    uint64_t* bars = reinterpret_cast<uint64_t*>(head_s + kHeadMax * kC + kHeadMax);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -231,6 +274,8 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
     // guards, and the rows of a slot beyond the board, are zero for the kernel's lifetime
     for (int i = threadIdx.x; i < 2 * kBufBytes / 16; i += kThreads) reinterpret_cast<uint4*>(x_s)[i] = make_uint4(0u, 0u, 0u, 0u);
     for (int i = threadIdx.x; i < p.n_layers * kC; i += kThreads) bias_s[i] = p.layers[i / kC].bias[i % kC];
+    for (int i = threadIdx.x; i < p.head_ch * kC; i += kThreads) head_s[i] = p.head_w[i];
+    if ((int)threadIdx.x < p.head_ch) head_s[kHeadMax * kC + threadIdx.x] = p.head_b[threadIdx.x];
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
@@ -377,6 +422,8 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
                     if (!valid) store_zero_row(dst_row);
                     else if (has_res) store_row<true>(dst_row, row, r, bias_t);
                     else store_row<false>(dst_row, row, r, bias_t);
+                    if (l + 1 == L && p.head_ch > 0 && valid)
+                        head_row(dst_row, row, head_s, p.head_ch, p.head_pc, board_of(round, bd), p.S, p.GP, p.hp, p.hv);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // rows -> the tensor cores' / the store's reads
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
@@ -433,16 +480,25 @@ int tower_resident_box_rows(int S) { return (S + 1) * (S + 1); }
 // Shared memory the kernel needs, or 0 when the board or the depth does not fit.
 size_t tower_resident_smem_bytes(int S, int n_layers) {
     if (S < 1 || (S + 1) * (S + 1) > kSlotRows || S + 2 > kGuardRows || n_layers < 1) return 0;
-    const size_t total = 2 * (size_t)kBufBytes + 9 * (size_t)kTapBytes + (size_t)n_layers * kC * 4 + kNumBars * 8 + 16 + 1024;
+    const size_t total = 2 * (size_t)kBufBytes + 9 * (size_t)kTapBytes + (size_t)n_layers * kC * 4 + (kHeadMax * kC + kHeadMax) * 4 +
+                         kNumBars * 8 + 16 + 1024;
     return total <= 232448 ? total : 0;
 }
 
 // The whole tower in one ordinary launch.  in_map / out_map: boxes of tower_resident_box_rows(S)
 // rows over the 64-channel input tensor and the output tensor; layers_dev: n_layers descriptors on
 // the device.
+int tower_resident_head_channels_max() { return kHeadMax; }
+
+// heads (optional, head_ch in 1..tower_resident_head_channels_max()): the heads' 1x1 convolutions on the
+// tower's output ride along in the last epilogue; results as launch_head_conv writes them.
 int launch_conv_tower_resident(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* layers_dev,
-                               int n_layers, int B, int S, cudaStream_t st) {
+                               int n_layers, int B, int S, cudaStream_t st, const float* head_w, const float* head_b,
+                               int head_ch, int head_pc, float* hp, float* hv) {
     if (!layers_dev || n_layers < 1 || B <= 0) return set_error(OB200_ERR_INVALID, "resident tower: bad arguments");
+    if (head_ch < 0 || head_ch > kHeadMax || head_pc < 0 || head_pc > head_ch ||
+        (head_ch > 0 && (!head_w || !head_b || (head_pc > 0 && !hp) || (head_pc < head_ch && !hv))))
+        return set_error(OB200_ERR_INVALID, "resident tower: bad head arguments");
     const size_t smem = tower_resident_smem_bytes(S, n_layers);
     if (!smem) return set_error(OB200_ERR_UNSUPPORTED, "resident tower: board size %d / %d layers do not fit shared memory", S, n_layers);
     if (int rc = require_device()) return rc;
@@ -461,6 +517,7 @@ int launch_conv_tower_resident(const BoardTensorMap& in_map, const BoardTensorMa
     p.layers = static_cast<const ResidentLayer*>(layers_dev); p.n_layers = n_layers; p.B = B; p.S = S; p.GP = S + 1; p.slots = slots;
     p.error = device_error_word();
     if (!p.error) return set_error(OB200_ERR_CUDA, "resident tower: cannot resolve the device error word");
+    p.head_w = head_w; p.head_b = head_b; p.head_ch = head_ch; p.head_pc = head_pc; p.hp = hp; p.hv = hv;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(B < sms ? B : sms); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];

@@ -269,7 +269,8 @@ def test_resident_tower_equals_layer_by_layer(api, monkeypatch, S, blocks, B):
         outs.append((logits, v, launches))
         net.close()
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
-    assert outs[0][2] == outs[1][2] - 2 * blocks                   # 1 tower launch instead of 1 + 2 * blocks
+    # 1 tower launch instead of 1 + 2 * blocks, and the heads' 1x1 convolutions ride along in it
+    assert outs[0][2] == outs[1][2] - 2 * blocks - 1
     assert api.device_error_code() == 0
 
 
