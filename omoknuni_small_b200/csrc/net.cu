@@ -50,9 +50,9 @@ struct ob200_net {
     void* pol_w = nullptr; float* pol_b = nullptr; float* pol_planes = nullptr; int pol_cout = 0;
     // device + pinned host staging of the host-buffer calls
     float *d_planes = nullptr, *d_policy = nullptr, *d_value = nullptr;
-    int16_t* d_hist = nullptr; uint8_t *d_nhist = nullptr, *d_tomove = nullptr;
+    int16_t* d_hist = nullptr;      // [histories | history lengths | sides to move] of the call in flight
     float *h_planes = nullptr, *h_policy = nullptr, *h_value = nullptr;
-    int16_t* h_hist = nullptr; uint8_t *h_nhist = nullptr, *h_tomove = nullptr;
+    int16_t* h_hist = nullptr;
     int* h_err = nullptr;           // pinned landing word for the device error code
     size_t planes_capacity = 0;     // floats per staging buffer
     std::vector<void*> owned_dev, owned_host;
@@ -360,15 +360,13 @@ int ob200_net_finalize(ob200_net* n) {
     if (int rc = dev_alloc(n, &n->d_value, MB, false)) return rc;
     n->planes_capacity = MB * (size_t)std::max(c.input_channels, 19) * S2;
     if (int rc = dev_alloc(n, &n->d_planes, n->planes_capacity, false)) return rc;
-    if (int rc = dev_alloc(n, &n->d_hist, MB * 16, false)) return rc;
-    if (int rc = dev_alloc(n, &n->d_nhist, MB, false)) return rc;
-    if (int rc = dev_alloc(n, &n->d_tomove, MB, false)) return rc;
+    // move histories, history lengths and sides to move of a call share one staging block (34 bytes per board,
+    // packed for the call's batch size), so that they reach the device in one copy
+    if (int rc = dev_alloc(n, &n->d_hist, MB * 17, false)) return rc;
     if (int rc = host_alloc(n, &n->h_planes, n->planes_capacity)) return rc;
     if (int rc = host_alloc(n, &n->h_policy, MB * A)) return rc;
     if (int rc = host_alloc(n, &n->h_value, MB)) return rc;
-    if (int rc = host_alloc(n, &n->h_hist, MB * 16)) return rc;
-    if (int rc = host_alloc(n, &n->h_nhist, MB)) return rc;
-    if (int rc = host_alloc(n, &n->h_tomove, MB)) return rc;
+    if (int rc = host_alloc(n, &n->h_hist, MB * 17)) return rc;
     if (int rc = host_alloc(n, &n->h_err, 1)) return rc;
     *n->h_err = 0;
     OB200_CUDA_OK(cudaStreamCreateWithFlags(&n->stream, cudaStreamNonBlocking));
@@ -581,13 +579,14 @@ int ob200_net_infer_gomoku(ob200_net* n, const int16_t* history, const uint8_t* 
         return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_infer_gomoku: the Gomoku encoder makes 17 or 19 planes; the network takes %d",
                          c.input_channels);
     OB200_CUDA_OK(cudaSetDevice(c.device));
-    std::memcpy(n->h_hist, history, (size_t)B * 16 * sizeof(int16_t));
-    std::memcpy(n->h_nhist, n_hist, (size_t)B);
-    std::memcpy(n->h_tomove, to_move, (size_t)B);
-    OB200_CUDA_OK(cudaMemcpyAsync(n->d_hist, n->h_hist, (size_t)B * 16 * sizeof(int16_t), cudaMemcpyHostToDevice, n->stream));
-    OB200_CUDA_OK(cudaMemcpyAsync(n->d_nhist, n->h_nhist, (size_t)B, cudaMemcpyHostToDevice, n->stream));
-    OB200_CUDA_OK(cudaMemcpyAsync(n->d_tomove, n->h_tomove, (size_t)B, cudaMemcpyHostToDevice, n->stream));
-    if (int rc = launch_encode_gomoku(n->d_hist, n->d_nhist, n->d_tomove, B, c.board_size, c.input_channels, n->cin_pad,
+    const size_t hist_bytes = (size_t)B * 16 * sizeof(int16_t);
+    uint8_t* h8 = reinterpret_cast<uint8_t*>(n->h_hist);
+    uint8_t* d8 = reinterpret_cast<uint8_t*>(n->d_hist);
+    std::memcpy(h8, history, hist_bytes);
+    std::memcpy(h8 + hist_bytes, n_hist, (size_t)B);
+    std::memcpy(h8 + hist_bytes + B, to_move, (size_t)B);
+    OB200_CUDA_OK(cudaMemcpyAsync(d8, h8, hist_bytes + 2 * (size_t)B, cudaMemcpyHostToDevice, n->stream));
+    if (int rc = launch_encode_gomoku(n->d_hist, d8 + hist_bytes, d8 + hist_bytes + B, B, c.board_size, c.input_channels, n->cin_pad,
                                       n->act_in, n->stream)) return rc;
     if (int rc = forward_device(n, n->act_in, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
     return finish_host_call(n, B, policy_out, value_out);
