@@ -360,7 +360,14 @@ def gpu_arm(args):
                     net_sw.forward_device(bts, Bs, pol_s, val_s, capi.OUT_PROBS)
                 for _ in range(3):
                     step_s()
-                sweep.append((Bs, float(np.mean(timed(step_s, 5)))))
+                step_ms = float(np.mean(timed(step_s, 5)))
+                bts_s = capi.encode_gomoku(dhs, dns, dts, 15, 17, net_sw.input_tensor_channels())
+
+                def tower_s():
+                    for _ in range(tower_reps):
+                        net_sw.tower_device(bts_s, Bs)
+                tower_s()
+                sweep.append((Bs, step_ms, float(np.mean(timed(tower_s, 5))) / tower_reps))
             net_sw.close()
         # ---- one layer as its own launch: 64 -> 64 conv with residual + ReLU ----
         rng = np.random.default_rng(0)
@@ -437,11 +444,11 @@ def gpu_arm(args):
     assert capi.device_error_code() == 0, "a kernel gave up on a bounded wait"
 
     reduced = replicas.max_over_ranks(
-        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms] + [m for _, m in sweep] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
+        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms] + [v for _, m, tm in sweep for v in (m, tm)] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
     total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms = reduced[:8]
-    sweep = [(bs, reduced[8 + i]) for i, (bs, _) in enumerate(sweep)]
+    sweep = [(bs, reduced[8 + 2 * i], reduced[9 + 2 * i]) for i, (bs, _, _) in enumerate(sweep)]
     for i, wr in enumerate(wide):
-        wr["ms"], wr["conv_ms"] = reduced[8 + len(sweep) + 2 * i], reduced[9 + len(sweep) + 2 * i]
+        wr["ms"], wr["conv_ms"] = reduced[8 + 2 * len(sweep) + 2 * i], reduced[9 + 2 * len(sweep) + 2 * i]
     totals = replicas.sum_counters(dist, capi.counters(), dev)   # the only cross-GPU step: per-GPU counters summed
     if rank == 0:
         flops_eval = synth.net_flops_per_eval(15, 17, 64, NET["blocks"], 225, NET["policy_head_ch"], NET["value_head_ch"])
@@ -507,7 +514,11 @@ def gpu_arm(args):
                                 "transposition_table": "on (device table, Zobrist keys)", "nodes_per_move": mcts_nodes},
                      "ms_per_move": mcts_ms / mcts_moves, "timing": "CUDA events around each move, inside the library"},
             "batch_sweep": [{"leaf_batch_per_gpu": bs, "ms_per_step": m, "value": world * bs / (m * 1e-3), "unit": UNIT,
-                             "tower_tflops": bs / (m * 1e-3) * flops_eval / 1e12} for bs, m in sweep],
+                             "tower_tflops": bs / (m * 1e-3) * flops_eval / 1e12,
+                             # the tower launch alone at this batch, as in `roofline`
+                             "tower_launch": {"us_per_launch": tm * 1e3, "achieved": tower_flops / B * bs / (tm * 1e-3) / 1e12,
+                                              "unit": "TFLOP/s", "frac": tower_flops / B * bs / (tm * 1e-3) / 1e12 / peaks["bf16_burst"]}}
+                            for bs, m, tm in sweep],
             "wide_towers": [wide_report(wr, world, peaks) for wr in wide],
             "clocks": clocks,
         }

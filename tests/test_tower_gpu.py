@@ -248,7 +248,7 @@ def pick_tower(monkeypatch, which):
 
 
 @pytest.mark.parametrize("S,blocks,B", [(15, 1, 1), (15, 1, 2), (15, 2, 3), (9, 2, 5), (10, 1, 40), (11, 1, 40), (13, 4, 700),
-                                        (15, 3, 150), (15, 10, 300), (15, 10, 1024)])
+                                        (15, 3, 150), (15, 10, 300), (15, 10, 1024), (15, 13, 10)])
 def test_resident_tower_equals_layer_by_layer(api, monkeypatch, S, blocks, B):
     """The board-resident tower (activations never leave shared memory) runs the same arithmetic in
     the same order as the launch-per-layer path: outputs must be bit-identical.  One and two
@@ -324,6 +324,26 @@ def test_single_launch_tower_repeats_bit_identically(api, monkeypatch, which, B,
     torch.cuda.synchronize()
     net.close()
     assert int(different) == 0
+    assert api.device_error_code() == 0
+
+
+def test_resident_tower_hands_over_when_the_shape_does_not_fit(api, monkeypatch):
+    """14 blocks = 29 layers of biases do not fit beside the boards in shared memory, a 19x19 board does
+    not fit at all, 128 filters are another kernel: the handle then takes one of the other paths."""
+    pick_tower(monkeypatch, "resident")
+    for S, blocks, F in ((15, 14, 64), (19, 1, 64), (15, 1, 128)):
+        shapes = synth.net_tensor_shapes(S, 17, F, blocks, S * S, 2, 1)
+        w = synth.make_weights(shapes, seed=3, init="torch_default", bn="random")
+        net = make_net(api, w, dict(cin=17, S=S, blocks=blocks, F=F, A=S * S, pc=2, vc=1), 4)
+        net.infer_planes(synth.make_stone_planes(3, S, 17, seed=1), api.OUT_LOGITS)
+        assert net.tower_path() in (0, 1)
+        net.close()
+    shapes = synth.net_tensor_shapes(15, 17, 64, 13, 225, 2, 1)
+    net = make_net(api, synth.make_weights(shapes, seed=3, init="torch_default", bn="random"),
+                   dict(cin=17, S=15, blocks=13, F=64, A=225, pc=2, vc=1), 4)
+    net.infer_planes(synth.make_stone_planes(3, 15, 17, seed=1), api.OUT_LOGITS)
+    assert net.tower_path() == 2
+    net.close()
     assert api.device_error_code() == 0
 
 
