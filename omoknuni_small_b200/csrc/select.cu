@@ -530,19 +530,35 @@ traverse_kernel(ob200_tree_view t, const int32_t* __restrict__ roots, int n_tree
             const size_t sim = (size_t)tree * sims_per_tree + k;
             bool done = true;
             if (depth < max_depth && node >= 0 && node < t.n_nodes) {
+                // the row of child links rides along with the statistics (rows of up to 256 slots: two 16-byte
+                // vectors per lane), so that the descent does not pay a second trip to L2 once the slot is known
+                const bool links_in_regs = t.child_node != nullptr && t.pitch <= 256 && ((uintptr_t)t.child_node & 15) == 0;
+                int4 ca = make_int4(-1, -1, -1, -1), cb = ca;
+                if (links_in_regs) {
+                    const int4* C4 = reinterpret_cast<const int4*>(t.child_node + (size_t)node * t.pitch);
+                    const int nvec = t.pitch >> 2;
+                    if (lane < nvec) ca = __ldcg(C4 + lane);
+                    if (lane + 32 < nvec) cb = __ldcg(C4 + 32 + lane);
+                }
                 const int sel = select_row<false>(t, node, c_puct, lane);
                 if (sel >= 0) {
                     int next = -1;
+                    if (links_in_regs) {
+                        const int4 c = (sel >> 7) ? cb : ca;          // vector sel / 4 sits in lane (sel / 4) % 32
+                        const int e4 = sel & 3;
+                        const int mine = e4 == 0 ? c.x : e4 == 1 ? c.y : e4 == 2 ? c.z : c.w;
+                        next = __shfl_sync(0xffffffffu, mine, (sel >> 2) & 31);
+                    }
                     if (lane == 0) {
                         const size_t e = (size_t)node * t.pitch + sel;
+                        // the next reader of this counter is a warp of this CTA, after the barrier below
                         if (vl_value > 0) atomicAdd(t.VL + e, vl_value);
                         int32_t* path = paths_out + sim * max_depth * 2;
                         path[2 * depth] = node;
                         path[2 * depth + 1] = sel;
-                        next = t.child_node ? __ldcg(t.child_node + e) : -1;
+                        if (!links_in_regs) next = t.child_node ? __ldcg(t.child_node + e) : -1;
                     }
-                    __threadfence();
-                    next = __shfl_sync(0xffffffffu, next, 0);
+                    if (!links_in_regs) next = __shfl_sync(0xffffffffu, next, 0);
                     ++depth;
                     node = next;
                     done = !(depth < max_depth && node >= 0 && node < t.n_nodes);
