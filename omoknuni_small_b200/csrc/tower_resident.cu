@@ -26,7 +26,7 @@
 // graph).  Every wait is bounded; a thread that gives up raises the device error word.
 // Measured (15x15, 21 layers, B200): 8,000-8,400 cycles per layer for a pair of boards (four tiles), against
 // 6,912 for the MMAs alone; 370 us for 1,024 boards (932 TFLOP/s) and 1,327 us for 4,096 (1,039 TFLOP/s)
-// where a launch per layer takes 432 / 1,650 us; 74-84 us for 1 to 148 boards (93-140 us per layer-launches).
+// where a launch per layer takes 432 / 1,650 us; 74-79 us for 1 to 148 boards (single-issuer variant) (93-140 us per layer-launches).
 #include "internal.h"
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -233,7 +233,11 @@ __device__ __forceinline__ bool issue_board_layer(uint32_t d_tmem, uint32_t a_lo
 }
 
 // T: 128-row tiles per board (1 for boards up to 10x10, 2 up to 15x15).
-template <int T>
+// PAIR: CTAs take their boards two at a time, with one MMA issuer per board (the general case).  When no CTA
+// has more than one board (batches up to the SM count) the second issuer's bookkeeping - the stagger signal, the
+// second hand-over of every weight block - is pure cost in the one thread everything waits for (84 us instead
+// of 78 us for the 21 layers); !PAIR is the same kernel with a single issuer (warp 0; warp 1 idles).
+template <int T, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
                            const ResidentParams p) {
@@ -264,7 +268,7 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
             mbar_init(in_full(bd), 1); mbar_init(act_ready(bd), 4 * T); mbar_init(acc_full(bd), 1);
             mbar_init(out_written(bd), 4 * T); mbar_init(x_free(bd), 1);
         }
-        for (int g = 0; g < kWGroups; ++g) { mbar_init(w_full(g), 1); mbar_init(w_empty(g), 2); }
+        for (int g = 0; g < kWGroups; ++g) { mbar_init(w_full(g), 1); mbar_init(w_empty(g), PAIR ? 2 : 1); }
         mbar_init(stagger, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -304,7 +308,7 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
                 const uint8_t* src = p.layers[it % L].w;
                 // a block comes back from both boards' issuers; in a round with a single board (the last one, when the
                 // CTA's board count is odd) the loader stands in for the missing issuer
-                const bool prev_alone = it > 0 && (n_my & 1) && (it - 1) / L == rounds - 1;
+                const bool prev_alone = PAIR && it > 0 && (n_my & 1) && (it - 1) / L == rounds - 1;
                 for (int g = 0; g < kWGroups; ++g) {
                     if (prev_alone) mbar_arrive(w_empty(g));
                     if (it > 0 && !mbar_wait(w_empty(g), (uint32_t)(it - 1) & 1u, abort_flag)) { ok = false; break; }
@@ -313,6 +317,62 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
                 }
             }
             if (!ok) { *abort_flag = 1; atomicExch(p.error, 4); }
+        }
+    } else if (!PAIR && warp < 2) {
+        if (warp == 0) {
+            // ---------------- single MMA issuer (!PAIR): the boards of a round one after the other ----------------
+            if (lane == 0) {
+                int tap_off[9];
+    #pragma unroll
+                for (int tap = 0; tap < 9; ++tap) tap_off[tap] = ((tap / 3) * p.GP + (tap % 3)) * (kRowBytes >> 4);
+                // descriptor of the row GP + 1 rows above a board's first row (tap 0 of position 0), per buffer and board
+                const uint32_t a_base_x = desc_lo(smem_u32(x_s) + slot_off(0) - (uint32_t)((p.GP + 1) * kRowBytes));
+                const uint32_t a_base_y = desc_lo(smem_u32(y_s) + slot_off(0) - (uint32_t)((p.GP + 1) * kRowBytes));
+                const uint32_t w_lo = desc_lo(smem_u32(w_s));
+                uint32_t ready_cnt[2] = {0u, 0u};
+                bool ok = true;
+                int it = 0;
+                for (int round = 0; ok && round < rounds; ++round) {
+                    const int nb = n_my - 2 * round >= 2 ? 2 : 1;
+                    for (int l = 0; ok && l < L; ++l, ++it) {
+                        const uint32_t a_layer = (l == 0 || !(l & 1)) ? a_base_y : a_base_x;   // stem and second convolutions read y, first ones x
+                        // unrolled over the two boards: "first board" is then a compile-time fact in each copy, and every
+                        // instruction between two MMAs costs issue time
+    #pragma unroll
+                        for (int bd = 0; bd < 2; ++bd) {
+                            if (bd >= nb) break;
+                            if (l == 0) {
+                                if (!mbar_wait(in_full(bd), (uint32_t)round & 1u, abort_flag)) { ok = false; break; }
+                            } else {
+                                if (!mbar_wait(act_ready(bd), ready_cnt[bd] & 1u, abort_flag)) { ok = false; break; }
+                                ++ready_cnt[bd];
+                            }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            const uint32_t a_lo = a_layer + (uint32_t)(bd * ((kSlotRows + kGuardRows) * kRowBytes >> 4));
+                            const uint32_t d_tmem = tmem_base + (uint32_t)((it & 1) * 256 + bd * 128);
+                            const bool first_board = bd == 0, last_board = bd == nb - 1;
+    #pragma unroll
+                            for (int tap = 0; tap < 9; ++tap) {
+                                // the issuing thread pays for every instruction between two MMAs (a wait costs about
+                                // 50 cycles, a commit 25, an MMA 48): weights are waited for and handed back three taps at a time
+                                if (first_board && tap % 3 == 0 && !mbar_wait(w_full(tap / 3), (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
+    #pragma unroll
+                                for (int tile = 0; tile < T; ++tile) {
+    #pragma unroll
+                                    for (int ks = 0; ks < kC / 16; ++ks)
+                                        umma(d_tmem + (uint32_t)(tile * kC),
+                                             a_lo + (uint32_t)(tile * (kTileM * kRowBytes >> 4) + tap_off[tap] + ks * 2),
+                                             w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), (tap | ks) ? 1u : 0u);
+                                }
+                                if (last_board && tap % 3 == 2) umma_commit(w_empty(tap / 3));   // the round's boards are through with these taps
+                            }
+                            if (!ok) break;
+                            umma_commit(acc_full(bd));
+                        }
+                    }
+                }
+                if (!ok) { *abort_flag = 1; atomicExch(p.error, 2); }
+            }
         }
     } else if (warp < 2) {
         // ---------------- MMA issuers: warp 0 for board 0, warp 1 for board 1 ----------------
@@ -507,11 +567,13 @@ int launch_conv_tower_resident(const BoardTensorMap& in_map, const BoardTensorMa
     OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int slots = (S + 1) * (S + 1);
     const bool two_tiles = slots > kTileM;
-    static size_t configured[64][2] = {{0, 0}};
-    if (dev >= 0 && dev < 64 && configured[dev][two_tiles] < smem) {
-        if (two_tiles) OB200_CUDA_OK(cudaFuncSetAttribute(conv_tower_resident_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        else OB200_CUDA_OK(cudaFuncSetAttribute(conv_tower_resident_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured[dev][two_tiles] = smem;
+    const bool pair = B > sms;          // some CTA has two boards or more
+    auto kernel = two_tiles ? (pair ? conv_tower_resident_kernel<2, true> : conv_tower_resident_kernel<2, false>)
+                            : (pair ? conv_tower_resident_kernel<1, true> : conv_tower_resident_kernel<1, false>);
+    static size_t configured[64][4] = {{0, 0, 0, 0}};
+    if (dev >= 0 && dev < 64 && configured[dev][two_tiles * 2 + pair] < smem) {
+        OB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[dev][two_tiles * 2 + pair] = smem;
     }
     ResidentParams p;
     p.layers = static_cast<const ResidentLayer*>(layers_dev); p.n_layers = n_layers; p.B = B; p.S = S; p.GP = S + 1; p.slots = slots;
@@ -526,8 +588,7 @@ int launch_conv_tower_resident(const BoardTensorMap& in_map, const BoardTensorMa
     cfg.attrs = attr; cfg.numAttrs = 1;
     const CUtensorMap& im = *reinterpret_cast<const CUtensorMap*>(&in_map);
     const CUtensorMap& om = *reinterpret_cast<const CUtensorMap*>(&out_map);
-    if (two_tiles) OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv_tower_resident_kernel<2>, im, om, p));
-    else OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv_tower_resident_kernel<1>, im, om, p));
+    OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, im, om, p));
     OB200_LAUNCHED("conv_tower_resident_kernel");
     return OB200_OK;
 }
