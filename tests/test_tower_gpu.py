@@ -299,7 +299,7 @@ def test_fused_tower_equals_layer_by_layer(api, monkeypatch, B):
 
 
 @pytest.mark.parametrize("which,B,iters", [("fused", 1024, 400), ("fused", 700, 200), ("resident", 1024, 400),
-                                           ("resident", 301, 200)])
+                                           ("resident", 301, 200), ("resident", 100, 300)])
 def test_single_launch_tower_repeats_bit_identically(api, monkeypatch, which, B, iters):
     """Hundreds of back-to-back single-launch towers on one input: every result equals the first
     (a tile read before its producer wrote it, or a flag left over from an earlier launch, would
