@@ -22,11 +22,14 @@
 //     next layer when both have come in.
 //   * Boards are assigned statically: CTA c takes boards c, c + grid, c + 2 grid, ... two at a time.
 //     The first input of a board arrives by TMA into y, the tower's output leaves by TMA from x.
+//   * The last layer's epilogue has a position's 64 output channels at hand and, when asked to, also
+//     computes the policy / value heads' 1x1 convolutions (up to four head channels) for it.
 // There is no communication between CTAs, so this is an ordinary launch (and may be captured in a
 // graph).  Every wait is bounded; a thread that gives up raises the device error word.
 // Measured (15x15, 21 layers, B200): 8,000-8,400 cycles per layer for a pair of boards (four tiles), against
 // 6,912 for the MMAs alone; 370 us for 1,024 boards (932 TFLOP/s) and 1,327 us for 4,096 (1,039 TFLOP/s)
-// where a launch per layer takes 432 / 1,650 us; 74-79 us for 1 to 148 boards (single-issuer variant) (93-140 us per layer-launches).
+// where a launch per layer takes 432 / 1,650 us; 74-79 us for 1 to 148 boards
+// (single-issuer variant; 93-140 us as a launch per layer).
 #include "internal.h"
 #include <cuda.h>
 #include <cuda_bf16.h>
