@@ -305,11 +305,18 @@ def gpu_arm(args):
         torch.cuda.synchronize()
         return [s.elapsed_time(e) for s, e in ev]
 
-    for _ in range(W):
-        step_resident()
-    torch.cuda.synchronize()
+    # bring the SM clock up from idle before the warm-up steps (memory fills only, none of the measured work):
+    # a short run's first timed steps otherwise see the clock still ramping
+    for _ in range(int(os.environ.get("OB200_BENCH_SPINUP", "200"))):
+        flush.zero_()
     sampler = ClockSampler(local)
     with sampler:
+        # the W warm-up steps run with the clock sampler already started: launching it perturbs the host for a
+        # moment, and a host that is late with a launch shows up as idle time inside the first step
+        for _ in range(W):
+            flush.zero_()
+            step_resident()
+        torch.cuda.synchronize()
         # ---- headline: K steps, device resident ----
         barrier()
         c0 = capi.counters()["kernel_launches"]
@@ -317,6 +324,8 @@ def gpu_arm(args):
         barrier()
         launches = capi.counters()["kernel_launches"] - c0
         total_ms = float(sum(ms))
+        if os.environ.get("OB200_BENCH_VERBOSE"):
+            print("per-step ms:", " ".join(f"{m:.3f}" for m in ms), file=sys.stderr)
         # ---- e2e: host buffers through the public call ----
         # inputs and outputs in page-locked host memory, allocated once (as an engine would keep them)
         pin = [torch.from_numpy(a).pin_memory() for a in (hist, nh, tm)]
