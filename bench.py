@@ -283,7 +283,9 @@ def gpu_arm(args):
     shapes = synth.net_tensor_shapes(NET["board_size"], NET["input_channels"], NET["filters"], NET["blocks"],
                                      NET["policy_size"], NET["policy_head_ch"], NET["value_head_ch"])
     w = synth.make_weights(shapes, seed=42, init="kaiming_normal")
-    net = capi.Net(17, 15, NET["blocks"], 64, 225, NET["policy_head_ch"], NET["value_head_ch"], 256, B, local).load(w)
+    DT = capi.DTYPE_F16 if args.dtype == "f16" else capi.DTYPE_BF16
+    DT_OTHER, other_name = (capi.DTYPE_BF16, "bf16") if DT == capi.DTYPE_F16 else (capi.DTYPE_F16, "f16")
+    net = capi.Net(17, 15, NET["blocks"], 64, 225, NET["policy_head_ch"], NET["value_head_ch"], 256, B, local, tower_dtype=DT).load(w)
     games, hist, nh, tm = synth.make_gomoku_games(B, 15, seed=replicas.shard_seed(1000, rank))
     d_hist, d_nh, d_tm = (torch.from_numpy(a).to(dev) for a in (hist, nh, tm))
     d_policy = torch.empty((B, 225), dtype=torch.float32, device=dev)
@@ -291,7 +293,7 @@ def gpu_arm(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > 126 MB L2
 
     def step_resident():
-        bt = capi.encode_gomoku(d_hist, d_nh, d_tm, 15, 17, net.input_tensor_channels())
+        bt = capi.encode_gomoku(d_hist, d_nh, d_tm, 15, 17, net.input_tensor_channels(), DT)
         net.forward_device(bt, B, d_policy, d_value, capi.OUT_PROBS)
 
     def timed(fn, n, per_iter_flush=True):
@@ -343,7 +345,7 @@ def gpu_arm(args):
             net.infer_gomoku(p_hist, p_nh, p_tm, out=outs)
             e2e_s += time.perf_counter() - t0
         # ---- the dominant kernel alone: the whole tower (one launch) ----
-        bt_in = capi.encode_gomoku(d_hist, d_nh, d_tm, 15, 17, net.input_tensor_channels())
+        bt_in = capi.encode_gomoku(d_hist, d_nh, d_tm, 15, 17, net.input_tensor_channels(), DT)
         tower_reps = 5
 
         def tower_loop():
@@ -354,10 +356,22 @@ def gpu_arm(args):
         tower_ms = float(np.mean(timed(tower_loop, 5))) / tower_reps
         tower_launches = (capi.counters()["kernel_launches"] - c_t0) // (5 * tower_reps)
         tower_path = net.tower_path()     # 2: boards resident in shared memory, 1: cooperative launch, 0: a launch per layer
+        # the same launch with the other 16-bit storage type (same instruction, other operand-format bits)
+        net_o = capi.Net(17, 15, NET["blocks"], 64, 225, NET["policy_head_ch"], NET["value_head_ch"], 256, B, local,
+                         tower_dtype=DT_OTHER).load(w)
+        bt_o = capi.encode_gomoku(d_hist, d_nh, d_tm, 15, 17, net_o.input_tensor_channels(), DT_OTHER)
+
+        def tower_loop_o():
+            for _ in range(tower_reps):
+                net_o.tower_device(bt_o, B)
+        tower_loop_o()
+        tower_o_ms = float(np.mean(timed(tower_loop_o, 5))) / tower_reps
+        net_o.close()
         # ---- the same network at the other batch sizes of the configurations (256: configs[0]; 4096) ----
         sweep = []
         if not args.no_sweep:
-            net_sw = capi.Net(17, 15, NET["blocks"], 64, 225, NET["policy_head_ch"], NET["value_head_ch"], 256, 4096, local).load(w)
+            net_sw = capi.Net(17, 15, NET["blocks"], 64, 225, NET["policy_head_ch"], NET["value_head_ch"], 256, 4096, local,
+                              tower_dtype=DT).load(w)
             for Bs in (256, 4096):
                 _, h_s, n_s, t_s = synth.make_gomoku_games(Bs, 15, seed=replicas.shard_seed(2000 + Bs, rank))
                 dhs, dns, dts = (torch.from_numpy(a).to(dev) for a in (h_s, n_s, t_s))
@@ -365,12 +379,12 @@ def gpu_arm(args):
                 val_s = torch.empty(Bs, dtype=torch.float32, device=dev)
 
                 def step_s():
-                    bts = capi.encode_gomoku(dhs, dns, dts, 15, 17, net_sw.input_tensor_channels())
+                    bts = capi.encode_gomoku(dhs, dns, dts, 15, 17, net_sw.input_tensor_channels(), DT)
                     net_sw.forward_device(bts, Bs, pol_s, val_s, capi.OUT_PROBS)
                 for _ in range(3):
                     step_s()
                 step_ms = float(np.mean(timed(step_s, 5)))
-                bts_s = capi.encode_gomoku(dhs, dns, dts, 15, 17, net_sw.input_tensor_channels())
+                bts_s = capi.encode_gomoku(dhs, dns, dts, 15, 17, net_sw.input_tensor_channels(), DT)
 
                 def tower_s():
                     for _ in range(tower_reps):
@@ -380,7 +394,7 @@ def gpu_arm(args):
             net_sw.close()
         # ---- one layer as its own launch: 64 -> 64 conv with residual + ReLU ----
         rng = np.random.default_rng(0)
-        wp = torch.from_numpy(capi.pack_conv3x3(rng.normal(0, 0.04, (64, 64, 3, 3)).astype(np.float32), None, 64).view(np.int16)).to(dev)
+        wp = torch.from_numpy(capi.pack_conv3x3(rng.normal(0, 0.04, (64, 64, 3, 3)).astype(np.float32), None, 64, DT).view(np.int16)).to(dev)
         bias = torch.zeros(64, device=dev)
         n_el = int(capi.lib().ob200_board_tensor_bytes(15, B, 64)) // 2
         bufs = [torch.zeros(n_el, dtype=torch.int16, device=dev) for _ in range(3)]
@@ -388,7 +402,7 @@ def gpu_arm(args):
 
         def conv_loop():
             for i in range(reps):
-                capi.conv3x3(bufs[i % 3], wp, bias, bufs[(i + 2) % 3], B, 15, 64, 64, True, out=bufs[(i + 1) % 3])
+                capi.conv3x3(bufs[i % 3], wp, bias, bufs[(i + 2) % 3], B, 15, 64, 64, True, out=bufs[(i + 1) % 3], dtype=DT)
         conv_loop()
         conv_ms = float(np.mean(timed(conv_loop, 5))) / reps
         # ---- batched PUCT selection + virtual loss, 65,536 x 225 ----
@@ -453,11 +467,11 @@ def gpu_arm(args):
     assert capi.device_error_code() == 0, "a kernel gave up on a bounded wait"
 
     reduced = replicas.max_over_ranks(
-        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms] + [v for _, m, tm in sweep for v in (m, tm)] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
-    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms = reduced[:8]
-    sweep = [(bs, reduced[8 + 2 * i], reduced[9 + 2 * i]) for i, (bs, _, _) in enumerate(sweep)]
+        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms] + [v for _, m, tm in sweep for v in (m, tm)] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
+    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms = reduced[:9]
+    sweep = [(bs, reduced[9 + 2 * i], reduced[10 + 2 * i]) for i, (bs, _, _) in enumerate(sweep)]
     for i, wr in enumerate(wide):
-        wr["ms"], wr["conv_ms"] = reduced[8 + 2 * len(sweep) + 2 * i], reduced[9 + 2 * len(sweep) + 2 * i]
+        wr["ms"], wr["conv_ms"] = reduced[9 + 2 * len(sweep) + 2 * i], reduced[10 + 2 * len(sweep) + 2 * i]
     totals = replicas.sum_counters(dist, capi.counters(), dev)   # the only cross-GPU step: per-GPU counters summed
     if rank == 0:
         flops_eval = synth.net_flops_per_eval(15, 17, 64, NET["blocks"], 225, NET["policy_head_ch"], NET["value_head_ch"])
@@ -472,7 +486,7 @@ def gpu_arm(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic",
+            "dtype": args.dtype, "data": "synthetic",
             "config": arm_config(B, world),
             "e2e": {"value": world * B * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": B * 34,
                     "d2h_bytes_per_step": B * 226 * 4},
@@ -493,6 +507,10 @@ def gpu_arm(args):
                          "traffic_source": {2: "profiles/conv_tower_resident_kernel_gomoku15_batch512.md (scaled by batch)",
                                             1: "profiles/conv_tower_kernel_gomoku15_batch512.md (scaled by batch)"}.get(
                                                 tower_path, "profiles/conv3x3_kernel_gomoku15_batch512.md (21 launches, scaled by batch)")},
+            # the tower launch with the other 16-bit storage type: same tcgen05.mma rate, so the same fraction is expected
+            "roofline_" + other_name: {"us_per_launch": tower_o_ms * 1e3, "achieved": tower_flops / (tower_o_ms * 1e-3) / 1e12,
+                                       "unit": "TFLOP/s", "frac": tower_flops / (tower_o_ms * 1e-3) / 1e12 / peaks["bf16_burst"],
+                                       "note": "identical launch, tower weights and board tensors stored as " + other_name},
             "roofline_conv_layer": {"kernel": "conv3x3_kernel (64->64, residual+ReLU), one layer as its own launch",
                          "bound": "tensor", "achieved": conv_tf,
                          "peak": peaks["bf16_burst"], "unit": "TFLOP/s", "frac": conv_tf / peaks["bf16_burst"],
@@ -548,6 +566,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=1024, help="leaf batch per GPU")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"],
+                    help="storage type of the tower's weights and activations (fp32 accumulate either way); fp16 is what "
+                         "holds the 2e-2 / 1e-2 tolerance against the fp32 forward on the benchmark's weights")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sweep", action="store_true", help="skip the batch 256 / 4096 runs of the same network")
     ap.add_argument("--wide-only", action="store_true",

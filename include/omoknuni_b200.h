@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define OB200_VERSION 1
+#define OB200_VERSION 2
 
 /* Status codes. */
 enum {
@@ -169,6 +169,16 @@ int ob200_launch_traverse(const ob200_tree_view* tree, const int32_t* roots, int
  *  TMA boxes and 128-byte-swizzled shared-memory tiles are built on.
  * ------------------------------------------------------------------------- */
 #define OB200_GUARD 32
+/* Storage type of a board tensor and of the packed tower weights.  BF16 is the
+ * default everywhere.  F16 (same tensor-core rate, 11 significant bits instead
+ * of 8, range up to 65,504 with activations saturating there instead of
+ * overflowing) is for networks whose residual stream is not normalised, where 21
+ * layers of bf16 rounding leave the logits several 1e-2 away from the fp32
+ * forward of ResNetModel::forward (src/nn/resnet_model.cpp:104-237).  Every
+ * tensor that meets in one call (input, weights, residual, output) must be of
+ * the same type; calls without a dtype argument read and write bf16. */
+#define OB200_DTYPE_BF16 0
+#define OB200_DTYPE_F16 1
 /* Positions (PT above) of a board tensor for a batch of B boards. */
 int64_t ob200_board_tensor_positions(int32_t board_size, int32_t B);
 /* Bytes of a board tensor with `channels` channels (rounded up to 8). */
@@ -196,6 +206,11 @@ int ob200_launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist,
                                const uint8_t* to_move, int32_t B, int32_t board_size,
                                int32_t planes, int32_t out_channels, void* board_tensor_out,
                                ob200_stream stream);
+/* The same with the board tensor's storage type chosen (OB200_DTYPE_*). */
+int ob200_launch_encode_gomoku_dt(const int16_t* history, const uint8_t* n_hist,
+                                  const uint8_t* to_move, int32_t B, int32_t board_size,
+                                  int32_t planes, int32_t out_channels, int32_t dtype,
+                                  void* board_tensor_out, ob200_stream stream);
 
 /* Gomoku board -> the reference's 3-plane representation, for networks built
  * with 3 input channels (src/nn/resnet_model.cpp:258-260).  Replaces
@@ -251,6 +266,12 @@ int ob200_launch_encode_go(const int8_t* stones, const int32_t* ko_point, const 
 int ob200_launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C,
                                         int32_t board_size, int32_t out_channels,
                                         void* board_tensor_out, ob200_stream stream);
+/* The same with the board tensor's storage type chosen (OB200_DTYPE_*); fp16 rounds
+ * to nearest even and magnitudes beyond 65,504 become infinity, as a conversion of
+ * the planes to torch.float16 would. */
+int ob200_launch_planes_to_board_tensor_dt(const float* planes_nchw, int32_t B, int32_t C,
+                                           int32_t board_size, int32_t out_channels, int32_t dtype,
+                                           void* board_tensor_out, ob200_stream stream);
 
 /* One 3x3 convolution layer (padding 1, stride 1) on board tensors with the
  * BatchNorm already folded into weight and bias:
@@ -264,6 +285,12 @@ int ob200_launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int
 int ob200_launch_conv3x3(const void* in, const void* packed_w, const float* bias,
                          const void* residual, void* out, int32_t B, int32_t board_size,
                          int32_t cin, int32_t cout, int32_t relu, ob200_stream stream);
+/* The same on tensors and packed weights of storage type `dtype` (OB200_DTYPE_*).
+ * fp16 outputs saturate at +-65,504 instead of overflowing to infinity. */
+int ob200_launch_conv3x3_dt(const void* in, const void* packed_w, const float* bias,
+                            const void* residual, void* out, int32_t B, int32_t board_size,
+                            int32_t cin, int32_t cout, int32_t relu, int32_t dtype,
+                            ob200_stream stream);
 /* Bytes of the packed bf16 weight image for (cin, cout); 0 when unsupported. */
 int64_t ob200_packed_conv3x3_bytes(int32_t cin, int32_t cout);
 /* Host helper: fp32 OIHW weights [cout][cin_real][3][3] scaled per output
@@ -273,6 +300,9 @@ int64_t ob200_packed_conv3x3_bytes(int32_t cin, int32_t cout);
  * copy it to the device for ob200_launch_conv3x3. */
 int ob200_pack_conv3x3_weights(const float* w_oihw, const float* scale, int32_t cout,
                                int32_t cin_real, int32_t cin, void* packed_out);
+/* The same, rounding to `dtype` (OB200_DTYPE_*); the image has the same size. */
+int ob200_pack_conv3x3_weights_dt(const float* w_oihw, const float* scale, int32_t cout,
+                                  int32_t cin_real, int32_t cin, int32_t dtype, void* packed_out);
 
 /* ------------------------------------------------------------------------- *
  *  Network handle: the residual policy/value network.
@@ -294,6 +324,11 @@ typedef struct ob200_net_config {
     int32_t device;           /* CUDA device ordinal                           */
     int32_t policy_kind;      /* OB200_POLICY_FC (the reference's head) or
                                  OB200_POLICY_CONV_PLANES                       */
+    int32_t tower_dtype;      /* OB200_DTYPE_BF16 (0) or OB200_DTYPE_F16: storage
+                                 type of the tower's weights and of every board
+                                 tensor of this handle, the input tensor of
+                                 ob200_net_forward_device included.  The heads
+                                 compute in fp32 either way.                    */
 } ob200_net_config;
 
 /* Policy head kinds.  FC: 1x1 conv to policy_head_ch channels + BatchNorm + ReLU

@@ -15,7 +15,10 @@
 //     (:610-623, :801-810) — inference() never throws;
 //   * getInputShape() = {channels, board, board}, getPolicySize() (:866-873).
 // Weights enter by the reference's parameter names (setTensor) or from a flat
-// file written by save().
+// file written by save().  save() needs the fp32 tensors as they were given: a
+// network that will be saved is constructed with keep_weights = true (a second
+// host copy of every tensor for the object's lifetime); without it the copies
+// are dropped when finalize() has uploaded the weights and save() writes nothing.
 #pragma once
 
 #include <cstdint>
@@ -35,7 +38,8 @@ class B200Network : public alphazero::nn::NeuralNetwork {
 public:
     B200Network(int64_t input_channels, int64_t board_size, int64_t num_res_blocks = 10, int64_t num_filters = 64,
                 int64_t policy_size = 0, int policy_head_ch = 32, int value_head_ch = 32, int max_batch = 1024,
-                int device = 0) {
+                int device = 0, bool keep_weights = false, int tower_dtype = OB200_DTYPE_BF16)
+        : keep_weights_(keep_weights) {
         cfg_.board_size = (int32_t)board_size;
         cfg_.input_channels = (int32_t)input_channels;
         cfg_.filters = (int32_t)num_filters;
@@ -46,6 +50,8 @@ public:
         cfg_.value_hidden = 256;
         cfg_.max_batch = max_batch;
         cfg_.device = device;
+        cfg_.policy_kind = OB200_POLICY_FC;
+        cfg_.tower_dtype = tower_dtype;
         if (ob200_net_create(&cfg_, &net_) != OB200_OK) {
             std::fprintf(stderr, "[B200Network] %s\n", ob200_last_error());
             net_ = nullptr;
@@ -60,7 +66,7 @@ public:
     // One tensor under the reference module's name, e.g. "res_blocks.3.bn1.running_var".
     bool setTensor(const std::string& name, const float* data, int64_t numel) {
         if (!net_) return false;
-        kept_.push_back({name, std::vector<float>(data, data + numel)});
+        if (keep_weights_) kept_.push_back({name, std::vector<float>(data, data + numel)});
         return report(ob200_net_set_tensor(net_, name.c_str(), data, numel));
     }
     bool finalize() { return net_ && report(ob200_net_finalize(net_)) && (ready_ = true); }
@@ -135,10 +141,16 @@ public:
     void load(const std::string& path) override {
         std::FILE* f = std::fopen(path.c_str(), "rb");
         if (!f) return;
+        std::fseek(f, 0, SEEK_END);
+        const long file_size = std::ftell(f);
+        std::fseek(f, 0, SEEK_SET);
         uint32_t len; uint64_t numel;
         while (std::fread(&len, 4, 1, f) == 1 && len < 4096) {
             std::string name(len, '\0');
             if (std::fread(&name[0], 1, len, f) != len || std::fread(&numel, 8, 1, f) != 1) break;
+            // a truncated or corrupt file must not turn into an allocation of whatever its bytes say
+            const long here = std::ftell(f);
+            if (here < 0 || file_size < here || numel > (uint64_t)(file_size - here) / 4) break;
             std::vector<float> data(numel);
             if (std::fread(data.data(), 4, numel, f) != numel) break;
             setTensor(name, data.data(), (int64_t)numel);
@@ -165,6 +177,7 @@ private:
     ob200_net_config cfg_{};
     ob200_net* net_ = nullptr;
     bool ready_ = false;
+    bool keep_weights_ = false;
     std::vector<Kept> kept_;
 };
 

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libomoknuni_b200.so")
 
 OUT_PROBS, OUT_LOGITS = 0, 1
 GUARD = 32
+DTYPE_BF16, DTYPE_F16 = 0, 1     # storage type of board tensors and packed tower weights
 
 
 class Error(RuntimeError):
@@ -34,7 +35,7 @@ POLICY_FC, POLICY_CONV_PLANES = 0, 1
 class NetConfig(C.Structure):
     _fields_ = [(k, C.c_int32) for k in ("board_size", "input_channels", "filters", "blocks", "policy_size",
                                           "policy_head_ch", "value_head_ch", "value_hidden", "max_batch", "device",
-                                          "policy_kind")]
+                                          "policy_kind", "tower_dtype")]
 
 
 class SearchConfig(C.Structure):
@@ -74,11 +75,19 @@ SIGNATURES = {
     "ob200_board_tensor_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
     "ob200_launch_encode_gomoku": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                              C.c_int32, C.c_void_p, C.c_void_p]),
+    "ob200_launch_encode_gomoku_dt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                                C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "ob200_launch_encode_go": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p, C.c_void_p]),
     "ob200_launch_encode_gomoku3": (C.c_int, [C.c_void_p, C.c_void_p] + [C.c_int32] * 3 + [C.c_void_p, C.c_void_p]),
     "ob200_launch_encode_chess": (C.c_int, [C.c_void_p] * 3 + [C.c_int32] * 2 + [C.c_void_p, C.c_void_p]),
     "ob200_launch_planes_to_board_tensor": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                                       C.c_void_p]),
+    "ob200_launch_planes_to_board_tensor_dt": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                                         C.c_void_p, C.c_void_p]),
+    "ob200_launch_conv3x3_dt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                          C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "ob200_pack_conv3x3_weights_dt": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                                C.c_void_p]),
     "ob200_launch_conv3x3": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
                                        C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "ob200_packed_conv3x3_bytes": (C.c_int64, [C.c_int32, C.c_int32]),
@@ -219,8 +228,8 @@ def board_positions(board_size, B):
     return int(lib().ob200_board_tensor_positions(board_size, B))
 
 
-def board_tensor_to_planes(bt_u16, board_size, B, channels):
-    """bf16 NHWC board tensor (numpy uint16 view, flat, `channels` rounded up to 8
+def board_tensor_to_planes(bt_u16, board_size, B, channels, dtype=DTYPE_BF16):
+    """16-bit NHWC board tensor (numpy uint16 view, flat, `channels` rounded up to 8
     per position) -> fp32 planes [B, channels, S, S] plus a flag telling whether
     every padding / guard element is zero.  Host-side helper for tests."""
     S, GP = board_size, board_size + 1
@@ -228,7 +237,7 @@ def board_tensor_to_planes(bt_u16, board_size, B, channels):
     PT = board_positions(S, B)
     Cp = (channels + 7) // 8 * 8
     a = np.asarray(bt_u16).reshape(-1)[: PT * Cp].reshape(PT, Cp)
-    f = (a.astype(np.uint32) << 16).view(np.float32)
+    f = a.view(np.float16).astype(np.float32) if dtype == DTYPE_F16 else (a.astype(np.uint32) << 16).view(np.float32)
     body = f[GUARD:GUARD + B * slots].reshape(B, GP, GP, Cp)
     planes = body[:, :S, :S, :channels].transpose(0, 3, 1, 2)
     pad_zero = (not f[:GUARD].any() and not f[GUARD + B * slots:].any()
@@ -236,8 +245,8 @@ def board_tensor_to_planes(bt_u16, board_size, B, channels):
     return np.ascontiguousarray(planes), bool(pad_zero)
 
 
-def planes_to_board_tensor_host(planes, out_channels):
-    """fp32 planes [B, C, S, S] -> bf16 NHWC board tensor as a flat numpy uint16
+def planes_to_board_tensor_host(planes, out_channels, dtype=DTYPE_BF16):
+    """fp32 planes [B, C, S, S] -> 16-bit NHWC board tensor as a flat numpy uint16
     array (round to nearest even), the host-side twin of the device conversion."""
     B, Cc, S, _ = planes.shape
     GP = S + 1
@@ -245,21 +254,21 @@ def planes_to_board_tensor_host(planes, out_channels):
     full = np.zeros((B, GP, GP, out_channels), np.float32)
     full[:, :S, :S, :Cc] = planes.transpose(0, 2, 3, 1)
     u = full.view(np.uint32)
-    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    r = full.astype(np.float16).view(np.uint16) if dtype == DTYPE_F16 else ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
     out = np.zeros((PT, out_channels), np.uint16)
     out[GUARD:GUARD + B * GP * GP] = r.reshape(B * GP * GP, out_channels)
     return out.reshape(-1)
 
 
-def encode_gomoku(history, n_hist, to_move, board_size=15, planes=19, out_channels=64):
-    """Device tensors in (int16 [B,16], uint8 [B], uint8 [B]) -> bf16 board tensor
-    (torch int16 tensor holding the bf16 bits)."""
+def encode_gomoku(history, n_hist, to_move, board_size=15, planes=19, out_channels=64, dtype=DTYPE_BF16):
+    """Device tensors in (int16 [B,16], uint8 [B], uint8 [B]) -> board tensor
+    (torch int16 tensor holding the bf16 / fp16 bits)."""
     import torch
     B = history.shape[0]
     nbytes = int(lib().ob200_board_tensor_bytes(board_size, B, out_channels))
     out = torch.empty(nbytes // 2, dtype=torch.int16, device=history.device)
-    check(lib().ob200_launch_encode_gomoku(_ptr(history), _ptr(n_hist), _ptr(to_move), B, board_size, planes,
-                                           out_channels, _ptr(out), _stream()))
+    check(lib().ob200_launch_encode_gomoku_dt(_ptr(history), _ptr(n_hist), _ptr(to_move), B, board_size, planes,
+                                              out_channels, dtype, _ptr(out), _stream()))
     return out
 
 
@@ -296,35 +305,35 @@ def encode_chess(pieces, meta, legal_to, out_channels=64):
     return out
 
 
-def planes_to_board_tensor(planes, out_channels):
+def planes_to_board_tensor(planes, out_channels, dtype=DTYPE_BF16):
     import torch
     B, Cc, S, _ = planes.shape
     nbytes = int(lib().ob200_board_tensor_bytes(S, B, out_channels))
     out = torch.empty(nbytes // 2, dtype=torch.int16, device=planes.device)
-    check(lib().ob200_launch_planes_to_board_tensor(_ptr(planes), B, Cc, S, out_channels, _ptr(out), _stream()))
+    check(lib().ob200_launch_planes_to_board_tensor_dt(_ptr(planes), B, Cc, S, out_channels, dtype, _ptr(out), _stream()))
     return out
 
 
-def pack_conv3x3(w_oihw, scale, cin=64):
+def pack_conv3x3(w_oihw, scale, cin=64, dtype=DTYPE_BF16):
     """fp32 [cout, cin_real, 3, 3] (+ per-output-channel scale or None) -> packed
-    bf16 image as numpy uint16."""
+    bf16 / fp16 image as numpy uint16."""
     w = np.ascontiguousarray(w_oihw, np.float32)
     cout, cin_real = w.shape[:2]
     out = np.empty(int(lib().ob200_packed_conv3x3_bytes(cin, cout)) // 2, np.uint16)
     sc = None if scale is None else np.ascontiguousarray(scale, np.float32)
-    check(lib().ob200_pack_conv3x3_weights(w.ctypes.data_as(C.c_void_p), None if sc is None else sc.ctypes.data_as(C.c_void_p),
-                                           cout, cin_real, cin, out.ctypes.data_as(C.c_void_p)))
+    check(lib().ob200_pack_conv3x3_weights_dt(w.ctypes.data_as(C.c_void_p), None if sc is None else sc.ctypes.data_as(C.c_void_p),
+                                              cout, cin_real, cin, dtype, out.ctypes.data_as(C.c_void_p)))
     return out
 
 
-def conv3x3(x_bt, packed_w, bias, residual_bt, B, board_size, cin=64, cout=64, relu=True, out=None):
-    """One conv layer on device board tensors (torch int16 tensors with bf16 bits)."""
+def conv3x3(x_bt, packed_w, bias, residual_bt, B, board_size, cin=64, cout=64, relu=True, out=None, dtype=DTYPE_BF16):
+    """One conv layer on device board tensors (torch int16 tensors with bf16 / fp16 bits)."""
     import torch
     if out is None:
         nbytes = int(lib().ob200_board_tensor_bytes(board_size, B, cout))
         out = torch.zeros(nbytes // 2, dtype=torch.int16, device=x_bt.device)
-    check(lib().ob200_launch_conv3x3(_ptr(x_bt), _ptr(packed_w), _ptr(bias), _ptr(residual_bt), _ptr(out), B, board_size,
-                                     cin, cout, int(relu), _stream()))
+    check(lib().ob200_launch_conv3x3_dt(_ptr(x_bt), _ptr(packed_w), _ptr(bias), _ptr(residual_bt), _ptr(out), B, board_size,
+                                        cin, cout, int(relu), dtype, _stream()))
     return out
 
 
@@ -335,9 +344,10 @@ class Net:
     under the same names, inference on host buffers)."""
 
     def __init__(self, input_channels, board_size, blocks, filters, policy_size, policy_head_ch=32, value_head_ch=32,
-                 value_hidden=256, max_batch=1024, device=0, policy_kind=POLICY_FC):
+                 value_hidden=256, max_batch=1024, device=0, policy_kind=POLICY_FC, tower_dtype=DTYPE_BF16):
         self.cfg = NetConfig(board_size, input_channels, filters, blocks, policy_size or board_size * board_size,
-                             policy_head_ch, value_head_ch, value_hidden, max_batch, device, policy_kind)
+                             policy_head_ch, value_head_ch, value_hidden, max_batch, device, policy_kind, tower_dtype)
+        self.tower_dtype = tower_dtype
         self.h = C.c_void_p()
         check(lib().ob200_net_create(C.byref(self.cfg), C.byref(self.h)))
         self.policy_size = self.cfg.policy_size

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstring>
 #include "../../include/omoknuni_b200.h"
 
 namespace ob200 {
@@ -37,6 +38,34 @@ inline cudaStream_t as_stream(ob200_stream s) { return reinterpret_cast<cudaStre
             return ::ob200::set_error(OB200_ERR_CUDA, "launch of %s failed: %s", name,   \
                                       cudaGetErrorString(_e));                           \
     } while (0)
+
+// fp32 -> the 16-bit storage types, round to nearest even (host side: weight packing).
+inline uint16_t f32_to_bf16_rne(float f) {
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40);  // NaN
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+// fp16; magnitudes beyond the largest finite value (65,504) saturate there, as the kernels' stores do.
+inline uint16_t f32_to_f16_rne_sat(float f) {
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    const uint16_t sign = (uint16_t)((u >> 16) & 0x8000u);
+    const uint32_t a = u & 0x7FFFFFFFu;
+    if (a > 0x7F800000u) return (uint16_t)(sign | 0x7E00u);            // NaN
+    if (a >= 0x477FF000u) return (uint16_t)(sign | 0x7BFFu);           // rounds to >= 65,520: saturate
+    if (a < 0x33000001u) return sign;                                  // below half the smallest subnormal
+    const int e = (int)(a >> 23) - 127;
+    uint32_t m = (a & 0x7FFFFFu) | 0x800000u;                          // 24-bit significand
+    int shift = e >= -14 ? 13 : 13 + (-14 - e);                        // bits dropped (subnormals drop more)
+    uint32_t q = m >> shift;
+    const uint32_t rem = m & ((1u << shift) - 1u), halfway = 1u << (shift - 1);
+    if (rem > halfway || (rem == halfway && (q & 1u))) ++q;
+    // normal: q has the hidden bit at 1 << 10 (a carry into 1 << 11 bumps the exponent by itself)
+    const uint32_t h = e >= -14 ? (((uint32_t)(e + 15) << 10) + (q - 0x400u)) : q;
+    return (uint16_t)(sign | h);
+}
 
 // Geometry of a board tensor (see the header's "Board tensors" section).
 struct BoardGeom {

@@ -1,4 +1,4 @@
-// Leaf state -> bf16 board tensor (sm_100a).
+// Leaf state -> 16-bit board tensor (bf16, or fp16 when the launcher is given that type; sm_100a).
 //
 // Output format (see "Board tensors" in omoknuni_b200.h): NHWC, positions on a
 // (S+1) x (S+1) grid per board whose last column / row are zero, guard
@@ -6,13 +6,14 @@
 // consecutive addresses; the kernels also write the zero padding, so the output
 // needs no memset.
 #include "internal.h"
-#include <cuda_bf16.h>
+#include "sm100_ptx.cuh"
 #include <mutex>
 
 namespace ob200 {
 namespace {
 
-struct alignas(16) Pack8 { __nv_bfloat16 v[8]; };
+struct alignas(16) Pack8 { uint16_t v[8]; };
+using ptx::store16;
 constexpr size_t kMaxBoardSmem = 200 * 1024;   // a board's block must fit a CTA's shared memory
 constexpr int kMaxDevices = 64;
 
@@ -26,7 +27,7 @@ constexpr int kEncThreads = 128;
 __global__ void __launch_bounds__(kEncThreads)
 encode_gomoku_kernel(const int16_t* __restrict__ history, const uint8_t* __restrict__ n_hist,
                      const uint8_t* __restrict__ to_move, int B, int S, int planes, int chunks,
-                     int chunk_shift, int cover, Pack8* __restrict__ out) {
+                     int chunk_shift, int cover, int f16, Pack8* __restrict__ out) {
     // cover = positions written (guards included); chunks = channels / 8 (chunk_shift = log2 when it
     // is a power of two, else -1).  Phase 1: a thread works out the 24 plane channels of one
     // position.  Phase 2: the block writes its 128 positions as 16-byte stores, consecutive threads
@@ -38,7 +39,7 @@ encode_gomoku_kernel(const int16_t* __restrict__ history, const uint8_t* __restr
 #pragma unroll
     for (int c = 0; c < 3; ++c)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[c].v[j] = __float2bfloat16(0.0f);
+        for (int j = 0; j < 8; ++j) o[c].v[j] = (uint16_t)0;
     const int p = pidx - OB200_GUARD;
     const int GP = S + 1, slots = GP * GP;
     if (p >= 0 && p < B * slots) {
@@ -55,11 +56,11 @@ encode_gomoku_kernel(const int16_t* __restrict__ history, const uint8_t* __restr
             for (int plane = 0; plane < 16; ++plane) {
                 const int k = (plane & 1) ? plane - 1 : plane + 1;
                 const int hk = (int)(int16_t)((k & 1) ? (hw[k >> 1] >> 16) : (hw[k >> 1] & 0xffffu));
-                if (k < nh && hk == cell) o[plane >> 3].v[plane & 7] = __float2bfloat16(1.0f);
+                if (k < nh && hk == cell) o[plane >> 3].v[plane & 7] = store16(1.0f, f16);
             }
             // plane 16: colour.  Planes 17 / 18 (attack / defense): zero, as the reference's CPU
             // code yields for every legal move (src/utils/attack_defense_module.cpp:96-154).
-            if (planes > 16 && to_move[b] == 1) o[2].v[0] = __float2bfloat16(1.0f);
+            if (planes > 16 && to_move[b] == 1) o[2].v[0] = store16(1.0f, f16);
         }
     }
 #pragma unroll
@@ -69,7 +70,7 @@ encode_gomoku_kernel(const int16_t* __restrict__ history, const uint8_t* __restr
     const int n = n_pos * chunks;
     Pack8 zero;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) zero.v[j] = __float2bfloat16(0.0f);
+    for (int j = 0; j < 8; ++j) zero.v[j] = (uint16_t)0;
     Pack8* dst = out + (size_t)base * chunks;
     for (int idx = threadIdx.x; idx < n; idx += kEncThreads) {
         const int pl = chunk_shift >= 0 ? idx >> chunk_shift : idx / chunks;
@@ -84,7 +85,7 @@ encode_gomoku_kernel(const int16_t* __restrict__ history, const uint8_t* __restr
 // first and after the last board.
 __global__ void __launch_bounds__(256)
 encode_gomoku_board_kernel(const int16_t* __restrict__ history, const uint8_t* __restrict__ n_hist,
-                           const uint8_t* __restrict__ to_move, int B, int S, int planes, int C, int cover,
+                           const uint8_t* __restrict__ to_move, int B, int S, int planes, int C, int cover, int f16,
                            uint8_t* __restrict__ out) {
     extern __shared__ __align__(128) uint8_t board_s[];
     const int GP = S + 1, slots = GP * GP, S2 = S * S;
@@ -102,8 +103,8 @@ encode_gomoku_board_kernel(const int16_t* __restrict__ history, const uint8_t* _
     for (int i = threadIdx.x; i < bytes / 16; i += blockDim.x) s16[i] = z;
     __syncthreads();
     const int b = blockIdx.x;
-    __nv_bfloat16* sb = reinterpret_cast<__nv_bfloat16*>(board_s);
-    const __nv_bfloat16 one = __float2bfloat16(1.0f);
+    uint16_t* sb = reinterpret_cast<uint16_t*>(board_s);
+    const uint16_t one = store16(1.0f, f16);
     if (threadIdx.x < 16) {
         const int plane = threadIdx.x;
         const int k = (plane & 1) ? plane - 1 : plane + 1;
@@ -150,7 +151,7 @@ constexpr int kGoMaxCells = 31 * 31;
 __global__ void __launch_bounds__(kGoThreads)
 encode_go_kernel(const int8_t* __restrict__ stones, const int32_t* __restrict__ ko_point,
                  const uint8_t* __restrict__ to_move, const uint32_t* __restrict__ legal_bits, int legal_words,
-                 int B, int S, int C, int cover, uint8_t* __restrict__ out) {
+                 int B, int S, int C, int cover, int f16, uint8_t* __restrict__ out) {
     extern __shared__ __align__(128) uint8_t board_s[];
     __shared__ int label[kGoMaxCells];
     __shared__ int gsize[kGoMaxCells];
@@ -210,22 +211,22 @@ encode_go_kernel(const int8_t* __restrict__ stones, const int32_t* __restrict__ 
     }
     __syncthreads();
     // ---- planes ----
-    __nv_bfloat16* sb = reinterpret_cast<__nv_bfloat16*>(board_s);
-    const __nv_bfloat16 one = __float2bfloat16(1.0f);
+    uint16_t* sb = reinterpret_cast<uint16_t*>(board_s);
+    const uint16_t one = store16(1.0f, f16);
     const int mover = to_move[b];
     const int ko = ko_point[b];
     const float half = fmaxf(1.0f, __fdiv_rn((float)S, 2.0f));
     for (int p = threadIdx.x; p < S2; p += blockDim.x) {
         const int x = p % S, y = p / S;
-        __nv_bfloat16* o = sb + (size_t)(y * GP + x) * C;
+        uint16_t* o = sb + (size_t)(y * GP + x) * C;
         const int s = st[p];
         if (s == 1) o[0] = one;
         if (s == 2) o[1] = one;
         if (mover == 1) o[2] = one;
-        if (s) o[s == 1 ? 3 : 4] = __float2bfloat16(fminf(1.0f, __fdiv_rn((float)glibs[label[p]], 10.0f)));
+        if (s) o[s == 1 ? 3 : 4] = store16(fminf(1.0f, __fdiv_rn((float)glibs[label[p]], 10.0f)), f16);
         if (p == ko) o[5] = one;
-        o[6] = __float2bfloat16(fminf(1.0f, fmaxf(0.0f, __fdiv_rn((float)min(x, S - 1 - x), half))));
-        o[7] = __float2bfloat16(fminf(1.0f, fmaxf(0.0f, __fdiv_rn((float)min(y, S - 1 - y), half))));
+        o[6] = store16(fminf(1.0f, fmaxf(0.0f, __fdiv_rn((float)min(x, S - 1 - x), half))), f16);
+        o[7] = store16(fminf(1.0f, fmaxf(0.0f, __fdiv_rn((float)min(y, S - 1 - y), half))), f16);
         if ((legal_bits[(size_t)b * legal_words + (p >> 5)] >> (p & 31)) & 1u) {
             const int nb[4] = {y > 0 ? p - S : -1, x + 1 < S ? p + 1 : -1, y + 1 < S ? p + S : -1, x > 0 ? p - 1 : -1};
             float capture = 0.0f, defense = 0.0f;
@@ -246,8 +247,8 @@ encode_go_kernel(const int8_t* __restrict__ stones, const int32_t* __restrict__ 
                 }
             }
             if (friendly_adj >= 2 && empty_adj <= 1) defense = __fadd_rn(defense, 0.3f);
-            o[8] = __float2bfloat16(fminf(1.0f, __fdiv_rn(capture, 5.0f)));
-            o[9] = __float2bfloat16(fminf(1.0f, defense));
+            o[8] = store16(fminf(1.0f, __fdiv_rn(capture, 5.0f)), f16);
+            o[9] = store16(fminf(1.0f, defense), f16);
         }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -270,7 +271,8 @@ encode_go_kernel(const int8_t* __restrict__ stones, const int32_t* __restrict__ 
 // (1, 3, 3, 5, 9, 100) of the enemy / own pieces on the 8 squares around it.
 __global__ void __launch_bounds__(64)
 encode_chess_kernel(const int8_t* __restrict__ pieces, const int32_t* __restrict__ meta,
-                    const uint32_t* __restrict__ legal_to, int B, int C, int cover, uint8_t* __restrict__ out) {
+                    const uint32_t* __restrict__ legal_to, int B, int C, int cover, int f16,
+                    uint8_t* __restrict__ out) {
     extern __shared__ __align__(128) uint8_t board_s[];
     __shared__ int8_t pc_s[64];
     constexpr int S = 8, GP = 9, slots = 81;
@@ -293,15 +295,15 @@ encode_chess_kernel(const int8_t* __restrict__ pieces, const int32_t* __restrict
     const int mover = m[0], castling_bits = m[1], ep = m[2], halfmove = m[3], chess960 = m[4], reps = m[5];
     __syncthreads();
     const int r0 = sq >> 3, c0 = sq & 7;
-    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(board_s) + (size_t)(r0 * GP + c0) * C;
-    const __nv_bfloat16 one = __float2bfloat16(1.0f);
+    uint16_t* o = reinterpret_cast<uint16_t*>(board_s) + (size_t)(r0 * GP + c0) * C;
+    const uint16_t one = store16(1.0f, f16);
     if (pc) o[(pc & 7) - 1 + ((pc & 8) ? 6 : 0)] = one;
     if (mover == 1) o[12] = one;
-    o[13] = __float2bfloat16(0.25f * (float)__popc(castling_bits & 15));
+    o[13] = store16(0.25f * (float)__popc(castling_bits & 15), f16);
     if (sq == ep) o[14] = one;
-    o[15] = __float2bfloat16(fminf(1.0f, __fdiv_rn((float)halfmove, 100.0f)));
+    o[15] = store16(fminf(1.0f, __fdiv_rn((float)halfmove, 100.0f)), f16);
     if (chess960) o[16] = one;
-    o[17] = __float2bfloat16(fminf(1.0f, fmaxf(0.0f, __fdiv_rn((float)reps, 3.0f))));
+    o[17] = store16(fminf(1.0f, fmaxf(0.0f, __fdiv_rn((float)reps, 3.0f))), f16);
     if ((legal_to[(size_t)b * 2 + (sq >> 5)] >> (sq & 31)) & 1u) {
         float attack = 0.0f, defense = 0.0f;
 #pragma unroll
@@ -317,8 +319,8 @@ encode_chess_kernel(const int8_t* __restrict__ pieces, const int32_t* __restrict
                 const float v = t == 1 ? 1.0f : t <= 3 ? 3.0f : t == 4 ? 5.0f : t == 5 ? 9.0f : 100.0f;
                 if (((q & 8) ? 2 : 1) != mover) attack = __fadd_rn(attack, v); else defense = __fadd_rn(defense, v);
             }
-        o[18] = __float2bfloat16(fminf(1.0f, __fdiv_rn(attack, 10.0f)));
-        o[19] = __float2bfloat16(fminf(1.0f, __fdiv_rn(defense, 10.0f)));
+        o[18] = store16(fminf(1.0f, __fdiv_rn(attack, 10.0f)), f16);
+        o[19] = store16(fminf(1.0f, __fdiv_rn(defense, 10.0f)), f16);
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
@@ -337,14 +339,14 @@ encode_chess_kernel(const int8_t* __restrict__ pieces, const int32_t* __restrict
 // opponent's, 2 ones iff BLACK is to move.  One thread per (position, 8-channel block).
 __global__ void __launch_bounds__(256)
 encode_gomoku3_kernel(const int8_t* __restrict__ stones, const uint8_t* __restrict__ to_move, int B, int S, int chunks,
-                      long long cover, Pack8* __restrict__ out) {
+                      long long cover, int f16, Pack8* __restrict__ out) {
     const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= cover * chunks) return;
     const long long pidx = gid / chunks;
     const int chunk = (int)(gid - pidx * chunks);
     Pack8 o;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o.v[j] = __float2bfloat16(0.0f);
+    for (int j = 0; j < 8; ++j) o.v[j] = (uint16_t)0;
     const long long p = pidx - OB200_GUARD;
     const int GP = S + 1, slots = GP * GP;
     if (chunk == 0 && p >= 0 && p < (long long)B * slots) {
@@ -352,9 +354,9 @@ encode_gomoku3_kernel(const int8_t* __restrict__ stones, const uint8_t* __restri
         const int y = r / GP, x = r - y * GP;
         if (y < S && x < S) {
             const int st = stones[(size_t)b * S * S + y * S + x], me = to_move[b];
-            if (st == me) o.v[0] = __float2bfloat16(1.0f);
-            else if (st != 0) o.v[1] = __float2bfloat16(1.0f);
-            if (me == 1) o.v[2] = __float2bfloat16(1.0f);
+            if (st == me) o.v[0] = store16(1.0f, f16);
+            else if (st != 0) o.v[1] = store16(1.0f, f16);
+            if (me == 1) o.v[2] = store16(1.0f, f16);
         }
     }
     out[gid] = o;
@@ -362,7 +364,7 @@ encode_gomoku3_kernel(const int8_t* __restrict__ stones, const uint8_t* __restri
 
 __global__ void __launch_bounds__(256)
 planes_to_board_tensor_kernel(const float* __restrict__ planes, int B, int C, int S, int chunks,
-                              long long cover, Pack8* __restrict__ out) {
+                              long long cover, int f16, Pack8* __restrict__ out) {
     const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (gid >= cover * chunks) return;
     const int chunk = (int)(gid % chunks);
@@ -370,7 +372,7 @@ planes_to_board_tensor_kernel(const float* __restrict__ planes, int B, int C, in
     const int GP = S + 1, slots = GP * GP;
     Pack8 o;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o.v[j] = __float2bfloat16(0.0f);
+    for (int j = 0; j < 8; ++j) o.v[j] = (uint16_t)0;
     if (p >= 0 && p < (long long)B * slots) {
         const int b = (int)(p / slots), r = (int)(p % slots);
         const int y = r / GP, x = r % GP;
@@ -378,7 +380,7 @@ planes_to_board_tensor_kernel(const float* __restrict__ planes, int B, int C, in
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const int c = chunk * 8 + j;
-                if (c < C) o.v[j] = __float2bfloat16(__ldg(planes + (((size_t)b * C + c) * S + y) * S + x));
+                if (c < C) o.v[j] = store16(__ldg(planes + (((size_t)b * C + c) * S + y) * S + x), f16);
             }
         }
     }
@@ -389,7 +391,9 @@ planes_to_board_tensor_kernel(const float* __restrict__ planes, int B, int C, in
 
 int launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, const uint8_t* to_move,
                          int32_t B, int32_t board_size, int32_t planes, int32_t out_channels,
-                         void* board_tensor_out, cudaStream_t stream) {
+                         void* board_tensor_out, cudaStream_t stream, int dtype) {
+    if (dtype != OB200_DTYPE_BF16 && dtype != OB200_DTYPE_F16) return set_error(OB200_ERR_INVALID, "encode: bad dtype %d", dtype);
+    const int f16 = dtype == OB200_DTYPE_F16;
     if (!history || !n_hist || !to_move || !board_tensor_out || B < 0)
         return set_error(OB200_ERR_INVALID, "ob200_launch_encode_gomoku: null pointer or negative batch");
     if (planes != 17 && planes != 19)
@@ -419,7 +423,7 @@ int launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, const ui
             OB200_CUDA_OK(cudaFuncSetAttribute(encode_gomoku_board_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                (int)kMaxBoardSmem));
         encode_gomoku_board_kernel<<<(unsigned)(B + 2), 256, board_bytes, stream>>>(
-            history, n_hist, to_move, B, board_size, planes, out_channels, (int)g.PT,
+            history, n_hist, to_move, B, board_size, planes, out_channels, (int)g.PT, f16,
             static_cast<uint8_t*>(board_tensor_out));
         OB200_LAUNCHED("encode_gomoku_board_kernel");
         return OB200_OK;
@@ -428,14 +432,16 @@ int launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, const ui
     for (int sft = 0; sft < 8; ++sft)
         if ((1 << sft) == chunks) chunk_shift = sft;
     encode_gomoku_kernel<<<(unsigned)((g.PT + kEncThreads - 1) / kEncThreads), kEncThreads, 0, stream>>>(
-        history, n_hist, to_move, B, board_size, planes, chunks, chunk_shift, (int)g.PT,
+        history, n_hist, to_move, B, board_size, planes, chunks, chunk_shift, (int)g.PT, f16,
         reinterpret_cast<Pack8*>(board_tensor_out));
     OB200_LAUNCHED("encode_gomoku_kernel");
     return OB200_OK;
 }
 
 int launch_encode_go(const int8_t* stones, const int32_t* ko_point, const uint8_t* to_move, const uint32_t* legal_bits,
-                     int32_t B, int32_t board_size, int32_t out_channels, void* board_tensor_out, cudaStream_t stream) {
+                     int32_t B, int32_t board_size, int32_t out_channels, void* board_tensor_out, cudaStream_t stream, int dtype) {
+    if (dtype != OB200_DTYPE_BF16 && dtype != OB200_DTYPE_F16) return set_error(OB200_ERR_INVALID, "encode: bad dtype %d", dtype);
+    const int f16 = dtype == OB200_DTYPE_F16;
     if (!stones || !ko_point || !to_move || !legal_bits || !board_tensor_out || B < 0)
         return set_error(OB200_ERR_INVALID, "ob200_launch_encode_go: null pointer or negative batch");
     if (board_size < 2 || board_size > 30 || out_channels < 10 || (out_channels & 7))
@@ -452,14 +458,16 @@ int launch_encode_go(const int8_t* stones, const int32_t* ko_point, const uint8_
         OB200_CUDA_OK(cudaFuncSetAttribute(encode_go_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)board_bytes));
     const int legal_words = (board_size * board_size + 31) / 32;
     encode_go_kernel<<<(unsigned)(B + 2), kGoThreads, board_bytes, stream>>>(
-        stones, ko_point, to_move, legal_bits, legal_words, B, board_size, out_channels, (int)g.PT,
+        stones, ko_point, to_move, legal_bits, legal_words, B, board_size, out_channels, (int)g.PT, f16,
         static_cast<uint8_t*>(board_tensor_out));
     OB200_LAUNCHED("encode_go_kernel");
     return OB200_OK;
 }
 
 int launch_encode_chess(const int8_t* pieces, const int32_t* meta, const uint32_t* legal_to, int32_t B,
-                        int32_t out_channels, void* board_tensor_out, cudaStream_t stream) {
+                        int32_t out_channels, void* board_tensor_out, cudaStream_t stream, int dtype) {
+    if (dtype != OB200_DTYPE_BF16 && dtype != OB200_DTYPE_F16) return set_error(OB200_ERR_INVALID, "encode: bad dtype %d", dtype);
+    const int f16 = dtype == OB200_DTYPE_F16;
     if (!pieces || !meta || !legal_to || !board_tensor_out || B < 0)
         return set_error(OB200_ERR_INVALID, "ob200_launch_encode_chess: null pointer or negative batch");
     if (out_channels < 20 || (out_channels & 7) || out_channels > 256)
@@ -467,14 +475,16 @@ int launch_encode_chess(const int8_t* pieces, const int32_t* meta, const uint32_
     if (int rc = require_device()) return rc;
     const BoardGeom g = board_geom(8, B);
     const size_t board_bytes = (size_t)81 * out_channels * 2;
-    encode_chess_kernel<<<(unsigned)(B + 2), 64, board_bytes, stream>>>(pieces, meta, legal_to, B, out_channels, (int)g.PT,
+    encode_chess_kernel<<<(unsigned)(B + 2), 64, board_bytes, stream>>>(pieces, meta, legal_to, B, out_channels, (int)g.PT, f16,
                                                                          static_cast<uint8_t*>(board_tensor_out));
     OB200_LAUNCHED("encode_chess_kernel");
     return OB200_OK;
 }
 
 int launch_encode_gomoku3(const int8_t* stones, const uint8_t* to_move, int32_t B, int32_t board_size, int32_t out_channels,
-                          void* board_tensor_out, cudaStream_t stream) {
+                          void* board_tensor_out, cudaStream_t stream, int dtype) {
+    if (dtype != OB200_DTYPE_BF16 && dtype != OB200_DTYPE_F16) return set_error(OB200_ERR_INVALID, "encode: bad dtype %d", dtype);
+    const int f16 = dtype == OB200_DTYPE_F16;
     if (!stones || !to_move || !board_tensor_out || B < 0)
         return set_error(OB200_ERR_INVALID, "ob200_launch_encode_gomoku3: null pointer or negative batch");
     if (board_size < 1 || board_size > 31 || out_channels < 8 || (out_channels & 7))
@@ -484,14 +494,16 @@ int launch_encode_gomoku3(const int8_t* stones, const uint8_t* to_move, int32_t 
     const BoardGeom g = board_geom(board_size, B);
     const int chunks = out_channels / 8;
     const long long total = g.PT * chunks;
-    encode_gomoku3_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(stones, to_move, B, board_size, chunks, g.PT,
+    encode_gomoku3_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(stones, to_move, B, board_size, chunks, g.PT, f16,
                                                                               reinterpret_cast<Pack8*>(board_tensor_out));
     OB200_LAUNCHED("encode_gomoku3_kernel");
     return OB200_OK;
 }
 
 int launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C, int32_t board_size,
-                                  int32_t out_channels, void* board_tensor_out, cudaStream_t stream) {
+                                  int32_t out_channels, void* board_tensor_out, cudaStream_t stream, int dtype) {
+    if (dtype != OB200_DTYPE_BF16 && dtype != OB200_DTYPE_F16) return set_error(OB200_ERR_INVALID, "encode: bad dtype %d", dtype);
+    const int f16 = dtype == OB200_DTYPE_F16;
     if (!planes_nchw || !board_tensor_out || B < 0 || C <= 0)
         return set_error(OB200_ERR_INVALID, "ob200_launch_planes_to_board_tensor: bad arguments");
     if (board_size < 1 || board_size > 31 || out_channels <= 0 || (out_channels & 7))
@@ -502,7 +514,7 @@ int launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C
     const int chunks = out_channels / 8;
     const long long total = g.PT * chunks;
     planes_to_board_tensor_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-        planes_nchw, B, C, board_size, chunks, g.PT, reinterpret_cast<Pack8*>(board_tensor_out));
+        planes_nchw, B, C, board_size, chunks, g.PT, f16, reinterpret_cast<Pack8*>(board_tensor_out));
     OB200_LAUNCHED("planes_to_board_tensor_kernel");
     return OB200_OK;
 }
@@ -518,6 +530,13 @@ int ob200_launch_encode_gomoku(const int16_t* history, const uint8_t* n_hist, co
                                void* board_tensor_out, ob200_stream stream) {
     return launch_encode_gomoku(history, n_hist, to_move, B, board_size, planes, out_channels, board_tensor_out,
                                 as_stream(stream));
+}
+
+int ob200_launch_encode_gomoku_dt(const int16_t* history, const uint8_t* n_hist, const uint8_t* to_move,
+                                  int32_t B, int32_t board_size, int32_t planes, int32_t out_channels, int32_t dtype,
+                                  void* board_tensor_out, ob200_stream stream) {
+    return launch_encode_gomoku(history, n_hist, to_move, B, board_size, planes, out_channels, board_tensor_out,
+                                as_stream(stream), dtype);
 }
 
 int ob200_launch_encode_go(const int8_t* stones, const int32_t* ko_point, const uint8_t* to_move,
@@ -541,6 +560,12 @@ int ob200_launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int
                                         int32_t out_channels, void* board_tensor_out, ob200_stream stream) {
     return launch_planes_to_board_tensor(planes_nchw, B, C, board_size, out_channels, board_tensor_out,
                                          as_stream(stream));
+}
+
+int ob200_launch_planes_to_board_tensor_dt(const float* planes_nchw, int32_t B, int32_t C, int32_t board_size,
+                                           int32_t out_channels, int32_t dtype, void* board_tensor_out, ob200_stream stream) {
+    return launch_planes_to_board_tensor(planes_nchw, B, C, board_size, out_channels, board_tensor_out,
+                                         as_stream(stream), dtype);
 }
 
 }  // extern "C"

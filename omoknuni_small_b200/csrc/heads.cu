@@ -11,13 +11,13 @@
 //   softmax_kernel     in-place softmax over a row.
 //   value_out_kernel   value_fc2 + tanh (one warp per board).
 #include "internal.h"
-#include <cuda_bf16.h>
+#include "sm100_ptx.cuh"
 #include <mutex>
 
 namespace ob200 {
 namespace {
 
-struct alignas(16) Pack8 { __nv_bfloat162 v[4]; };
+struct alignas(16) Pack8 { uint32_t v[4]; };
 
 // A warp takes 32 consecutive positions of the board tensor (pad positions included, their
 // results are dropped).  Eight lanes share a position: lane = 8 * (position within a group of 4)
@@ -33,7 +33,7 @@ template <int HCT>
 __global__ void __launch_bounds__(kHeadThreads)
 head_conv_kernel(const uint8_t* __restrict__ tower, const float* __restrict__ w,
                  const float* __restrict__ bias, int HC, int pc, float* __restrict__ hp,
-                 float* __restrict__ hv, int B, int S, int C) {
+                 float* __restrict__ hv, int B, int S, int C, int f16) {
     extern __shared__ float w_s[];  // HCT == 0: [HC][C] folded weights then [HC] biases
     const int lane = threadIdx.x & 31, sub = lane >> 3, blk = lane & 7;
     if (HCT == 0) {
@@ -57,8 +57,9 @@ head_conv_kernel(const uint8_t* __restrict__ tower, const float* __restrict__ w,
             const Pack8 v = *reinterpret_cast<const Pack8*>(src + (size_t)it * 4 * row_bytes + (size_t)sl * 128);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const float2 f = __bfloat1622float2(v.v[j]);
-                a[it][2 * j] = f.x; a[it][2 * j + 1] = f.y;
+                // the tower's storage type: both conversions are exact
+                if (f16) ptx::unpack2<true>(v.v[j], a[it][2 * j], a[it][2 * j + 1]);
+                else ptx::unpack2<false>(v.v[j], a[it][2 * j], a[it][2 * j + 1]);
             }
         }
     };
@@ -264,23 +265,24 @@ value_out_kernel(const float* __restrict__ hidden, const float* __restrict__ w2,
 }  // namespace
 
 int launch_head_conv(const void* tower, const float* w, const float* bias, int HC, int pc,
-                     float* hp, float* hv, int B, int S, cudaStream_t st, int C) {
+                     float* hp, float* hv, int B, int S, cudaStream_t st, int C, int dtype) {
+    const int f16 = dtype == OB200_DTYPE_F16;
     if (C < 64 || C % 64) return set_error(OB200_ERR_INVALID, "head conv: tower channels %d not a multiple of 64", C);
     const long long total = (long long)B * (S + 1) * (S + 1);   // positions, one warp per 32
     const unsigned grid = (unsigned)((total + kHeadThreads - 1) / kHeadThreads);
     const uint8_t* t = static_cast<const uint8_t*>(tower);
     switch (HC) {
-        case 1: head_conv_kernel<1><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C); break;
-        case 2: head_conv_kernel<2><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C); break;
-        case 3: head_conv_kernel<3><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C); break;
-        case 4: head_conv_kernel<4><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C); break;
+        case 1: head_conv_kernel<1><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C, f16); break;
+        case 2: head_conv_kernel<2><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C, f16); break;
+        case 3: head_conv_kernel<3><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C, f16); break;
+        case 4: head_conv_kernel<4><<<grid, kHeadThreads, 0, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C, f16); break;
         default: {
             const size_t smem = (size_t)(HC * C + HC) * sizeof(float);
             if (smem > 200 * 1024)
                 return set_error(OB200_ERR_UNSUPPORTED, "head conv: %d head channels x %d tower channels exceed shared memory", HC, C);
             if (smem > 48 * 1024)
                 OB200_CUDA_OK(cudaFuncSetAttribute(head_conv_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            head_conv_kernel<0><<<grid, kHeadThreads, smem, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C);
+            head_conv_kernel<0><<<grid, kHeadThreads, smem, st>>>(t, w, bias, HC, pc, hp, hv, B, S, C, f16);
         }
     }
     OB200_LAUNCHED("head_conv_kernel");
@@ -338,7 +340,7 @@ static int value_head_scratch_ptr(float** out) {
 
 int launch_value_head_static(const void* tower, const float* vw, const float* vb, int vc, const float* W1T,
                              const float* b1, const float* w2, float b2, int H, int B, int S, float* value_out,
-                             cudaStream_t st) {
+                             cudaStream_t st, int dtype) {
     const size_t need = (size_t)B * ((size_t)vc * S * S + (size_t)H);
     if (need > kStaticScratchFloats)
         return set_error(OB200_ERR_TOO_LARGE,
@@ -349,7 +351,7 @@ int launch_value_head_static(const void* tower, const float* vw, const float* vb
     float* hv = scratch;                                  // [B][vc * S * S]
     float* hidden = scratch + (size_t)B * vc * S * S;     // [B][H]
     // every element read below is written first by the launch before it: nothing needs clearing
-    if (int rc = launch_head_conv(tower, vw, vb, vc, 0, hv, hv, B, S, st)) return rc;
+    if (int rc = launch_head_conv(tower, vw, vb, vc, 0, hv, hv, B, S, st, 64, dtype)) return rc;
     if (int rc = launch_fc(hv, W1T, b1, hidden, B, vc * S * S, H, 1, st)) return rc;
     return launch_value_out(hidden, w2, b2, H, B, value_out, st);
 }

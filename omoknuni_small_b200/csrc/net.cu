@@ -123,7 +123,7 @@ int add_conv(ob200_net* n, const std::string& conv, const std::string& bn, int c
     std::vector<float> scale, shift;
     if (int rc = bn_fold(n, bn, F, scale, shift)) return rc;
     std::vector<uint16_t> packed((size_t)9 * cin * F);
-    if (int rc = ob200_pack_conv3x3_weights(w->data(), scale.data(), F, cin_real, cin, packed.data())) return rc;
+    if (int rc = ob200_pack_conv3x3_weights_dt(w->data(), scale.data(), F, cin_real, cin, n->cfg.tower_dtype, packed.data())) return rc;
     uint16_t* dw = nullptr; float* db = nullptr;
     if (int rc = upload(n, &dw, packed)) return rc;
     if (int rc = upload(n, &db, shift)) return rc;
@@ -137,8 +137,8 @@ int tower_conv(ob200_net* n, const BoardTensorMap& in_map, int cin, const BoardT
     const ob200_net_config& c = n->cfg;
     if (n->wide)
         return launch_conv_wide_maps(in_map, out_map, res_map, n->conv_w[layer], n->conv_b[layer], B, c.board_size, cin,
-                                     c.filters, 9, 1, st);
-    return launch_conv3x3_maps(in_map, out_map, res_map, n->conv_w[layer], n->conv_b[layer], B, c.board_size, 1, st);
+                                     c.filters, 9, 1, st, nullptr, c.tower_dtype);
+    return launch_conv3x3_maps(in_map, out_map, res_map, n->conv_w[layer], n->conv_b[layer], B, c.board_size, 1, st, c.tower_dtype);
 }
 
 // Load map over a caller's input board tensor holding B boards.
@@ -184,6 +184,8 @@ int ob200_net_create(const ob200_net_config* cfg, ob200_net** out) {
                          cfg->input_channels, cfg->filters);
     if (cfg->policy_kind != OB200_POLICY_FC && cfg->policy_kind != OB200_POLICY_CONV_PLANES)
         return set_error(OB200_ERR_INVALID, "ob200_net_create: bad policy_kind %d", cfg->policy_kind);
+    if (cfg->tower_dtype != OB200_DTYPE_BF16 && cfg->tower_dtype != OB200_DTYPE_F16)
+        return set_error(OB200_ERR_INVALID, "ob200_net_create: bad tower_dtype %d", cfg->tower_dtype);
     if (cfg->policy_kind == OB200_POLICY_CONV_PLANES) {
         if (cfg->filters == 64)
             return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_create: the convolutional policy head needs filters 128 or 256");
@@ -271,7 +273,7 @@ int ob200_net_finalize(ob200_net* n) {
         std::copy(cw->begin(), cw->end(), wpad.begin());
         std::copy(cb->begin(), cb->end(), bpad.begin());
         std::vector<uint16_t> packed(conv_wide_packed_bytes(F, n->pol_cout, 1) / 2);
-        if (int rc = conv_wide_pack(wpad.data(), nullptr, n->pol_cout, F, F, 1, packed.data())) return rc;
+        if (int rc = conv_wide_pack(wpad.data(), nullptr, n->pol_cout, F, F, 1, packed.data(), c.tower_dtype)) return rc;
         uint16_t* dw = nullptr;
         if (int rc = upload(n, &dw, packed)) return rc;
         n->pol_w = dw;
@@ -404,7 +406,7 @@ int tower_device(ob200_net* n, const void* input_bt, int B, int* out_buf, cudaSt
         const bool with_heads = heads_done && c.policy_kind != OB200_POLICY_CONV_PLANES && hc <= tower_resident_head_channels_max();
         const int rc = launch_conv_tower_resident(own_input ? n->in_map_board : board_map, n->out_map_board, n->resident_layers,
                                                   1 + 2 * c.blocks, B, S, st, n->head_w, n->head_b, with_heads ? hc : 0,
-                                                  with_heads ? c.policy_head_ch : 0, n->hp, n->hv);
+                                                  with_heads ? c.policy_head_ch : 0, n->hp, n->hv, c.tower_dtype);
         if (rc == OB200_OK) { done = true; x = 0; n->tower_path = 2; if (heads_done) *heads_done = with_heads; }
         else if (rc == OB200_ERR_UNSUPPORTED) n->resident = false;
         else return rc;
@@ -429,7 +431,7 @@ int tower_device(ob200_net* n, const void* input_bt, int B, int* out_buf, cudaSt
     if (!done && n->fused && capturing == cudaStreamCaptureStatusNone && (n->fused_forced || (l2_resident && enough_tiles))) {
         if (++n->fused_epoch == 0) ++n->fused_epoch;   // flags start at zero: epoch 0 is never used
         const int rc = launch_conv_tower(in_map, n->fused_layers, 1 + 2 * c.blocks, n->fused_flags, n->fused_pitch,
-                                         n->fused_done, n->fused_epoch, B, S, st);
+                                         n->fused_done, n->fused_epoch, B, S, st, c.tower_dtype);
         if (rc == OB200_OK) { done = true; x = n->fused_final; n->tower_path = 1; }
         else if (rc == OB200_ERR_UNSUPPORTED) n->fused = false;   // not launchable here: layer by layer from now on
         else return rc;
@@ -459,14 +461,14 @@ int forward_device(ob200_net* n, const void* input_bt, int B, float* policy_out,
     const int S2 = S * S, pc = c.policy_head_ch, vc = c.value_head_ch;
     if (c.policy_kind == OB200_POLICY_CONV_PLANES) {
         if (int rc = launch_conv_wide_maps(n->act_load[x], n->act_load[x], nullptr, n->pol_w, n->pol_b, B, S, F, n->pol_cout, 1, 0,
-                                           st, n->pol_planes)) return rc;
+                                           st, n->pol_planes, c.tower_dtype)) return rc;
         const long long total = (long long)B * pc * S2;
         policy_planes_gather_kernel<<<(unsigned)std::min<long long>((total + 255) / 256, 148 * 16), 256, 0, st>>>(
             n->pol_planes, n->pol_cout, pc, B, S, policy_out);
         OB200_LAUNCHED("policy_planes_gather_kernel");
-        if (int rc = launch_head_conv(n->act[x], n->head_w, n->head_b, vc, 0, n->hv, n->hv, B, S, st, F)) return rc;
+        if (int rc = launch_head_conv(n->act[x], n->head_w, n->head_b, vc, 0, n->hv, n->hv, B, S, st, F, c.tower_dtype)) return rc;
     } else if (!heads_done) {
-        if (int rc = launch_head_conv(n->act[x], n->head_w, n->head_b, pc + vc, pc, n->hp, n->hv, B, S, st, F)) return rc;
+        if (int rc = launch_head_conv(n->act[x], n->head_w, n->head_b, pc + vc, pc, n->hp, n->hv, B, S, st, F, c.tower_dtype)) return rc;
     }
     // the two heads are independent from here on: the value head (FC + FC/tanh) runs on a second
     // stream beside the policy head (FC + softmax) and joins `st` again at the end
@@ -564,7 +566,7 @@ int ob200_net_infer_planes(ob200_net* n, const float* planes, int32_t B, int32_t
     for (int b = 0; b < B; ++b)
         std::memcpy(n->h_planes + (size_t)b * used * S2, planes + (size_t)b * C * S2, (size_t)used * S2 * sizeof(float));
     OB200_CUDA_OK(cudaMemcpyAsync(n->d_planes, n->h_planes, (size_t)B * used * S2 * sizeof(float), cudaMemcpyHostToDevice, n->stream));
-    if (int rc = launch_planes_to_board_tensor(n->d_planes, B, used, c.board_size, n->cin_pad, n->act_in, n->stream)) return rc;
+    if (int rc = launch_planes_to_board_tensor(n->d_planes, B, used, c.board_size, n->cin_pad, n->act_in, n->stream, c.tower_dtype)) return rc;
     if (int rc = forward_device(n, n->act_in, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
     return finish_host_call(n, B, policy_out, value_out);
 }
@@ -587,7 +589,7 @@ int ob200_net_infer_gomoku(ob200_net* n, const int16_t* history, const uint8_t* 
     std::memcpy(h8 + hist_bytes + B, to_move, (size_t)B);
     OB200_CUDA_OK(cudaMemcpyAsync(d8, h8, hist_bytes + 2 * (size_t)B, cudaMemcpyHostToDevice, n->stream));
     if (int rc = launch_encode_gomoku(n->d_hist, d8 + hist_bytes, d8 + hist_bytes + B, B, c.board_size, c.input_channels, n->cin_pad,
-                                      n->act_in, n->stream)) return rc;
+                                      n->act_in, n->stream, c.tower_dtype)) return rc;
     if (int rc = forward_device(n, n->act_in, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
     return finish_host_call(n, B, policy_out, value_out);
 }
@@ -620,14 +622,18 @@ int ob200_net_value_head_noalloc(ob200_net* n, const void* tower_board_tensor, i
         return set_error(OB200_ERR_INVALID, "ob200_net_value_head_noalloc: null argument");
     if (!n->finalized) return set_error(OB200_ERR_STATE, "ob200_net_value_head_noalloc: weights not finalised");
     if (B < 1) return set_error(OB200_ERR_INVALID, "ob200_net_value_head_noalloc: batch %d", B);
-    if (int rc = require_device()) return rc;
+    // like every other call on a handle: one call at a time, on the handle's own device (the scratch array
+    // is looked up per device, and the weights live on this one)
+    std::lock_guard<std::mutex> lk(n->mu);
     const ob200_net_config& c = n->cfg;
+    OB200_CUDA_OK(cudaSetDevice(c.device));
+    if (int rc = require_device()) return rc;
     const int pc = c.policy_kind == OB200_POLICY_CONV_PLANES ? 0 : c.policy_head_ch;
     if (c.filters != 64)
         return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_value_head_noalloc: covers towers of 64 filters");
     return launch_value_head_static(tower_board_tensor, n->head_w + (size_t)pc * c.filters, n->head_b + pc,
                                     c.value_head_ch, n->W1T, n->b1, n->w2, n->b2, c.value_hidden, B, c.board_size,
-                                    value_out, as_stream(stream));
+                                    value_out, as_stream(stream), c.tower_dtype);
 }
 
 int64_t ob200_value_head_noalloc_capacity(void) { return (int64_t)value_head_static_capacity(); }

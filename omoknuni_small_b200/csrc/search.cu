@@ -400,7 +400,7 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
     // ---- roots: create, evaluate, priors (+ noise) ----
     init_roots_kernel<<<T, 128, 0, st>>>(s->tv, s->root_stones, T, s->n_used, s->term_count);
     OB200_LAUNCHED("init_roots_kernel");
-    if (int rc = launch_encode_gomoku(s->root_hist, s->root_nh, s->root_tm, T, S, nc->input_channels, 64, s->input_bt, st)) return rc;
+    if (int rc = launch_encode_gomoku(s->root_hist, s->root_nh, s->root_tm, T, S, nc->input_channels, 64, s->input_bt, st, nc->tower_dtype)) return rc;
     if (int rc = net_forward_for_search(s->net, s->input_bt, T, s->policy, s->value, st)) return rc;
     if (int rc = ob200_launch_set_priors(&s->tv, s->roots, T, s->policy, A, nullptr, st)) return rc;
     if (c.dirichlet_epsilon > 0.0f) {
@@ -417,7 +417,7 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
                                                             s->root_count, s->leaf_hist, s->leaf_nh, s->leaf_tm,
                                                             s->term_value, s->term_count);
         OB200_LAUNCHED("leaf_prepare_kernel");
-        if (int rc = launch_encode_gomoku(s->leaf_hist, s->leaf_nh, s->leaf_tm, L, S, nc->input_channels, 64, s->input_bt, st)) return rc;
+        if (int rc = launch_encode_gomoku(s->leaf_hist, s->leaf_nh, s->leaf_tm, L, S, nc->input_channels, 64, s->input_bt, st, nc->tower_dtype)) return rc;
         if (int rc = net_forward_for_search(s->net, s->input_bt, L, s->policy, s->value, st)) return rc;
         expand_kernel<<<(L * 32 + 255) / 256, 256, 0, st>>>(s->tv, s->paths, s->path_len, L, c.max_depth, s->policy, A,
                                                            s->value, s->term_value, (float)c.value_sign, s->max_nodes,

@@ -24,8 +24,7 @@
 // Every wait on an mbarrier is bounded; when one runs out the CTA raises the
 // device error word, leaves its loops, frees its TMEM and returns.
 #include "internal.h"
-#include <cuda.h>
-#include <cuda_bf16.h>
+#include "sm100_ptx.cuh"
 #include <cstdlib>
 #include <cstring>
 #include <vector>
@@ -49,7 +48,6 @@ constexpr int kChPerThread = kC / (kEpiWarps / 4);   // channels one epilogue th
 constexpr int kThreads = 64 + 32 * kEpiWarps * kEpiGroups;
 constexpr int kNumBars = 2 * kStages + 2 * kAccStages + 1 + kEpiGroups;
 constexpr int kSmemBytes = kWBytes + kStages * kStageBytes + kEpiGroups * kOutBytes + kNumBars * 8 + kC * 4 + 16 + 1024;
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct ConvParams {
     const uint8_t* w;         // packed, pre-swizzled weights
@@ -63,86 +61,23 @@ struct ConvParams {
     int relu;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if ((i & 255) == 255 && *abort_flag) return false;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
-}
-
-// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes,
-// 8-row groups 1024 bytes apart (stride byte offset); the leading byte offset is
-// not used by swizzled K-major layouts and is encoded as 1.  The swizzle is a
-// function of the shared-memory address itself (16-byte chunk index XOR address
-// bits 7-9), so a descriptor may start at any 128-byte row of a tile that TMA
-// wrote with the same swizzle; the base-offset field stays 0 (measured: a
-// non-zero base offset on a row-shifted start gives wrong products).
-// Split in two words so that the issuing thread only adds to the low one.
-constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
-// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128, N = 64.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kC >> 3) << 17) |
-                            ((uint32_t)(kTileM >> 4) << 24);
-
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
-        "mov.b64 da, {%1, %3};\nmov.b64 db, {%2, %3};\n"
-        "setp.ne.b32 p, %5, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}"
-        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(kIdesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
+using namespace ptx;
 __device__ __forceinline__ void group_bar(int id) {   // the threads of one epilogue group
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(32 * kEpiWarps) : "memory");
 }
+// Barrier of one epilogue group that also tells every thread whether any of them reports `bad`:
+// the group gives up on a wait as a whole, so no thread is ever left at a barrier its siblings
+// have walked away from.
+__device__ __forceinline__ bool group_any(int id, bool bad) {
+    uint32_t r;
+    asm volatile(
+        "{\n.reg .pred p, q;\nsetp.ne.b32 q, %2, 0;\nbar.red.or.pred p, %1, %3, q;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(r) : "r"(id), "r"((uint32_t)bad), "r"(32 * kEpiWarps) : "memory");
+    return r != 0;
+}
 
+// F16: activations and weights are fp16 instead of bf16.
+template <bool F16>
 __global__ void __launch_bounds__(kThreads, 1)
 conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
                const __grid_constant__ CUtensorMap res_map, const ConvParams p) {
@@ -158,6 +93,7 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t kIdesc = make_idesc(F16, kTileM, kC);
     const uint32_t bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
@@ -239,7 +175,7 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
 #pragma unroll
                     for (int ks = 0; ks < kC / 16; ++ks)
                         umma(d_tmem, a_lo + (uint32_t)(tap_off[tap] + ks * 2),
-                             w_lo + (uint32_t)(tap * (kC * kRowBytes >> 4) + ks * 2), (tap | ks) ? 1u : 0u);
+                             w_lo + (uint32_t)(tap * (kC * kRowBytes >> 4) + ks * 2), kIdesc, (tap | ks) ? 1u : 0u);
                 }
                 umma_commit(empty_bar(s));      // smem stage free once these MMAs have read it
                 umma_commit(accfull_bar(a));    // accumulator ready for the epilogue
@@ -285,9 +221,14 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
                     tma_load_2d(stage_out_u32, &res_map, 0, OB200_GUARD + tile * kTileM, res_bar(group));
                 }
             }
-            if (!mbar_wait(accfull_bar(a), pa, abort_flag)) {
+            // Both waits of the tile first, then one vote of the whole group on their outcome (which is also
+            // the barrier behind the leader's wait above: the staging tile is free).
+            bool good = mbar_wait(accfull_bar(a), pa, abort_flag);
+            if (good && has_res) good = mbar_wait(res_bar(group), res_phase, abort_flag);
+            if (group_any(1 + 2 * group, !good)) {
                 *abort_flag = 1; atomicExch(p.error, 3); break;
             }
+            if (has_res) res_phase ^= 1u;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t r[kChPerThread];
 #pragma unroll
@@ -297,15 +238,6 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(accempty_bar(a));
-
-            if (has_res) {
-                if (!mbar_wait(res_bar(group), res_phase, abort_flag)) {
-                    *abort_flag = 1; atomicExch(p.error, 5); break;
-                }
-                res_phase ^= 1u;
-            } else {
-                group_bar(1 + 2 * group);   // after the leader's wait above: the staging tile is free
-            }
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) {
                 // 128-byte swizzle of the staging tile: 16-byte chunk k of row r sits at chunk k ^ (r % 8)
@@ -317,12 +249,12 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
                     uint32_t ow[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        // bf16 -> fp32 is a 16-bit shift
-                        float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bias_t[c * 8 + 2 * j] + __uint_as_float(rw[j] << 16);
-                        float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bias_t[c * 8 + 2 * j + 1] + __uint_as_float(rw[j] & 0xFFFF0000u);
+                        float r0, r1;
+                        unpack2<F16>(rw[j], r0, r1);      // an absent residual reads as +0 in either type
+                        float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bias_t[c * 8 + 2 * j] + r0;
+                        float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bias_t[c * 8 + 2 * j + 1] + r1;
                         if (p.relu) { v0 = fmaxf(v0, 0.0f); v1 = fmaxf(v1, 0.0f); }
-                        const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
-                        ow[j] = *reinterpret_cast<const uint32_t*>(&h2);
+                        ow[j] = pack2<F16>(v0, v1);
                     }
                     o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                 }
@@ -348,14 +280,6 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
     }
-}
-
-inline uint16_t f32_to_bf16_rne(float f) {
-    uint32_t u;
-    std::memcpy(&u, &f, 4);
-    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40);  // NaN
-    u += 0x7FFFu + ((u >> 16) & 1u);
-    return (uint16_t)(u >> 16);
 }
 
 }  // namespace
@@ -411,18 +335,20 @@ int make_board_tensor_map(const void* base, long long rows, int box_rows, BoardT
 int conv_halo_rows(int S) { return S + 2; }   // |dy*(S+1)+dx| <= S+2 rows before / after a tile
 
 int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const BoardTensorMap* res_map,
-                        const void* packed_w, const float* bias, int B, int S, int relu, cudaStream_t st) {
+                        const void* packed_w, const float* bias, int B, int S, int relu, cudaStream_t st, int dtype) {
     if (!packed_w || !bias || B <= 0) return set_error(OB200_ERR_INVALID, "conv3x3: null pointer or empty batch");
+    if (dtype != OB200_DTYPE_BF16 && dtype != OB200_DTYPE_F16) return set_error(OB200_ERR_INVALID, "conv3x3: bad dtype %d", dtype);
     if (S < 1 || conv_halo_rows(S) > kHaloMax)
         return set_error(OB200_ERR_UNSUPPORTED, "conv3x3: board_size %d outside [1, %d]", S, kHaloMax - 2);
     if ((uintptr_t)packed_w & 15) return set_error(OB200_ERR_INVALID, "conv3x3: weights must be 16-byte aligned");
     if (int rc = require_device()) return rc;
-    static bool configured[64] = {false};
+    static bool configured[64][2] = {{false, false}};
     int dev = 0;
     OB200_CUDA_OK(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        OB200_CUDA_OK(cudaFuncSetAttribute(conv3x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        configured[dev] = true;
+    auto kernel = dtype == OB200_DTYPE_F16 ? conv3x3_kernel<true> : conv3x3_kernel<false>;
+    if (dev < 0 || dev >= 64 || !configured[dev][dtype]) {
+        OB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        if (dev >= 0 && dev < 64) configured[dev][dtype] = true;
     }
     int sms = 0;
     OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -440,7 +366,7 @@ int launch_conv3x3_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv3x3_kernel, *reinterpret_cast<const CUtensorMap*>(&in_map),
+    OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, *reinterpret_cast<const CUtensorMap*>(&in_map),
                                      *reinterpret_cast<const CUtensorMap*>(&out_map),
                                      *reinterpret_cast<const CUtensorMap*>(res_map ? res_map : &out_map), p));
     OB200_LAUNCHED("conv3x3_kernel");
@@ -456,7 +382,14 @@ extern "C" {
 int ob200_launch_conv3x3(const void* in, const void* packed_w, const float* bias, const void* residual,
                          void* out, int32_t B, int32_t board_size, int32_t cin, int32_t cout, int32_t relu,
                          ob200_stream stream) {
+    return ob200_launch_conv3x3_dt(in, packed_w, bias, residual, out, B, board_size, cin, cout, relu, OB200_DTYPE_BF16, stream);
+}
+
+int ob200_launch_conv3x3_dt(const void* in, const void* packed_w, const float* bias, const void* residual,
+                            void* out, int32_t B, int32_t board_size, int32_t cin, int32_t cout, int32_t relu,
+                            int32_t dtype, ob200_stream stream) {
     if (!in || !out || B <= 0) return set_error(OB200_ERR_INVALID, "ob200_launch_conv3x3: null pointer or empty batch");
+    if (dtype != OB200_DTYPE_BF16 && dtype != OB200_DTYPE_F16) return set_error(OB200_ERR_INVALID, "ob200_launch_conv3x3: bad dtype %d", dtype);
     if (conv_wide_covers(cin, cout)) {
         if (board_size < 1 || conv_halo_rows(board_size) > kHaloMax)
             return set_error(OB200_ERR_UNSUPPORTED, "ob200_launch_conv3x3: board_size %d outside [1, %d]", board_size, kHaloMax - 2);
@@ -468,7 +401,7 @@ int ob200_launch_conv3x3(const void* in, const void* packed_w, const float* bias
         if (residual)
             if (int rc = make_board_tensor_map(residual, gw.PT, kTileM, &wrm, cout)) return rc;
         return launch_conv_wide_maps(wim, wom, residual ? &wrm : nullptr, packed_w, bias, B, board_size, cin, cout, 9, relu,
-                                     as_stream(stream));
+                                     as_stream(stream), nullptr, dtype);
     }
     if (cin != kC || cout != kC)
         return set_error(OB200_ERR_UNSUPPORTED,
@@ -482,7 +415,7 @@ int ob200_launch_conv3x3(const void* in, const void* packed_w, const float* bias
     BoardTensorMap rm;
     if (residual)
         if (int rc = make_board_tensor_map(residual, g.PT, kTileM, &rm)) return rc;
-    return launch_conv3x3_maps(im, om, residual ? &rm : nullptr, packed_w, bias, B, board_size, relu, as_stream(stream));
+    return launch_conv3x3_maps(im, om, residual ? &rm : nullptr, packed_w, bias, B, board_size, relu, as_stream(stream), dtype);
 }
 
 int64_t ob200_packed_conv3x3_bytes(int32_t cin, int32_t cout) {
@@ -491,13 +424,20 @@ int64_t ob200_packed_conv3x3_bytes(int32_t cin, int32_t cout) {
     return (int64_t)kWBytes;
 }
 
-// Packed image: [tap = ky*3+kx][cout][cin] bf16, one 128-byte row per output channel and
+// Packed image: [tap = ky*3+kx][cout][cin] bf16 (or fp16), one 128-byte row per output channel and
 // tap, its 16-byte chunks (8 input channels) permuted by the 128-byte swizzle
 // (chunk j of row r stored at chunk j ^ (r % 8)) — the K-major shared-memory operand
 // layout of the tensor core, ready for a plain bulk copy.
 int ob200_pack_conv3x3_weights(const float* w_oihw, const float* scale, int32_t cout, int32_t cin_real,
                                int32_t cin, void* packed_out) {
-    if (conv_wide_covers(cin, cout)) return conv_wide_pack(w_oihw, scale, cout, cin_real, cin, 9, packed_out);
+    return ob200_pack_conv3x3_weights_dt(w_oihw, scale, cout, cin_real, cin, OB200_DTYPE_BF16, packed_out);
+}
+
+int ob200_pack_conv3x3_weights_dt(const float* w_oihw, const float* scale, int32_t cout, int32_t cin_real,
+                                  int32_t cin, int32_t dtype, void* packed_out) {
+    if (dtype != OB200_DTYPE_BF16 && dtype != OB200_DTYPE_F16)
+        return set_error(OB200_ERR_INVALID, "ob200_pack_conv3x3_weights: bad dtype %d", dtype);
+    if (conv_wide_covers(cin, cout)) return conv_wide_pack(w_oihw, scale, cout, cin_real, cin, 9, packed_out, dtype);
     if (!w_oihw || !packed_out || cout != kC || cin != kC || cin_real <= 0 || cin_real > cin)
         return set_error(OB200_ERR_INVALID, "ob200_pack_conv3x3_weights: covered shapes are 64 -> 64 and {64,128,192,256} -> {128,256}; got cout %d, cin_real %d, cin %d",
                          cout, cin_real, cin);
@@ -508,7 +448,7 @@ int ob200_pack_conv3x3_weights(const float* w_oihw, const float* scale, int32_t 
                 float v = 0.0f;
                 if (ci < cin_real) v = w_oihw[((size_t)co * cin_real + ci) * 9 + tap] * (scale ? scale[co] : 1.0f);
                 const size_t byte = (size_t)tap * kC * kRowBytes + (size_t)co * kRowBytes + ((((ci >> 3) ^ (co & 7))) << 4) + (ci & 7) * 2;
-                o[byte / 2] = f32_to_bf16_rne(v);
+                o[byte / 2] = dtype == OB200_DTYPE_F16 ? f32_to_f16_rne_sat(v) : f32_to_bf16_rne(v);
             }
     return OB200_OK;
 }

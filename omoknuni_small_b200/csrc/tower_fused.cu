@@ -32,8 +32,7 @@
 // error word and stops publishing, which makes its neighbours give up in turn.
 #include "internal.h"
 #include <cooperative_groups.h>
-#include <cuda.h>
-#include <cuda_bf16.h>
+#include "sm100_ptx.cuh"
 
 namespace ob200 {
 namespace {
@@ -50,7 +49,6 @@ constexpr int kEpiGroups = 2;
 constexpr int kEpiWarps = 4;
 constexpr int kThreads = 96 + 32 * kEpiWarps * kEpiGroups + 32 * kEpiGroups;   // warps: 0 loads, 1 MMA, 2 weights, 3-10 epilogue, 11-12 store / publish
 constexpr int kNumBars = 2 * kStages + 2 * kAccStages + 4 + 2 * kEpiGroups;
-constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr uint32_t kFlagSpin = 1u << 20;
 
 struct alignas(128) TowerLayerDev {
@@ -76,30 +74,7 @@ struct TowerParams {
     int stage_bytes;          // (128 + 2 * halo) rows, rounded up to 1024
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if ((i & 255) == 255 && *abort_flag) return false;
-    }
-    return false;
-}
+using namespace ptx;
 // The halo flags of a tile (f[0..2]) and of the CTA's next tile (f[3..5]) in one poll: relaxed
 // loads in flight together (plus the layer's count of published tiles), one acquire fence when
 // the first three are up.  *next_ok tells whether the next tile's three were up as well.
@@ -123,46 +98,11 @@ __device__ __forceinline__ bool flags_wait(const int* const (&f)[6], const int* 
     }
     return false;
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
-}
-constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kC >> 3) << 17) |
-                            ((uint32_t)(kTileM >> 4) << 24);
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
-        "mov.b64 da, {%1, %3};\nmov.b64 db, {%2, %3};\n"
-        "setp.ne.b32 p, %5, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}"
-        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(kIdesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
+// F16: activations and weights are fp16 instead of bf16.
+template <bool F16>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tower_kernel(const __grid_constant__ CUtensorMap stem_in_map, const TowerParams p) {
+    constexpr uint32_t kIdesc = make_idesc(F16, kTileM, kC);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* w_s = smem;                                   // two weight buffers
@@ -278,7 +218,7 @@ conv_tower_kernel(const __grid_constant__ CUtensorMap stem_in_map, const TowerPa
 #pragma unroll
                         for (int ks = 0; ks < kC / 16; ++ks)
                             umma(d_tmem, a_lo + (uint32_t)(tap_off[tap] + ks * 2),
-                                 w_lo + (uint32_t)(tap * (kC * kRowBytes >> 4) + ks * 2), (tap | ks) ? 1u : 0u);
+                                 w_lo + (uint32_t)(tap * (kC * kRowBytes >> 4) + ks * 2), kIdesc, (tap | ks) ? 1u : 0u);
                     }
                     umma_commit(empty_bar(s));
                     umma_commit(accfull_bar(a));
@@ -317,7 +257,8 @@ conv_tower_kernel(const __grid_constant__ CUtensorMap stem_in_map, const TowerPa
                     const int rr = pos % p.slots;
                     valid = (rr / p.GP < p.S) && (rr % p.GP < p.S);
                 }
-                if (!mbar_wait(accfull_bar(a), pa, abort_flag)) { ok = false; break; }
+                // a warp gives up as a whole (the TMEM loads below need all 32 lanes)
+                if (!__all_sync(0xffffffffu, mbar_wait(accfull_bar(a), pa, abort_flag))) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 uint32_t r[kC];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * kC), r);
@@ -326,7 +267,7 @@ conv_tower_kernel(const __grid_constant__ CUtensorMap stem_in_map, const TowerPa
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(accempty_bar(a));
-                if (!mbar_wait(ready_bar(group), ready_phase, abort_flag)) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(ready_bar(group), ready_phase, abort_flag))) { ok = false; break; }
                 ready_phase ^= 1u;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
@@ -339,11 +280,12 @@ conv_tower_kernel(const __grid_constant__ CUtensorMap stem_in_map, const TowerPa
                         uint32_t ow[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bias_t[c * 8 + 2 * j] + __uint_as_float(rw[j] << 16);
-                            float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bias_t[c * 8 + 2 * j + 1] + __uint_as_float(rw[j] & 0xFFFF0000u);
+                            float r0, r1;
+                            unpack2<F16>(rw[j], r0, r1);
+                            float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bias_t[c * 8 + 2 * j] + r0;
+                            float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bias_t[c * 8 + 2 * j + 1] + r1;
                             v0 = fmaxf(v0, 0.0f); v1 = fmaxf(v1, 0.0f);
-                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
-                            ow[j] = *reinterpret_cast<const uint32_t*>(&h2);
+                            ow[j] = pack2<F16>(v0, v1);
                         }
                         o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                     }
@@ -457,7 +399,7 @@ size_t tower_fused_smem_bytes(int S, int n_layers) {
 // n_layers x tiles_pitch ints that only ever hold earlier epochs; done: n_layers ints (zeroed here).  Returns OB200_ERR_UNSUPPORTED
 // when the cooperative launch is not possible (the caller then runs layer by layer).
 int launch_conv_tower(const BoardTensorMap& stem_in_map, const void* layers_dev, int n_layers, int* flags, int tiles_pitch,
-                      int* done, int epoch, int B, int S, cudaStream_t st) {
+                      int* done, int epoch, int B, int S, cudaStream_t st, int dtype) {
     if (!layers_dev || !flags || !done || n_layers < 1 || B <= 0) return set_error(OB200_ERR_INVALID, "conv tower: bad arguments");
     const size_t smem = tower_fused_smem_bytes(S, n_layers);
     if (!smem) return set_error(OB200_ERR_UNSUPPORTED, "conv tower: board size %d / %d layers do not fit shared memory", S, n_layers);
@@ -467,10 +409,12 @@ int launch_conv_tower(const BoardTensorMap& stem_in_map, const void* layers_dev,
     OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     OB200_CUDA_OK(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
     if (!coop) return set_error(OB200_ERR_UNSUPPORTED, "conv tower: the device does not support cooperative launches");
-    static size_t configured[64] = {0};
-    if (dev >= 0 && dev < 64 && configured[dev] < smem) {
-        OB200_CUDA_OK(cudaFuncSetAttribute(conv_tower_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured[dev] = smem;
+    const bool f16 = dtype == OB200_DTYPE_F16;
+    auto kernel = f16 ? conv_tower_kernel<true> : conv_tower_kernel<false>;
+    static size_t configured[64][2] = {{0, 0}};
+    if (dev >= 0 && dev < 64 && configured[dev][f16] < smem) {
+        OB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[dev][f16] = smem;
     }
     const BoardGeom g = board_geom(S, B);
     TowerParams p;
@@ -482,13 +426,13 @@ int launch_conv_tower(const BoardTensorMap& stem_in_map, const void* layers_dev,
     if (p.num_tiles > tiles_pitch) return set_error(OB200_ERR_TOO_LARGE, "conv tower: %d tiles exceed the flag pitch %d", p.num_tiles, tiles_pitch);
     const int grid = p.num_tiles < sms ? p.num_tiles : sms;
     int per_sm = 0;
-    OB200_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, conv_tower_kernel, kThreads, smem));
+    OB200_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem));
     if (per_sm < 1 || grid > per_sm * sms)
         return set_error(OB200_ERR_UNSUPPORTED, "conv tower: %d CTAs cannot all be resident", grid);
     OB200_CUDA_OK(cudaMemsetAsync(done, 0, (size_t)n_layers * sizeof(int), st));
     CUtensorMap stem = *reinterpret_cast<const CUtensorMap*>(&stem_in_map);
     void* args[] = {&stem, &p};
-    OB200_CUDA_OK(cudaLaunchCooperativeKernel((const void*)conv_tower_kernel, dim3(grid), dim3(kThreads), args, smem, st));
+    OB200_CUDA_OK(cudaLaunchCooperativeKernel((const void*)kernel, dim3(grid), dim3(kThreads), args, smem, st));
     OB200_LAUNCHED("conv_tower_kernel");
     return OB200_OK;
 }

@@ -31,8 +31,7 @@
 // where a launch per layer takes 432 / 1,650 us; 74-79 us for 1 to 148 boards
 // (single-issuer variant; 93-140 us as a launch per layer).
 #include "internal.h"
-#include <cuda.h>
-#include <cuda_bf16.h>
+#include "sm100_ptx.cuh"
 #include <cstring>
 
 namespace ob200 {
@@ -53,7 +52,6 @@ constexpr int kStaggerTap = 6;                       // board 1 starts a layer w
 constexpr int kWGroups = 3;                          // the weight ring is handed over in groups of three taps
 constexpr int kWGroupBytes = 3 * kTapBytes;          // 24,576
 constexpr int kNumBars = 2 + 2 + 2 + kWGroups + kWGroups + 2 + 2 + 1;
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct alignas(32) ResidentLayer {
     const uint8_t* w;         // packed weights (ob200_pack_conv3x3_weights): 9 taps x 8 KB
@@ -78,78 +76,11 @@ struct ResidentParams {
     float* hv;                // [B][head_ch - head_pc][S*S]
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if ((i & 255) == 255 && *abort_flag) return false;
-    }
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
-}
-constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kC >> 3) << 17) |
-                            ((uint32_t)(kTileM >> 4) << 24);
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
-        "mov.b64 da, {%1, %3};\nmov.b64 db, {%2, %3};\n"
-        "setp.ne.b32 p, %5, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}"
-        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(kIdesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
+using namespace ptx;
 
-// relu(v) rounded to bf16, two at a time (lo in the low half)
-__device__ __forceinline__ uint32_t relu_bf16x2(float lo, float hi) {
-    uint32_t d;
-    asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-    return d;
-}
 // One 128-byte row of a layer's output: relu(accumulator + bias [+ residual, which is the row's old content]).
 // 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8).
-template <bool RES>
+template <bool RES, bool F16>
 __device__ __forceinline__ void store_row(uint8_t* dst_row, int row, const uint32_t* r, const float* bias_t) {
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
@@ -163,15 +94,16 @@ __device__ __forceinline__ void store_row(uint8_t* dst_row, int row, const uint3
         for (int j = 0; j < 4; ++j) {
             float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bb[2 * j];
             float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bb[2 * j + 1];
-            if (RES) { v0 += __uint_as_float(rw[j] << 16); v1 += __uint_as_float(rw[j] & 0xFFFF0000u); }
-            ow[j] = relu_bf16x2(v0, v1);
+            if (RES) { float r0, r1; unpack2<F16>(rw[j], r0, r1); v0 += r0; v1 += r1; }
+            ow[j] = pack2_relu<F16>(v0, v1);
         }
         *slot = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
-// The heads' 1x1 convolutions for one position, from the row just written (bf16, as the head kernel would
+// The heads' 1x1 convolutions for one position, from the row just written (16-bit, as the head kernel would
 // read it from the tower's output tensor).  Same order of additions as head_conv_kernel: eight partial sums
 // over eight consecutive channels each, added as ((0+1)+(2+3))+((4+5)+(6+7)), then the bias, then ReLU.
+template <bool F16>
 __device__ __noinline__ void head_row(const uint8_t* row_ptr, int row, const float* head_s, int head_ch, int head_pc,
                                       int board, int S, int GP, float* hp, float* hv) {
     float a[kC];
@@ -181,8 +113,7 @@ __device__ __noinline__ void head_row(const uint8_t* row_ptr, int row, const flo
         const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            a[c * 8 + 2 * j] = __uint_as_float(w4[j] << 16);
-            a[c * 8 + 2 * j + 1] = __uint_as_float(w4[j] & 0xFFFF0000u);
+            unpack2<F16>(w4[j], a[c * 8 + 2 * j], a[c * 8 + 2 * j + 1]);
         }
     }
     const int y = row / GP, x = row - y * GP, S2 = S * S, cell = y * S + x;
@@ -207,40 +138,13 @@ __device__ __forceinline__ void store_zero_row(uint8_t* dst_row) {
     for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(dst_row)[c] = make_uint4(0u, 0u, 0u, 0u);
 }
 
-// The MMAs of one board and layer: 9 taps x T tiles x 4 k-steps, tap-outer so that a block of three taps
-// is handed back to the loader as early as possible.  ALONE: the round has a single board, whose issuer
-// hands the weight blocks back twice (the loader counts two boards).  SIGNAL: board 0 of a pair tells
-// board 1's issuer when it has issued tap kStaggerTap.  Everything that can be is a compile-time fact:
-// every instruction between two MMAs costs the issuing thread time.
-template <int T, bool ALONE, bool SIGNAL>
-__device__ __forceinline__ bool issue_board_layer(uint32_t d_tmem, uint32_t a_lo, uint32_t w_lo, const int (&tap_off)[9],
-                                                  uint32_t w_full0, uint32_t w_empty0, uint32_t stagger, uint32_t parity,
-                                                  volatile int* abort_flag) {
-#pragma unroll
-    for (int tap = 0; tap < 9; ++tap) {
-        if (tap % 3 == 0 && !mbar_wait(w_full0 + 8u * (tap / 3), parity, abort_flag)) return false;
-#pragma unroll
-        for (int tile = 0; tile < T; ++tile) {
-#pragma unroll
-            for (int ks = 0; ks < kC / 16; ++ks)
-                umma(d_tmem + (uint32_t)(tile * kC), a_lo + (uint32_t)(tile * (kTileM * kRowBytes >> 4) + tap_off[tap] + ks * 2),
-                     w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), (tap | ks) ? 1u : 0u);
-        }
-        if (tap % 3 == 2) {
-            umma_commit(w_empty0 + 8u * (tap / 3));
-            if (ALONE) umma_commit(w_empty0 + 8u * (tap / 3));
-        }
-        if (SIGNAL && tap == kStaggerTap) mbar_arrive(stagger);
-    }
-    return true;
-}
-
 // T: 128-row tiles per board (1 for boards up to 10x10, 2 up to 15x15).
 // PAIR: CTAs take their boards two at a time, with one MMA issuer per board (the general case).  When no CTA
 // has more than one board (batches up to the SM count) the second issuer's bookkeeping - the stagger signal, the
 // second hand-over of every weight block - is pure cost in the one thread everything waits for (84 us instead
 // of 78 us for the 21 layers); !PAIR is the same kernel with a single issuer (warp 0; warp 1 idles).
-template <int T, bool PAIR>
+// F16: the boards and weights are fp16 instead of bf16 (same instruction, other operand-format bits).
+template <int T, bool PAIR, bool F16>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
                            const ResidentParams p) {
@@ -256,6 +160,7 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t kIdesc = make_idesc(F16, kTileM, kC);
     const uint32_t bar0 = smem_u32(bars);
     auto in_full = [&](int bd) { return bar0 + 8u * bd; };               // the board's first input has landed in y
     auto act_ready = [&](int bd) { return bar0 + 8u * (2 + bd); };       // the previous layer's output is written
@@ -365,7 +270,7 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
                                     for (int ks = 0; ks < kC / 16; ++ks)
                                         umma(d_tmem + (uint32_t)(tile * kC),
                                              a_lo + (uint32_t)(tile * (kTileM * kRowBytes >> 4) + tap_off[tap] + ks * 2),
-                                             w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), (tap | ks) ? 1u : 0u);
+                                             w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), kIdesc, (tap | ks) ? 1u : 0u);
                                 }
                                 if (last_board && tap % 3 == 2) umma_commit(w_empty(tap / 3));   // the round's boards are through with these taps
                             }
@@ -424,7 +329,7 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
                             for (int ks = 0; ks < kC / 16; ++ks)
                                 umma(d_tmem + (uint32_t)(tile * kC),
                                      a_lo + (uint32_t)(tile * (kTileM * kRowBytes >> 4) + tap_off[tap] + ks * 2),
-                                     w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), (tap | ks) ? 1u : 0u);
+                                     w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), kIdesc, (tap | ks) ? 1u : 0u);
                         }
                         if (tap % 3 == 2) {
                             umma_commit(w_empty(tap / 3));
@@ -483,10 +388,10 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
                     }
                     uint8_t* dst_row = (to_x ? x_s : y_s) + slot_off(bd) + row * kRowBytes;
                     if (!valid) store_zero_row(dst_row);
-                    else if (has_res) store_row<true>(dst_row, row, r, bias_t);
-                    else store_row<false>(dst_row, row, r, bias_t);
+                    else if (has_res) store_row<true, F16>(dst_row, row, r, bias_t);
+                    else store_row<false, F16>(dst_row, row, r, bias_t);
                     if (l + 1 == L && p.head_ch > 0 && valid)
-                        head_row(dst_row, row, head_s, p.head_ch, p.head_pc, board_of(round, bd), p.S, p.GP, p.hp, p.hv);
+                        head_row<F16>(dst_row, row, head_s, p.head_ch, p.head_pc, board_of(round, bd), p.S, p.GP, p.hp, p.hv);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // rows -> the tensor cores' / the store's reads
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
@@ -557,7 +462,7 @@ int tower_resident_head_channels_max() { return kHeadMax; }
 // tower's output ride along in the last epilogue; results as launch_head_conv writes them.
 int launch_conv_tower_resident(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* layers_dev,
                                int n_layers, int B, int S, cudaStream_t st, const float* head_w, const float* head_b,
-                               int head_ch, int head_pc, float* hp, float* hv) {
+                               int head_ch, int head_pc, float* hp, float* hv, int dtype) {
     if (!layers_dev || n_layers < 1 || B <= 0) return set_error(OB200_ERR_INVALID, "resident tower: bad arguments");
     if (head_ch < 0 || head_ch > kHeadMax || head_pc < 0 || head_pc > head_ch ||
         (head_ch > 0 && (!head_w || !head_b || (head_pc > 0 && !hp) || (head_pc < head_ch && !hv))))
@@ -571,12 +476,16 @@ int launch_conv_tower_resident(const BoardTensorMap& in_map, const BoardTensorMa
     const int slots = (S + 1) * (S + 1);
     const bool two_tiles = slots > kTileM;
     const bool pair = B > sms;          // some CTA has two boards or more
-    auto kernel = two_tiles ? (pair ? conv_tower_resident_kernel<2, true> : conv_tower_resident_kernel<2, false>)
-                            : (pair ? conv_tower_resident_kernel<1, true> : conv_tower_resident_kernel<1, false>);
-    static size_t configured[64][4] = {{0, 0, 0, 0}};
-    if (dev >= 0 && dev < 64 && configured[dev][two_tiles * 2 + pair] < smem) {
+    const bool f16 = dtype == OB200_DTYPE_F16;
+    auto kernel = f16 ? (two_tiles ? (pair ? conv_tower_resident_kernel<2, true, true> : conv_tower_resident_kernel<2, false, true>)
+                                   : (pair ? conv_tower_resident_kernel<1, true, true> : conv_tower_resident_kernel<1, false, true>))
+                      : (two_tiles ? (pair ? conv_tower_resident_kernel<2, true, false> : conv_tower_resident_kernel<2, false, false>)
+                                   : (pair ? conv_tower_resident_kernel<1, true, false> : conv_tower_resident_kernel<1, false, false>));
+    static size_t configured[64][8] = {{0}};
+    const int variant = f16 * 4 + two_tiles * 2 + pair;
+    if (dev >= 0 && dev < 64 && configured[dev][variant] < smem) {
         OB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured[dev][two_tiles * 2 + pair] = smem;
+        configured[dev][variant] = smem;
     }
     ResidentParams p;
     p.layers = static_cast<const ResidentLayer*>(layers_dev); p.n_layers = n_layers; p.B = B; p.S = S; p.GP = S + 1; p.slots = slots;

@@ -25,8 +25,7 @@
 // Every wait on an mbarrier is bounded; when one runs out the CTA raises the
 // device error word, leaves its loops, frees its TMEM and returns.
 #include "internal.h"
-#include <cuda.h>
-#include <cuda_bf16.h>
+#include "sm100_ptx.cuh"
 #include <cstring>
 
 namespace ob200 {
@@ -51,7 +50,6 @@ constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2 * kAccStages + kEpiGrou
 constexpr int kMaxCout = 256;
 constexpr int kSmemBytes = kAStages * kAStageBytes + kBStages * kBStageBytes + kEpiGroups * kOutBytes +
                            kNumBars * 8 + kMaxCout * 4 + 16 + 1024;
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 struct WideParams {
     const uint8_t* w;         // packed weights: [n_half][k_slice][tap] blocks of 128 x 64, pre-swizzled
@@ -70,83 +68,26 @@ struct WideParams {
     int relu;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if ((i & 255) == 255 && *abort_flag) return false;
-    }
-    return false;
-}
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
-}
-
-// Shared-memory matrix descriptor, K-major, 128-byte swizzle (rows of 128 bytes, 8-row groups
-// 1024 bytes apart, base offset 0: the swizzle is a function of the shared-memory address, so
-// a descriptor may start at any 128-byte row of a tile TMA wrote with the same swizzle).
-constexpr uint32_t kDescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
-__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
-// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, M = 128, N = 128.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kN >> 3) << 17) |
-                            ((uint32_t)(kTileM >> 4) << 24);
-
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
-        "mov.b64 da, {%1, %3};\nmov.b64 db, {%2, %3};\n"
-        "setp.ne.b32 p, %5, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}"
-        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(kDescHi), "r"(kIdesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
+using namespace ptx;
 __device__ __forceinline__ void group_bar(int id) {   // the 128 threads of one epilogue group
     asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory");
 }
+// Barrier of one epilogue group that also tells every thread whether any of them reports `bad`:
+// the group gives up on a wait as a whole, so no thread is left at a barrier its siblings have left.
+__device__ __forceinline__ bool group_any(int id, bool bad) {
+    uint32_t r;
+    asm volatile(
+        "{\n.reg .pred p, q;\nsetp.ne.b32 q, %2, 0;\nbar.red.or.pred p, %1, 128, q;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(r) : "r"(id), "r"((uint32_t)bad) : "memory");
+    return r != 0;
+}
 
-template <int TAPS>
+// F16: activations and weights are fp16 instead of bf16.
+template <int TAPS, bool F16>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
                  const __grid_constant__ CUtensorMap res_map, const WideParams p) {
+    constexpr uint32_t kIdesc = make_idesc(F16, kTileM, kN);
     extern __shared__ uint8_t smem_raw[];
     // swizzled tiles need 1024-byte aligned bases
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -270,12 +211,12 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                         const uint32_t at = a_lo + (uint32_t)tap_off[tap];
 #pragma unroll
                         for (int ks = 0; ks < kSlice / 16; ++ks)
-                            umma(d_tmem, at + (uint32_t)(ks * 2), b_lo + (uint32_t)(ks * 2), (tap | ks) ? 1u : (uint32_t)(kc != 0));
+                            umma(d_tmem, at + (uint32_t)(ks * 2), b_lo + (uint32_t)(ks * 2), kIdesc, (tap | ks) ? 1u : (uint32_t)(kc != 0));
                         if (two) {
 #pragma unroll
                             for (int ks = 0; ks < kSlice / 16; ++ks)
                                 umma(d_tmem + (uint32_t)kN, at + (uint32_t)(kTileM * (kRowBytes >> 4) + ks * 2),
-                                     b_lo + (uint32_t)(ks * 2), (tap | ks) ? 1u : (uint32_t)(kc != 0));
+                                     b_lo + (uint32_t)(ks * 2), kIdesc, (tap | ks) ? 1u : (uint32_t)(kc != 0));
                         }
                         umma_commit(bempty_bar(sb));    // weight block free once these MMAs have read it
                         if (++sb == kBStages) { sb = 0; phb ^= 1u; }
@@ -327,7 +268,7 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                     tma_load_2d(stage_out_u32, &res_map, nh * kN, OB200_GUARD + tile * kTileM, res_bar(group));
                 }
             }
-            if (!mbar_wait(accfull_bar(a), pa, abort_flag)) {
+            if (group_any(1 + 2 * group, !mbar_wait(accfull_bar(a), pa, abort_flag))) {
                 *abort_flag = 1; atomicExch(p.error, 3); break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -376,12 +317,9 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                     }
                     continue;
                 }
-                if (has_res) {
-                    if (!mbar_wait(res_bar(group), res_phase, abort_flag)) { ok = false; break; }
-                    res_phase ^= 1u;
-                } else {
-                    group_bar(1 + 2 * group);   // after the leader's wait: the staging tile is free
-                }
+                // the vote is also the barrier behind the leader's wait: the staging tile is free
+                if (group_any(1 + 2 * group, has_res && !mbar_wait(res_bar(group), res_phase, abort_flag))) { ok = false; break; }
+                if (has_res) res_phase ^= 1u;
                 const float* bias_t = bias_s + nh * kN + half * 64;
                 uint8_t* my_row = stage_out + row * kRowBytes;
 #pragma unroll
@@ -395,12 +333,12 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
                         uint32_t ow[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            // bf16 -> fp32 is a 16-bit shift
-                            float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bias_t[c * 8 + 2 * j] + __uint_as_float(rw[j] << 16);
-                            float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bias_t[c * 8 + 2 * j + 1] + __uint_as_float(rw[j] & 0xFFFF0000u);
+                            float r0, r1;
+                            unpack2<F16>(rw[j], r0, r1);
+                            float v0 = __uint_as_float(r[c * 8 + 2 * j]) + bias_t[c * 8 + 2 * j] + r0;
+                            float v1 = __uint_as_float(r[c * 8 + 2 * j + 1]) + bias_t[c * 8 + 2 * j + 1] + r1;
                             if (p.relu) { v0 = fmaxf(v0, 0.0f); v1 = fmaxf(v1, 0.0f); }
-                            const __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
-                            ow[j] = *reinterpret_cast<const uint32_t*>(&h2);
+                            ow[j] = pack2<F16>(v0, v1);
                         }
                         o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                     }
@@ -430,14 +368,6 @@ conv_wide_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_consta
     }
 }
 
-inline uint16_t f32_to_bf16_rne(float f) {
-    uint32_t u;
-    std::memcpy(&u, &f, 4);
-    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40);  // NaN
-    u += 0x7FFFu + ((u >> 16) & 1u);
-    return (uint16_t)(u >> 16);
-}
-
 }  // namespace
 
 bool conv_wide_covers(int cin, int cout) {
@@ -447,7 +377,8 @@ int conv_wide_box_rows() { return kBoxRows; }
 
 int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const BoardTensorMap* res_map,
                           const void* packed_w, const float* bias, int B, int S, int cin, int cout, int taps, int relu,
-                          cudaStream_t st, float* out_f32) {
+                          cudaStream_t st, float* out_f32, int dtype) {
+    if (dtype != OB200_DTYPE_BF16 && dtype != OB200_DTYPE_F16) return set_error(OB200_ERR_INVALID, "conv (wide): bad dtype %d", dtype);
     if (!packed_w || !bias || B <= 0) return set_error(OB200_ERR_INVALID, "conv (wide): null pointer or empty batch");
     if (!conv_wide_covers(cin, cout) || (taps != 9 && taps != 1))
         return set_error(OB200_ERR_UNSUPPORTED, "conv (wide): %d -> %d channels with %d taps is not covered", cin, cout, taps);
@@ -458,10 +389,12 @@ int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& ou
     static bool configured[64] = {false};
     int dev = 0;
     OB200_CUDA_OK(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        OB200_CUDA_OK(cudaFuncSetAttribute(conv_wide_kernel<9>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        OB200_CUDA_OK(cudaFuncSetAttribute(conv_wide_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-        configured[dev] = true;
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        OB200_CUDA_OK(cudaFuncSetAttribute(conv_wide_kernel<9, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        OB200_CUDA_OK(cudaFuncSetAttribute(conv_wide_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        OB200_CUDA_OK(cudaFuncSetAttribute(conv_wide_kernel<9, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        OB200_CUDA_OK(cudaFuncSetAttribute(conv_wide_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     int sms = 0;
     OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -487,20 +420,21 @@ int launch_conv_wide_maps(const BoardTensorMap& in_map, const BoardTensorMap& ou
     const CUtensorMap& im = *reinterpret_cast<const CUtensorMap*>(&in_map);
     const CUtensorMap& om = *reinterpret_cast<const CUtensorMap*>(&out_map);
     const CUtensorMap& rm = *reinterpret_cast<const CUtensorMap*>(res_map ? res_map : &out_map);
-    if (taps == 9) OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv_wide_kernel<9>, im, om, rm, p));
-    else OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, conv_wide_kernel<1>, im, om, rm, p));
+    auto kernel = dtype == OB200_DTYPE_F16 ? (taps == 9 ? conv_wide_kernel<9, true> : conv_wide_kernel<1, true>)
+                                           : (taps == 9 ? conv_wide_kernel<9, false> : conv_wide_kernel<1, false>);
+    OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, im, om, rm, p));
     OB200_LAUNCHED("conv_wide_kernel");
     return OB200_OK;
 }
 
 size_t conv_wide_packed_bytes(int cin, int cout, int taps) { return (size_t)taps * cin * cout * 2; }
 
-// Packed image: blocks [n_half][k_slice][tap] of 128 output channels x 64 input channels, bf16,
+// Packed image: blocks [n_half][k_slice][tap] of 128 output channels x 64 input channels, bf16 (or fp16),
 // one 128-byte row per output channel, its 16-byte chunks (8 input channels) permuted by the
 // 128-byte swizzle (chunk j of row r stored at chunk j ^ (r % 8)): the K-major shared-memory
 // operand layout of the tensor core, ready for plain bulk copies in the order the kernel
 // consumes them.  w: [cout][cin_real][taps] fp32 (OIHW), scale: per output channel or null.
-int conv_wide_pack(const float* w, const float* scale, int cout, int cin_real, int cin, int taps, void* packed_out) {
+int conv_wide_pack(const float* w, const float* scale, int cout, int cin_real, int cin, int taps, void* packed_out, int dtype) {
     if (!w || !packed_out || !conv_wide_covers(cin, cout) || cin_real <= 0 || cin_real > cin || (taps != 9 && taps != 1))
         return set_error(OB200_ERR_INVALID, "conv (wide) pack: cout %d, cin_real %d, cin %d, taps %d not covered", cout,
                          cin_real, cin, taps);
@@ -514,7 +448,7 @@ int conv_wide_pack(const float* w, const float* scale, int cout, int cin_real, i
                 const int nh = co / kN, col = co % kN, kc = ci / kSlice, cil = ci % kSlice;
                 const size_t block = ((size_t)nh * KS + kc) * taps + tap;
                 const size_t byte = block * kBStageBytes + (size_t)col * kRowBytes + ((((cil >> 3) ^ (col & 7))) << 4) + (cil & 7) * 2;
-                o[byte / 2] = f32_to_bf16_rne(v);
+                o[byte / 2] = dtype == OB200_DTYPE_F16 ? f32_to_f16_rne_sat(v) : f32_to_bf16_rne(v);
             }
     return OB200_OK;
 }

@@ -6,8 +6,8 @@ torch CPU fp32 ops, taking weights under the reference's parameter names.  The
 two head widths the reference hard-codes as 32 (:81-96) are read from the
 weight shapes, so the same code covers the 2-channel / 1-channel heads of the
 benchmark configuration.  Pinned against the reference's own class through
-oracle/_ref/libref_net.so (tests/test_oracle_vs_reference.py) and the golden
-fixtures in tests/golden/.
+oracle/_ref/libref_net.so (tests/test_oracle.py) and the golden fixtures in
+tests/golden/.
 """
 import numpy as np
 import torch
@@ -69,14 +69,29 @@ def _bf16(t):
     return t.to(torch.bfloat16).to(torch.float32)
 
 
+def _f16(t):
+    # the device stores fp16 activations saturated at the largest finite value
+    return t.clamp(-65504.0, 65504.0).to(torch.float16).to(torch.float32)
+
+
 def forward_bf16(weights, planes, blocks=None):
+    """forward_stored with bfloat16 storage (the device path's default)."""
+    return forward_stored(weights, planes, blocks, _bf16)
+
+
+def forward_f16(weights, planes, blocks=None):
+    """forward_stored with float16 storage (the device path's OB200_DTYPE_F16)."""
+    return forward_stored(weights, planes, blocks, _f16)
+
+
+def forward_stored(weights, planes, blocks=None, _bf16=_bf16):
     """The same network with the storage precision of the device path, still in
     fp32 arithmetic on the CPU: BatchNorm folded into the convolution
     (w * gamma / sqrt(var + eps), shift as fp32 bias), folded tower weights and
-    every stored activation rounded to bfloat16, heads in fp32 on the bf16 tower
-    output.  It says what the bf16 design computes; the gap between this and
-    forward() is the price of bf16, the gap between this and the device is
-    kernel error."""
+    every stored activation rounded to the 16-bit storage type (`_bf16`: the
+    rounding function), heads in fp32 on the tower output.  It says what the
+    16-bit design computes; the gap between this and forward() is the price of
+    the storage type, the gap between this and the device is kernel error."""
     w = {k: torch.from_numpy(np.ascontiguousarray(v, np.float32)) for k, v in weights.items()}
     if blocks is None:
         blocks = 1 + max([int(k.split(".")[1]) for k in w if k.startswith("res_blocks.")] + [-1])
@@ -106,7 +121,7 @@ def forward_bf16(weights, planes, blocks=None):
             wf, b = fold("policy_conv", "policy_bn")
             pol = F.relu(F.conv2d(x, wf) + b[None, :, None, None])
             logits = F.linear(pol.reshape(pol.shape[0], -1), w["policy_fc.weight"], w["policy_fc.bias"])
-        else:   # convolutional policy head: bf16 weights on the tensor cores, fp32 accumulate and output
+        else:   # convolutional policy head: 16-bit weights on the tensor cores, fp32 accumulate and output
             logits = F.conv2d(x, _bf16(w["policy_conv.weight"]), w["policy_conv.bias"]).reshape(x.shape[0], -1)
         wf, b = fold("value_conv", "value_bn")
         val = F.relu(F.conv2d(x, wf) + b[None, :, None, None])

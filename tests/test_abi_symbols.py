@@ -34,7 +34,7 @@ def test_bindings_cover_every_declared_symbol():
 
 
 def test_pure_host_helpers(lib):
-    assert lib.ob200_version() == 1
+    assert lib.ob200_version() == 2
     assert lib.ob200_tree_pitch(225) == 228 and lib.ob200_tree_mask_words(225) == 8
     assert lib.ob200_tree_pitch(4672) == 4672 and lib.ob200_tree_mask_words(4672) == 146
     # 15x15 boards live on a 16x16 grid: 256 positions per board + 2 x 32 guards
@@ -59,6 +59,24 @@ def test_weight_packing_layout(lib):
                 row[chunk * 8:(chunk + 1) * 8] = vals[tap, co, chunk ^ (co % 8)]
             assert np.array_equal(row[:17], w[co, :, tap // 3, tap % 3] * 0.5)
             assert not row[17:].any()                                 # channels >= 17 carry zero weights
+
+
+def test_weight_packing_f16(lib):
+    """The fp16 image has the layout of the bf16 one, values rounded to nearest even and saturated."""
+    import numpy as np
+    from omoknuni_small_b200 import capi
+    rng = np.random.default_rng(1)
+    w = rng.normal(0, 1, (64, 64, 3, 3)).astype(np.float32)
+    w[0, 0, 0, 0], w[1, 0, 0, 0], w[2, 0, 0, 0] = 1e6, -1e6, 3e-8       # beyond the range on both sides, below the subnormals
+    packed = capi.pack_conv3x3(w, None, 64, capi.DTYPE_F16).reshape(9, 64, 8, 8)
+    vals = packed.view(np.float16).astype(np.float32)
+    want = np.clip(w, -65504.0, 65504.0).astype(np.float16).astype(np.float32)
+    for tap in range(9):
+        for co in (0, 1, 2, 33, 63):
+            row = np.empty(64, np.float32)
+            for chunk in range(8):
+                row[chunk * 8:(chunk + 1) * 8] = vals[tap, co, chunk ^ (co % 8)]
+            assert np.array_equal(row, want[co, :, tap // 3, tap % 3])
 
 
 @pytest.mark.skipif(os.path.exists("/dev/nvidiactl"), reason="a GPU is present")

@@ -15,12 +15,12 @@ def api(lib):
     return capi
 
 
-def run_encode(api, hist, nh, tm, S, planes, out_channels=64):
+def run_encode(api, hist, nh, tm, S, planes, out_channels=64, dtype=0):
     import torch
     bt = api.encode_gomoku(torch.from_numpy(hist).cuda(), torch.from_numpy(nh).cuda(), torch.from_numpy(tm).cuda(), S,
-                           planes, out_channels)
+                           planes, out_channels, dtype)
     torch.cuda.synchronize()
-    return api.board_tensor_to_planes(bt.cpu().numpy().view(np.uint16), S, hist.shape[0], out_channels)
+    return api.board_tensor_to_planes(bt.cpu().numpy().view(np.uint16), S, hist.shape[0], out_channels, dtype)
 
 
 @pytest.mark.parametrize("planes", [17, 19])
@@ -36,6 +36,15 @@ def test_encode_matches_reference_golden(api, planes):
 def test_encode_matches_oracle(api, oracle, B, S, seed):
     games, hist, nh, tm = synth.make_gomoku_games(B, S, seed=seed)
     got, pad_zero = run_encode(api, hist, nh, tm, S, 19)
+    assert pad_zero and np.array_equal(got[:, :19], oracle.gomoku_encode(hist, nh, tm, S, 19))
+
+
+@pytest.mark.parametrize("B,S", [(257, 15), (7, 19), (3, 31)])
+def test_encode_f16_storage(api, oracle, B, S):
+    """The same planes as an fp16 board tensor (both encoder kernels: the board-per-CTA one and,
+    for 31x31, the per-position one)."""
+    games, hist, nh, tm = synth.make_gomoku_games(B, S, seed=B)
+    got, pad_zero = run_encode(api, hist, nh, tm, S, 19, dtype=api.DTYPE_F16)
     assert pad_zero and np.array_equal(got[:, :19], oracle.gomoku_encode(hist, nh, tm, S, 19))
 
 
@@ -59,6 +68,9 @@ def test_planes_to_board_tensor_round_trip(api):
     torch.cuda.synchronize()
     got = bt.cpu().numpy().view(np.uint16)
     assert np.array_equal(got, api.planes_to_board_tensor_host(x, 64))
+    bt = api.planes_to_board_tensor(torch.from_numpy(x).cuda(), 64, api.DTYPE_F16)
+    torch.cuda.synchronize()
+    assert np.array_equal(bt.cpu().numpy().view(np.uint16), api.planes_to_board_tensor_host(x, 64, api.DTYPE_F16))
 
 
 def bf16_round(a):

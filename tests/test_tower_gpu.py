@@ -5,8 +5,10 @@ Tolerances.  One layer: inputs and weights are bf16-exact, accumulation is
 fp32, the output is rounded to bf16 once, so |err| <= 2^-8 * |y| + 1e-5.
 Whole network: policy logits within 2e-2 and value within 1e-2 (max-abs) of the
 fp32 forward for the reference module's own initialisation and for seeded
-weights with random BatchNorm statistics; for the Kaiming-normal benchmark
-weights see test_network_kaiming_normal_benchmark_weights."""
+weights with random BatchNorm statistics in the default bf16 storage; for the
+Kaiming-normal benchmark weights the bound holds with fp16 storage
+(test_network_kaiming_normal_benchmark_weights_f16) and is missed by bf16 storage
+(test_network_kaiming_normal_benchmark_weights_bf16_gap says by how much)."""
 import numpy as np
 import pytest
 
@@ -29,22 +31,27 @@ def bf16_round(a):
     return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
 
 
-def conv_case(api, B, S, cin_real, cin, residual, relu, seed, cout=64):
+def f16_round(a):
+    return np.ascontiguousarray(a, np.float32).astype(np.float16).astype(np.float32)
+
+
+def conv_case(api, B, S, cin_real, cin, residual, relu, seed, cout=64, dtype=0, scale=1.0, wscale=0.1):
     import torch
     import torch.nn.functional as F
     rng = np.random.default_rng(seed)
-    x = bf16_round(rng.normal(0, 1, (B, cin_real, S, S)).astype(np.float32))
-    w = bf16_round(rng.normal(0, 0.1, (cout, cin_real, 3, 3)).astype(np.float32))
+    rnd = f16_round if dtype == 1 else bf16_round
+    x = rnd(rng.normal(0, scale, (B, cin_real, S, S)).astype(np.float32))
+    w = rnd(rng.normal(0, wscale, (cout, cin_real, 3, 3)).astype(np.float32))
     bias = rng.normal(0, 0.5, cout).astype(np.float32)
-    res = bf16_round(rng.normal(0, 1, (B, cout, S, S)).astype(np.float32)) if residual else None
+    res = rnd(rng.normal(0, 1, (B, cout, S, S)).astype(np.float32)) if residual else None
     y = F.conv2d(torch.from_numpy(x), torch.from_numpy(w), padding=1).numpy() + bias[None, :, None, None]
     if residual:
         y = y + res
     if relu:
         y = np.maximum(y, 0)
-    xd = torch.from_numpy(api.planes_to_board_tensor_host(x, cin).view(np.int16)).cuda()
-    rd = torch.from_numpy(api.planes_to_board_tensor_host(res, cout).view(np.int16)).cuda() if residual else None
-    wd = torch.from_numpy(api.pack_conv3x3(w, None, cin).view(np.int16)).cuda()
+    xd = torch.from_numpy(api.planes_to_board_tensor_host(x, cin, dtype).view(np.int16)).cuda()
+    rd = torch.from_numpy(api.planes_to_board_tensor_host(res, cout, dtype).view(np.int16)).cuda() if residual else None
+    wd = torch.from_numpy(api.pack_conv3x3(w, None, cin, dtype).view(np.int16)).cuda()
     bd = torch.from_numpy(bias).cuda()
     # pre-fill the output with a pattern: the kernel must overwrite padding positions with zero
     out = torch.full((int(api.lib().ob200_board_tensor_bytes(S, B, cout)) // 2,), 0x3F80, dtype=torch.int16, device="cuda")
@@ -52,10 +59,10 @@ def conv_case(api, B, S, cin_real, cin, residual, relu, seed, cout=64):
     o2 = out.view(PT, cout)
     o2[:api.GUARD] = 0
     o2[PT - api.GUARD:] = 0
-    api.conv3x3(xd, wd, bd, rd, B, S, cin, cout, relu, out=out)
+    api.conv3x3(xd, wd, bd, rd, B, S, cin, cout, relu, out=out, dtype=dtype)
     torch.cuda.synchronize()
     assert api.device_error_code() == 0
-    got, pad_zero = api.board_tensor_to_planes(out.cpu().numpy().view(np.uint16), S, B, cout)
+    got, pad_zero = api.board_tensor_to_planes(out.cpu().numpy().view(np.uint16), S, B, cout, dtype)
     return got, y, pad_zero
 
 
@@ -98,9 +105,43 @@ def test_conv3x3_layer_wide(api, B, S, cin_real, cin, cout, residual, relu):
     assert pad_zero, "padding / guard positions of the output are not zero"
 
 
-def make_net(api, w, cfg, max_batch):
+@pytest.mark.parametrize("B,S,cin_real,cin,cout,residual,relu", [
+    (2, 15, 64, 64, 64, True, True),
+    (3, 15, 17, 64, 64, False, True),        # the stem
+    (700, 15, 64, 64, 64, True, True),       # every CTA loops
+    (5, 9, 64, 64, 64, True, False),
+    (2, 19, 128, 128, 128, True, True),      # the streamed-weight kernel
+    (6, 8, 256, 256, 256, True, True),
+])
+def test_conv3x3_layer_f16(api, B, S, cin_real, cin, cout, residual, relu):
+    """The same layer with fp16 storage (OB200_DTYPE_F16): inputs and weights fp16-exact, fp32
+    accumulation, one rounding to fp16 (11 significant bits)."""
+    got, want, pad_zero = conv_case(api, B, S, cin_real, cin, residual, relu, seed=B * 100 + S + cout, cout=cout, dtype=1)
+    err = np.abs(got - want)
+    tol = np.abs(want) * 2.0 ** -11 + 1e-4
+    bad = np.argwhere(err > tol)
+    assert bad.size == 0, f"{len(bad)} of {err.size} elements off; first {bad[:5].tolist()}; max err {err.max():.4g}"
+    assert pad_zero, "padding / guard positions of the output are not zero"
+
+
+def test_conv3x3_f16_saturates_instead_of_overflowing(api):
+    """fp16 storage ends at 65,504.  Inputs of magnitude ~1,000 times weights of magnitude ~2 over 576
+    products push many sums beyond that: the stored outputs must be clamped to +-65,504 (+65,504 / 0 behind a ReLU), never
+    inf or NaN, so that one outsized activation does not poison everything downstream."""
+    for relu in (False, True):
+        got, want, pad_zero = conv_case(api, 3, 15, 64, 64, False, relu, seed=99, dtype=1, scale=1000.0, wscale=2.0)
+        assert np.isfinite(got).all()
+        over = np.abs(want) > 65504.0
+        assert over.mean() > 0.05, "the case must actually overflow"
+        assert np.array_equal(got[over], np.sign(want[over]) * 65504.0)
+        fine = np.abs(want) < 60000.0
+        assert np.abs(got[fine] - want[fine]).max() <= 65504.0 * 2.0 ** -10
+        assert pad_zero
+
+
+def make_net(api, w, cfg, max_batch, dtype=0):
     return api.Net(cfg["cin"], cfg["S"], cfg["blocks"], cfg["F"], cfg["A"], cfg["pc"], cfg["vc"], 256, max_batch,
-                   policy_kind=cfg.get("kind", 0)).load(w)
+                   policy_kind=cfg.get("kind", 0), tower_dtype=dtype).load(w)
 
 
 def mixed_planes(B, S, C, scalar_planes, seed):
@@ -202,28 +243,51 @@ def test_network_torch_default_init_benchmark_shape(api, heads):
     assert np.abs(v - ref_v).max() <= VALUE_TOL
 
 
-def test_network_kaiming_normal_benchmark_weights(api):
-    """The benchmark's weights (Kaiming-normal convolutions with ReLU gain, identity BatchNorm,
-    2/1-channel heads).  With this initialisation the residual stream doubles in variance per
-    block, and ANY pipeline that stores activations in bf16 (8 significant bits, 21 layers)
-    lands about 0.1 (logits) / 0.02 (value) away from fp32: the fp32-arithmetic emulation of
-    bf16 storage (oracle/net_ref.forward_bf16) is that far from fp32 itself, and two bf16
-    implementations differ from each other by a similar amount because one flipped rounding
-    early on is amplified by the later layers.  The kernels' own arithmetic is held to a tight
-    bound by test_conv3x3_layer; here the device's gap to fp32 must not exceed the emulation's
-    gap by more than half, and the preferred move must agree wherever fp32's margin is clear."""
+def kaiming_case():
     from oracle import net_ref
     shapes = synth.net_tensor_shapes(15, 17, 64, 10, 225, 2, 1)
     w = synth.make_weights(shapes, seed=42, init="kaiming_normal", bn="identity")
     x = synth.make_stone_planes(256, 15, 17, seed=1000)
-    ref_logits, ref_v = net_ref.forward(w, x)
+    return w, x, net_ref.forward(w, x)
+
+
+def test_network_kaiming_normal_benchmark_weights_f16(api):
+    """The benchmark's weights (Kaiming-normal convolutions with ReLU gain, identity BatchNorm,
+    2/1-channel heads) at the stated tolerance: logits within 2e-2, value within 1e-2 of the fp32
+    forward.  With identity BatchNorm the residual stream doubles in variance per block and 21 layers of
+    8-bit significands drift several 1e-2 from fp32 (next test); fp16 storage (11 bits, activations
+    peak near 32, far inside its range) holds the bound, and is what the benchmark runs."""
+    from oracle import net_ref
+    w, x, (ref_logits, ref_v) = kaiming_case()
+    net = make_net(api, w, dict(cin=17, S=15, blocks=10, F=64, A=225, pc=2, vc=1), 256, dtype=api.DTYPE_F16)
+    logits, v = net.infer_planes(x, api.OUT_LOGITS)
+    assert net.tower_path() == 2
+    emu_logits, emu_v = net_ref.forward_f16(w, x)
+    f_err, fv_err = np.abs(logits - ref_logits).max(), np.abs(v - ref_v).max()
+    print(f"kaiming-normal, fp16 storage: max|logit| {np.abs(ref_logits).max():.2f}; device vs fp32 {f_err:.4f} / {fv_err:.4f}; "
+          f"fp16 emulation vs fp32 {np.abs(emu_logits - ref_logits).max():.4f} / {np.abs(emu_v - ref_v).max():.4f}")
+    assert f_err <= POLICY_TOL and fv_err <= VALUE_TOL
+    assert (logits.argmax(1) == ref_logits.argmax(1)).mean() >= 0.98
+    probs, _ = net.infer_planes(x, api.OUT_PROBS)
+    assert np.abs(probs - net_ref.softmax(ref_logits)).max() <= 1e-3
+
+
+def test_network_kaiming_normal_benchmark_weights_bf16_gap(api):
+    """The same weights in the default bf16 storage MISS the 2e-2 / 1e-2 bound: the fp32-arithmetic
+    emulation of bf16 storage (oracle/net_ref.forward_bf16) is itself about 0.09 (logits) / 0.02 (value)
+    from fp32, and so is the device.  This test documents that gap and holds the kernels to the
+    emulation (the device's gap to fp32 must not exceed the emulation's by more than half, and the
+    preferred move must agree wherever fp32's margin is clear); networks with such weights belong on
+    OB200_DTYPE_F16."""
+    from oracle import net_ref
+    w, x, (ref_logits, ref_v) = kaiming_case()
     emu_logits, emu_v = net_ref.forward_bf16(w, x)
     net = make_net(api, w, dict(cin=17, S=15, blocks=10, F=64, A=225, pc=2, vc=1), 256)
     logits, v = net.infer_planes(x, api.OUT_LOGITS)
     k_err, kv_err = np.abs(logits - emu_logits).max(), np.abs(v - emu_v).max()
     f_err, fv_err = np.abs(logits - ref_logits).max(), np.abs(v - ref_v).max()
     e_err = np.abs(emu_logits - ref_logits).max()
-    print(f"kaiming-normal: max|logit| {np.abs(ref_logits).max():.2f}; device vs bf16 emulation {k_err:.4f} / {kv_err:.4f}; "
+    print(f"kaiming-normal, bf16 storage: max|logit| {np.abs(ref_logits).max():.2f}; device vs bf16 emulation {k_err:.4f} / {kv_err:.4f}; "
           f"device vs fp32 {f_err:.4f} / {fv_err:.4f}; bf16 emulation vs fp32 {e_err:.4f}")
     ev_err = np.abs(emu_v - ref_v).max()
     assert f_err <= 1.5 * e_err + POLICY_TOL and fv_err <= 1.5 * ev_err + VALUE_TOL
@@ -233,6 +297,28 @@ def test_network_kaiming_normal_benchmark_weights(api):
     rows = np.arange(len(order))
     margin = ref_logits[rows, order[:, -1]] - ref_logits[rows, order[:, -2]]
     assert (logits.argmax(1) == order[:, -1])[margin > 2 * f_err].all()
+
+
+@pytest.mark.parametrize("name,cfg,B", [
+    ("gomoku15_f64_heads32", dict(cin=19, S=15, blocks=3, F=64, A=225, pc=32, vc=32), 20),
+    ("go19_f64", dict(cin=17, S=19, blocks=2, F=64, A=362, pc=2, vc=1), 9),         # too large to stay resident
+    ("go19_f128", dict(cin=17, S=19, blocks=2, F=128, A=362, pc=2, vc=1), 7),
+    ("chess8_f256_planes", dict(cin=119, S=8, blocks=2, F=256, A=4672, pc=73, vc=1, kind=1), 11),
+])
+def test_network_f16_storage_other_shapes(api, name, cfg, B):
+    """fp16 storage on the other tower paths: head kernel instead of the riding-along heads, the
+    per-layer / cooperative 64-filter kernels (19x19), the streamed-weight kernel and the
+    convolution-plane policy head."""
+    from oracle import net_ref
+    shapes = synth.net_tensor_shapes(cfg["S"], cfg["cin"], cfg["F"], cfg["blocks"], cfg["A"], cfg["pc"], cfg["vc"],
+                                     policy_planes=cfg.get("kind", 0) == 1)
+    w = synth.make_weights(shapes, seed=12, init="torch_default", bn="random")
+    x = mixed_planes(B, cfg["S"], cfg["cin"], 7 if cfg["cin"] == 119 else 0, seed=2100 + B)
+    ref_logits, ref_v = net_ref.forward(w, x)
+    net = make_net(api, w, cfg, B + 3, dtype=api.DTYPE_F16)
+    logits, v = net.infer_planes(x, api.OUT_LOGITS)
+    assert np.abs(logits - ref_logits).max() <= POLICY_TOL / 4, np.abs(logits - ref_logits).max()
+    assert np.abs(v - ref_v).max() <= VALUE_TOL / 4
 
 
 def pick_tower(monkeypatch, which):
@@ -271,6 +357,25 @@ def test_resident_tower_equals_layer_by_layer(api, monkeypatch, S, blocks, B):
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
     # 1 tower launch instead of 1 + 2 * blocks, and the heads' 1x1 convolutions ride along in it
     assert outs[0][2] == outs[1][2] - 2 * blocks - 1
+    assert api.device_error_code() == 0
+
+
+@pytest.mark.parametrize("S,blocks,B", [(15, 10, 300), (9, 2, 5), (15, 3, 149)])
+def test_f16_tower_paths_bit_identical(api, monkeypatch, S, blocks, B):
+    """fp16 storage: the board-resident tower, the cooperative single-launch tower and the
+    launch-per-layer path are the same arithmetic in the same order, bit for bit."""
+    shapes = synth.net_tensor_shapes(S, 17, 64, blocks, S * S, 2, 1)
+    w = synth.make_weights(shapes, seed=6, init="torch_default", bn="random")
+    x = synth.make_stone_planes(B, S, 17, seed=4100 + B)
+    outs = []
+    for which, path in (("resident", 2), ("fused", 1), ("layers", 0)):
+        pick_tower(monkeypatch, which)
+        net = make_net(api, w, dict(cin=17, S=S, blocks=blocks, F=64, A=S * S, pc=2, vc=1), B, dtype=api.DTYPE_F16)
+        outs.append(net.infer_planes(x, api.OUT_LOGITS))
+        assert net.tower_path() == path
+        net.close()
+    for o in outs[1:]:
+        assert np.array_equal(outs[0][0], o[0]) and np.array_equal(outs[0][1], o[1])
     assert api.device_error_code() == 0
 
 

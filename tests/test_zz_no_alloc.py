@@ -16,18 +16,19 @@ from omoknuni_small_b200 import synth
 pytestmark = pytest.mark.gpu
 
 
-def test_value_head_noalloc_matches_forward_twice(lib):
+@pytest.mark.parametrize("dtype", [0, 1], ids=["bf16", "f16"])
+def test_value_head_noalloc_matches_forward_twice(lib, dtype):
     import torch
     from omoknuni_small_b200 import capi
     shapes = synth.net_tensor_shapes(15, 17, 64, 2, 225, 2, 1)
     w = synth.make_weights(shapes, seed=5, init="torch_default", bn="random")
     B = 96
-    net = capi.Net(17, 15, 2, 64, 225, 2, 1, 256, B).load(w)
+    net = capi.Net(17, 15, 2, 64, 225, 2, 1, 256, B, tower_dtype=dtype).load(w)
     policy = torch.empty((B, 225), dtype=torch.float32, device="cuda")
     value = torch.empty(B, dtype=torch.float32, device="cuda")
     for call, seed in enumerate((11, 12)):                       # two calls in a row, different inputs
         x = synth.make_stone_planes(B, 15, 17, seed=seed)
-        bt = capi.planes_to_board_tensor(torch.from_numpy(x).cuda(), net.input_tensor_channels())
+        bt = capi.planes_to_board_tensor(torch.from_numpy(x).cuda(), net.input_tensor_channels(), dtype)
         net.forward_device(bt, B, policy, value, capi.OUT_PROBS)     # the existing entry point
         torch.cuda.synchronize()
         want = value.cpu().numpy().copy()
