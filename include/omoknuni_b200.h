@@ -456,7 +456,8 @@ int ob200_debug_bounded_wait(int32_t spin_limit, ob200_stream stream);
  *  Where the reference leaves things open or racy this defines them:
  *  children are in action order (the reference shuffles them); simulations of a
  *  tree inside a round run in sequence; a leaf reached twice in a round is
- *  expanded once and backed up twice; a terminal leaf takes the game result
+ *  expanded once (by the simulation with the lowest index; nodes are numbered in
+ *  simulation order, so a search is reproducible bit for bit) and backed up twice; a terminal leaf takes the game result
  *  (-1 for the side to move after a five-in-a-row, 0 for a full board) instead
  *  of the network value (the reference's batched loop asks the network even
  *  then; its serial loop uses the result); value_sign = +1 adds the leaf value
@@ -490,7 +491,10 @@ typedef struct ob200_search_stats {
     int64_t evaluations;        /* positions sent to the network (roots included)  */
     int64_t nodes;              /* nodes allocated, all trees                      */
     int64_t terminal_leaves;    /* simulations that ended in a finished game       */
-    double device_ms;           /* device time of the call (CUDA events)           */
+    double device_ms;           /* device time of the enqueued work (CUDA events)  */
+    double wall_ms;             /* host time of the whole call: root set-up, noise
+                                   sampling, copies, the wait and the read-back
+                                   included                                        */
 } ob200_search_stats;
 
 /* `net` must be a finalised 15x15 Gomoku network with max_batch >= leaf_batch;
@@ -506,6 +510,18 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
 /* Test hooks: device pointers of the search's tree view and node counter, and a
  * synchronous device-to-host copy for reading them. */
 int ob200_search_debug_tree(ob200_search* s, ob200_tree_view* view_out, int32_t* nodes_used_out);
+/* More test hooks, for comparing a search with a CPU restatement fed the same
+ * network outputs.  value_quantum > 0: network values are rounded to multiples
+ * of 1 / value_quantum before they are backed up (sums of such values are exact
+ * in fp32 whatever the order of the atomic additions).  record_rounds > 0: the
+ * policy [leaf_batch][225] and value [leaf_batch] arrays of the root evaluation
+ * (entry 0, n_trees rows used) and of the first record_rounds rounds of every
+ * later ob200_search_run are kept on the device; ob200_search_debug_record gives
+ * their device pointers ([record_rounds + 1] entries each) and the root noise
+ * [n_trees][228] of the last run. */
+int ob200_search_debug_hooks(ob200_search* s, float value_quantum, int32_t record_rounds);
+int ob200_search_debug_record(ob200_search* s, const float** policy_out, const float** value_out,
+                              const float** noise_out);
 int ob200_copy_to_host(void* dst_host, const void* src_device, int64_t bytes);
 
 /* Per-device counters for the end-of-run reduction (the only cross-GPU step;

@@ -47,7 +47,7 @@ class SearchConfig(C.Structure):
 
 class SearchStats(C.Structure):
     _fields_ = [("simulations", C.c_int64), ("evaluations", C.c_int64), ("nodes", C.c_int64),
-                ("terminal_leaves", C.c_int64), ("device_ms", C.c_double)]
+                ("terminal_leaves", C.c_int64), ("device_ms", C.c_double), ("wall_ms", C.c_double)]
 
 
 class Counters(C.Structure):
@@ -114,6 +114,8 @@ SIGNATURES = {
     "ob200_search_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_float, C.c_void_p, C.c_void_p,
                                    C.POINTER(SearchStats)]),
     "ob200_search_debug_tree": (C.c_int, [C.c_void_p, C.POINTER(TreeView), C.POINTER(C.c_int32)]),
+    "ob200_search_debug_hooks": (C.c_int, [C.c_void_p, C.c_float, C.c_int32]),
+    "ob200_search_debug_record": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "ob200_copy_to_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
     "ob200_get_counters": (C.c_int, [C.POINTER(Counters)]),
     "ob200_reset_counters": (None, []),
@@ -454,6 +456,24 @@ class Search:
                                      temperature, pi.ctypes.data_as(C.c_void_p), visits.ctypes.data_as(C.c_void_p),
                                      C.byref(st)))
         return pi, visits, {k: getattr(st, k) for k, _ in SearchStats._fields_}
+
+    def debug_hooks(self, value_quantum=0.0, record_rounds=0):
+        """Test hooks: round network values to multiples of 1 / value_quantum; keep the network outputs of the
+        root evaluation and of the first `record_rounds` rounds of each run."""
+        check(lib().ob200_search_debug_hooks(self.h, value_quantum, record_rounds))
+        self._rec_rounds = record_rounds
+
+    def record(self):
+        """(policy [R + 1, L, 225], value [R + 1, L], noise [T, 228]) of the last run, as numpy arrays."""
+        pp, vp, nz = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        check(lib().ob200_search_debug_record(self.h, C.byref(pp), C.byref(vp), C.byref(nz)))
+        R, L, T = self._rec_rounds, self.cfg.leaf_batch, self.cfg.n_trees
+
+        def pull(ptr, shape):
+            a = np.empty(shape, np.float32)
+            check(lib().ob200_copy_to_host(a.ctypes.data_as(C.c_void_p), ptr, a.nbytes))
+            return a
+        return pull(pp, (R + 1, L, 225)), pull(vp, (R + 1, L)), pull(nz, (T, 228))
 
     def tree(self):
         """Host copies of the search's tree arrays (for tests): dict of numpy arrays + nodes used."""

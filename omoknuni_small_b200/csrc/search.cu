@@ -12,6 +12,7 @@
 // node t (< n_trees) is the root of tree t; a node's child slot is the board
 // cell of the move (slot == action), its existence bit says the cell is empty.
 #include "internal.h"
+#include <chrono>
 #include <cmath>
 #include <cstring>
 #include <random>
@@ -42,6 +43,15 @@ struct ob200_search {
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     uint64_t moves_done = 0;
+    // expansion plan of a round (per simulation)
+    int32_t *plan_status = nullptr, *plan_aux = nullptr, *plan_new_id = nullptr;
+    unsigned long long* plan_hash = nullptr;
+    // test hooks: leaf values rounded to multiples of 1 / value_quantum (0 = off); a record of what every network
+    // call of a move returned
+    float value_quantum = 0.0f;
+    float *rec_policy = nullptr, *rec_value = nullptr;   // [rec_rounds + 1][leaf_batch][A], [rec_rounds + 1][leaf_batch]
+    int rec_rounds = 0;
+    double wall_ms = 0.0;                                // host time of the last ob200_search_run
     std::vector<void*> owned;
 };
 
@@ -81,7 +91,8 @@ __global__ void mix_noise_kernel(ob200_tree_view t, const float* __restrict__ no
     const size_t row = (size_t)tree * t.pitch;
     const uint32_t* m = t.legal_bits + (size_t)tree * t.mask_words;
     for (int s = threadIdx.x; s < t.n_children; s += blockDim.x)
-        if (bit(m, s)) t.P[row + s] = (1.0f - eps) * t.P[row + s] + eps * noise[(size_t)tree * t.pitch + s];
+        if (bit(m, s))   // (1 - eps) * prior + eps * noise, each operation rounded as the reference's C++ does (no fused multiply-add)
+            t.P[row + s] = __fadd_rn(__fmul_rn(__fsub_rn(1.0f, eps), t.P[row + s]), __fmul_rn(eps, noise[(size_t)tree * t.pitch + s]));
 }
 
 // One thread per simulation: the leaf position from root + path.
@@ -142,66 +153,176 @@ __global__ void leaf_prepare_kernel(const int32_t* __restrict__ paths, const int
     if (tv == tv) atomicAdd(term_count, 1);
 }
 
-// One warp per simulation: create the node behind the leaf edge (once per edge)
-// with priors from the network policy, and choose the value to back up.
+// Expansion of a round's leaf edges, in two kernels.  The outcome is a function of the inputs alone
+// (no dependence on which thread runs first), and it is the outcome of taking the round's simulations
+// one after another in index order:
+//   * an edge reached by several simulations of the round is expanded by the one with the lowest index;
+//   * new nodes get consecutive ids in the order of the simulations that create them;
+//   * with the transposition table, the position behind an edge (Zobrist key: stones + side to move, as
+//     GomokuState::compute_hash_signature_internal, src/games/gomoku/gomoku_state.cpp:947-958) is looked
+//     up first; if this game already has a node for it - from an earlier round, or from a simulation of
+//     this round with a lower index - the edge is pointed at that node (the reference re-points the
+//     parent's child reference, src/mcts/mcts_engine_batch_tree_simple.cpp:117-162) and nothing is created.
+//
+// expand_plan_kernel is ONE CTA that walks the simulations in phases separated by __syncthreads:
+//   A  leaf value (game result for finished games, else the network's); lowest index claims the edge
+//      (atomicMin of a code that orders by index);
+//   B  winners look their position up in the table as it was before the round;
+//   C  the others enter their key (or find the slot a sibling of this round took) and the lowest index
+//      per key becomes its owner;
+//   D  owners are counted in index order (block scan) -> node ids;
+//   E  edges and table entries are pointed at the ids.
+// expand_rows_kernel (a warp per simulation) then fills the rows of the nodes created.
+constexpr int kPlanThreads = 1024;
+enum : int32_t { kPlanNone = 0, kPlanCandidate = 1, kPlanNew = 2, kPlanShareOld = 3, kPlanShareNew = 4, kPlanOwner = 5 };
+
+struct PlanScratch {
+    int32_t* status;            // [L] one of kPlan*
+    int32_t* aux;               // [L] table slot (candidate / owner), node id (share old), owner's index (share new)
+    int32_t* new_id;            // [L] id of the node this simulation creates, or -1
+    unsigned long long* hash;   // [L] key of the position behind the edge
+};
+
+__device__ __forceinline__ float quantized(float v, float q) { return q > 0.0f ? __fdiv_rn(rintf(__fmul_rn(v, q)), q) : v; }
+
+__global__ void __launch_bounds__(kPlanThreads)
+expand_plan_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const int32_t* __restrict__ path_len,
+                   int n_sims, int max_depth, const float* __restrict__ value, const float* __restrict__ term_value,
+                   float value_sign, float value_quantum, int max_nodes, int32_t* n_used, float* __restrict__ leaf_value,
+                   int sims_per_tree, const uint8_t* __restrict__ root_tm, const unsigned long long* __restrict__ zobrist,
+                   const unsigned long long* __restrict__ node_hash, unsigned long long* tt_key, int32_t* tt_val, int tt_size,
+                   PlanScratch ps) {
+    __shared__ int warp_sums[kPlanThreads / 32];
+    __shared__ int carry_s;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    auto code = [&](int i) { return -2 - (n_sims - 1 - i); };            // lower index -> smaller code; all below -1
+    auto edge = [&](int i, int len) {
+        const int32_t* p = paths + (size_t)i * max_depth * 2;
+        return (size_t)p[2 * (len - 1)] * t.pitch + p[2 * (len - 1) + 1];
+    };
+    auto length = [&](int i) { const int len = path_len[i]; return len > max_depth ? max_depth : len; };
+    // ---- A: values, claims ----
+    for (int i = tid; i < n_sims; i += kPlanThreads) {
+        const int len = length(i);
+        const float tv = term_value[i];
+        const bool terminal = tv == tv;
+        leaf_value[i] = value_sign * (terminal ? tv : quantized(value[i], value_quantum));
+        int st = kPlanNone;
+        if (len > 0 && !terminal) {
+            const size_t e = edge(i, len);
+            if (*reinterpret_cast<volatile int32_t*>(t.child_node + e) < 0) { atomicMin(t.child_node + e, code(i)); st = kPlanCandidate; }
+        }
+        ps.status[i] = st; ps.aux[i] = -1; ps.new_id[i] = -1;
+    }
+    __syncthreads();
+    // ---- B: winners; table lookup against the state before this round ----
+    for (int i = tid; i < n_sims; i += kPlanThreads) {
+        if (ps.status[i] != kPlanCandidate) continue;
+        const int len = length(i);
+        const size_t e = edge(i, len);
+        if (*reinterpret_cast<volatile int32_t*>(t.child_node + e) != code(i)) { ps.status[i] = kPlanNone; continue; }
+        if (tt_size <= 0) { ps.status[i] = kPlanNew; continue; }
+        const int32_t* p = paths + (size_t)i * max_depth * 2;
+        const int parent = p[2 * (len - 1)], slot = p[2 * (len - 1) + 1];
+        const int rtm = root_tm[i / sims_per_tree];
+        const int mover = ((len - 1) & 1) ? 3 - rtm : rtm;
+        unsigned long long h = node_hash[parent] ^ zobrist[(mover - 1) * 225 + slot] ^ zobrist[450];
+        if (h == 0) h = 1;
+        ps.hash[i] = h;
+        int st = kPlanNew;                                                // probe limit reached: a node outside the table
+        unsigned idx = (unsigned)(h >> 17) & (unsigned)(tt_size - 1);
+        for (int tries = 0; tries < 64; ++tries, idx = (idx + 1) & (unsigned)(tt_size - 1)) {
+            const unsigned long long k = *reinterpret_cast<volatile unsigned long long*>(tt_key + idx);
+            if (k == 0) { st = kPlanCandidate; break; }
+            if (k == h) {
+                const int other = *reinterpret_cast<volatile int32_t*>(tt_val + idx);
+                if (other >= 0) { st = kPlanShareOld; ps.aux[i] = other; } else st = kPlanCandidate;
+                break;
+            }
+        }
+        ps.status[i] = st;
+    }
+    __syncthreads();
+    // ---- C: candidates enter their key; the lowest index per key owns it ----
+    for (int i = tid; i < n_sims; i += kPlanThreads) {
+        if (ps.status[i] != kPlanCandidate) continue;
+        const unsigned long long h = ps.hash[i];
+        int found = -1;
+        unsigned idx = (unsigned)(h >> 17) & (unsigned)(tt_size - 1);
+        for (int tries = 0; tries < 64 && found < 0; ++tries, idx = (idx + 1) & (unsigned)(tt_size - 1)) {
+            unsigned long long k = *reinterpret_cast<volatile unsigned long long*>(tt_key + idx);
+            if (k == 0) { k = atomicCAS(tt_key + idx, 0ull, h); if (k == 0) k = h; }
+            if (k == h) found = (int)idx;
+        }
+        if (found < 0) { ps.status[i] = kPlanNew; continue; }
+        atomicMin(tt_val + found, code(i));
+        ps.aux[i] = found;
+    }
+    __syncthreads();
+    for (int i = tid; i < n_sims; i += kPlanThreads) {
+        if (ps.status[i] != kPlanCandidate) continue;
+        const int v = *reinterpret_cast<volatile int32_t*>(tt_val + ps.aux[i]);
+        if (v == code(i)) ps.status[i] = kPlanOwner;
+        else { ps.status[i] = kPlanShareNew; ps.aux[i] = n_sims - 1 - (-2 - v); }
+    }
+    // ---- D: ids in index order ----
+    if (tid == 0) carry_s = *n_used;
+    __syncthreads();
+    for (int base = 0; base < n_sims; base += kPlanThreads) {
+        const int i = base + tid;
+        const int st = i < n_sims ? ps.status[i] : kPlanNone;
+        const int flag = (st == kPlanOwner || st == kPlanNew) ? 1 : 0;
+        int incl = flag;
+        for (int off = 1; off < 32; off <<= 1) { const int o = __shfl_up_sync(0xffffffffu, incl, off); if (lane >= off) incl += o; }
+        if (lane == 31) warp_sums[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = warp_sums[lane];
+            for (int off = 1; off < 32; off <<= 1) { const int o = __shfl_up_sync(0xffffffffu, w, off); if (lane >= off) w += o; }
+            warp_sums[lane] = w;                                          // inclusive sums over the warps
+        }
+        __syncthreads();
+        const int before = carry_s + (warp ? warp_sums[warp - 1] : 0) + incl - flag;
+        if (flag) ps.new_id[i] = before < max_nodes ? before : -1;       // pool exhausted: the edge stays a leaf
+        __syncthreads();
+        if (tid == 0) carry_s += warp_sums[kPlanThreads / 32 - 1];
+        __syncthreads();
+    }
+    if (tid == 0) *n_used = carry_s < max_nodes ? carry_s : max_nodes;
+    // ---- E: point edges and table entries at the nodes ----
+    for (int i = tid; i < n_sims; i += kPlanThreads) {
+        const int st = ps.status[i];
+        if (st == kPlanNone) continue;
+        const size_t e = edge(i, length(i));
+        int child = -1;
+        if (st == kPlanOwner) { child = ps.new_id[i]; tt_val[ps.aux[i]] = child; }
+        else if (st == kPlanNew) child = ps.new_id[i];
+        else if (st == kPlanShareOld) child = ps.aux[i];
+        else if (st == kPlanShareNew) child = ps.new_id[ps.aux[i]];
+        t.child_node[e] = child;
+    }
+}
+
+// One warp per simulation that creates a node: existence mask = the parent's minus the move, priors =
+// clamp(policy, 0, 1) on the existing slots with no renormalisation (MCTSNode::expand +
+// setPriorProbabilities, src/mcts/mcts_node.cpp:238-436,546-553), statistics zero.
 __global__ void __launch_bounds__(256)
-expand_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const int32_t* __restrict__ path_len,
-              int n_sims, int max_depth, const float* __restrict__ policy, int policy_size,
-              const float* __restrict__ value, const float* __restrict__ term_value, float value_sign,
-              int max_nodes, int32_t* n_used, float* __restrict__ leaf_value, int sims_per_tree,
-              const uint8_t* __restrict__ root_tm, const unsigned long long* __restrict__ zobrist,
-              unsigned long long* node_hash, unsigned long long* tt_key, int32_t* tt_val, int tt_size) {
+expand_rows_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const int32_t* __restrict__ path_len,
+                   int n_sims, int max_depth, const float* __restrict__ policy, int policy_size,
+                   unsigned long long* node_hash, int tt_size, PlanScratch ps) {
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (i >= n_sims) return;
+    const int st = ps.status[i];
+    const int id = ps.new_id[i];
+    if ((st != kPlanOwner && st != kPlanNew) || id < 0) return;
     int len = path_len[i];
     if (len > max_depth) len = max_depth;
-    const float tv = term_value[i];
-    const bool terminal = tv == tv;
-    if (lane == 0) leaf_value[i] = value_sign * (terminal ? tv : value[i]);
-    if (len == 0 || terminal) return;
     const int32_t* p = paths + (size_t)i * max_depth * 2;
     const int parent = p[2 * (len - 1)], slot = p[2 * (len - 1) + 1];
-    const size_t e = (size_t)parent * t.pitch + slot;
-    int id = -1, tt_slot = -1;
-    unsigned long long h = 0;
-    if (lane == 0 && atomicCAS(t.child_node + e, -1, -2) == -1) {     // first simulation on this edge claims it
-        bool shared = false;
-        if (tt_size > 0) {
-            // Zobrist key of the position behind the edge: the parent's key, the mover's stone, the
-            // side to move flipped (GomokuState::compute_hash_signature_internal keys the board and
-            // the player, not the move order: src/games/gomoku/gomoku_state.cpp:947-958)
-            const int rtm = root_tm[i / sims_per_tree];
-            const int mover = ((len - 1) & 1) ? 3 - rtm : rtm;
-            h = node_hash[parent] ^ zobrist[(mover - 1) * 225 + slot] ^ zobrist[450];
-            if (h == 0) h = 1;
-            unsigned idx = (unsigned)(h >> 17) & (unsigned)(tt_size - 1);
-            for (int tries = 0; tries < 64; ++tries, idx = (idx + 1) & (unsigned)(tt_size - 1)) {
-                unsigned long long k = tt_key[idx];
-                if (k == 0) k = atomicCAS(tt_key + idx, 0ull, h);       // try to take the empty slot
-                if (k == 0) { tt_slot = (int)idx; break; }               // ours: filled in once the node exists
-                if (k == h) {                                            // same position reached before
-                    const int other = *reinterpret_cast<volatile int32_t*>(tt_val + idx);
-                    if (other >= 0) { atomicExch(t.child_node + e, other); shared = true; }
-                    break;                                               // (or being created right now: no sharing)
-                }
-            }
-        }
-        if (!shared) {
-            id = atomicAdd(n_used, 1);
-            if (id >= max_nodes) {                                    // pool exhausted: the edge stays a leaf
-                atomicSub(n_used, 1);
-                atomicExch(t.child_node + e, -1);
-                id = -1;
-            }
-        }
-    }
-    id = __shfl_sync(0xffffffffu, id, 0);
-    if (id < 0) return;     // another simulation of the same batch creates the node, it is shared, or nobody can
     const size_t row = (size_t)id * t.pitch;
     const uint32_t* pm = t.legal_bits + (size_t)parent * t.mask_words;
     uint32_t* cm = t.legal_bits + (size_t)id * t.mask_words;
     for (int w = lane; w < t.mask_words; w += 32) cm[w] = pm[w] & ~((w == (slot >> 5)) ? (1u << (slot & 31)) : 0u);
-    __syncwarp();
     const float* pol = policy + (size_t)i * policy_size;
     for (int s = lane; s < t.pitch; s += 32) {
         float pr = 0.0f;
@@ -211,10 +332,7 @@ expand_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const int32_
     }
     if (lane == 0) {
         t.node_visits[id] = 0;
-        if (tt_size > 0) node_hash[id] = h;
-        __threadfence();
-        atomicExch(t.child_node + e, id);
-        if (tt_slot >= 0) atomicExch(tt_val + tt_slot, id);          // visible to later transpositions
+        if (tt_size > 0) node_hash[id] = ps.hash[i];
     }
 }
 
@@ -281,6 +399,8 @@ int ob200_search_create(ob200_net* net, const ob200_search_config* cfg, ob200_se
     A_(salloc(s, &s->leaf_value, (size_t)L)); A_(salloc(s, &s->term_value, (size_t)L));
     A_(salloc(s, &s->policy, (size_t)L * s->A)); A_(salloc(s, &s->value, (size_t)L));
     A_(salloc(s, &s->noise, (size_t)T * s->pitch));
+    A_(salloc(s, &s->plan_status, (size_t)L)); A_(salloc(s, &s->plan_aux, (size_t)L)); A_(salloc(s, &s->plan_new_id, (size_t)L));
+    A_(salloc(s, &s->plan_hash, (size_t)L));
     if (cfg->use_transposition_table) {
         s->tt_size = 1;
         while (s->tt_size < 2 * s->max_nodes) s->tt_size <<= 1;
@@ -328,6 +448,28 @@ int ob200_search_debug_tree(ob200_search* s, ob200_tree_view* view_out, int32_t*
     return OB200_OK;
 }
 
+int ob200_search_debug_hooks(ob200_search* s, float value_quantum, int32_t record_rounds) {
+    if (!s || value_quantum < 0.0f || record_rounds < 0) return set_error(OB200_ERR_INVALID, "ob200_search_debug_hooks: bad argument");
+    const ob200_net_config* nc = net_config(s->net);
+    OB200_CUDA_OK(cudaSetDevice(nc->device));
+    s->value_quantum = value_quantum;
+    if (record_rounds > 0 && !s->rec_policy) {
+        const size_t L = (size_t)s->cfg.leaf_batch;
+        if (int rc = salloc(s, &s->rec_policy, (size_t)(record_rounds + 1) * L * s->A)) return rc;
+        if (int rc = salloc(s, &s->rec_value, (size_t)(record_rounds + 1) * L)) return rc;
+        s->rec_rounds = record_rounds;
+    }
+    return OB200_OK;
+}
+
+int ob200_search_debug_record(ob200_search* s, const float** policy_out, const float** value_out, const float** noise_out) {
+    if (!s) return set_error(OB200_ERR_INVALID, "ob200_search_debug_record: null argument");
+    if (policy_out) *policy_out = s->rec_policy;
+    if (value_out) *value_out = s->rec_value;
+    if (noise_out) *noise_out = s->noise;
+    return OB200_OK;
+}
+
 int ob200_copy_to_host(void* dst_host, const void* src_device, int64_t bytes) {
     if (!dst_host || !src_device || bytes < 0) return set_error(OB200_ERR_INVALID, "ob200_copy_to_host: bad argument");
     OB200_CUDA_OK(cudaMemcpy(dst_host, src_device, (size_t)bytes, cudaMemcpyDeviceToHost));
@@ -341,6 +483,7 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
     const ob200_search_config& c = s->cfg;
     const int T = c.n_trees, L = c.leaf_batch, S = s->S, A = s->A;
     const ob200_net_config* nc = net_config(s->net);
+    const auto wall0 = std::chrono::steady_clock::now();
     OB200_CUDA_OK(cudaSetDevice(nc->device));
     // ---- roots from the move lists (host) ----
     std::vector<uint32_t> stones((size_t)T * 16, 0u);
@@ -376,12 +519,16 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
         std::mt19937_64 rng(c.seed + 0x9E3779B97F4A7C15ull * (s->moves_done + 1));
         std::gamma_distribution<float> gamma(c.dirichlet_alpha, 1.0f);
         for (int t = 0; t < T; ++t) {
-            double sum = 0.0;
-            for (int a = 0; a < A; ++a) {
-                const bool occ = ((stones[(size_t)t * 16 + (a >> 5)] | stones[(size_t)t * 16 + 8 + (a >> 5)]) >> (a & 31)) & 1u;
-                if (!occ) { const float g = gamma(rng); noise[(size_t)t * s->pitch + a] = g; sum += g; }
-            }
-            if (sum > 0) for (int a = 0; a < A; ++a) noise[(size_t)t * s->pitch + a] = (float)(noise[(size_t)t * s->pitch + a] / sum);
+            // one Gamma(alpha, 1) draw per child in child order, summed and divided in fp32; a zero sum gives
+            // uniform noise (src/mcts/mcts_engine_eval.cpp:83-100)
+            float* row = noise.data() + (size_t)t * s->pitch;
+            float sum = 0.0f;
+            int children = 0;
+            auto occupied = [&](int a) { return ((stones[(size_t)t * 16 + (a >> 5)] | stones[(size_t)t * 16 + 8 + (a >> 5)]) >> (a & 31)) & 1u; };
+            for (int a = 0; a < A; ++a)
+                if (!occupied(a)) { row[a] = gamma(rng); sum += row[a]; ++children; }
+            for (int a = 0; a < A; ++a)
+                if (!occupied(a)) row[a] = sum > 0.0f ? row[a] / sum : 1.0f / (float)children;
         }
         OB200_CUDA_OK(cudaMemcpyAsync(s->noise, noise.data(), noise.size() * 4, cudaMemcpyHostToDevice, st));
     }
@@ -403,6 +550,10 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
     if (int rc = launch_encode_gomoku(s->root_hist, s->root_nh, s->root_tm, T, S, nc->input_channels, 64, s->input_bt, st, nc->tower_dtype)) return rc;
     if (int rc = net_forward_for_search(s->net, s->input_bt, T, s->policy, s->value, st)) return rc;
     if (int rc = ob200_launch_set_priors(&s->tv, s->roots, T, s->policy, A, nullptr, st)) return rc;
+    if (s->rec_policy) {
+        OB200_CUDA_OK(cudaMemcpyAsync(s->rec_policy, s->policy, (size_t)T * A * 4, cudaMemcpyDeviceToDevice, st));
+        OB200_CUDA_OK(cudaMemcpyAsync(s->rec_value, s->value, (size_t)T * 4, cudaMemcpyDeviceToDevice, st));
+    }
     if (c.dirichlet_epsilon > 0.0f) {
         mix_noise_kernel<<<T, 128, 0, st>>>(s->tv, s->noise, c.dirichlet_epsilon);
         OB200_LAUNCHED("mix_noise_kernel");
@@ -419,11 +570,19 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
         OB200_LAUNCHED("leaf_prepare_kernel");
         if (int rc = launch_encode_gomoku(s->leaf_hist, s->leaf_nh, s->leaf_tm, L, S, nc->input_channels, 64, s->input_bt, st, nc->tower_dtype)) return rc;
         if (int rc = net_forward_for_search(s->net, s->input_bt, L, s->policy, s->value, st)) return rc;
-        expand_kernel<<<(L * 32 + 255) / 256, 256, 0, st>>>(s->tv, s->paths, s->path_len, L, c.max_depth, s->policy, A,
-                                                           s->value, s->term_value, (float)c.value_sign, s->max_nodes,
-                                                           s->n_used, s->leaf_value, s->sims_per_round, s->root_tm,
-                                                           s->zobrist, s->node_hash, s->tt_key, s->tt_val, s->tt_size);
-        OB200_LAUNCHED("expand_kernel");
+        if (s->rec_policy && r < s->rec_rounds) {
+            OB200_CUDA_OK(cudaMemcpyAsync(s->rec_policy + (size_t)(r + 1) * L * A, s->policy, (size_t)L * A * 4, cudaMemcpyDeviceToDevice, st));
+            OB200_CUDA_OK(cudaMemcpyAsync(s->rec_value + (size_t)(r + 1) * L, s->value, (size_t)L * 4, cudaMemcpyDeviceToDevice, st));
+        }
+        const PlanScratch ps{s->plan_status, s->plan_aux, s->plan_new_id, s->plan_hash};
+        expand_plan_kernel<<<1, kPlanThreads, 0, st>>>(s->tv, s->paths, s->path_len, L, c.max_depth, s->value, s->term_value,
+                                                       (float)c.value_sign, s->value_quantum, s->max_nodes, s->n_used,
+                                                       s->leaf_value, s->sims_per_round, s->root_tm, s->zobrist, s->node_hash,
+                                                       s->tt_key, s->tt_val, s->tt_size, ps);
+        OB200_LAUNCHED("expand_plan_kernel");
+        expand_rows_kernel<<<(L * 32 + 255) / 256, 256, 0, st>>>(s->tv, s->paths, s->path_len, L, c.max_depth, s->policy, A,
+                                                                s->node_hash, s->tt_size, ps);
+        OB200_LAUNCHED("expand_rows_kernel");
         if (int rc = ob200_launch_backup(&s->tv, s->paths, s->path_len, s->leaf_value, L, c.max_depth, c.virtual_loss, st)) return rc;
     }
     OB200_CUDA_OK(cudaEventRecord(s->ev1, st));
@@ -460,6 +619,7 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
         stats->simulations = (int64_t)rounds * L;
         stats->evaluations = (int64_t)rounds * L + T;
         stats->nodes = used; stats->terminal_leaves = terms; stats->device_ms = ms;
+        stats->wall_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - wall0).count();
     }
     return OB200_OK;
 }

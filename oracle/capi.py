@@ -176,6 +176,130 @@ def chess_encode(pieces, meta, legal_to):
     return out
 
 
+def zobrist_keys(seed):
+    """The 451 Zobrist keys of a search created with `seed` (splitmix64 stream): [0,225) BLACK stones,
+    [225,450) WHITE stones, [450] side to move."""
+    M = (1 << 64) - 1
+    x = (seed ^ 0xD1B54A32D192ED03) & M
+    out = np.empty(451, np.uint64)
+    for i in range(451):
+        x = (x + 0x9E3779B97F4A7C15) & M
+        v = x
+        v = ((v ^ (v >> 30)) * 0xBF58476D1CE4E5B9) & M
+        v = ((v ^ (v >> 27)) * 0x94D049BB133111EB) & M
+        out[i] = v ^ (v >> 31)
+    return out
+
+
+def root_hash(moves, tree_index, zobrist):
+    """Key of a root position: its stones, the side to move, and the per-game salt that keeps the
+    games of one search from sharing nodes."""
+    M = (1 << 64) - 1
+    h = 0
+    for i, m in enumerate(moves):
+        h ^= int(zobrist[(i & 1) * 225 + int(m)])
+    if len(moves) & 1:
+        h ^= int(zobrist[450])
+    return h ^ ((0x9E3779B97F4A7C15 * (tree_index + 1)) & M)
+
+
+def search_new_trees(move_lists, max_nodes, n_children=225):
+    """Edge arrays for a search over the given games: node t is the root of game t (existence mask =
+    empty cells), everything else unused."""
+    T = len(move_lists)
+    pitch, mw = (n_children + 3) // 4 * 4, (n_children + 31) // 32
+    t = {"N": np.zeros((max_nodes, pitch), np.int32), "W": np.zeros((max_nodes, pitch), np.float32),
+         "P": np.zeros((max_nodes, pitch), np.float32), "VL": np.zeros((max_nodes, pitch), np.int32),
+         "child_node": np.full((max_nodes, pitch), -1, np.int32), "legal_bits": np.zeros((max_nodes, mw), np.uint32),
+         "node_visits": np.zeros(max_nodes, np.int32), "n_children": n_children, "nodes": T}
+    for g, mv in enumerate(move_lists):
+        empty = np.ones(n_children, bool)
+        empty[np.asarray(mv, np.int64)] = False
+        bits = np.zeros(mw * 32, np.uint8)
+        bits[:n_children] = empty
+        t["legal_bits"][g] = np.packbits(bits.reshape(mw, 32), axis=1, bitorder="little").view(np.uint32).reshape(mw)
+    return t
+
+
+def mix_noise(tree, node_ids, noise, eps):
+    ids = np.ascontiguousarray(node_ids, np.int32)
+    noise = np.ascontiguousarray(noise, np.float32)
+    L = lib()
+    L.oracle_mix_noise.argtypes = [_f32, _u32, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, _f32, C.c_float]
+    L.oracle_mix_noise(tree["P"], tree["legal_bits"], tree["n_children"], tree["P"].shape[1],
+                       tree["legal_bits"].shape[1], _opt(ids), len(ids), noise, eps)
+
+
+def dirichlet_normalize(gammas):
+    g = np.ascontiguousarray(gammas, np.float32).copy()
+    L = lib()
+    L.oracle_dirichlet_normalize.argtypes = [_f32, C.c_int]
+    L.oracle_dirichlet_normalize(g, len(g))
+    return g
+
+
+def search_expand(tree, node_hash, paths, path_len, sims_per_tree, move_lists, policy, value, value_sign,
+                  value_quantum, zobrist, board_size=15):
+    """The expansion step of one round (oracle_search_expand in oracle.c).  tree["nodes"] is the node
+    counter and is advanced; node_hash (uint64 [max_nodes]) is None with the table off.  Returns
+    (leaf_values, terminal flags)."""
+    paths = np.ascontiguousarray(paths, np.int32)
+    n, max_depth, _ = paths.shape
+    T = len(move_lists)
+    stride = max(1, max(len(m) for m in move_lists))
+    moves = np.full((T, stride), -1, np.int16)
+    nm = np.zeros(T, np.int32)
+    for g, m in enumerate(move_lists):
+        moves[g, :len(m)] = m
+        nm[g] = len(m)
+    used = np.array([tree["nodes"]], np.int32)
+    leaf = np.zeros(n, np.float32)
+    term = np.zeros(n, np.int32)
+    policy = np.ascontiguousarray(policy, np.float32)
+    _u64 = np.ctypeslib.ndpointer(np.uint64, flags="C_CONTIGUOUS")
+    L = lib()
+    L.oracle_search_expand.argtypes = [_i32, _f32, _f32, _i32, _u32, _i32, _i32, C.c_void_p, _i32, C.c_int, C.c_int, C.c_int,
+                                       C.c_int, _i32, _i32, C.c_int, C.c_int, C.c_int, _i16, _i32, C.c_int, C.c_int, _f32,
+                                       C.c_int, _f32, C.c_float, C.c_float, _u64, C.c_int, _f32, _i32]
+    L.oracle_search_expand(tree["N"], tree["W"], tree["P"], tree["VL"], tree["legal_bits"], tree["node_visits"],
+                           tree["child_node"], _opt(node_hash), used, tree["N"].shape[0], tree["n_children"],
+                           tree["N"].shape[1], tree["legal_bits"].shape[1], paths, np.ascontiguousarray(path_len, np.int32),
+                           n, max_depth, sims_per_tree, moves, nm, stride, board_size, policy, policy.shape[1],
+                           np.ascontiguousarray(value, np.float32), float(value_sign), float(value_quantum),
+                           np.ascontiguousarray(zobrist, np.uint64), T, leaf, term)
+    tree["nodes"] = int(used[0])
+    return leaf, term
+
+
+def search_move(move_lists, root_policy, noise, eps, round_policy, round_value, sims_per_tree, max_nodes, c_puct=1.5,
+                vl_value=3, max_depth=64, value_sign=1.0, value_quantum=0.0, tt_seed=None):
+    """One move of the leaf-parallel search for a group of games, given what the network returned:
+    root_policy [T, 225]; round_policy [R, T * sims_per_tree, 225], round_value [R, T * sims_per_tree].
+    noise [T, pitch] (or None) is mixed into the root priors with weight eps.  tt_seed: seed of the Zobrist
+    keys, None = table off.  Returns the tree dict (tree["nodes"] nodes used) and per-round terminal counts."""
+    T = len(move_lists)
+    tree = search_new_trees(move_lists, max_nodes)
+    roots = np.arange(T, dtype=np.int32)
+    set_priors(tree, roots, root_policy)
+    if noise is not None and eps > 0:
+        mix_noise(tree, roots, noise, eps)
+    zob = zobrist_keys(tt_seed if tt_seed is not None else 0)
+    node_hash = None
+    if tt_seed is not None:
+        node_hash = np.zeros(max_nodes, np.uint64)
+        for g, mv in enumerate(move_lists):
+            node_hash[g] = root_hash(mv, g, zob)
+    terminals = 0
+    for r in range(len(round_policy)):
+        paths, plen = traverse(tree, roots, sims_per_tree, c_puct, vl_value, max_depth)
+        leaf, term = search_expand(tree, node_hash, paths, plen, sims_per_tree, move_lists, round_policy[r], round_value[r],
+                                   value_sign, value_quantum, zob)
+        terminals += int((term > 0).sum())
+        backup(tree, paths, plen, leaf, vl_value)
+    tree["terminal_leaves"] = terminals
+    return tree
+
+
 def gomoku_result(moves, board_size=15):
     """0 ongoing, 1 BLACK won, 2 WHITE won, 3 draw, judged on the last move (freestyle rules)."""
     mv = np.ascontiguousarray(moves, np.int16)

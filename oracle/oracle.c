@@ -436,3 +436,114 @@ void oracle_gomoku_planes3_batch(const signed char* stones, const unsigned char*
             planes[((size_t)b * 3 + 2) * S2 + p] = me == 1 ? 1.0f : 0.0f;
         }
 }
+
+/* ---------------------------------------------------------------------------
+ * One round of the leaf-parallel search on edge arrays: what happens between the
+ * descent (oracle_traverse) and the backup (oracle_backup).
+ *
+ * The reference's pieces: MCTSNode::expand creates one child per legal move
+ * (src/mcts/mcts_node.cpp:238-436; for Gomoku legal = empty cell, so the child
+ * set of a new node is its parent's minus the move just made);
+ * setPriorProbabilities gives child a the prior clamp(policy[a], 0, 1) with no
+ * renormalisation (:546-553); the batched loop backs up the network value of
+ * the leaf with the sign it has there (mcts_engine_batch_tree_simple.cpp:276-281),
+ * the serial loop uses the game result for a finished game
+ * (mcts_engine_search.cpp:588-610); the transposition table maps the Zobrist
+ * key of a position (stones + side to move,
+ * GomokuState::compute_hash_signature_internal, gomoku_state.cpp:947-958) to its
+ * node and the parent's child reference is pointed at a node found there
+ * (mcts_engine_batch_tree_simple.cpp:117-162).
+ *
+ * Order: the simulations of the round are taken one after another in index
+ * order (the reference leaves the order to its thread scheduler).  A leaf edge
+ * that an earlier simulation of the round already expanded is left alone; new
+ * nodes get consecutive ids; with the table on (node_hash != NULL), a position
+ * that already has a node in this game (node_hash equal; every node but the
+ * roots is in the table) is shared instead of created.
+ *
+ * root_moves[t * moves_stride + i]: the game so far (BLACK first).  zobrist: 451
+ * keys ([0,225) BLACK stones, [225,450) WHITE, [450] side to move).
+ * terminal_out[i]: 0 not terminal, 1 the side to move has lost, 2 draw. */
+static float quantized(float v, float q) { return q > 0.0f ? rintf(v * q) / q : v; }
+
+void oracle_search_expand(int32_t* N, float* W, float* P, int32_t* VL, uint32_t* legal,
+                          int32_t* node_visits, int32_t* child_node, uint64_t* node_hash,
+                          int32_t* n_used, int max_nodes, int n_children, int pitch, int mask_words,
+                          const int32_t* paths, const int32_t* path_len, int n_sims, int max_depth,
+                          int sims_per_tree, const int16_t* root_moves, const int32_t* root_n_moves,
+                          int moves_stride, int S, const float* policy, int policy_size,
+                          const float* value, float value_sign, float value_quantum,
+                          const uint64_t* zobrist, int n_trees, float* leaf_value_out,
+                          int32_t* terminal_out) {
+    int16_t game[32 * 32];
+    for (int i = 0; i < n_sims; ++i) {
+        const int tree = i / sims_per_tree;
+        const int len = path_len[i] > max_depth ? max_depth : path_len[i];
+        const int32_t* p = paths + (size_t)i * max_depth * 2;
+        const int n0 = root_n_moves[tree];
+        /* the leaf position: the root's moves, then the path's */
+        for (int k = 0; k < n0; ++k) game[k] = root_moves[(size_t)tree * moves_stride + k];
+        for (int d = 0; d < len; ++d) game[n0 + d] = (int16_t)p[2 * d + 1];
+        int term = 0;
+        float tv = 0.0f;
+        if (len > 0) {
+            const int res = oracle_gomoku_result(game, n0 + len, S);
+            if (res == 1 || res == 2) { term = 1; tv = -1.0f; }   /* the last mover won: the side to move has lost */
+            else if (res == 3) { term = 2; tv = 0.0f; }
+        }
+        terminal_out[i] = term;
+        leaf_value_out[i] = value_sign * (term ? tv : quantized(value[i], value_quantum));
+        if (len == 0 || term) continue;
+        const int parent = p[2 * (len - 1)], slot = p[2 * (len - 1) + 1];
+        const size_t e = (size_t)parent * pitch + slot;
+        if (child_node[e] >= 0) continue;                         /* expanded before, or earlier in this round */
+        uint64_t h = 0;
+        if (node_hash) {
+            const int mover = 1 + ((n0 + len - 1) & 1);           /* who made the move behind the edge */
+            h = node_hash[parent] ^ zobrist[(mover - 1) * 225 + slot] ^ zobrist[450];
+            if (h == 0) h = 1;
+            int found = -1;
+            for (int k = n_trees; k < *n_used && found < 0; ++k)
+                if (node_hash[k] == h) found = k;
+            if (found >= 0) { child_node[e] = found; continue; }  /* transposition: share the node */
+        }
+        if (*n_used >= max_nodes) continue;                       /* pool exhausted: the edge stays a leaf */
+        const int id = (*n_used)++;
+        const size_t row = (size_t)id * pitch;
+        const uint32_t* pm = legal + (size_t)parent * mask_words;
+        uint32_t* cm = legal + (size_t)id * mask_words;
+        for (int w = 0; w < mask_words; ++w) cm[w] = pm[w] & ~((w == (slot >> 5)) ? (1u << (slot & 31)) : 0u);
+        for (int s = 0; s < pitch; ++s) {
+            float pr = 0.0f;
+            if (s < n_children && ((cm[s >> 5] >> (s & 31)) & 1u) && s < policy_size)
+                pr = fminf(1.0f, fmaxf(0.0f, policy[(size_t)i * policy_size + s]));
+            N[row + s] = 0; W[row + s] = 0.0f; VL[row + s] = 0; P[row + s] = pr; child_node[row + s] = -1;
+        }
+        node_visits[id] = 0;
+        if (node_hash) node_hash[id] = h;
+        child_node[e] = id;
+    }
+}
+
+/* MCTSEngine::addDirichletNoise, src/mcts/mcts_engine_eval.cpp:83-110.  The noise
+ * part (:83-100): one Gamma(alpha, 1) draw per child (`gammas`, in child order),
+ * summed in fp32 and each divided by the sum; a zero sum gives uniform noise. */
+void oracle_dirichlet_normalize(float* gammas, int n) {
+    float sum = 0.0f;
+    for (int i = 0; i < n; ++i) sum += gammas[i];
+    for (int i = 0; i < n; ++i) gammas[i] = sum > 0.0f ? gammas[i] / sum : 1.0f / (float)n;
+}
+/* The mix (:102-109): prior = (1 - eps) * prior + eps * noise on every child of the
+ * root.  noise: [n][pitch], indexed by child slot. */
+void oracle_mix_noise(float* P, const uint32_t* legal, int n_children, int pitch, int mask_words,
+                      const int32_t* node_ids, int n, const float* noise, float eps) {
+    for (int i = 0; i < n; ++i) {
+        const int node = node_ids ? node_ids[i] : i;
+        const uint32_t* m = legal + (size_t)node * mask_words;
+        for (int s = 0; s < n_children; ++s)
+            if ((m[s >> 5] >> (s & 31)) & 1u) {
+                float* p = P + (size_t)node * pitch + s;
+                *p = (1.0f - eps) * *p + eps * noise[(size_t)i * pitch + s];
+            }
+    }
+}

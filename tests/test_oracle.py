@@ -293,3 +293,39 @@ def test_network_live_against_resnetmodel(oracle):
     lp, v, _ = net.forward(x)
     logits, val = net_ref.forward(w, x)
     assert np.abs(net_ref.log_softmax(logits) - lp).max() < 2e-6 and np.abs(val - v).max() < 2e-6
+
+
+def test_search_round_restatement_invariants(oracle):
+    """oracle.search_move (descent -> expansion -> backup per round) on seeded policy / value arrays: visits are
+    conserved, virtual loss returns to zero, a child's existence mask is its parent's minus the move, priors are
+    the clamped policy rows, and with the table on positions reached by two move orders share one node."""
+    rng = np.random.default_rng(5)
+    T, spt, R = 2, 8, 40
+    games = [[112, 113], [0, 224, 16]]
+    root_pol = rng.dirichlet(np.full(225, 0.5), T).astype(np.float32)
+    # every leaf gets the same policy, peaked on six cells: the trees go deep over permutations of those cells
+    row = np.full(225, 0.001, np.float32)
+    row[[40, 41, 42, 55, 56, 57]] = 0.16
+    pol = np.broadcast_to(row, (R, T * spt, 225)).copy()
+    val = (rng.integers(-256, 257, (R, T * spt)) / 256.0).astype(np.float32)
+    noise = np.zeros((T, 228), np.float32)
+    out = {}
+    for tt in (None, 3):
+        tr = oracle.search_move(games, root_pol, noise, 0.0, pol, val, spt, T * (1 + R * spt), value_quantum=256.0, tt_seed=tt)
+        n = tr["nodes"]
+        assert not tr["VL"].any()
+        assert (tr["N"][:T, :225].sum(1) == spt * R).all() and (tr["node_visits"][:T] == spt * R).all()
+        child = tr["child_node"][:n, :225]
+        parents, slots = np.nonzero(child >= 0)
+        incoming = np.zeros(n, np.int64)
+        for p, a in zip(parents, slots):
+            c = child[p, a]
+            lp = np.unpackbits(tr["legal_bits"][p].view(np.uint8), bitorder="little")[:225]
+            lc = np.unpackbits(tr["legal_bits"][c].view(np.uint8), bitorder="little")[:225]
+            assert lp[a] and not lc[a] and np.array_equal(np.delete(lp, a), np.delete(lc, a))
+            assert not tr["P"][c, :225][lc == 0].any()
+            incoming[c] += tr["N"][p, a]
+        assert np.array_equal(incoming[T:], tr["node_visits"][T:n])
+        out[tt] = (n, len(parents))
+    assert out[None][1] == out[None][0] - T            # a tree: one edge per node
+    assert out[3][0] < out[None][0] and out[3][1] > out[3][0] - T   # shared nodes: fewer nodes, more edges than nodes

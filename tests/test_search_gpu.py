@@ -1,8 +1,13 @@
-"""The leaf-parallel search loop on the device.  Whole-search results cannot be compared
-with the reference bit for bit (the reference shuffles children and races on virtual loss),
-so — like the reference's own engine tests (tests/mcts/mcts_engine_test.cpp:143-157) — the
-checks are invariants: visit conservation, legality, virtual loss back to zero, consistent
-expansion, probabilities that sum to one, and game-result handling on a forced win."""
+"""The leaf-parallel search loop on the device.
+
+Against the reference itself a whole search cannot be compared bit for bit (the reference
+shuffles children and races on virtual loss).  Two kinds of checks instead:
+  * against the CPU restatement (oracle.search_move: descent, expansion, root noise, transposition
+    redirect, backup, each citing the reference code it follows) fed the very network outputs the
+    device search saw: every array of the tree must be equal bit for bit;
+  * invariants, like the reference's own engine tests (tests/mcts/mcts_engine_test.cpp:143-157):
+    visit conservation, legality, virtual loss back to zero, consistent expansion, probabilities
+    that sum to one, and game-result handling on a forced win."""
 import numpy as np
 import pytest
 
@@ -60,6 +65,87 @@ def test_search_invariants(net):
     pi2, visits2, st2 = s.run(games, temperature=0.0)
     assert (visits2.sum(1) == sims).all() and ((pi2 == 1).sum(1) == 1).all() and (pi2.sum(1) == 1).all()
     assert np.array_equal(pi2.argmax(1), visits2.argmax(1))
+
+
+def open_four(extra_white=0):
+    black = [7 * 15 + c for c in (3, 4, 5, 6)]
+    white = [0, 14, 210, 224]
+    return [m for pair in zip(black, white) for m in pair]
+
+
+SEARCH_CASES = [
+    # name, games (None = seeded openings), trees, simulations per tree and round, rounds, table, noise weight, sign
+    ("openings", None, 8, 8, 12, False, 0.25, 1),
+    ("openings_table", None, 8, 8, 12, True, 0.25, 1),
+    ("long_table", None, 4, 16, 48, True, 0.0, 1),            # 768 simulations per tree: transpositions do occur
+    ("open_four_negamax", "four", 4, 16, 12, True, 0.25, -1),  # finished games among the leaves, duplicates in a batch
+    ("one_tree", None, 1, 32, 6, True, 0.25, 1),
+]
+
+
+@pytest.mark.parametrize("name,games,T,spt,R,table,eps,sign", SEARCH_CASES, ids=[c[0] for c in SEARCH_CASES])
+def test_search_equals_the_oracle_on_the_same_network_outputs(net, oracle, name, games, T, spt, R, table, eps, sign):
+    """The device search and the CPU restatement, given the same root policies, root noise and per-round
+    policy / value arrays: node count, existence masks, child links, visit counts, virtual loss, priors and
+    value sums must all be identical.  (Network values are rounded to multiples of 1/256 on both sides so
+    that the value sums do not depend on the order of the device's atomic additions.)"""
+    from omoknuni_small_b200 import capi
+    if games == "four":
+        games = [open_four()] * T
+    else:
+        games, _, _, _ = synth.make_gomoku_games(T, 15, seed=40 + T, max_moves=20)
+    s = capi.Search(net, n_trees=T, sims_per_move=spt * R, leaf_batch=T * spt, max_depth=32, c_puct=1.5, virtual_loss=3,
+                    dirichlet_alpha=0.3, dirichlet_epsilon=eps, value_sign=sign, transposition_table=table, seed=7)
+    s.debug_hooks(value_quantum=256.0, record_rounds=R)
+    for move in range(2):                                          # a second move on the same handle starts clean
+        pi, visits, st = s.run(games, temperature=1.0)
+        assert capi.device_error_code() == 0
+        pol, val, noise = s.record()
+        dev = s.tree()
+        max_nodes = T * (1 + R * spt)
+        ref = oracle.search_move(games, pol[0, :T], noise if eps > 0 else None, eps, pol[1:], val[1:], spt, max_nodes,
+                                 c_puct=1.5, vl_value=3, max_depth=32, value_sign=float(sign), value_quantum=256.0,
+                                 tt_seed=7 if table else None)
+        n = ref["nodes"]
+        assert dev["nodes"] == n == st["nodes"], (dev["nodes"], n)
+        assert st["terminal_leaves"] == ref["terminal_leaves"]
+        for key in ("legal_bits", "child_node", "N", "VL", "node_visits"):
+            assert np.array_equal(dev[key][:n], ref[key][:n]), key
+        assert np.array_equal(dev["P"][:n].view(np.uint32), ref["P"][:n].view(np.uint32)), "priors differ"
+        assert np.array_equal(dev["W"][:n].view(np.uint32), ref["W"][:n].view(np.uint32)), "value sums differ"
+        assert np.array_equal(visits, ref["N"][:T, :225])
+    if name == "long_table":
+        child = dev["child_node"][:n, :225]
+        assert (child >= 0).sum() > n - T, "the case is meant to contain transpositions"
+    if name == "open_four_negamax":
+        assert st["terminal_leaves"] > 0
+
+
+def test_expanded_priors_are_the_clamped_policy_and_root_noise_is_mixed_in(net, oracle):
+    """MCTSNode::setPriorProbabilities / addDirichletNoise, stated directly: a node created from leaf i has
+    P = clamp(policy[i], 0, 1) on its existing slots and 0 elsewhere; the root has
+    (1 - eps) * clamp(policy) + eps * noise with the noise summing to one over the empty cells."""
+    from omoknuni_small_b200 import capi
+    T, eps = 8, 0.25
+    games, _, _, _ = synth.make_gomoku_games(T, 15, seed=3, max_moves=20)
+    s = capi.Search(net, n_trees=T, sims_per_move=1, leaf_batch=T, max_depth=8, dirichlet_epsilon=eps, seed=11)
+    s.debug_hooks(0.0, 1)
+    s.run(games)
+    pol, val, noise = s.record()
+    tr = s.tree()
+    assert tr["nodes"] == 2 * T                                   # one simulation per tree: one new node each
+    for t in range(T):
+        legal = legal_of(tr["legal_bits"][t])
+        assert abs(noise[t, :225][legal].sum() - 1) < 1e-5 and not noise[t, :225][~legal].any() and (noise[t] >= 0).all()
+        want = (np.float32(1) - np.float32(eps)) * np.clip(pol[0, t], 0, 1) + np.float32(eps) * noise[t, :225]
+        assert np.array_equal(tr["P"][t, :225][legal], want.astype(np.float32)[legal]) and not tr["P"][t, :225][~legal].any()
+        a = int(np.nonzero(tr["child_node"][t, :225] >= 0)[0][0])  # the edge the simulation took
+        c = tr["child_node"][t, a]
+        lc = legal_of(tr["legal_bits"][c])
+        assert np.array_equal(tr["P"][c, :225][lc], np.clip(pol[1, t], 0, 1)[lc]) and not tr["P"][c, :225][~lc].any()
+    g = np.random.default_rng(0).gamma(0.3, 1.0, 200).astype(np.float32)
+    n = oracle.dirichlet_normalize(g)
+    assert abs(n.sum() - 1) < 1e-5 and np.array_equal(oracle.dirichlet_normalize(np.zeros(5, np.float32)), np.full(5, 0.2, np.float32))
 
 
 def test_search_takes_the_win_and_counts_terminals(net):
