@@ -59,7 +59,10 @@ int ob200_device_count(void);
  *  holds the child slots of node r; rows are `pitch` elements apart, pitch a
  *  multiple of 4 so that rows start on 16-byte boundaries; slots in
  *  [n_children, pitch) are padding and never selected.  Child slot order is
- *  the tie-break order (lowest slot wins).
+ *  the tie-break order (lowest slot wins).  N, W, P and VL must be 16-byte
+ *  aligned (checked: OB200_ERR_INVALID otherwise); legal_bits needs 4-byte
+ *  alignment only, but a 16-byte aligned mask array with mask_words a multiple of
+ *  4 is what lets large launches take the fastest selection kernel.
  * ------------------------------------------------------------------------- */
 typedef struct ob200_tree_view {
     int32_t* N;              /* [n_nodes][pitch] visit count of the child      */
@@ -153,6 +156,58 @@ int ob200_launch_traverse(const ob200_tree_view* tree, const int32_t* roots, int
                           int32_t sims_per_tree, float c_puct, int32_t vl_value,
                           int32_t max_depth, int32_t* paths_out, int32_t* path_len_out,
                           ob200_stream stream);
+
+/* ------------------------------------------------------------------------- *
+ *  Tree handle: the same operations with HOST buffers at the boundary, for a
+ *  C++ search loop that keeps its own control flow and moves the per-node work
+ *  of MCTSNode (include/mcts/mcts_node.h:39-101) to the device in batches - the
+ *  calls MCTSEngine::executeBatchedTreeSearch makes one node at a time at
+ *  src/mcts/mcts_engine_batch_tree_simple.cpp:100-111 (selectChild,
+ *  applyVirtualLoss) and :249-281 (expand, setPriorProbabilities, update,
+ *  revertVirtualLoss).  The handle owns the device arrays (ob200_tree_view_of
+ *  gives them to the ob200_launch_* layer), its stream and page-locked staging;
+ *  calls on one handle are serialised and return when their results are on the
+ *  host.  Node ids are dense, in creation order.
+ * ------------------------------------------------------------------------- */
+typedef struct ob200_tree ob200_tree;
+int ob200_tree_create(int32_t device, int32_t max_nodes, int32_t n_children, ob200_tree** out);
+void ob200_tree_destroy(ob200_tree* tree);
+/* Device arrays of the handle (n_nodes = capacity). */
+int ob200_tree_view_of(ob200_tree* tree, ob200_tree_view* view_out);
+int32_t ob200_tree_node_count(ob200_tree* tree);
+/* Forgets every node (a new search). */
+int ob200_tree_clear(ob200_tree* tree);
+/* Appends n nodes with zero statistics and no child links; node i gets the child
+ * slots whose bit is set in exists_bits[i * words_per_node ...] (words_per_node
+ * >= ceil(n_children / 32)).  The slot set of a node is what MCTSNode::expand
+ * (src/mcts/mcts_node.cpp:238-436) creates children for: the legal moves.
+ * *first_id_out = id of the first new node.  OB200_ERR_TOO_LARGE beyond capacity. */
+int ob200_tree_add_nodes(ob200_tree* tree, int32_t n, const uint32_t* exists_bits,
+                         int32_t words_per_node, int32_t* first_id_out);
+/* child_node[parent[i]][slot[i]] = child[i] (-1 unlinks): what expand's
+ * children_ vector and updateChildReference (include/mcts/mcts_node.h) hold. */
+int ob200_tree_link(ob200_tree* tree, int32_t n, const int32_t* parent, const int32_t* slot,
+                    const int32_t* child);
+/* ob200_launch_puct_select on HOST arrays: sel_out[i] for node_ids[i]. */
+int ob200_tree_select(ob200_tree* tree, const int32_t* node_ids, int32_t n, float c_puct,
+                      int32_t vl_value, int32_t apply_vl, int32_t* sel_out);
+/* amount > 0: MCTSNode::addVirtualLoss(amount) on edge (node_ids[i], slots[i]);
+ * amount < 0: removeVirtualLoss(-amount), clamped at zero; slots[i] < 0 skipped. */
+int ob200_tree_virtual_loss(ob200_tree* tree, const int32_t* node_ids, const int32_t* slots,
+                            int32_t n, int32_t amount);
+/* ob200_launch_backup on HOST arrays. */
+int ob200_tree_backup(ob200_tree* tree, const int32_t* paths, const int32_t* path_len,
+                      const float* leaf_values, int32_t n, int32_t max_depth, int32_t vl_value);
+/* ob200_launch_set_priors on HOST arrays (slot == action). */
+int ob200_tree_set_priors(ob200_tree* tree, const int32_t* node_ids, int32_t n, const float* policy,
+                          int32_t policy_size);
+/* Rows [first_node, first_node + n_nodes) of one array to / from the host: N, W, P,
+ * VL, CHILD rows of `pitch` 4-byte elements, EXISTS rows of `mask_words` words,
+ * VISITS one int per node (pitch / mask_words as ob200_tree_view_of reports). */
+enum { OB200_TREE_N = 0, OB200_TREE_W = 1, OB200_TREE_P = 2, OB200_TREE_VL = 3, OB200_TREE_CHILD = 4,
+       OB200_TREE_EXISTS = 5, OB200_TREE_VISITS = 6 };
+int ob200_tree_read(ob200_tree* tree, int32_t field, int32_t first_node, int32_t n_nodes, void* host_out);
+int ob200_tree_write(ob200_tree* tree, int32_t field, int32_t first_node, int32_t n_nodes, const void* host_in);
 
 /* ------------------------------------------------------------------------- *
  *  Board tensors: the activation format of the encoder and the network.

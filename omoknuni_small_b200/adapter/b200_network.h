@@ -62,6 +62,7 @@ public:
     B200Network& operator=(const B200Network&) = delete;
 
     bool ok() const { return net_ != nullptr; }
+    ob200_net* handle() const { return ready_ ? net_ : nullptr; }   // for the search adapter; null until finalised
 
     // One tensor under the reference module's name, e.g. "res_blocks.3.bn1.running_var".
     bool setTensor(const std::string& name, const float* data, int64_t numel) {

@@ -7,7 +7,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libomoknuni_b200.so")
-SOURCES = ["common.cpp", "select.cu", "encode.cu", "tower.cu", "tower_wide.cu", "tower_fused.cu", "tower_resident.cu", "heads.cu", "net.cu", "search.cu"]
+SOURCES = ["common.cpp", "select.cu", "encode.cu", "tower.cu", "tower_wide.cu", "tower_fused.cu", "tower_resident.cu", "heads.cu", "net.cu", "search.cu", "tree.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "-x", "cu"]
 

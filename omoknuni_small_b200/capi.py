@@ -71,6 +71,19 @@ SIGNATURES = {
                                           C.c_void_p]),
     "ob200_launch_traverse": (C.c_int, [C.POINTER(TreeView), C.c_void_p, C.c_int32, C.c_int32, C.c_float, C.c_int32,
                                         C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "ob200_tree_create": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
+    "ob200_tree_destroy": (None, [C.c_void_p]),
+    "ob200_tree_view_of": (C.c_int, [C.c_void_p, C.POINTER(TreeView)]),
+    "ob200_tree_node_count": (C.c_int32, [C.c_void_p]),
+    "ob200_tree_clear": (C.c_int, [C.c_void_p]),
+    "ob200_tree_add_nodes": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
+    "ob200_tree_link": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "ob200_tree_select": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_float, C.c_int32, C.c_int32, C.c_void_p]),
+    "ob200_tree_virtual_loss": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32]),
+    "ob200_tree_backup": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32]),
+    "ob200_tree_set_priors": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32]),
+    "ob200_tree_read": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "ob200_tree_write": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "ob200_board_tensor_positions": (C.c_int64, [C.c_int32, C.c_int32]),
     "ob200_board_tensor_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
     "ob200_launch_encode_gomoku": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,

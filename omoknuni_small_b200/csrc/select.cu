@@ -605,7 +605,10 @@ int ob200_launch_puct_select(const ob200_tree_view* tree, const int32_t* node_id
     if (int rc = require_device()) return rc;
     const int stage_bytes = (4 * tree->pitch * 4 + tree->mask_words * 4 + 127) & ~127;
     const int staged_smem = kStagedWarps * kStagedDepth * stage_bytes + kStagedWarps * kStagedDepth * 8;
-    if (tree->pitch <= kStagedMaxPitch && (tree->mask_words & 3) == 0 && n >= 1024 && staged_smem <= 227 * 1024) {
+    // the staged kernel fetches every row, the mask row included, with 16-byte-granular bulk copies: a mask array
+    // that is not 16-byte aligned (a slice of a larger buffer) takes the direct kernel instead
+    const bool mask_aligned = ((uintptr_t)tree->legal_bits & 15) == 0;
+    if (tree->pitch <= kStagedMaxPitch && (tree->mask_words & 3) == 0 && mask_aligned && n >= 1024 && staged_smem <= 227 * 1024) {
         // rows small enough to ring-buffer in shared memory: persistent staged kernel
         int dev = 0, sms = 0;
         OB200_CUDA_OK(cudaGetDevice(&dev));

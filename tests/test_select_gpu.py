@@ -142,6 +142,29 @@ def test_select_staged_path_with_node_ids(api, oracle):
     assert np.array_equal(dt.host("VL"), ref["VL"])
 
 
+def test_select_with_a_mask_array_that_is_only_4_byte_aligned(api, oracle):
+    """The existence-mask array may be a slice of a larger buffer: 4-byte alignment is all the ABI
+    asks of it.  A large launch then runs on the direct kernel (the staged one copies mask rows in
+    16-byte units) and gives the same indices."""
+    import ctypes as C
+    import torch
+    t = synth.make_selection_tree(2048, 225, seed=31)
+    dt = api.DeviceTree(t)
+    mw = t["legal_bits"].shape[1]
+    holder = torch.zeros(2048 * mw + 8, dtype=torch.int32, device="cuda")
+    shifted = holder[1:1 + 2048 * mw]                               # base + 4 bytes
+    shifted.copy_(dt.t["legal_bits"].reshape(-1))
+    assert shifted.data_ptr() % 16 == 4
+    dt.view.legal_bits = shifted.data_ptr()
+    sel = dt.select(c_puct=1.5, vl_value=3, apply_vl=False).cpu().numpy()
+    assert np.array_equal(sel, oracle.puct_select(synth.copy_tree(t), c_puct=1.5, vl_value=3, apply_vl=False))
+    # the statistics arrays do need 16 bytes: an argument check, nothing is launched
+    dt.view.N = dt.t["N"].data_ptr() + 4
+    with pytest.raises(api.Error) as e:
+        dt.select(c_puct=1.5, vl_value=3, apply_vl=False)
+    assert e.value.code == 1
+
+
 def test_vl_revert_clamps_at_zero(api, oracle):
     import torch
     t = synth.make_selection_tree(128, 225, seed=22, vl_max=2)
