@@ -329,21 +329,36 @@ def gpu_arm(args):
         if os.environ.get("OB200_BENCH_VERBOSE"):
             print("per-step ms:", " ".join(f"{m:.3f}" for m in ms), file=sys.stderr)
         # ---- e2e: host buffers through the public call ----
-        # inputs and outputs in page-locked host memory, allocated once (as an engine would keep them)
+        # inputs and outputs in page-locked host memory, allocated once (as an engine would keep them).  The caller
+        # keeps two batches in flight (ob200_net_submit_gomoku / ob200_net_wait): while one batch's 926 KB of results
+        # travel back, the next batch's kernels run.  Every step still copies its own inputs in and its own results out.
         pin = [torch.from_numpy(a).pin_memory() for a in (hist, nh, tm)]
         p_hist, p_nh, p_tm = (t_.numpy() for t_ in pin)
-        out_pol = torch.empty((B, 225), dtype=torch.float32).pin_memory()
-        out_val = torch.empty(B, dtype=torch.float32).pin_memory()
-        outs = (out_pol.numpy(), out_val.numpy())
+        out_bufs = [(torch.empty((B, 225), dtype=torch.float32).pin_memory(), torch.empty(B, dtype=torch.float32).pin_memory())
+                    for _ in range(2)]
+        outs2 = [(a.numpy(), b.numpy()) for a, b in out_bufs]
         for _ in range(2):
-            net.infer_gomoku(p_hist, p_nh, p_tm, out=outs)
-        e2e_s = 0.0
+            net.infer_gomoku(p_hist, p_nh, p_tm, out=outs2[0])
+        torch.cuda.synchronize()
+        flush.zero_()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        pending = []
+        for i in range(K):
+            if len(pending) == 2:
+                net.wait(pending.pop(0))
+            pending.append(net.submit_gomoku(p_hist, p_nh, p_tm, outs2[i % 2]))
+        for tk in pending:
+            net.wait(tk)
+        e2e_s = time.perf_counter() - t0
+        # the same call one batch at a time (submit + wait back to back), L2 flushed before each
+        e2e_sync_s = 0.0
         for _ in range(K):
             flush.zero_()
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            net.infer_gomoku(p_hist, p_nh, p_tm, out=outs)
-            e2e_s += time.perf_counter() - t0
+            net.infer_gomoku(p_hist, p_nh, p_tm, out=outs2[0])
+            e2e_sync_s += time.perf_counter() - t0
         # ---- the dominant kernel alone: the whole tower (one launch) ----
         bt_in = capi.encode_gomoku(d_hist, d_nh, d_tm, 15, 17, net.input_tensor_channels(), DT)
         tower_reps = 5
@@ -450,11 +465,13 @@ def gpu_arm(args):
                              virtual_loss=3, dirichlet_alpha=0.3, dirichlet_epsilon=0.25, value_sign=1,
                              transposition_table=True, seed=rank)
         search.run(openings)                                   # warm-up move
-        mcts_ms, mcts_sims, mcts_evals, mcts_moves = 0.0, 0, 0, max(2, min(K, 5))
+        mcts_ms, mcts_wall_ms, mcts_sims, mcts_evals, mcts_moves = 0.0, 0.0, 0, 0, max(2, min(K, 5))
         for _ in range(mcts_moves):
             flush.zero_()
             torch.cuda.synchronize()
+            t0 = time.perf_counter()
             _, _, st = search.run(openings)
+            mcts_wall_ms += (time.perf_counter() - t0) * 1e3          # the whole call as the caller sees it
             mcts_ms += st["device_ms"]; mcts_sims += st["simulations"]; mcts_evals += st["evaluations"]
             mcts_nodes = st["nodes"]
         torch.cuda.synchronize()
@@ -465,13 +482,34 @@ def gpu_arm(args):
         for wc in WIDE_NETS:
             wide.append(time_wide_net(capi, torch, wc, dev, local, rank, flush, timed, min(K, 5)))
     assert capi.device_error_code() == 0, "a kernel gave up on a bounded wait"
+    # ---- parity on every rank, after the timed regions: this rank's shard of selection inputs (225-wide and
+    # chess-wide rows) and of Gomoku positions against the CPU restatement, bit for bit ----
+    from oracle import capi as oc
+    sel_ok, enc_ok = 1, 1
+    for nodes, children, seed in ((4096, SEL_CHILDREN, 7), (256, SELW_CHILDREN, 9)):
+        tp = synth.make_selection_tree(nodes, children, seed=replicas.shard_seed(seed, rank))
+        ref = synth.copy_tree(tp)
+        dtp = capi.DeviceTree(tp, dev)
+        got = dtp.select(None, 1.5, 3, True).cpu().numpy()
+        want = oc.puct_select(ref, c_puct=1.5, vl_value=3, apply_vl=True)
+        ok = np.array_equal(got, want) and np.array_equal(dtp.host("VL"), ref["VL"])
+        dtp.vl_revert(torch.from_numpy(got).to(dev), 3)
+        oc.vl_revert(ref, want, 3)
+        sel_ok &= int(ok and np.array_equal(dtp.host("VL"), ref["VL"]) and np.array_equal(ref["VL"], tp["VL"]))
+    _, h_p, n_p, t_p = synth.make_gomoku_games(256, 15, seed=replicas.shard_seed(1000, rank))
+    for dt_enc in (capi.DTYPE_BF16, capi.DTYPE_F16):
+        bt_p = capi.encode_gomoku(torch.from_numpy(h_p).to(dev), torch.from_numpy(n_p).to(dev), torch.from_numpy(t_p).to(dev), 15, 19, 64, dt_enc)
+        torch.cuda.synchronize()
+        planes_p, pad_zero = capi.board_tensor_to_planes(bt_p.cpu().numpy().view(np.uint16), 15, 256, 64, dt_enc)
+        enc_ok &= int(pad_zero and np.array_equal(planes_p[:, :19], oc.gomoku_encode(h_p, n_p, t_p, 15, 19)) and not planes_p[:, 19:].any())
+    parity = replicas.sum_counters(dist, {"selection_ranks_ok": sel_ok, "encode_ranks_ok": enc_ok}, dev)
 
     reduced = replicas.max_over_ranks(
-        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms] + [v for _, m, tm in sweep for v in (m, tm)] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
-    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms = reduced[:9]
-    sweep = [(bs, reduced[9 + 2 * i], reduced[10 + 2 * i]) for i, (bs, _, _) in enumerate(sweep)]
+        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms, e2e_sync_s * 1e3, mcts_wall_ms] + [v for _, m, tm in sweep for v in (m, tm)] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
+    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms, e2e_sync_ms, mcts_wall_ms = reduced[:11]
+    sweep = [(bs, reduced[11 + 2 * i], reduced[12 + 2 * i]) for i, (bs, _, _) in enumerate(sweep)]
     for i, wr in enumerate(wide):
-        wr["ms"], wr["conv_ms"] = reduced[9 + 2 * len(sweep) + 2 * i], reduced[10 + 2 * len(sweep) + 2 * i]
+        wr["ms"], wr["conv_ms"] = reduced[11 + 2 * len(sweep) + 2 * i], reduced[12 + 2 * len(sweep) + 2 * i]
     totals = replicas.sum_counters(dist, capi.counters(), dev)   # the only cross-GPU step: per-GPU counters summed
     if rank == 0:
         flops_eval = synth.net_flops_per_eval(15, 17, 64, NET["blocks"], 225, NET["policy_head_ch"], NET["value_head_ch"])
@@ -489,7 +527,9 @@ def gpu_arm(args):
             "dtype": args.dtype, "data": "synthetic",
             "config": arm_config(B, world),
             "e2e": {"value": world * B * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": B * 34,
-                    "d2h_bytes_per_step": B * 226 * 4},
+                    "d2h_bytes_per_step": B * 226 * 4,
+                    "how": "ob200_net_submit_gomoku / ob200_net_wait with two batches in flight, pinned host buffers, wall clock over all steps",
+                    "one_batch_at_a_time": world * B * K / (e2e_sync_ms * 1e-3)},
             "gpu_launches": int(launches), "counters_all_gpus": totals,
             "tower_tflops": value / world * flops_eval / 1e12,
             "roofline": {"kernel": {2: "conv_tower_resident_kernel (stem + 20 convolutions 64->64 in one launch, boards resident in shared memory)",
@@ -522,6 +562,11 @@ def gpu_arm(args):
                          "traffic_source": "profiles/conv3x3_kernel_gomoku15_batch512.md (scaled by batch)"},
             "selection": {"value": SEL_NODES / (sel_ms * 1e-3), "unit": "node selections/s (select + VL apply + VL revert)",
                           "nodes": SEL_NODES, "children": SEL_CHILDREN, "ms_per_pass": sel_ms,
+                          # the whole pass (select + apply, then the clamped revert): 3,656 algorithmic bytes per node
+                          "pass_roofline": {"bound": "hbm", "achieved": sel_bytes / (sel_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                            "frac": sel_bytes / (sel_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "us_per_pass": sel_ms * 1e3,
+                                            "algorithmic_bytes": sel_bytes, "peak_source": peaks["source"]},
+                          # the select + apply kernel alone
                           "roofline": {"kernel": "puct_select_staged_kernel", "bound": "hbm",
                                        "achieved": selk_bytes / (selk_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                                        "unit": "GB/s", "frac": selk_bytes / (selk_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
@@ -535,11 +580,15 @@ def gpu_arm(args):
                                         "achieved_gbs": synth.selection_bytes_per_node(SELW_CHILDREN) * SELW_NODES / (selw_ms * 1e-3) / 1e9,
                                         "frac_of_hbm": synth.selection_bytes_per_node(SELW_CHILDREN) * SELW_NODES / (selw_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}},
             "mcts": {"value": world * mcts_sims / (mcts_ms * 1e-3), "unit": "simulations/s",
+                     # the same simulations over the wall clock around ob200_search_run (root set-up, noise sampling,
+                     # copies, the wait and the read-back of the visit counts included)
+                     "wall_value": world * mcts_sims / (mcts_wall_ms * 1e-3), "ms_per_move_wall": mcts_wall_ms / mcts_moves,
                      "leaf_evals_per_sec": world * mcts_evals / (mcts_ms * 1e-3),
                      "config": {"games_per_gpu": 64, "sims_per_move": 800, "leaf_batch": B, "c_puct": 1.5, "virtual_loss": 3,
                                 "dirichlet": [0.3, 0.25], "openings": "seeded random, 0-20 stones", "moves_timed": mcts_moves,
                                 "transposition_table": "on (device table, Zobrist keys)", "nodes_per_move": mcts_nodes},
-                     "ms_per_move": mcts_ms / mcts_moves, "timing": "CUDA events around each move, inside the library"},
+                     "ms_per_move": mcts_ms / mcts_moves,
+                     "timing": "value: CUDA events around the enqueued work of each move, inside the library; wall_value: perf_counter around the call"},
             "batch_sweep": [{"leaf_batch_per_gpu": bs, "ms_per_step": m, "value": world * bs / (m * 1e-3), "unit": UNIT,
                              "tower_tflops": bs / (m * 1e-3) * flops_eval / 1e12,
                              # the tower launch alone at this batch, as in `roofline`
@@ -548,6 +597,10 @@ def gpu_arm(args):
                             for bs, m, tm in sweep],
             "wide_towers": [wide_report(wr, world, peaks) for wr in wide],
             "clocks": clocks,
+            # ranks whose selection (indices and virtual-loss state after apply and after revert; 4,096 x 225 and
+            # 256 x 4,672 rows of the rank's own shard) and Gomoku encoding (256 positions, both storage types) equal
+            # the CPU restatement bit for bit
+            "parity": dict(parity, ranks=world),
         }
         if world == 1 and not args.no_cpu:
             base, _ = cpu_baseline(3, 1)
@@ -557,6 +610,9 @@ def gpu_arm(args):
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+    if parity["selection_ranks_ok"] != world or parity["encode_ranks_ok"] != world:
+        print(f"parity mismatch: {parity} of {world} ranks", file=sys.stderr)
+        sys.exit(1)
 
 
 def main():

@@ -429,6 +429,20 @@ int ob200_net_infer_planes(ob200_net* net, const float* planes, int32_t B, int32
 int ob200_net_infer_gomoku(ob200_net* net, const int16_t* history, const uint8_t* n_hist,
                            const uint8_t* to_move, int32_t B, float* policy_out,
                            float* value_out, int32_t out_kind);
+/* The same call split in two, so that one thread can keep two batches in flight:
+ * submit returns when the work is enqueued (*ticket_out names the call), wait
+ * returns when its results are in policy_out / value_out.  While the results of
+ * one batch travel back to the host the kernels of the next one run.  At most two
+ * calls may be pending per handle (a third submit returns OB200_ERR_STATE); all
+ * buffers of a call must stay valid and untouched until its wait returns; every
+ * submitted ticket must be waited for before the handle is destroyed.  (The
+ * one-call forms above overlap in the same way when several threads call them
+ * on one handle, which is how the reference's engines call NeuralNetwork::inference
+ * when no global queue is set, src/mcts/mcts_engine_batch_tree_simple.cpp:231-233.) */
+int ob200_net_submit_gomoku(ob200_net* net, const int16_t* history, const uint8_t* n_hist,
+                            const uint8_t* to_move, int32_t B, float* policy_out,
+                            float* value_out, int32_t out_kind, int32_t* ticket_out);
+int ob200_net_wait(ob200_net* net, int32_t ticket);
 /* DEVICE in, DEVICE out, asynchronous on `stream`: input is a board tensor of
  * ob200_net_input_tensor_channels() channels holding B <= max_batch boards
  * (ob200_board_tensor_bytes(board_size, B, channels) bytes, 16-byte aligned). */

@@ -79,26 +79,55 @@ public:
         std::vector<alphazero::mcts::NetworkOutput> out(n);
         for (auto& o : out) { o.policy.assign(A, 1.0f / (float)A); o.value = 0.0f; }   // the reference's default outputs
         if (n == 0 || !net_ || !ready_) return out;
+        // Requests larger than max_batch go slice by slice with two slices in flight: while the results of one
+        // travel back to the host, the next one's kernels run (ob200_net_submit_gomoku / ob200_net_wait).
+        struct Slice {
+            std::vector<float> policy, value;
+            std::vector<int16_t> hist; std::vector<uint8_t> nh, tm;
+            size_t first = 0; int B = 0; int32_t ticket = -1;
+        } slice[2];
         try {
-            std::vector<float> policy((size_t)cfg_.max_batch * A), value(cfg_.max_batch);
-            for (size_t first = 0; first < n; first += (size_t)cfg_.max_batch) {
+            for (auto& sl : slice) { sl.policy.resize((size_t)cfg_.max_batch * A); sl.value.resize(cfg_.max_batch); }
+            auto collect = [&](Slice& sl) {
+                if (sl.ticket < 0) return;
+                const int rc = ob200_net_wait(net_, sl.ticket);
+                sl.ticket = -1;
+                if (rc != OB200_OK) { report(rc); return; }                  // this slice keeps the default outputs
+                for (int b = 0; b < sl.B; ++b) {
+                    out[sl.first + b].policy.assign(sl.policy.begin() + (size_t)b * A, sl.policy.begin() + (size_t)(b + 1) * A);
+                    out[sl.first + b].value = sl.value[b];
+                }
+            };
+            int turn = 0;
+            for (size_t first = 0; first < n; first += (size_t)cfg_.max_batch, turn ^= 1) {
+                Slice& sl = slice[turn];
+                collect(sl);                                                 // the slice submitted two turns ago
                 const int B = (int)std::min(n - first, (size_t)cfg_.max_batch);
+                sl.first = first; sl.B = B;
                 const bool gomoku = allGomoku(states, first, B) && (cfg_.input_channels == 17 || cfg_.input_channels == 19);
                 int rc;
                 if (gomoku) {
                     // Gomoku: the device encoder needs only the last 16 moves and the side to move
-                    std::vector<int16_t> hist((size_t)B * 16, (int16_t)-1);
-                    std::vector<uint8_t> nh(B, 0), tm(B, 2);
+                    sl.hist.assign((size_t)B * 16, (int16_t)-1);
+                    sl.nh.assign(B, 0); sl.tm.assign(B, 2);
                     for (int b = 0; b < B; ++b) {
                         const auto& st = states[first + b];
                         if (!st) continue;                                  // null state: zero planes
                         const std::vector<int> mv = st->getMoveHistory();
                         const int k = (int)std::min<size_t>(16, mv.size());
-                        for (int i = 0; i < k; ++i) hist[(size_t)b * 16 + i] = (int16_t)mv[mv.size() - 1 - i];
-                        nh[b] = (uint8_t)k;
-                        tm[b] = (uint8_t)st->getCurrentPlayer();
+                        for (int i = 0; i < k; ++i) sl.hist[(size_t)b * 16 + i] = (int16_t)mv[mv.size() - 1 - i];
+                        sl.nh[b] = (uint8_t)k;
+                        sl.tm[b] = (uint8_t)st->getCurrentPlayer();
                     }
-                    rc = ob200_net_infer_gomoku(net_, hist.data(), nh.data(), tm.data(), B, policy.data(), value.data(),
+                    rc = ob200_net_submit_gomoku(net_, sl.hist.data(), sl.nh.data(), sl.tm.data(), B, sl.policy.data(), sl.value.data(),
+                                                 OB200_OUT_PROBS, &sl.ticket);
+                    if (rc == OB200_OK) continue;
+                    sl.ticket = -1;
+                    if (rc != OB200_ERR_STATE) { report(rc); continue; }
+                    // both of the handle's slots are taken (other threads are calling inference() too): finish our other
+                    // slice, then take this one through the one-call form, which waits its turn
+                    collect(slice[turn ^ 1]);
+                    rc = ob200_net_infer_gomoku(net_, sl.hist.data(), sl.nh.data(), sl.tm.data(), B, sl.policy.data(), sl.value.data(),
                                                 OB200_OUT_PROBS);
                 } else {
                     // any other game: the state's own planes, as prepareInputTensor gathers them (:258-260, :410-494)
@@ -113,16 +142,20 @@ public:
                                 std::memcpy(&planes[(((size_t)b * C + c) * S + r) * S], t[c][r].data(),
                                             sizeof(float) * std::min<size_t>(S, t[c][r].size()));
                     }
-                    rc = ob200_net_infer_planes(net_, planes.data(), B, C, policy.data(), value.data(), OB200_OUT_PROBS);
+                    rc = ob200_net_infer_planes(net_, planes.data(), B, C, sl.policy.data(), sl.value.data(), OB200_OUT_PROBS);
                 }
                 if (rc != OB200_OK) { report(rc); continue; }               // this slice keeps the default outputs
                 for (int b = 0; b < B; ++b) {
-                    out[first + b].policy.assign(policy.begin() + (size_t)b * A, policy.begin() + (size_t)(b + 1) * A);
-                    out[first + b].value = value[b];
+                    out[first + b].policy.assign(sl.policy.begin() + (size_t)b * A, sl.policy.begin() + (size_t)(b + 1) * A);
+                    out[first + b].value = sl.value[b];
                 }
             }
+            collect(slice[turn]);
+            collect(slice[turn ^ 1]);
         } catch (...) {
-            // as the reference: swallow and keep the defaults
+            // as the reference: swallow and keep the defaults (a slice still in flight writes into buffers of
+            // this frame: wait for it before they go away)
+            for (auto& sl : slice) if (sl.ticket >= 0) { ob200_net_wait(net_, sl.ticket); sl.ticket = -1; }
         }
         return out;
     }

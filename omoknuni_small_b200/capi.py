@@ -112,6 +112,9 @@ SIGNATURES = {
     "ob200_net_infer_planes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32]),
     "ob200_net_infer_gomoku": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
                                          C.c_void_p, C.c_int32]),
+    "ob200_net_submit_gomoku": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+                                          C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]),
+    "ob200_net_wait": (C.c_int, [C.c_void_p, C.c_int32]),
     "ob200_net_forward_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
                                            C.c_void_p]),
     "ob200_debug_bounded_wait": (C.c_int, [C.c_int32, C.c_void_p]),
@@ -403,6 +406,23 @@ class Net:
                                            tm.ctypes.data_as(C.c_void_p), B, pol.ctypes.data_as(C.c_void_p),
                                            val.ctypes.data_as(C.c_void_p), out_kind))
         return pol, val
+
+    def submit_gomoku(self, history, n_hist, to_move, out, out_kind=OUT_PROBS):
+        """Asynchronous infer_gomoku: enqueues the call and returns a ticket for wait().  The arrays (C-contiguous
+        int16 / uint8 / uint8 inputs, float32 outputs in `out`) must stay alive and untouched until then; at most two
+        calls may be pending."""
+        pol, val = out
+        B = history.shape[0]
+        assert history.dtype == np.int16 and n_hist.dtype == np.uint8 and to_move.dtype == np.uint8
+        assert pol.dtype == np.float32 and val.dtype == np.float32 and pol.shape == (B, self.policy_size) and val.shape == (B,)
+        ticket = C.c_int32(-1)
+        check(lib().ob200_net_submit_gomoku(self.h, history.ctypes.data_as(C.c_void_p), n_hist.ctypes.data_as(C.c_void_p),
+                                            to_move.ctypes.data_as(C.c_void_p), B, pol.ctypes.data_as(C.c_void_p),
+                                            val.ctypes.data_as(C.c_void_p), out_kind, C.byref(ticket)))
+        return ticket.value
+
+    def wait(self, ticket):
+        check(lib().ob200_net_wait(self.h, ticket))
 
     def input_tensor_channels(self):
         return int(lib().ob200_net_input_tensor_channels(self.h))

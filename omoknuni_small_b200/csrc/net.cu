@@ -9,6 +9,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <condition_variable>
 #include <map>
 #include <mutex>
 #include <string>
@@ -48,12 +49,26 @@ struct ob200_net {
     float *hp = nullptr, *hv = nullptr, *hidden = nullptr;
     // device: policy as convolution planes (policy_kind 1): 1x1 convolution on the tensor cores
     void* pol_w = nullptr; float* pol_b = nullptr; float* pol_planes = nullptr; int pol_cout = 0;
-    // device + pinned host staging of the host-buffer calls
-    float *d_planes = nullptr, *d_policy = nullptr, *d_value = nullptr;
-    int16_t* d_hist = nullptr;      // [histories | history lengths | sides to move] of the call in flight
-    float *h_planes = nullptr, *h_policy = nullptr, *h_value = nullptr;
-    int16_t* h_hist = nullptr;
-    int* h_err = nullptr;           // pinned landing word for the device error code
+    // device + pinned host staging of the host-buffer calls.  Two calls may be in flight per handle: while the
+    // results of one travel back to the host on the copy stream, the next one's kernels run.  What the two must
+    // not share is doubled (a "slot"): the device output arrays, their pinned landing buffers, the input staging.
+    struct Slot {
+        bool busy = false;
+        int B = 0;
+        float *d_policy = nullptr, *d_value = nullptr;
+        float *h_policy = nullptr, *h_value = nullptr;
+        int16_t* h_hist = nullptr;
+        int* h_err = nullptr;       // pinned landing word for the device error code
+        float *user_policy = nullptr, *user_value = nullptr;
+        bool direct = false;        // results are copied straight into the caller's page-locked buffers
+        cudaEvent_t computed = nullptr, done = nullptr;
+    } slot[2];
+    std::condition_variable slot_cv;
+    cudaStream_t copy_stream = nullptr;   // device -> host copies of results
+    cudaEvent_t planes_copied = nullptr;  // the planes staging buffer has been read by its host -> device copy
+    float *d_planes = nullptr;
+    int16_t* d_hist = nullptr;      // [histories | history lengths | sides to move] of the call being enqueued
+    float *h_planes = nullptr;
     size_t planes_capacity = 0;     // floats per staging buffer
     std::vector<void*> owned_dev, owned_host;
 };
@@ -213,6 +228,9 @@ void ob200_net_destroy(ob200_net* n) {
     cudaSetDevice(n->cfg.device);
     if (n->stream) { cudaStreamSynchronize(n->stream); cudaStreamDestroy(n->stream); }
     if (n->side_stream) { cudaStreamSynchronize(n->side_stream); cudaStreamDestroy(n->side_stream); }
+    if (n->copy_stream) { cudaStreamSynchronize(n->copy_stream); cudaStreamDestroy(n->copy_stream); }
+    if (n->planes_copied) cudaEventDestroy(n->planes_copied);
+    for (auto& sl : n->slot) { if (sl.computed) cudaEventDestroy(sl.computed); if (sl.done) cudaEventDestroy(sl.done); }
     if (n->fork_ev) cudaEventDestroy(n->fork_ev);
     if (n->join_ev) cudaEventDestroy(n->join_ev);
     for (void* p : n->owned_dev) cudaFree(p);
@@ -358,21 +376,28 @@ int ob200_net_finalize(ob200_net* n) {
     if (int rc = dev_alloc(n, &n->hp, MB * (planes_policy ? 1 : Kp), false)) return rc;
     if (int rc = dev_alloc(n, &n->hv, MB * Kv, false)) return rc;
     if (int rc = dev_alloc(n, &n->hidden, MB * H, false)) return rc;
-    if (int rc = dev_alloc(n, &n->d_policy, MB * A, false)) return rc;
-    if (int rc = dev_alloc(n, &n->d_value, MB, false)) return rc;
+    for (auto& sl : n->slot) {
+        if (int rc = dev_alloc(n, &sl.d_policy, MB * A, false)) return rc;
+        if (int rc = dev_alloc(n, &sl.d_value, MB, false)) return rc;
+        if (int rc = host_alloc(n, &sl.h_policy, MB * A)) return rc;
+        if (int rc = host_alloc(n, &sl.h_value, MB)) return rc;
+        if (int rc = host_alloc(n, &sl.h_hist, MB * 17)) return rc;
+        if (int rc = host_alloc(n, &sl.h_err, 1)) return rc;
+        *sl.h_err = 0;
+        OB200_CUDA_OK(cudaEventCreateWithFlags(&sl.computed, cudaEventDisableTiming));
+        OB200_CUDA_OK(cudaEventCreateWithFlags(&sl.done, cudaEventDisableTiming));
+    }
     n->planes_capacity = MB * (size_t)std::max(c.input_channels, 19) * S2;
     if (int rc = dev_alloc(n, &n->d_planes, n->planes_capacity, false)) return rc;
     // move histories, history lengths and sides to move of a call share one staging block (34 bytes per board,
     // packed for the call's batch size), so that they reach the device in one copy
     if (int rc = dev_alloc(n, &n->d_hist, MB * 17, false)) return rc;
     if (int rc = host_alloc(n, &n->h_planes, n->planes_capacity)) return rc;
-    if (int rc = host_alloc(n, &n->h_policy, MB * A)) return rc;
-    if (int rc = host_alloc(n, &n->h_value, MB)) return rc;
-    if (int rc = host_alloc(n, &n->h_hist, MB * 17)) return rc;
-    if (int rc = host_alloc(n, &n->h_err, 1)) return rc;
-    *n->h_err = 0;
     OB200_CUDA_OK(cudaStreamCreateWithFlags(&n->stream, cudaStreamNonBlocking));
     OB200_CUDA_OK(cudaStreamCreateWithFlags(&n->side_stream, cudaStreamNonBlocking));
+    OB200_CUDA_OK(cudaStreamCreateWithFlags(&n->copy_stream, cudaStreamNonBlocking));
+    OB200_CUDA_OK(cudaEventCreateWithFlags(&n->planes_copied, cudaEventDisableTiming));
+    OB200_CUDA_OK(cudaEventRecord(n->planes_copied, n->stream));
     OB200_CUDA_OK(cudaEventCreateWithFlags(&n->fork_ev, cudaEventDisableTiming));
     OB200_CUDA_OK(cudaEventCreateWithFlags(&n->join_ev, cudaEventDisableTiming));
     OB200_CUDA_OK(cudaDeviceSynchronize());
@@ -509,30 +534,76 @@ bool is_pinned_host(const void* p) {
     return a.type == cudaMemoryTypeHost;
 }
 
-// Copies results back, waits, and reports a kernel that gave up on a wait.  Outputs the caller
-// keeps in page-locked memory are written by the copy engine directly; pageable ones go through
-// the handle's pinned staging buffers.
-int finish_host_call(ob200_net* n, int B, float* policy_out, float* value_out) {
+// A free slot for a host-buffer call; with `wait` the caller sleeps until one of the two is handed back.
+// The handle's mutex is held (lk).  Returns the slot index, or -1 when both are pending and !wait.
+int acquire_slot(ob200_net* n, std::unique_lock<std::mutex>& lk, bool wait) {
+    for (;;) {
+        for (int i = 0; i < 2; ++i)
+            if (!n->slot[i].busy) { n->slot[i].busy = true; return i; }
+        if (!wait) return -1;
+        n->slot_cv.wait(lk);
+    }
+}
+void release_slot(ob200_net* n, int i) {
+    { std::lock_guard<std::mutex> lk(n->mu); n->slot[i].busy = false; }
+    n->slot_cv.notify_one();
+}
+
+// After the forward has been enqueued on the handle's stream: results travel back on the copy stream, so the
+// next call's kernels can run meanwhile.  Outputs the caller keeps in page-locked memory are written by the
+// copy engine directly; pageable ones go through the slot's pinned buffers (copied out in wait_slot).
+int enqueue_results(ob200_net* n, int si, int B, float* policy_out, float* value_out) {
+    ob200_net::Slot& sl = n->slot[si];
     const size_t A = n->cfg.policy_size;
-    const bool direct = is_pinned_host(policy_out) && is_pinned_host(value_out);
-    float* pol_dst = direct ? policy_out : n->h_policy;
-    float* val_dst = direct ? value_out : n->h_value;
-    OB200_CUDA_OK(cudaMemcpyAsync(pol_dst, n->d_policy, (size_t)B * A * sizeof(float), cudaMemcpyDeviceToHost, n->stream));
-    OB200_CUDA_OK(cudaMemcpyAsync(val_dst, n->d_value, (size_t)B * sizeof(float), cudaMemcpyDeviceToHost, n->stream));
+    sl.B = B; sl.user_policy = policy_out; sl.user_value = value_out;
+    sl.direct = is_pinned_host(policy_out) && is_pinned_host(value_out);
+    OB200_CUDA_OK(cudaEventRecord(sl.computed, n->stream));
+    OB200_CUDA_OK(cudaStreamWaitEvent(n->copy_stream, sl.computed, 0));
+    OB200_CUDA_OK(cudaMemcpyAsync(sl.direct ? policy_out : sl.h_policy, sl.d_policy, (size_t)B * A * sizeof(float), cudaMemcpyDeviceToHost, n->copy_stream));
+    OB200_CUDA_OK(cudaMemcpyAsync(sl.direct ? value_out : sl.h_value, sl.d_value, (size_t)B * sizeof(float), cudaMemcpyDeviceToHost, n->copy_stream));
     int* errw = device_error_word();
-    if (errw) OB200_CUDA_OK(cudaMemcpyAsync(n->h_err, errw, sizeof(int), cudaMemcpyDeviceToHost, n->stream));
-    OB200_CUDA_OK(cudaStreamSynchronize(n->stream));
-    const int err = errw ? *n->h_err : 0;
-    if (err) {
-        cudaMemsetAsync(errw, 0, sizeof(int), n->stream);
-        cudaStreamSynchronize(n->stream);
-        return set_error(OB200_ERR_TIMEOUT, "a tower kernel gave up on a bounded wait (role code %d); outputs are not valid", err);
-    }
-    if (!direct) {
-        std::memcpy(policy_out, n->h_policy, (size_t)B * A * sizeof(float));
-        std::memcpy(value_out, n->h_value, (size_t)B * sizeof(float));
-    }
+    if (errw) OB200_CUDA_OK(cudaMemcpyAsync(sl.h_err, errw, sizeof(int), cudaMemcpyDeviceToHost, n->copy_stream));
+    OB200_CUDA_OK(cudaEventRecord(sl.done, n->copy_stream));
     return OB200_OK;
+}
+
+// Waits for a slot's results, reports a kernel that gave up on a bounded wait, hands the slot back.
+int wait_slot(ob200_net* n, int si) {
+    ob200_net::Slot& sl = n->slot[si];
+    const size_t A = n->cfg.policy_size;
+    const cudaError_t e = cudaEventSynchronize(sl.done);
+    int rc = OB200_OK;
+    if (e != cudaSuccess) rc = set_error(OB200_ERR_CUDA, "waiting for the results failed: %s", cudaGetErrorString(e));
+    else if (*sl.h_err) {
+        const int err = *sl.h_err;
+        *sl.h_err = 0;
+        int* errw = device_error_word();
+        if (errw) { cudaMemsetAsync(errw, 0, sizeof(int), n->copy_stream); cudaStreamSynchronize(n->copy_stream); }
+        rc = set_error(OB200_ERR_TIMEOUT, "a tower kernel gave up on a bounded wait (role code %d); outputs are not valid", err);
+    } else if (!sl.direct) {
+        std::memcpy(sl.user_policy, sl.h_policy, (size_t)sl.B * A * sizeof(float));
+        std::memcpy(sl.user_value, sl.h_value, (size_t)sl.B * sizeof(float));
+    }
+    release_slot(n, si);
+    return rc;
+}
+
+// Gomoku histories -> staging -> device -> encoder -> forward -> results on their way back.  Handle mutex held.
+int enqueue_gomoku(ob200_net* n, int si, const int16_t* history, const uint8_t* n_hist, const uint8_t* to_move, int32_t B,
+                   float* policy_out, float* value_out, int32_t out_kind) {
+    const ob200_net_config& c = n->cfg;
+    ob200_net::Slot& sl = n->slot[si];
+    const size_t hist_bytes = (size_t)B * 16 * sizeof(int16_t);
+    uint8_t* h8 = reinterpret_cast<uint8_t*>(sl.h_hist);
+    uint8_t* d8 = reinterpret_cast<uint8_t*>(n->d_hist);
+    std::memcpy(h8, history, hist_bytes);
+    std::memcpy(h8 + hist_bytes, n_hist, (size_t)B);
+    std::memcpy(h8 + hist_bytes + B, to_move, (size_t)B);
+    OB200_CUDA_OK(cudaMemcpyAsync(d8, h8, hist_bytes + 2 * (size_t)B, cudaMemcpyHostToDevice, n->stream));
+    if (int rc = launch_encode_gomoku(n->d_hist, d8 + hist_bytes, d8 + hist_bytes + B, B, c.board_size, c.input_channels, n->cin_pad,
+                                      n->act_in, n->stream, c.tower_dtype)) return rc;
+    if (int rc = forward_device(n, n->act_in, B, sl.d_policy, sl.d_value, out_kind, n->stream)) return rc;
+    return enqueue_results(n, si, B, policy_out, value_out);
 }
 
 }  // namespace
@@ -554,7 +625,7 @@ extern "C" {
 int ob200_net_infer_planes(ob200_net* n, const float* planes, int32_t B, int32_t C, float* policy_out,
                            float* value_out, int32_t out_kind) {
     if (int rc = check_call(n, B, planes, policy_out, value_out, out_kind, "ob200_net_infer_planes")) return rc;
-    std::lock_guard<std::mutex> lk(n->mu);
+    std::unique_lock<std::mutex> lk(n->mu);
     const ob200_net_config& c = n->cfg;
     const size_t S2 = (size_t)c.board_size * c.board_size;
     if (C < 1 || (size_t)B * C * S2 > n->planes_capacity)
@@ -563,35 +634,69 @@ int ob200_net_infer_planes(ob200_net* n, const float* planes, int32_t B, int32_t
     // as ResNetModel::forward: the first min(C, input_channels) planes are used (:117-147);
     // planes beyond input_channels are dropped while staging
     const int used = C < c.input_channels ? C : c.input_channels;
+    const int si = acquire_slot(n, lk, true);
+    OB200_CUDA_OK(cudaEventSynchronize(n->planes_copied));      // the previous call's copy has read the staging buffer
     for (int b = 0; b < B; ++b)
         std::memcpy(n->h_planes + (size_t)b * used * S2, planes + (size_t)b * C * S2, (size_t)used * S2 * sizeof(float));
-    OB200_CUDA_OK(cudaMemcpyAsync(n->d_planes, n->h_planes, (size_t)B * used * S2 * sizeof(float), cudaMemcpyHostToDevice, n->stream));
-    if (int rc = launch_planes_to_board_tensor(n->d_planes, B, used, c.board_size, n->cin_pad, n->act_in, n->stream, c.tower_dtype)) return rc;
-    if (int rc = forward_device(n, n->act_in, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
-    return finish_host_call(n, B, policy_out, value_out);
+    int rc = OB200_OK;
+    auto step = [&](int r) { if (!rc) rc = r; };
+    if (cudaMemcpyAsync(n->d_planes, n->h_planes, (size_t)B * used * S2 * sizeof(float), cudaMemcpyHostToDevice, n->stream) != cudaSuccess ||
+        cudaEventRecord(n->planes_copied, n->stream) != cudaSuccess)
+        rc = set_error(OB200_ERR_CUDA, "ob200_net_infer_planes: copying the planes to the device failed");
+    step(rc ? rc : launch_planes_to_board_tensor(n->d_planes, B, used, c.board_size, n->cin_pad, n->act_in, n->stream, c.tower_dtype));
+    step(rc ? rc : forward_device(n, n->act_in, B, n->slot[si].d_policy, n->slot[si].d_value, out_kind, n->stream));
+    step(rc ? rc : enqueue_results(n, si, B, policy_out, value_out));
+    lk.unlock();
+    if (rc) { release_slot(n, si); return rc; }
+    return wait_slot(n, si);
+}
+
+static int check_gomoku(ob200_net* n, const uint8_t* n_hist, const uint8_t* to_move, const char* who) {
+    if (!n_hist || !to_move) return set_error(OB200_ERR_INVALID, "%s: null argument", who);
+    const ob200_net_config& c = n->cfg;
+    if (c.input_channels != 17 && c.input_channels != 19)
+        return set_error(OB200_ERR_UNSUPPORTED, "%s: the Gomoku encoder makes 17 or 19 planes; the network takes %d", who, c.input_channels);
+    return OB200_OK;
 }
 
 int ob200_net_infer_gomoku(ob200_net* n, const int16_t* history, const uint8_t* n_hist, const uint8_t* to_move,
                            int32_t B, float* policy_out, float* value_out, int32_t out_kind) {
     if (int rc = check_call(n, B, history, policy_out, value_out, out_kind, "ob200_net_infer_gomoku")) return rc;
-    if (!n_hist || !to_move) return set_error(OB200_ERR_INVALID, "ob200_net_infer_gomoku: null argument");
-    std::lock_guard<std::mutex> lk(n->mu);
-    const ob200_net_config& c = n->cfg;
-    if (c.input_channels != 17 && c.input_channels != 19)
-        return set_error(OB200_ERR_UNSUPPORTED, "ob200_net_infer_gomoku: the Gomoku encoder makes 17 or 19 planes; the network takes %d",
-                         c.input_channels);
-    OB200_CUDA_OK(cudaSetDevice(c.device));
-    const size_t hist_bytes = (size_t)B * 16 * sizeof(int16_t);
-    uint8_t* h8 = reinterpret_cast<uint8_t*>(n->h_hist);
-    uint8_t* d8 = reinterpret_cast<uint8_t*>(n->d_hist);
-    std::memcpy(h8, history, hist_bytes);
-    std::memcpy(h8 + hist_bytes, n_hist, (size_t)B);
-    std::memcpy(h8 + hist_bytes + B, to_move, (size_t)B);
-    OB200_CUDA_OK(cudaMemcpyAsync(d8, h8, hist_bytes + 2 * (size_t)B, cudaMemcpyHostToDevice, n->stream));
-    if (int rc = launch_encode_gomoku(n->d_hist, d8 + hist_bytes, d8 + hist_bytes + B, B, c.board_size, c.input_channels, n->cin_pad,
-                                      n->act_in, n->stream, c.tower_dtype)) return rc;
-    if (int rc = forward_device(n, n->act_in, B, n->d_policy, n->d_value, out_kind, n->stream)) return rc;
-    return finish_host_call(n, B, policy_out, value_out);
+    if (int rc = check_gomoku(n, n_hist, to_move, "ob200_net_infer_gomoku")) return rc;
+    std::unique_lock<std::mutex> lk(n->mu);
+    OB200_CUDA_OK(cudaSetDevice(n->cfg.device));
+    const int si = acquire_slot(n, lk, true);
+    const int rc = enqueue_gomoku(n, si, history, n_hist, to_move, B, policy_out, value_out, out_kind);
+    lk.unlock();
+    if (rc) { release_slot(n, si); return rc; }
+    return wait_slot(n, si);      // without the handle's mutex: another thread's call is enqueued meanwhile
+}
+
+int ob200_net_submit_gomoku(ob200_net* n, const int16_t* history, const uint8_t* n_hist, const uint8_t* to_move,
+                            int32_t B, float* policy_out, float* value_out, int32_t out_kind, int32_t* ticket_out) {
+    if (!ticket_out) return set_error(OB200_ERR_INVALID, "ob200_net_submit_gomoku: null ticket");
+    *ticket_out = -1;
+    if (int rc = check_call(n, B, history, policy_out, value_out, out_kind, "ob200_net_submit_gomoku")) return rc;
+    if (int rc = check_gomoku(n, n_hist, to_move, "ob200_net_submit_gomoku")) return rc;
+    std::unique_lock<std::mutex> lk(n->mu);
+    OB200_CUDA_OK(cudaSetDevice(n->cfg.device));
+    const int si = acquire_slot(n, lk, false);
+    if (si < 0) return set_error(OB200_ERR_STATE, "ob200_net_submit_gomoku: two calls are pending on this handle already; wait for one first");
+    const int rc = enqueue_gomoku(n, si, history, n_hist, to_move, B, policy_out, value_out, out_kind);
+    lk.unlock();
+    if (rc) { release_slot(n, si); return rc; }
+    *ticket_out = si;
+    return OB200_OK;
+}
+
+int ob200_net_wait(ob200_net* n, int32_t ticket) {
+    if (!n || ticket < 0 || ticket > 1) return set_error(OB200_ERR_INVALID, "ob200_net_wait: bad handle or ticket %d", ticket);
+    {
+        std::lock_guard<std::mutex> lk(n->mu);
+        if (!n->slot[ticket].busy) return set_error(OB200_ERR_STATE, "ob200_net_wait: ticket %d is not pending", ticket);
+    }
+    if (cudaSetDevice(n->cfg.device) != cudaSuccess) { cudaGetLastError(); return set_error(OB200_ERR_CUDA, "ob200_net_wait: cannot select the device"); }
+    return wait_slot(n, ticket);
 }
 
 int ob200_net_forward_device(ob200_net* n, const void* input_board_tensor, int32_t B, float* policy_out,

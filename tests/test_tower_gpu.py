@@ -585,3 +585,53 @@ def test_inference_argument_errors(api):
     assert e.value.code == 7                                   # beyond max_batch
     with pytest.raises(api.Error):
         api.Net(17, 15, 1, 96, 225)                            # tower width outside this build
+
+
+def test_two_batches_in_flight_give_the_same_results(api):
+    """submit / wait with two calls pending (the results of one batch travel back while the next one computes)
+    and the one-call form from four threads at once: every batch gets exactly the outputs of a plain
+    synchronous call; a third submit without a wait is refused with a status."""
+    import threading
+    import torch
+    shapes = synth.net_tensor_shapes(15, 17, 64, 3, 225, 2, 1)
+    w = synth.make_weights(shapes, seed=8, init="torch_default", bn="random")
+    B, n_batches = 200, 7
+    net = make_net(api, w, dict(cin=17, S=15, blocks=3, F=64, A=225, pc=2, vc=1), 256)
+    batches = [synth.make_gomoku_games(B, 15, seed=600 + i)[1:] for i in range(n_batches)]
+    want = [net.infer_gomoku(h, nh, tm) for h, nh, tm in batches]
+    # pinned and pageable output buffers alike
+    for pinned in (True, False):
+        outs = []
+        for _ in range(n_batches):
+            if pinned:
+                p, v = torch.empty((B, 225), dtype=torch.float32).pin_memory(), torch.empty(B, dtype=torch.float32).pin_memory()
+                outs.append((p.numpy(), v.numpy(), p, v))
+            else:
+                outs.append((np.empty((B, 225), np.float32), np.empty(B, np.float32)))
+        tickets = []
+        for i, (h, nh, tm) in enumerate(batches):
+            if len(tickets) == 2:
+                net.wait(tickets.pop(0))
+            tickets.append(net.submit_gomoku(h, nh, tm, outs[i][:2]))
+        with pytest.raises(api.Error) as e:                                  # both slots are pending here
+            net.submit_gomoku(*batches[0], outs[0][:2])
+        assert e.value.code == 4
+        for t in tickets:
+            net.wait(t)
+        with pytest.raises(api.Error):
+            net.wait(0)                                                      # nothing pending any more
+        for i in range(n_batches):
+            assert np.array_equal(outs[i][0], want[i][0]) and np.array_equal(outs[i][1], want[i][1]), i
+    got = [None] * n_batches
+
+    def worker(k):
+        for i in range(k, n_batches, 4):
+            got[i] = net.infer_gomoku(*batches[i])
+    threads = [threading.Thread(target=worker, args=(k,)) for k in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for i in range(n_batches):
+        assert np.array_equal(got[i][0], want[i][0]) and np.array_equal(got[i][1], want[i][1]), i
+    assert api.device_error_code() == 0
