@@ -10,16 +10,20 @@
 // otherwise competes with the tensor cores' operand reads - and every hand-over through global
 // memory.  What is left is the MMA issue rate (128x64x16 tcgen05.mma: 48 cycles each, 36 per tile).
 //
-//   * Two boards are in flight per CTA, each with its own MMA-issuing warp: while board 0's layer-l
-//     accumulators are drained and written back as layer l+1's input, the tensor cores run board 1's
-//     layer l (board 1 runs two thirds of a layer behind board 0).  The thread that issues
-//     tcgen05.mma pays for every instruction between two MMAs and waits at every layer boundary; with
-//     two issuers the tensor cores always have the other board's MMAs to take.  TMEM holds both
-//     boards' accumulators for two consecutive layers (2 x 2 boards x 2 tiles x 64 columns = 512).
+//   * Two boards are in flight per CTA, and every 128-row TILE of a board has its own MMA-issuing warp
+//     (four issuers for two 15x15 boards): while board 0's layer-l accumulators are drained and written
+//     back as layer l+1's input, the tensor cores run board 1's layer l (board 1 runs two thirds of a
+//     layer behind board 0).  The thread that issues tcgen05.mma is held by every MMA and pays for every
+//     instruction between two of them (descriptor arithmetic, the waits for weights, the commits:
+//     56-59 cycles per MMA for one thread, measured, against 48 for the instruction itself) and waits at
+//     every layer boundary; with an issuer per tile the tensor cores take the next MMA from whichever
+//     thread has one ready.  MMAs of one tile stay in one thread, so their order - and with it every
+//     bit of the result - does not depend on the interleaving.  TMEM holds both boards' accumulators
+//     for two consecutive layers (2 x 2 boards x 2 tiles x 64 columns = 512).
 //   * Weights stream from L2 through a one-layer ring of three 24 KB blocks (three taps each): the
-//     MMAs of a board go tap by tap (both tiles of a tap back to back), a block is handed back by a
-//     tcgen05.commit of each board's issuer, and the loader refills it with the same taps of the
-//     next layer when both have come in.
+//     MMAs of a tile go tap by tap, a block is handed back by a tcgen05.commit of every issuer, and
+//     the loader refills it with the same taps of the next layer when all have come in (it stands in
+//     for the issuers of an absent second board).
 //   * Boards are assigned statically: CTA c takes boards c, c + grid, c + 2 grid, ... two at a time.
 //     The first input of a board arrives by TMA into y, the tower's output leaves by TMA from x.
 //   * The last layer's epilogue has a position's 64 output channels at hand and, when asked to, also
@@ -47,11 +51,12 @@ constexpr int kBufRows = 3 * kGuardRows + 2 * kSlotRows;     // 584
 constexpr int kBufBytes = kBufRows * kRowBytes;      // 74,752
 constexpr int kTmemCols = 512;
 constexpr int kEpiWarps = 8;                         // two groups of four: group g drains tile g of the board
-constexpr int kThreads = 64 + 32 * kEpiWarps + 32;   // warps 0, 1: MMA issue for board 0 / 1, warps 2-9: epilogue, warp 10: weight loader
+constexpr int kIssuers = 4;                          // warp w < 4 issues the MMAs of board w / 2, tile w % 2
+constexpr int kThreads = 32 * kIssuers + 32 * kEpiWarps + 32;   // warps 0-3: MMA issue, warps 4-11: epilogue, warp 12: weight loader
 constexpr int kStaggerTap = 6;                       // board 1 starts a layer when board 0 has issued this tap of it
 constexpr int kWGroups = 3;                          // the weight ring is handed over in groups of three taps
 constexpr int kWGroupBytes = 3 * kTapBytes;          // 24,576
-constexpr int kNumBars = 2 + 2 + 2 + kWGroups + kWGroups + 2 + 2 + 1;
+constexpr int kNumBars = 2 + 2 + 4 + kWGroups + kWGroups + 2 + 2 + 1;
 
 struct alignas(32) ResidentLayer {
     const uint8_t* w;         // packed weights (ob200_pack_conv3x3_weights): 9 taps x 8 KB
@@ -139,10 +144,8 @@ __device__ __forceinline__ void store_zero_row(uint8_t* dst_row) {
 }
 
 // T: 128-row tiles per board (1 for boards up to 10x10, 2 up to 15x15).
-// PAIR: CTAs take their boards two at a time, with one MMA issuer per board (the general case).  When no CTA
-// has more than one board (batches up to the SM count) the second issuer's bookkeeping - the stagger signal, the
-// second hand-over of every weight block - is pure cost in the one thread everything waits for (84 us instead
-// of 78 us for the 21 layers); !PAIR is the same kernel with a single issuer (warp 0; warp 1 idles).
+// PAIR: CTAs take their boards two at a time (the general case).  When no CTA has more than one board
+// (batches up to the SM count) the barriers count the issuers of one board only.
 // F16: the boards and weights are fp16 instead of bf16 (same instruction, other operand-format bits).
 template <int T, bool PAIR, bool F16>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -164,19 +167,21 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
     const uint32_t bar0 = smem_u32(bars);
     auto in_full = [&](int bd) { return bar0 + 8u * bd; };               // the board's first input has landed in y
     auto act_ready = [&](int bd) { return bar0 + 8u * (2 + bd); };       // the previous layer's output is written
-    auto acc_full = [&](int bd) { return bar0 + 8u * (4 + bd); };        // the board's MMAs of this layer are complete
-    auto w_full = [&](int g) { return bar0 + 8u * (6 + g); };
-    auto w_empty = [&](int g) { return bar0 + 8u * (6 + kWGroups + g); };
-    auto out_written = [&](int bd) { return bar0 + 8u * (6 + 2 * kWGroups + bd); };    // the tower's output is complete in x
-    auto x_free = [&](int bd) { return bar0 + 8u * (8 + 2 * kWGroups + bd); };         // the output store has read x
-    const uint32_t stagger = bar0 + 8u * (10 + 2 * kWGroups);                          // board 0 is far enough into the layer
+    auto acc_full = [&](int bd, int tile) { return bar0 + 8u * (4 + 2 * bd + tile); };   // the tile's MMAs of this layer are complete
+    auto w_full = [&](int g) { return bar0 + 8u * (8 + g); };
+    auto w_empty = [&](int g) { return bar0 + 8u * (8 + kWGroups + g); };
+    auto out_written = [&](int bd) { return bar0 + 8u * (8 + 2 * kWGroups + bd); };    // the tower's output is complete in x
+    auto x_free = [&](int bd) { return bar0 + 8u * (10 + 2 * kWGroups + bd); };        // the output store has read x
+    const uint32_t stagger = bar0 + 8u * (12 + 2 * kWGroups);                          // board 0 is far enough into the layer
 
     if (threadIdx.x == 0) {
         for (int bd = 0; bd < 2; ++bd) {
-            mbar_init(in_full(bd), 1); mbar_init(act_ready(bd), 4 * T); mbar_init(acc_full(bd), 1);
+            mbar_init(in_full(bd), 1); mbar_init(act_ready(bd), 4 * T);
+            mbar_init(acc_full(bd, 0), 1); mbar_init(acc_full(bd, 1), 1);
             mbar_init(out_written(bd), 4 * T); mbar_init(x_free(bd), 1);
         }
-        for (int g = 0; g < kWGroups; ++g) { mbar_init(w_full(g), 1); mbar_init(w_empty(g), PAIR ? 2 : 1); }
+        // a weight block comes back from every issuer of a full round
+        for (int g = 0; g < kWGroups; ++g) { mbar_init(w_full(g), 1); mbar_init(w_empty(g), (PAIR ? 2 : 1) * T); }
         mbar_init(stagger, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -206,7 +211,7 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
     auto board_of = [&](int round, int bd) { return (int)blockIdx.x + (2 * round + bd) * (int)gridDim.x; };
     auto slot_off = [&](int bd) { return (uint32_t)((kGuardRows + bd * (kSlotRows + kGuardRows)) * kRowBytes); };
 
-    if (warp == 10) {
+    if (warp == kIssuers + kEpiWarps) {
         // ---------------- weight loader ----------------
         // constants of the network: may start before the kernels ahead of this one in the stream are complete
         if (lane == 0) {
@@ -214,11 +219,12 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
             bool ok = true;
             for (int it = 0; ok && it < total; ++it) {
                 const uint8_t* src = p.layers[it % L].w;
-                // a block comes back from both boards' issuers; in a round with a single board (the last one, when the
-                // CTA's board count is odd) the loader stands in for the missing issuer
+                // a block comes back from every issuer; in a round with a single board (the last one, when the
+                // CTA's board count is odd) the loader stands in for the issuers of the missing board
                 const bool prev_alone = PAIR && it > 0 && (n_my & 1) && (it - 1) / L == rounds - 1;
                 for (int g = 0; g < kWGroups; ++g) {
-                    if (prev_alone) mbar_arrive(w_empty(g));
+                    if (prev_alone)
+                        for (int k = 0; k < T; ++k) mbar_arrive(w_empty(g));
                     if (it > 0 && !mbar_wait(w_empty(g), (uint32_t)(it - 1) & 1u, abort_flag)) { ok = false; break; }
                     mbar_arrive_expect_tx(w_full(g), (uint32_t)kWGroupBytes);
                     bulk_g2s(smem_u32(w_s + g * kWGroupBytes), src + (size_t)g * kWGroupBytes, (uint32_t)kWGroupBytes, w_full(g));
@@ -226,84 +232,27 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
             }
             if (!ok) { *abort_flag = 1; atomicExch(p.error, 4); }
         }
-    } else if (!PAIR && warp < 2) {
-        if (warp == 0) {
-            // ---------------- single MMA issuer (!PAIR): the boards of a round one after the other ----------------
-            if (lane == 0) {
-                int tap_off[9];
-    #pragma unroll
-                for (int tap = 0; tap < 9; ++tap) tap_off[tap] = ((tap / 3) * p.GP + (tap % 3)) * (kRowBytes >> 4);
-                // descriptor of the row GP + 1 rows above a board's first row (tap 0 of position 0), per buffer and board
-                const uint32_t a_base_x = desc_lo(smem_u32(x_s) + slot_off(0) - (uint32_t)((p.GP + 1) * kRowBytes));
-                const uint32_t a_base_y = desc_lo(smem_u32(y_s) + slot_off(0) - (uint32_t)((p.GP + 1) * kRowBytes));
-                const uint32_t w_lo = desc_lo(smem_u32(w_s));
-                uint32_t ready_cnt[2] = {0u, 0u};
-                bool ok = true;
-                int it = 0;
-                for (int round = 0; ok && round < rounds; ++round) {
-                    const int nb = n_my - 2 * round >= 2 ? 2 : 1;
-                    for (int l = 0; ok && l < L; ++l, ++it) {
-                        const uint32_t a_layer = (l == 0 || !(l & 1)) ? a_base_y : a_base_x;   // stem and second convolutions read y, first ones x
-                        // unrolled over the two boards: "first board" is then a compile-time fact in each copy, and every
-                        // instruction between two MMAs costs issue time
-    #pragma unroll
-                        for (int bd = 0; bd < 2; ++bd) {
-                            if (bd >= nb) break;
-                            if (l == 0) {
-                                if (!mbar_wait(in_full(bd), (uint32_t)round & 1u, abort_flag)) { ok = false; break; }
-                            } else {
-                                if (!mbar_wait(act_ready(bd), ready_cnt[bd] & 1u, abort_flag)) { ok = false; break; }
-                                ++ready_cnt[bd];
-                            }
-                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                            const uint32_t a_lo = a_layer + (uint32_t)(bd * ((kSlotRows + kGuardRows) * kRowBytes >> 4));
-                            const uint32_t d_tmem = tmem_base + (uint32_t)((it & 1) * 256 + bd * 128);
-                            const bool first_board = bd == 0, last_board = bd == nb - 1;
-    #pragma unroll
-                            for (int tap = 0; tap < 9; ++tap) {
-                                // the issuing thread pays for every instruction between two MMAs (a wait costs about
-                                // 50 cycles, a commit 25, an MMA 48): weights are waited for and handed back three taps at a time
-                                if (first_board && tap % 3 == 0 && !mbar_wait(w_full(tap / 3), (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
-    #pragma unroll
-                                for (int tile = 0; tile < T; ++tile) {
-    #pragma unroll
-                                    for (int ks = 0; ks < kC / 16; ++ks)
-                                        umma(d_tmem + (uint32_t)(tile * kC),
-                                             a_lo + (uint32_t)(tile * (kTileM * kRowBytes >> 4) + tap_off[tap] + ks * 2),
-                                             w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), kIdesc, (tap | ks) ? 1u : 0u);
-                                }
-                                if (last_board && tap % 3 == 2) umma_commit(w_empty(tap / 3));   // the round's boards are through with these taps
-                            }
-                            if (!ok) break;
-                            umma_commit(acc_full(bd));
-                        }
-                    }
-                }
-                if (!ok) { *abort_flag = 1; atomicExch(p.error, 2); }
-            }
-        }
-    } else if (warp < 2) {
-        // ---------------- MMA issuers: warp 0 for board 0, warp 1 for board 1 ----------------
-        // The issuing thread pays for every instruction between two MMAs (an MMA holds it 48 cycles, a wait
-        // about 50, a commit 25), and at a layer boundary it waits for the epilogue.  With one issuer per
-        // board the tensor cores take the other board's MMAs meanwhile.  Board 1 runs two thirds of a layer
-        // behind board 0 (it starts a layer when board 0 has issued tap kStaggerTap), so that one board's MMAs
-        // cover the other's epilogue; both hand the weight blocks back, and the loader waits for both.
-        if (lane == 0) {
-            const int bd = warp;
+    } else if (warp < kIssuers) {
+        // ---------------- MMA issuers: warp w for board w / 2, tile w % 2 ----------------
+        // Board 1 runs two thirds of a layer behind board 0 (its issuers start a layer when board 0's first
+        // issuer has issued tap kStaggerTap), so that one board's MMAs cover the other's epilogue; every
+        // issuer hands the weight blocks back, and the loader waits for all of them.
+        const int bd = warp >> 1, tile = warp & 1;
+        if (lane == 0 && tile < T && (PAIR || bd == 0)) {
             int tap_off[9];
 #pragma unroll
             for (int tap = 0; tap < 9; ++tap) tap_off[tap] = ((tap / 3) * p.GP + (tap % 3)) * (kRowBytes >> 4);
-            // descriptor of the row GP + 1 rows above the board's first row (tap 0 of position 0), per buffer
-            const uint32_t a_base_x = desc_lo(smem_u32(x_s) + slot_off(bd) - (uint32_t)((p.GP + 1) * kRowBytes));
-            const uint32_t a_base_y = desc_lo(smem_u32(y_s) + slot_off(bd) - (uint32_t)((p.GP + 1) * kRowBytes));
+            // descriptor of the row GP + 1 rows above the tile's first row (tap 0 of its position 0), per buffer
+            const uint32_t tile_off = (uint32_t)(tile * kTileM * kRowBytes) - (uint32_t)((p.GP + 1) * kRowBytes);
+            const uint32_t a_base_x = desc_lo(smem_u32(x_s) + slot_off(bd) + tile_off);
+            const uint32_t a_base_y = desc_lo(smem_u32(y_s) + slot_off(bd) + tile_off);
             const uint32_t w_lo = desc_lo(smem_u32(w_s));
             uint32_t ready_cnt = 0u, stagger_cnt = 0u;
             bool ok = true;
             int it = 0;
             for (int round = 0; ok && round < rounds; ++round) {
                 const int nb = n_my - 2 * round >= 2 ? 2 : 1;
-                if (bd >= nb) break;                    // a single board in the last round: issuer 1 is done
+                if (bd >= nb) break;                    // a single board in the last round: board 1's issuers are done
                 for (int l = 0; ok && l < L; ++l, ++it) {
                     const uint32_t a_lo = (l == 0 || !(l & 1)) ? a_base_y : a_base_x;   // stem and second convolutions read y, first ones x
                     if (l == 0) {
@@ -317,39 +266,36 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
                         ++stagger_cnt;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t d_tmem = tmem_base + (uint32_t)((it & 1) * 256 + bd * 128);
+                    const uint32_t d_tmem = tmem_base + (uint32_t)((it & 1) * 256 + bd * 128 + tile * kC);
 #pragma unroll
                     for (int tap = 0; tap < 9; ++tap) {
+                        // weights are waited for and handed back three taps at a time (a wait costs the issuing
+                        // thread about 50 cycles, a commit 25)
                         if (tap % 3 == 0) {
                             if (!mbar_wait(w_full(tap / 3), (uint32_t)it & 1u, abort_flag)) { ok = false; break; }
                         }
 #pragma unroll
-                        for (int tile = 0; tile < T; ++tile) {
-#pragma unroll
-                            for (int ks = 0; ks < kC / 16; ++ks)
-                                umma(d_tmem + (uint32_t)(tile * kC),
-                                     a_lo + (uint32_t)(tile * (kTileM * kRowBytes >> 4) + tap_off[tap] + ks * 2),
-                                     w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), kIdesc, (tap | ks) ? 1u : 0u);
-                        }
-                        if (tap % 3 == 2) {
-                            umma_commit(w_empty(tap / 3));
-                        }
-                        if (tap == kStaggerTap && bd == 0) mbar_arrive(stagger);
+                        for (int ks = 0; ks < kC / 16; ++ks)
+                            umma(d_tmem, a_lo + (uint32_t)(tap_off[tap] + ks * 2),
+                                 w_lo + (uint32_t)(tap * (kTapBytes >> 4) + ks * 2), kIdesc, (tap | ks) ? 1u : 0u);
+                        if (tap % 3 == 2) umma_commit(w_empty(tap / 3));
+                        if (PAIR && tap == kStaggerTap && warp == 0) mbar_arrive(stagger);
                     }
                     if (!ok) break;
-                    umma_commit(acc_full(bd));
+                    umma_commit(acc_full(bd, tile));
                 }
             }
             if (!ok) { *abort_flag = 1; atomicExch(p.error, 2); }
         }
-    } else if (warp - 2 < 4 * T) {
+    } else if (warp - kIssuers < 4 * T) {
         // ---------------- epilogue: TMEM -> registers -> the next layer's input rows ----------------
+        // group g (four warps, one per TMEM lane quadrant) drains tile g as soon as that tile's MMAs are complete
         asm volatile("griddepcontrol.wait;" ::: "memory");   // inputs come from the kernels ahead in the stream
-        const int group = (warp - 2) >> 2;
+        const int group = (warp - kIssuers) >> 2;
         const int q = warp & 3;                          // TMEM lane quadrant this warp may read
         const int row = group * kTileM + q * 32 + lane;  // row within the board's slot
         const bool valid = row < p.slots && (row / p.GP < p.S) && (row % p.GP < p.S);
-        const bool elected = warp == 2 && lane == 0;     // issues the boards' loads and stores
+        const bool elected = warp == kIssuers && lane == 0;     // issues the boards' loads and stores
         const uint32_t in_bytes = (uint32_t)p.slots * kRowBytes;
         bool ok = true;
         if (elected)
@@ -368,7 +314,7 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
                 for (int bd = 0; bd < nb; ++bd) {
                     // every wait's outcome is voted on, so that a warp gives up as a whole (the TMEM loads below
                     // need all 32 lanes; the elected lane may come late from its store)
-                    bool good = mbar_wait(acc_full(bd), (bd ? full_cnt1 : full_cnt0) & 1u, abort_flag);
+                    bool good = mbar_wait(acc_full(bd, group), (bd ? full_cnt1 : full_cnt0) & 1u, abort_flag);
                     if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
                     if (bd) ++full_cnt1; else ++full_cnt0;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
