@@ -83,17 +83,25 @@ struct ResidentParams {
 
 using namespace ptx;
 
-// One 128-byte row of a layer's output: relu(accumulator + bias [+ residual, which is the row's old content]).
+// One 128-byte row of a layer's output: relu(accumulator + bias [+ residual]).
 // 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r % 8).
-template <bool RES, bool F16>
-__device__ __forceinline__ void store_row(uint8_t* dst_row, int row, const uint32_t* r, const float* bias_t) {
+// The residual is the row's old content; res holds it (chunk c in res[c]), read by load_row before the layer's
+// accumulators were waited for: the row has held the block's input since this very thread wrote it two layers ago.
+__device__ __forceinline__ void load_row(const uint8_t* src_row, int row, uint4 (&res)[8]) {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < 8; ++c) res[c] = *reinterpret_cast<const uint4*>(src_row + ((c ^ (row & 7)) << 4));
+}
+// C0: the first of the four chunks (32 channels) covered, r holding their accumulators.
+template <bool RES, bool F16, int C0>
+__device__ __forceinline__ void store_half_row(uint8_t* dst_row, int row, const uint32_t* r_in, const float* bias_t, const uint4 (&res)[8]) {
+    const uint32_t* r = r_in - C0 * 8;
+#pragma unroll
+    for (int c = C0; c < C0 + 4; ++c) {
         uint4* slot = reinterpret_cast<uint4*>(dst_row + ((c ^ (row & 7)) << 4));
         const float4 b0 = *reinterpret_cast<const float4*>(bias_t + c * 8), b1 = *reinterpret_cast<const float4*>(bias_t + c * 8 + 4);
         const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
         uint32_t rw[4] = {0u, 0u, 0u, 0u};
-        if (RES) { const uint4 rv = *slot; rw[0] = rv.x; rw[1] = rv.y; rw[2] = rv.z; rw[3] = rv.w; }
+        if (RES) { rw[0] = res[c].x; rw[1] = res[c].y; rw[2] = res[c].z; rw[3] = res[c].w; }
         uint32_t ow[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -312,16 +320,19 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
                 const bool to_x = l == 0 || !(l & 1);
                 const float* bias_t = bias_s + l * kC;
                 for (int bd = 0; bd < nb; ++bd) {
+                    uint8_t* dst_row = (to_x ? x_s : y_s) + slot_off(bd) + row * kRowBytes;
+                    uint4 res[8];
+                    if (has_res && valid) load_row(dst_row, row, res);      // while the tile's MMAs still run
                     // every wait's outcome is voted on, so that a warp gives up as a whole (the TMEM loads below
                     // need all 32 lanes; the elected lane may come late from its store)
                     bool good = mbar_wait(acc_full(bd, group), (bd ? full_cnt1 : full_cnt0) & 1u, abort_flag);
                     if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
                     if (bd) ++full_cnt1; else ++full_cnt0;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    uint32_t r[kC];
+                    // the row goes in two halves of 32 channels: half the accumulators in registers at a time
+                    uint32_t r[32];
                     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((it & 1) * 256 + bd * 128 + group * kC);
                     tmem_ld32(taddr, r);
-                    tmem_ld32(taddr + 32, r + 32);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (l == 0 && round > 0) {
                         // x still holds the previous round's output until its store has read it
@@ -332,10 +343,14 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
                         good = mbar_wait(x_free(bd), (uint32_t)(round - 1) & 1u, abort_flag);
                         if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
                     }
-                    uint8_t* dst_row = (to_x ? x_s : y_s) + slot_off(bd) + row * kRowBytes;
                     if (!valid) store_zero_row(dst_row);
-                    else if (has_res) store_row<true, F16>(dst_row, row, r, bias_t);
-                    else store_row<false, F16>(dst_row, row, r, bias_t);
+                    else if (has_res) store_half_row<true, F16, 0>(dst_row, row, r, bias_t, res);
+                    else store_half_row<false, F16, 0>(dst_row, row, r, bias_t, res);
+                    tmem_ld32(taddr + 32, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (!valid) {}
+                    else if (has_res) store_half_row<true, F16, 4>(dst_row, row, r, bias_t, res);
+                    else store_half_row<false, F16, 4>(dst_row, row, r, bias_t, res);
                     if (l + 1 == L && p.head_ch > 0 && valid)
                         head_row<F16>(dst_row, row, head_s, p.head_ch, p.head_pc, board_of(round, bd), p.S, p.GP, p.hp, p.hv);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // rows -> the tensor cores' / the store's reads
