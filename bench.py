@@ -293,8 +293,8 @@ def gpu_arm(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # > 126 MB L2
 
     def step_resident():
-        bt = capi.encode_gomoku(d_hist, d_nh, d_tm, 15, 17, net.input_tensor_channels(), DT)
-        net.forward_device(bt, B, d_policy, d_value, capi.OUT_PROBS)
+        # encode -> tower -> heads from device-resident move histories (ob200_net_forward_gomoku_device)
+        net.forward_gomoku_device(d_hist, d_nh, d_tm, d_policy, d_value, capi.OUT_PROBS)
 
     def timed(fn, n, per_iter_flush=True):
         ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
@@ -394,8 +394,7 @@ def gpu_arm(args):
                 val_s = torch.empty(Bs, dtype=torch.float32, device=dev)
 
                 def step_s():
-                    bts = capi.encode_gomoku(dhs, dns, dts, 15, 17, net_sw.input_tensor_channels(), DT)
-                    net_sw.forward_device(bts, Bs, pol_s, val_s, capi.OUT_PROBS)
+                    net_sw.forward_gomoku_device(dhs, dns, dts, pol_s, val_s, capi.OUT_PROBS)
                 for _ in range(3):
                     step_s()
                 step_ms = float(np.mean(timed(step_s, 5)))

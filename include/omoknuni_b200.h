@@ -449,6 +449,16 @@ int ob200_net_wait(ob200_net* net, int32_t ticket);
 int ob200_net_forward_device(ob200_net* net, const void* input_board_tensor, int32_t B,
                              float* policy_out, float* value_out, int32_t out_kind,
                              ob200_stream stream);
+/* DEVICE in, DEVICE out, asynchronous on `stream`, Gomoku positions given as move
+ * histories (the arrays of ob200_launch_encode_gomoku, history 16-byte aligned):
+ * encode -> tower -> heads.  On the board-resident tower path (64 filters, boards
+ * up to 15x15) the tower kernel writes its own input planes from the histories -
+ * no encoder launch and no input tensor in device memory; on the other paths the
+ * encoder kernel runs first.  Results are those of ob200_launch_encode_gomoku +
+ * ob200_net_forward_device. */
+int ob200_net_forward_gomoku_device(ob200_net* net, const int16_t* history, const uint8_t* n_hist,
+                                    const uint8_t* to_move, int32_t B, float* policy_out,
+                                    float* value_out, int32_t out_kind, ob200_stream stream);
 /* Device pointer of the tower's output board tensor of the last forward
  * (filters channels), for tests. */
 const void* ob200_net_debug_tower_output(ob200_net* net);

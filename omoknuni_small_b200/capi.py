@@ -117,6 +117,8 @@ SIGNATURES = {
     "ob200_net_wait": (C.c_int, [C.c_void_p, C.c_int32]),
     "ob200_net_forward_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
                                            C.c_void_p]),
+    "ob200_net_forward_gomoku_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+                                                  C.c_void_p, C.c_int32, C.c_void_p]),
     "ob200_debug_bounded_wait": (C.c_int, [C.c_int32, C.c_void_p]),
     "ob200_net_debug_tower_output": (C.c_void_p, [C.c_void_p]),
     "ob200_net_debug_tower_path": (C.c_int32, [C.c_void_p]),
@@ -430,6 +432,11 @@ class Net:
     def forward_device(self, input_bt, B, policy_out, value_out, out_kind=OUT_PROBS):
         check(lib().ob200_net_forward_device(self.h, _ptr(input_bt), B, _ptr(policy_out), _ptr(value_out), out_kind,
                                              _stream()))
+
+    def forward_gomoku_device(self, history, n_hist, to_move, policy_out, value_out, out_kind=OUT_PROBS):
+        """encode -> tower -> heads on device move histories (torch tensors: int16 [B,16], uint8 [B], uint8 [B])."""
+        check(lib().ob200_net_forward_gomoku_device(self.h, _ptr(history), _ptr(n_hist), _ptr(to_move), history.shape[0],
+                                                    _ptr(policy_out), _ptr(value_out), out_kind, _stream()))
 
     def tower_device(self, input_bt, B):
         """The residual tower alone on a device input tensor (asynchronous)."""

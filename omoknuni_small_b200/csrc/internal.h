@@ -39,11 +39,14 @@ void tower_resident_fill_layer(void* dst, const void* w, const float* bias, int 
 int tower_resident_box_rows(int S);
 size_t tower_resident_smem_bytes(int S, int n_layers);   // 0: does not fit
 int tower_resident_head_channels_max();
-// head_ch > 0: the heads' 1x1 convolutions ride along in the last epilogue (results as launch_head_conv's)
+// head_ch > 0: the heads' 1x1 convolutions ride along in the last epilogue (results as launch_head_conv's).
+// enc_hist != null: the input is not read through in_map but written by the kernel from Gomoku move histories
+// ([B][16] int16, 16-byte aligned; history lengths and sides to move [B]; 17 or 19 planes), as launch_encode_gomoku would.
 int launch_conv_tower_resident(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* layers_dev,
                                int n_layers, int B, int S, cudaStream_t st, const float* head_w = nullptr,
                                const float* head_b = nullptr, int head_ch = 0, int head_pc = 0, float* hp = nullptr,
-                               float* hv = nullptr, int dtype = 0);
+                               float* hv = nullptr, int dtype = 0, const int16_t* enc_hist = nullptr,
+                               const uint8_t* enc_nh = nullptr, const uint8_t* enc_tm = nullptr, int enc_planes = 0);
 // Towers of 128 / 256 channels (tower_wide.cu): cin a multiple of 64 up to 256, cout 128 or 256,
 // taps 9 (3x3) or 1 (1x1).  in_map: boxes of conv_wide_box_rows() rows over a cin-channel tensor;
 // out_map / res_map (residual, or null): boxes of 128 rows over a cout-channel tensor.

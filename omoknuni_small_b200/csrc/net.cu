@@ -415,8 +415,13 @@ namespace {
 // `input_bt`: a board tensor of cin_pad channels holding the B input boards (the handle's own staging
 // tensor or a caller's).
 // heads_done (optional): the caller wants the heads' 1x1 convolutions too; set when the tower kernel took them along.
-int tower_device(ob200_net* n, const void* input_bt, int B, int* out_buf, cudaStream_t st, bool* heads_done = nullptr) {
+// gomoku (optional): the input is given as Gomoku move histories on the device instead of a board tensor; the
+// board-resident tower writes its own input rows from them, the other paths run the encoder kernel first.
+struct GomokuInput { const int16_t* hist; const uint8_t* nh; const uint8_t* tm; };
+int tower_device(ob200_net* n, const void* input_bt, int B, int* out_buf, cudaStream_t st, bool* heads_done = nullptr,
+                 const GomokuInput* gomoku = nullptr) {
     const ob200_net_config& c = n->cfg;
+    if (gomoku) input_bt = n->act_in;
     const int S = c.board_size;
     const int F = c.filters;
     int x = 0, y = 1, z = 2;
@@ -431,11 +436,16 @@ int tower_device(ob200_net* n, const void* input_bt, int B, int* out_buf, cudaSt
         const bool with_heads = heads_done && c.policy_kind != OB200_POLICY_CONV_PLANES && hc <= tower_resident_head_channels_max();
         const int rc = launch_conv_tower_resident(own_input ? n->in_map_board : board_map, n->out_map_board, n->resident_layers,
                                                   1 + 2 * c.blocks, B, S, st, n->head_w, n->head_b, with_heads ? hc : 0,
-                                                  with_heads ? c.policy_head_ch : 0, n->hp, n->hv, c.tower_dtype);
+                                                  with_heads ? c.policy_head_ch : 0, n->hp, n->hv, c.tower_dtype,
+                                                  gomoku ? gomoku->hist : nullptr, gomoku ? gomoku->nh : nullptr,
+                                                  gomoku ? gomoku->tm : nullptr, c.input_channels);
         if (rc == OB200_OK) { done = true; x = 0; n->tower_path = 2; if (heads_done) *heads_done = with_heads; }
         else if (rc == OB200_ERR_UNSUPPORTED) n->resident = false;
         else return rc;
     }
+    if (!done && gomoku)       // the other tower paths read an input tensor: encode into the handle's own
+        if (int rc = launch_encode_gomoku(gomoku->hist, gomoku->nh, gomoku->tm, B, S, c.input_channels, n->cin_pad, n->act_in, st,
+                                          c.tower_dtype)) return rc;
     BoardTensorMap conv_map;
     if (!done && !own_input)
         if (int rc = input_map(n, input_bt, B, n->box_in, &conv_map)) return rc;
@@ -476,13 +486,13 @@ int tower_device(ob200_net* n, const void* input_bt, int B, int* out_buf, cudaSt
 }
 
 int forward_device(ob200_net* n, const void* input_bt, int B, float* policy_out, float* value_out,
-                   int out_kind, cudaStream_t st) {
+                   int out_kind, cudaStream_t st, const GomokuInput* gomoku = nullptr) {
     const ob200_net_config& c = n->cfg;
     const int S = c.board_size;
     const int F = c.filters;
     int x = 0;
     bool heads_done = false;
-    if (int rc = tower_device(n, input_bt, B, &x, st, &heads_done)) return rc;
+    if (int rc = tower_device(n, input_bt, B, &x, st, &heads_done, gomoku)) return rc;
     const int S2 = S * S, pc = c.policy_head_ch, vc = c.value_head_ch;
     if (c.policy_kind == OB200_POLICY_CONV_PLANES) {
         if (int rc = launch_conv_wide_maps(n->act_load[x], n->act_load[x], nullptr, n->pol_w, n->pol_b, B, S, F, n->pol_cout, 1, 0,
@@ -600,9 +610,8 @@ int enqueue_gomoku(ob200_net* n, int si, const int16_t* history, const uint8_t* 
     std::memcpy(h8 + hist_bytes, n_hist, (size_t)B);
     std::memcpy(h8 + hist_bytes + B, to_move, (size_t)B);
     OB200_CUDA_OK(cudaMemcpyAsync(d8, h8, hist_bytes + 2 * (size_t)B, cudaMemcpyHostToDevice, n->stream));
-    if (int rc = launch_encode_gomoku(n->d_hist, d8 + hist_bytes, d8 + hist_bytes + B, B, c.board_size, c.input_channels, n->cin_pad,
-                                      n->act_in, n->stream, c.tower_dtype)) return rc;
-    if (int rc = forward_device(n, n->act_in, B, sl.d_policy, sl.d_value, out_kind, n->stream)) return rc;
+    const GomokuInput g{n->d_hist, d8 + hist_bytes, d8 + hist_bytes + B};
+    if (int rc = forward_device(n, nullptr, B, sl.d_policy, sl.d_value, out_kind, n->stream, &g)) return rc;
     return enqueue_results(n, si, B, policy_out, value_out);
 }
 
@@ -610,12 +619,14 @@ int enqueue_gomoku(ob200_net* n, int si, const int16_t* history, const uint8_t* 
 }  // namespace ob200
 
 namespace ob200 {
-// For the search loop: forward on a device input tensor, probabilities out, no locking
+// For the search loop: forward on device move histories, probabilities out, no locking
 // beyond the handle's (the search is the handle's only user while it runs).
-int net_forward_for_search(ob200_net* n, const void* input_bt, int B, float* policy, float* value, cudaStream_t st) {
+int net_forward_gomoku_for_search(ob200_net* n, const int16_t* hist, const uint8_t* nh, const uint8_t* tm, int B, float* policy,
+                                  float* value, cudaStream_t st) {
     if (!n || !n->finalized) return set_error(OB200_ERR_STATE, "search: the network is not finalised");
     std::lock_guard<std::mutex> lk(n->mu);
-    return forward_device(n, input_bt, B, policy, value, OB200_OUT_PROBS, st);
+    const GomokuInput g{hist, nh, tm};
+    return forward_device(n, nullptr, B, policy, value, OB200_OUT_PROBS, st, &g);
 }
 const ob200_net_config* net_config(ob200_net* n) { return (n && n->finalized) ? &n->cfg : nullptr; }
 }  // namespace ob200
@@ -705,6 +716,17 @@ int ob200_net_forward_device(ob200_net* n, const void* input_board_tensor, int32
     std::lock_guard<std::mutex> lk(n->mu);
     OB200_CUDA_OK(cudaSetDevice(n->cfg.device));
     return forward_device(n, input_board_tensor, B, policy_out, value_out, out_kind, as_stream(stream));
+}
+
+int ob200_net_forward_gomoku_device(ob200_net* n, const int16_t* history, const uint8_t* n_hist, const uint8_t* to_move,
+                                    int32_t B, float* policy_out, float* value_out, int32_t out_kind, ob200_stream stream) {
+    if (int rc = check_call(n, B, history, policy_out, value_out, out_kind, "ob200_net_forward_gomoku_device")) return rc;
+    if (int rc = check_gomoku(n, n_hist, to_move, "ob200_net_forward_gomoku_device")) return rc;
+    if ((uintptr_t)history & 15) return set_error(OB200_ERR_INVALID, "ob200_net_forward_gomoku_device: history must be 16-byte aligned");
+    std::lock_guard<std::mutex> lk(n->mu);
+    OB200_CUDA_OK(cudaSetDevice(n->cfg.device));
+    const GomokuInput g{history, n_hist, to_move};
+    return forward_device(n, nullptr, B, policy_out, value_out, out_kind, as_stream(stream), &g);
 }
 
 const void* ob200_net_debug_tower_output(ob200_net* n) { return n ? n->tower_out : nullptr; }

@@ -39,7 +39,6 @@ struct ob200_search {
     int32_t* tt_val = nullptr;
     int tt_size = 0;                           // power of two; 0 = table off
     std::vector<unsigned long long> zobrist_host;
-    void* input_bt = nullptr;                  // encoder output for leaf_batch boards
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     uint64_t moves_done = 0;
@@ -341,7 +340,8 @@ expand_rows_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const i
 
 // Accessors of the network handle that the search needs (defined in net.cu).
 namespace ob200 {
-int net_forward_for_search(ob200_net* n, const void* input_bt, int B, float* policy, float* value, cudaStream_t st);
+int net_forward_gomoku_for_search(ob200_net* n, const int16_t* hist, const uint8_t* nh, const uint8_t* tm, int B, float* policy,
+                                  float* value, cudaStream_t st);
 const ob200_net_config* net_config(ob200_net* n);
 }
 
@@ -407,9 +407,6 @@ int ob200_search_create(ob200_net* net, const ob200_search_config* cfg, ob200_se
         A_(salloc(s, &s->zobrist, 451)); A_(salloc(s, &s->node_hash, (size_t)s->max_nodes));
         A_(salloc(s, &s->tt_key, (size_t)s->tt_size)); A_(salloc(s, &s->tt_val, (size_t)s->tt_size));
     }
-    uint8_t* bt = nullptr;
-    A_(salloc(s, &bt, (size_t)ob200_board_tensor_bytes(15, L, 64)));
-    s->input_bt = bt;
     if (rc) { ob200_search_destroy(s); return rc; }
     s->tv.n_nodes = s->max_nodes; s->tv.n_children = s->A; s->tv.pitch = s->pitch; s->tv.mask_words = s->mask_words;
     std::vector<int32_t> roots(T);
@@ -547,8 +544,7 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
     // ---- roots: create, evaluate, priors (+ noise) ----
     init_roots_kernel<<<T, 128, 0, st>>>(s->tv, s->root_stones, T, s->n_used, s->term_count);
     OB200_LAUNCHED("init_roots_kernel");
-    if (int rc = launch_encode_gomoku(s->root_hist, s->root_nh, s->root_tm, T, S, nc->input_channels, 64, s->input_bt, st, nc->tower_dtype)) return rc;
-    if (int rc = net_forward_for_search(s->net, s->input_bt, T, s->policy, s->value, st)) return rc;
+    if (int rc = net_forward_gomoku_for_search(s->net, s->root_hist, s->root_nh, s->root_tm, T, s->policy, s->value, st)) return rc;
     if (int rc = ob200_launch_set_priors(&s->tv, s->roots, T, s->policy, A, nullptr, st)) return rc;
     if (s->rec_policy) {
         OB200_CUDA_OK(cudaMemcpyAsync(s->rec_policy, s->policy, (size_t)T * A * 4, cudaMemcpyDeviceToDevice, st));
@@ -568,8 +564,7 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
                                                             s->root_count, s->leaf_hist, s->leaf_nh, s->leaf_tm,
                                                             s->term_value, s->term_count);
         OB200_LAUNCHED("leaf_prepare_kernel");
-        if (int rc = launch_encode_gomoku(s->leaf_hist, s->leaf_nh, s->leaf_tm, L, S, nc->input_channels, 64, s->input_bt, st, nc->tower_dtype)) return rc;
-        if (int rc = net_forward_for_search(s->net, s->input_bt, L, s->policy, s->value, st)) return rc;
+        if (int rc = net_forward_gomoku_for_search(s->net, s->leaf_hist, s->leaf_nh, s->leaf_tm, L, s->policy, s->value, st)) return rc;
         if (s->rec_policy && r < s->rec_rounds) {
             OB200_CUDA_OK(cudaMemcpyAsync(s->rec_policy + (size_t)(r + 1) * L * A, s->policy, (size_t)L * A * 4, cudaMemcpyDeviceToDevice, st));
             OB200_CUDA_OK(cudaMemcpyAsync(s->rec_value + (size_t)(r + 1) * L, s->value, (size_t)L * 4, cudaMemcpyDeviceToDevice, st));

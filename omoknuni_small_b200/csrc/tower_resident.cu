@@ -28,6 +28,9 @@
 //     The first input of a board arrives by TMA into y, the tower's output leaves by TMA from x.
 //   * The last layer's epilogue has a position's 64 output channels at hand and, when asked to, also
 //     computes the policy / value heads' 1x1 convolutions (up to four head channels) for it.
+//   * Given Gomoku move histories instead of an input tensor, the epilogue threads write a board's
+//     input planes straight into its buffer (a position's row is 17 ones or zeros): no encoder launch,
+//     no input tensor in HBM.
 // There is no communication between CTAs, so this is an ordinary launch (and may be captured in a
 // graph).  Every wait is bounded; a thread that gives up raises the device error word.
 // Measured (15x15, 21 layers, B200): 8,000-8,400 cycles per layer for a pair of boards (four tiles), against
@@ -79,6 +82,12 @@ struct ResidentParams {
     int head_ch, head_pc;     // channels in all, and how many of them belong to the policy head
     float* hp;                // [B][head_pc][S*S]
     float* hv;                // [B][head_ch - head_pc][S*S]
+    // optional: the tower's input comes from Gomoku move histories instead of an input tensor - the epilogue
+    // threads write each board's input rows themselves (the planes of ob200_launch_encode_gomoku).  enc_hist == null: off.
+    const int16_t* enc_hist;  // [B][16] k-th most recent move
+    const uint8_t* enc_nh;    // [B]
+    const uint8_t* enc_tm;    // [B] 1 BLACK, 2 WHITE
+    int enc_planes;           // 17 or 19
 };
 
 using namespace ptx;
@@ -112,6 +121,30 @@ __device__ __forceinline__ void store_half_row(uint8_t* dst_row, int row, const 
         }
         *slot = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
+}
+// The input row of one position from the board's move history, as encode_gomoku_board_kernel writes it
+// (GomokuState::getEnhancedTensorRepresentation, reference src/games/gomoku/gomoku_state.cpp:223-262): plane p < 16
+// is one where move k = p + 1 (p even) / p - 1 (p odd) of the history was played, plane 16 is one everywhere iff
+// BLACK is to move, planes 17 / 18 (attack / defense) are zero as the reference's CPU code computes them.
+template <bool F16>
+__device__ __forceinline__ void write_input_row(uint8_t* dst_row, int row, bool valid, int cell, const int16_t* hist, int nh, int tm, int planes) {
+    uint32_t w[12] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};     // channels 0-23, two per word
+    if (valid) {
+        const uint4 ha = __ldg(reinterpret_cast<const uint4*>(hist)), hb = __ldg(reinterpret_cast<const uint4*>(hist) + 1);
+        const uint32_t hw[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+        const uint32_t one = F16 ? 0x3C00u : 0x3F80u;
+#pragma unroll
+        for (int pl = 0; pl < 16; ++pl) {
+            const int k = (pl & 1) ? pl - 1 : pl + 1;
+            const int hk = (int)(int16_t)((k & 1) ? (hw[k >> 1] >> 16) : (hw[k >> 1] & 0xffffu));
+            if (k < nh && hk == cell) w[pl >> 1] |= one << ((pl & 1) * 16);
+        }
+        if (planes > 16 && tm == 1) w[8] = one;
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(dst_row + ((c ^ (row & 7)) << 4)) =
+            c < 3 ? make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]) : make_uint4(0u, 0u, 0u, 0u);
 }
 // The heads' 1x1 convolutions for one position, from the row just written (16-bit, as the head kernel would
 // read it from the tower's output tensor).  Same order of additions as head_conv_kernel: eight partial sums
@@ -184,7 +217,7 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
 
     if (threadIdx.x == 0) {
         for (int bd = 0; bd < 2; ++bd) {
-            mbar_init(in_full(bd), 1); mbar_init(act_ready(bd), 4 * T);
+            mbar_init(in_full(bd), p.enc_hist ? 4 * T : 1); mbar_init(act_ready(bd), 4 * T);
             mbar_init(acc_full(bd, 0), 1); mbar_init(acc_full(bd, 1), 1);
             mbar_init(out_written(bd), 4 * T); mbar_init(x_free(bd), 1);
         }
@@ -306,11 +339,24 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
         const bool elected = warp == kIssuers && lane == 0;     // issues the boards' loads and stores
         const uint32_t in_bytes = (uint32_t)p.slots * kRowBytes;
         bool ok = true;
-        if (elected)
+        const bool encode = p.enc_hist != nullptr;
+        const int cell = (row / p.GP) * p.S + row % p.GP;
+        // a board's input: by TMA from the input tensor, or written here from its move history
+        auto encode_board = [&](int board, int bd) {
+            write_input_row<F16>(y_s + slot_off(bd) + row * kRowBytes, row, valid, cell, p.enc_hist + (size_t)board * 16,
+                                 p.enc_nh[board], p.enc_tm[board], p.enc_planes);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // rows -> the tensor cores' reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(in_full(bd));
+        };
+        if (encode) {
+            for (int bd = 0; bd < 2 && bd < n_my; ++bd) encode_board(board_of(0, bd), bd);
+        } else if (elected) {
             for (int bd = 0; bd < 2 && bd < n_my; ++bd) {
                 mbar_arrive_expect_tx(in_full(bd), in_bytes);
                 tma_load_2d(smem_u32(y_s) + slot_off(bd), &in_map, 0, OB200_GUARD + board_of(0, bd) * p.slots, in_full(bd));
             }
+        }
         uint32_t full_cnt0 = 0u, full_cnt1 = 0u;
         int it = 0;
         for (int round = 0; ok && round < rounds; ++round) {
@@ -360,19 +406,21 @@ conv_tower_resident_kernel(const __grid_constant__ CUtensorMap in_map, const __g
                         if (lane == 0) mbar_arrive(act_ready(bd));
                     } else {
                         if (lane == 0) mbar_arrive(out_written(bd));
-                        if (elected) good = mbar_wait(out_written(bd), (uint32_t)round & 1u, abort_flag);
+                        const bool successor = 2 * (round + 1) + bd < n_my;
+                        // the board is through when every warp has drained its tile: y is free then (both tiles' last MMAs
+                        // are complete) and the successor may come in
+                        if (elected || (encode && successor)) good = mbar_wait(out_written(bd), (uint32_t)round & 1u, abort_flag);
                         if (elected && good) {
                             tma_store_2d(&out_map, 0, OB200_GUARD + board_of(round, bd) * p.slots, smem_u32(x_s) + slot_off(bd));
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                            // y is free (the last layer's MMAs are complete) and so are the accumulators (every warp has
-                            // drained them): the board's successor may come in
-                            if (2 * (round + 1) + bd < n_my) {
+                            if (successor && !encode) {
                                 mbar_arrive_expect_tx(in_full(bd), in_bytes);
                                 tma_load_2d(smem_u32(y_s) + slot_off(bd), &in_map, 0, OB200_GUARD + board_of(round + 1, bd) * p.slots,
                                             in_full(bd));
                             }
                         }
                         if (!__all_sync(0xffffffffu, good)) { ok = false; break; }
+                        if (encode && successor) encode_board(board_of(round + 1, bd), bd);
                     }
                 }
             }
@@ -423,7 +471,10 @@ int tower_resident_head_channels_max() { return kHeadMax; }
 // tower's output ride along in the last epilogue; results as launch_head_conv writes them.
 int launch_conv_tower_resident(const BoardTensorMap& in_map, const BoardTensorMap& out_map, const void* layers_dev,
                                int n_layers, int B, int S, cudaStream_t st, const float* head_w, const float* head_b,
-                               int head_ch, int head_pc, float* hp, float* hv, int dtype) {
+                               int head_ch, int head_pc, float* hp, float* hv, int dtype, const int16_t* enc_hist,
+                               const uint8_t* enc_nh, const uint8_t* enc_tm, int enc_planes) {
+    if (enc_hist && (!enc_nh || !enc_tm || (enc_planes != 17 && enc_planes != 19) || ((uintptr_t)enc_hist & 15)))
+        return set_error(OB200_ERR_INVALID, "resident tower: bad move-history arguments (17 or 19 planes, histories 16-byte aligned)");
     if (!layers_dev || n_layers < 1 || B <= 0) return set_error(OB200_ERR_INVALID, "resident tower: bad arguments");
     if (head_ch < 0 || head_ch > kHeadMax || head_pc < 0 || head_pc > head_ch ||
         (head_ch > 0 && (!head_w || !head_b || (head_pc > 0 && !hp) || (head_pc < head_ch && !hv))))
@@ -453,6 +504,7 @@ int launch_conv_tower_resident(const BoardTensorMap& in_map, const BoardTensorMa
     p.error = device_error_word();
     if (!p.error) return set_error(OB200_ERR_CUDA, "resident tower: cannot resolve the device error word");
     p.head_w = head_w; p.head_b = head_b; p.head_ch = head_ch; p.head_pc = head_pc; p.hp = hp; p.hv = hv;
+    p.enc_hist = enc_hist; p.enc_nh = enc_nh; p.enc_tm = enc_tm; p.enc_planes = enc_planes;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(B < sms ? B : sms); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];

@@ -635,3 +635,37 @@ def test_two_batches_in_flight_give_the_same_results(api):
     for i in range(n_batches):
         assert np.array_equal(got[i][0], want[i][0]) and np.array_equal(got[i][1], want[i][1]), i
     assert api.device_error_code() == 0
+
+
+@pytest.mark.parametrize("S,blocks,B,dtype,which", [(15, 2, 1, 0, "resident"), (15, 3, 300, 0, "resident"), (15, 10, 1024, 1, "resident"),
+                                                    (15, 2, 149, 1, "resident"), (9, 2, 37, 0, "resident"), (13, 2, 450, 1, "resident"),
+                                                    (15, 2, 300, 0, "layers"), (19, 1, 5, 1, "layers")])
+def test_forward_from_move_histories_equals_encode_then_forward(api, monkeypatch, S, blocks, B, dtype, which):
+    """ob200_net_forward_gomoku_device (the board-resident tower writes its own input planes from the move
+    histories) against ob200_launch_encode_gomoku followed by ob200_net_forward_device: the same planes, so the
+    same bits out - boards of one and two tiles, one to seven boards per CTA, both storage types, and the tower
+    paths that run the encoder kernel themselves."""
+    import torch
+    pick_tower(monkeypatch, which)
+    shapes = synth.net_tensor_shapes(S, 19, 64, blocks, S * S, 2, 1)
+    w = synth.make_weights(shapes, seed=13, init="torch_default", bn="random")
+    net = make_net(api, w, dict(cin=19, S=S, blocks=blocks, F=64, A=S * S, pc=2, vc=1), B, dtype=dtype)
+    games, hist, nh, tm = synth.make_gomoku_games(B, S, seed=900 + B)
+    dh, dn, dt = (torch.from_numpy(a).cuda() for a in (hist, nh, tm))
+    outs = []
+    for fused in (True, False):
+        pol = torch.zeros((B, S * S), dtype=torch.float32, device="cuda")
+        val = torch.zeros(B, dtype=torch.float32, device="cuda")
+        if fused:
+            net.forward_gomoku_device(dh, dn, dt, pol, val, api.OUT_LOGITS)
+        else:
+            bt = api.encode_gomoku(dh, dn, dt, S, 19, net.input_tensor_channels(), dtype)
+            net.forward_device(bt, B, pol, val, api.OUT_LOGITS)
+        torch.cuda.synchronize()
+        outs.append((pol.cpu().numpy(), val.cpu().numpy()))
+    assert net.tower_path() == (2 if which == "resident" else 0)
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+    assert np.abs(outs[0][0]).max() > 0 and api.device_error_code() == 0
+    # and through the host-buffer call
+    pol_h, val_h = net.infer_gomoku(hist, nh, tm, api.OUT_LOGITS)
+    assert np.array_equal(pol_h, outs[0][0]) and np.array_equal(val_h, outs[0][1])
