@@ -575,7 +575,7 @@ def gpu_arm(args):
                           "pass_gbs": sel_bytes / (sel_ms * 1e-3) / 1e9,
                           "wide_rows": {"nodes": SELW_NODES, "children": SELW_CHILDREN, "ms_per_pass": selw_ms,
                                         "value": SELW_NODES / (selw_ms * 1e-3), "unit": "node selections/s (select + VL apply + VL revert)",
-                                        "kernel": "puct_select_wide_kernel (one CTA per node)",
+                                        "kernel": "puct_select_segmented_kernel (256-slot segments through per-warp rings) + puct_select_finish_kernel",
                                         "achieved_gbs": synth.selection_bytes_per_node(SELW_CHILDREN) * SELW_NODES / (selw_ms * 1e-3) / 1e9,
                                         "frac_of_hbm": synth.selection_bytes_per_node(SELW_CHILDREN) * SELW_NODES / (selw_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}},
             "mcts": {"value": world * mcts_sims / (mcts_ms * 1e-3), "unit": "simulations/s",

@@ -10,6 +10,10 @@
 // shuffle butterfly whose combine rule keeps the lowest slot on equal scores.
 #include "internal.h"
 #include <cfloat>
+#include <map>
+#include <mutex>
+#include <type_traits>
+#include <utility>
 
 namespace ob200 {
 namespace {
@@ -161,88 +165,7 @@ __device__ __forceinline__ void bracket(int n, float w, float p, int vl, float e
     hi = legal ? fmaf(kBracket, m, s) : -INFINITY;
 }
 
-// ---------------------------------------------------------------------------
-// Wide rows (chess: 4,672 children = 75 KB of statistics per node): one CTA per
-// node.  Pass 1: every thread brackets its slots (16-byte loads, upper bounds
-// kept in shared memory) and the CTA takes the best lower bound T.  Pass 2: the
-// few slots whose upper bound reaches T are re-read (they are still in L2) and
-// scored with the exact expression; ties go to the lowest slot.  Same argument
-// for bit-exactness as above.
-// ---------------------------------------------------------------------------
-constexpr int kWideThreads = 256;
 constexpr int kWideMinPitch = 1024;
-__global__ void __launch_bounds__(kWideThreads)
-puct_select_wide_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids, int n, float c_puct,
-                        int vl_value, int apply_vl, int32_t* __restrict__ sel_out) {
-    extern __shared__ __align__(16) float hi_s[];          // [pitch] upper bounds, -inf for slots that do not exist
-    __shared__ float red_f[kWideThreads / 32];
-    __shared__ int red_i[kWideThreads / 32];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nvec = t.pitch >> 2;
-    for (int i = blockIdx.x; i < n; i += gridDim.x) {
-        int node = node_ids ? node_ids[i] : i;
-        if (node < 0 || node >= t.n_nodes) {
-            if (threadIdx.x == 0) sel_out[i] = -1;
-            continue;
-        }
-        const size_t row = (size_t)node * t.pitch;
-        const int4* N4 = reinterpret_cast<const int4*>(t.N + row);
-        const float4* W4 = reinterpret_cast<const float4*>(t.W + row);
-        const float4* P4 = reinterpret_cast<const float4*>(t.P + row);
-        const int4* V4 = reinterpret_cast<const int4*>(t.VL + row);
-        const uint32_t* mask = t.legal_bits + (size_t)node * t.mask_words;
-        const float explore = __fmul_rn(c_puct, __fsqrt_rn((float)t.node_visits[node]));
-        float lo_best = -INFINITY;
-        for (int v = threadIdx.x; v < nvec; v += kWideThreads) {
-            const int4 nn = __ldcg(N4 + v); const float4 ww = __ldcg(W4 + v); const float4 pp = __ldcg(P4 + v);
-            const int4 ll = __ldcg(V4 + v);
-            const uint32_t m = (__ldg(mask + (v >> 3)) >> ((v & 7) * 4)) & 0xFu;
-            float lo; float4 h;
-            bracket(nn.x, ww.x, pp.x, ll.x, explore, m & 1u, lo, h.x); lo_best = fmaxf(lo_best, lo);
-            bracket(nn.y, ww.y, pp.y, ll.y, explore, m & 2u, lo, h.y); lo_best = fmaxf(lo_best, lo);
-            bracket(nn.z, ww.z, pp.z, ll.z, explore, m & 4u, lo, h.z); lo_best = fmaxf(lo_best, lo);
-            bracket(nn.w, ww.w, pp.w, ll.w, explore, m & 8u, lo, h.w); lo_best = fmaxf(lo_best, lo);
-            reinterpret_cast<float4*>(hi_s)[v] = h;
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) lo_best = fmaxf(lo_best, __shfl_xor_sync(0xffffffffu, lo_best, off));
-        if (lane == 0) red_f[warp] = lo_best;
-        __syncthreads();
-        float T = red_f[0];
-#pragma unroll
-        for (int w = 1; w < kWideThreads / 32; ++w) T = fmaxf(T, red_f[w]);
-        Best b{-INFINITY, -1};
-        for (int v = threadIdx.x; v < nvec; v += kWideThreads) {
-            const float4 h = reinterpret_cast<const float4*>(hi_s)[v];
-            const float he[4] = {h.x, h.y, h.z, h.w};
-            const uint32_t m = (__ldg(mask + (v >> 3)) >> ((v & 7) * 4)) & 0xFu;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (((m >> e) & 1u) && he[e] >= T) {
-                    const int slot = v * 4 + e;
-                    const float sc = puct_score(__ldcg(t.N + row + slot), __ldcg(t.W + row + slot), __ldcg(t.P + row + slot),
-                                                __ldcg(t.VL + row + slot), explore);
-                    if (sc > b.score) { b.score = sc; b.idx = slot; }
-                }
-            }
-        }
-        b = warp_combine(b);
-        __syncthreads();                       // red_f has been read by everyone
-        if (lane == 0) { red_f[warp] = b.score; red_i[warp] = b.idx; }
-        __syncthreads();
-        if (warp == 0) {
-            Best c{-INFINITY, -1};
-            if (lane < kWideThreads / 32) { c.score = red_f[lane]; c.idx = red_i[lane]; }
-            c = warp_combine(c);
-            int sel = c.idx >= 0 ? c.idx : least_visited_row(t.N + row, mask, t.n_children, lane);
-            if (lane == 0) {
-                sel_out[i] = sel;
-                if (sel >= 0 && apply_vl && vl_value > 0) atomicAdd(t.VL + row + sel, vl_value);
-            }
-        }
-        __syncthreads();                       // shared memory is reused by the next node
-    }
-}
 
 // ---------------------------------------------------------------------------
 // Staged variant for rows of up to 256 slots: a persistent grid, every warp
@@ -290,6 +213,9 @@ puct_select_staged_kernel(ob200_tree_view t, const int32_t* __restrict__ node_id
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
+    // a kernel launched behind this one with programmatic stream serialization (the virtual-loss revert) may be
+    // scheduled from now on; it waits for this grid's completion before it reads anything
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const int total_warps = gridDim.x * kStagedWarps;
     const int first = blockIdx.x * kStagedWarps + warp;
@@ -413,6 +339,265 @@ puct_select_staged_kernel(ob200_tree_view t, const int32_t* __restrict__ node_id
     }
 }
 
+// ---------------------------------------------------------------------------
+// Wide rows (chess: 4,672 children = 75 KB of statistics per node), segmented: a node's row is cut into segments
+// of 256 slots and every (node, segment) pair is one work item of the staged design above - a warp per item, a
+// three-deep ring of 4 KB segments per warp filled by bulk async copies - so the bytes stream at the rate of the
+// narrow-row kernel.  A segment yields its exact maximum (score, lowest slot) and folds it into the node's 64-bit
+// word of scratch with one atomic maximum: order-preserving bits of the score above the complemented slot, so the
+// largest word is the largest score and, among equals, the lowest slot.  A second small kernel (one thread per
+// node, started as a programmatic dependent) turns the word into the selection, applies the virtual loss and
+// zeroes the word for the next launch.  The maximum of the segments' exact maxima is the row's exact maximum, so
+// the choice is the reference's bit for bit.
+// ---------------------------------------------------------------------------
+// The approximate score of one slot (see bracket() for the error bound), folded into the lane's running maximum
+// of the existing slots' scores and of the error scale m.  A NaN score is never a candidate and fmaxf ignores it.
+// MAGIC converts the two counts to fp32 with an integer add and a subtraction of 2^23 (exact for 0 <= x < 2^23)
+// instead of two conversion instructions, which share the quarter-rate unit with the reciprocals; `range`
+// collects the bits of every count so that the caller can tell when a count was outside that range.
+template <bool MAGIC>
+__device__ __forceinline__ void approx_score(int n, float w, float p, int vl, float explore, bool exists, float& s_out,
+                                             float& lane_s, float& lane_m, uint32_t& range) {
+    const int ev = n + vl;
+    float evf, vlf, d2;
+    if (MAGIC) {
+        evf = __fsub_rn(__int_as_float(ev + 0x4B000000), 8388608.0f);
+        vlf = __fsub_rn(__int_as_float(vl + 0x4B000000), 8388608.0f);
+        d2 = __fsub_rn(__int_as_float(ev + 0x4B000001), 8388608.0f);
+        range |= (uint32_t)ev | (uint32_t)vl;
+    } else {
+        evf = (float)ev; vlf = (float)vl; d2 = __fadd_rn(1.0f, evf);
+    }
+    const float q = ev > 0 ? __fmul_rn(__fsub_rn(w, vlf), rcp_approx(evf)) : 0.0f;
+    const float u = __fmul_rn(__fmul_rn(p, explore), rcp_approx(d2));
+    const float s = __fadd_rn(q, u);
+    s_out = s;
+    if (exists) { lane_s = fmaxf(lane_s, s); lane_m = fmaxf(lane_m, __fadd_rn(fabsf(q), fabsf(u))); }
+}
+constexpr int kSegSlots = 256;
+#ifndef OB200_SEG_WARPS
+#define OB200_SEG_WARPS 27
+#define OB200_SEG_DEPTH 2
+#endif
+constexpr int kSegWarps = OB200_SEG_WARPS;   // warps x stages x 4 KB <= 216 KB of shared memory
+constexpr int kSegDepth = OB200_SEG_DEPTH;
+// fp32 -> unsigned bits with the same order (-0 < +0, which no comparison here depends on)
+__device__ __forceinline__ uint32_t order_bits(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__global__ void __launch_bounds__(kSegWarps * 32, 1)
+puct_select_segmented_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids, int n, int segs, float c_puct,
+                             unsigned long long* __restrict__ best_word, int* error_word) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kRowBytes = kSegSlots * 4;
+    constexpr int kStageBytes = 4 * kRowBytes;
+    uint8_t* ring = smem + (size_t)warp * kSegDepth * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kSegWarps * kSegDepth * kStageBytes) + warp * kSegDepth;
+    if (lane == 0) {
+        for (int d = 0; d < kSegDepth; ++d)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(s_u32(bars + d)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // A warp takes a contiguous run of (entry, segment) pairs, so most steps stay on the same node: its id and visit
+    // count are looked up once per node, and the best of the node's segments seen by this warp is folded into the
+    // node's word once.  (Handing the runs out through a counter instead measured slower: 38.6 to 44.9 us against
+    // 34.2 us for 2,048 rows of 4,672, the fewer the runs per warp the worse.)
+    const int total_warps = gridDim.x * kSegWarps;
+    const int w_index = blockIdx.x * kSegWarps + warp;
+    const long long items = (long long)n * segs;
+    const int base_items = (int)(items / total_warps), extra = (int)(items - (long long)base_items * total_warps);
+    const long long first = (long long)w_index * base_items + min(w_index, extra);
+    int to_look_up = base_items + (w_index < extra ? 1 : 0);
+    struct Item { int entry, seg, node, slots, visits; uint32_t bits; };
+    int nx_entry = (int)(first / segs), nx_seg = (int)(first - (long long)nx_entry * segs);      // the next pair to look up
+    int c_entry = -1, c_node = -1, c_visits = 0;
+    int ahead_node = node_ids && nx_entry < n ? __ldg(node_ids + nx_entry) : nx_entry;      // node id of entry nx_entry
+    const int mask_lane = lane >> 3, mask_shift = (lane & 7) * 4;
+    auto lookup = [&]() {
+        Item a{n, 0, -1, 0, 0, 0u};
+        if (to_look_up <= 0) return a;
+        --to_look_up;
+        a.entry = nx_entry; a.seg = nx_seg;
+        if (++nx_seg == segs) { nx_seg = 0; ++nx_entry; }
+        if (a.entry != c_entry) {                 // a new node: its id was requested one node ahead, its visit count
+            c_entry = a.entry;                    // is not needed before the segment is scored
+            const int node = ahead_node;
+            ahead_node = node_ids && a.entry + 1 < n ? __ldg(node_ids + a.entry + 1) : a.entry + 1;
+            c_node = (node >= 0 && node < t.n_nodes) ? node : -1;
+            if (c_node >= 0) c_visits = __ldg(t.node_visits + c_node);
+        }
+        if (c_node < 0) return a;
+        a.node = c_node; a.visits = c_visits;
+        a.slots = min(kSegSlots, t.pitch - a.seg * kSegSlots);
+        // vectors lane and lane + 32 of the segment: four existence bits each, from the node's mask row (eight
+        // vectors a word, so the two words of a lane are four apart)
+        const uint32_t* mask = t.legal_bits + (size_t)c_node * t.mask_words + a.seg * (kSegSlots / 32) + mask_lane;
+        if (lane * 4 < a.slots) a.bits = (__ldg(mask) >> mask_shift) & 0xFu;
+        if (lane * 4 + 128 < a.slots) a.bits |= ((__ldg(mask + 4) >> mask_shift) & 0xFu) << 4;
+        return a;
+    };
+    auto fetch = [&](const Item& a, int stage) {       // call with lanes 0-3
+        if (a.node < 0) return;
+        const uint32_t bar = s_u32(bars + stage);
+        const uint32_t dst = s_u32(ring + (size_t)stage * kStageBytes);
+        const uint32_t bytes = (uint32_t)a.slots * 4;
+        if (lane == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(4 * bytes) : "memory");
+        const size_t off = (size_t)a.node * t.pitch + (size_t)a.seg * kSegSlots;
+        const void* src = lane == 0 ? (const void*)(t.N + off) : lane == 1 ? (const void*)(t.W + off)
+                        : lane == 2 ? (const void*)(t.P + off) : (const void*)(t.VL + off);
+        row_copy(dst + lane * kRowBytes, src, bytes, bar);
+    };
+    Best nb{-INFINITY, -1};                       // best of the current entry's segments so far (slot within the row)
+    int nb_entry = -1;
+    float explore = 0.0f;                         // c_puct * sqrt(visits) of that entry's node
+    auto flush = [&]() {
+        // + 0.0f turns -0 into +0: the two compare equal in the reference and must not be ordered by their bits
+        if (lane == 0 && nb.idx >= 0)
+            atomicMax(best_word + nb_entry, ((unsigned long long)order_bits(__fadd_rn(nb.score, 0.0f)) << 32) | (uint32_t)~(uint32_t)nb.idx);
+        nb.score = -INFINITY; nb.idx = -1;
+    };
+    Item q[kSegDepth - 1];
+#pragma unroll
+    for (int d = 0; d < kSegDepth - 1; ++d) {
+        q[d] = lookup();
+        if (lane < 4) fetch(q[d], d);
+    }
+    uint32_t phase_bits = 0;
+    for (int k = 0;; ++k) {
+        const int stage = k % kSegDepth;
+        __syncwarp();                           // every lane is done reading the stage about to be refilled
+        const Item cur = q[0];
+        if (cur.entry >= n) break;
+#pragma unroll
+        for (int d = 0; d + 1 < kSegDepth - 1; ++d) q[d] = q[d + 1];
+        q[kSegDepth - 2] = lookup();
+        if (lane < 4) fetch(q[kSegDepth - 2], (k + kSegDepth - 1) % kSegDepth);
+        if (cur.node < 0) continue;               // the finishing kernel reports -1 for an entry that names no node
+        if (cur.entry != nb_entry) {
+            flush();
+            nb_entry = cur.entry;
+            explore = __fmul_rn(c_puct, __fsqrt_rn((float)cur.visits));
+        }
+        if (!bar_wait(s_u32(bars + stage), (phase_bits >> stage) & 1u)) {
+            if (lane == 0) atomicExch(error_word, 4);
+            break;
+        }
+        phase_bits ^= 1u << stage;
+        const uint8_t* st = ring + (size_t)stage * kStageBytes;
+        const int4* N4 = reinterpret_cast<const int4*>(st);
+        const float4* W4 = reinterpret_cast<const float4*>(st + kRowBytes);
+        const float4* P4 = reinterpret_cast<const float4*>(st + 2 * kRowBytes);
+        const int4* V4 = reinterpret_cast<const int4*>(st + 3 * kRowBytes);
+        // Approximate scores s~ (one MUFU reciprocal per division) with |s - s~| < kBracket * m, m = |q~| + |u~|;
+        // M = the largest m of the segment bounds every slot's error, so the segment's exact maximum is attained
+        // among the slots with s~ >= max s~ - 2 kBracket M.
+        float sc[8];
+        float lane_s = -INFINITY, lane_m = 0.0f;
+        uint32_t range = 0;
+        auto scores = [&](auto magic) {
+            constexpr bool kMagic = decltype(magic)::value;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t m = (cur.bits >> (4 * h)) & 0xFu;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sc[4 * h + j] = -INFINITY;
+                if (m) {                          // a vector without an existing child (most of a chess row) costs nothing
+                    const int v = lane + 32 * h;
+                    const int4 nn = N4[v]; const float4 ww = W4[v]; const float4 pp = P4[v]; const int4 ll = V4[v];
+                    approx_score<kMagic>(nn.x, ww.x, pp.x, ll.x, explore, m & 1u, sc[4 * h + 0], lane_s, lane_m, range);
+                    approx_score<kMagic>(nn.y, ww.y, pp.y, ll.y, explore, m & 2u, sc[4 * h + 1], lane_s, lane_m, range);
+                    approx_score<kMagic>(nn.z, ww.z, pp.z, ll.z, explore, m & 4u, sc[4 * h + 2], lane_s, lane_m, range);
+                    approx_score<kMagic>(nn.w, ww.w, pp.w, ll.w, explore, m & 8u, sc[4 * h + 3], lane_s, lane_m, range);
+                }
+            }
+        };
+        scores(std::true_type{});
+        if (__any_sync(0xffffffffu, range >> 23)) {       // a count beyond 2^23 or negative: the conversions proper
+            lane_s = -INFINITY; lane_m = 0.0f;
+            scores(std::false_type{});
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            lane_s = fmaxf(lane_s, __shfl_xor_sync(0xffffffffu, lane_s, off));
+            lane_m = fmaxf(lane_m, __shfl_xor_sync(0xffffffffu, lane_m, off));
+        }
+        float thr = fmaf(-2.0f * kBracket, lane_m, lane_s);
+        thr = thr == thr ? thr : -INFINITY;       // inf - inf: no usable bound, every existing slot is a candidate
+        uint32_t cand = 0;
+#pragma unroll
+        for (int k2 = 0; k2 < 8; ++k2) cand |= (uint32_t)(sc[k2] >= thr) << k2;
+        cand &= cur.bits;
+        const int32_t* Ns = reinterpret_cast<const int32_t*>(N4);
+        const float* Ws = reinterpret_cast<const float*>(W4);
+        const float* Ps = reinterpret_cast<const float*>(P4);
+        const int32_t* Vs = reinterpret_cast<const int32_t*>(V4);
+        // the exact expression for the candidates (usually one or two of the 256), by the whole warp at once
+        uint32_t lanes = __ballot_sync(0xffffffffu, cand != 0);
+        while (lanes) {
+            const int l = __ffs(lanes) - 1;
+            lanes &= lanes - 1;
+            uint32_t c = __shfl_sync(0xffffffffu, cand, l);
+            while (c) {
+                const int k2 = __ffs(c) - 1;
+                c &= c - 1;
+                const int slot = (l + 32 * (k2 >> 2)) * 4 + (k2 & 3);
+                const float e = puct_score(Ns[slot], Ws[slot], Ps[slot], Vs[slot], explore);
+                const int row_slot = cur.seg * kSegSlots + slot;
+                if (e > nb.score || (e == nb.score && row_slot < nb.idx)) { nb.score = e; nb.idx = row_slot; }
+            }
+        }
+    }
+    flush();
+}
+
+// One warp per entry of the launch: the node's word -> selection (lowest-visited existing child when no score
+// was comparable, as the narrow-row kernels), virtual loss, word back to zero.
+__global__ void __launch_bounds__(256)
+puct_select_finish_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids, int n, int vl_value, int apply_vl,
+                          int32_t* __restrict__ sel_out, unsigned long long* __restrict__ best_word) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const int entry = (int)((blockIdx.x * (unsigned)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+    if (entry >= n) return;
+    const int node = node_ids ? __ldg(node_ids + entry) : entry;
+    const unsigned long long w = __ldcg(best_word + entry);
+    int sel = -1;
+    if (node >= 0 && node < t.n_nodes)
+        sel = w ? (int)~(uint32_t)w
+                : least_visited_row(t.N + (size_t)node * t.pitch, t.legal_bits + (size_t)node * t.mask_words, t.n_children, lane);
+    if (lane == 0) {
+        sel_out[entry] = sel;
+        if (sel >= 0 && apply_vl && vl_value > 0) atomicAdd(t.VL + (size_t)node * t.pitch + sel, vl_value);
+        if (w) best_word[entry] = 0ull;
+    }
+}
+
+// One 64-bit word per entry of a wide-row launch, zero between launches.  Launches on one stream are ordered, so
+// the words are kept per (device, stream) and grown on demand; a stream's words are never freed (a few KB each).
+static unsigned long long* wide_scratch(int dev, cudaStream_t stream, int n) {
+    struct Slot { unsigned long long* p; int cap; };
+    static std::mutex mu;
+    static std::map<std::pair<int, cudaStream_t>, Slot> slots;
+    std::lock_guard<std::mutex> lock(mu);
+    Slot& s = slots[{dev, stream}];
+    if (s.cap >= n) return s.p;
+    // the old words may still be in use by launches in flight on this stream: release them in stream order
+    if (s.p && cudaFreeAsync(s.p, stream) != cudaSuccess) return nullptr;
+    s.p = nullptr; s.cap = 0;
+    const int cap = n < 1024 ? 1024 : n;
+    unsigned long long* p = nullptr;
+    if (cudaMallocAsync(reinterpret_cast<void**>(&p), (size_t)cap * 8, stream) != cudaSuccess) return nullptr;
+    if (cudaMemsetAsync(p, 0, (size_t)cap * 8, stream) != cudaSuccess) { cudaFreeAsync(p, stream); return nullptr; }
+    s.p = p; s.cap = cap;
+    return p;
+}
+
 // max(old - amount, 0) as one atomic step (sequentially the same result as
 // the reference's fetch_sub followed by the store of zero).
 __device__ __forceinline__ void vl_sub_clamped(int32_t* addr, int amount, bool one_first) {
@@ -437,14 +622,23 @@ __global__ void vl_apply_kernel(ob200_tree_view t, const int32_t* __restrict__ n
     atomicAdd(t.VL + (size_t)node * t.pitch + s, vl_value);
 }
 
+// MCTSNode::removeVirtualLoss(int) as the reference writes it (src/mcts/mcts_node_virtual_loss.cpp:32-42, and its
+// kernel src/mcts/gpu_virtual_loss_kernels.cu:123-129): subtract, and if the counter held less than the amount, put it
+// back to zero.  One atomic round trip in the common case; reverts that meet on one counter end at the same value
+// as in any sequential order (all of them subtract the same amount, and the zero is written last).
+// Launched with programmatic stream serialization: its CTAs may be scheduled while the kernel ahead of it in the
+// stream (the selection that produces `sel`) is still running, and wait here until that kernel's writes are visible.
 __global__ void vl_revert_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids,
                                  const int32_t* __restrict__ sel, int n, int vl_value) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int node = node_ids ? node_ids[i] : i;
     const int s = sel[i];
     if (node < 0 || node >= t.n_nodes || s < 0 || s >= t.n_children) return;
-    vl_sub_clamped(t.VL + (size_t)node * t.pitch + s, vl_value, false);
+    int32_t* addr = t.VL + (size_t)node * t.pitch + s;
+    const int old = atomicSub(addr, vl_value);
+    if (old < vl_value) atomicMax(addr, 0);
 }
 
 __global__ void backup_kernel(ob200_tree_view t, const int32_t* __restrict__ paths,
@@ -625,18 +819,39 @@ int ob200_launch_puct_select(const ob200_tree_view* tree, const int32_t* node_id
         puct_select_staged_kernel<<<want < sms ? want : sms, kStagedWarps * 32, smem, as_stream(stream)>>>(
             *tree, node_ids, n, c_puct, vl_value, apply_vl, sel_out, errw);
         OB200_LAUNCHED("puct_select_staged_kernel");
-    } else if (tree->pitch >= kWideMinPitch && (size_t)tree->pitch * 4 <= 160 * 1024) {
-        // chess-wide rows: a CTA per node
+    } else if (tree->pitch >= kWideMinPitch) {
+        // chess-wide rows: segments of 256 slots through the staged design, a counter and a (score, slot) pair per
+        // segment as scratch, allocated and freed in stream order
         int dev = 0, sms = 0;
         OB200_CUDA_OK(cudaGetDevice(&dev));
         OB200_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        const int smem = tree->pitch * 4;
-        if (smem > 48 * 1024)
-            OB200_CUDA_OK(cudaFuncSetAttribute(puct_select_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        const int want = sms * 8;
-        puct_select_wide_kernel<<<n < want ? n : want, kWideThreads, smem, as_stream(stream)>>>(
-            *tree, node_ids, n, c_puct, vl_value, apply_vl, sel_out);
-        OB200_LAUNCHED("puct_select_wide_kernel");
+        const int segs = (tree->pitch + kSegSlots - 1) / kSegSlots;
+        const int smem = kSegWarps * kSegDepth * 4 * kSegSlots * 4 + kSegWarps * kSegDepth * 8;
+        static bool configured_w[64] = {false};
+        if (dev < 0 || dev >= 64 || !configured_w[dev]) {
+            OB200_CUDA_OK(cudaFuncSetAttribute(puct_select_segmented_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            if (dev >= 0 && dev < 64) configured_w[dev] = true;
+        }
+        int* errw = device_error_word();
+        if (!errw) return set_error(OB200_ERR_CUDA, "ob200_launch_puct_select: cannot resolve the device error word");
+        unsigned long long* words = wide_scratch(dev, as_stream(stream), n);
+        if (!words) return set_error(OB200_ERR_CUDA, "ob200_launch_puct_select: cannot allocate %d selection words", n);
+        const long long items = (long long)n * segs;
+        const long long want = (items + kSegWarps - 1) / kSegWarps;
+        puct_select_segmented_kernel<<<(unsigned)(want < sms ? want : sms), kSegWarps * 32, smem, as_stream(stream)>>>(
+            *tree, node_ids, n, segs, c_puct, words, errw);
+        OB200_CUDA_OK(cudaGetLastError());
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)((n + 7) / 8));
+        cfg.blockDim = dim3(256);
+        cfg.stream = as_stream(stream);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, puct_select_finish_kernel, *tree, node_ids, n, vl_value, apply_vl, sel_out, words));
+        counters().launches.fetch_add(2, std::memory_order_relaxed);
     } else {
         const int blocks = (n + kWarpsPerBlock - 1) / kWarpsPerBlock;
         puct_select_kernel<<<blocks, kWarpsPerBlock * 32, 0, as_stream(stream)>>>(*tree, node_ids, n, c_puct, vl_value,
@@ -664,7 +879,13 @@ int ob200_launch_vl_revert(const ob200_tree_view* tree, const int32_t* node_ids,
     if (n < 0 || !sel) return set_error(OB200_ERR_INVALID, "ob200_launch_vl_revert: bad arguments");
     if (int rc = require_device()) return rc;
     if (n == 0 || vl_value <= 0) return OB200_OK;
-    vl_revert_kernel<<<(n + 255) / 256, 256, 0, as_stream(stream)>>>(*tree, node_ids, sel, n, vl_value);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((n + 255) / 256)); cfg.blockDim = dim3(256); cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, vl_revert_kernel, *tree, node_ids, sel, (int)n, (int)vl_value));
     OB200_LAUNCHED("vl_revert_kernel");
     return OB200_OK;
 }

@@ -86,8 +86,8 @@ def test_select_full_size_pass(api, oracle):
 
 
 def test_select_wide_rows_edge_cases(api, oracle):
-    """Chess-wide rows (4,672 slots) take the CTA-per-node kernel: the same edge cases, a node
-    list with repeats and out-of-range ids, more nodes than CTAs."""
+    """Chess-wide rows (4,672 slots) take the segmented kernel: the same edge cases, a node
+    list with repeats and out-of-range ids, more (node, segment) pairs than warps."""
     import torch
     nc = 4672
     t = synth.make_selection_tree(1500, nc, seed=31)
@@ -99,11 +99,16 @@ def test_select_wide_rows_edge_cases(api, oracle):
     t["node_visits"][5] = 0                                 # unvisited parent: exploration term is 0
     t["VL"][6] = 1000                                       # large virtual loss everywhere
     t["P"][7, :nc] = 1.0 / nc; t["N"][7] = 3; t["W"][7] = 1.5; t["VL"][7] = 0   # a wide tie at a non-zero score
+    t["N"][8, 100:140] = 2 ** 24 + 3; t["W"][8, 100:140] = 2.0 ** 24    # visit counts beyond the fast conversion's range
+    t["N"][8, 3000] = 2 ** 30; t["W"][8, 3000] = 2.0 ** 30
+    t["VL"][9, 5] = -2; t["VL"][9, 4000] = -1               # negative counts take the conversions proper as well
+    t["N"][10] = 1; t["VL"][10] = 0; t["W"][10] = 0.0; t["P"][10] = 0.0   # a tie of zeros of both signs across segments:
+    t["W"][10, :600] = -0.0; t["P"][10, :600] = -0.0        # -0 == +0, so the lowest existing slot wins
     ref = synth.copy_tree(t)
     rng = np.random.default_rng(5)
-    ids = np.concatenate([np.array([0, 1, 2, 3, 4, 5, 6, 7, 7, 1499, 1], np.int32),
+    ids = np.concatenate([np.array([0, 1, 2, 3, 4, 5, 6, 7, 7, 1499, 1, 8, 9, 10], np.int32),
                           rng.integers(0, 1500, 1400).astype(np.int32)])
-    ids[20], ids[21] = -1, 1500
+    ids[24], ids[25] = -1, 1500
     dt = api.DeviceTree(t)
     sel = dt.select(torch.from_numpy(ids).cuda(), c_puct=1.5, vl_value=3, apply_vl=False).cpu().numpy()
     want = np.full(len(ids), -1, np.int32)
