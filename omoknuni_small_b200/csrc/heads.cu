@@ -142,12 +142,18 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
                  : "memory");
 }
-__global__ void __launch_bounds__(256)
-fc_kernel(const float* __restrict__ in, const float* __restrict__ WT, const float* __restrict__ bias,
-          float* __restrict__ out, int B, int K, int Nout, int relu) {
-    __shared__ __align__(16) FcStage st[2][kFcStages];
+struct FcProblem {
+    const float* in;     // [B][K]
+    const float* WT;     // [K][Nout]
+    const float* bias;   // [Nout]
+    float* out;          // [B][Nout]
+    int K, Nout, relu;
+};
+__device__ __forceinline__ void fc_tile(FcStage (*st)[kFcStages], const float* __restrict__ in, const float* __restrict__ WT,
+                                        const float* __restrict__ bias, float* __restrict__ out, int B, int K, int Nout,
+                                        int relu, int tile_b, int tile_n) {
     const int half = threadIdx.x >> 7, t = threadIdx.x & 127;
-    const int b0 = blockIdx.x * kFcTileB, n0 = blockIdx.y * kFcTileN;
+    const int b0 = tile_b * kFcTileB, n0 = tile_n * kFcTileN;
     const int tb = (t >> 4) * 4, tn = (t & 15) * 4;   // 8 x 16 threads
     const int tiles = (K + kFcTileK - 1) / kFcTileK, split = (tiles + 1) / 2;
     const int first = half ? split : 0, last = half ? tiles : split;
@@ -224,6 +230,26 @@ fc_kernel(const float* __restrict__ in, const float* __restrict__ WT, const floa
     }
 }
 
+__global__ void __launch_bounds__(256)
+fc_kernel(const float* __restrict__ in, const float* __restrict__ WT, const float* __restrict__ bias,
+          float* __restrict__ out, int B, int K, int Nout, int relu) {
+    __shared__ __align__(16) FcStage st[2][kFcStages];
+    fc_tile(st, in, WT, bias, out, B, K, Nout, relu, blockIdx.x, blockIdx.y);
+}
+
+// Two independent layers over the same boards in one launch (the policy FC and the value head's first FC): the
+// first tiles_n0 values of blockIdx.y are output tiles of problem 0, the rest of problem 1.  Each output is
+// computed exactly as fc_kernel computes it.
+__global__ void __launch_bounds__(256)
+fc_pair_kernel(FcProblem p0, FcProblem p1, int B, int tiles_n0) {
+    __shared__ __align__(16) FcStage st[2][kFcStages];
+    asm volatile("griddepcontrol.wait;" ::: "memory");               // the inputs come from the kernel ahead in the stream
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const bool first = (int)blockIdx.y < tiles_n0;
+    const FcProblem& p = first ? p0 : p1;
+    fc_tile(st, p.in, p.WT, p.bias, p.out, B, p.K, p.Nout, p.relu, blockIdx.x, first ? blockIdx.y : blockIdx.y - tiles_n0);
+}
+
 __device__ __forceinline__ float block_reduce(float v, bool is_max, float* red) {
     for (int off = 16; off > 0; off >>= 1) {
         const float o = __shfl_xor_sync(0xffffffffu, v, off);
@@ -262,7 +288,64 @@ value_out_kernel(const float* __restrict__ hidden, const float* __restrict__ w2,
     if (lane == 0) value[b] = tanhf(s + b2);
 }
 
+// The tails of both heads in one launch, started as a programmatic dependent of fc_pair_kernel: CTAs
+// [0, softmax_rows) normalise one row of logits each as softmax_kernel does, the rest finish four boards' values
+// each as value_out_kernel does (a warp per board).
+__global__ void __launch_bounds__(128)
+head_tails_kernel(float* __restrict__ logits, int A, int softmax_rows, const float* __restrict__ hidden,
+                  const float* __restrict__ w2, float b2, int H, int B, float* __restrict__ value) {
+    __shared__ float red[4];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if ((int)blockIdx.x < softmax_rows) {
+        float* row = logits + (size_t)blockIdx.x * A;
+        float m = -INFINITY;
+        for (int i = threadIdx.x; i < A; i += blockDim.x) m = fmaxf(m, row[i]);
+        m = block_reduce(m, true, red);
+        float s = 0.0f;
+        for (int i = threadIdx.x; i < A; i += blockDim.x) s += expf(row[i] - m);
+        s = block_reduce(s, false, red);
+        const float inv = 1.0f / s;
+        for (int i = threadIdx.x; i < A; i += blockDim.x) row[i] = expf(row[i] - m) * inv;
+    } else {
+        const int b = ((int)blockIdx.x - softmax_rows) * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+        if (b >= B) return;
+        float s = 0.0f;
+        for (int i = lane; i < H; i += 32) s = fmaf(hidden[(size_t)b * H + i], w2[i], s);
+        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (lane == 0) value[b] = tanhf(s + b2);
+    }
+}
+
 }  // namespace
+
+// The FC part of both heads in two launches: {policy FC (when policy_in is given), value FC1 + ReLU}, then
+// {softmax over the logits (when asked), value FC2 + tanh}.  Results equal launch_fc / launch_softmax /
+// launch_value_out on the same buffers bit for bit.
+int launch_head_fcs(const float* policy_in, const float* WpT, const float* bp, float* policy_out, int policy_k, int policy_size,
+                    int softmax, const float* value_in, const float* W1T, const float* b1, float* hidden, int value_k, int H,
+                    const float* w2, float b2, float* value_out, int B, cudaStream_t st) {
+    const FcProblem p0{policy_in, WpT, bp, policy_out, policy_k, policy_size, 0};
+    const FcProblem p1{value_in, W1T, b1, hidden, value_k, H, 1};
+    const int tiles0 = policy_in ? (policy_size + kFcTileN - 1) / kFcTileN : 0, tiles1 = (H + kFcTileN - 1) / kFcTileN;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((B + kFcTileB - 1) / kFcTileB, tiles0 + tiles1);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, fc_pair_kernel, p0, p1, B, tiles0));
+    counters().launches.fetch_add(1, std::memory_order_relaxed);
+    const int rows = softmax ? B : 0;
+    cfg.gridDim = dim3((unsigned)(rows + (B + 3) / 4));
+    cfg.blockDim = dim3(128);
+    OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, head_tails_kernel, policy_out, policy_size, rows, (const float*)hidden, w2, b2, H, B, value_out));
+    counters().launches.fetch_add(1, std::memory_order_relaxed);
+    return OB200_OK;
+}
 
 int launch_head_conv(const void* tower, const float* w, const float* bias, int HC, int pc,
                      float* hp, float* hv, int B, int S, cudaStream_t st, int C, int dtype) {

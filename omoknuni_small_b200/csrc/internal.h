@@ -65,6 +65,11 @@ int launch_head_conv(const void* tower, const float* w, const float* bias, int H
 int launch_fc(const float* in, const float* WT, const float* bias, float* out, int B, int K, int Nout, int relu,
               cudaStream_t st);
 int launch_softmax(float* x, int B, int A, cudaStream_t st);
+// Both heads' FC layers in two launches ({policy FC, value FC1}, {softmax, value FC2 + tanh}); policy_in may be
+// null (a policy that is already in policy_out); results as the single-layer launchers give them.
+int launch_head_fcs(const float* policy_in, const float* WpT, const float* bp, float* policy_out, int policy_k, int policy_size,
+                    int softmax, const float* value_in, const float* W1T, const float* b1, float* hidden, int value_k, int H,
+                    const float* w2, float b2, float* value_out, int B, cudaStream_t st);
 int launch_value_out(const float* hidden, const float* w2, float b2, int H, int B, float* value, cudaStream_t st);
 int launch_value_head_static(const void* tower, const float* vw, const float* vb, int vc, const float* W1T,
                              const float* b1, const float* w2, float b2, int H, int B, int S, float* value_out,

@@ -26,8 +26,6 @@ struct ob200_net {
     bool finalized = false;
     std::mutex mu;                  // calls on one handle are serialised
     cudaStream_t stream = nullptr;  // used by the host-buffer calls
-    cudaStream_t side_stream = nullptr;   // the value head runs here, beside the policy head
-    cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
     // device: tower
     std::vector<void*> conv_w;      // packed bf16, 1 + 2 * blocks
     std::vector<float*> conv_b;
@@ -227,12 +225,9 @@ void ob200_net_destroy(ob200_net* n) {
     if (!n) return;
     cudaSetDevice(n->cfg.device);
     if (n->stream) { cudaStreamSynchronize(n->stream); cudaStreamDestroy(n->stream); }
-    if (n->side_stream) { cudaStreamSynchronize(n->side_stream); cudaStreamDestroy(n->side_stream); }
     if (n->copy_stream) { cudaStreamSynchronize(n->copy_stream); cudaStreamDestroy(n->copy_stream); }
     if (n->planes_copied) cudaEventDestroy(n->planes_copied);
     for (auto& sl : n->slot) { if (sl.computed) cudaEventDestroy(sl.computed); if (sl.done) cudaEventDestroy(sl.done); }
-    if (n->fork_ev) cudaEventDestroy(n->fork_ev);
-    if (n->join_ev) cudaEventDestroy(n->join_ev);
     for (void* p : n->owned_dev) cudaFree(p);
     for (void* p : n->owned_host) cudaFreeHost(p);
     delete n;
@@ -394,12 +389,9 @@ int ob200_net_finalize(ob200_net* n) {
     if (int rc = dev_alloc(n, &n->d_hist, MB * 17, false)) return rc;
     if (int rc = host_alloc(n, &n->h_planes, n->planes_capacity)) return rc;
     OB200_CUDA_OK(cudaStreamCreateWithFlags(&n->stream, cudaStreamNonBlocking));
-    OB200_CUDA_OK(cudaStreamCreateWithFlags(&n->side_stream, cudaStreamNonBlocking));
     OB200_CUDA_OK(cudaStreamCreateWithFlags(&n->copy_stream, cudaStreamNonBlocking));
     OB200_CUDA_OK(cudaEventCreateWithFlags(&n->planes_copied, cudaEventDisableTiming));
     OB200_CUDA_OK(cudaEventRecord(n->planes_copied, n->stream));
-    OB200_CUDA_OK(cudaEventCreateWithFlags(&n->fork_ev, cudaEventDisableTiming));
-    OB200_CUDA_OK(cudaEventCreateWithFlags(&n->join_ev, cudaEventDisableTiming));
     OB200_CUDA_OK(cudaDeviceSynchronize());
     n->host.clear();
     n->finalized = true;
@@ -505,24 +497,11 @@ int forward_device(ob200_net* n, const void* input_bt, int B, float* policy_out,
     } else if (!heads_done) {
         if (int rc = launch_head_conv(n->act[x], n->head_w, n->head_b, pc + vc, pc, n->hp, n->hv, B, S, st, F, c.tower_dtype)) return rc;
     }
-    // the two heads are independent from here on: the value head (FC + FC/tanh) runs on a second
-    // stream beside the policy head (FC + softmax) and joins `st` again at the end
-    cudaStream_t vst = st;
-    if (n->side_stream && n->fork_ev && n->join_ev) {
-        OB200_CUDA_OK(cudaEventRecord(n->fork_ev, st));
-        OB200_CUDA_OK(cudaStreamWaitEvent(n->side_stream, n->fork_ev, 0));
-        vst = n->side_stream;
-    }
-    if (c.policy_kind != OB200_POLICY_CONV_PLANES)
-        if (int rc = launch_fc(n->hp, n->WpT, n->bp, policy_out, B, pc * S2, c.policy_size, 0, st)) return rc;
-    if (out_kind == OB200_OUT_PROBS)
-        if (int rc = launch_softmax(policy_out, B, c.policy_size, st)) return rc;
-    if (int rc = launch_fc(n->hv, n->W1T, n->b1, n->hidden, B, vc * S2, c.value_hidden, 1, vst)) return rc;
-    if (int rc = launch_value_out(n->hidden, n->w2, n->b2, c.value_hidden, B, value_out, vst)) return rc;
-    if (vst != st) {
-        OB200_CUDA_OK(cudaEventRecord(n->join_ev, vst));
-        OB200_CUDA_OK(cudaStreamWaitEvent(st, n->join_ev, 0));
-    }
+    // the FC layers of both heads: {policy FC, value FC1} in one launch, {softmax, value FC2 + tanh} in the next
+    const bool fc_policy = c.policy_kind != OB200_POLICY_CONV_PLANES;
+    if (int rc = launch_head_fcs(fc_policy ? n->hp : nullptr, n->WpT, n->bp, policy_out, pc * S2, c.policy_size,
+                                 out_kind == OB200_OUT_PROBS, n->hv, n->W1T, n->b1, n->hidden, vc * S2, c.value_hidden, n->w2,
+                                 n->b2, value_out, B, st)) return rc;
     counters().evals.fetch_add((uint64_t)B, std::memory_order_relaxed);
     counters().batches.fetch_add(1, std::memory_order_relaxed);
     return OB200_OK;
