@@ -543,6 +543,9 @@ def gpu_arm(args):
                          # input tensor and the weights are read; the board-resident tower writes nothing back to DRAM
                          # (its output stays in L2), the cooperative-launch tower works out of L2 after the first layer
                          "traffic": {2: 18.38e6, 1: 21.05e6}.get(tower_path, 21 * 33.66e6) * B / 512.0, "traffic_unit": "bytes/launch",
+                         # the same kernel as the network step launches it (input planes written from the move histories,
+                         # no input tensor): the packed weights once and 34 bytes of history per board
+                         "traffic_in_step": 1.765e6 + 34.0 * B,
                          "traffic_source": {2: "profiles/conv_tower_resident_kernel_gomoku15_batch512.md (scaled by batch)",
                                             1: "profiles/conv_tower_kernel_gomoku15_batch512.md (scaled by batch)"}.get(
                                                 tower_path, "profiles/conv3x3_kernel_gomoku15_batch512.md (21 launches, scaled by batch)")},
