@@ -562,7 +562,20 @@ typedef struct ob200_search_config {
     float dirichlet_epsilon;    /* 0.25; 0 disables the root noise                 */
     int32_t value_sign;         /* +1 reference batched loop, -1 negamax           */
     int32_t use_transposition_table; /* MCTSSettings::use_transposition_table      */
-    uint64_t seed;              /* root-noise generator, Zobrist keys              */
+    uint64_t seed;              /* root-noise generator, Zobrist keys, widening    */
+    /* MCTSNode::expand's two limits on the children a node gets
+     * (src/mcts/mcts_node.cpp:283-340).  max_children: the first max_children
+     * legal moves in move order; 0 = the reference's 1,000 (never reached on a
+     * 225-move board).  use_progressive_widening (MCTSSettings, off in the shipped
+     * configuration): a node keeps a random subset of
+     * max(8, progressive_widening_c * (visits + 1)^progressive_widening_k) of its
+     * legal moves; a node is expanded once, with no visits yet, so the count is
+     * max(8, floor(c)).  The subset is a function of (seed, number of
+     * ob200_search_run calls so far, node id). */
+    int32_t max_children;
+    int32_t use_progressive_widening;
+    float progressive_widening_c;
+    float progressive_widening_k;
 } ob200_search_config;
 
 typedef struct ob200_search_stats {

@@ -42,6 +42,10 @@ public:
         c.value_sign = 1;                                    // the reference's batched loop
         c.use_transposition_table = settings.use_transposition_table ? 1 : 0;
         c.seed = seed;
+        c.max_children = 0;                                  // MCTSNode::expand's own cap of 1,000
+        c.use_progressive_widening = settings.use_progressive_widening ? 1 : 0;
+        c.progressive_widening_c = settings.progressive_widening_c;
+        c.progressive_widening_k = settings.progressive_widening_k;
         cfg_ = c;
         if (!net_ || !net_->handle() || ob200_search_create(net_->handle(), &c, &search_) != OB200_OK) {
             std::fprintf(stderr, "[B200GomokuSearch] %s\n", ob200_last_error());

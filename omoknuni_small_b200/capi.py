@@ -38,11 +38,23 @@ class NetConfig(C.Structure):
                                           "policy_kind", "tower_dtype")]
 
 
+def widening_seed(seed, runs_before):
+    """The 64-bit value that, with a node's id and a move, ranks the moves of a node under progressive widening
+    during the (runs_before + 1)-th ob200_search_run of a handle created with `seed`."""
+    m = (1 << 64) - 1
+    z = (seed + 0x632BE59BD9B4E019 * (runs_before + 1)) & m
+    z ^= z >> 31
+    z = (z * 0xD6E8FEB86659FD93) & m
+    z ^= z >> 32
+    return z
+
+
 class SearchConfig(C.Structure):
     _fields_ = [("n_trees", C.c_int32), ("sims_per_move", C.c_int32), ("leaf_batch", C.c_int32), ("max_depth", C.c_int32),
                 ("c_puct", C.c_float), ("virtual_loss", C.c_int32), ("dirichlet_alpha", C.c_float),
                 ("dirichlet_epsilon", C.c_float), ("value_sign", C.c_int32), ("use_transposition_table", C.c_int32),
-                ("seed", C.c_uint64)]
+                ("seed", C.c_uint64), ("max_children", C.c_int32), ("use_progressive_widening", C.c_int32),
+                ("progressive_widening_c", C.c_float), ("progressive_widening_k", C.c_float)]
 
 
 class SearchStats(C.Structure):
@@ -472,10 +484,14 @@ class Search:
     MCTSEngine::search for many games at once)."""
 
     def __init__(self, net, n_trees=64, sims_per_move=800, leaf_batch=1024, max_depth=64, c_puct=1.5, virtual_loss=3,
-                 dirichlet_alpha=0.3, dirichlet_epsilon=0.25, value_sign=1, transposition_table=False, seed=0):
+                 dirichlet_alpha=0.3, dirichlet_epsilon=0.25, value_sign=1, transposition_table=False, seed=0,
+                 max_children=0, progressive_widening=None):
+        """progressive_widening: None (off, as the reference's shipped configuration) or (c, k) of MCTSSettings."""
         self.net = net                       # keep the network alive
+        pw = progressive_widening
         self.cfg = SearchConfig(n_trees, sims_per_move, leaf_batch, max_depth, c_puct, virtual_loss, dirichlet_alpha,
-                                dirichlet_epsilon, value_sign, int(transposition_table), seed)
+                                dirichlet_epsilon, value_sign, int(transposition_table), seed, max_children,
+                                int(pw is not None), pw[0] if pw else 0.0, pw[1] if pw else 0.0)
         self.h = C.c_void_p()
         check(lib().ob200_search_create(net.h, C.byref(self.cfg), C.byref(self.h)))
 

@@ -12,10 +12,12 @@
 // node t (< n_trees) is the root of tree t; a node's child slot is the board
 // cell of the move (slot == action), its existence bit says the cell is empty.
 #include "internal.h"
+#include <algorithm>
 #include <chrono>
 #include <cmath>
 #include <cstring>
 #include <random>
+#include <utility>
 #include <vector>
 
 struct ob200_search {
@@ -42,6 +44,8 @@ struct ob200_search {
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     uint64_t moves_done = 0;
+    uint32_t* empty_bits = nullptr;            // [max_nodes][mask_words], only when a node's children can be fewer than its legal moves
+    int max_children = 1000, widen_target = 0;
     // expansion plan of a round (per simulation)
     int32_t *plan_status = nullptr, *plan_aux = nullptr, *plan_new_id = nullptr;
     unsigned long long* plan_hash = nullptr;
@@ -61,9 +65,88 @@ constexpr int kMaxDepth = 64;
 
 __device__ __forceinline__ bool bit(const uint32_t* m, int i) { return (m[i >> 5] >> (i & 31)) & 1u; }
 
-// Roots: existence mask = empty cells, statistics zero, no children yet.
+// Which of a new node's legal moves become children (MCTSNode::expand, src/mcts/mcts_node.cpp:283-340): at most
+// max_children of them, the first in move order (the reference's cap of 1,000), and with progressive widening a
+// random subset of `target` of those.  The reference draws the subset with a generator seeded from the operating
+// system's entropy source; here a move's rank is the 64-bit mix of (seed, node id, move), so the same seed gives
+// the same subset, and the `target` lowest ranks are kept.
+struct Widening {
+    uint32_t* empty;            // [max_nodes][mask_words] empty cells of every node's position; null: every legal move is a child
+    int max_children;           // <= 0: no cap
+    int target;                 // <= 0: no widening
+    unsigned long long seed;
+};
+__host__ __device__ __forceinline__ unsigned long long widen_key(unsigned long long seed, int id, int s) {
+    unsigned long long z = seed ^ ((unsigned long long)(id + 1) * 0x9E3779B97F4A7C15ull) ^ ((unsigned long long)(s + 1) * 0xC2B2AE3D27D4EB4Full);
+    z ^= z >> 30; z *= 0xBF58476D1CE4E5B9ull; z ^= z >> 27; z *= 0x94D049BB133111EBull; z ^= z >> 31;
+    return z;
+}
+// One warp, rows of at most 256 slots (8 mask words): exists <- the chosen subset of `empty`.
+__device__ void widen_mask_warp(const uint32_t* empty, uint32_t* exists, int mask_words, const Widening& wd, int id, int lane) {
+    uint32_t w[8];
+    int total = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        w[k] = k < mask_words ? empty[k] : 0u;
+        if (wd.max_children > 0) {                      // the cap: the first max_children legal moves in move order
+            int keep = wd.max_children - total;
+            if (keep < 0) keep = 0;
+            while (__popc(w[k]) > keep) w[k] &= ~(1u << (31 - __clz(w[k])));
+        }
+        total += __popc(w[k]);
+    }
+    if (wd.target > 0 && total > wd.target) {
+        // lane l owns slots 8 l .. 8 l + 7; a slot stays when fewer than `target` legal slots rank below it
+        uint32_t mine = (w[lane >> 2] >> ((lane & 3) * 8)) & 0xFFu;
+        unsigned long long key[8];
+        int rank[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { key[j] = widen_key(wd.seed, id, lane * 8 + j); rank[j] = 0; }
+        for (int l = 0; l < 32; ++l) {
+            const uint32_t theirs = __shfl_sync(0xffffffffu, mine, l);
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+                const unsigned long long k = __shfl_sync(0xffffffffu, key[jj], l);
+                if (!((theirs >> jj) & 1u)) continue;
+                const int s2 = l * 8 + jj;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) rank[j] += (k < key[j] || (k == key[j] && s2 < lane * 8 + j)) ? 1 : 0;
+            }
+        }
+        uint32_t keep = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) keep |= (uint32_t)(((mine >> j) & 1u) && rank[j] < wd.target) << j;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) word |= __shfl_sync(0xffffffffu, keep, 4 * k + b) << (8 * b);
+            w[k] = word;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+        if (k < mask_words && lane == 0) exists[k] = w[k];
+}
+
+// The same choice on the host (the root noise is drawn for the root's children): plain loops.
+void widen_mask_host(const uint32_t* empty, uint32_t* exists, int n_children, int mask_words, int max_children, int target,
+                     unsigned long long seed, int id) {
+    int total = 0;
+    for (int w = 0; w < mask_words; ++w) exists[w] = 0;
+    for (int s = 0; s < n_children; ++s)
+        if (((empty[s >> 5] >> (s & 31)) & 1u) && (max_children <= 0 || total < max_children)) { exists[s >> 5] |= 1u << (s & 31); ++total; }
+    if (target <= 0 || total <= target) return;
+    std::vector<std::pair<unsigned long long, int>> ranked;
+    for (int s = 0; s < n_children; ++s)
+        if ((exists[s >> 5] >> (s & 31)) & 1u) ranked.emplace_back(widen_key(seed, id, s), s);
+    std::sort(ranked.begin(), ranked.end());
+    for (size_t r = (size_t)target; r < ranked.size(); ++r) exists[ranked[r].second >> 5] &= ~(1u << (ranked[r].second & 31));
+}
+
+// Roots: existence mask = empty cells (or the widened subset of them), statistics zero, no children yet.
 __global__ void init_roots_kernel(ob200_tree_view t, const uint32_t* __restrict__ stones, int n_trees,
-                                  int32_t* n_used, int32_t* term_count) {
+                                  int32_t* n_used, int32_t* term_count, Widening wd) {
     const int tree = blockIdx.x;
     const uint32_t* st = stones + (size_t)tree * 16;
     const size_t row = (size_t)tree * t.pitch;
@@ -71,11 +154,16 @@ __global__ void init_roots_kernel(ob200_tree_view t, const uint32_t* __restrict_
         t.N[row + s] = 0; t.W[row + s] = 0.0f; t.VL[row + s] = 0; t.P[row + s] = 0.0f;
         t.child_node[row + s] = -1;
     }
+    uint32_t* own = (wd.empty ? wd.empty : t.legal_bits) + (size_t)tree * t.mask_words;
     for (int w = threadIdx.x; w < t.mask_words; w += blockDim.x) {
         uint32_t occupied = st[w] | st[8 + w];
         uint32_t valid = 0xFFFFFFFFu;
         if ((w + 1) * 32 > t.n_children) valid = (w * 32 >= t.n_children) ? 0u : ((1u << (t.n_children - w * 32)) - 1u);
-        t.legal_bits[(size_t)tree * t.mask_words + w] = ~occupied & valid;
+        own[w] = ~occupied & valid;
+    }
+    if (wd.empty) {
+        __syncthreads();
+        if (threadIdx.x < 32) widen_mask_warp(own, t.legal_bits + (size_t)tree * t.mask_words, t.mask_words, wd, tree, threadIdx.x);
     }
     if (threadIdx.x == 0) {
         t.node_visits[tree] = 0;
@@ -308,7 +396,7 @@ expand_plan_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const i
 __global__ void __launch_bounds__(256)
 expand_rows_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const int32_t* __restrict__ path_len,
                    int n_sims, int max_depth, const float* __restrict__ policy, int policy_size,
-                   unsigned long long* node_hash, int tt_size, PlanScratch ps) {
+                   unsigned long long* node_hash, int tt_size, PlanScratch ps, Widening wd) {
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (i >= n_sims) return;
     const int st = ps.status[i];
@@ -319,13 +407,17 @@ expand_rows_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const i
     const int32_t* p = paths + (size_t)i * max_depth * 2;
     const int parent = p[2 * (len - 1)], slot = p[2 * (len - 1) + 1];
     const size_t row = (size_t)id * t.pitch;
-    const uint32_t* pm = t.legal_bits + (size_t)parent * t.mask_words;
+    // the position's empty cells: the parent's minus the move; they are the children unless the node is widened
+    const uint32_t* pm = (wd.empty ? wd.empty : t.legal_bits) + (size_t)parent * t.mask_words;
+    uint32_t* own = (wd.empty ? wd.empty : t.legal_bits) + (size_t)id * t.mask_words;
     uint32_t* cm = t.legal_bits + (size_t)id * t.mask_words;
-    for (int w = lane; w < t.mask_words; w += 32) cm[w] = pm[w] & ~((w == (slot >> 5)) ? (1u << (slot & 31)) : 0u);
+    for (int w = lane; w < t.mask_words; w += 32) own[w] = pm[w] & ~((w == (slot >> 5)) ? (1u << (slot & 31)) : 0u);
+    __syncwarp();
+    if (wd.empty) { widen_mask_warp(own, cm, t.mask_words, wd, id, lane); __syncwarp(); }
     const float* pol = policy + (size_t)i * policy_size;
     for (int s = lane; s < t.pitch; s += 32) {
         float pr = 0.0f;
-        if (s < t.n_children && bit(pm, s) && s != slot) pr = fminf(1.0f, fmaxf(0.0f, pol[s]));
+        if (s < t.n_children && bit(cm, s)) pr = fminf(1.0f, fmaxf(0.0f, pol[s]));
         t.N[row + s] = 0; t.W[row + s] = 0.0f; t.VL[row + s] = 0; t.P[row + s] = pr;
         t.child_node[row + s] = -1;
     }
@@ -371,7 +463,8 @@ int ob200_search_create(ob200_net* net, const ob200_search_config* cfg, ob200_se
         return set_error(OB200_ERR_UNSUPPORTED, "ob200_search_create: the search is built for 15x15 Gomoku networks (17 or 19 planes, 225 moves)");
     if (cfg->n_trees < 1 || cfg->sims_per_move < 1 || cfg->leaf_batch < cfg->n_trees || cfg->leaf_batch % cfg->n_trees ||
         cfg->leaf_batch > nc->max_batch || cfg->max_depth < 1 || cfg->max_depth > kMaxDepth || cfg->virtual_loss < 0 ||
-        (cfg->value_sign != 1 && cfg->value_sign != -1) || cfg->dirichlet_epsilon < 0 || cfg->dirichlet_epsilon > 1)
+        (cfg->value_sign != 1 && cfg->value_sign != -1) || cfg->dirichlet_epsilon < 0 || cfg->dirichlet_epsilon > 1 ||
+        cfg->max_children < 0 || (cfg->use_progressive_widening && !(cfg->progressive_widening_c >= 0.0f)))
         return set_error(OB200_ERR_INVALID,
                          "ob200_search_create: need leaf_batch a multiple of n_trees and <= the network's max_batch (%d), max_depth in [1,%d], value_sign +-1",
                          nc->max_batch, kMaxDepth);
@@ -390,6 +483,10 @@ int ob200_search_create(ob200_net* net, const ob200_search_config* cfg, ob200_se
     A_(salloc(s, &s->tv.VL, edges)); A_(salloc(s, &s->tv.child_node, edges));
     A_(salloc(s, &s->tv.legal_bits, (size_t)s->max_nodes * s->mask_words));
     A_(salloc(s, &s->tv.node_visits, (size_t)s->max_nodes));
+    s->max_children = cfg->max_children > 0 ? cfg->max_children : 1000;
+    if (cfg->use_progressive_widening)       // the reference's count for a node without visits: (visits + 1)^k = 1
+        s->widen_target = (int)std::max(8.0f, (float)((double)cfg->progressive_widening_c * std::pow(1.0, (double)cfg->progressive_widening_k)));
+    if (s->widen_target > 0 || s->max_children < s->A) A_(salloc(s, &s->empty_bits, (size_t)s->max_nodes * s->mask_words));
     A_(salloc(s, &s->n_used, 1)); A_(salloc(s, &s->term_count, 1));
     A_(salloc(s, &s->root_stones, (size_t)T * 16)); A_(salloc(s, &s->root_hist, (size_t)T * 16));
     A_(salloc(s, &s->root_nh, (size_t)T)); A_(salloc(s, &s->root_tm, (size_t)T)); A_(salloc(s, &s->root_count, (size_t)T));
@@ -509,6 +606,9 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
     OB200_CUDA_OK(cudaMemcpyAsync(s->root_nh, nh.data(), T, cudaMemcpyHostToDevice, st));
     OB200_CUDA_OK(cudaMemcpyAsync(s->root_tm, tm.data(), T, cudaMemcpyHostToDevice, st));
     OB200_CUDA_OK(cudaMemcpyAsync(s->root_count, count.data(), T * 4, cudaMemcpyHostToDevice, st));
+    // the widening ranks change from move to move
+    unsigned long long wseed = c.seed + 0x632BE59BD9B4E019ull * (s->moves_done + 1);
+    wseed ^= wseed >> 31; wseed *= 0xD6E8FEB86659FD93ull; wseed ^= wseed >> 32;
     // root noise: Gamma(alpha, 1) per existing child, normalised (addDirichletNoise, :83-110)
     std::vector<float> noise;
     if (c.dirichlet_epsilon > 0.0f) {
@@ -521,11 +621,18 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
             float* row = noise.data() + (size_t)t * s->pitch;
             float sum = 0.0f;
             int children = 0;
-            auto occupied = [&](int a) { return ((stones[(size_t)t * 16 + (a >> 5)] | stones[(size_t)t * 16 + 8 + (a >> 5)]) >> (a & 31)) & 1u; };
+            uint32_t empty[8], child[8];
+            for (int w = 0; w < 8; ++w) {
+                const uint32_t valid = (w + 1) * 32 <= A ? 0xFFFFFFFFu : (w * 32 >= A ? 0u : ((1u << (A - w * 32)) - 1u));
+                empty[w] = ~(stones[(size_t)t * 16 + w] | stones[(size_t)t * 16 + 8 + w]) & valid;
+                child[w] = empty[w];
+            }
+            if (s->empty_bits) widen_mask_host(empty, child, A, 8, s->max_children, s->widen_target, wseed, t);
+            auto is_child = [&](int a) { return (child[a >> 5] >> (a & 31)) & 1u; };
             for (int a = 0; a < A; ++a)
-                if (!occupied(a)) { row[a] = gamma(rng); sum += row[a]; ++children; }
+                if (is_child(a)) { row[a] = gamma(rng); sum += row[a]; ++children; }
             for (int a = 0; a < A; ++a)
-                if (!occupied(a)) row[a] = sum > 0.0f ? row[a] / sum : 1.0f / (float)children;
+                if (is_child(a)) row[a] = sum > 0.0f ? row[a] / sum : 1.0f / (float)children;
         }
         OB200_CUDA_OK(cudaMemcpyAsync(s->noise, noise.data(), noise.size() * 4, cudaMemcpyHostToDevice, st));
     }
@@ -542,7 +649,8 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
     }
     OB200_CUDA_OK(cudaEventRecord(s->ev0, st));
     // ---- roots: create, evaluate, priors (+ noise) ----
-    init_roots_kernel<<<T, 128, 0, st>>>(s->tv, s->root_stones, T, s->n_used, s->term_count);
+    const Widening wd{s->empty_bits, s->empty_bits ? s->max_children : 0, s->empty_bits ? s->widen_target : 0, wseed};
+    init_roots_kernel<<<T, 128, 0, st>>>(s->tv, s->root_stones, T, s->n_used, s->term_count, wd);
     OB200_LAUNCHED("init_roots_kernel");
     if (int rc = net_forward_gomoku_for_search(s->net, s->root_hist, s->root_nh, s->root_tm, T, s->policy, s->value, st)) return rc;
     if (int rc = ob200_launch_set_priors(&s->tv, s->roots, T, s->policy, A, nullptr, st)) return rc;
@@ -576,7 +684,7 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
                                                        s->tt_key, s->tt_val, s->tt_size, ps);
         OB200_LAUNCHED("expand_plan_kernel");
         expand_rows_kernel<<<(L * 32 + 255) / 256, 256, 0, st>>>(s->tv, s->paths, s->path_len, L, c.max_depth, s->policy, A,
-                                                                s->node_hash, s->tt_size, ps);
+                                                                s->node_hash, s->tt_size, ps, wd);
         OB200_LAUNCHED("expand_rows_kernel");
         if (int rc = ob200_launch_backup(&s->tv, s->paths, s->path_len, s->leaf_value, L, c.max_depth, c.virtual_loss, st)) return rc;
     }

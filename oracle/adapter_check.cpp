@@ -402,6 +402,10 @@ int run_engine(int argc, char** argv) {
             double sum = 0;
             for (float p : r.probabilities) { REQUIRE(p >= 0.0f, "negative probability"); sum += p; }
             REQUIRE(std::fabs(sum - 1.0) < 1e-4, "probabilities sum to %g", sum);
+            // MCTSSettings' defaults switch progressive widening on with c = 2: a node gets max(8, 2) = 8 children
+            int moves_tried = 0;
+            for (float p : r.probabilities) moves_tried += p > 0.0f;
+            REQUIRE(settings.use_progressive_widening && moves_tried >= 1 && moves_tried <= 8, "game %d: %d root moves visited under widening", g, moves_tried);
             REQUIRE(r.stats.total_nodes > 1 && r.stats.total_evaluations > 0, "stats: nodes %zu evaluations %zu", r.stats.total_nodes, r.stats.total_evaluations);
             REQUIRE(r.stats.avg_batch_size > 1.0f && r.stats.total_batches_processed > 0, "stats: batches");
             REQUIRE(r.stats.nodes_per_second > 0.0f, "stats: rate");

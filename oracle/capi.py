@@ -203,9 +203,27 @@ def root_hash(moves, tree_index, zobrist):
     return h ^ ((0x9E3779B97F4A7C15 * (tree_index + 1)) & M)
 
 
-def search_new_trees(move_lists, max_nodes, n_children=225):
+def widen_mask(empty_words, n_children, max_children, target, seed, node_id):
+    """The children a node gets out of its legal moves (oracle_widen_mask in oracle.c)."""
+    e = np.ascontiguousarray(empty_words, np.uint32)
+    out = np.zeros_like(e)
+    L = lib()
+    L.oracle_widen_mask.argtypes = [_u32, _u32, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_int]
+    L.oracle_widen_mask(e, out, n_children, len(e), max_children, target, seed, node_id)
+    return out
+
+
+def widen_target(c, k, visits=0):
+    L = lib()
+    L.oracle_widen_target.argtypes = [C.c_float, C.c_float, C.c_int]
+    L.oracle_widen_target.restype = C.c_int
+    return int(L.oracle_widen_target(c, k, visits))
+
+
+def search_new_trees(move_lists, max_nodes, n_children=225, widen=None):
     """Edge arrays for a search over the given games: node t is the root of game t (existence mask =
-    empty cells), everything else unused."""
+    empty cells), everything else unused.  widen = (max_children, target, seed): the empty cells are kept in
+    tree["empty_bits"] and the roots' children are the chosen subset of them."""
     T = len(move_lists)
     pitch, mw = (n_children + 3) // 4 * 4, (n_children + 31) // 32
     t = {"N": np.zeros((max_nodes, pitch), np.int32), "W": np.zeros((max_nodes, pitch), np.float32),
@@ -218,6 +236,10 @@ def search_new_trees(move_lists, max_nodes, n_children=225):
         bits = np.zeros(mw * 32, np.uint8)
         bits[:n_children] = empty
         t["legal_bits"][g] = np.packbits(bits.reshape(mw, 32), axis=1, bitorder="little").view(np.uint32).reshape(mw)
+    if widen is not None:
+        t["empty_bits"] = t["legal_bits"].copy()
+        for g in range(T):
+            t["legal_bits"][g] = widen_mask(t["empty_bits"][g], n_children, widen[0], widen[1], widen[2], g)
     return t
 
 
@@ -239,10 +261,10 @@ def dirichlet_normalize(gammas):
 
 
 def search_expand(tree, node_hash, paths, path_len, sims_per_tree, move_lists, policy, value, value_sign,
-                  value_quantum, zobrist, board_size=15):
-    """The expansion step of one round (oracle_search_expand in oracle.c).  tree["nodes"] is the node
-    counter and is advanced; node_hash (uint64 [max_nodes]) is None with the table off.  Returns
-    (leaf_values, terminal flags)."""
+                  value_quantum, zobrist, board_size=15, widen=None):
+    """The expansion step of one round (oracle_search_expand_widen in oracle.c).  tree["nodes"] is the node
+    counter and is advanced; node_hash (uint64 [max_nodes]) is None with the table off; widen as in
+    search_new_trees.  Returns (leaf_values, terminal flags)."""
     paths = np.ascontiguousarray(paths, np.int32)
     n, max_depth, _ = paths.shape
     T = len(move_lists)
@@ -258,27 +280,30 @@ def search_expand(tree, node_hash, paths, path_len, sims_per_tree, move_lists, p
     policy = np.ascontiguousarray(policy, np.float32)
     _u64 = np.ctypeslib.ndpointer(np.uint64, flags="C_CONTIGUOUS")
     L = lib()
-    L.oracle_search_expand.argtypes = [_i32, _f32, _f32, _i32, _u32, _i32, _i32, C.c_void_p, _i32, C.c_int, C.c_int, C.c_int,
-                                       C.c_int, _i32, _i32, C.c_int, C.c_int, C.c_int, _i16, _i32, C.c_int, C.c_int, _f32,
-                                       C.c_int, _f32, C.c_float, C.c_float, _u64, C.c_int, _f32, _i32]
-    L.oracle_search_expand(tree["N"], tree["W"], tree["P"], tree["VL"], tree["legal_bits"], tree["node_visits"],
+    L.oracle_search_expand_widen.argtypes = [_i32, _f32, _f32, _i32, _u32, _i32, _i32, C.c_void_p, _i32, C.c_int, C.c_int, C.c_int,
+                                             C.c_int, _i32, _i32, C.c_int, C.c_int, C.c_int, _i16, _i32, C.c_int, C.c_int, _f32,
+                                             C.c_int, _f32, C.c_float, C.c_float, _u64, C.c_int, _f32, _i32, C.c_void_p, C.c_int,
+                                             C.c_int, C.c_uint64]
+    wd = widen if widen is not None else (0, 0, 0)
+    L.oracle_search_expand_widen(tree["N"], tree["W"], tree["P"], tree["VL"], tree["legal_bits"], tree["node_visits"],
                            tree["child_node"], _opt(node_hash), used, tree["N"].shape[0], tree["n_children"],
                            tree["N"].shape[1], tree["legal_bits"].shape[1], paths, np.ascontiguousarray(path_len, np.int32),
                            n, max_depth, sims_per_tree, moves, nm, stride, board_size, policy, policy.shape[1],
                            np.ascontiguousarray(value, np.float32), float(value_sign), float(value_quantum),
-                           np.ascontiguousarray(zobrist, np.uint64), T, leaf, term)
+                           np.ascontiguousarray(zobrist, np.uint64), T, leaf, term,
+                           _opt(tree["empty_bits"]) if widen is not None else None, wd[0], wd[1], wd[2])
     tree["nodes"] = int(used[0])
     return leaf, term
 
 
 def search_move(move_lists, root_policy, noise, eps, round_policy, round_value, sims_per_tree, max_nodes, c_puct=1.5,
-                vl_value=3, max_depth=64, value_sign=1.0, value_quantum=0.0, tt_seed=None):
+                vl_value=3, max_depth=64, value_sign=1.0, value_quantum=0.0, tt_seed=None, widen=None):
     """One move of the leaf-parallel search for a group of games, given what the network returned:
     root_policy [T, 225]; round_policy [R, T * sims_per_tree, 225], round_value [R, T * sims_per_tree].
     noise [T, pitch] (or None) is mixed into the root priors with weight eps.  tt_seed: seed of the Zobrist
     keys, None = table off.  Returns the tree dict (tree["nodes"] nodes used) and per-round terminal counts."""
     T = len(move_lists)
-    tree = search_new_trees(move_lists, max_nodes)
+    tree = search_new_trees(move_lists, max_nodes, widen=widen)
     roots = np.arange(T, dtype=np.int32)
     set_priors(tree, roots, root_policy)
     if noise is not None and eps > 0:
@@ -293,7 +318,7 @@ def search_move(move_lists, root_policy, noise, eps, round_policy, round_value, 
     for r in range(len(round_policy)):
         paths, plen = traverse(tree, roots, sims_per_tree, c_puct, vl_value, max_depth)
         leaf, term = search_expand(tree, node_hash, paths, plen, sims_per_tree, move_lists, round_policy[r], round_value[r],
-                                   value_sign, value_quantum, zob)
+                                   value_sign, value_quantum, zob, widen=widen)
         terminals += int((term > 0).sum())
         backup(tree, paths, plen, leaf, vl_value)
     tree["terminal_leaves"] = terminals
@@ -405,6 +430,18 @@ def ref_gomoku_planes(moves, board_size=15):
     if tm < 0:
         raise ValueError("illegal move in list")
     return p19, p3, tm
+
+
+def ref_expand_gomoku(moves, use_progressive_widening, cpw, kpw, board_size=15):
+    """Actions of the children MCTSNode::expand creates at the position after `moves`."""
+    mv = np.ascontiguousarray(moves, np.int16)
+    out = np.zeros(board_size * board_size, np.int32)
+    L = ref_tree()
+    L.ref_expand_gomoku.argtypes = [_i16, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, _i32, C.c_int]
+    L.ref_expand_gomoku.restype = C.c_int
+    n = L.ref_expand_gomoku(mv, len(mv), board_size, int(use_progressive_widening), cpw, kpw, out, len(out))
+    assert n >= 0
+    return out[:n].copy()
 
 
 def ref_gomoku_result(moves, board_size=15):

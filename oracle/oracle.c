@@ -466,7 +466,49 @@ void oracle_gomoku_planes3_batch(const signed char* stones, const unsigned char*
  * terminal_out[i]: 0 not terminal, 1 the side to move has lost, 2 draw. */
 static float quantized(float v, float q) { return q > 0.0f ? rintf(v * q) / q : v; }
 
-void oracle_search_expand(int32_t* N, float* W, float* P, int32_t* VL, uint32_t* legal,
+/* The children a new node gets out of its legal moves (MCTSNode::expand,
+ * src/mcts/mcts_node.cpp:283-340): at most max_children, the first in move order (:287-291, 1,000 in the
+ * reference), and with progressive widening `target` of those chosen at random (:297-340 with the shuffle at
+ * :356).  The reference seeds its shuffle from the operating system, so its subset cannot be reproduced; the
+ * choice restated here is the library's: a move's rank is a 64-bit mix of (seed, node id, move) and the `target`
+ * lowest ranks stay.  max_children <= 0: no cap; target <= 0: no widening. */
+static uint64_t widen_key(uint64_t seed, int id, int s) {
+    uint64_t z = seed ^ ((uint64_t)(id + 1) * 0x9E3779B97F4A7C15ull) ^ ((uint64_t)(s + 1) * 0xC2B2AE3D27D4EB4Full);
+    z ^= z >> 30; z *= 0xBF58476D1CE4E5B9ull; z ^= z >> 27; z *= 0x94D049BB133111EBull; z ^= z >> 31;
+    return z;
+}
+void oracle_widen_mask(const uint32_t* empty, uint32_t* exists, int n_children, int mask_words,
+                       int max_children, int target, uint64_t seed, int id) {
+    int total = 0;
+    for (int w = 0; w < mask_words; ++w) exists[w] = 0;
+    for (int s = 0; s < n_children; ++s)
+        if (((empty[s >> 5] >> (s & 31)) & 1u) && (max_children <= 0 || total < max_children)) {
+            exists[s >> 5] |= 1u << (s & 31);
+            ++total;
+        }
+    if (target <= 0 || total <= target) return;
+    uint32_t capped[64];                       /* the moves that survived the cap: ranks are taken among them */
+    for (int w = 0; w < mask_words && w < 64; ++w) capped[w] = exists[w];
+    for (int s = 0; s < n_children; ++s) {
+        if (!((capped[s >> 5] >> (s & 31)) & 1u)) continue;
+        const uint64_t k = widen_key(seed, id, s);
+        int rank = 0;
+        for (int s2 = 0; s2 < n_children; ++s2) {
+            if (s2 == s || !((capped[s2 >> 5] >> (s2 & 31)) & 1u)) continue;
+            const uint64_t k2 = widen_key(seed, id, s2);
+            if (k2 < k || (k2 == k && s2 < s)) ++rank;
+        }
+        if (rank >= target) exists[s >> 5] &= ~(1u << (s & 31));
+    }
+}
+/* The count progressive widening asks for at a node with `visits` visits (:305-308):
+ * max(8, c * (visits + 1)^k), computed in double and compared as float as the reference's expression does. */
+int oracle_widen_target(float cpw, float kpw, int visits) {
+    const float want = (float)((double)cpw * pow((double)(visits + 1), (double)kpw));
+    return (int)(want > 8.0f ? want : 8.0f);
+}
+
+void oracle_search_expand_widen(int32_t* N, float* W, float* P, int32_t* VL, uint32_t* legal,
                           int32_t* node_visits, int32_t* child_node, uint64_t* node_hash,
                           int32_t* n_used, int max_nodes, int n_children, int pitch, int mask_words,
                           const int32_t* paths, const int32_t* path_len, int n_sims, int max_depth,
@@ -474,7 +516,8 @@ void oracle_search_expand(int32_t* N, float* W, float* P, int32_t* VL, uint32_t*
                           int moves_stride, int S, const float* policy, int policy_size,
                           const float* value, float value_sign, float value_quantum,
                           const uint64_t* zobrist, int n_trees, float* leaf_value_out,
-                          int32_t* terminal_out) {
+                          int32_t* terminal_out, uint32_t* empty, int max_children, int widen_target,
+                          uint64_t widen_seed) {
     int16_t game[32 * 32];
     for (int i = 0; i < n_sims; ++i) {
         const int tree = i / sims_per_tree;
@@ -510,9 +553,12 @@ void oracle_search_expand(int32_t* N, float* W, float* P, int32_t* VL, uint32_t*
         if (*n_used >= max_nodes) continue;                       /* pool exhausted: the edge stays a leaf */
         const int id = (*n_used)++;
         const size_t row = (size_t)id * pitch;
-        const uint32_t* pm = legal + (size_t)parent * mask_words;
+        /* empty != NULL: the positions' empty cells are kept apart from the children a node was given */
+        const uint32_t* pm = (empty ? empty : legal) + (size_t)parent * mask_words;
+        uint32_t* own = (empty ? empty : legal) + (size_t)id * mask_words;
         uint32_t* cm = legal + (size_t)id * mask_words;
-        for (int w = 0; w < mask_words; ++w) cm[w] = pm[w] & ~((w == (slot >> 5)) ? (1u << (slot & 31)) : 0u);
+        for (int w = 0; w < mask_words; ++w) own[w] = pm[w] & ~((w == (slot >> 5)) ? (1u << (slot & 31)) : 0u);
+        if (empty) oracle_widen_mask(own, cm, n_children, mask_words, max_children, widen_target, widen_seed, id);
         for (int s = 0; s < pitch; ++s) {
             float pr = 0.0f;
             if (s < n_children && ((cm[s >> 5] >> (s & 31)) & 1u) && s < policy_size)
@@ -523,6 +569,21 @@ void oracle_search_expand(int32_t* N, float* W, float* P, int32_t* VL, uint32_t*
         if (node_hash) node_hash[id] = h;
         child_node[e] = id;
     }
+}
+
+void oracle_search_expand(int32_t* N, float* W, float* P, int32_t* VL, uint32_t* legal,
+                          int32_t* node_visits, int32_t* child_node, uint64_t* node_hash,
+                          int32_t* n_used, int max_nodes, int n_children, int pitch, int mask_words,
+                          const int32_t* paths, const int32_t* path_len, int n_sims, int max_depth,
+                          int sims_per_tree, const int16_t* root_moves, const int32_t* root_n_moves,
+                          int moves_stride, int S, const float* policy, int policy_size,
+                          const float* value, float value_sign, float value_quantum,
+                          const uint64_t* zobrist, int n_trees, float* leaf_value_out,
+                          int32_t* terminal_out) {
+    oracle_search_expand_widen(N, W, P, VL, legal, node_visits, child_node, node_hash, n_used, max_nodes, n_children,
+                               pitch, mask_words, paths, path_len, n_sims, max_depth, sims_per_tree, root_moves,
+                               root_n_moves, moves_stride, S, policy, policy_size, value, value_sign, value_quantum,
+                               zobrist, n_trees, leaf_value_out, terminal_out, NULL, 0, 0, 0);
 }
 
 /* MCTSEngine::addDirichletNoise, src/mcts/mcts_engine_eval.cpp:83-110.  The noise

@@ -9,6 +9,7 @@
 //   alphazero::mcts::MCTSNode::selectChild        src/mcts/mcts_node.cpp:90
 //   MCTSNode::addVirtualLoss/removeVirtualLoss    src/mcts/mcts_node_virtual_loss.cpp:15,32
 //   MCTSNode::update                              src/mcts/mcts_node_virtual_loss.cpp:54
+//   MCTSNode::expand                              src/mcts/mcts_node.cpp:238
 //   GomokuState::getEnhancedTensorRepresentation  src/games/gomoku/gomoku_state.cpp:210
 //   GomokuState::getTensorRepresentation          src/games/gomoku/gomoku_state.cpp:184
 #include <cstdint>
@@ -272,6 +273,20 @@ int ref_chess_random_encode(uint64_t seed, int n_plies, int8_t* pieces, int32_t*
         for (int r = 0; r < 8; ++r)
             std::memcpy(planes20 + (c * 8 + r) * 8, t[c][r].data(), sizeof(float) * 8);
     return played;
+}
+
+// MCTSNode::expand (src/mcts/mcts_node.cpp:238-436) on a Gomoku position reached by `moves`: the actions of the
+// children it creates, in the node's own (shuffled) order.  Returns their number, or -1 when more than `cap`.
+int ref_expand_gomoku(const int16_t* moves, int n_moves, int board_size, int use_progressive_widening, float cpw,
+                      float kpw, int32_t* actions_out, int cap) {
+    auto st = std::make_unique<alphazero::games::gomoku::GomokuState>(board_size, false, false, 0, false);
+    for (int i = 0; i < n_moves; ++i) st->makeMove(moves[i]);
+    auto node = MCTSNode::create(std::move(st), nullptr);
+    node->expand(use_progressive_widening != 0, cpw, kpw);
+    const std::vector<int>& acts = node->getActions();
+    if ((int)acts.size() > cap) return -1;
+    for (size_t i = 0; i < acts.size(); ++i) actions_out[i] = acts[i];
+    return (int)acts.size();
 }
 
 }  // extern "C"

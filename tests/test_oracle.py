@@ -329,3 +329,65 @@ def test_search_round_restatement_invariants(oracle):
         out[tt] = (n, len(parents))
     assert out[None][1] == out[None][0] - T            # a tree: one edge per node
     assert out[3][0] < out[None][0] and out[3][1] > out[3][0] - T   # shared nodes: fewer nodes, more edges than nodes
+
+
+def test_widening_count_and_choice_against_the_reference_expand(oracle):
+    """MCTSNode::expand's limits on a node's children (src/mcts/mcts_node.cpp:283-340).  The count progressive
+    widening asks for is pinned to the compiled reference (its random subset itself cannot be: it is seeded from
+    the operating system); the restated choice keeps that many of the legal moves, is a function of (seed, node,
+    move) only, and takes every move about equally often."""
+    assert oracle.widen_target(2.0, 0.5) == 8 and oracle.widen_target(20.5, 0.5) == 20
+    assert oracle.widen_target(0.5, 5.0) == 8 and oracle.widen_target(1.0, 10.0, visits=3) == 4 ** 10
+    moves = [112, 113, 98]
+    empty = np.ones(225, bool)
+    empty[moves] = False
+    words = np.packbits(np.concatenate([empty, np.zeros(31, bool)]), bitorder="little").view(np.uint32)
+    legal_of = lambda w: np.unpackbits(w.view(np.uint8), bitorder="little")[:225].astype(bool)
+    if oracle.have_ref_tree():
+        for use, c, k in [(True, 2.0, 0.5), (True, 20.5, 0.5), (True, 0.5, 5.0), (True, 300.0, 1.0), (False, 2.0, 0.5)]:
+            acts = oracle.ref_expand_gomoku(moves, use, c, k)
+            want = min(222, oracle.widen_target(c, k)) if use else 222
+            assert len(acts) == want == len(set(acts.tolist())) and empty[acts].all(), (use, c, k, len(acts))
+            got = legal_of(oracle.widen_mask(words, 225, 1000, oracle.widen_target(c, k) if use else 0, 99, 5))
+            assert got.sum() == want and not (got & ~empty).any()
+    # the cap: the first moves in move order; then the subset is taken among them
+    capped = legal_of(oracle.widen_mask(words, 225, 40, 0, 1, 0))
+    assert capped.sum() == 40 and np.array_equal(np.nonzero(capped)[0], np.nonzero(empty)[0][:40])
+    both = legal_of(oracle.widen_mask(words, 225, 40, 8, 1, 0))
+    assert both.sum() == 8 and not (both & ~capped).any()
+    # deterministic in (seed, node); different nodes and seeds choose differently; no move is favoured
+    a = legal_of(oracle.widen_mask(words, 225, 0, 8, 7, 3))
+    assert np.array_equal(a, legal_of(oracle.widen_mask(words, 225, 0, 8, 7, 3)))
+    assert not np.array_equal(a, legal_of(oracle.widen_mask(words, 225, 0, 8, 7, 4)))
+    assert not np.array_equal(a, legal_of(oracle.widen_mask(words, 225, 0, 8, 8, 3)))
+    counts = np.zeros(225)
+    for node in range(3000):
+        counts += legal_of(oracle.widen_mask(words, 225, 0, 8, 11, node))
+    assert counts[~empty].sum() == 0
+    expect = 3000 * 8 / 222
+    assert np.abs(counts[empty] - expect).max() < 5 * np.sqrt(expect)
+
+
+def test_search_restatement_with_widening(oracle):
+    """oracle.search_move with progressive widening: every node has at most `target` children, all of them legal
+    moves of its position, and a child's position is its parent's plus the move (so a widened parent's other legal
+    moves are legal again below it)."""
+    rng = np.random.default_rng(6)
+    T, spt, R = 2, 8, 30
+    games = [[112, 113], [0, 224, 16]]
+    pol = rng.dirichlet(np.ones(225) * 0.3, size=(R + 1, T * spt)).astype(np.float32)
+    val = (np.round(rng.uniform(-1, 1, (R + 1, T * spt)) * 256) / 256).astype(np.float32)
+    tree = oracle.search_move(games, pol[0, :T], None, 0.0, pol[1:], val[1:], spt, T * (1 + R * spt), tt_seed=3,
+                              widen=(1000, 8, 12345))
+    n = tree["nodes"]
+    legal_of = lambda w: np.unpackbits(w.view(np.uint8), bitorder="little")[:225].astype(bool)
+    assert n > T
+    for node in range(n):
+        kids, empty = legal_of(tree["legal_bits"][node]), legal_of(tree["empty_bits"][node])
+        assert kids.sum() == min(8, empty.sum()) and not (kids & ~empty).any()
+        assert not tree["P"][node, :225][~kids].any()
+    child = tree["child_node"][:n, :225]
+    for p, a in zip(*np.nonzero(child >= 0)):
+        ep, ec = legal_of(tree["empty_bits"][p]), legal_of(tree["empty_bits"][child[p, a]])
+        assert legal_of(tree["legal_bits"][p])[a] and ep[a] and not ec[a] and np.array_equal(np.delete(ep, a), np.delete(ec, a))
+    assert (tree["N"][:T, :225].sum(1) == spt * R).all() and not tree["VL"].any()

@@ -80,11 +80,17 @@ SEARCH_CASES = [
     ("long_table", None, 4, 16, 48, True, 0.0, 1),            # 768 simulations per tree: transpositions do occur
     ("open_four_negamax", "four", 4, 16, 12, True, 0.25, -1),  # finished games among the leaves, duplicates in a batch
     ("one_tree", None, 1, 32, 6, True, 0.25, 1),
+    # MCTSNode::expand's limits: progressive widening (c, k) -> max(8, c) children per node; the cap on children
+    ("widened", None, 8, 8, 12, True, 0.25, 1, {"pw": (2.0, 0.5)}),
+    ("widened_20", None, 4, 16, 12, False, 0.25, 1, {"pw": (20.5, 0.5)}),
+    ("capped_40", None, 4, 16, 12, True, 0.25, 1, {"max_children": 40}),
+    ("capped_and_widened", "four", 4, 16, 12, True, 0.0, -1, {"max_children": 60, "pw": (12.0, 1.0)}),
 ]
+SEARCH_CASES = [c if len(c) == 9 else c + ({},) for c in SEARCH_CASES]
 
 
-@pytest.mark.parametrize("name,games,T,spt,R,table,eps,sign", SEARCH_CASES, ids=[c[0] for c in SEARCH_CASES])
-def test_search_equals_the_oracle_on_the_same_network_outputs(net, oracle, name, games, T, spt, R, table, eps, sign):
+@pytest.mark.parametrize("name,games,T,spt,R,table,eps,sign,limits", SEARCH_CASES, ids=[c[0] for c in SEARCH_CASES])
+def test_search_equals_the_oracle_on_the_same_network_outputs(net, oracle, name, games, T, spt, R, table, eps, sign, limits):
     """The device search and the CPU restatement, given the same root policies, root noise and per-round
     policy / value arrays: node count, existence masks, child links, visit counts, virtual loss, priors and
     value sums must all be identical.  (Network values are rounded to multiples of 1/256 on both sides so
@@ -95,9 +101,12 @@ def test_search_equals_the_oracle_on_the_same_network_outputs(net, oracle, name,
     else:
         games, _, _, _ = synth.make_gomoku_games(T, 15, seed=40 + T, max_moves=20)
     s = capi.Search(net, n_trees=T, sims_per_move=spt * R, leaf_batch=T * spt, max_depth=32, c_puct=1.5, virtual_loss=3,
-                    dirichlet_alpha=0.3, dirichlet_epsilon=eps, value_sign=sign, transposition_table=table, seed=7)
+                    dirichlet_alpha=0.3, dirichlet_epsilon=eps, value_sign=sign, transposition_table=table, seed=7,
+                    max_children=limits.get("max_children", 0), progressive_widening=limits.get("pw"))
     s.debug_hooks(value_quantum=256.0, record_rounds=R)
+    target = oracle.widen_target(*limits["pw"]) if "pw" in limits else 0
     for move in range(2):                                          # a second move on the same handle starts clean
+        widen = (limits.get("max_children", 1000), target, capi.widening_seed(7, move)) if limits else None
         pi, visits, st = s.run(games, temperature=1.0)
         assert capi.device_error_code() == 0
         pol, val, noise = s.record()
@@ -105,9 +114,16 @@ def test_search_equals_the_oracle_on_the_same_network_outputs(net, oracle, name,
         max_nodes = T * (1 + R * spt)
         ref = oracle.search_move(games, pol[0, :T], noise if eps > 0 else None, eps, pol[1:], val[1:], spt, max_nodes,
                                  c_puct=1.5, vl_value=3, max_depth=32, value_sign=float(sign), value_quantum=256.0,
-                                 tt_seed=7 if table else None)
+                                 tt_seed=7 if table else None, widen=widen)
         n = ref["nodes"]
         assert dev["nodes"] == n == st["nodes"], (dev["nodes"], n)
+        if limits:
+            kids = np.array([legal_of(dev["legal_bits"][k]).sum() for k in range(n)])
+            most = min(limits.get("max_children", 1000), target or 1000)
+            assert kids.max() == most and (kids[:T] == most).all()
+            if eps > 0:                                           # the root noise is a distribution over the root's children
+                for t in range(T):
+                    assert not noise[t, :225][~legal_of(dev["legal_bits"][t])].any() and abs(noise[t].sum() - 1) < 1e-5
         assert st["terminal_leaves"] == ref["terminal_leaves"]
         for key in ("legal_bits", "child_node", "N", "VL", "node_visits"):
             assert np.array_equal(dev[key][:n], ref[key][:n]), key
