@@ -277,6 +277,22 @@ int ob200_launch_encode_gomoku3(const int8_t* stones, const uint8_t* to_move, in
                                 int32_t board_size, int32_t out_channels, void* board_tensor_out,
                                 ob200_stream stream);
 
+/* The Gomoku attack / defense planes as an operator of its own.  Replaces
+ * GomokuAttackDefenseModule::compute_planes / compute_bonuses
+ * (src/utils/attack_defense_module.cpp:50-111, threat counts :205-222, :333-487).
+ * stones [B][S*S] (0 empty, 1 black, 2 white), to_move [B]; attack_out,
+ * defense_out [B][S*S] fp32, zero on occupied cells.  For an empty cell m:
+ * attack = threats(after, mover) - threats(before, mover), defense =
+ * threats(before, opponent) - threats(after, opponent), `before` with m empty.
+ * stone_placed == 0 is compute_planes' call pattern: `after` is the position
+ * itself, so both planes are zero everywhere (what the encoders write into
+ * planes 17 / 18).  stone_placed != 0: `after` has the mover's stone on m, as
+ * compute_bonuses is called with a board that already holds the chosen move.
+ * Device pointers; board_size in [6, 32]. */
+int ob200_launch_gomoku_attack_defense(const int8_t* stones, const uint8_t* to_move, int32_t B,
+                                       int32_t board_size, int32_t stone_placed, float* attack_out,
+                                       float* defense_out, ob200_stream stream);
+
 /* Chess state -> the reference's 20 input planes, written as a bf16 board
  * tensor (board_size 8) of `out_channels` (a multiple of 8, >= 24) channels.
  * Replaces ChessState::getEnhancedTensorRepresentation

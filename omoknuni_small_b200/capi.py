@@ -104,6 +104,7 @@ SIGNATURES = {
                                                 C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "ob200_launch_encode_go": (C.c_int, [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p, C.c_void_p]),
     "ob200_launch_encode_gomoku3": (C.c_int, [C.c_void_p, C.c_void_p] + [C.c_int32] * 3 + [C.c_void_p, C.c_void_p]),
+    "ob200_launch_gomoku_attack_defense": (C.c_int, [C.c_void_p, C.c_void_p] + [C.c_int32] * 3 + [C.c_void_p] * 3),
     "ob200_launch_encode_chess": (C.c_int, [C.c_void_p] * 3 + [C.c_int32] * 2 + [C.c_void_p, C.c_void_p]),
     "ob200_launch_planes_to_board_tensor": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                                       C.c_void_p]),
@@ -324,6 +325,17 @@ def encode_gomoku3(stones, to_move, board_size, out_channels=64):
     out = torch.empty(nbytes // 2, dtype=torch.int16, device=stones.device)
     check(lib().ob200_launch_encode_gomoku3(_ptr(stones), _ptr(to_move), B, board_size, out_channels, _ptr(out), _stream()))
     return out
+
+
+def gomoku_attack_defense(stones, to_move, board_size, stone_placed=False):
+    """Device tensors in (int8 [B,S*S], uint8 [B]) -> (attack, defense) fp32 [B,S*S] each."""
+    import torch
+    B = stones.shape[0]
+    att = torch.empty((B, board_size * board_size), dtype=torch.float32, device=stones.device)
+    dfn = torch.empty_like(att)
+    check(lib().ob200_launch_gomoku_attack_defense(_ptr(stones), _ptr(to_move), B, board_size, int(stone_placed), _ptr(att),
+                                                   _ptr(dfn), _stream()))
+    return att, dfn
 
 
 def encode_chess(pieces, meta, legal_to, out_channels=64):

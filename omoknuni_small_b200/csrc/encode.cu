@@ -519,6 +519,82 @@ int launch_planes_to_board_tensor(const float* planes_nchw, int32_t B, int32_t C
     return OB200_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Gomoku attack / defense planes (GomokuAttackDefenseModule, src/utils/attack_defense_module.cpp).
+// A colour's threat count (:205-222) is the number of windows, over the four line directions, of 5 cells with
+// both end cells empty and 3 or 2 of its stones among the 3 between them, plus windows of 6 with 4 or 3 among
+// the 4 between (:333-392 rows and columns, :394-487 diagonals; whatever else lies between does not matter).
+// For an empty cell m and the side to move p (:61-111, :113-203):
+//   attack[m]  = threats(after, p) - threats(before, p),  defense[m] = threats(before, o) - threats(after, o),
+// `before` being the board with m empty and `after` the board the module is handed.  compute_planes hands it the
+// position itself (m still empty), so both planes come out zero for every cell: stone_placed == 0.  With
+// stone_placed != 0 `after` carries p's stone on m, the way the module's own tests call compute_bonuses.
+// Only the windows through m differ between the two boards, so a thread visits those: 4 directions x (5 + 6).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+gomoku_attack_defense_kernel(const int8_t* __restrict__ stones, const uint8_t* __restrict__ to_move, int B, int S,
+                             int stone_placed, float* __restrict__ attack, float* __restrict__ defense) {
+    extern __shared__ int8_t board[];
+    const int b = blockIdx.x;
+    if (b >= B) return;
+    const int cells = S * S;
+    for (int i = threadIdx.x; i < cells; i += blockDim.x) board[i] = stones[(size_t)b * cells + i];
+    __syncthreads();
+    const int p = to_move[b], o = p == 1 ? 2 : 1;
+    for (int m = threadIdx.x; m < cells; m += blockDim.x) {
+        float att = 0.0f, def = 0.0f;
+        if (board[m] == 0) {
+            const int r = m / S, c = m - r * S;
+            const int after_m = stone_placed ? p : 0;
+            int att_after = 0, att_before = 0, def_after = 0, def_before = 0;
+            const int dr[4] = {0, 1, 1, 1}, dc[4] = {1, 0, 1, -1};
+#pragma unroll
+            for (int d = 0; d < 4; ++d) {
+#pragma unroll
+                for (int len = 5; len <= 6; ++len) {
+                    const int need = len - 2;                     // stones asked for between the end cells
+                    for (int k = 0; k < len; ++k) {               // m is the k-th cell of the window
+                        const int r0 = r - k * dr[d], c0 = c - k * dc[d];
+                        const int r1 = r0 + (len - 1) * dr[d], c1 = c0 + (len - 1) * dc[d];
+                        if (r0 < 0 || r1 >= S || c0 < 0 || c0 >= S || c1 < 0 || c1 >= S) continue;
+                        int mine = 0, theirs = 0;
+                        bool ends_empty = true;
+                        for (int j = 0; j < len; ++j) {
+                            if (j == k) continue;
+                            const int v = board[(r0 + j * dr[d]) * S + c0 + j * dc[d]];
+                            if (j == 0 || j == len - 1) ends_empty = ends_empty && v == 0;
+                            else { mine += v == p; theirs += v == o; }
+                        }
+                        if (!ends_empty) continue;
+                        const bool m_is_end = k == 0 || k == len - 1;
+                        // before: m empty.  after: m holds after_m.
+                        const bool open_before = true, open_after = !m_is_end || after_m == 0;
+                        const int mine_after = mine + ((!m_is_end && after_m == p) ? 1 : 0);
+                        att_before += open_before && (mine == need || mine == need - 1);
+                        att_after += open_after && (mine_after == need || mine_after == need - 1);
+                        def_before += open_before && (theirs == need || theirs == need - 1);
+                        def_after += open_after && (theirs == need || theirs == need - 1);
+                    }
+                }
+            }
+            att = (float)(att_after - att_before);
+            def = (float)(def_before - def_after);
+        }
+        attack[(size_t)b * cells + m] = att;
+        defense[(size_t)b * cells + m] = def;
+    }
+}
+
+int launch_gomoku_attack_defense(const int8_t* stones, const uint8_t* to_move, int B, int S, int stone_placed,
+                                 float* attack, float* defense, cudaStream_t st) {
+    if (!stones || !to_move || !attack || !defense) return set_error(OB200_ERR_INVALID, "attack/defense planes: null pointer");
+    if (B < 0 || S < 6 || S > 32) return set_error(OB200_ERR_INVALID, "attack/defense planes: need B >= 0 and board_size in [6, 32]");
+    if (B == 0) return OB200_OK;
+    gomoku_attack_defense_kernel<<<B, 256, S * S, st>>>(stones, to_move, B, S, stone_placed, attack, defense);
+    OB200_LAUNCHED("gomoku_attack_defense_kernel");
+    return OB200_OK;
+}
+
 }  // namespace ob200
 
 using namespace ob200;
@@ -549,6 +625,11 @@ int ob200_launch_encode_go(const int8_t* stones, const int32_t* ko_point, const 
 int ob200_launch_encode_gomoku3(const int8_t* stones, const uint8_t* to_move, int32_t B, int32_t board_size,
                                 int32_t out_channels, void* board_tensor_out, ob200_stream stream) {
     return launch_encode_gomoku3(stones, to_move, B, board_size, out_channels, board_tensor_out, as_stream(stream));
+}
+
+int ob200_launch_gomoku_attack_defense(const int8_t* stones, const uint8_t* to_move, int32_t B, int32_t board_size,
+                                       int32_t stone_placed, float* attack_out, float* defense_out, ob200_stream stream) {
+    return launch_gomoku_attack_defense(stones, to_move, B, board_size, stone_placed, attack_out, defense_out, as_stream(stream));
 }
 
 int ob200_launch_encode_chess(const int8_t* pieces, const int32_t* meta, const uint32_t* legal_to, int32_t B,

@@ -230,3 +230,32 @@ def net_flops_per_eval(board_size, input_channels, filters, blocks, policy_size,
     f += 2 * S2 * filters * policy_head_ch + 2 * policy_head_ch * S2 * policy_size
     f += 2 * S2 * filters * value_head_ch + 2 * value_head_ch * S2 * value_hidden + 2 * value_hidden
     return f
+
+
+def make_threat_positions(n, board_size=15, seed=3):
+    """Gomoku boards (int8 [n, S*S]: 0 empty, 1 black, 2 white) and sides to move (uint8 [n]) with lines planted in
+    them: a few scattered stones, then two to five runs of 2-4 stones of one colour along a random direction,
+    some with a gap, so that open and broken threes and fours of both colours occur.  Not reachable by legal play
+    in general (stone counts are arbitrary), which the window arithmetic does not care about."""
+    rng = np.random.default_rng(seed)
+    S = board_size
+    boards = np.zeros((n, S * S), np.int8)
+    for b in range(n):
+        k = int(rng.integers(0, 12))
+        boards[b, rng.choice(S * S, k, replace=False)] = rng.integers(1, 3, k)
+        for _ in range(int(rng.integers(2, 6))):
+            colour = int(rng.integers(1, 3))
+            dr, dc = [(0, 1), (1, 0), (1, 1), (1, -1)][int(rng.integers(0, 4))]
+            length = int(rng.integers(2, 5))
+            gap = int(rng.integers(0, length + 1)) if rng.random() < 0.4 else -1
+            span = length + (gap >= 0)
+            r0 = int(rng.integers(0, S - (span - 1) * dr))
+            c0 = int(rng.integers((span - 1) if dc < 0 else 0, S - (span - 1) * max(dc, 0)))
+            j = 0
+            for i in range(span):
+                if i == gap:
+                    continue
+                boards[b, (r0 + i * dr) * S + c0 + i * dc] = colour
+                j += 1
+    to_move = rng.integers(1, 3, n).astype(np.uint8)
+    return boards, to_move

@@ -325,6 +325,28 @@ def search_move(move_lists, root_policy, noise, eps, round_policy, round_value, 
     return tree
 
 
+def gomoku_threats(board, color, board_size=15):
+    """Open-three / open-four window count of a colour (oracle_gomoku_threats in oracle.c)."""
+    bd = np.ascontiguousarray(board, np.int8).reshape(-1)
+    L = lib()
+    L.oracle_gomoku_threats.argtypes = [np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS"), C.c_int, C.c_int]
+    return int(L.oracle_gomoku_threats(bd, board_size, color))
+
+
+def gomoku_attack_defense(stones, to_move, board_size=15, stone_placed=False):
+    """(attack, defense) fp32 [B, S*S] for boards int8 [B, S*S] (oracle_gomoku_attack_defense in oracle.c)."""
+    st = np.ascontiguousarray(stones, np.int8)
+    tm = np.ascontiguousarray(to_move, np.uint8)
+    att = np.zeros(st.shape, np.float32)
+    dfn = np.zeros(st.shape, np.float32)
+    L = lib()
+    i8 = np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS")
+    u8 = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
+    L.oracle_gomoku_attack_defense.argtypes = [i8, u8, C.c_int, C.c_int, C.c_int, _f32, _f32]
+    L.oracle_gomoku_attack_defense(st, tm, st.shape[0], board_size, int(stone_placed), att, dfn)
+    return att, dfn
+
+
 def gomoku_result(moves, board_size=15):
     """0 ongoing, 1 BLACK won, 2 WHITE won, 3 draw, judged on the last move (freestyle rules)."""
     mv = np.ascontiguousarray(moves, np.int16)
@@ -442,6 +464,31 @@ def ref_expand_gomoku(moves, use_progressive_widening, cpw, kpw, board_size=15):
     n = L.ref_expand_gomoku(mv, len(mv), board_size, int(use_progressive_widening), cpw, kpw, out, len(out))
     assert n >= 0
     return out[:n].copy()
+
+
+def ref_attack_defense_planes(moves, board_size=15):
+    """GomokuAttackDefenseModule::compute_planes on the GomokuState reached by `moves`: (attack, defense) [S*S]."""
+    mv = np.ascontiguousarray(moves, np.int16)
+    att = np.zeros(board_size * board_size, np.float32)
+    dfn = np.zeros_like(att)
+    L = ref_tree()
+    L.ref_attack_defense_planes.argtypes = [_i16, C.c_int, C.c_int, _f32, _f32]
+    L.ref_attack_defense_planes.restype = C.c_int
+    assert L.ref_attack_defense_planes(mv, len(mv), board_size, att, dfn) == 0
+    return att, dfn
+
+
+def ref_attack_defense_bonuses(board, player, board_size=15):
+    """GomokuAttackDefenseModule::compute_bonuses for every empty cell of `board` (int8 [S*S]) with the player's
+    stone placed on it first: (attack, defense) [S*S]."""
+    bd = np.ascontiguousarray(board, np.int8).reshape(-1)
+    att = np.zeros(board_size * board_size, np.float32)
+    dfn = np.zeros_like(att)
+    L = ref_tree()
+    L.ref_attack_defense_bonuses.argtypes = [np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS"), C.c_int, C.c_int, _f32, _f32]
+    L.ref_attack_defense_bonuses.restype = C.c_int
+    assert L.ref_attack_defense_bonuses(bd, board_size, player, att, dfn) == 0
+    return att, dfn
 
 
 def ref_gomoku_result(moves, board_size=15):

@@ -608,3 +608,51 @@ void oracle_mix_noise(float* P, const uint32_t* legal, int n_children, int pitch
             }
     }
 }
+
+/* GomokuAttackDefenseModule, src/utils/attack_defense_module.cpp.
+ * count_threats_for_color (:205-222): windows of 5 asking for 3 stones and windows of 6 asking for 4, along rows
+ * and columns (:333-392, count_1d_patterns on the mask and on its transpose) and along both diagonals (:394-487).
+ * A window counts when both end cells are empty and the cells between them hold exactly `need` or `need - 1`
+ * stones of the colour ("perfect" and "broken" are added up, :375-390). */
+static int threat_windows(const int8_t* board, int S, int color, int len, int need) {
+    static const int dr[4] = {0, 1, 1, 1}, dc[4] = {1, 0, 1, -1};
+    int count = 0;
+    for (int d = 0; d < 4; ++d)
+        for (int r = 0; r < S; ++r)
+            for (int c = 0; c < S; ++c) {
+                const int r1 = r + (len - 1) * dr[d], c1 = c + (len - 1) * dc[d];
+                if (r1 >= S || c1 < 0 || c1 >= S) continue;
+                int inside = 0;
+                for (int k = 1; k < len - 1; ++k) inside += board[(r + k * dr[d]) * S + c + k * dc[d]] == color;
+                const int ends_empty = board[r * S + c] == 0 && board[r1 * S + c1] == 0;
+                if (ends_empty && (inside == need || inside == need - 1)) ++count;
+            }
+    return count;
+}
+int oracle_gomoku_threats(const int8_t* board, int S, int color) {
+    return threat_windows(board, S, color, 5, 3) + threat_windows(board, S, color, 6, 4);
+}
+/* compute_planes (:61-111) with compute_attack_bonus / compute_defense_bonus (:113-203) for every empty cell m of
+ * every board: `after` is the board handed to the module - the position itself (stone_placed == 0, what
+ * compute_planes does) or the position with the mover's stone on m (stone_placed != 0) - and `before` is `after`
+ * with m cleared when it is empty or the mover's (:123-139).  attack = threats(after, mover) - threats(before,
+ * mover); defense = threats(before, opponent) - threats(after, opponent).  Occupied cells stay zero. */
+void oracle_gomoku_attack_defense(const int8_t* stones, const uint8_t* to_move, int B, int S, int stone_placed,
+                                  float* attack, float* defense) {
+    int8_t after[32 * 32], before[32 * 32];
+    const int cells = S * S;
+    for (int b = 0; b < B; ++b) {
+        const int p = to_move[b], o = p == 1 ? 2 : 1;
+        for (int m = 0; m < cells; ++m) {
+            attack[(size_t)b * cells + m] = 0.0f;
+            defense[(size_t)b * cells + m] = 0.0f;
+            if (stones[(size_t)b * cells + m] != 0) continue;
+            memcpy(after, stones + (size_t)b * cells, (size_t)cells);
+            if (stone_placed) after[m] = (int8_t)p;
+            memcpy(before, after, (size_t)cells);
+            if (before[m] == 0 || before[m] == p) before[m] = 0;
+            attack[(size_t)b * cells + m] = (float)oracle_gomoku_threats(after, S, p) - (float)oracle_gomoku_threats(before, S, p);
+            defense[(size_t)b * cells + m] = (float)oracle_gomoku_threats(before, S, o) - (float)oracle_gomoku_threats(after, S, o);
+        }
+    }
+}

@@ -10,6 +10,8 @@
 //   MCTSNode::addVirtualLoss/removeVirtualLoss    src/mcts/mcts_node_virtual_loss.cpp:15,32
 //   MCTSNode::update                              src/mcts/mcts_node_virtual_loss.cpp:54
 //   MCTSNode::expand                              src/mcts/mcts_node.cpp:238
+//   GomokuAttackDefenseModule::compute_planes     src/utils/attack_defense_module.cpp:61
+//   GomokuAttackDefenseModule::compute_bonuses    src/utils/attack_defense_module.cpp:50
 //   GomokuState::getEnhancedTensorRepresentation  src/games/gomoku/gomoku_state.cpp:210
 //   GomokuState::getTensorRepresentation          src/games/gomoku/gomoku_state.cpp:184
 #include <cstdint>
@@ -27,6 +29,7 @@
 #include "games/go/go_state.h"
 #include "games/chess/chess_state.h"
 #include "games/chess/chess_types.h"
+#include "utils/attack_defense_module.h"
 #include "ref_tiny_state.h"
 
 using alphazero::core::GameResult;
@@ -287,6 +290,43 @@ int ref_expand_gomoku(const int16_t* moves, int n_moves, int board_size, int use
     if ((int)acts.size() > cap) return -1;
     for (size_t i = 0; i < acts.size(); ++i) actions_out[i] = acts[i];
     return (int)acts.size();
+}
+
+// GomokuAttackDefenseModule::compute_planes (src/utils/attack_defense_module.cpp:61-111) on the GomokuState reached
+// by `moves`.
+int ref_attack_defense_planes(const int16_t* moves, int n_moves, int board_size, float* attack, float* defense) {
+    std::vector<std::unique_ptr<alphazero::core::IGameState>> states;
+    auto st = std::make_unique<alphazero::games::gomoku::GomokuState>(board_size, false, false, 0, false);
+    for (int i = 0; i < n_moves; ++i) st->makeMove(moves[i]);
+    states.push_back(std::move(st));
+    alphazero::GomokuAttackDefenseModule module(board_size);
+    auto planes = module.compute_planes(states);
+    for (int r = 0; r < board_size; ++r)
+        for (int c = 0; c < board_size; ++c) {
+            attack[r * board_size + c] = planes.first[0][r][c];
+            defense[r * board_size + c] = planes.second[0][r][c];
+        }
+    return 0;
+}
+
+// compute_bonuses (:50-59, :113-203) for every empty cell of a board, called the way the module's own tests call
+// it: the board handed over already holds the player's stone on the chosen cell.
+int ref_attack_defense_bonuses(const int8_t* board, int board_size, int player, float* attack, float* defense) {
+    alphazero::GomokuAttackDefenseModule module(board_size);
+    std::vector<std::vector<std::vector<int>>> batch(1, std::vector<std::vector<int>>(board_size, std::vector<int>(board_size, 0)));
+    for (int r = 0; r < board_size; ++r)
+        for (int c = 0; c < board_size; ++c) batch[0][r][c] = board[r * board_size + c];
+    for (int m = 0; m < board_size * board_size; ++m) {
+        attack[m] = defense[m] = 0.0f;
+        const int r = m / board_size, c = m % board_size;
+        if (batch[0][r][c] != 0) continue;
+        batch[0][r][c] = player;
+        auto [a, d] = module.compute_bonuses(batch, std::vector<int>{m}, std::vector<int>{player});
+        batch[0][r][c] = 0;
+        attack[m] = a[0];
+        defense[m] = d[0];
+    }
+    return 0;
 }
 
 }  // extern "C"

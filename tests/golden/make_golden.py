@@ -16,6 +16,9 @@ the inputs' checksums and the reference's outputs:
   chess_golden.npz   ChessState (pieces, side to move, castling, en passant, clocks,
                      legal destinations) and its getEnhancedTensorRepresentation
                      planes after seeded random legal play (`make_golden.py chess`)
+  attack_defense_golden.npz  GomokuAttackDefenseModule: compute_planes on played games (all zero) and
+                     compute_bonuses with the stone placed on boards with planted threes and
+                     fours (`make_golden.py attack_defense`)
   net_golden.npz     ResNetModel::forward (log-softmax policy, value): (a) a tiny
                      model with the reference's own libtorch default
                      initialisation, its weights stored here rounded to fp16
@@ -134,6 +137,28 @@ def make_chess():
                         planes=planes)
 
 
+def make_attack_defense():
+    boards, to_move = synth.make_threat_positions(40, 15, seed=77)
+    att = np.zeros(boards.shape, np.float32)
+    dfn = np.zeros(boards.shape, np.float32)
+    for b in range(len(boards)):
+        att[b], dfn[b] = capi.ref_attack_defense_bonuses(boards[b], int(to_move[b]), 15)
+    small, small_tm = synth.make_threat_positions(12, 9, seed=78)
+    att9 = np.zeros(small.shape, np.float32)
+    dfn9 = np.zeros(small.shape, np.float32)
+    for b in range(len(small)):
+        att9[b], dfn9[b] = capi.ref_attack_defense_bonuses(small[b], int(small_tm[b]), 9)
+    games, _, _, _ = synth.make_gomoku_games(24, 15, seed=79, max_moves=60)
+    planes_nonzero = 0
+    for g in games:
+        a, d = capi.ref_attack_defense_planes(g, 15)
+        planes_nonzero += int(np.count_nonzero(a)) + int(np.count_nonzero(d))
+    np.savez_compressed(os.path.join(HERE, "attack_defense_golden.npz"), inputs_sha256=checksum(boards, to_move, small, small_tm),
+                        attack15=att.astype(np.int8), defense15=dfn.astype(np.int8), attack9=att9.astype(np.int8),
+                        defense9=dfn9.astype(np.int8), integral=np.array(bool((att == np.rint(att)).all() and (dfn == np.rint(dfn)).all())),
+                        compute_planes_nonzero=np.array(planes_nonzero))
+
+
 if __name__ == "__main__":
     if not (capi.have_ref_tree() and capi.have_ref_net()):
         sys.exit("oracle/_ref is not built: run `make -C oracle ref` where the reference checkout exists")
@@ -143,11 +168,15 @@ if __name__ == "__main__":
     if sys.argv[1:] == ["chess"]:
         make_chess()
         sys.exit(0)
+    if sys.argv[1:] == ["attack_defense"]:
+        make_attack_defense()
+        sys.exit(0)
     make_select()
     make_encode()
     make_net()
     make_results()
     make_go()
     make_chess()
+    make_attack_defense()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -170,3 +170,34 @@ def test_encode_gomoku3_matches_oracle(api, oracle, B, S, C):
     torch.cuda.synchronize()
     got, pad_zero = api.board_tensor_to_planes(bt.cpu().numpy().view(np.uint16), S, B, C)
     assert pad_zero and np.array_equal(got[:, :3], oracle.gomoku_planes3(stones, tm)) and not got[:, 3:].any()
+
+
+def test_attack_defense_matches_reference_golden(api):
+    """GomokuAttackDefenseModule::compute_bonuses, stone placed, on boards with planted threes and fours
+    (tests/golden/make_golden.py): the device operator gives the reference's numbers exactly."""
+    import torch
+    from test_oracle import load_attack_defense_golden
+    for S, boards, tm, att, dfn in load_attack_defense_golden():
+        a, d = api.gomoku_attack_defense(torch.from_numpy(boards).cuda(), torch.from_numpy(tm).cuda(), S, stone_placed=True)
+        assert np.array_equal(a.cpu().numpy(), att) and np.array_equal(d.cpu().numpy(), dfn)
+        assert np.count_nonzero(att) > 50 and np.count_nonzero(dfn) > 5
+
+
+@pytest.mark.parametrize("B,S,seed", [(256, 15, 1), (33, 9, 2), (8, 19, 3), (5, 6, 4)])
+def test_attack_defense_matches_oracle(api, oracle, B, S, seed):
+    """Both call patterns against the CPU restatement (full recounts of every window, as the reference does it):
+    the position itself - what compute_planes hands over, every plane zero, which is what the encoders write into
+    planes 17 / 18 - and the position with the mover's stone on the cell."""
+    import torch
+    boards, tm = synth.make_threat_positions(B, S, seed=seed)
+    for placed in (False, True):
+        a, d = api.gomoku_attack_defense(torch.from_numpy(boards).cuda(), torch.from_numpy(tm).cuda(), S, stone_placed=placed)
+        ra, rd = oracle.gomoku_attack_defense(boards, tm, S, placed)
+        assert np.array_equal(a.cpu().numpy(), ra) and np.array_equal(d.cpu().numpy(), rd)
+        if not placed:
+            assert not ra.any() and not rd.any()
+    if S == 15:
+        # the encoder's planes 17 / 18 for played games are that all-zero result
+        games, hist, nh, t2 = synth.make_gomoku_games(64, 15, seed=seed, max_moves=60)
+        got, _ = run_encode(api, hist, nh, t2, 15, 19)
+        assert not got[:, 17:19].any()

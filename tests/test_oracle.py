@@ -391,3 +391,47 @@ def test_search_restatement_with_widening(oracle):
         ep, ec = legal_of(tree["empty_bits"][p]), legal_of(tree["empty_bits"][child[p, a]])
         assert legal_of(tree["legal_bits"][p])[a] and ep[a] and not ec[a] and np.array_equal(np.delete(ep, a), np.delete(ec, a))
     assert (tree["N"][:T, :225].sum(1) == spt * R).all() and not tree["VL"].any()
+
+
+def load_attack_defense_golden():
+    """[(board_size, boards int8 [n, S*S], to_move, attack, defense)] from attack_defense_golden.npz; the inputs are
+    regenerated from their seeds and checked against the stored checksum."""
+    import hashlib
+    g = np.load(os.path.join(GOLD, "attack_defense_golden.npz"))
+    boards, tm = synth.make_threat_positions(40, 15, seed=77)
+    small, small_tm = synth.make_threat_positions(12, 9, seed=78)
+    h = hashlib.sha256()
+    for a in (boards, tm, small, small_tm):
+        h.update(np.ascontiguousarray(a).tobytes())
+    assert h.hexdigest() == str(g["inputs_sha256"]), "synth.make_threat_positions changed: regenerate the fixture"
+    assert bool(g["integral"]) and int(g["compute_planes_nonzero"]) == 0
+    return [(15, boards, tm, g["attack15"].astype(np.float32), g["defense15"].astype(np.float32)),
+            (9, small, small_tm, g["attack9"].astype(np.float32), g["defense9"].astype(np.float32))]
+
+
+def test_attack_defense_matches_reference_golden(oracle):
+    """The threat-window restatement against GomokuAttackDefenseModule::compute_bonuses (stone placed) on boards
+    with planted threes and fours; the fixture also records that compute_planes itself returned nothing but
+    zeros on 24 played games."""
+    for S, boards, tm, att, dfn in load_attack_defense_golden():
+        a, d = oracle.gomoku_attack_defense(boards, tm, S, stone_placed=True)
+        assert np.array_equal(a, att) and np.array_equal(d, dfn)
+        a0, d0 = oracle.gomoku_attack_defense(boards, tm, S, stone_placed=False)
+        assert not a0.any() and not d0.any()
+    # a known answer: three in a row with open ends is one window of 5 and two of 6
+    board = np.zeros(225, np.int8)
+    board[[7 * 15 + 5, 7 * 15 + 6, 7 * 15 + 7]] = 1
+    assert oracle.gomoku_threats(board, 1) == 1 + 2 + 0 and oracle.gomoku_threats(board, 2) == 0
+
+
+def test_attack_defense_live_against_the_reference_module(oracle):
+    _need_ref(oracle, "tree")
+    boards, tm = synth.make_threat_positions(16, 15, seed=5)
+    ra, rd = oracle.gomoku_attack_defense(boards, tm, 15, True)
+    for b in range(len(boards)):
+        a, d = oracle.ref_attack_defense_bonuses(boards[b], int(tm[b]), 15)
+        assert np.array_equal(a, ra[b]) and np.array_equal(d, rd[b])
+    games, _, _, _ = synth.make_gomoku_games(6, 15, seed=9, max_moves=40)
+    for g in games:
+        a, d = oracle.ref_attack_defense_planes(g, 15)
+        assert not a.any() and not d.any()
