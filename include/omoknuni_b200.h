@@ -567,6 +567,8 @@ int ob200_debug_bounded_wait(int32_t spin_limit, ob200_stream stream);
  * ------------------------------------------------------------------------- */
 typedef struct ob200_search ob200_search;
 
+enum { OB200_RULES_FREESTYLE = 0, OB200_RULES_OMOK = 1, OB200_RULES_RENJU = 2 };
+
 typedef struct ob200_search_config {
     int32_t n_trees;            /* concurrent games on this GPU                    */
     int32_t sims_per_move;      /* simulations per tree per move (800)             */
@@ -592,6 +594,13 @@ typedef struct ob200_search_config {
     int32_t use_progressive_widening;
     float progressive_widening_c;
     float progressive_widening_k;
+    /* The Gomoku variant (GomokuState's use_renju / use_omok constructor flags,
+     * src/games/gomoku/gomoku_state.cpp:23-31, :915-943): OB200_RULES_*.  Omok
+     * denies BLACK a move that makes six or more in a row or open threes in two
+     * directions (src/games/gomoku/gomoku_rules.cpp:118-198); a win is five or more
+     * for either side, as in freestyle.  Renju's forbidden moves (:200-879) are not
+     * built: OB200_ERR_UNSUPPORTED. */
+    int32_t rules;
 } ob200_search_config;
 
 typedef struct ob200_search_stats {

@@ -27,7 +27,7 @@ public:
     // src/selfplay/self_play_manager.cpp:366-376).  settings.batch_size is the leaf batch of one
     // network call (rounded up to a multiple of n_games).
     B200GomokuSearch(std::shared_ptr<B200Network> net, const alphazero::mcts::MCTSSettings& settings, int n_games,
-                     uint64_t seed = 0)
+                     uint64_t seed = 0, int rules = OB200_RULES_FREESTYLE)
         : net_(std::move(net)), settings_(settings), n_games_(n_games), rng_(seed) {
         ob200_search_config c{};
         c.n_trees = n_games;
@@ -46,6 +46,7 @@ public:
         c.use_progressive_widening = settings.use_progressive_widening ? 1 : 0;
         c.progressive_widening_c = settings.progressive_widening_c;
         c.progressive_widening_k = settings.progressive_widening_k;
+        c.rules = rules;                                     // the variant the GomokuStates were constructed with
         cfg_ = c;
         if (!net_ || !net_->handle() || ob200_search_create(net_->handle(), &c, &search_) != OB200_OK) {
             std::fprintf(stderr, "[B200GomokuSearch] %s\n", ob200_last_error());

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libomoknuni_b200.so")
 
 OUT_PROBS, OUT_LOGITS = 0, 1
 GUARD = 32
+RULES_FREESTYLE, RULES_OMOK, RULES_RENJU = 0, 1, 2
 DTYPE_BF16, DTYPE_F16 = 0, 1     # storage type of board tensors and packed tower weights
 
 
@@ -54,7 +55,7 @@ class SearchConfig(C.Structure):
                 ("c_puct", C.c_float), ("virtual_loss", C.c_int32), ("dirichlet_alpha", C.c_float),
                 ("dirichlet_epsilon", C.c_float), ("value_sign", C.c_int32), ("use_transposition_table", C.c_int32),
                 ("seed", C.c_uint64), ("max_children", C.c_int32), ("use_progressive_widening", C.c_int32),
-                ("progressive_widening_c", C.c_float), ("progressive_widening_k", C.c_float)]
+                ("progressive_widening_c", C.c_float), ("progressive_widening_k", C.c_float), ("rules", C.c_int32)]
 
 
 class SearchStats(C.Structure):
@@ -497,13 +498,14 @@ class Search:
 
     def __init__(self, net, n_trees=64, sims_per_move=800, leaf_batch=1024, max_depth=64, c_puct=1.5, virtual_loss=3,
                  dirichlet_alpha=0.3, dirichlet_epsilon=0.25, value_sign=1, transposition_table=False, seed=0,
-                 max_children=0, progressive_widening=None):
-        """progressive_widening: None (off, as the reference's shipped configuration) or (c, k) of MCTSSettings."""
+                 max_children=0, progressive_widening=None, rules=0):
+        """progressive_widening: None (off, as the reference's shipped configuration) or (c, k) of MCTSSettings.
+        rules: RULES_FREESTYLE or RULES_OMOK."""
         self.net = net                       # keep the network alive
         pw = progressive_widening
         self.cfg = SearchConfig(n_trees, sims_per_move, leaf_batch, max_depth, c_puct, virtual_loss, dirichlet_alpha,
                                 dirichlet_epsilon, value_sign, int(transposition_table), seed, max_children,
-                                int(pw is not None), pw[0] if pw else 0.0, pw[1] if pw else 0.0)
+                                int(pw is not None), pw[0] if pw else 0.0, pw[1] if pw else 0.0, rules)
         self.h = C.c_void_p()
         check(lib().ob200_search_create(net.h, C.byref(self.cfg), C.byref(self.h)))
 

@@ -71,11 +71,57 @@ __device__ __forceinline__ bool bit(const uint32_t* m, int i) { return (m[i >> 5
 // system's entropy source; here a move's rank is the 64-bit mix of (seed, node id, move), so the same seed gives
 // the same subset, and the `target` lowest ranks are kept.
 struct Widening {
-    uint32_t* empty;            // [max_nodes][mask_words] empty cells of every node's position; null: every legal move is a child
+    uint32_t* empty;            // [max_nodes][mask_words] empty cells of every node's position; null: every empty cell is a child
     int max_children;           // <= 0: no cap
     int target;                 // <= 0: no widening
     unsigned long long seed;
+    int rules;                  // OB200_RULES_*: which empty cells BLACK may not play
 };
+
+// Omok: BLACK may not make six or more in a row, nor open threes in two directions at once
+// (GomokuRules::is_black_omok_forbidden, src/games/gomoku/gomoku_rules.cpp:118-198).  black / empty: bitmaps of the
+// position (the cell itself is empty); S the board size.  An "open three in a direction" is the reference's: three
+// consecutive black stones containing the cell, with the cell before and the cell after them on the board and empty.
+__host__ __device__ inline bool omok_forbidden(const uint32_t* black, const uint32_t* empty, int S, int cell) {
+    const int r = cell / S, c = cell - r * S;
+    auto is_black = [&](int rr, int cc) {
+        if (rr < 0 || rr >= S || cc < 0 || cc >= S) return false;
+        const int a = rr * S + cc;
+        return a == cell || ((black[a >> 5] >> (a & 31)) & 1u);
+    };
+    auto is_empty = [&](int rr, int cc) {
+        if (rr < 0 || rr >= S || cc < 0 || cc >= S) return false;
+        const int a = rr * S + cc;
+        return a != cell && ((empty[a >> 5] >> (a & 31)) & 1u);
+    };
+    const int dr[4] = {1, 0, 1, 1}, dc[4] = {0, 1, 1, -1};
+    int open_threes = 0;
+    for (int d = 0; d < 4; ++d) {
+        int run = 1;
+        for (int k = 1; k < S && is_black(r + k * dr[d], c + k * dc[d]); ++k) ++run;
+        for (int k = 1; k < S && is_black(r - k * dr[d], c - k * dc[d]); ++k) ++run;
+        if (run >= 6) return true;
+        bool open = false;
+        for (int i = 0; i < 3 && !open; ++i) {
+            const int r0 = r - i * dr[d], c0 = c - i * dc[d];
+            if (is_black(r0, c0) && is_black(r0 + dr[d], c0 + dc[d]) && is_black(r0 + 2 * dr[d], c0 + 2 * dc[d]))
+                open = is_empty(r0 - dr[d], c0 - dc[d]) && is_empty(r0 + 3 * dr[d], c0 + 3 * dc[d]);
+        }
+        open_threes += open;
+    }
+    return open_threes >= 2;
+}
+// One warp: legal <- empty minus the cells the rules deny the side to move (8 words, shared memory).
+__device__ void legal_moves_warp(const uint32_t* black, const uint32_t* empty, uint32_t* legal, int S, int mask_words,
+                                 int rules, bool black_to_move, int lane) {
+    if (lane < 8) legal[lane] = lane < mask_words ? empty[lane] : 0u;
+    __syncwarp();
+    if (rules == OB200_RULES_OMOK && black_to_move)
+        for (int cell = lane; cell < S * S; cell += 32)
+            if (((empty[cell >> 5] >> (cell & 31)) & 1u) && omok_forbidden(black, empty, S, cell))
+                atomicAnd(&legal[cell >> 5], ~(1u << (cell & 31)));
+    __syncwarp();
+}
 __host__ __device__ __forceinline__ unsigned long long widen_key(unsigned long long seed, int id, int s) {
     unsigned long long z = seed ^ ((unsigned long long)(id + 1) * 0x9E3779B97F4A7C15ull) ^ ((unsigned long long)(s + 1) * 0xC2B2AE3D27D4EB4Full);
     z ^= z >> 30; z *= 0xBF58476D1CE4E5B9ull; z ^= z >> 27; z *= 0x94D049BB133111EBull; z ^= z >> 31;
@@ -146,7 +192,8 @@ void widen_mask_host(const uint32_t* empty, uint32_t* exists, int n_children, in
 
 // Roots: existence mask = empty cells (or the widened subset of them), statistics zero, no children yet.
 __global__ void init_roots_kernel(ob200_tree_view t, const uint32_t* __restrict__ stones, int n_trees,
-                                  int32_t* n_used, int32_t* term_count, Widening wd) {
+                                  int32_t* n_used, int32_t* term_count, Widening wd, const uint8_t* __restrict__ root_tm, int S) {
+    __shared__ uint32_t legal_s[8];
     const int tree = blockIdx.x;
     const uint32_t* st = stones + (size_t)tree * 16;
     const size_t row = (size_t)tree * t.pitch;
@@ -163,7 +210,10 @@ __global__ void init_roots_kernel(ob200_tree_view t, const uint32_t* __restrict_
     }
     if (wd.empty) {
         __syncthreads();
-        if (threadIdx.x < 32) widen_mask_warp(own, t.legal_bits + (size_t)tree * t.mask_words, t.mask_words, wd, tree, threadIdx.x);
+        if (threadIdx.x < 32) {
+            legal_moves_warp(st, own, legal_s, S, t.mask_words, wd.rules, root_tm[tree] == 1, threadIdx.x);
+            widen_mask_warp(legal_s, t.legal_bits + (size_t)tree * t.mask_words, t.mask_words, wd, tree, threadIdx.x);
+        }
     }
     if (threadIdx.x == 0) {
         t.node_visits[tree] = 0;
@@ -396,8 +446,10 @@ expand_plan_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const i
 __global__ void __launch_bounds__(256)
 expand_rows_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const int32_t* __restrict__ path_len,
                    int n_sims, int max_depth, const float* __restrict__ policy, int policy_size,
-                   unsigned long long* node_hash, int tt_size, PlanScratch ps, Widening wd) {
-    const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+                   unsigned long long* node_hash, int tt_size, PlanScratch ps, Widening wd,
+                   const uint32_t* __restrict__ root_stones, const uint8_t* __restrict__ root_tm, int sims_per_tree, int S) {
+    __shared__ uint32_t black_s[8][8], legal_s[8][8];
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
     if (i >= n_sims) return;
     const int st = ps.status[i];
     const int id = ps.new_id[i];
@@ -413,7 +465,24 @@ expand_rows_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const i
     uint32_t* cm = t.legal_bits + (size_t)id * t.mask_words;
     for (int w = lane; w < t.mask_words; w += 32) own[w] = pm[w] & ~((w == (slot >> 5)) ? (1u << (slot & 31)) : 0u);
     __syncwarp();
-    if (wd.empty) { widen_mask_warp(own, cm, t.mask_words, wd, id, lane); __syncwarp(); }
+    if (wd.empty) {
+        const int tree = i / sims_per_tree;
+        const bool black_to_move = (root_tm[tree] == 1) == ((len & 1) == 0);     // the root's side moves at even depths
+        if (wd.rules != OB200_RULES_FREESTYLE && black_to_move) {
+            // BLACK's stones at the new node: the root's, and the path's moves made by BLACK
+            if (lane < 8) black_s[wi][lane] = root_stones[(size_t)tree * 16 + lane];
+            __syncwarp();
+            for (int d = lane; d < len; d += 32) {
+                const bool black_moved = (root_tm[tree] == 1) == ((d & 1) == 0);
+                const int a = p[2 * d + 1];
+                if (black_moved) atomicOr(&black_s[wi][a >> 5], 1u << (a & 31));
+            }
+            __syncwarp();
+        }
+        legal_moves_warp(black_s[wi], own, legal_s[wi], S, t.mask_words, wd.rules, black_to_move, lane);
+        widen_mask_warp(legal_s[wi], cm, t.mask_words, wd, id, lane);
+        __syncwarp();
+    }
     const float* pol = policy + (size_t)i * policy_size;
     for (int s = lane; s < t.pitch; s += 32) {
         float pr = 0.0f;
@@ -464,10 +533,13 @@ int ob200_search_create(ob200_net* net, const ob200_search_config* cfg, ob200_se
     if (cfg->n_trees < 1 || cfg->sims_per_move < 1 || cfg->leaf_batch < cfg->n_trees || cfg->leaf_batch % cfg->n_trees ||
         cfg->leaf_batch > nc->max_batch || cfg->max_depth < 1 || cfg->max_depth > kMaxDepth || cfg->virtual_loss < 0 ||
         (cfg->value_sign != 1 && cfg->value_sign != -1) || cfg->dirichlet_epsilon < 0 || cfg->dirichlet_epsilon > 1 ||
-        cfg->max_children < 0 || (cfg->use_progressive_widening && !(cfg->progressive_widening_c >= 0.0f)))
+        cfg->max_children < 0 || (cfg->use_progressive_widening && !(cfg->progressive_widening_c >= 0.0f)) ||
+        cfg->rules < 0 || cfg->rules > OB200_RULES_RENJU)
         return set_error(OB200_ERR_INVALID,
                          "ob200_search_create: need leaf_batch a multiple of n_trees and <= the network's max_batch (%d), max_depth in [1,%d], value_sign +-1",
                          nc->max_batch, kMaxDepth);
+    if (cfg->rules == OB200_RULES_RENJU)
+        return set_error(OB200_ERR_UNSUPPORTED, "ob200_search_create: Renju's forbidden moves are not built; freestyle and Omok are");
     OB200_CUDA_OK(cudaSetDevice(nc->device));
     if (int rc = require_device()) return rc;
     ob200_search* s = new ob200_search;
@@ -486,7 +558,8 @@ int ob200_search_create(ob200_net* net, const ob200_search_config* cfg, ob200_se
     s->max_children = cfg->max_children > 0 ? cfg->max_children : 1000;
     if (cfg->use_progressive_widening)       // the reference's count for a node without visits: (visits + 1)^k = 1
         s->widen_target = (int)std::max(8.0f, (float)((double)cfg->progressive_widening_c * std::pow(1.0, (double)cfg->progressive_widening_k)));
-    if (s->widen_target > 0 || s->max_children < s->A) A_(salloc(s, &s->empty_bits, (size_t)s->max_nodes * s->mask_words));
+    if (s->widen_target > 0 || s->max_children < s->A || cfg->rules != OB200_RULES_FREESTYLE)
+        A_(salloc(s, &s->empty_bits, (size_t)s->max_nodes * s->mask_words));
     A_(salloc(s, &s->n_used, 1)); A_(salloc(s, &s->term_count, 1));
     A_(salloc(s, &s->root_stones, (size_t)T * 16)); A_(salloc(s, &s->root_hist, (size_t)T * 16));
     A_(salloc(s, &s->root_nh, (size_t)T)); A_(salloc(s, &s->root_tm, (size_t)T)); A_(salloc(s, &s->root_count, (size_t)T));
@@ -627,7 +700,14 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
                 empty[w] = ~(stones[(size_t)t * 16 + w] | stones[(size_t)t * 16 + 8 + w]) & valid;
                 child[w] = empty[w];
             }
-            if (s->empty_bits) widen_mask_host(empty, child, A, 8, s->max_children, s->widen_target, wseed, t);
+            if (c.rules == OB200_RULES_OMOK && tm[t] == 1)
+                for (int a = 0; a < A; ++a)
+                    if (((empty[a >> 5] >> (a & 31)) & 1u) && omok_forbidden(&stones[(size_t)t * 16], empty, s->S, a)) child[a >> 5] &= ~(1u << (a & 31));
+            if (s->empty_bits) {
+                uint32_t legal[8];
+                for (int w = 0; w < 8; ++w) legal[w] = child[w];
+                widen_mask_host(legal, child, A, 8, s->max_children, s->widen_target, wseed, t);
+            }
             auto is_child = [&](int a) { return (child[a >> 5] >> (a & 31)) & 1u; };
             for (int a = 0; a < A; ++a)
                 if (is_child(a)) { row[a] = gamma(rng); sum += row[a]; ++children; }
@@ -649,8 +729,8 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
     }
     OB200_CUDA_OK(cudaEventRecord(s->ev0, st));
     // ---- roots: create, evaluate, priors (+ noise) ----
-    const Widening wd{s->empty_bits, s->empty_bits ? s->max_children : 0, s->empty_bits ? s->widen_target : 0, wseed};
-    init_roots_kernel<<<T, 128, 0, st>>>(s->tv, s->root_stones, T, s->n_used, s->term_count, wd);
+    const Widening wd{s->empty_bits, s->empty_bits ? s->max_children : 0, s->empty_bits ? s->widen_target : 0, wseed, c.rules};
+    init_roots_kernel<<<T, 128, 0, st>>>(s->tv, s->root_stones, T, s->n_used, s->term_count, wd, s->root_tm, s->S);
     OB200_LAUNCHED("init_roots_kernel");
     if (int rc = net_forward_gomoku_for_search(s->net, s->root_hist, s->root_nh, s->root_tm, T, s->policy, s->value, st)) return rc;
     if (int rc = ob200_launch_set_priors(&s->tv, s->roots, T, s->policy, A, nullptr, st)) return rc;
@@ -684,7 +764,8 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
                                                        s->tt_key, s->tt_val, s->tt_size, ps);
         OB200_LAUNCHED("expand_plan_kernel");
         expand_rows_kernel<<<(L * 32 + 255) / 256, 256, 0, st>>>(s->tv, s->paths, s->path_len, L, c.max_depth, s->policy, A,
-                                                                s->node_hash, s->tt_size, ps, wd);
+                                                                s->node_hash, s->tt_size, ps, wd, s->root_stones, s->root_tm,
+                                                                s->sims_per_round, s->S);
         OB200_LAUNCHED("expand_rows_kernel");
         if (int rc = ob200_launch_backup(&s->tv, s->paths, s->path_len, s->leaf_value, L, c.max_depth, c.virtual_loss, st)) return rc;
     }

@@ -220,10 +220,21 @@ def widen_target(c, k, visits=0):
     return int(L.oracle_widen_target(c, k, visits))
 
 
+def gomoku_legal_mask(moves, board_size=15, rules=0):
+    """Legal moves of the position after `moves` as mask words (oracle_gomoku_legal_mask in oracle.c); rules 1 = Omok."""
+    mv = np.ascontiguousarray(moves, np.int16)
+    mw = (board_size * board_size + 31) // 32
+    out = np.zeros(mw, np.uint32)
+    L = lib()
+    L.oracle_gomoku_legal_mask.argtypes = [_i16, C.c_int, C.c_int, C.c_int, _u32, C.c_int]
+    L.oracle_gomoku_legal_mask(mv, len(mv), board_size, rules, out, mw)
+    return out
+
+
 def search_new_trees(move_lists, max_nodes, n_children=225, widen=None):
     """Edge arrays for a search over the given games: node t is the root of game t (existence mask =
-    empty cells), everything else unused.  widen = (max_children, target, seed): the empty cells are kept in
-    tree["empty_bits"] and the roots' children are the chosen subset of them."""
+    empty cells), everything else unused.  widen = (max_children, target, seed[, rules]): the empty cells are kept
+    in tree["empty_bits"] and the roots' children are the chosen subset of the moves the rules allow."""
     T = len(move_lists)
     pitch, mw = (n_children + 3) // 4 * 4, (n_children + 31) // 32
     t = {"N": np.zeros((max_nodes, pitch), np.int32), "W": np.zeros((max_nodes, pitch), np.float32),
@@ -238,8 +249,10 @@ def search_new_trees(move_lists, max_nodes, n_children=225, widen=None):
         t["legal_bits"][g] = np.packbits(bits.reshape(mw, 32), axis=1, bitorder="little").view(np.uint32).reshape(mw)
     if widen is not None:
         t["empty_bits"] = t["legal_bits"].copy()
+        rules = widen[3] if len(widen) > 3 else 0
         for g in range(T):
-            t["legal_bits"][g] = widen_mask(t["empty_bits"][g], n_children, widen[0], widen[1], widen[2], g)
+            legal = gomoku_legal_mask(move_lists[g], 15, rules) if rules else t["empty_bits"][g]
+            t["legal_bits"][g] = widen_mask(legal, n_children, widen[0], widen[1], widen[2], g)
     return t
 
 
@@ -283,15 +296,16 @@ def search_expand(tree, node_hash, paths, path_len, sims_per_tree, move_lists, p
     L.oracle_search_expand_widen.argtypes = [_i32, _f32, _f32, _i32, _u32, _i32, _i32, C.c_void_p, _i32, C.c_int, C.c_int, C.c_int,
                                              C.c_int, _i32, _i32, C.c_int, C.c_int, C.c_int, _i16, _i32, C.c_int, C.c_int, _f32,
                                              C.c_int, _f32, C.c_float, C.c_float, _u64, C.c_int, _f32, _i32, C.c_void_p, C.c_int,
-                                             C.c_int, C.c_uint64]
-    wd = widen if widen is not None else (0, 0, 0)
+                                             C.c_int, C.c_uint64, C.c_int]
+    wd = tuple(widen) if widen is not None else (0, 0, 0)
+    wd = wd if len(wd) > 3 else wd + (0,)
     L.oracle_search_expand_widen(tree["N"], tree["W"], tree["P"], tree["VL"], tree["legal_bits"], tree["node_visits"],
                            tree["child_node"], _opt(node_hash), used, tree["N"].shape[0], tree["n_children"],
                            tree["N"].shape[1], tree["legal_bits"].shape[1], paths, np.ascontiguousarray(path_len, np.int32),
                            n, max_depth, sims_per_tree, moves, nm, stride, board_size, policy, policy.shape[1],
                            np.ascontiguousarray(value, np.float32), float(value_sign), float(value_quantum),
                            np.ascontiguousarray(zobrist, np.uint64), T, leaf, term,
-                           _opt(tree["empty_bits"]) if widen is not None else None, wd[0], wd[1], wd[2])
+                           _opt(tree["empty_bits"]) if widen is not None else None, wd[0], wd[1], wd[2], wd[3])
     tree["nodes"] = int(used[0])
     return leaf, term
 
@@ -489,6 +503,18 @@ def ref_attack_defense_bonuses(board, player, board_size=15):
     L.ref_attack_defense_bonuses.restype = C.c_int
     assert L.ref_attack_defense_bonuses(bd, board_size, player, att, dfn) == 0
     return att, dfn
+
+
+def ref_gomoku_legal_moves(moves, board_size=15, renju=False, omok=False):
+    """GomokuState::getLegalMoves after `moves` on a state constructed with the given variant flags (bool [S*S]);
+    None when one of the moves was refused by the state."""
+    mv = np.ascontiguousarray(moves, np.int16)
+    out = np.zeros(board_size * board_size, np.uint8)
+    L = ref_tree()
+    L.ref_gomoku_legal_moves.argtypes = [_i16, C.c_int, C.c_int, C.c_int, C.c_int, np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")]
+    L.ref_gomoku_legal_moves.restype = C.c_int
+    rc = L.ref_gomoku_legal_moves(mv, len(mv), board_size, int(renju), int(omok), out)
+    return out.astype(bool) if rc == 0 else None
 
 
 def ref_gomoku_result(moves, board_size=15):

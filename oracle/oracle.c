@@ -466,6 +466,54 @@ void oracle_gomoku_planes3_batch(const signed char* stones, const unsigned char*
  * terminal_out[i]: 0 not terminal, 1 the side to move has lost, 2 draw. */
 static float quantized(float v, float q) { return q > 0.0f ? rintf(v * q) / q : v; }
 
+/* GomokuRules::is_black_omok_forbidden, src/games/gomoku/gomoku_rules.cpp:176-198: with BLACK's stone on `action`
+ * (an empty cell), a line of six or more through it (omok_is_six_in_a_row :118-127 over get_line_length_at_action
+ * :38-69), or an open three in two or more of the four directions (omok_makes_double_three :161-174).  An open
+ * three in a direction (check_omok_open_three_in_direction :129-159): one of the three placements of three
+ * consecutive cells containing the action is all BLACK, and the cell before and the cell after it are on the board
+ * and empty.  board: 0 empty, 1 black, 2 white. */
+int oracle_omok_forbidden(const int8_t* board, int S, int action) {
+    static const int dr[4] = {1, 0, 1, 1}, dc[4] = {0, 1, 1, -1};
+    const int r = action / S, c = action % S;
+#define OB_BLACK(rr, cc) ((rr) >= 0 && (rr) < S && (cc) >= 0 && (cc) < S && (((rr) * S + (cc)) == action || board[(rr) * S + (cc)] == 1))
+#define OB_EMPTY(rr, cc) ((rr) >= 0 && (rr) < S && (cc) >= 0 && (cc) < S && ((rr) * S + (cc)) != action && board[(rr) * S + (cc)] == 0)
+    int open_threes = 0;
+    for (int d = 0; d < 4; ++d) {
+        int run = 1;
+        for (int k = 1; k < S && OB_BLACK(r + k * dr[d], c + k * dc[d]); ++k) ++run;
+        for (int k = 1; k < S && OB_BLACK(r - k * dr[d], c - k * dc[d]); ++k) ++run;
+        if (run >= 6) return 1;
+    }
+    for (int d = 0; d < 4; ++d) {
+        int open = 0;
+        for (int i = 0; i < 3 && !open; ++i) {
+            const int r0 = r - i * dr[d], c0 = c - i * dc[d];
+            int three = 1;
+            for (int k = 0; k < 3; ++k) three = three && OB_BLACK(r0 + k * dr[d], c0 + k * dc[d]);
+            if (three && OB_EMPTY(r0 - dr[d], c0 - dc[d]) && OB_EMPTY(r0 + 3 * dr[d], c0 + 3 * dc[d])) open = 1;
+        }
+        open_threes += open;
+    }
+#undef OB_BLACK
+#undef OB_EMPTY
+    return open_threes >= 2;
+}
+/* The legal moves of a Gomoku position (GomokuState::is_move_valid_internal, src/games/gomoku/gomoku_state.cpp:
+ * 915-943, without the opening restriction): the empty cells, minus BLACK's forbidden ones under Omok (rules 1)
+ * when BLACK is to move.  legal_out: one bit per cell, mask_words words. */
+void oracle_gomoku_legal_mask(const int16_t* moves, int n_moves, int S, int rules, uint32_t* legal_out, int mask_words) {
+    int8_t board[32 * 32];
+    memset(board, 0, sizeof board);
+    for (int i = 0; i < n_moves; ++i) board[moves[i]] = (int8_t)(1 + (i & 1));
+    for (int w = 0; w < mask_words; ++w) legal_out[w] = 0;
+    const int black_to_move = (n_moves & 1) == 0;
+    for (int a = 0; a < S * S; ++a) {
+        if (board[a]) continue;
+        if (rules == 1 && black_to_move && oracle_omok_forbidden(board, S, a)) continue;
+        legal_out[a >> 5] |= 1u << (a & 31);
+    }
+}
+
 /* The children a new node gets out of its legal moves (MCTSNode::expand,
  * src/mcts/mcts_node.cpp:283-340): at most max_children, the first in move order (:287-291, 1,000 in the
  * reference), and with progressive widening `target` of those chosen at random (:297-340 with the shuffle at
@@ -517,7 +565,7 @@ void oracle_search_expand_widen(int32_t* N, float* W, float* P, int32_t* VL, uin
                           const float* value, float value_sign, float value_quantum,
                           const uint64_t* zobrist, int n_trees, float* leaf_value_out,
                           int32_t* terminal_out, uint32_t* empty, int max_children, int widen_target,
-                          uint64_t widen_seed) {
+                          uint64_t widen_seed, int rules) {
     int16_t game[32 * 32];
     for (int i = 0; i < n_sims; ++i) {
         const int tree = i / sims_per_tree;
@@ -558,7 +606,12 @@ void oracle_search_expand_widen(int32_t* N, float* W, float* P, int32_t* VL, uin
         uint32_t* own = (empty ? empty : legal) + (size_t)id * mask_words;
         uint32_t* cm = legal + (size_t)id * mask_words;
         for (int w = 0; w < mask_words; ++w) own[w] = pm[w] & ~((w == (slot >> 5)) ? (1u << (slot & 31)) : 0u);
-        if (empty) oracle_widen_mask(own, cm, n_children, mask_words, max_children, widen_target, widen_seed, id);
+        if (empty) {
+            /* the moves the rules leave the side to move, then the limits on children */
+            uint32_t legal_now[64];
+            oracle_gomoku_legal_mask(game, n0 + len, S, rules, legal_now, mask_words);
+            oracle_widen_mask(legal_now, cm, n_children, mask_words, max_children, widen_target, widen_seed, id);
+        }
         for (int s = 0; s < pitch; ++s) {
             float pr = 0.0f;
             if (s < n_children && ((cm[s >> 5] >> (s & 31)) & 1u) && s < policy_size)
@@ -583,7 +636,7 @@ void oracle_search_expand(int32_t* N, float* W, float* P, int32_t* VL, uint32_t*
     oracle_search_expand_widen(N, W, P, VL, legal, node_visits, child_node, node_hash, n_used, max_nodes, n_children,
                                pitch, mask_words, paths, path_len, n_sims, max_depth, sims_per_tree, root_moves,
                                root_n_moves, moves_stride, S, policy, policy_size, value, value_sign, value_quantum,
-                               zobrist, n_trees, leaf_value_out, terminal_out, NULL, 0, 0, 0);
+                               zobrist, n_trees, leaf_value_out, terminal_out, NULL, 0, 0, 0, 0);
 }
 
 /* MCTSEngine::addDirichletNoise, src/mcts/mcts_engine_eval.cpp:83-110.  The noise

@@ -329,4 +329,17 @@ int ref_attack_defense_bonuses(const int8_t* board, int board_size, int player, 
     return 0;
 }
 
+// GomokuState::getLegalMoves (through is_move_valid_internal, src/games/gomoku/gomoku_state.cpp:915-943) on a state
+// constructed with the variant flags, after `moves`.  legal_out: one byte per cell.  -1 when a move was not legal.
+int ref_gomoku_legal_moves(const int16_t* moves, int n_moves, int board_size, int use_renju, int use_omok, uint8_t* legal_out) {
+    alphazero::games::gomoku::GomokuState st(board_size, use_renju != 0, use_omok != 0, 0, false);
+    for (int i = 0; i < n_moves; ++i) {
+        if (!st.isLegalMove(moves[i])) return -1;
+        st.makeMove(moves[i]);
+    }
+    std::memset(legal_out, 0, (size_t)board_size * board_size);
+    for (int a : st.getLegalMoves()) legal_out[a] = 1;
+    return 0;
+}
+
 }  // extern "C"

@@ -19,6 +19,8 @@ the inputs' checksums and the reference's outputs:
   attack_defense_golden.npz  GomokuAttackDefenseModule: compute_planes on played games (all zero) and
                      compute_bonuses with the stone placed on boards with planted threes and
                      fours (`make_golden.py attack_defense`)
+  omok_golden.npz    GomokuState(use_omok) legal moves after seeded play that keeps to the centre, so that
+                     six-in-a-row and double-three cells occur (`make_golden.py omok`)
   net_golden.npz     ResNetModel::forward (log-softmax policy, value): (a) a tiny
                      model with the reference's own libtorch default
                      initialisation, its weights stored here rounded to fp16
@@ -159,6 +161,35 @@ def make_attack_defense():
                         compute_planes_nonzero=np.array(planes_nonzero))
 
 
+def make_omok():
+    rng = np.random.default_rng(2025)
+    games, masks, forbidden = [], [], 0
+    while len(games) < 64:
+        moves = []
+        for _ in range(int(rng.integers(8, 70))):
+            legal = capi.ref_gomoku_legal_moves(moves, 15, False, True)
+            cand = np.nonzero(legal)[0]
+            if len(cand) == 0 or (moves and capi.ref_gomoku_result(moves, 15) != 0):
+                break
+            near = [a for a in cand if abs(a // 15 - 7) <= 3 and abs(a % 15 - 7) <= 3]
+            moves.append(int(rng.choice(near if near and rng.random() < 0.85 else cand)))
+        if moves and capi.ref_gomoku_result(moves, 15) != 0:
+            moves.pop()
+        legal = capi.ref_gomoku_legal_moves(moves, 15, False, True)
+        empty = np.ones(225, bool)
+        empty[moves] = False
+        n_forbidden = int((empty & ~legal).sum())
+        if n_forbidden == 0 and len(games) % 4 != 3:      # keep mostly positions where the rule bites
+            continue
+        forbidden += n_forbidden
+        games.append(moves)
+        masks.append(legal)
+    flat = np.concatenate([np.asarray(g, np.int16) for g in games])
+    ptr = np.cumsum([0] + [len(g) for g in games])
+    np.savez_compressed(os.path.join(HERE, "omok_golden.npz"), moves=flat, row_ptr=ptr, legal_bits=np.packbits(np.array(masks)),
+                        forbidden_cells=np.array(forbidden))
+
+
 if __name__ == "__main__":
     if not (capi.have_ref_tree() and capi.have_ref_net()):
         sys.exit("oracle/_ref is not built: run `make -C oracle ref` where the reference checkout exists")
@@ -167,6 +198,9 @@ if __name__ == "__main__":
         sys.exit(0)
     if sys.argv[1:] == ["chess"]:
         make_chess()
+        sys.exit(0)
+    if sys.argv[1:] == ["omok"]:
+        make_omok()
         sys.exit(0)
     if sys.argv[1:] == ["attack_defense"]:
         make_attack_defense()
@@ -178,5 +212,6 @@ if __name__ == "__main__":
     make_go()
     make_chess()
     make_attack_defense()
+    make_omok()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -435,3 +435,54 @@ def test_attack_defense_live_against_the_reference_module(oracle):
     for g in games:
         a, d = oracle.ref_attack_defense_planes(g, 15)
         assert not a.any() and not d.any()
+
+
+def load_omok_golden():
+    """(games, legal [n, 225] bool) from omok_golden.npz: GomokuState(use_omok)'s legal moves after seeded play."""
+    g = np.load(os.path.join(GOLD, "omok_golden.npz"))
+    ptr = g["row_ptr"]
+    games = [g["moves"][ptr[i]:ptr[i + 1]].astype(np.int64).tolist() for i in range(len(ptr) - 1)]
+    legal = np.unpackbits(g["legal_bits"])[:len(games) * 225].reshape(len(games), 225).astype(bool)
+    assert int(g["forbidden_cells"]) >= 40
+    return games, legal
+
+
+def _legal_of(words, n=225):
+    return np.unpackbits(np.ascontiguousarray(words).view(np.uint8), bitorder="little")[:n].astype(bool)
+
+
+def test_omok_legal_moves_match_reference_golden(oracle):
+    """BLACK's forbidden moves under Omok (six or more in a row, open threes in two directions) against the legal
+    moves of the reference's GomokuState constructed with use_omok, and two known answers."""
+    games, legal = load_omok_golden()
+    forbidden = 0
+    for mv, want in zip(games, legal):
+        got = _legal_of(oracle.gomoku_legal_mask(mv, 15, rules=1))
+        assert np.array_equal(got, want), mv
+        empty = np.ones(225, bool)
+        empty[mv] = False
+        forbidden += int((empty & ~got).sum())
+        assert np.array_equal(_legal_of(oracle.gomoku_legal_mask(mv, 15, rules=0)), empty)
+    assert forbidden >= 40
+    # a cross of two open twos: the centre makes two open threes; black to move (white's stones far away)
+    black = [7 * 15 + 6, 7 * 15 + 8, 6 * 15 + 7, 8 * 15 + 7]
+    white = [0, 14, 210, 224]
+    mv = [m for pair in zip(black, white) for m in pair]
+    assert not _legal_of(oracle.gomoku_legal_mask(mv, 15, rules=1))[7 * 15 + 7]
+    assert _legal_of(oracle.gomoku_legal_mask(mv, 15, rules=0))[7 * 15 + 7]
+    # five with a gap: the gap would make six
+    black = [7 * 15 + c for c in (2, 3, 4, 6, 7)]
+    white = [0, 14, 210, 224, 1]
+    mv = [m for pair in zip(black, white) for m in pair]
+    assert not _legal_of(oracle.gomoku_legal_mask(mv, 15, rules=1))[7 * 15 + 5]
+    # with WHITE to move nothing is forbidden
+    assert _legal_of(oracle.gomoku_legal_mask(mv + [7 * 15 + 10], 15, rules=1))[7 * 15 + 5]
+
+
+def test_omok_legal_moves_live_against_gomokustate(oracle):
+    _need_ref(oracle, "tree")
+    games, _ = load_omok_golden()
+    for mv in games[:24]:
+        for cut in (len(mv), len(mv) - 1, len(mv) // 2):
+            want = oracle.ref_gomoku_legal_moves(mv[:cut], 15, renju=False, omok=True)
+            assert want is not None and np.array_equal(_legal_of(oracle.gomoku_legal_mask(mv[:cut], 15, rules=1)), want)

@@ -85,6 +85,9 @@ SEARCH_CASES = [
     ("widened_20", None, 4, 16, 12, False, 0.25, 1, {"pw": (20.5, 0.5)}),
     ("capped_40", None, 4, 16, 12, True, 0.25, 1, {"max_children": 40}),
     ("capped_and_widened", "four", 4, 16, 12, True, 0.0, -1, {"max_children": 60, "pw": (12.0, 1.0)}),
+    # Omok: BLACK's forbidden moves are no children, at the roots and below
+    ("omok", "omok", 16, 8, 12, True, 0.25, 1, {"rules": 1}),
+    ("omok_widened", "omok", 8, 16, 8, False, 0.25, 1, {"rules": 1, "pw": (16.0, 0.5)}),
 ]
 SEARCH_CASES = [c if len(c) == 9 else c + ({},) for c in SEARCH_CASES]
 
@@ -98,15 +101,22 @@ def test_search_equals_the_oracle_on_the_same_network_outputs(net, oracle, name,
     from omoknuni_small_b200 import capi
     if games == "four":
         games = [open_four()] * T
+    elif games == "omok":
+        from test_oracle import load_omok_golden
+        all_games, all_legal = load_omok_golden()
+        black_to_move = [k for k, g in enumerate(all_games) if len(g) % 2 == 0]
+        pick = (black_to_move + [k for k in range(len(all_games)) if k not in black_to_move])[:T]
+        games, root_legal = [all_games[k] for k in pick], all_legal[pick]
     else:
         games, _, _, _ = synth.make_gomoku_games(T, 15, seed=40 + T, max_moves=20)
     s = capi.Search(net, n_trees=T, sims_per_move=spt * R, leaf_batch=T * spt, max_depth=32, c_puct=1.5, virtual_loss=3,
                     dirichlet_alpha=0.3, dirichlet_epsilon=eps, value_sign=sign, transposition_table=table, seed=7,
-                    max_children=limits.get("max_children", 0), progressive_widening=limits.get("pw"))
+                    max_children=limits.get("max_children", 0), progressive_widening=limits.get("pw"),
+                    rules=limits.get("rules", 0))
     s.debug_hooks(value_quantum=256.0, record_rounds=R)
     target = oracle.widen_target(*limits["pw"]) if "pw" in limits else 0
     for move in range(2):                                          # a second move on the same handle starts clean
-        widen = (limits.get("max_children", 1000), target, capi.widening_seed(7, move)) if limits else None
+        widen = (limits.get("max_children", 1000), target, capi.widening_seed(7, move), limits.get("rules", 0)) if limits else None
         pi, visits, st = s.run(games, temperature=1.0)
         assert capi.device_error_code() == 0
         pol, val, noise = s.record()
@@ -117,7 +127,13 @@ def test_search_equals_the_oracle_on_the_same_network_outputs(net, oracle, name,
                                  tt_seed=7 if table else None, widen=widen)
         n = ref["nodes"]
         assert dev["nodes"] == n == st["nodes"], (dev["nodes"], n)
-        if limits:
+        if limits.get("rules"):
+            # the roots' children are the legal moves of the reference's GomokuState(use_omok), or a subset of them
+            for t in range(T):
+                kids = legal_of(dev["legal_bits"][t])
+                assert not (kids & ~root_legal[t]).any() and (target or np.array_equal(kids, root_legal[t]))
+            assert any((~root_legal[t] & ~np.isin(np.arange(225), games[t])).any() for t in range(T)), "no forbidden cell among the roots"
+        elif limits:
             kids = np.array([legal_of(dev["legal_bits"][k]).sum() for k in range(n)])
             most = min(limits.get("max_children", 1000), target or 1000)
             assert kids.max() == most and (kids[:T] == most).all()
@@ -299,6 +315,9 @@ def test_search_argument_errors(net):
         capi.Search(net, n_trees=3, leaf_batch=64)                   # leaf_batch not a multiple of n_trees
     with pytest.raises(capi.Error):
         capi.Search(net, n_trees=64, leaf_batch=1024)                # beyond the network's max_batch (256)
+    with pytest.raises(capi.Error) as e:
+        capi.Search(net, n_trees=2, leaf_batch=8, rules=capi.RULES_RENJU)   # Renju's forbidden moves are not built
+    assert e.value.code == 5 and "Renju" in str(e.value)
     s = capi.Search(net, n_trees=2, sims_per_move=8, leaf_batch=8)
     with pytest.raises(capi.Error):
         s.run([[5, 5], [1]])                                         # a cell played twice
