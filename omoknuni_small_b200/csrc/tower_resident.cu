@@ -1,6 +1,6 @@
 // The 64-filter residual tower with the boards RESIDENT in shared memory (sm_100a).
 //
-// A board of up to 15x15 cells is at most 256 padded positions x 64 channels = 32 KB in bf16, and a
+// A board of up to 15x15 cells is at most 256 padded positions x 64 channels = 32 KB in bf16 or fp16, and a
 // 3x3 convolution never looks outside its own board (the padded row / column around every board is
 // zero).  So a CTA can take a board through ALL the layers without the activations ever leaving the
 // SM: two buffers per board (x: block input / residual / block output, y: the middle of a block),
@@ -33,10 +33,10 @@
 //     no input tensor in HBM.
 // There is no communication between CTAs, so this is an ordinary launch (and may be captured in a
 // graph).  Every wait is bounded; a thread that gives up raises the device error word.
-// Measured (15x15, 21 layers, B200): 8,000-8,400 cycles per layer for a pair of boards (four tiles), against
-// 6,912 for the MMAs alone; 370 us for 1,024 boards (932 TFLOP/s) and 1,327 us for 4,096 (1,039 TFLOP/s)
-// where a launch per layer takes 432 / 1,650 us; 74-79 us for 1 to 148 boards
-// (single-issuer variant; 93-140 us as a launch per layer).
+// Measured (15x15, 21 layers, B200): about 7,400 cycles per layer for a pair of boards (four tiles), against
+// 6,912 for the MMAs alone, and about 5,450 for a lone board; 320-332 us for 1,024 boards (1,037-1,074 TFLOP/s)
+// and 1,174 us for 4,096 (1,173 TFLOP/s) where a launch per layer takes 466 / 1,650 us; 74-79 us for 1 to
+// 148 boards (93-140 us as a launch per layer).
 #include "internal.h"
 #include "sm100_ptx.cuh"
 #include <cstring>
