@@ -598,8 +598,12 @@ typedef struct ob200_search_config {
      * src/games/gomoku/gomoku_state.cpp:23-31, :915-943): OB200_RULES_*.  Omok
      * denies BLACK a move that makes six or more in a row or open threes in two
      * directions (src/games/gomoku/gomoku_rules.cpp:118-198); a win is five or more
-     * for either side, as in freestyle.  Renju's forbidden moves (:200-879) are not
-     * built: OB200_ERR_UNSUPPORTED. */
+     * for either side, as in freestyle.  Renju denies BLACK overlines, double
+     * fours and double threes as the reference defines them (:200-879; an exact
+     * five is always allowed), and BLACK wins only with exactly five and no longer
+     * line through the stone (gomoku_state.cpp:812-843).  The double-three test
+     * follows the cell that would complete a three through at most four nested
+     * levels.  The opening restriction (use_pro_long_opening) is not built. */
     int32_t rules;
 } ob200_search_config;
 

@@ -580,7 +580,6 @@ int wait_slot(ob200_net* n, int si) {
 // Gomoku histories -> staging -> device -> encoder -> forward -> results on their way back.  Handle mutex held.
 int enqueue_gomoku(ob200_net* n, int si, const int16_t* history, const uint8_t* n_hist, const uint8_t* to_move, int32_t B,
                    float* policy_out, float* value_out, int32_t out_kind) {
-    const ob200_net_config& c = n->cfg;
     ob200_net::Slot& sl = n->slot[si];
     const size_t hist_bytes = (size_t)B * 16 * sizeof(int16_t);
     uint8_t* h8 = reinterpret_cast<uint8_t*>(sl.h_hist);

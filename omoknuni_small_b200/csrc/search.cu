@@ -111,14 +111,169 @@ __host__ __device__ inline bool omok_forbidden(const uint32_t* black, const uint
     }
     return open_threes >= 2;
 }
+// Renju: BLACK's forbidden moves - overline, double four, double three
+// (GomokuRules::is_black_renju_forbidden and what it calls, src/games/gomoku/gomoku_rules.cpp:200-879).
+// A thread tests one cell on its own copy of BLACK's stones (hypothetical stones are set and cleared in it);
+// empty0 is the position's empty-cell bitmap, so a cell is empty when it is in empty0 and not in the copy.
+// The reference's double-three test recurses through the cell that would complete each three to a straight
+// four; the recursion is unrolled at compile time to kRenjuDepth levels (the deepest seen on 600 dense
+// boards is 3), beyond which a test answers "not a double three", as the CPU restatement does.
+constexpr int kRenjuDepth = 4;
+struct RjBoard {
+    uint32_t bk[8];
+    const uint32_t* empty0;
+    int S;
+    __device__ bool in(int r, int c) const { return r >= 0 && r < S && c >= 0 && c < S; }
+    __device__ bool black(int r, int c) const { return in(r, c) && ((bk[(r * S + c) >> 5] >> ((r * S + c) & 31)) & 1u); }
+    __device__ bool empty(int r, int c) const {
+        if (!in(r, c)) return false;
+        const int a = r * S + c;
+        return ((empty0[a >> 5] >> (a & 31)) & 1u) && !((bk[a >> 5] >> (a & 31)) & 1u);
+    }
+    __device__ void set(int a) { bk[a >> 5] |= 1u << (a & 31); }
+    __device__ void clear(int a) { bk[a >> 5] &= ~(1u << (a & 31)); }
+};
+__device__ __constant__ int kRjDr[4] = {1, 0, 1, 1};
+__device__ __constant__ int kRjDc[4] = {0, 1, 1, -1};
+// get_line_length_at_action (:38-69): BLACK's run through a cell that holds a black stone
+__device__ __noinline__ int rj_len(const RjBoard& b, int a, int d) {
+    const int r = a / b.S, c = a - r * b.S;
+    if (!b.black(r, c)) return 0;
+    int n = 1;
+    for (int i = 1; i < b.S && b.black(r + i * kRjDr[d], c + i * kRjDc[d]); ++i) ++n;
+    for (int i = 1; i < b.S && b.black(r - i * kRjDr[d], c - i * kRjDc[d]); ++i) ++n;
+    return n;
+}
+__device__ __noinline__ int rj_len_if_filled(RjBoard& b, int cell, int d) {     // `cell` is empty
+    b.set(cell);
+    const int n = rj_len(b, cell, d);
+    b.clear(cell);
+    return n;
+}
+__device__ __noinline__ bool rj_overline(const RjBoard& b, int a) {              // renju_is_overline :251-258
+    for (int d = 0; d < 4; ++d) if (rj_len(b, a, d) > 5) return true;
+    return false;
+}
+// count_renju_fours_at_action :260-436: per direction at most one four - a solid four that one more stone makes
+// exactly five, else four stones and a gap in a window of five whose gap makes exactly five, else a stone one gap
+// away (at distance 2-4) whose gap would join a run of three or more with room to extend.
+__device__ __noinline__ int rj_fours(RjBoard& b, int a) {
+    const int S = b.S, r = a / S, c = a - r * S;
+    int count = 0;
+    for (int d = 0; d < 4; ++d) {
+        const int dr = kRjDr[d], dc = kRjDc[d];
+        bool found = false;
+        for (int off = 0; off < 4 && !found; ++off) {
+            const int r0 = r - off * dr, c0 = c - off * dc;
+            bool solid = true;
+            for (int i = 0; i < 4; ++i) solid = solid && b.black(r0 + i * dr, c0 + i * dc);
+            if (!solid) continue;
+            const int rb = r0 - dr, cb = c0 - dc, ra = r0 + 4 * dr, ca = c0 + 4 * dc;
+            bool five = false;
+            if (b.empty(rb, cb) && rj_len_if_filled(b, rb * S + cb, d) == 5) five = true;
+            if (!five && b.empty(ra, ca) && rj_len_if_filled(b, ra * S + ca, d) == 5) five = true;
+            found = five;
+        }
+        for (int off = 0; off < 5 && !found; ++off) {
+            const int r0 = r - off * dr, c0 = c - off * dc;
+            int stones = 0, empties = 0, gap = -1;
+            bool valid = true;
+            for (int i = 0; i < 5 && valid; ++i) {
+                const int rk = r0 + i * dr, ck = c0 + i * dc;
+                if (!b.in(rk, ck)) { valid = false; break; }
+                if (b.black(rk, ck)) ++stones;
+                else if (b.empty(rk, ck)) { ++empties; gap = rk * S + ck; }
+                else valid = false;
+            }
+            if (valid && stones == 4 && empties == 1 && rj_len_if_filled(b, gap, d) == 5) found = true;
+        }
+        for (int dist = 2; dist <= 4 && !found; ++dist) {
+            const int rf = r + dist * dr, cf = c + dist * dc;
+            if (b.black(rf, cf)) {
+                const int rg = r + (dist - 1) * dr, cg = c + (dist - 1) * dc;
+                if (b.empty(rg, cg) && rj_len_if_filled(b, rg * S + cg, d) >= 3 &&
+                    (b.empty(r - dr, c - dc) || b.empty(rf + dr, cf + dc))) { found = true; break; }
+            }
+            const int rk = r - dist * dr, ck = c - dist * dc;
+            if (b.black(rk, ck)) {
+                const int rg = r - (dist - 1) * dr, cg = c - (dist - 1) * dc;
+                if (b.empty(rg, cg) && rj_len_if_filled(b, rg * S + cg, d) >= 3 &&
+                    (b.empty(rk - dr, ck - dc) || b.empty(r + dr, c + dc))) { found = true; break; }
+            }
+        }
+        count += found;
+    }
+    return count;
+}
+template <int DEPTH> __device__ bool rj_double_three(RjBoard& b, int a);
+// A triple of consecutive black stones from (r0, c0) along d is a "three" (is_renju_three_definition :580-635) when
+// a stone on one of its two empty end extensions gives a straight four (both ends empty, :637-676) that is itself
+// allowed (no overline, no double four, no double three) and makes no five or more.
+template <int DEPTH>
+__device__ bool rj_three(RjBoard& b, int r0, int c0, int d) {
+    const int dr = kRjDr[d], dc = kRjDc[d], S = b.S;
+    for (int e = 0; e < 2; ++e) {
+        const int rs = e == 0 ? r0 - dr : r0 + 3 * dr, cs = e == 0 ? c0 - dc : c0 + 3 * dc;
+        if (!b.empty(rs, cs)) continue;
+        const int spot = rs * S + cs;
+        b.set(spot);
+        const int rf = e == 0 ? rs : r0, cf = e == 0 ? cs : c0;       // first stone of the four
+        bool ok = b.empty(rf - dr, cf - dc) && b.empty(rf + 4 * dr, cf + 4 * dc);
+        if (ok && (rj_overline(b, spot) || rj_fours(b, spot) >= 2 || rj_double_three<DEPTH + 1>(b, spot))) ok = false;
+        if (ok)
+            for (int d2 = 0; d2 < 4; ++d2)
+                if (rj_len(b, spot, d2) >= 5) { ok = false; break; }
+        b.clear(spot);
+        if (ok) return true;
+    }
+    return false;
+}
+// check_renju_double_three_recursive :460-578: two or more threes through the stone on `a`.  (The reference then
+// counts how many of them can be taken to an allowed straight four and lets the move pass when at most one can;
+// that count repeats the test that made each of them a three, so it equals the number of threes.)
+template <int DEPTH>
+__device__ bool rj_double_three(RjBoard& b, int a) {
+    if constexpr (DEPTH > kRenjuDepth) {
+        return false;
+    } else {
+        const int S = b.S, r = a / S, c = a - r * S;
+        int threes = 0;
+        for (int d = 0; d < 4; ++d)
+            for (int off = 0; off < 3; ++off) {
+                const int r0 = r - off * kRjDr[d], c0 = c - off * kRjDc[d];
+                bool all = true;
+                for (int k = 0; k < 3; ++k) all = all && b.black(r0 + k * kRjDr[d], c0 + k * kRjDc[d]);
+                if (all && rj_three<DEPTH>(b, r0, c0, d)) ++threes;
+            }
+        return threes >= 2;
+    }
+}
+// is_black_renju_forbidden :200-249 for an empty cell
+__device__ bool renju_forbidden(const uint32_t* black, const uint32_t* empty0, int S, int cell) {
+    RjBoard b;
+    for (int w = 0; w < 8; ++w) b.bk[w] = black[w];
+    b.empty0 = empty0; b.S = S;
+    b.set(cell);
+    bool exact_five = false, over = false;
+    for (int d = 0; d < 4; ++d) {
+        const int n = rj_len(b, cell, d);
+        exact_five = exact_five || n == 5;
+        over = over || n > 5;
+    }
+    if (exact_five && !over) return false;
+    if (over) return true;
+    if (rj_fours(b, cell) >= 2) return true;
+    return rj_double_three<0>(b, cell);
+}
 // One warp: legal <- empty minus the cells the rules deny the side to move (8 words, shared memory).
 __device__ void legal_moves_warp(const uint32_t* black, const uint32_t* empty, uint32_t* legal, int S, int mask_words,
                                  int rules, bool black_to_move, int lane) {
     if (lane < 8) legal[lane] = lane < mask_words ? empty[lane] : 0u;
     __syncwarp();
-    if (rules == OB200_RULES_OMOK && black_to_move)
+    if (rules != OB200_RULES_FREESTYLE && black_to_move)
         for (int cell = lane; cell < S * S; cell += 32)
-            if (((empty[cell >> 5] >> (cell & 31)) & 1u) && omok_forbidden(black, empty, S, cell))
+            if (((empty[cell >> 5] >> (cell & 31)) & 1u) &&
+                (rules == OB200_RULES_OMOK ? omok_forbidden(black, empty, S, cell) : renju_forbidden(black, empty, S, cell)))
                 atomicAnd(&legal[cell >> 5], ~(1u << (cell & 31)));
     __syncwarp();
 }
@@ -242,7 +397,7 @@ __global__ void leaf_prepare_kernel(const int32_t* __restrict__ paths, const int
                                     const uint8_t* __restrict__ root_nh, const uint8_t* __restrict__ root_tm,
                                     const int32_t* __restrict__ root_count, int16_t* __restrict__ leaf_hist,
                                     uint8_t* __restrict__ leaf_nh, uint8_t* __restrict__ leaf_tm,
-                                    float* __restrict__ term_value, int32_t* term_count) {
+                                    float* __restrict__ term_value, int32_t* term_count, int rules) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_sims) return;
     const int tree = i / sims_per_tree;
@@ -276,13 +431,16 @@ __global__ void leaf_prepare_kernel(const int32_t* __restrict__ paths, const int
             return false;
         };
         const int dr[4] = {0, 1, 1, 1}, dc[4] = {1, 0, 1, -1};
-        bool win = false;
-        for (int dir = 0; dir < 4 && !win; ++dir) {
+        // five or more wins; under Renju BLACK needs exactly five and no longer line through the stone
+        // (GomokuState::refresh_winner_cache, src/games/gomoku/gomoku_state.cpp:812-860)
+        bool five_up = false, exact = false, over = false;
+        for (int dir = 0; dir < 4; ++dir) {
             int run = 1;
-            for (int k = 1; k < 5 && has(r0 + k * dr[dir], c0 + k * dc[dir]); ++k) ++run;
-            for (int k = 1; k < 5 && has(r0 - k * dr[dir], c0 - k * dc[dir]); ++k) ++run;
-            win = run >= 5;
+            for (int k = 1; k < 6 && has(r0 + k * dr[dir], c0 + k * dc[dir]); ++k) ++run;
+            for (int k = 1; k < 6 && has(r0 - k * dr[dir], c0 - k * dc[dir]); ++k) ++run;
+            five_up = five_up || run >= 5; exact = exact || run == 5; over = over || run > 5;
         }
+        const bool win = (rules == OB200_RULES_RENJU && mover == 1) ? (exact && !over) : five_up;
         if (win) tv = -1.0f;                                    // the side to move has lost
         else if (root_count[tree] + len >= S * S) tv = 0.0f;    // full board
     }
@@ -538,8 +696,6 @@ int ob200_search_create(ob200_net* net, const ob200_search_config* cfg, ob200_se
         return set_error(OB200_ERR_INVALID,
                          "ob200_search_create: need leaf_batch a multiple of n_trees and <= the network's max_batch (%d), max_depth in [1,%d], value_sign +-1",
                          nc->max_batch, kMaxDepth);
-    if (cfg->rules == OB200_RULES_RENJU)
-        return set_error(OB200_ERR_UNSUPPORTED, "ob200_search_create: Renju's forbidden moves are not built; freestyle and Omok are");
     OB200_CUDA_OK(cudaSetDevice(nc->device));
     if (int rc = require_device()) return rc;
     ob200_search* s = new ob200_search;
@@ -750,7 +906,7 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
         leaf_prepare_kernel<<<(L + 127) / 128, 128, 0, st>>>(s->paths, s->path_len, L, s->sims_per_round, c.max_depth, S,
                                                             s->root_stones, s->root_hist, s->root_nh, s->root_tm,
                                                             s->root_count, s->leaf_hist, s->leaf_nh, s->leaf_tm,
-                                                            s->term_value, s->term_count);
+                                                            s->term_value, s->term_count, c.rules);
         OB200_LAUNCHED("leaf_prepare_kernel");
         if (int rc = net_forward_gomoku_for_search(s->net, s->leaf_hist, s->leaf_nh, s->leaf_tm, L, s->policy, s->value, st)) return rc;
         if (s->rec_policy && r < s->rec_rounds) {

@@ -361,10 +361,12 @@ def gomoku_attack_defense(stones, to_move, board_size=15, stone_placed=False):
     return att, dfn
 
 
-def gomoku_result(moves, board_size=15):
-    """0 ongoing, 1 BLACK won, 2 WHITE won, 3 draw, judged on the last move (freestyle rules)."""
+def gomoku_result(moves, board_size=15, rules=0):
+    """0 ongoing, 1 BLACK won, 2 WHITE won, 3 draw, judged on the last move (rules 2: Renju's exact five for BLACK)."""
     mv = np.ascontiguousarray(moves, np.int16)
-    return int(lib().oracle_gomoku_result(mv, len(mv), board_size))
+    L = lib()
+    L.oracle_gomoku_result_rules.argtypes = [_i16, C.c_int, C.c_int, C.c_int]
+    return int(L.oracle_gomoku_result_rules(mv, len(mv), board_size, rules))
 
 
 # ---- the reference's own classes (oracle/_ref) --------------------------------
@@ -520,6 +522,15 @@ def ref_gomoku_legal_moves(moves, board_size=15, renju=False, omok=False):
 def ref_gomoku_result(moves, board_size=15):
     mv = np.ascontiguousarray(moves, np.int32)
     return int(ref_tree().ref_gomoku_result(board_size, mv, len(mv)))
+
+
+def ref_gomoku_result_variant(moves, board_size=15, renju=False, omok=False):
+    """The result GomokuState(variant flags) reports after `moves`, played without legality checks."""
+    mv = np.ascontiguousarray(moves, np.int32)
+    L = ref_tree()
+    L.ref_gomoku_result_variant.argtypes = [C.c_int, _i32, C.c_int, C.c_int, C.c_int]
+    L.ref_gomoku_result_variant.restype = C.c_int
+    return int(L.ref_gomoku_result_variant(board_size, mv, len(mv), int(renju), int(omok)))
 
 
 def ref_gomoku_encode_batch(move_lists, board_size=15, threads=0):

@@ -237,7 +237,9 @@ void oracle_gomoku_encode_batch(const int16_t* history, const uint8_t* n_hist,
  * GomokuRules::is_five_in_a_row(action, player, allow_overline = true) for freestyle
  * (src/games/gomoku/gomoku_rules.cpp:71-100: a line of length >= 5 through the stone in
  * any of 4 directions); isTerminal (:131-156) adds the stalemate of a full board. */
-int oracle_gomoku_result(const int16_t* moves, int n, int S) {
+/* rules 2 (Renju): BLACK wins only with a line of exactly five through the stone and no longer one
+ * (refresh_winner_cache :812-843); WHITE, and both sides under the other rules, with five or more. */
+int oracle_gomoku_result_rules(const int16_t* moves, int n, int S, int rules) {
     signed char board[32 * 32];
     memset(board, 0, sizeof(board));
     for (int i = 0; i < n; ++i) board[moves[i]] = (signed char)(1 + (i & 1));
@@ -245,6 +247,7 @@ int oracle_gomoku_result(const int16_t* moves, int n, int S) {
     const int last = moves[n - 1], who = board[last];
     const int r0 = last / S, c0 = last % S;
     static const int DR[4] = {1, 0, 1, 1}, DC[4] = {0, 1, 1, -1};
+    int five_up = 0, exact = 0, over = 0;
     for (int d = 0; d < 4; ++d) {
         int len = 1;
         for (int k = 1;; ++k) {
@@ -257,10 +260,12 @@ int oracle_gomoku_result(const int16_t* moves, int n, int S) {
             if (r < 0 || r >= S || c < 0 || c >= S || board[r * S + c] != who) break;
             ++len;
         }
-        if (len >= 5) return who;
+        five_up = five_up || len >= 5; exact = exact || len == 5; over = over || len > 5;
     }
+    if ((rules == 2 && who == 1) ? (exact && !over) : five_up) return who;
     return n >= S * S ? 3 : 0;
 }
+int oracle_gomoku_result(const int16_t* moves, int n, int S) { return oracle_gomoku_result_rules(moves, n, S, 0); }
 
 /* Go planes, as GoState::getEnhancedTensorRepresentation (src/games/go/go_state.cpp:596-704)
  * with the CPU code of computeAttackDefensePlanes (:1306-1476).  Inputs are what the state
@@ -498,9 +503,159 @@ int oracle_omok_forbidden(const int8_t* board, int S, int action) {
 #undef OB_EMPTY
     return open_threes >= 2;
 }
+/* ---------------------------------------------------------------------------------------------
+ * Renju: BLACK's forbidden moves.  GomokuRules::is_black_renju_forbidden and what it calls,
+ * src/games/gomoku/gomoku_rules.cpp:200-879, restated on a board array (0 empty, 1 black, 2 white) that
+ * already holds BLACK's stone on the cell under test; hypothetical further stones are set and cleared in
+ * place where the reference wraps its board accessor in another lambda.
+ * ------------------------------------------------------------------------------------------- */
+static const int RJ_DR[4] = {1, 0, 1, 1}, RJ_DC[4] = {0, 1, 1, -1};
+#define RJ_IN(S, r, c) ((r) >= 0 && (r) < (S) && (c) >= 0 && (c) < (S))
+static int rj_black(const int8_t* b, int S, int r, int c) { return RJ_IN(S, r, c) && b[r * S + c] == 1; }
+static int rj_empty(const int8_t* b, int S, int r, int c) { return RJ_IN(S, r, c) && b[r * S + c] == 0; }
+/* get_line_length_at_action (:38-69): BLACK's run through a cell that holds a black stone, else 0 */
+static int rj_len(const int8_t* b, int S, int a, int d) {
+    const int r = a / S, c = a % S;
+    if (b[a] != 1) return 0;
+    int n = 1;
+    for (int i = 1; i < S && rj_black(b, S, r + i * RJ_DR[d], c + i * RJ_DC[d]); ++i) ++n;
+    for (int i = 1; i < S && rj_black(b, S, r - i * RJ_DR[d], c - i * RJ_DC[d]); ++i) ++n;
+    return n;
+}
+static int rj_len_if_filled(int8_t* b, int S, int cell, int d) {      /* the run through `cell` with a black stone put there */
+    const int8_t keep = b[cell];
+    b[cell] = 1;
+    const int n = rj_len(b, S, cell, d);
+    b[cell] = keep;
+    return n;
+}
+static int rj_overline(const int8_t* b, int S, int a) {               /* renju_is_overline :251-258 */
+    for (int d = 0; d < 4; ++d) if (rj_len(b, S, a, d) > 5) return 1;
+    return 0;
+}
+/* count_renju_fours_at_action :260-436: per direction at most one four - a solid four that one more stone makes
+ * exactly five, else four stones and a gap in a window of five whose gap makes exactly five, else a stone one
+ * gap away (at distance 2-4) whose gap would join a run of three or more with room to extend. */
+static int rj_fours(int8_t* b, int S, int a) {
+    const int r = a / S, c = a % S;
+    int count = 0;
+    for (int d = 0; d < 4; ++d) {
+        const int dr = RJ_DR[d], dc = RJ_DC[d];
+        int found = 0;
+        for (int off = 0; off < 4 && !found; ++off) {
+            const int r0 = r - off * dr, c0 = c - off * dc;
+            int solid = 1;
+            for (int i = 0; i < 4; ++i) solid = solid && rj_black(b, S, r0 + i * dr, c0 + i * dc);
+            if (!solid) continue;
+            const int rb = r0 - dr, cb = c0 - dc, ra = r0 + 4 * dr, ca = c0 + 4 * dc;
+            const int open_before = rj_empty(b, S, rb, cb), open_after = rj_empty(b, S, ra, ca);
+            int five = 0;
+            if (open_before && rj_len_if_filled(b, S, rb * S + cb, d) == 5) five = 1;
+            if (!five && open_after && rj_len_if_filled(b, S, ra * S + ca, d) == 5) five = 1;
+            if (five) found = 1;
+        }
+        for (int off = 0; off < 5 && !found; ++off) {
+            const int r0 = r - off * dr, c0 = c - off * dc;
+            int stones = 0, empties = 0, gap = -1, valid = 1;
+            for (int i = 0; i < 5 && valid; ++i) {
+                const int rk = r0 + i * dr, ck = c0 + i * dc;
+                if (!RJ_IN(S, rk, ck)) { valid = 0; break; }
+                if (b[rk * S + ck] == 1) ++stones;
+                else if (b[rk * S + ck] == 0) { ++empties; gap = rk * S + ck; }
+                else valid = 0;
+            }
+            if (valid && stones == 4 && empties == 1 && rj_len_if_filled(b, S, gap, d) == 5) found = 1;
+        }
+        for (int dist = 2; dist <= 4 && !found; ++dist) {
+            const int rf = r + dist * dr, cf = c + dist * dc;
+            if (rj_black(b, S, rf, cf)) {
+                const int rg = r + (dist - 1) * dr, cg = c + (dist - 1) * dc;
+                if (rj_empty(b, S, rg, cg) && rj_len_if_filled(b, S, rg * S + cg, d) >= 3 &&
+                    (rj_empty(b, S, r - dr, c - dc) || rj_empty(b, S, rf + dr, cf + dc))) { found = 1; break; }
+            }
+            const int rk = r - dist * dr, ck = c - dist * dc;
+            if (rj_black(b, S, rk, ck)) {
+                const int rg = r - (dist - 1) * dr, cg = c - (dist - 1) * dc;
+                if (rj_empty(b, S, rg, cg) && rj_len_if_filled(b, S, rg * S + cg, d) >= 3 &&
+                    (rj_empty(b, S, rk - dr, ck - dc) || rj_empty(b, S, r + dr, c + dc))) { found = 1; break; }
+            }
+        }
+        count += found;
+    }
+    return count;
+}
+static int rj_depth_hits = 0;                                        /* how often the depth limit below cut a recursion */
+static int rj_depth_seen = 0;                                        /* deepest recursion so far */
+int oracle_renju_depth_hits(void) { return rj_depth_hits; }
+int oracle_renju_depth_seen(void) { return rj_depth_seen; }
+enum { RJ_MAX_DEPTH = 6 };
+static int rj_double_three(int8_t* b, int S, int a, int depth);
+/* A triple of consecutive black stones starting at (r0, c0) along d is a "three" (is_renju_three_definition
+ * :580-635) when one of its two end extensions is empty and putting a stone there gives a straight four (four in
+ * a row with both ends empty, :637-676) that is itself allowed (no overline, no double four, no double three -
+ * check_s4_forbidden_primary :472-484 and the checker it is given, :449-456) and makes no five or more. */
+static int rj_three(int8_t* b, int S, int r0, int c0, int d, int depth) {
+    const int dr = RJ_DR[d], dc = RJ_DC[d];
+    const int ext[2][2] = {{r0 - dr, c0 - dc}, {r0 + 3 * dr, c0 + 3 * dc}};
+    for (int e = 0; e < 2; ++e) {
+        const int rs = ext[e][0], cs = ext[e][1];
+        if (!rj_empty(b, S, rs, cs)) continue;
+        const int spot = rs * S + cs;
+        b[spot] = 1;
+        /* the four: the triple plus the spot */
+        const int rf = e == 0 ? rs : r0, cf = e == 0 ? cs : c0;      /* first stone of the four */
+        int ok = rj_empty(b, S, rf - dr, cf - dc) && rj_empty(b, S, rf + 4 * dr, cf + 4 * dc);
+        if (ok && (rj_overline(b, S, spot) || rj_fours(b, S, spot) >= 2 || rj_double_three(b, S, spot, depth + 1))) ok = 0;
+        if (ok)
+            for (int d2 = 0; d2 < 4; ++d2)
+                if (rj_len(b, S, spot, d2) >= 5) { ok = 0; break; }
+        b[spot] = 0;
+        if (ok) return 1;
+    }
+    return 0;
+}
+/* check_renju_double_three_recursive :460-578: the threes through the stone on `a`; fewer than two: allowed.  With
+ * two or more the reference then asks how many of them can be taken to an allowed straight four
+ * (check_renju_double_three_exception_recursive :678-745) and lets the move pass when at most one can - which is
+ * the very test that made each of them a three, so the count equals the number of threes; it is restated as the
+ * reference states it all the same. */
+static int rj_double_three(int8_t* b, int S, int a, int depth) {
+    if (depth > RJ_MAX_DEPTH) { ++rj_depth_hits; return 0; }
+    if (depth > rj_depth_seen) rj_depth_seen = depth;
+    const int r = a / S, c = a % S;
+    int threes = 0, resolvable = 0;
+    int tr[12], tc[12], td[12];
+    for (int d = 0; d < 4; ++d)
+        for (int off = 0; off < 3; ++off) {
+            const int r0 = r - off * RJ_DR[d], c0 = c - off * RJ_DC[d];
+            int all = 1;
+            for (int k = 0; k < 3; ++k) all = all && rj_black(b, S, r0 + k * RJ_DR[d], c0 + k * RJ_DC[d]);
+            if (all && rj_three(b, S, r0, c0, d, depth)) { tr[threes] = r0; tc[threes] = c0; td[threes] = d; ++threes; }
+        }
+    if (threes < 2) return 0;
+    for (int t = 0; t < threes; ++t) resolvable += rj_three(b, S, tr[t], tc[t], td[t], depth);
+    return resolvable <= 1 ? 0 : 1;
+}
+/* is_black_renju_forbidden :200-249 for an empty cell of `board` */
+int oracle_renju_forbidden(const int8_t* board, int S, int action) {
+    int8_t b[32 * 32];
+    memcpy(b, board, (size_t)S * S);
+    b[action] = 1;
+    int exact_five = 0, over = 0;
+    for (int d = 0; d < 4; ++d) {
+        const int n = rj_len(b, S, action, d);
+        exact_five = exact_five || n == 5;
+        over = over || n > 5;
+    }
+    if (exact_five && !over) return 0;
+    if (over) return 1;
+    if (rj_fours(b, S, action) >= 2) return 1;
+    return rj_double_three(b, S, action, 0);
+}
+
 /* The legal moves of a Gomoku position (GomokuState::is_move_valid_internal, src/games/gomoku/gomoku_state.cpp:
  * 915-943, without the opening restriction): the empty cells, minus BLACK's forbidden ones under Omok (rules 1)
- * when BLACK is to move.  legal_out: one bit per cell, mask_words words. */
+ * or Renju (rules 2) when BLACK is to move.  legal_out: one bit per cell, mask_words words. */
 void oracle_gomoku_legal_mask(const int16_t* moves, int n_moves, int S, int rules, uint32_t* legal_out, int mask_words) {
     int8_t board[32 * 32];
     memset(board, 0, sizeof board);
@@ -510,6 +665,7 @@ void oracle_gomoku_legal_mask(const int16_t* moves, int n_moves, int S, int rule
     for (int a = 0; a < S * S; ++a) {
         if (board[a]) continue;
         if (rules == 1 && black_to_move && oracle_omok_forbidden(board, S, a)) continue;
+        if (rules == 2 && black_to_move && oracle_renju_forbidden(board, S, a)) continue;
         legal_out[a >> 5] |= 1u << (a & 31);
     }
 }
@@ -578,7 +734,7 @@ void oracle_search_expand_widen(int32_t* N, float* W, float* P, int32_t* VL, uin
         int term = 0;
         float tv = 0.0f;
         if (len > 0) {
-            const int res = oracle_gomoku_result(game, n0 + len, S);
+            const int res = oracle_gomoku_result_rules(game, n0 + len, S, rules);
             if (res == 1 || res == 2) { term = 1; tv = -1.0f; }   /* the last mover won: the side to move has lost */
             else if (res == 3) { term = 2; tv = 0.0f; }
         }

@@ -199,6 +199,22 @@ int ref_gomoku_result(int board_size, const int32_t* moves, int n_moves) {
     }
 }
 
+// The same on a state constructed with the variant flags; the moves are played without asking isLegalMove, so that
+// a line longer than five by BLACK can be put on the board.
+int ref_gomoku_result_variant(int board_size, const int32_t* moves, int n_moves, int use_renju, int use_omok) {
+    alphazero::games::gomoku::GomokuState st(board_size, use_renju != 0, use_omok != 0, 0, false);
+    for (int i = 0; i < n_moves; ++i) {
+        try { st.makeMove(moves[i]); } catch (...) { return -1; }
+    }
+    if (!st.isTerminal()) return 0;
+    switch (st.getGameResult()) {
+        case GameResult::WIN_PLAYER1: return 1;
+        case GameResult::WIN_PLAYER2: return 2;
+        case GameResult::DRAW: return 3;
+        default: return 0;
+    }
+}
+
 // Real GoState (Chinese rules, positional superko as the constructor's defaults): play
 // `n_moves` actions (cell index y*S+x, or -1 for a pass) from the empty board, then export what a
 // device encoder takes (stones 0/1/2, ko point or -1, side to move, legal cells as bytes; the

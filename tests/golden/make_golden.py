@@ -21,6 +21,8 @@ the inputs' checksums and the reference's outputs:
                      fours (`make_golden.py attack_defense`)
   omok_golden.npz    GomokuState(use_omok) legal moves after seeded play that keeps to the centre, so that
                      six-in-a-row and double-three cells occur (`make_golden.py omok`)
+  renju_golden.npz   the same for GomokuState(use_renju): overlines, double fours, double threes, and the
+                     state's result (BLACK wins with exactly five only) (`make_golden.py renju`)
   net_golden.npz     ResNetModel::forward (log-softmax policy, value): (a) a tiny
                      model with the reference's own libtorch default
                      initialisation, its weights stored here rounded to fp16
@@ -161,13 +163,13 @@ def make_attack_defense():
                         compute_planes_nonzero=np.array(planes_nonzero))
 
 
-def make_omok():
-    rng = np.random.default_rng(2025)
+def make_variant(name, renju, omok, seed):
+    rng = np.random.default_rng(seed)
     games, masks, forbidden = [], [], 0
     while len(games) < 64:
         moves = []
         for _ in range(int(rng.integers(8, 70))):
-            legal = capi.ref_gomoku_legal_moves(moves, 15, False, True)
+            legal = capi.ref_gomoku_legal_moves(moves, 15, renju, omok)
             cand = np.nonzero(legal)[0]
             if len(cand) == 0 or (moves and capi.ref_gomoku_result(moves, 15) != 0):
                 break
@@ -175,7 +177,7 @@ def make_omok():
             moves.append(int(rng.choice(near if near and rng.random() < 0.85 else cand)))
         if moves and capi.ref_gomoku_result(moves, 15) != 0:
             moves.pop()
-        legal = capi.ref_gomoku_legal_moves(moves, 15, False, True)
+        legal = capi.ref_gomoku_legal_moves(moves, 15, renju, omok)
         empty = np.ones(225, bool)
         empty[moves] = False
         n_forbidden = int((empty & ~legal).sum())
@@ -186,8 +188,16 @@ def make_omok():
         masks.append(legal)
     flat = np.concatenate([np.asarray(g, np.int16) for g in games])
     ptr = np.cumsum([0] + [len(g) for g in games])
-    np.savez_compressed(os.path.join(HERE, "omok_golden.npz"), moves=flat, row_ptr=ptr, legal_bits=np.packbits(np.array(masks)),
+    np.savez_compressed(os.path.join(HERE, name), moves=flat, row_ptr=ptr, legal_bits=np.packbits(np.array(masks)),
                         forbidden_cells=np.array(forbidden))
+
+
+def make_omok():
+    make_variant("omok_golden.npz", False, True, 2025)
+
+
+def make_renju():
+    make_variant("renju_golden.npz", True, False, 2026)
 
 
 if __name__ == "__main__":
@@ -202,6 +212,9 @@ if __name__ == "__main__":
     if sys.argv[1:] == ["omok"]:
         make_omok()
         sys.exit(0)
+    if sys.argv[1:] == ["renju"]:
+        make_renju()
+        sys.exit(0)
     if sys.argv[1:] == ["attack_defense"]:
         make_attack_defense()
         sys.exit(0)
@@ -213,5 +226,6 @@ if __name__ == "__main__":
     make_chess()
     make_attack_defense()
     make_omok()
+    make_renju()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -437,9 +437,10 @@ def test_attack_defense_live_against_the_reference_module(oracle):
         assert not a.any() and not d.any()
 
 
-def load_omok_golden():
-    """(games, legal [n, 225] bool) from omok_golden.npz: GomokuState(use_omok)'s legal moves after seeded play."""
-    g = np.load(os.path.join(GOLD, "omok_golden.npz"))
+def load_omok_golden(name="omok_golden.npz"):
+    """(games, legal [n, 225] bool) from omok_golden.npz / renju_golden.npz: the legal moves of the reference's
+    GomokuState constructed with use_omok / use_renju, after seeded play."""
+    g = np.load(os.path.join(GOLD, name))
     ptr = g["row_ptr"]
     games = [g["moves"][ptr[i]:ptr[i + 1]].astype(np.int64).tolist() for i in range(len(ptr) - 1)]
     legal = np.unpackbits(g["legal_bits"])[:len(games) * 225].reshape(len(games), 225).astype(bool)
@@ -486,3 +487,53 @@ def test_omok_legal_moves_live_against_gomokustate(oracle):
         for cut in (len(mv), len(mv) - 1, len(mv) // 2):
             want = oracle.ref_gomoku_legal_moves(mv[:cut], 15, renju=False, omok=True)
             assert want is not None and np.array_equal(_legal_of(oracle.gomoku_legal_mask(mv[:cut], 15, rules=1)), want)
+
+
+def test_renju_legal_moves_match_reference_golden(oracle):
+    """BLACK's forbidden moves under Renju (overline, double four, double three, as the reference defines them)
+    against the legal moves of the reference's GomokuState constructed with use_renju; the recursion limit of the
+    restatement is never reached; and the win rule: BLACK needs exactly five."""
+    import ctypes as C
+    games, legal = load_omok_golden("renju_golden.npz")
+    forbidden = 0
+    for mv, want in zip(games, legal):
+        got = _legal_of(oracle.gomoku_legal_mask(mv, 15, rules=2))
+        assert np.array_equal(got, want), mv
+        empty = np.ones(225, bool)
+        empty[mv] = False
+        forbidden += int((empty & ~got).sum())
+    assert forbidden >= 500
+    L = oracle.lib()
+    L.oracle_renju_depth_hits.restype = C.c_int
+    assert L.oracle_renju_depth_hits() == 0
+    # the gap of X X X _ X X would make six: forbidden under Renju; an exact five is allowed
+    black = [7 * 15 + c for c in (2, 3, 4, 6, 7)]
+    white = [0, 14, 210, 224, 1]
+    mv = [m for pair in zip(black, white) for m in pair]
+    assert not _legal_of(oracle.gomoku_legal_mask(mv, 15, rules=2))[7 * 15 + 5]
+    assert oracle.gomoku_result(mv + [7 * 15 + 5], 15, rules=2) == 0 and oracle.gomoku_result(mv + [7 * 15 + 5], 15, rules=0) == 1
+    black = [7 * 15 + c for c in (3, 4, 6, 7)]
+    mv = [m for pair in zip(black, white[:4]) for m in pair]
+    assert _legal_of(oracle.gomoku_legal_mask(mv, 15, rules=2))[7 * 15 + 5]
+    assert oracle.gomoku_result(mv + [7 * 15 + 5], 15, rules=2) == 1
+    # WHITE wins with six under Renju
+    white6 = [7 * 15 + c for c in (2, 3, 4, 6, 7, 5)]
+    black6 = [0, 14, 210, 224, 1, 16]
+    assert oracle.gomoku_result([m for pair in zip(black6, white6) for m in pair], 15, rules=2) == 2
+
+
+def test_renju_live_against_gomokustate(oracle):
+    _need_ref(oracle, "tree")
+    games, _ = load_omok_golden("renju_golden.npz")
+    for mv in games[:24]:
+        for cut in (len(mv), len(mv) - 1, len(mv) // 2):
+            want = oracle.ref_gomoku_legal_moves(mv[:cut], 15, renju=True, omok=False)
+            assert want is not None and np.array_equal(_legal_of(oracle.gomoku_legal_mask(mv[:cut], 15, rules=2)), want)
+    black = [7 * 15 + c for c in (3, 4, 6, 7)]
+    white = [0, 14, 210, 224]
+    mv = [m for pair in zip(black, white) for m in pair] + [7 * 15 + 5]
+    assert oracle.ref_gomoku_result_variant(mv, 15, renju=True) == oracle.gomoku_result(mv, 15, rules=2) == 1
+    white6 = [7 * 15 + c for c in (2, 3, 4, 6, 7, 5)]
+    black6 = [0, 14, 210, 224, 1, 16]
+    mv = [m for pair in zip(black6, white6) for m in pair]
+    assert oracle.ref_gomoku_result_variant(mv, 15, renju=True) == oracle.gomoku_result(mv, 15, rules=2) == 2

@@ -88,6 +88,9 @@ SEARCH_CASES = [
     # Omok: BLACK's forbidden moves are no children, at the roots and below
     ("omok", "omok", 16, 8, 12, True, 0.25, 1, {"rules": 1}),
     ("omok_widened", "omok", 8, 16, 8, False, 0.25, 1, {"rules": 1, "pw": (16.0, 0.5)}),
+    # Renju: overlines, double fours and double threes are no children of BLACK's nodes; BLACK wins with exactly five
+    ("renju", "renju", 16, 8, 12, True, 0.25, 1, {"rules": 2}),
+    ("renju_negamax", "renju", 8, 16, 8, False, 0.0, -1, {"rules": 2}),
 ]
 SEARCH_CASES = [c if len(c) == 9 else c + ({},) for c in SEARCH_CASES]
 
@@ -101,9 +104,9 @@ def test_search_equals_the_oracle_on_the_same_network_outputs(net, oracle, name,
     from omoknuni_small_b200 import capi
     if games == "four":
         games = [open_four()] * T
-    elif games == "omok":
+    elif games in ("omok", "renju"):
         from test_oracle import load_omok_golden
-        all_games, all_legal = load_omok_golden()
+        all_games, all_legal = load_omok_golden(games + "_golden.npz")
         black_to_move = [k for k, g in enumerate(all_games) if len(g) % 2 == 0]
         pick = (black_to_move + [k for k in range(len(all_games)) if k not in black_to_move])[:T]
         games, root_legal = [all_games[k] for k in pick], all_legal[pick]
@@ -128,7 +131,7 @@ def test_search_equals_the_oracle_on_the_same_network_outputs(net, oracle, name,
         n = ref["nodes"]
         assert dev["nodes"] == n == st["nodes"], (dev["nodes"], n)
         if limits.get("rules"):
-            # the roots' children are the legal moves of the reference's GomokuState(use_omok), or a subset of them
+            # the roots' children are the legal moves of the reference's GomokuState(use_omok / use_renju), or a subset
             for t in range(T):
                 kids = legal_of(dev["legal_bits"][t])
                 assert not (kids & ~root_legal[t]).any() and (target or np.array_equal(kids, root_legal[t]))
@@ -315,9 +318,8 @@ def test_search_argument_errors(net):
         capi.Search(net, n_trees=3, leaf_batch=64)                   # leaf_batch not a multiple of n_trees
     with pytest.raises(capi.Error):
         capi.Search(net, n_trees=64, leaf_batch=1024)                # beyond the network's max_batch (256)
-    with pytest.raises(capi.Error) as e:
-        capi.Search(net, n_trees=2, leaf_batch=8, rules=capi.RULES_RENJU)   # Renju's forbidden moves are not built
-    assert e.value.code == 5 and "Renju" in str(e.value)
+    with pytest.raises(capi.Error):
+        capi.Search(net, n_trees=2, leaf_batch=8, rules=3)           # no such rule set
     s = capi.Search(net, n_trees=2, sims_per_move=8, leaf_batch=8)
     with pytest.raises(capi.Error):
         s.run([[5, 5], [1]])                                         # a cell played twice
