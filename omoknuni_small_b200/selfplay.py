@@ -19,9 +19,11 @@ import numpy as np
 GAME_TYPE_GOMOKU = 3   # core::GameType::GOMOKU (reference include/core/igamestate.h:18-24)
 
 
-def gomoku_result(moves, board_size=15):
+def gomoku_result(moves, board_size=15, rules=0):
     """0 ongoing, 1 BLACK won, 2 WHITE won, 3 draw — judged on the last move, five
-    or more in a row wins (freestyle; reference src/games/gomoku/gomoku_rules.cpp:71-100)."""
+    or more in a row wins (reference src/games/gomoku/gomoku_rules.cpp:71-100); under Renju
+    (rules 2) BLACK needs exactly five and no longer line through the stone
+    (src/games/gomoku/gomoku_state.cpp:812-843)."""
     n = len(moves)
     if n == 0:
         return 0
@@ -32,6 +34,7 @@ def gomoku_result(moves, board_size=15):
     last = int(moves[-1])
     who = int(board[last])
     r0, c0 = divmod(last, S)
+    runs = []
     for dr, dc in ((1, 0), (0, 1), (1, 1), (1, -1)):
         run = 1
         for sgn in (1, -1):
@@ -40,8 +43,10 @@ def gomoku_result(moves, board_size=15):
                 run += 1
                 r += sgn * dr
                 c += sgn * dc
-        if run >= 5:
-            return who
+        runs.append(run)
+    won = (5 in runs and max(runs) == 5) if (rules == 2 and who == 1) else max(runs) >= 5
+    if won:
+        return who
     return 3 if n >= S * S else 0
 
 
@@ -91,7 +96,7 @@ class SelfPlay:
                     move = int(pi.argmax()) if temp < 0.01 else int(self.rng.choice(len(pi), p=pi / pi.sum()))
                     slots[t].append(move)
                     policies[t].append(pi.tolist())
-                    result = gomoku_result(slots[t], self.S)
+                    result = gomoku_result(slots[t], self.S, self.search.cfg.rules)
                     if result == 0 and len(slots[t]) >= self.max_moves:
                         result = 3
                 if result:
