@@ -456,7 +456,15 @@ def gpu_arm(args):
                 dtw.vl_revert(selw, 3)
         selw_loop()
         selw_ms = float(np.mean(timed(selw_loop, 3, per_iter_flush=False))) / 5
-        del dtw, tw
+        del dtw
+        # the same rows four times over (8,192 nodes, 617 MB per pass): the 2,048-node pass is a 35 us launch of which
+        # about 8 us are ramp-up and tail; this one shows the kernels' steady rate
+        tw4 = {k: (np.concatenate([v] * 4) if isinstance(v, np.ndarray) else v) for k, v in tw.items()}
+        dtw = capi.DeviceTree(tw4, dev)
+        selw = torch.empty(4 * SELW_NODES, dtype=torch.int32, device=dev)
+        selw_loop()
+        selw_big_ms = float(np.mean(timed(selw_loop, 3, per_iter_flush=False))) / 5
+        del dtw, tw, tw4
         # ---- leaf-parallel MCTS: 64 games, 800 simulations per move, leaf batch = B ----
         n_trees, sims = 64, 800
         openings, _, _, _ = synth.make_gomoku_games(n_trees, 15, seed=replicas.shard_seed(100, rank), max_moves=20)
@@ -504,11 +512,11 @@ def gpu_arm(args):
     parity = replicas.sum_counters(dist, {"selection_ranks_ok": sel_ok, "encode_ranks_ok": enc_ok}, dev)
 
     reduced = replicas.max_over_ranks(
-        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms, e2e_sync_s * 1e3, mcts_wall_ms] + [v for _, m, tm in sweep for v in (m, tm)] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
-    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms, e2e_sync_ms, mcts_wall_ms = reduced[:11]
-    sweep = [(bs, reduced[11 + 2 * i], reduced[12 + 2 * i]) for i, (bs, _, _) in enumerate(sweep)]
+        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms, e2e_sync_s * 1e3, mcts_wall_ms, selw_big_ms] + [v for _, m, tm in sweep for v in (m, tm)] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
+    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms, e2e_sync_ms, mcts_wall_ms, selw_big_ms = reduced[:12]
+    sweep = [(bs, reduced[12 + 2 * i], reduced[13 + 2 * i]) for i, (bs, _, _) in enumerate(sweep)]
     for i, wr in enumerate(wide):
-        wr["ms"], wr["conv_ms"] = reduced[11 + 2 * len(sweep) + 2 * i], reduced[12 + 2 * len(sweep) + 2 * i]
+        wr["ms"], wr["conv_ms"] = reduced[12 + 2 * len(sweep) + 2 * i], reduced[13 + 2 * len(sweep) + 2 * i]
     totals = replicas.sum_counters(dist, capi.counters(), dev)   # the only cross-GPU step: per-GPU counters summed
     if rank == 0:
         flops_eval = synth.net_flops_per_eval(15, 17, 64, NET["blocks"], 225, NET["policy_head_ch"], NET["value_head_ch"])
@@ -580,7 +588,11 @@ def gpu_arm(args):
                                         "value": SELW_NODES / (selw_ms * 1e-3), "unit": "node selections/s (select + VL apply + VL revert)",
                                         "kernel": "puct_select_segmented_kernel (256-slot segments through per-warp rings) + puct_select_finish_kernel",
                                         "achieved_gbs": synth.selection_bytes_per_node(SELW_CHILDREN) * SELW_NODES / (selw_ms * 1e-3) / 1e9,
-                                        "frac_of_hbm": synth.selection_bytes_per_node(SELW_CHILDREN) * SELW_NODES / (selw_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}},
+                                        "frac_of_hbm": synth.selection_bytes_per_node(SELW_CHILDREN) * SELW_NODES / (selw_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                        # the same pass over four times the nodes (617 MB): the kernels' steady rate
+                                        "at_8192_nodes": {"ms_per_pass": selw_big_ms,
+                                                          "achieved_gbs": synth.selection_bytes_per_node(SELW_CHILDREN) * 4 * SELW_NODES / (selw_big_ms * 1e-3) / 1e9,
+                                                          "frac_of_hbm": synth.selection_bytes_per_node(SELW_CHILDREN) * 4 * SELW_NODES / (selw_big_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}}},
             "mcts": {"value": world * mcts_sims / (mcts_ms * 1e-3), "unit": "simulations/s",
                      # the same simulations over the wall clock around ob200_search_run (root set-up, noise sampling,
                      # copies, the wait and the read-back of the visit counts included)

@@ -165,7 +165,8 @@ __device__ __forceinline__ void bracket(int n, float w, float p, int vl, float e
     hi = legal ? fmaf(kBracket, m, s) : -INFINITY;
 }
 
-constexpr int kWideMinPitch = 1024;
+constexpr int kWideMinPitch = 1024;          // rows at least this wide always take the segmented kernel
+constexpr long long kSegMinItems = 24576;    // narrower rows (257-1,023 slots) take it from this many segments on
 
 // ---------------------------------------------------------------------------
 // Staged variant for rows of up to 256 slots: a persistent grid, every warp
@@ -819,8 +820,10 @@ int ob200_launch_puct_select(const ob200_tree_view* tree, const int32_t* node_id
         puct_select_staged_kernel<<<want < sms ? want : sms, kStagedWarps * 32, smem, as_stream(stream)>>>(
             *tree, node_ids, n, c_puct, vl_value, apply_vl, sel_out, errw);
         OB200_LAUNCHED("puct_select_staged_kernel");
-    } else if (tree->pitch >= kWideMinPitch) {
-        // chess-wide rows: segments of 256 slots through the staged design, a counter and a (score, slot) pair per
+    } else if (tree->pitch >= kWideMinPitch ||
+               (tree->pitch > kStagedMaxPitch && (long long)n * ((tree->pitch + kSegSlots - 1) / kSegSlots) >= kSegMinItems)) {
+        // wide rows (chess: 4,672; Go's 362 in large launches: 16,384 x 362 takes 28.4 us against 33.9 us with a
+        // warp per node, 4,096 x 512 17.5 us against 13.5 us): segments of 256 slots through the staged design, a (score, slot) word per
         // segment as scratch, allocated and freed in stream order
         int dev = 0, sms = 0;
         OB200_CUDA_OK(cudaGetDevice(&dev));
