@@ -214,6 +214,9 @@ puct_select_staged_kernel(ob200_tree_view t, const int32_t* __restrict__ node_id
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
+    // launched as a programmatic dependent: the set-up above may run while the kernel ahead in the stream (the
+    // previous pass's revert) finishes; its writes are visible from here on
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // a kernel launched behind this one with programmatic stream serialization (the virtual-loss revert) may be
     // scheduled from now on; it waits for this grid's completion before it reads anything
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -402,6 +405,9 @@ puct_select_segmented_kernel(ob200_tree_view t, const int32_t* __restrict__ node
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
+    // launched as a programmatic dependent: the set-up above may run while the kernel ahead in the stream (the
+    // previous pass's revert) finishes; its writes are visible from here on
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // A warp takes a contiguous run of (entry, segment) pairs, so most steps stay on the same node: its id and visit
@@ -632,6 +638,7 @@ __global__ void vl_apply_kernel(ob200_tree_view t, const int32_t* __restrict__ n
 __global__ void vl_revert_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids,
                                  const int32_t* __restrict__ sel, int n, int vl_value) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // the next selection may set itself up
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int node = node_ids ? node_ids[i] : i;
@@ -817,9 +824,18 @@ int ob200_launch_puct_select(const ob200_tree_view* tree, const int32_t* node_id
         int* errw = device_error_word();
         if (!errw) return set_error(OB200_ERR_CUDA, "ob200_launch_puct_select: cannot resolve the device error word");
         const int want = (n + kStagedWarps - 1) / kStagedWarps;
-        puct_select_staged_kernel<<<want < sms ? want : sms, kStagedWarps * 32, smem, as_stream(stream)>>>(
-            *tree, node_ids, n, c_puct, vl_value, apply_vl, sel_out, errw);
-        OB200_LAUNCHED("puct_select_staged_kernel");
+        cudaLaunchAttribute pdl[1];
+        pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        pdl[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchConfig_t lc = {};
+        lc.gridDim = dim3((unsigned)(want < sms ? want : sms));
+        lc.blockDim = dim3(kStagedWarps * 32);
+        lc.dynamicSmemBytes = (size_t)smem;
+        lc.stream = as_stream(stream);
+        lc.attrs = pdl;
+        lc.numAttrs = 1;
+        OB200_CUDA_OK(cudaLaunchKernelEx(&lc, puct_select_staged_kernel, *tree, node_ids, n, c_puct, vl_value, apply_vl, sel_out, errw));
+        counters().launches.fetch_add(1, std::memory_order_relaxed);
     } else if (tree->pitch >= kWideMinPitch ||
                (tree->pitch > kStagedMaxPitch && (long long)n * ((tree->pitch + kSegSlots - 1) / kSegSlots) >= kSegMinItems)) {
         // wide rows (chess: 4,672; Go's 362 in large launches: 16,384 x 362 takes 28.4 us against 33.9 us with a
@@ -841,16 +857,21 @@ int ob200_launch_puct_select(const ob200_tree_view* tree, const int32_t* node_id
         if (!words) return set_error(OB200_ERR_CUDA, "ob200_launch_puct_select: cannot allocate %d selection words", n);
         const long long items = (long long)n * segs;
         const long long want = (items + kSegWarps - 1) / kSegWarps;
-        puct_select_segmented_kernel<<<(unsigned)(want < sms ? want : sms), kSegWarps * 32, smem, as_stream(stream)>>>(
-            *tree, node_ids, n, segs, c_puct, words, errw);
-        OB200_CUDA_OK(cudaGetLastError());
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)((n + 7) / 8));
-        cfg.blockDim = dim3(256);
-        cfg.stream = as_stream(stream);
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(want < sms ? want : sms));
+        cfg.blockDim = dim3(kSegWarps * 32);
+        cfg.dynamicSmemBytes = (size_t)smem;
+        cfg.stream = as_stream(stream);
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, puct_select_segmented_kernel, *tree, node_ids, n, segs, c_puct, words, errw));
+        cfg = cudaLaunchConfig_t{};
+        cfg.gridDim = dim3((unsigned)((n + 7) / 8));
+        cfg.blockDim = dim3(256);
+        cfg.stream = as_stream(stream);
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, puct_select_finish_kernel, *tree, node_ids, n, vl_value, apply_vl, sel_out, words));
