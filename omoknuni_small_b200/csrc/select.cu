@@ -698,6 +698,66 @@ set_priors_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids, int n
     }
 }
 
+// select_row for rows of at most 256 slots (two vectors a lane), as the descent uses it: approximate scores with one
+// error scale for the row, the exact expression only for the slots that can hold the maximum (see approx_score and
+// the segmented kernel above; the choice is the reference's bit for bit), instead of two IEEE divisions per slot.
+__device__ __forceinline__ int select_row_narrow(const ob200_tree_view& t, int node, float c_puct, int lane) {
+    const int nvec = t.pitch >> 2;
+    const size_t row = (size_t)node * t.pitch;
+    const int4* N4 = reinterpret_cast<const int4*>(t.N + row);
+    const float4* W4 = reinterpret_cast<const float4*>(t.W + row);
+    const float4* P4 = reinterpret_cast<const float4*>(t.P + row);
+    const int4* V4 = reinterpret_cast<const int4*>(t.VL + row);
+    const uint32_t* mask = t.legal_bits + (size_t)node * t.mask_words;
+    const float explore = __fmul_rn(c_puct, __fsqrt_rn((float)t.node_visits[node]));
+    int n8[8], l8[8];
+    float w8[8], p8[8];
+    uint32_t bits = 0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int v = lane + 32 * h;
+        const bool have = v < nvec;
+        const int vi = have ? v : 0;
+        const int4 nn = __ldcg(N4 + vi);
+        const float4 ww = __ldcg(W4 + vi);
+        const float4 pp = __ldcg(P4 + vi);
+        const int4 ll = __ldcg(V4 + vi);
+        if (have) bits |= ((__ldg(mask + (vi >> 3)) >> ((vi & 7) * 4)) & 0xFu) << (4 * h);
+        n8[4 * h] = nn.x; n8[4 * h + 1] = nn.y; n8[4 * h + 2] = nn.z; n8[4 * h + 3] = nn.w;
+        w8[4 * h] = ww.x; w8[4 * h + 1] = ww.y; w8[4 * h + 2] = ww.z; w8[4 * h + 3] = ww.w;
+        p8[4 * h] = pp.x; p8[4 * h + 1] = pp.y; p8[4 * h + 2] = pp.z; p8[4 * h + 3] = pp.w;
+        l8[4 * h] = ll.x; l8[4 * h + 1] = ll.y; l8[4 * h + 2] = ll.z; l8[4 * h + 3] = ll.w;
+    }
+    float sc[8];
+    float lane_s = -INFINITY, lane_m = 0.0f;
+    uint32_t range = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) approx_score<true>(n8[k], w8[k], p8[k], l8[k], explore, (bits >> k) & 1u, sc[k], lane_s, lane_m, range);
+    if (__any_sync(0xffffffffu, range >> 23)) {               // a count beyond 2^23 or negative: the conversions proper
+        lane_s = -INFINITY; lane_m = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) approx_score<false>(n8[k], w8[k], p8[k], l8[k], explore, (bits >> k) & 1u, sc[k], lane_s, lane_m, range);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        lane_s = fmaxf(lane_s, __shfl_xor_sync(0xffffffffu, lane_s, off));
+        lane_m = fmaxf(lane_m, __shfl_xor_sync(0xffffffffu, lane_m, off));
+    }
+    float thr = fmaf(-2.0f * kBracket, lane_m, lane_s);
+    thr = thr == thr ? thr : -INFINITY;
+    Best b{-INFINITY, -1};
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+        if (((bits >> k) & 1u) && sc[k] >= thr) {
+            const float e = puct_score(n8[k], w8[k], p8[k], l8[k], explore);
+            if (e > b.score) { b.score = e; b.idx = (lane + 32 * (k >> 2)) * 4 + (k & 3); }
+        }
+    b = warp_combine(b);
+    if (b.idx < 0)
+        return least_visited_row(t.N + row, mask, t.n_children, lane);
+    return b.idx;
+}
+
 // One CTA per tree.  Simulations of a tree are ordered: simulation k must see the virtual loss
 // that simulations < k left on every edge it scores.  They still overlap as a wavefront: the CTA
 // advances in steps, a simulation takes one level per step, and simulation k starts at least one
@@ -742,7 +802,7 @@ traverse_kernel(ob200_tree_view t, const int32_t* __restrict__ roots, int n_tree
                     if (lane < nvec) ca = __ldcg(C4 + lane);
                     if (lane + 32 < nvec) cb = __ldcg(C4 + 32 + lane);
                 }
-                const int sel = select_row<false>(t, node, c_puct, lane);
+                const int sel = t.pitch <= 256 ? select_row_narrow(t, node, c_puct, lane) : select_row<false>(t, node, c_puct, lane);
                 if (sel >= 0) {
                     int next = -1;
                     if (links_in_regs) {
