@@ -39,6 +39,29 @@ inline cudaStream_t as_stream(ob200_stream s) { return reinterpret_cast<cudaStre
                                       cudaGetErrorString(_e));                           \
     } while (0)
 
+#ifdef __CUDACC__
+// Programmatic dependent launch, both ends.  A kernel that starts with OB200_PDL_ENTER() and is launched with
+// launch_dependent() may have its CTAs scheduled while the kernel ahead of it in the stream is still running: it
+// waits until that kernel has completed and its writes are visible, then lets the kernel behind it be scheduled in
+// turn.  Launched any other way the two instructions do nothing.  Every kernel of such a chain must start this way,
+// because "completed" is what carries the ordering on to the kernels further ahead.
+#define OB200_PDL_ENTER()                                                 \
+    do {                                                                  \
+        asm volatile("griddepcontrol.wait;" ::: "memory");                \
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   \
+    } while (0)
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // fp32 -> the 16-bit storage types, round to nearest even (host side: weight packing).
 inline uint16_t f32_to_bf16_rne(float f) {
     uint32_t u;

@@ -398,6 +398,7 @@ __global__ void leaf_prepare_kernel(const int32_t* __restrict__ paths, const int
                                     const int32_t* __restrict__ root_count, int16_t* __restrict__ leaf_hist,
                                     uint8_t* __restrict__ leaf_nh, uint8_t* __restrict__ leaf_tm,
                                     float* __restrict__ term_value, int32_t* term_count, int rules) {
+    OB200_PDL_ENTER();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_sims) return;
     const int tree = i / sims_per_tree;
@@ -489,6 +490,7 @@ expand_plan_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const i
                    PlanScratch ps) {
     __shared__ int warp_sums[kPlanThreads / 32];
     __shared__ int carry_s;
+    OB200_PDL_ENTER();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     auto code = [&](int i) { return -2 - (n_sims - 1 - i); };            // lower index -> smaller code; all below -1
     auto edge = [&](int i, int len) {
@@ -607,6 +609,7 @@ expand_rows_kernel(ob200_tree_view t, const int32_t* __restrict__ paths, const i
                    unsigned long long* node_hash, int tt_size, PlanScratch ps, Widening wd,
                    const uint32_t* __restrict__ root_stones, const uint8_t* __restrict__ root_tm, int sims_per_tree, int S) {
     __shared__ uint32_t black_s[8][8], legal_s[8][8];
+    OB200_PDL_ENTER();
     const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
     if (i >= n_sims) return;
     const int st = ps.status[i];
@@ -903,26 +906,24 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
     for (int r = 0; r < rounds; ++r) {
         if (int rc = ob200_launch_traverse(&s->tv, s->roots, T, s->sims_per_round, c.c_puct, c.virtual_loss, c.max_depth,
                                            s->paths, s->path_len, st)) return rc;
-        leaf_prepare_kernel<<<(L + 127) / 128, 128, 0, st>>>(s->paths, s->path_len, L, s->sims_per_round, c.max_depth, S,
-                                                            s->root_stones, s->root_hist, s->root_nh, s->root_tm,
-                                                            s->root_count, s->leaf_hist, s->leaf_nh, s->leaf_tm,
-                                                            s->term_value, s->term_count, c.rules);
-        OB200_LAUNCHED("leaf_prepare_kernel");
+        OB200_CUDA_OK(launch_dependent(leaf_prepare_kernel, dim3((L + 127) / 128), dim3(128), 0, st, s->paths, s->path_len, L,
+                                       s->sims_per_round, c.max_depth, S, s->root_stones, s->root_hist, s->root_nh, s->root_tm,
+                                       s->root_count, s->leaf_hist, s->leaf_nh, s->leaf_tm, s->term_value, s->term_count, c.rules));
+        counters().launches.fetch_add(1, std::memory_order_relaxed);
         if (int rc = net_forward_gomoku_for_search(s->net, s->leaf_hist, s->leaf_nh, s->leaf_tm, L, s->policy, s->value, st)) return rc;
         if (s->rec_policy && r < s->rec_rounds) {
             OB200_CUDA_OK(cudaMemcpyAsync(s->rec_policy + (size_t)(r + 1) * L * A, s->policy, (size_t)L * A * 4, cudaMemcpyDeviceToDevice, st));
             OB200_CUDA_OK(cudaMemcpyAsync(s->rec_value + (size_t)(r + 1) * L, s->value, (size_t)L * 4, cudaMemcpyDeviceToDevice, st));
         }
         const PlanScratch ps{s->plan_status, s->plan_aux, s->plan_new_id, s->plan_hash};
-        expand_plan_kernel<<<1, kPlanThreads, 0, st>>>(s->tv, s->paths, s->path_len, L, c.max_depth, s->value, s->term_value,
-                                                       (float)c.value_sign, s->value_quantum, s->max_nodes, s->n_used,
-                                                       s->leaf_value, s->sims_per_round, s->root_tm, s->zobrist, s->node_hash,
-                                                       s->tt_key, s->tt_val, s->tt_size, ps);
-        OB200_LAUNCHED("expand_plan_kernel");
-        expand_rows_kernel<<<(L * 32 + 255) / 256, 256, 0, st>>>(s->tv, s->paths, s->path_len, L, c.max_depth, s->policy, A,
-                                                                s->node_hash, s->tt_size, ps, wd, s->root_stones, s->root_tm,
-                                                                s->sims_per_round, s->S);
-        OB200_LAUNCHED("expand_rows_kernel");
+        OB200_CUDA_OK(launch_dependent(expand_plan_kernel, dim3(1), dim3(kPlanThreads), 0, st, s->tv, s->paths, s->path_len, L, c.max_depth,
+                                       s->value, s->term_value, (float)c.value_sign, s->value_quantum, s->max_nodes, s->n_used,
+                                       s->leaf_value, s->sims_per_round, s->root_tm, s->zobrist, s->node_hash, s->tt_key, s->tt_val,
+                                       s->tt_size, ps));
+        OB200_CUDA_OK(launch_dependent(expand_rows_kernel, dim3((L * 32 + 255) / 256), dim3(256), 0, st, s->tv, s->paths, s->path_len, L,
+                                       c.max_depth, s->policy, A, s->node_hash, s->tt_size, ps, wd, s->root_stones, s->root_tm,
+                                       s->sims_per_round, s->S));
+        counters().launches.fetch_add(2, std::memory_order_relaxed);
         if (int rc = ob200_launch_backup(&s->tv, s->paths, s->path_len, s->leaf_value, L, c.max_depth, c.virtual_loss, st)) return rc;
     }
     OB200_CUDA_OK(cudaEventRecord(s->ev1, st));

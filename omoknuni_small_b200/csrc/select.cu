@@ -653,6 +653,7 @@ __global__ void backup_kernel(ob200_tree_view t, const int32_t* __restrict__ pat
                               const int32_t* __restrict__ path_len,
                               const float* __restrict__ leaf_values, int n, int max_depth,
                               int vl_value) {
+    OB200_PDL_ENTER();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     int len = path_len[i];
@@ -775,6 +776,7 @@ traverse_kernel(ob200_tree_view t, const int32_t* __restrict__ roots, int n_tree
     const int tree = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) { n_started = 0; n_finished = 0; }
+    OB200_PDL_ENTER();
     __syncthreads();
     const int root = roots[tree];
     int k = -1;            // simulation this warp is running, -1 = idle
@@ -982,9 +984,9 @@ int ob200_launch_backup(const ob200_tree_view* tree, const int32_t* paths, const
         return set_error(OB200_ERR_INVALID, "ob200_launch_backup: bad arguments");
     if (int rc = require_device()) return rc;
     if (n == 0) return OB200_OK;
-    backup_kernel<<<(n + 127) / 128, 128, 0, as_stream(stream)>>>(*tree, paths, path_len, leaf_values, n, max_depth,
-                                                                  vl_value);
-    OB200_LAUNCHED("backup_kernel");
+    OB200_CUDA_OK(launch_dependent(backup_kernel, dim3((n + 127) / 128), dim3(128), 0, as_stream(stream), *tree, paths, path_len,
+                                   leaf_values, n, max_depth, vl_value));
+    counters().launches.fetch_add(1, std::memory_order_relaxed);
     counters().backups.fetch_add((uint64_t)n, std::memory_order_relaxed);
     return OB200_OK;
 }
@@ -1013,9 +1015,9 @@ int ob200_launch_traverse(const ob200_tree_view* tree, const int32_t* roots, int
     if (int rc = require_device()) return rc;
     if (n_trees == 0) return OB200_OK;
     // one CTA per tree: trees are few and latency-bound, so spread them over the SMs
-    traverse_kernel<<<n_trees, kTravWarps * 32, 0, as_stream(stream)>>>(*tree, roots, n_trees, sims_per_tree, c_puct,
-                                                                          vl_value, max_depth, paths_out, path_len_out);
-    OB200_LAUNCHED("traverse_kernel");
+    OB200_CUDA_OK(launch_dependent(traverse_kernel, dim3(n_trees), dim3(kTravWarps * 32), 0, as_stream(stream), *tree, roots, n_trees,
+                                   sims_per_tree, c_puct, vl_value, max_depth, paths_out, path_len_out));
+    counters().launches.fetch_add(1, std::memory_order_relaxed);
     counters().selections.fetch_add((uint64_t)n_trees * sims_per_tree, std::memory_order_relaxed);
     return OB200_OK;
 }
