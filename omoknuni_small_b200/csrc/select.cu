@@ -563,26 +563,32 @@ puct_select_segmented_kernel(ob200_tree_view t, const int32_t* __restrict__ node
     flush();
 }
 
-// One warp per entry of the launch: the node's word -> selection (lowest-visited existing child when no score
-// was comparable, as the narrow-row kernels), virtual loss, word back to zero.
+// One thread per entry of the launch: the node's word -> selection (lowest-visited existing child when no score
+// was comparable, as the narrow-row kernels; rare, so it is a plain scan), virtual loss, word back to zero.
 __global__ void __launch_bounds__(256)
 puct_select_finish_kernel(ob200_tree_view t, const int32_t* __restrict__ node_ids, int n, int vl_value, int apply_vl,
                           int32_t* __restrict__ sel_out, unsigned long long* __restrict__ best_word) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int entry = (int)((blockIdx.x * (unsigned)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+    const int entry = (int)(blockIdx.x * (unsigned)blockDim.x + threadIdx.x);
     if (entry >= n) return;
     const int node = node_ids ? __ldg(node_ids + entry) : entry;
     const unsigned long long w = __ldcg(best_word + entry);
     int sel = -1;
-    if (node >= 0 && node < t.n_nodes)
-        sel = w ? (int)~(uint32_t)w
-                : least_visited_row(t.N + (size_t)node * t.pitch, t.legal_bits + (size_t)node * t.mask_words, t.n_children, lane);
-    if (lane == 0) {
-        sel_out[entry] = sel;
-        if (sel >= 0 && apply_vl && vl_value > 0) atomicAdd(t.VL + (size_t)node * t.pitch + sel, vl_value);
-        if (w) best_word[entry] = 0ull;
+    if (node >= 0 && node < t.n_nodes) {
+        if (w) {
+            sel = (int)~(uint32_t)w;
+        } else {
+            const int32_t* N = t.N + (size_t)node * t.pitch;
+            const uint32_t* mask = t.legal_bits + (size_t)node * t.mask_words;
+            int mn = INT_MAX;
+            for (int s = 0; s < t.n_children; ++s)
+                if (((mask[s >> 5] >> (s & 31)) & 1u) && N[s] < mn) { mn = N[s]; sel = s; }
+        }
     }
+    sel_out[entry] = sel;
+    if (sel >= 0 && apply_vl && vl_value > 0) atomicAdd(t.VL + (size_t)node * t.pitch + sel, vl_value);
+    if (w) best_word[entry] = 0ull;
 }
 
 // One 64-bit word per entry of a wide-row launch, zero between launches.  Launches on one stream are ordered, so
@@ -931,7 +937,7 @@ int ob200_launch_puct_select(const ob200_tree_view* tree, const int32_t* node_id
         cfg.numAttrs = 1;
         OB200_CUDA_OK(cudaLaunchKernelEx(&cfg, puct_select_segmented_kernel, *tree, node_ids, n, segs, c_puct, words, errw));
         cfg = cudaLaunchConfig_t{};
-        cfg.gridDim = dim3((unsigned)((n + 7) / 8));
+        cfg.gridDim = dim3((unsigned)((n + 255) / 256));
         cfg.blockDim = dim3(256);
         cfg.stream = as_stream(stream);
         cfg.attrs = attr;
