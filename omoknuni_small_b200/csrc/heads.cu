@@ -8,8 +8,9 @@
 //   fc_kernel          out[b][j] = act(sum_i in[b][i] * WT[i][j] + bias[j]);
 //                      register-tiled (32 boards x 64 outputs per CTA, 4 x 4 per
 //                      thread, cp.async pipeline), weight matrix stored transposed.
-//   softmax_kernel     in-place softmax over a row.
-//   value_out_kernel   value_fc2 + tanh (one warp per board).
+//   fc_pair_kernel     the policy FC and the value head's first FC as one launch.
+//   head_tails_kernel  in-place softmax over the rows of logits, and value_fc2 + tanh, as one launch.
+//   value_out_kernel   value_fc2 + tanh (one warp per board), for the value head on its own.
 #include "internal.h"
 #include "sm100_ptx.cuh"
 #include <mutex>
@@ -264,19 +265,6 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float* red) 
     return v;
 }
 
-__global__ void __launch_bounds__(128) softmax_kernel(float* __restrict__ x, int A) {
-    __shared__ float red[4];
-    float* row = x + (size_t)blockIdx.x * A;
-    float m = -INFINITY;
-    for (int i = threadIdx.x; i < A; i += blockDim.x) m = fmaxf(m, row[i]);
-    m = block_reduce(m, true, red);
-    float s = 0.0f;
-    for (int i = threadIdx.x; i < A; i += blockDim.x) s += expf(row[i] - m);
-    s = block_reduce(s, false, red);
-    const float inv = 1.0f / s;
-    for (int i = threadIdx.x; i < A; i += blockDim.x) row[i] = expf(row[i] - m) * inv;
-}
-
 __global__ void __launch_bounds__(256)
 value_out_kernel(const float* __restrict__ hidden, const float* __restrict__ w2, float b2, int H, int B,
                  float* __restrict__ value) {
@@ -289,7 +277,7 @@ value_out_kernel(const float* __restrict__ hidden, const float* __restrict__ w2,
 }
 
 // The tails of both heads in one launch, started as a programmatic dependent of fc_pair_kernel: CTAs
-// [0, softmax_rows) normalise one row of logits each as softmax_kernel does, the rest finish four boards' values
+// [0, softmax_rows) normalise one row of logits each (maximum, sum of exponentials, division), the rest finish four boards' values
 // each as value_out_kernel does (a warp per board).
 __global__ void __launch_bounds__(128)
 head_tails_kernel(float* __restrict__ logits, int A, int softmax_rows, const float* __restrict__ hidden,
@@ -320,8 +308,8 @@ head_tails_kernel(float* __restrict__ logits, int A, int softmax_rows, const flo
 }  // namespace
 
 // The FC part of both heads in two launches: {policy FC (when policy_in is given), value FC1 + ReLU}, then
-// {softmax over the logits (when asked), value FC2 + tanh}.  Results equal launch_fc / launch_softmax /
-// launch_value_out on the same buffers bit for bit.
+// {softmax over the logits (when asked), value FC2 + tanh}.  The FC results equal launch_fc / launch_value_out on
+// the same buffers bit for bit.
 int launch_head_fcs(const float* policy_in, const float* WpT, const float* bp, float* policy_out, int policy_k, int policy_size,
                     int softmax, const float* value_in, const float* W1T, const float* b1, float* hidden, int value_k, int H,
                     const float* w2, float b2, float* value_out, int B, cudaStream_t st) {
@@ -377,12 +365,6 @@ int launch_fc(const float* in, const float* WT, const float* bias, float* out, i
     dim3 grid((B + kFcTileB - 1) / kFcTileB, (Nout + kFcTileN - 1) / kFcTileN);
     fc_kernel<<<grid, 256, 0, st>>>(in, WT, bias, out, B, K, Nout, relu);
     OB200_LAUNCHED("fc_kernel");
-    return OB200_OK;
-}
-
-int launch_softmax(float* x, int B, int A, cudaStream_t st) {
-    softmax_kernel<<<B, 128, 0, st>>>(x, A);
-    OB200_LAUNCHED("softmax_kernel");
     return OB200_OK;
 }
 

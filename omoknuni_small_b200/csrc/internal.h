@@ -64,7 +64,6 @@ int launch_head_conv(const void* tower, const float* w, const float* bias, int H
                      float* hv, int B, int S, cudaStream_t st, int C = 64, int dtype = 0);
 int launch_fc(const float* in, const float* WT, const float* bias, float* out, int B, int K, int Nout, int relu,
               cudaStream_t st);
-int launch_softmax(float* x, int B, int A, cudaStream_t st);
 // Both heads' FC layers in two launches ({policy FC, value FC1}, {softmax, value FC2 + tanh}); policy_in may be
 // null (a policy that is already in policy_out); results as the single-layer launchers give them.
 int launch_head_fcs(const float* policy_in, const float* WpT, const float* bp, float* policy_out, int policy_k, int policy_size,
