@@ -99,7 +99,12 @@ int32_t ob200_tree_mask_words(int32_t n_children);
  *   the reference's fallback does.
  *   If apply_vl != 0 and vl_value > 0: atomically VL[node][sel] += vl_value.
  * Distinct entries of node_ids may repeat; each sees the table as it was when
- * it read it (entries of one launch are not ordered against each other). */
+ * it read it (entries of one launch are not ordered against each other).
+ * Rows of more than 256 slots in large launches (every launch of rows of 1,024
+ * slots or more) use 8 bytes of scratch per entry, which the library keeps per
+ * (device, stream) and obtains with cudaMallocAsync when a launch needs more
+ * than the stream has: make the first such launch of a stream outside stream
+ * capture.  Launches of rows up to 256 slots allocate nothing. */
 int ob200_launch_puct_select(const ob200_tree_view* tree, const int32_t* node_ids, int32_t n,
                              float c_puct, int32_t vl_value, int32_t apply_vl,
                              int32_t* sel_out, ob200_stream stream);
