@@ -361,6 +361,13 @@ def gpu_arm(args):
             e2e_sync_s += time.perf_counter() - t0
         # ---- the dominant kernel alone: the whole tower (one launch) ----
         bt_in = capi.encode_gomoku(d_hist, d_nh, d_tm, 15, 17, net.input_tensor_channels(), DT)
+
+        # the encoder as a launch of its own (callers that keep their own network; the network step above does not
+        # launch it: the tower writes its input planes itself)
+        def enc_loop():
+            for _ in range(5):
+                capi.encode_gomoku(d_hist, d_nh, d_tm, 15, 17, net.input_tensor_channels(), DT, out=bt_in)
+        enc_ms = float(np.mean(timed(enc_loop, 3))) / 5
         tower_reps = 5
 
         def tower_loop():
@@ -512,11 +519,11 @@ def gpu_arm(args):
     parity = replicas.sum_counters(dist, {"selection_ranks_ok": sel_ok, "encode_ranks_ok": enc_ok}, dev)
 
     reduced = replicas.max_over_ranks(
-        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms, e2e_sync_s * 1e3, mcts_wall_ms, selw_big_ms] + [v for _, m, tm in sweep for v in (m, tm)] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
-    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms, e2e_sync_ms, mcts_wall_ms, selw_big_ms = reduced[:12]
-    sweep = [(bs, reduced[12 + 2 * i], reduced[13 + 2 * i]) for i, (bs, _, _) in enumerate(sweep)]
+        dist, [total_ms, e2e_s * 1e3, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms, e2e_sync_s * 1e3, mcts_wall_ms, selw_big_ms, enc_ms] + [v for _, m, tm in sweep for v in (m, tm)] + [v for wr in wide for v in (wr["ms"], wr["conv_ms"])], dev)
+    total_ms, e2e_ms, conv_ms, sel_ms, selk_ms, mcts_ms, selw_ms, tower_ms, tower_o_ms, e2e_sync_ms, mcts_wall_ms, selw_big_ms, enc_ms = reduced[:13]
+    sweep = [(bs, reduced[13 + 2 * i], reduced[14 + 2 * i]) for i, (bs, _, _) in enumerate(sweep)]
     for i, wr in enumerate(wide):
-        wr["ms"], wr["conv_ms"] = reduced[12 + 2 * len(sweep) + 2 * i], reduced[13 + 2 * len(sweep) + 2 * i]
+        wr["ms"], wr["conv_ms"] = reduced[13 + 2 * len(sweep) + 2 * i], reduced[14 + 2 * len(sweep) + 2 * i]
     totals = replicas.sum_counters(dist, capi.counters(), dev)   # the only cross-GPU step: per-GPU counters summed
     if rank == 0:
         flops_eval = synth.net_flops_per_eval(15, 17, 64, NET["blocks"], 225, NET["policy_head_ch"], NET["value_head_ch"])
@@ -570,6 +577,12 @@ def gpu_arm(args):
                          # residual from DRAM, output left in L2), scaled by the boards processed
                          "traffic": 33.66e6 * B / 512.0, "traffic_unit": "bytes/launch",
                          "traffic_source": "profiles/conv3x3_kernel_gomoku15_batch512.md (scaled by batch)"},
+            # the stand-alone encoder launch: 8 KB of 17-plane positions per board (225 x 17 x 2 B + 34 B of history in) by the
+            # north star's count; the kernel writes the whole padded 64-channel board tensor (32 KB per board)
+            "encoder": {"kernel": "encode_gomoku_board_kernel", "us_per_launch": enc_ms * 1e3, "boards": B,
+                        "algorithmic_gbs": B * (225 * 17 * 2 + 34) / (enc_ms * 1e-3) / 1e9,
+                        "written_gbs": B * 256 * 64 * 2 / (enc_ms * 1e-3) / 1e9,
+                        "note": "not part of the network step: the tower writes its own input planes"},
             "selection": {"value": SEL_NODES / (sel_ms * 1e-3), "unit": "node selections/s (select + VL apply + VL revert)",
                           "nodes": SEL_NODES, "children": SEL_CHILDREN, "ms_per_pass": sel_ms,
                           # the whole pass (select + apply, then the clamped revert): 3,656 algorithmic bytes per node

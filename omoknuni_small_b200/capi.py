@@ -294,13 +294,15 @@ def planes_to_board_tensor_host(planes, out_channels, dtype=DTYPE_BF16):
     return out.reshape(-1)
 
 
-def encode_gomoku(history, n_hist, to_move, board_size=15, planes=19, out_channels=64, dtype=DTYPE_BF16):
+def encode_gomoku(history, n_hist, to_move, board_size=15, planes=19, out_channels=64, dtype=DTYPE_BF16, out=None):
     """Device tensors in (int16 [B,16], uint8 [B], uint8 [B]) -> board tensor
-    (torch int16 tensor holding the bf16 / fp16 bits)."""
+    (torch int16 tensor holding the bf16 / fp16 bits; `out`: a tensor of that size to write into)."""
     import torch
     B = history.shape[0]
     nbytes = int(lib().ob200_board_tensor_bytes(board_size, B, out_channels))
-    out = torch.empty(nbytes // 2, dtype=torch.int16, device=history.device)
+    if out is None:
+        out = torch.empty(nbytes // 2, dtype=torch.int16, device=history.device)
+    assert out.numel() * out.element_size() == nbytes
     check(lib().ob200_launch_encode_gomoku_dt(_ptr(history), _ptr(n_hist), _ptr(to_move), B, board_size, planes,
                                               out_channels, dtype, _ptr(out), _stream()))
     return out
