@@ -489,6 +489,10 @@ def gpu_arm(args):
             mcts_ms += st["device_ms"]; mcts_sims += st["simulations"]; mcts_evals += st["evaluations"]
             mcts_nodes = st["nodes"]
         torch.cuda.synchronize()
+        # one more move, outside the figures above, with events around the five phases of every round
+        search.phase_timing(True)
+        search.run(openings)
+        mcts_phases = search.phase_timing(False)
         search.close()
         # ---- the wider towers (parity-test configurations timed for their roofline): Go 19x19 20x128 at
         # batch 2048, chess 8x8 20x256 with 73 policy planes at batch 4096; forward on a resident input ----
@@ -615,6 +619,10 @@ def gpu_arm(args):
                                 "dirichlet": [0.3, 0.25], "openings": "seeded random, 0-20 stones", "moves_timed": mcts_moves,
                                 "transposition_table": "on (device table, Zobrist keys)", "nodes_per_move": mcts_nodes},
                      "ms_per_move": mcts_ms / mcts_moves,
+                     # rank 0's phase sums over one extra move timed with events between the phases (which costs the
+                     # overlap of each phase's launch with its predecessor, so the sum exceeds ms_per_move); the descent
+                     # reads a row of 3,656 B per tree level, the network is the step above
+                     "phases_ms_one_move": mcts_phases,
                      "timing": "value: CUDA events around the enqueued work of each move, inside the library; wall_value: perf_counter around the call"},
             "batch_sweep": [{"leaf_batch_per_gpu": bs, "ms_per_step": m, "value": world * bs / (m * 1e-3), "unit": UNIT,
                              "tower_tflops": bs / (m * 1e-3) * flops_eval / 1e12,

@@ -648,6 +648,13 @@ int ob200_search_debug_tree(ob200_search* s, ob200_tree_view* view_out, int32_t*
 int ob200_search_debug_hooks(ob200_search* s, float value_quantum, int32_t record_rounds);
 int ob200_search_debug_record(ob200_search* s, const float** policy_out, const float** value_out,
                               const float** noise_out);
+/* Measurement hook.  enable != 0: the next ob200_search_run calls record events
+ * around the five phases of every round (descent, leaf positions, network,
+ * expansion, backup); the events break the programmatic-dependent chain between
+ * the phases, so such a run is a little slower than a plain one.  phase_ms_out
+ * (5 doubles, may be NULL) receives the sums over the rounds of the last run
+ * that was timed this way. */
+int ob200_search_debug_phases(ob200_search* s, int32_t enable, double* phase_ms_out);
 int ob200_copy_to_host(void* dst_host, const void* src_device, int64_t bytes);
 
 /* Per-device counters for the end-of-run reduction (the only cross-GPU step;

@@ -147,6 +147,7 @@ SIGNATURES = {
                                    C.POINTER(SearchStats)]),
     "ob200_search_debug_tree": (C.c_int, [C.c_void_p, C.POINTER(TreeView), C.POINTER(C.c_int32)]),
     "ob200_search_debug_hooks": (C.c_int, [C.c_void_p, C.c_float, C.c_int32]),
+    "ob200_search_debug_phases": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
     "ob200_search_debug_record": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
     "ob200_copy_to_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
     "ob200_get_counters": (C.c_int, [C.POINTER(Counters)]),
@@ -534,6 +535,13 @@ class Search:
         root evaluation and of the first `record_rounds` rounds of each run."""
         check(lib().ob200_search_debug_hooks(self.h, value_quantum, record_rounds))
         self._rec_rounds = record_rounds
+
+    def phase_timing(self, enable=True):
+        """Switches per-phase event timing of the following runs on or off; returns the sums (ms) of the last timed run
+        as a dict: descent, leaf_positions, network, expansion, backup."""
+        out = (C.c_double * 5)()
+        check(lib().ob200_search_debug_phases(self.h, int(enable), out))
+        return dict(zip(("descent", "leaf_positions", "network", "expansion", "backup"), [float(v) for v in out]))
 
     def record(self):
         """(policy [R + 1, L, 225], value [R + 1, L], noise [T, 228]) of the last run, as numpy arrays."""

@@ -55,6 +55,10 @@ struct ob200_search {
     float *rec_policy = nullptr, *rec_value = nullptr;   // [rec_rounds + 1][leaf_batch][A], [rec_rounds + 1][leaf_batch]
     int rec_rounds = 0;
     double wall_ms = 0.0;                                // host time of the last ob200_search_run
+    // test / measurement hook: events around the five phases of every round of the next run
+    bool phase_timing = false;
+    std::vector<cudaEvent_t> phase_ev;                   // [rounds][6]
+    double phase_ms[5] = {0, 0, 0, 0, 0};                // descent, leaf positions, network, expansion, backup
     std::vector<void*> owned;
 };
 
@@ -763,6 +767,7 @@ void ob200_search_destroy(ob200_search* s) {
     if (s->stream) { cudaStreamSynchronize(s->stream); cudaStreamDestroy(s->stream); }
     if (s->ev0) cudaEventDestroy(s->ev0);
     if (s->ev1) cudaEventDestroy(s->ev1);
+    for (cudaEvent_t e : s->phase_ev) if (e) cudaEventDestroy(e);
     for (void* p : s->owned) cudaFree(p);
     delete s;
 }
@@ -785,6 +790,14 @@ int ob200_search_debug_hooks(ob200_search* s, float value_quantum, int32_t recor
         if (int rc = salloc(s, &s->rec_value, (size_t)(record_rounds + 1) * L)) return rc;
         s->rec_rounds = record_rounds;
     }
+    return OB200_OK;
+}
+
+int ob200_search_debug_phases(ob200_search* s, int32_t enable, double* phase_ms_out) {
+    if (!s) return set_error(OB200_ERR_INVALID, "ob200_search_debug_phases: null argument");
+    if (phase_ms_out)
+        for (int k = 0; k < 5; ++k) phase_ms_out[k] = s->phase_ms[k];
+    s->phase_timing = enable != 0;
     return OB200_OK;
 }
 
@@ -903,14 +916,24 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
     }
     // ---- rounds ----
     const int rounds = (c.sims_per_move + s->sims_per_round - 1) / s->sims_per_round;
+    if (s->phase_timing && (int)s->phase_ev.size() < rounds * 6) {
+        const size_t have = s->phase_ev.size();
+        s->phase_ev.resize((size_t)rounds * 6, nullptr);
+        for (size_t i = have; i < s->phase_ev.size(); ++i) OB200_CUDA_OK(cudaEventCreate(&s->phase_ev[i]));
+    }
+    auto mark = [&](int r, int k) { return s->phase_timing ? cudaEventRecord(s->phase_ev[(size_t)r * 6 + k], st) : cudaSuccess; };
     for (int r = 0; r < rounds; ++r) {
+        OB200_CUDA_OK(mark(r, 0));
         if (int rc = ob200_launch_traverse(&s->tv, s->roots, T, s->sims_per_round, c.c_puct, c.virtual_loss, c.max_depth,
                                            s->paths, s->path_len, st)) return rc;
+        OB200_CUDA_OK(mark(r, 1));
         OB200_CUDA_OK(launch_dependent(leaf_prepare_kernel, dim3((L + 127) / 128), dim3(128), 0, st, s->paths, s->path_len, L,
                                        s->sims_per_round, c.max_depth, S, s->root_stones, s->root_hist, s->root_nh, s->root_tm,
                                        s->root_count, s->leaf_hist, s->leaf_nh, s->leaf_tm, s->term_value, s->term_count, c.rules));
         counters().launches.fetch_add(1, std::memory_order_relaxed);
+        OB200_CUDA_OK(mark(r, 2));
         if (int rc = net_forward_gomoku_for_search(s->net, s->leaf_hist, s->leaf_nh, s->leaf_tm, L, s->policy, s->value, st)) return rc;
+        OB200_CUDA_OK(mark(r, 3));
         if (s->rec_policy && r < s->rec_rounds) {
             OB200_CUDA_OK(cudaMemcpyAsync(s->rec_policy + (size_t)(r + 1) * L * A, s->policy, (size_t)L * A * 4, cudaMemcpyDeviceToDevice, st));
             OB200_CUDA_OK(cudaMemcpyAsync(s->rec_value + (size_t)(r + 1) * L, s->value, (size_t)L * 4, cudaMemcpyDeviceToDevice, st));
@@ -924,7 +947,9 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
                                        c.max_depth, s->policy, A, s->node_hash, s->tt_size, ps, wd, s->root_stones, s->root_tm,
                                        s->sims_per_round, s->S));
         counters().launches.fetch_add(2, std::memory_order_relaxed);
+        OB200_CUDA_OK(mark(r, 4));
         if (int rc = ob200_launch_backup(&s->tv, s->paths, s->path_len, s->leaf_value, L, c.max_depth, c.virtual_loss, st)) return rc;
+        OB200_CUDA_OK(mark(r, 5));
     }
     OB200_CUDA_OK(cudaEventRecord(s->ev1, st));
     // ---- results: root visit counts -> pi (getActionProbabilities, src/mcts/mcts_engine_tree.cpp:389-465) ----
@@ -954,6 +979,15 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
         for (int a = 0; a < A; ++a) pi[a] = (float)(pi[a] / sum);
     }
     s->moves_done++;
+    if (s->phase_timing) {
+        for (double& v : s->phase_ms) v = 0.0;
+        for (int r = 0; r < rounds; ++r)
+            for (int k = 0; k < 5; ++k) {
+                float ms = 0.0f;
+                cudaEventElapsedTime(&ms, s->phase_ev[(size_t)r * 6 + k], s->phase_ev[(size_t)r * 6 + k + 1]);
+                s->phase_ms[k] += ms;
+            }
+    }
     if (stats) {
         float ms = 0.0f;
         cudaEventElapsedTime(&ms, s->ev0, s->ev1);
