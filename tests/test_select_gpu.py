@@ -19,7 +19,8 @@ def api(lib):
     return capi
 
 
-@pytest.mark.parametrize("n_nodes,nc,seed", [(4096, 225, 7), (257, 362, 8), (16384, 362, 12), (64, 4672, 9), (300, 3, 10), (33, 1, 11)])
+@pytest.mark.parametrize("n_nodes,nc,seed", [(4096, 225, 7), (257, 362, 8), (16384, 362, 12), (64, 4672, 9), (300, 3, 10), (33, 1, 11),
+                                               (12288, 260, 13), (300, 1024, 14), (70, 8192, 15), (33, 1027, 16), (1500, 256, 17)])
 def test_select_apply_revert_bit_exact(api, oracle, n_nodes, nc, seed):
     import torch
     t = synth.make_selection_tree(n_nodes, nc, seed=seed)
