@@ -24,6 +24,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <functional>
 #include <memory>
 #include <mutex>
 #include <string>
@@ -214,5 +215,13 @@ private:
     bool keep_weights_ = false;
     std::vector<Kept> kept_;
 };
+
+// The engine's other injection point: MCTSEngine(InferenceFunction, const MCTSSettings&)
+// (include/mcts/mcts_engine.h:230-231, :247), which every engine test of the reference uses.  The function keeps the
+// network alive.
+inline std::function<std::vector<alphazero::mcts::NetworkOutput>(const std::vector<std::unique_ptr<alphazero::core::IGameState>>&)>
+makeInferenceFunction(std::shared_ptr<B200Network> net) {
+    return [net](const std::vector<std::unique_ptr<alphazero::core::IGameState>>& states) { return net->inference(states); };
+}
 
 }  // namespace omoknuni_b200

@@ -115,6 +115,14 @@ int run_direct(int argc, char** argv) {
     net->load(argv[2]);
     const auto out = net->inference(states);     // more states than max_batch: the adapter slices
     REQUIRE(out.size() == states.size() && net->getPolicySize() == 225 && net->getInputShape()[0] == cin, "shapes");
+    // the same network as the std::function the engine's other constructor takes (include/mcts/mcts_engine.h:230-231)
+    {
+        const auto fn = omoknuni_b200::makeInferenceFunction(std::static_pointer_cast<omoknuni_b200::B200Network>(net));
+        const auto again = fn(states);
+        REQUIRE(again.size() == out.size(), "inference function: size");
+        for (size_t i = 0; i < out.size(); ++i)
+            REQUIRE(again[i].value == out[i].value && again[i].policy == out[i].policy, "inference function: state %zu differs", i);
+    }
     if (!write_out(argv[4], out)) return 5;
     std::printf("adapter_check direct: %zu states evaluated\n", out.size());
     return 0;
