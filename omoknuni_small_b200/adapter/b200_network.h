@@ -195,6 +195,20 @@ public:
     }
     std::vector<int64_t> getInputShape() const override { return {cfg_.input_channels, cfg_.board_size, cfg_.board_size}; }
     int64_t getPolicySize() const override { return cfg_.policy_size; }
+    // The optional part of the interface (include/nn/neural_network.h:60-119): inference() is the batch path; the
+    // same weights give the same bits on every call; what the reference's optimisation switches ask for is how the
+    // library works anyway (one launch per tower that can be captured in a graph, activations resident on the GPU).
+    bool supportsEvaluateBatch() const override { return true; }
+    std::vector<alphazero::mcts::NetworkOutput> evaluateBatch(
+        const std::vector<std::unique_ptr<alphazero::core::IGameState>>& states) override { return inference(states); }
+    bool isDeterministic() const override { return true; }
+    GPUOptimizationStatus getGPUOptimizationStatus() const override {
+        GPUOptimizationStatus st;
+        st.cuda_graphs_supported = true;
+        st.persistent_kernels_enabled = ready_;
+        st.model_is_deterministic = true;
+        return st;
+    }
 
 private:
     struct Kept { std::string name; std::vector<float> data; };

@@ -120,6 +120,10 @@ int run_direct(int argc, char** argv) {
         const auto fn = omoknuni_b200::makeInferenceFunction(std::static_pointer_cast<omoknuni_b200::B200Network>(net));
         const auto again = fn(states);
         REQUIRE(again.size() == out.size(), "inference function: size");
+        REQUIRE(net->supportsEvaluateBatch() && net->isDeterministic() && net->getGPUOptimizationStatus().model_is_deterministic,
+                "optional interface");
+        const auto one = net->evaluate(*states[0]);
+        REQUIRE(one.value == out[0].value && one.policy == out[0].policy, "evaluate(state) differs from inference()");
         for (size_t i = 0; i < out.size(); ++i)
             REQUIRE(again[i].value == out[i].value && again[i].policy == out[i].policy, "inference function: state %zu differs", i);
     }
