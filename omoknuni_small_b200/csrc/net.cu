@@ -56,16 +56,17 @@ struct ob200_net {
         float *d_policy = nullptr, *d_value = nullptr;
         float *h_policy = nullptr, *h_value = nullptr;
         int16_t* h_hist = nullptr;
+        int16_t* d_hist = nullptr;  // [histories | history lengths | sides to move] of the batch in this slot
         int* h_err = nullptr;       // pinned landing word for the device error code
         float *user_policy = nullptr, *user_value = nullptr;
         bool direct = false;        // results are copied straight into the caller's page-locked buffers
-        cudaEvent_t computed = nullptr, done = nullptr;
+        cudaEvent_t computed = nullptr, done = nullptr, hist_ready = nullptr;
     } slot[2];
     std::condition_variable slot_cv;
     cudaStream_t copy_stream = nullptr;   // device -> host copies of results
+    cudaStream_t in_stream = nullptr;     // host -> device copies of move histories, ahead of the batch that reads them
     cudaEvent_t planes_copied = nullptr;  // the planes staging buffer has been read by its host -> device copy
     float *d_planes = nullptr;
-    int16_t* d_hist = nullptr;      // [histories | history lengths | sides to move] of the call being enqueued
     float *h_planes = nullptr;
     size_t planes_capacity = 0;     // floats per staging buffer
     std::vector<void*> owned_dev, owned_host;
@@ -227,7 +228,12 @@ void ob200_net_destroy(ob200_net* n) {
     if (n->stream) { cudaStreamSynchronize(n->stream); cudaStreamDestroy(n->stream); }
     if (n->copy_stream) { cudaStreamSynchronize(n->copy_stream); cudaStreamDestroy(n->copy_stream); }
     if (n->planes_copied) cudaEventDestroy(n->planes_copied);
-    for (auto& sl : n->slot) { if (sl.computed) cudaEventDestroy(sl.computed); if (sl.done) cudaEventDestroy(sl.done); }
+    if (n->in_stream) { cudaStreamSynchronize(n->in_stream); cudaStreamDestroy(n->in_stream); }
+    for (auto& sl : n->slot) {
+        if (sl.computed) cudaEventDestroy(sl.computed);
+        if (sl.done) cudaEventDestroy(sl.done);
+        if (sl.hist_ready) cudaEventDestroy(sl.hist_ready);
+    }
     for (void* p : n->owned_dev) cudaFree(p);
     for (void* p : n->owned_host) cudaFreeHost(p);
     delete n;
@@ -376,7 +382,11 @@ int ob200_net_finalize(ob200_net* n) {
         if (int rc = dev_alloc(n, &sl.d_value, MB, false)) return rc;
         if (int rc = host_alloc(n, &sl.h_policy, MB * A)) return rc;
         if (int rc = host_alloc(n, &sl.h_value, MB)) return rc;
+        // move histories, history lengths and sides to move of a batch share one staging block (34 bytes per board,
+        // packed for the batch's size), so that they reach the device in one copy
         if (int rc = host_alloc(n, &sl.h_hist, MB * 17)) return rc;
+        if (int rc = dev_alloc(n, &sl.d_hist, MB * 17, false)) return rc;
+        OB200_CUDA_OK(cudaEventCreateWithFlags(&sl.hist_ready, cudaEventDisableTiming));
         if (int rc = host_alloc(n, &sl.h_err, 1)) return rc;
         *sl.h_err = 0;
         OB200_CUDA_OK(cudaEventCreateWithFlags(&sl.computed, cudaEventDisableTiming));
@@ -384,12 +394,10 @@ int ob200_net_finalize(ob200_net* n) {
     }
     n->planes_capacity = MB * (size_t)std::max(c.input_channels, 19) * S2;
     if (int rc = dev_alloc(n, &n->d_planes, n->planes_capacity, false)) return rc;
-    // move histories, history lengths and sides to move of a call share one staging block (34 bytes per board,
-    // packed for the call's batch size), so that they reach the device in one copy
-    if (int rc = dev_alloc(n, &n->d_hist, MB * 17, false)) return rc;
     if (int rc = host_alloc(n, &n->h_planes, n->planes_capacity)) return rc;
     OB200_CUDA_OK(cudaStreamCreateWithFlags(&n->stream, cudaStreamNonBlocking));
     OB200_CUDA_OK(cudaStreamCreateWithFlags(&n->copy_stream, cudaStreamNonBlocking));
+    OB200_CUDA_OK(cudaStreamCreateWithFlags(&n->in_stream, cudaStreamNonBlocking));
     OB200_CUDA_OK(cudaEventCreateWithFlags(&n->planes_copied, cudaEventDisableTiming));
     OB200_CUDA_OK(cudaEventRecord(n->planes_copied, n->stream));
     OB200_CUDA_OK(cudaDeviceSynchronize());
@@ -583,12 +591,16 @@ int enqueue_gomoku(ob200_net* n, int si, const int16_t* history, const uint8_t* 
     ob200_net::Slot& sl = n->slot[si];
     const size_t hist_bytes = (size_t)B * 16 * sizeof(int16_t);
     uint8_t* h8 = reinterpret_cast<uint8_t*>(sl.h_hist);
-    uint8_t* d8 = reinterpret_cast<uint8_t*>(n->d_hist);
+    uint8_t* d8 = reinterpret_cast<uint8_t*>(sl.d_hist);
     std::memcpy(h8, history, hist_bytes);
     std::memcpy(h8 + hist_bytes, n_hist, (size_t)B);
     std::memcpy(h8 + hist_bytes + B, to_move, (size_t)B);
-    OB200_CUDA_OK(cudaMemcpyAsync(d8, h8, hist_bytes + 2 * (size_t)B, cudaMemcpyHostToDevice, n->stream));
-    const GomokuInput g{n->d_hist, d8 + hist_bytes, d8 + hist_bytes + B};
+    // the copy goes on a stream of its own, so that it runs while the batch ahead still computes; the slot's device
+    // block is free: its previous batch was waited for before the slot was handed out again
+    OB200_CUDA_OK(cudaMemcpyAsync(d8, h8, hist_bytes + 2 * (size_t)B, cudaMemcpyHostToDevice, n->in_stream));
+    OB200_CUDA_OK(cudaEventRecord(sl.hist_ready, n->in_stream));
+    OB200_CUDA_OK(cudaStreamWaitEvent(n->stream, sl.hist_ready, 0));
+    const GomokuInput g{sl.d_hist, d8 + hist_bytes, d8 + hist_bytes + B};
     if (int rc = forward_device(n, nullptr, B, sl.d_policy, sl.d_value, out_kind, n->stream, &g)) return rc;
     return enqueue_results(n, si, B, policy_out, value_out);
 }
