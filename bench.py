@@ -546,7 +546,7 @@ def gpu_arm(args):
             "config": arm_config(B, world),
             "e2e": {"value": world * B * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": B * 34,
                     "d2h_bytes_per_step": B * 226 * 4,
-                    "how": "ob200_net_submit_gomoku / ob200_net_wait with two batches in flight, pinned host buffers, wall clock over all steps",
+                    "how": "ob200_net_submit_gomoku / ob200_net_wait with two batches in flight, pinned host buffers, wall clock over all steps; every batch's inputs come from host memory and its results go back there, L2 flushed once before the first batch (one_batch_at_a_time: before every batch)",
                     "one_batch_at_a_time": world * B * K / (e2e_sync_ms * 1e-3)},
             "gpu_launches": int(launches), "counters_all_gpus": totals,
             "tower_tflops": value / world * flops_eval / 1e12,
