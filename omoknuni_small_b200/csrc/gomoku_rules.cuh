@@ -1,14 +1,11 @@
 // Which cells of a Gomoku position become children of a search node: the moves the rule set leaves the side to move
 // (freestyle, Omok, Renju: GomokuRules, src/games/gomoku/gomoku_rules.cpp) and the limits MCTSNode::expand puts on
 // the number of children (the cap and progressive widening, src/mcts/mcts_node.cpp:283-340).  Device code for one
-// warp per node on bitmaps of at most 256 cells, with the host twin of the widening choice.
+// warp per node on bitmaps of at most 256 cells.
 #pragma once
 #include "internal.h"
 #include <cuda_runtime.h>
-#include <algorithm>
 #include <cstdint>
-#include <utility>
-#include <vector>
 
 namespace ob200 {
 namespace rules {
@@ -276,21 +273,6 @@ static __device__ void widen_mask_warp(const uint32_t* empty, uint32_t* exists, 
 #pragma unroll
     for (int k = 0; k < 8; ++k)
         if (k < mask_words && lane == 0) exists[k] = w[k];
-}
-
-// The same choice on the host (the root noise is drawn for the root's children): plain loops.
-inline void widen_mask_host(const uint32_t* empty, uint32_t* exists, int n_children, int mask_words, int max_children, int target,
-                     unsigned long long seed, int id) {
-    int total = 0;
-    for (int w = 0; w < mask_words; ++w) exists[w] = 0;
-    for (int s = 0; s < n_children; ++s)
-        if (((empty[s >> 5] >> (s & 31)) & 1u) && (max_children <= 0 || total < max_children)) { exists[s >> 5] |= 1u << (s & 31); ++total; }
-    if (target <= 0 || total <= target) return;
-    std::vector<std::pair<unsigned long long, int>> ranked;
-    for (int s = 0; s < n_children; ++s)
-        if ((exists[s >> 5] >> (s & 31)) & 1u) ranked.emplace_back(widen_key(seed, id, s), s);
-    std::sort(ranked.begin(), ranked.end());
-    for (size_t r = (size_t)target; r < ranked.size(); ++r) exists[ranked[r].second >> 5] &= ~(1u << (ranked[r].second & 31));
 }
 
 }  // namespace rules

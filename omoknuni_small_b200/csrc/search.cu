@@ -45,6 +45,9 @@ struct ob200_search {
     cudaStream_t stream = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     uint64_t moves_done = 0;
+    // Gamma(alpha, 1) variates for the root noise of move number gamma_for (counted from 1): [n_trees][A]
+    std::vector<float> gamma_host, noise_host;
+    uint64_t gamma_for = 0;
     uint32_t* empty_bits = nullptr;            // [max_nodes][mask_words], only when a node's children can be fewer than its legal moves
     int max_children = 1000, widen_target = 0;
     // expansion plan of a round (per simulation)
@@ -408,6 +411,17 @@ int salloc(ob200_search* s, T** out, size_t count) {
 
 }  // namespace
 
+namespace {
+// One Gamma(alpha, 1) variate per (tree, cell) for move number `move`; a function of (seed, move) alone.
+void draw_gammas(ob200_search* s, uint64_t move) {
+    std::mt19937_64 rng(s->cfg.seed + 0x9E3779B97F4A7C15ull * move);
+    std::gamma_distribution<float> gamma(s->cfg.dirichlet_alpha, 1.0f);
+    s->gamma_host.resize((size_t)s->cfg.n_trees * s->A);
+    for (float& g : s->gamma_host) g = gamma(rng);
+    s->gamma_for = move;
+}
+}  // namespace
+
 extern "C" {
 
 int ob200_search_create(ob200_net* net, const ob200_search_config* cfg, ob200_search** out) {
@@ -576,40 +590,6 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
     // the widening ranks change from move to move
     unsigned long long wseed = c.seed + 0x632BE59BD9B4E019ull * (s->moves_done + 1);
     wseed ^= wseed >> 31; wseed *= 0xD6E8FEB86659FD93ull; wseed ^= wseed >> 32;
-    // root noise: Gamma(alpha, 1) per existing child, normalised (addDirichletNoise, :83-110)
-    std::vector<float> noise;
-    if (c.dirichlet_epsilon > 0.0f) {
-        noise.assign((size_t)T * s->pitch, 0.0f);
-        std::mt19937_64 rng(c.seed + 0x9E3779B97F4A7C15ull * (s->moves_done + 1));
-        std::gamma_distribution<float> gamma(c.dirichlet_alpha, 1.0f);
-        for (int t = 0; t < T; ++t) {
-            // one Gamma(alpha, 1) draw per child in child order, summed and divided in fp32; a zero sum gives
-            // uniform noise (src/mcts/mcts_engine_eval.cpp:83-100)
-            float* row = noise.data() + (size_t)t * s->pitch;
-            float sum = 0.0f;
-            int children = 0;
-            uint32_t empty[8], child[8];
-            for (int w = 0; w < 8; ++w) {
-                const uint32_t valid = (w + 1) * 32 <= A ? 0xFFFFFFFFu : (w * 32 >= A ? 0u : ((1u << (A - w * 32)) - 1u));
-                empty[w] = ~(stones[(size_t)t * 16 + w] | stones[(size_t)t * 16 + 8 + w]) & valid;
-                child[w] = empty[w];
-            }
-            if (c.rules == OB200_RULES_OMOK && tm[t] == 1)
-                for (int a = 0; a < A; ++a)
-                    if (((empty[a >> 5] >> (a & 31)) & 1u) && omok_forbidden(&stones[(size_t)t * 16], empty, s->S, a)) child[a >> 5] &= ~(1u << (a & 31));
-            if (s->empty_bits) {
-                uint32_t legal[8];
-                for (int w = 0; w < 8; ++w) legal[w] = child[w];
-                widen_mask_host(legal, child, A, 8, s->max_children, s->widen_target, wseed, t);
-            }
-            auto is_child = [&](int a) { return (child[a >> 5] >> (a & 31)) & 1u; };
-            for (int a = 0; a < A; ++a)
-                if (is_child(a)) { row[a] = gamma(rng); sum += row[a]; ++children; }
-            for (int a = 0; a < A; ++a)
-                if (is_child(a)) row[a] = sum > 0.0f ? row[a] / sum : 1.0f / (float)children;
-        }
-        OB200_CUDA_OK(cudaMemcpyAsync(s->noise, noise.data(), noise.size() * 4, cudaMemcpyHostToDevice, st));
-    }
     if (s->tt_size) {
         std::vector<unsigned long long> rh(T, 0ull);
         for (int t = 0; t < T; ++t) {
@@ -626,6 +606,31 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
     const Widening wd{s->empty_bits, s->empty_bits ? s->max_children : 0, s->empty_bits ? s->widen_target : 0, wseed, c.rules};
     init_roots_kernel<<<T, 128, 0, st>>>(s->tv, s->root_stones, T, s->n_used, s->term_count, wd, s->root_tm, s->S);
     OB200_LAUNCHED("init_roots_kernel");
+    // root noise: Gamma(alpha, 1) per existing child, normalised (addDirichletNoise, :83-110).  The children are what
+    // the kernel above made of the rules and the limits on children, so their masks are read back (2 KB, the GPU has
+    // nothing else to do yet); the Gamma variates of this move were drawn while the previous move ran on the GPU.
+    if (c.dirichlet_epsilon > 0.0f) {
+        std::vector<uint32_t> root_mask((size_t)T * s->mask_words);
+        OB200_CUDA_OK(cudaMemcpyAsync(root_mask.data(), s->tv.legal_bits, root_mask.size() * 4, cudaMemcpyDeviceToHost, st));
+        if (s->gamma_for != s->moves_done + 1) draw_gammas(s, s->moves_done + 1);
+        OB200_CUDA_OK(cudaStreamSynchronize(st));
+        std::vector<float>& noise = s->noise_host;
+        noise.assign((size_t)T * s->pitch, 0.0f);
+        for (int t = 0; t < T; ++t) {
+            // one variate per child in child order, summed and divided in fp32; a zero sum gives uniform noise (:83-100)
+            float* row = noise.data() + (size_t)t * s->pitch;
+            const float* g = s->gamma_host.data() + (size_t)t * A;
+            const uint32_t* child = root_mask.data() + (size_t)t * s->mask_words;
+            float sum = 0.0f;
+            int children = 0;
+            auto is_child = [&](int a) { return (child[a >> 5] >> (a & 31)) & 1u; };
+            for (int a = 0; a < A; ++a)
+                if (is_child(a)) { row[a] = g[a]; sum += row[a]; ++children; }
+            for (int a = 0; a < A; ++a)
+                if (is_child(a)) row[a] = sum > 0.0f ? row[a] / sum : 1.0f / (float)children;
+        }
+        OB200_CUDA_OK(cudaMemcpyAsync(s->noise, noise.data(), noise.size() * 4, cudaMemcpyHostToDevice, st));
+    }
     if (int rc = net_forward_gomoku_for_search(s->net, s->root_hist, s->root_nh, s->root_tm, T, s->policy, s->value, st)) return rc;
     if (int rc = ob200_launch_set_priors(&s->tv, s->roots, T, s->policy, A, nullptr, st)) return rc;
     if (s->rec_policy) {
@@ -674,6 +679,9 @@ int ob200_search_run(ob200_search* s, const int16_t* moves, const int32_t* n_mov
         OB200_CUDA_OK(mark(r, 5));
     }
     OB200_CUDA_OK(cudaEventRecord(s->ev1, st));
+    // the next move's Gamma variates, while this one runs on the GPU (the copies into pageable memory below return only
+    // when the stream has drained)
+    if (c.dirichlet_epsilon > 0.0f) draw_gammas(s, s->moves_done + 2);
     // ---- results: root visit counts -> pi (getActionProbabilities, src/mcts/mcts_engine_tree.cpp:389-465) ----
     std::vector<int32_t> rootN((size_t)T * s->pitch);
     int32_t used = 0, terms = 0;

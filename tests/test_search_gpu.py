@@ -140,9 +140,9 @@ def test_search_equals_the_oracle_on_the_same_network_outputs(net, oracle, name,
             kids = np.array([legal_of(dev["legal_bits"][k]).sum() for k in range(n)])
             most = min(limits.get("max_children", 1000), target or 1000)
             assert kids.max() == most and (kids[:T] == most).all()
-            if eps > 0:                                           # the root noise is a distribution over the root's children
-                for t in range(T):
-                    assert not noise[t, :225][~legal_of(dev["legal_bits"][t])].any() and abs(noise[t].sum() - 1) < 1e-5
+        if limits and eps > 0:                                    # the root noise is a distribution over the root's children
+            for t in range(T):
+                assert not noise[t, :225][~legal_of(dev["legal_bits"][t])].any() and abs(noise[t].sum() - 1) < 1e-5
         assert st["terminal_leaves"] == ref["terminal_leaves"]
         for key in ("legal_bits", "child_node", "N", "VL", "node_visits"):
             assert np.array_equal(dev[key][:n], ref[key][:n]), key
