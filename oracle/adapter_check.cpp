@@ -127,8 +127,32 @@ int run_direct(int argc, char** argv) {
         for (size_t i = 0; i < out.size(); ++i)
             REQUIRE(again[i].value == out[i].value && again[i].policy == out[i].policy, "inference function: state %zu differs", i);
     }
+    // several engine threads calling inference() on the same network at once, as the reference's engines do when no
+    // global queue is set up (src/mcts/mcts_engine_batch_tree_simple.cpp:231-233): every thread's results equal the
+    // single-threaded ones
+    {
+        const int n_threads = 4, rounds = 6;
+        std::atomic<int> mismatches{0};
+        std::vector<std::thread> threads;
+        for (int th = 0; th < n_threads; ++th)
+            threads.emplace_back([&, th] {
+                for (int r = 0; r < rounds; ++r) {
+                    // a different slice of the states per thread and round, sizes on both sides of max_batch
+                    const size_t first = (size_t)((th * 7 + r * 13) % (int)games.size());
+                    const size_t count = std::min(games.size() - first, (size_t)(1 + (th * 31 + r * 17) % 100));
+                    States mine;
+                    for (size_t i = 0; i < count; ++i) mine.push_back(make_state(games[first + i]));
+                    const auto got = net->inference(mine);
+                    if (got.size() != count) { mismatches++; continue; }
+                    for (size_t i = 0; i < count; ++i)
+                        if (got[i].value != out[first + i].value || got[i].policy != out[first + i].policy) mismatches++;
+                }
+            });
+        for (auto& t : threads) t.join();
+        REQUIRE(mismatches.load() == 0, "%d results of concurrent inference() calls differ from the single-threaded ones", mismatches.load());
+    }
     if (!write_out(argv[4], out)) return 5;
-    std::printf("adapter_check direct: %zu states evaluated\n", out.size());
+    std::printf("adapter_check direct: %zu states evaluated; 4 threads x 6 concurrent calls equal\n", out.size());
     return 0;
 }
 
