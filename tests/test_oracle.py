@@ -537,3 +537,41 @@ def test_renju_live_against_gomokustate(oracle):
     black6 = [0, 14, 210, 224, 1, 16]
     mv = [m for pair in zip(black6, white6) for m in pair]
     assert oracle.ref_gomoku_result_variant(mv, 15, renju=True) == oracle.gomoku_result(mv, 15, rules=2) == 2
+
+
+def test_rule_cases_of_the_reference_unit_tests(oracle):
+    """The known answers of the reference's own rule tests (tests/games/gomoku/gomoku_test.cpp:372-452 Omok,
+    :485-637 Renju): stone sets with BLACK to move and the cell whose legality the test asserts."""
+    import ctypes as C
+    L = oracle.lib()
+    i8 = np.ctypeslib.ndpointer(np.int8, flags="C_CONTIGUOUS")
+    L.oracle_omok_forbidden.argtypes = [i8, C.c_int, C.c_int]
+    L.oracle_renju_forbidden.argtypes = [i8, C.c_int, C.c_int]
+
+    def board(black, white):
+        b = np.zeros(225, np.int8)
+        for r, c in black:
+            b[r * 15 + c] = 1
+        for r, c in white:
+            b[r * 15 + c] = 2
+        return b
+    omok = [  # OmokDoubleThree{PlusShape, XShape, Corner_NE, Corner_SW, TT_W, TT_N, TT_E, TT_S}: all forbidden
+        ([(2, 3), (3, 2), (3, 4), (4, 3)], (3, 3)), ([(2, 2), (2, 4), (4, 2), (4, 4)], (3, 3)),
+        ([(1, 2), (3, 2), (2, 1), (2, 3)], (2, 2)), ([(2, 2), (2, 3), (1, 1), (3, 1)], (2, 1)),
+        ([(3, 1), (3, 2), (2, 3), (4, 3)], (3, 3)), ([(1, 3), (2, 3), (3, 2), (3, 4)], (3, 3)),
+        ([(3, 5), (3, 4), (2, 3), (4, 3)], (3, 3)), ([(5, 3), (4, 3), (3, 2), (3, 4)], (3, 3))]
+    for black, (r, c) in omok:
+        assert L.oracle_omok_forbidden(board(black, [(8, 8)]), 15, r * 15 + c) == 1, (black, r, c)
+    renju = [  # (black, white, cell, forbidden): RenjuOverlineBlack, DoubleFourBlack, SimpleDoubleThreeBlackForbidden,
+        #        DoubleThreeException_a, DoubleThreeException_b
+        ([(7, 3), (7, 4), (7, 5), (7, 6), (7, 8)], [(0, 0)], (7, 7), 1),
+        ([(2, 3), (2, 4), (2, 6), (4, 2), (4, 3), (4, 5), (4, 6)], [(7, 7)], (2, 5), 1),
+        ([(2, 3), (4, 5), (2, 5), (4, 3)], [(7, 7)], (3, 4), 1),
+        ([(2, 2), (2, 4), (4, 1), (5, 2)], [(7, 7)], (3, 3), 0),
+        ([(5, 7), (6, 7), (8, 7), (7, 5), (7, 6), (7, 8)], [(4, 7), (7, 4), (7, 9)], (7, 7), 0)]
+    for black, white, (r, c), want in renju:
+        assert L.oracle_renju_forbidden(board(black, white), 15, r * 15 + c) == want, (black, r, c)
+    # RenjuOverlineWhite / RenjuDoubleFourWhiteAllowed: WHITE is never restricted, and its six in a row wins
+    white6 = [7 * 15 + c for c in (3, 4, 5, 7, 8, 6)]
+    black6 = [0, 14, 210, 224, 1, 16]
+    assert oracle.gomoku_result([m for pair in zip(black6, white6) for m in pair], 15, rules=2) == 2
