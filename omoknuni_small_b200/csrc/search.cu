@@ -10,7 +10,9 @@
 //
 // Tree layout: one ob200_tree_view over a pool of nodes shared by all trees;
 // node t (< n_trees) is the root of tree t; a node's child slot is the board
-// cell of the move (slot == action), its existence bit says the cell is empty.
+// cell of the move (slot == action), its existence bit says the cell is a child:
+// an empty cell that the rule set allows the side to move (gomoku_rules.cuh) and
+// that survived the limits on children, when those are on.
 #include "internal.h"
 #include "gomoku_rules.cuh"
 #include <algorithm>

@@ -1,13 +1,18 @@
 // Batched PUCT selection, virtual loss, backup and prior scatter over
 // structure-of-arrays edge statistics (sm_100a).
 //
-// One warp owns one node row.  Rows are `pitch` (multiple of 4) elements, so
-// every lane issues 128-bit loads of N, W, P and VL; a 225-slot row is 57
-// vectors = two fully independent load rounds per lane.  Scores use IEEE
-// round-to-nearest intrinsics in the operation order of
-// MCTSNode::selectChild (reference src/mcts/mcts_node.cpp:143-167), so no
-// FMA contraction or fast-math can change a comparison.  The argmax is a
-// shuffle butterfly whose combine rule keeps the lowest slot on equal scores.
+// Rows are `pitch` (multiple of 4) elements.  Scores use IEEE round-to-nearest
+// intrinsics in the operation order of MCTSNode::selectChild (reference
+// src/mcts/mcts_node.cpp:143-167), so no FMA contraction or fast-math can
+// change a comparison; the kernels that bracket scores with reciprocals first
+// evaluate that expression for every slot that can hold the maximum, and the
+// combine rule keeps the lowest slot on equal scores.  Three selection kernels:
+//   puct_select_kernel            a warp per row, 128-bit loads (small launches, any width);
+//   puct_select_staged_kernel     a warp per row of up to 256 slots, rows staged in shared
+//                                 memory through per-warp rings of bulk async copies;
+//   puct_select_segmented_kernel  wider rows cut into 256-slot segments through the same rings,
+//                                 a 64-bit atomic maximum per row, puct_select_finish_kernel.
+// Then the virtual-loss kernels, backup, prior scatter, and the wavefront descent (traverse_kernel).
 #include "internal.h"
 #include <cfloat>
 #include <map>
